@@ -1,0 +1,157 @@
+/*
+ * mlcg_b200 — C ABI of the B200 (sm_100a) kernels behind mlcg's coarse-grained force-field hot path.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless the comment says "host". The library never allocates,
+ *     frees or synchronises: the caller owns inputs, outputs and workspaces and passes the stream.
+ *   - `dtype`: 0 = float32, 1 = float64 (the type of positions and of every floating tensor of a call).
+ *   - Node tensors are row-major [N, F]; edge tensors are row-major [E, F]; index rows are contiguous.
+ *   - Return value: 0 on success, a negative MLCGB_E_* code otherwise (mlcgb_strerror gives the text).
+ *     Data-dependent conditions are reported through a 4-word device `status` array the caller zeroes:
+ *     status[0] bit 0 = a centre had more neighbours than max_num_neighbors (list truncated),
+ *     status[0] bit 1 = an index was out of range and the element was skipped,
+ *     status[0] bit 2 = an edge had no reverse partner (graph not symmetric).
+ *   - `stream` is a cudaStream_t passed as void*.
+ *
+ * Each entry point names the reference interface it stands in for (path inside the mlcg repository).
+ */
+#ifndef MLCG_B200_H
+#define MLCG_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MLCGB_OK 0
+#define MLCGB_E_ARG (-1)       /* null pointer, negative size, unsupported dtype / option */
+#define MLCGB_E_WORKSPACE (-2) /* workspace too small */
+#define MLCGB_E_LAUNCH (-3)    /* the CUDA runtime refused a launch (see mlcgb_last_cuda_error) */
+#define MLCGB_E_LIMIT (-4)     /* a size is beyond what the entry point supports */
+
+#define MLCGB_F32 0
+#define MLCGB_F64 1
+
+#define MLCGB_RULE_NATIVE 0  /* mlcg_opt_radius: skip self, keep the first max_num_neighbors by index */
+#define MLCGB_RULE_CLUSTER 1 /* torch_cluster.radius_graph: max_num_neighbors+1 incl. self, self dropped */
+
+const char *mlcgb_strerror(int code);
+int mlcgb_last_cuda_error(void); /* cudaError_t of the last failed launch on this host thread */
+int mlcgb_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Radius graph.  Replaces torch_cluster.radius_graph as called at
+ * src/mlcg/neighbor_list/torch_impl.py:216-224 and mlcg::radius_cuda
+ * (src/opt_radius/mlcg_opt_radius/radius.cu:197-307).  Two calls around one host read of the edge
+ * count: `count` builds the per-structure cell lists in the workspace, writes deg[N] and the
+ * exclusive prefix sum offsets[N+1] (offsets[N] = E); `fill` writes the edges, centre-major with
+ * neighbours ascending, which is the order both reference back ends produce.
+ * The pair test is ((dx*dx + dy*dy) + dz*dz) < (T)(r*r) with every operation rounded separately.
+ * ---------------------------------------------------------------------------------------------- */
+int mlcgb_batch_to_ptr(const int64_t *batch, int64_t N, int64_t B, int64_t *ptr /* [B+1] */, void *stream);
+/* radius.py:64-75 (bucketize of arange(B+1) into the sorted batch vector). */
+
+size_t mlcgb_radius_workspace_bytes(int64_t N, int64_t B, int dtype);
+
+int mlcgb_radius_count(const void *pos /* [N,3] */, int dtype, const int64_t *ptr /* [B+1] */, int64_t N, int64_t B,
+                       double r, int64_t max_num_neighbors, int loop, int rule, void *workspace, size_t workspace_bytes,
+                       int32_t *deg /* [N] */, int64_t *offsets /* [N+1] */, int32_t *status, void *stream);
+
+int mlcgb_radius_fill(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int loop,
+                      const void *workspace, size_t workspace_bytes, const int64_t *offsets, int64_t E,
+                      int64_t *edge_index /* [2,E]: row 0 centre, row 1 neighbour */,
+                      void *distance /* [E] or NULL */, int64_t *mapping_batch /* [E] or NULL */,
+                      int32_t *row0_i32 /* [E] or NULL */, int32_t *row1_i32 /* [E] or NULL */, int32_t *status,
+                      void *stream);
+
+/* For each edge (a,b) of a centre-sorted list, the position of (b,a); -1 and status bit 2 if absent.
+ * No reference counterpart: PyG aggregates at edge_index[1] with atomics (src/mlcg/nn/schnet.py:346);
+ * this permutation is what lets the aggregation run as an ordered segmented sum instead. */
+int mlcgb_edge_twin(const int32_t *row0, const int32_t *row1, const int64_t *offsets, int64_t E, int64_t N,
+                    int32_t *twin /* [E] */, int32_t *status, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Edge geometry.  compute_distances, src/mlcg/geometry/internal_coordinates.py:72-100, split into
+ * its linear part dr = pos[row1] - pos[row0] and that part's transpose (used by every derivative).
+ * ---------------------------------------------------------------------------------------------- */
+int mlcgb_edge_diff(const void *pos /* [N,3] */, int dtype, const int32_t *row0, const int32_t *row1, int64_t E,
+                    int64_t N, void *dr /* [E,3] */, int32_t *status, void *stream);
+
+/* out[n] = sum_{k in [ptr_in[n],ptr_in[n+1])} g[perm_in ? perm_in[k] : k] - sum_{k in [ptr_out..)} g[perm_out ? ... : k]
+ * ("in" = edges whose row1 is n, "out" = edges whose row0 is n). Ordered, no atomics. */
+int mlcgb_node_scatter_diff(const void *g /* [E,3] */, int dtype, const int64_t *ptr_in, const int32_t *perm_in,
+                            const int64_t *ptr_out, const int32_t *perm_out, int64_t N, int64_t E,
+                            void *out /* [N,3] */, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Radial basis times cutoff envelope, and its derivatives with respect to the distance.
+ * GaussianBasis.forward src/mlcg/nn/radial_basis/gaussian.py:83-102, ExpNormalBasis.forward
+ * src/mlcg/nn/radial_basis/exp_normal.py:104-124, CosineCutoff.forward src/mlcg/nn/cutoff.py:110-153.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+    int kind;         /* 0 Gaussian: exp(p1[0]*(d-p0[k])^2); 1 exp-normal: exp(-p1[k]*(exp(alpha*(lower-d))-p0[k])^2) */
+    int num_rbf;      /* R */
+    int cutoff_kind;  /* 0 identity, 1 cosine */
+    int reserved;
+    double lower, upper; /* envelope bounds */
+    double alpha;        /* exp-normal only: 5/(upper-lower) */
+    const void *p0;      /* [R] offsets | means (device) */
+    const void *p1;      /* [1] coeff   | [R] betas (device) */
+} mlcgb_rbf_spec;
+
+/* out[e,k] = d^order/dd^order ( basis_k(d_e) * envelope(d_e) ), order 0..3 */
+int mlcgb_rbf_expand(const void *d /* [E] */, int dtype, int64_t E, const mlcgb_rbf_spec *spec /* host */, int order,
+                     void *out /* [E,R] */, void *stream);
+/* s[e] = sum_k G[e,k] * d^order/dd^order( basis_k * envelope )(d_e) */
+int mlcgb_rbf_contract(const void *d, const void *G /* [E,R] */, int dtype, int64_t E, const mlcgb_rbf_spec *spec,
+                       int order, void *s /* [E] */, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Continuous-filter convolution primitives.  CFConv.forward / .message, src/mlcg/nn/schnet.py:312-368:
+ * x_j = x[edge_index[0]], message x_j * W, sum at edge_index[1].  Forward, backward and double
+ * backward are all instances of these two kernels with the roles of the index rows exchanged.
+ * ---------------------------------------------------------------------------------------------- */
+/* out[n,:] = sum_{k in [ptr[n],ptr[n+1])} a[nbr[k],:] * V[eperm ? eperm[k] : k, :]   (ordered, no atomics) */
+int mlcgb_seg_mul_sum(const void *a /* [Na,F] */, const void *V /* [E,F] */, int dtype, const int64_t *ptr /* [N+1] */,
+                      const int32_t *nbr /* [E] */, const int32_t *eperm /* [E] or NULL */, int64_t N, int64_t E,
+                      int64_t F, void *out /* [N,F] */, void *stream);
+/* V[e,:] = a[ia[e],:] * b[ib[e],:] */
+int mlcgb_edge_mul(const void *a, const void *b, int dtype, const int32_t *ia, const int32_t *ib, int64_t E, int64_t F,
+                   void *V /* [E,F] */, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Filter-generating network GEMMs.  MLP([R,F,F]) built at src/mlcg/nn/schnet.py:446-450 and run by
+ * src/mlcg/nn/mlp.py:56-58 (torch.nn.Linear -> cuBLAS in the reference).  fp32/fp64 accumulate.
+ *   mode 0 (NT): C[M,N] = A[M,K] * B[N,K]^T (+ bias[N])      forward of a Linear layer
+ *   mode 1 (NN): C[M,N] = A[M,K] * B[K,N]                    gradient w.r.t. the layer input
+ *   mode 2 (TN): C[M,N] = A[K,M]^T * B[K,N]                  gradient w.r.t. the weight (K = edges)
+ * `workspace` is only used by mode 2 (split over K); size from mlcgb_gemm_workspace_bytes.
+ * ---------------------------------------------------------------------------------------------- */
+size_t mlcgb_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, int dtype);
+int mlcgb_gemm(int mode, const void *A, const void *B, const void *bias /* [N] or NULL */, int dtype, int64_t M,
+               int64_t N, int64_t K, void *C, void *workspace, size_t workspace_bytes, void *stream);
+
+/* out[b] = sum_{n in [ptr[b],ptr[b+1])} x[n]  — the per-structure energy sum, src/mlcg/nn/schnet.py:158 */
+int mlcgb_segment_sum(const void *x /* [N] */, int dtype, const int64_t *ptr /* [B+1] */, int64_t B, void *out /* [B] */,
+                      void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Prior energy terms with analytic gradients.  `kind`:
+ *   0 bond      k (d - x0)^2                       src/mlcg/nn/prior/harmonic.py:110-120,229-242
+ *   1 angle     k (cos(theta) - x0)^2              src/mlcg/nn/prior/harmonic.py:284-297
+ *   2 dihedral  v0 + sum_n k1_n sin(n phi) + k2_n cos(n phi)   src/mlcg/nn/prior/fourier_series.py:105-198
+ *   3 repulsion (sigma/d)^6                        src/mlcg/nn/prior/repulsion.py:88-140
+ * `mapping` is [order, M] int64 as the neighbour-list dictionary holds it; `params` is [P, M] with one
+ * row per parameter (bond/angle: x0,k; dihedral: v0,k1_1..k1_n,k2_1..k2_n; repulsion: sigma).
+ * energy[B] and grad[N,3] (= dE/dpos, not its negative) are ACCUMULATED into: zero them first.
+ * ---------------------------------------------------------------------------------------------- */
+int mlcgb_prior_terms(int kind, const void *pos /* [N,3] */, int dtype, const int64_t *mapping, const int64_t *mapping_batch,
+                      const void *params, int n_params, int64_t M, int64_t N, int64_t B, void *energy /* [B] */,
+                      void *grad /* [N,3] or NULL */, int32_t *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLCG_B200_H */

@@ -1,0 +1,78 @@
+"""ctypes binding of ``libmlcg_b200.so`` — the C ABI declared in ``include/mlcg_b200.h``.
+
+The library is the only compute back end of this package.  If it cannot be loaded the import of
+:mod:`mlcg_b200` still works (so CPU-only tooling can inspect the modules), but every operator call
+raises: there is no CPU or pure-torch fallback.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmlcg_b200.so")
+
+c_i64, c_int, c_dbl, c_vp, c_sz = ctypes.c_int64, ctypes.c_int, ctypes.c_double, ctypes.c_void_p, ctypes.c_size_t
+
+
+class RbfSpecStruct(ctypes.Structure):
+    """Mirror of ``mlcgb_rbf_spec``."""
+
+    _fields_ = [("kind", c_int), ("num_rbf", c_int), ("cutoff_kind", c_int), ("reserved", c_int),
+                ("lower", c_dbl), ("upper", c_dbl), ("alpha", c_dbl), ("p0", c_vp), ("p1", c_vp)]
+
+
+# name -> (restype, argtypes); one entry per symbol declared in include/mlcg_b200.h
+SIGNATURES = {
+    "mlcgb_strerror": (ctypes.c_char_p, [c_int]),
+    "mlcgb_last_cuda_error": (c_int, []),
+    "mlcgb_version": (c_int, []),
+    "mlcgb_batch_to_ptr": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp]),
+    "mlcgb_radius_workspace_bytes": (c_sz, [c_i64, c_i64, c_int]),
+    "mlcgb_radius_count": (c_int, [c_vp, c_int, c_vp, c_i64, c_i64, c_dbl, c_i64, c_int, c_int, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]),
+    "mlcgb_radius_fill": (c_int, [c_vp, c_int, c_vp, c_i64, c_i64, c_dbl, c_int, c_vp, c_sz, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "mlcgb_edge_twin": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "mlcgb_edge_diff": (c_int, [c_vp, c_int, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "mlcgb_node_scatter_diff": (c_int, [c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp]),
+    "mlcgb_rbf_expand": (c_int, [c_vp, c_int, c_i64, ctypes.POINTER(RbfSpecStruct), c_int, c_vp, c_vp]),
+    "mlcgb_rbf_contract": (c_int, [c_vp, c_vp, c_int, c_i64, ctypes.POINTER(RbfSpecStruct), c_int, c_vp, c_vp]),
+    "mlcgb_seg_mul_sum": (c_int, [c_vp, c_vp, c_int, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp]),
+    "mlcgb_edge_mul": (c_int, [c_vp, c_vp, c_int, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp]),
+    "mlcgb_gemm_workspace_bytes": (c_sz, [c_int, c_i64, c_i64, c_i64, c_int]),
+    "mlcgb_gemm": (c_int, [c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp]),
+    "mlcgb_segment_sum": (c_int, [c_vp, c_int, c_vp, c_i64, c_vp, c_vp]),
+    "mlcgb_prior_terms": (c_int, [c_int, c_vp, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
+}
+
+_lib = None
+_load_error = None
+
+
+class ExtensionMissing(RuntimeError):
+    pass
+
+
+def load():
+    """Return the loaded library or raise :class:`ExtensionMissing` (never falls back)."""
+    global _lib, _load_error
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        _load_error = f"{LIB_PATH} not found; build it with `python -m mlcg_b200.build`"
+        raise ExtensionMissing(_load_error)
+    try:
+        lib = ctypes.CDLL(LIB_PATH)
+    except OSError as exc:  # e.g. libcudart missing
+        _load_error = f"cannot load {LIB_PATH}: {exc}"
+        raise ExtensionMissing(_load_error) from exc
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means header and library disagree
+        fn.restype, fn.argtypes = res, args
+    _lib = lib
+    return lib
+
+
+def check(code: int, what: str):
+    if code != 0:
+        lib = load()
+        msg = lib.mlcgb_strerror(code).decode()
+        extra = f" (cudaError {lib.mlcgb_last_cuda_error()})" if code == -3 else ""
+        raise RuntimeError(f"mlcg_b200: {what} failed: {msg}{extra}")

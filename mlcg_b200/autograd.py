@@ -1,0 +1,276 @@
+"""Differentiable operators built on the kernel primitives.
+
+Force matching differentiates the forces (themselves a gradient) with respect to the weights, so
+every operator's backward must again be differentiable (``create_graph=self.training`` at
+``src/mlcg/nn/gradients.py:216-222``).  The operators below are closed under differentiation: the
+backward of each one is written with operators of the same family, the same way the reference's
+native distance op chains ``RadiusDistanceAGF`` -> ``RadiusDistanceAGB``
+(``src/opt_radius/mlcg_opt_radius/radius.py:91-158``), so derivatives of any order come out of
+autograd without further code.
+
+Bilinear family on a fixed edge list (row 0 = centre, row 1 = neighbour)::
+
+    SegIn (a, V)[n] = sum_{e: row1(e)=n} a[row0(e)] * V[e]      CFConv aggregation, schnet.py:346,350-368
+    SegOut(a, V)[m] = sum_{e: row0(e)=m} a[row1(e)] * V[e]      its transpose
+    EdgeMul(a, b)[e] = a[row0(e)] * b[row1(e)]
+"""
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .backend import RbfSpec, get_backend
+
+
+@dataclass
+class EdgePlan:
+    """Index structures derived once per edge list and shared by every operator and derivative order."""
+
+    N: int
+    E: int
+    row0: torch.Tensor                 # int32 [E]
+    row1: torch.Tensor                 # int32 [E]
+    ptr_out: torch.Tensor              # int64 [N+1]  edges grouped by row0
+    perm_out: Optional[torch.Tensor]   # int32 [E] edge ids in that grouping; None = edges already in this order
+    nbr_out: torch.Tensor              # int32 [E]  row1 in that grouping
+    ptr_in: torch.Tensor               # int64 [N+1]  edges grouped by row1
+    perm_in: torch.Tensor              # int32 [E]
+    nbr_in: torch.Tensor               # int32 [E]  row0 in that grouping
+    symmetric: bool = False            # every edge has its reverse, and perm_in maps an edge to it
+
+    @staticmethod
+    def from_centre_sorted(row0, row1, offsets, N, symmetric: bool) -> "EdgePlan":
+        """Edges sorted by (row0, row1) as the radius graph emits them."""
+        be = get_backend()
+        E = row0.numel()
+        if symmetric:
+            twin, _ = be.edge_twin(row0, row1, offsets, N)
+            # the k-th edge grouped by row1 is the reverse of the k-th edge grouped by row0
+            return EdgePlan(N, E, row0, row1, offsets, None, row1, offsets, twin, row1, True)
+        return EdgePlan._general(row0, row1, N, ptr_out=offsets, perm_out=None)
+
+    @staticmethod
+    def from_edge_index(edge_index: torch.Tensor, N: int) -> "EdgePlan":
+        """Any ``[2, E]`` edge list (torch sort / bincount; not the fast path)."""
+        row0 = edge_index[0].to(torch.int32).contiguous()
+        row1 = edge_index[1].to(torch.int32).contiguous()
+        E = row0.numel()
+        ordered = bool((row0[1:] >= row0[:-1]).all()) if E > 1 else True
+        ptr_out = _ptr_from_index(row0, N)
+        perm_out = None if ordered else torch.argsort(row0.to(torch.int64), stable=True).to(torch.int32)
+        return EdgePlan._general(row0, row1, N, ptr_out, perm_out)
+
+    @staticmethod
+    def _general(row0, row1, N, ptr_out, perm_out) -> "EdgePlan":
+        perm_in = torch.argsort(row1.to(torch.int64), stable=True).to(torch.int32)
+        nbr_in = row0[perm_in.long()].contiguous()
+        nbr_out = row1 if perm_out is None else row1[perm_out.long()].contiguous()
+        return EdgePlan(N, row0.numel(), row0, row1, ptr_out, perm_out, nbr_out, _ptr_from_index(row1, N), perm_in, nbr_in, False)
+
+
+def _ptr_from_index(idx: torch.Tensor, N: int) -> torch.Tensor:
+    counts = torch.bincount(idx.to(torch.int64), minlength=N)
+    ptr = torch.zeros(N + 1, dtype=torch.int64, device=idx.device)
+    torch.cumsum(counts, 0, out=ptr[1:])
+    return ptr
+
+
+def attach_plan(edge_index: torch.Tensor, plan: EdgePlan) -> torch.Tensor:
+    edge_index._mlcgb_plan = plan
+    return edge_index
+
+
+def plan_of(edge_index: torch.Tensor, N: int) -> EdgePlan:
+    """The plan travelling with an edge list built by this package, else one derived on the spot."""
+    plan = getattr(edge_index, "_mlcgb_plan", None)
+    if plan is None or plan.N != N or plan.E != edge_index.shape[1]:
+        plan = EdgePlan.from_edge_index(edge_index, N)
+        edge_index._mlcgb_plan = plan
+    return plan
+
+
+# ------------------------------------------------------------------------------- bilinear family
+class SegIn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, V, plan: EdgePlan, v_symmetric: bool = False):
+        ctx.plan = plan
+        ctx.save_for_backward(a, V)
+        be = get_backend()
+        if v_symmetric and plan.symmetric:
+            # V[e] == V[reverse(e)] bit for bit (it depends on the distance only), so the grouping by
+            # row1 can be read as the grouping by row0 and V is streamed in storage order
+            return be.seg_mul_sum(a, V, plan.ptr_out, plan.nbr_out, plan.perm_out, plan.N)
+        return be.seg_mul_sum(a, V, plan.ptr_in, plan.nbr_in, plan.perm_in, plan.N)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, V = ctx.saved_tensors
+        ga = SegOut.apply(g, V, ctx.plan) if ctx.needs_input_grad[0] else None
+        gV = EdgeMul.apply(a, g, ctx.plan) if ctx.needs_input_grad[1] else None
+        return ga, gV, None, None
+
+
+class SegOut(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, V, plan: EdgePlan):
+        ctx.plan = plan
+        ctx.save_for_backward(a, V)
+        return get_backend().seg_mul_sum(a, V, plan.ptr_out, plan.nbr_out, plan.perm_out, plan.N)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, V = ctx.saved_tensors
+        ga = SegIn.apply(g, V, ctx.plan) if ctx.needs_input_grad[0] else None
+        gV = EdgeMul.apply(g, a, ctx.plan) if ctx.needs_input_grad[1] else None
+        return ga, gV, None
+
+
+class EdgeMul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, plan: EdgePlan):
+        ctx.plan = plan
+        ctx.save_for_backward(a, b)
+        return get_backend().edge_mul(a, b, plan.row0, plan.row1)
+
+    @staticmethod
+    def backward(ctx, gV):
+        a, b = ctx.saved_tensors
+        ga = SegOut.apply(b, gV, ctx.plan) if ctx.needs_input_grad[0] else None
+        gb = SegIn.apply(a, gV, ctx.plan) if ctx.needs_input_grad[1] else None
+        return ga, gb, None
+
+
+# ------------------------------------------------------------------------------- edge geometry
+class EdgeDiff(torch.autograd.Function):
+    """dr[e] = pos[row1(e)] - pos[row0(e)] (internal_coordinates.py:93-96, no cell shifts)."""
+
+    @staticmethod
+    def forward(ctx, pos, plan: EdgePlan):
+        ctx.plan = plan
+        return get_backend().edge_diff(pos, plan.row0, plan.row1)
+
+    @staticmethod
+    def backward(ctx, g):
+        return NodeScatterDiff.apply(g, ctx.plan), None
+
+
+class NodeScatterDiff(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g, plan: EdgePlan):
+        ctx.plan = plan
+        return get_backend().node_scatter_diff(g, plan.ptr_in, plan.perm_in, plan.ptr_out, plan.perm_out, plan.N)
+
+    @staticmethod
+    def backward(ctx, gg):
+        return EdgeDiff.apply(gg, ctx.plan), None
+
+
+def edge_distances(pos: torch.Tensor, plan: EdgePlan) -> torch.Tensor:
+    return EdgeDiff.apply(pos, plan).norm(p=2, dim=1)
+
+
+# ------------------------------------------------------------------------------- radial basis
+MAX_RBF_ORDER = 3
+
+
+class RbfExpand(torch.autograd.Function):
+    """``order``-th distance derivative of basis x envelope, ``[E, R]``."""
+
+    @staticmethod
+    def forward(ctx, d, spec: RbfSpec, order: int):
+        if order > MAX_RBF_ORDER:
+            raise NotImplementedError("radial-basis derivatives beyond third order are not implemented")
+        ctx.spec, ctx.order = spec, order
+        ctx.save_for_backward(d)
+        return get_backend().rbf_expand(d, spec, order)
+
+    @staticmethod
+    def backward(ctx, G):
+        (d,) = ctx.saved_tensors
+        return RbfContract.apply(d, G, ctx.spec, ctx.order + 1), None, None
+
+
+class RbfContract(torch.autograd.Function):
+    """s[e] = sum_k G[e,k] * d^order(basis_k x envelope)/dd^order."""
+
+    @staticmethod
+    def forward(ctx, d, G, spec: RbfSpec, order: int):
+        if order > MAX_RBF_ORDER:
+            raise NotImplementedError("radial-basis derivatives beyond third order are not implemented")
+        ctx.spec, ctx.order = spec, order
+        ctx.save_for_backward(d, G)
+        return get_backend().rbf_contract(d, G, spec, order)
+
+    @staticmethod
+    def backward(ctx, gs):
+        d, G = ctx.saved_tensors
+        gd = gs * RbfContract.apply(d, G, ctx.spec, ctx.order + 1) if ctx.needs_input_grad[0] else None
+        gG = gs.unsqueeze(-1) * RbfExpand.apply(d, ctx.spec, ctx.order) if ctx.needs_input_grad[1] else None
+        return gd, gG, None, None
+
+
+# ------------------------------------------------------------------------------- GEMM family
+class MatmulNT(torch.autograd.Function):
+    """Y = X W^T (+ bias): ``torch.nn.Linear`` as the filter network applies it (mlp.py:41-58)."""
+
+    @staticmethod
+    def forward(ctx, X, W, bias=None):
+        ctx.save_for_backward(X, W)
+        ctx.has_bias = bias is not None
+        return get_backend().gemm(0, X, W, bias)
+
+    @staticmethod
+    def backward(ctx, gY):
+        X, W = ctx.saved_tensors
+        gX = MatmulNN.apply(gY, W) if ctx.needs_input_grad[0] else None
+        gW = MatmulTN.apply(gY, X) if ctx.needs_input_grad[1] else None
+        gb = gY.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return gX, gW, gb
+
+
+class MatmulNN(torch.autograd.Function):
+    """Z = G W."""
+
+    @staticmethod
+    def forward(ctx, G, W):
+        ctx.save_for_backward(G, W)
+        return get_backend().gemm(1, G, W)
+
+    @staticmethod
+    def backward(ctx, gZ):
+        G, W = ctx.saved_tensors
+        gG = MatmulNT.apply(gZ, W) if ctx.needs_input_grad[0] else None
+        gW = MatmulTN.apply(G, gZ) if ctx.needs_input_grad[1] else None
+        return gG, gW
+
+
+class MatmulTN(torch.autograd.Function):
+    """P = G^T X (contraction over the edge dimension)."""
+
+    @staticmethod
+    def forward(ctx, G, X):
+        ctx.save_for_backward(G, X)
+        return get_backend().gemm(2, G, X)
+
+    @staticmethod
+    def backward(ctx, gP):
+        G, X = ctx.saved_tensors
+        gG = MatmulNT.apply(X, gP) if ctx.needs_input_grad[0] else None
+        gX = MatmulNN.apply(G, gP) if ctx.needs_input_grad[1] else None
+        return gG, gX
+
+
+# ------------------------------------------------------------------------------- per-structure sum
+class SegmentSum(torch.autograd.Function):
+    """out[b] = sum of x over the nodes of structure b (``scatter(energy, batch)``, schnet.py:158)."""
+
+    @staticmethod
+    def forward(ctx, x, ptr, batch):
+        ctx.save_for_backward(batch)
+        ctx.shape = x.shape
+        return get_backend().segment_sum(x.reshape(-1), ptr)
+
+    @staticmethod
+    def backward(ctx, g):
+        (batch,) = ctx.saved_tensors
+        return g.index_select(0, batch).reshape(ctx.shape), None, None

@@ -1,0 +1,76 @@
+// Shared helpers for the sm_100a kernels of mlcg_b200.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/mlcg_b200.h"
+
+namespace mlcgb {
+
+constexpr int kNumSM = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+
+enum StatusBits : int { kTruncated = 1, kBadIndex = 2, kAsymmetric = 4 };
+
+extern thread_local int g_last_cuda_error;
+
+inline int check_launch() {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        return MLCGB_E_LAUNCH;
+    }
+    return MLCGB_OK;
+}
+
+inline int grid_for(int64_t work_items, int per_block, int max_waves = 64) {
+    int64_t blocks = (work_items + per_block - 1) / per_block;
+    int64_t cap = (int64_t)kNumSM * max_waves;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+template <typename T> struct Vec4;
+template <> struct Vec4<float> { using type = float4; };
+template <> struct Vec4<double> { using type = double4; };
+
+// Explicitly rounded arithmetic: the pair test must not be contracted into fused multiply-adds,
+// so that the host oracle (compiled with -ffp-contract=off) takes the same decision bit for bit.
+__device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
+__device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
+__device__ __forceinline__ float sub_rn(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ double sub_rn(double a, double b) { return __dsub_rn(a, b); }
+
+template <typename T>
+__device__ __forceinline__ T dist2_rn(T xi, T yi, T zi, T xj, T yj, T zj) {
+    const T dx = sub_rn(xj, xi), dy = sub_rn(yj, yi), dz = sub_rn(zj, zi);
+    return add_rn(add_rn(mul_rn(dx, dx), mul_rn(dy, dy)), mul_rn(dz, dz));
+}
+
+__device__ __forceinline__ unsigned lanemask_lt() {
+    unsigned m;
+    asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+    return m;
+}
+
+template <typename T>
+__device__ __forceinline__ T warp_sum(T v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+}  // namespace mlcgb
+
+#define MLCGB_DISPATCH_DTYPE(dtype, ...)                     \
+    [&]() -> int {                                           \
+        if ((dtype) == MLCGB_F32) {                          \
+            using scalar_t = float;                          \
+            return __VA_ARGS__();                            \
+        } else if ((dtype) == MLCGB_F64) {                   \
+            using scalar_t = double;                         \
+            return __VA_ARGS__();                            \
+        }                                                    \
+        return MLCGB_E_ARG;                                  \
+    }()

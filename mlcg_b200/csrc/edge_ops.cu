@@ -1,0 +1,259 @@
+// Gather / segmented-sum primitives of the continuous-filter convolution and of the edge geometry.
+//
+// All of them are bandwidth kernels: an [E,F] edge tensor is streamed once with 128-bit loads
+// (one warp covers a 512-byte row when F = 128), node rows are gathered (they stay L2-resident:
+// N*F*4 bytes is a few tens of MB), and sums run over a CSR segment in edge order, so results are
+// reproducible run to run and no atomics are issued.
+#include "common.cuh"
+
+namespace mlcgb {
+
+template <typename T> struct VecIO;
+template <> struct VecIO<float> {
+    using V = float4;
+    static constexpr int W = 4;
+};
+template <> struct VecIO<double> {
+    using V = double2;
+    static constexpr int W = 2;
+};
+
+__device__ __forceinline__ float4 vmul(const float4 &a, const float4 &b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+__device__ __forceinline__ double2 vmul(const double2 &a, const double2 &b) { return make_double2(a.x * b.x, a.y * b.y); }
+__device__ __forceinline__ void vfma(float4 &acc, const float4 &a, const float4 &b) {
+    acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y); acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
+}
+__device__ __forceinline__ void vfma(double2 &acc, const double2 &a, const double2 &b) {
+    acc.x = fma(a.x, b.x, acc.x); acc.y = fma(a.y, b.y, acc.y);
+}
+__device__ __forceinline__ float4 vzero(float4 *) { return make_float4(0.f, 0.f, 0.f, 0.f); }
+__device__ __forceinline__ double2 vzero(double2 *) { return make_double2(0.0, 0.0); }
+
+// streaming (evict-first) load for edge tensors that are read exactly once
+__device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
+__device__ __forceinline__ double2 ld_stream(const double2 *p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4 *p, const float4 &v) { __stcs(p, v); }
+__device__ __forceinline__ void st_stream(double2 *p, const double2 &v) { __stcs(p, v); }
+
+// ------------------------------------------------------------------------------- seg_mul_sum
+// One group of G lanes per destination row; G*W elements per pass over the feature dimension.
+template <typename T, int G, bool VEC>
+__global__ void __launch_bounds__(256)
+seg_mul_sum_kernel(const T *__restrict__ a, const T *__restrict__ V, const int64_t *__restrict__ ptr,
+                   const int32_t *__restrict__ nbr, const int32_t *__restrict__ eperm, int64_t N, int64_t F,
+                   T *__restrict__ out) {
+    using VT = typename VecIO<T>::V;
+    constexpr int W = VEC ? VecIO<T>::W : 1;
+    const int gl = threadIdx.x % G;
+    const int64_t group = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+    const int64_t ngroups = ((int64_t)gridDim.x * blockDim.x) / G;
+    const int64_t Fv = F / W;  // vectors per row
+    for (int64_t n = group; n < N; n += ngroups) {
+        const int64_t k0 = ptr[n], k1 = ptr[n + 1];
+        for (int64_t c = gl; c < Fv; c += G) {
+            if (VEC) {
+                VT acc0 = vzero((VT *)nullptr), acc1 = vzero((VT *)nullptr);
+                int64_t k = k0;
+                for (; k + 3 < k1; k += 4) {  // four edges in flight per lane
+                    int64_t e[4];
+                    int32_t j[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) { j[u] = nbr[k + u]; e[u] = eperm ? (int64_t)eperm[k + u] : k + u; }
+                    VT v[4], x[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        v[u] = ld_stream(reinterpret_cast<const VT *>(V + e[u] * F) + c);
+                        x[u] = __ldg(reinterpret_cast<const VT *>(a + (int64_t)j[u] * F) + c);
+                    }
+                    vfma(acc0, x[0], v[0]);
+                    vfma(acc1, x[1], v[1]);
+                    vfma(acc0, x[2], v[2]);
+                    vfma(acc1, x[3], v[3]);
+                }
+                for (; k < k1; k++) {
+                    const int64_t e = eperm ? (int64_t)eperm[k] : k;
+                    const VT v = ld_stream(reinterpret_cast<const VT *>(V + e * F) + c);
+                    const VT x = __ldg(reinterpret_cast<const VT *>(a + (int64_t)nbr[k] * F) + c);
+                    vfma(acc0, x, v);
+                }
+                VT r;
+                if constexpr (sizeof(T) == 4) {
+                    r = make_float4(acc0.x + acc1.x, acc0.y + acc1.y, acc0.z + acc1.z, acc0.w + acc1.w);
+                } else {
+                    r = make_double2(acc0.x + acc1.x, acc0.y + acc1.y);
+                }
+                reinterpret_cast<VT *>(out + n * F)[c] = r;
+            } else {
+                T acc = T(0);
+                for (int64_t k = k0; k < k1; k++) {
+                    const int64_t e = eperm ? (int64_t)eperm[k] : k;
+                    acc = fma(a[(int64_t)nbr[k] * F + c], V[e * F + c], acc);
+                }
+                out[n * F + c] = acc;
+            }
+        }
+    }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+edge_mul_kernel(const T *__restrict__ a, const T *__restrict__ b, const int32_t *__restrict__ ia,
+                const int32_t *__restrict__ ib, int64_t E, int64_t F, T *__restrict__ V) {
+    using VT = typename VecIO<T>::V;
+    constexpr int W = VEC ? VecIO<T>::W : 1;
+    const int64_t Fv = F / W;
+    const int64_t total = E * Fv;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e = t / Fv, c = t - e * Fv;
+        if (VEC) {
+            const VT x = __ldg(reinterpret_cast<const VT *>(a + (int64_t)ia[e] * F) + c);
+            const VT y = __ldg(reinterpret_cast<const VT *>(b + (int64_t)ib[e] * F) + c);
+            st_stream(reinterpret_cast<VT *>(V + e * F) + c, vmul(x, y));
+        } else {
+            V[e * F + c] = a[(int64_t)ia[e] * F + c] * b[(int64_t)ib[e] * F + c];
+        }
+    }
+}
+
+// --------------------------------------------------------------------------------- edge geometry
+template <typename T>
+__global__ void edge_diff_kernel(const T *__restrict__ pos, const int32_t *__restrict__ row0,
+                                 const int32_t *__restrict__ row1, int64_t E, int64_t N, T *__restrict__ dr,
+                                 int32_t *__restrict__ status) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t a = row0[e], b = row1[e];
+        if (a < 0 || a >= N || b < 0 || b >= N) {
+            atomicOr(status, (int)kBadIndex);
+            dr[e * 3] = dr[e * 3 + 1] = dr[e * 3 + 2] = T(0);
+            continue;
+        }
+#pragma unroll
+        for (int c = 0; c < 3; c++) dr[e * 3 + c] = pos[b * 3 + c] - pos[a * 3 + c];
+    }
+}
+
+// one warp per node; lanes stride over the node's edges, fixed-shape shuffle reduction
+template <typename T>
+__global__ void __launch_bounds__(256)
+node_scatter_diff_kernel(const T *__restrict__ g, const int64_t *__restrict__ ptr_in, const int32_t *__restrict__ perm_in,
+                         const int64_t *__restrict__ ptr_out, const int32_t *__restrict__ perm_out, int64_t N,
+                         T *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t n = warp; n < N; n += nwarps) {
+        T s0 = T(0), s1 = T(0), s2 = T(0);
+        for (int64_t k = ptr_in[n] + lane; k < ptr_in[n + 1]; k += 32) {
+            const int64_t e = perm_in ? (int64_t)perm_in[k] : k;
+            s0 += g[e * 3]; s1 += g[e * 3 + 1]; s2 += g[e * 3 + 2];
+        }
+        for (int64_t k = ptr_out[n] + lane; k < ptr_out[n + 1]; k += 32) {
+            const int64_t e = perm_out ? (int64_t)perm_out[k] : k;
+            s0 -= g[e * 3]; s1 -= g[e * 3 + 1]; s2 -= g[e * 3 + 2];
+        }
+        s0 = warp_sum(s0); s1 = warp_sum(s1); s2 = warp_sum(s2);
+        if (lane == 0) { out[n * 3] = s0; out[n * 3 + 1] = s1; out[n * 3 + 2] = s2; }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+segment_sum_kernel(const T *__restrict__ x, const int64_t *__restrict__ ptr, int64_t B, T *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t b = warp; b < B; b += nwarps) {
+        T s = T(0);
+        for (int64_t k = ptr[b] + lane; k < ptr[b + 1]; k += 32) s += x[k];
+        s = warp_sum(s);
+        if (lane == 0) out[b] = s;
+    }
+}
+
+template <typename T>
+static int seg_mul_sum_launch(const void *a, const void *V, const int64_t *ptr, const int32_t *nbr, const int32_t *eperm,
+                              int64_t N, int64_t F, void *out, cudaStream_t st) {
+    constexpr int W = VecIO<T>::W;
+    const bool vec = (F % W == 0) && ((uintptr_t)a % 16 == 0) && ((uintptr_t)V % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    const int64_t Fv = vec ? F / W : F;
+    int G = 32;
+    while (G > 1 && G / 2 >= Fv) G /= 2;  // smallest power of two >= Fv, capped at a warp
+    const int grid = grid_for(N * G, 256, 16);
+#define LAUNCH(GG)                                                                                                           \
+    if (vec) seg_mul_sum_kernel<T, GG, true><<<grid, 256, 0, st>>>((const T *)a, (const T *)V, ptr, nbr, eperm, N, F, (T *)out); \
+    else seg_mul_sum_kernel<T, GG, false><<<grid, 256, 0, st>>>((const T *)a, (const T *)V, ptr, nbr, eperm, N, F, (T *)out)
+    switch (G) {
+        case 32: LAUNCH(32); break;
+        case 16: LAUNCH(16); break;
+        case 8: LAUNCH(8); break;
+        case 4: LAUNCH(4); break;
+        case 2: LAUNCH(2); break;
+        default: LAUNCH(1); break;
+    }
+#undef LAUNCH
+    return check_launch();
+}
+
+}  // namespace mlcgb
+
+using namespace mlcgb;
+
+extern "C" {
+
+int mlcgb_seg_mul_sum(const void *a, const void *V, int dtype, const int64_t *ptr, const int32_t *nbr, const int32_t *eperm,
+                      int64_t N, int64_t E, int64_t F, void *out, void *stream) {
+    if (N < 0 || E < 0 || F <= 0) return MLCGB_E_ARG;
+    if (N == 0) return MLCGB_OK;
+    if (!ptr || !out || (E > 0 && (!a || !V || !nbr))) return MLCGB_E_ARG;
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] { return seg_mul_sum_launch<scalar_t>(a, V, ptr, nbr, eperm, N, F, out, (cudaStream_t)stream); });
+}
+
+int mlcgb_edge_mul(const void *a, const void *b, int dtype, const int32_t *ia, const int32_t *ib, int64_t E, int64_t F, void *V,
+                   void *stream) {
+    if (E < 0 || F <= 0) return MLCGB_E_ARG;
+    if (E == 0) return MLCGB_OK;
+    if (!a || !b || !ia || !ib || !V) return MLCGB_E_ARG;
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        constexpr int W = VecIO<scalar_t>::W;
+        const bool vec = (F % W == 0) && ((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)V % 16 == 0);
+        const int64_t work = E * (vec ? F / W : F);
+        const int grid = grid_for(work, 256, 32);
+        if (vec) edge_mul_kernel<scalar_t, true><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)b, ia, ib, E, F, (scalar_t *)V);
+        else edge_mul_kernel<scalar_t, false><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)b, ia, ib, E, F, (scalar_t *)V);
+        return check_launch();
+    });
+}
+
+int mlcgb_edge_diff(const void *pos, int dtype, const int32_t *row0, const int32_t *row1, int64_t E, int64_t N, void *dr,
+                    int32_t *status, void *stream) {
+    if (E < 0 || N < 0 || !status) return MLCGB_E_ARG;
+    if (E == 0) return MLCGB_OK;
+    if (!pos || !row0 || !row1 || !dr) return MLCGB_E_ARG;
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        edge_diff_kernel<scalar_t><<<grid_for(E, 256), 256, 0, (cudaStream_t)stream>>>((const scalar_t *)pos, row0, row1, E, N, (scalar_t *)dr, status);
+        return check_launch();
+    });
+}
+
+int mlcgb_node_scatter_diff(const void *g, int dtype, const int64_t *ptr_in, const int32_t *perm_in, const int64_t *ptr_out,
+                            const int32_t *perm_out, int64_t N, int64_t E, void *out, void *stream) {
+    if (N < 0 || E < 0) return MLCGB_E_ARG;
+    if (N == 0) return MLCGB_OK;
+    if (!ptr_in || !ptr_out || !out || (E > 0 && !g)) return MLCGB_E_ARG;
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        node_scatter_diff_kernel<scalar_t><<<grid_for(N * 32, 256), 256, 0, (cudaStream_t)stream>>>((const scalar_t *)g, ptr_in, perm_in, ptr_out, perm_out, N, (scalar_t *)out);
+        return check_launch();
+    });
+}
+
+int mlcgb_segment_sum(const void *x, int dtype, const int64_t *ptr, int64_t B, void *out, void *stream) {
+    if (B < 0) return MLCGB_E_ARG;
+    if (B == 0) return MLCGB_OK;
+    if (!x || !ptr || !out) return MLCGB_E_ARG;
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        segment_sum_kernel<scalar_t><<<grid_for(B * 32, 256), 256, 0, (cudaStream_t)stream>>>((const scalar_t *)x, ptr, B, (scalar_t *)out);
+        return check_launch();
+    });
+}
+
+}  // extern "C"

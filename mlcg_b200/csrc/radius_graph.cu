@@ -1,0 +1,529 @@
+// Radius graph for batches of independent structures (non-periodic), sm_100a.
+//
+// Output contract (same as torch_cluster.radius_graph(flow="target_to_source") and mlcg::radius_cuda):
+// edges (centre i, neighbour j), both in the same structure, squared distance strictly below r*r,
+// centre-major with neighbours in ascending index order, at most max_num_neighbors per centre.
+//
+// Plan:  build_cells (one CTA per large structure: bounding box, cell grid, counting sort of the
+//        points by cell, all counters in shared memory)
+//     -> neighbours<COUNT> (one warp per centre, 3x3 rows of cells, each row a contiguous run of
+//        cell-sorted points; small structures scan all their points instead)
+//     -> exclusive scan of the degrees (three small kernels, no spin-waits)
+//     -> [host reads E] -> neighbours<FILL> (same walk; hits are marked in a per-warp bitmask in
+//        shared memory indexed by local point index, then emitted in ascending order, which gives
+//        the canonical order without a sort).
+#include "common.cuh"
+
+namespace mlcgb {
+
+constexpr int kBruteMax = 384;     // structures up to this size scan all their points
+constexpr int kSmemCells = 8192;   // upper bound on cells per structure (shared-memory counters)
+constexpr int kNbrWarps = 8;       // warps per CTA in the neighbour kernels
+constexpr int kCapBits = 8192;     // bitmask window per warp (local point indices per pass)
+constexpr int kBuildThreads = 512;
+constexpr int kScanBlock = 1024;
+
+struct CellParam { int gx, gy, gz, use_cells; };
+
+template <typename T> using V4 = typename Vec4<T>::type;
+
+__device__ __forceinline__ int idx_of(const float4 &p) { return __float_as_int(p.w); }
+__device__ __forceinline__ int idx_of(const double4 &p) { return (int)__double_as_longlong(p.w); }
+__device__ __forceinline__ float4 make_v4(float x, float y, float z, int i) { return make_float4(x, y, z, __int_as_float(i)); }
+__device__ __forceinline__ double4 make_v4(double x, double y, double z, int i) {
+    return make_double4(x, y, z, __longlong_as_double((long long)i));
+}
+
+struct WsLayout {
+    size_t spos, cellparam, cell_of, cell_start, bsum, total;
+};
+static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+static WsLayout ws_layout(int64_t N, int64_t B, int dtype) {
+    WsLayout L;
+    size_t v4 = dtype == MLCGB_F64 ? 32 : 16;
+    size_t o = 0;
+    L.spos = o;        o += align256((size_t)N * v4);
+    L.cellparam = o;   o += align256((size_t)B * sizeof(CellParam));
+    L.cell_of = o;     o += align256((size_t)N * 4);
+    L.cell_start = o;  o += align256((size_t)(N + B) * 4);
+    L.bsum = o;        o += align256((size_t)((N + kScanBlock - 1) / kScanBlock + 1) * 8);
+    L.total = o;
+    return L;
+}
+
+// ------------------------------------------------------------------------------------------ build
+template <typename T>
+__global__ void __launch_bounds__(kBuildThreads)
+build_cells_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, T rcut,
+                   V4<T> *__restrict__ spos, CellParam *__restrict__ cellparam, int32_t *__restrict__ cell_of,
+                   int32_t *__restrict__ cell_start) {
+    __shared__ int counts[kSmemCells + 1];
+    __shared__ T red[6][kBuildThreads / 32];
+    __shared__ T s_org[3];
+    __shared__ T s_invh;
+    __shared__ int s_g[3];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    for (int64_t b = blockIdx.x; b < B; b += gridDim.x) {
+        const int64_t lo = ptr[b];
+        const int64_t n64 = ptr[b + 1] - lo;
+        if (n64 <= kBruteMax) {
+            if (tid == 0) cellparam[b] = CellParam{0, 0, 0, 0};
+            continue;
+        }
+        const int n = (int)n64;
+        // bounding box
+        T mn[3] = {T(INFINITY), T(INFINITY), T(INFINITY)}, mx[3] = {T(-INFINITY), T(-INFINITY), T(-INFINITY)};
+        for (int i = tid; i < n; i += kBuildThreads)
+#pragma unroll
+            for (int a = 0; a < 3; a++) {
+                const T v = pos[(lo + i) * 3 + a];
+                mn[a] = fmin(mn[a], v);
+                mx[a] = fmax(mx[a], v);
+            }
+#pragma unroll
+        for (int a = 0; a < 3; a++) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                mn[a] = fmin(mn[a], __shfl_xor_sync(0xffffffffu, mn[a], o));
+                mx[a] = fmax(mx[a], __shfl_xor_sync(0xffffffffu, mx[a], o));
+            }
+            if (lane == 0) { red[a][warp] = mn[a]; red[3 + a][warp] = mx[a]; }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            double lo3[3], ext[3], extmax = 0.0;
+            bool finite = true;
+            for (int a = 0; a < 3; a++) {
+                T m0 = red[a][0], m1 = red[3 + a][0];
+                for (int w = 1; w < kBuildThreads / 32; w++) { m0 = fmin(m0, red[a][w]); m1 = fmax(m1, red[3 + a][w]); }
+                lo3[a] = (double)m0;
+                ext[a] = (double)m1 - (double)m0;
+                if (!(ext[a] >= 0.0) || !isfinite(ext[a]) || !isfinite(lo3[a])) finite = false;
+                if (ext[a] > extmax) extmax = ext[a];
+            }
+            int g[3] = {1, 1, 1};
+            double h = 1.0;
+            if (finite && rcut > T(0)) {
+                // Cell edge: the cutoff plus a margin that covers every rounding between the
+                // pair test and the cell assignment, so that a pair passing the test always
+                // sits in adjacent cells.
+                h = (double)rcut * 1.001 + extmax * 1e-6 + 1e-30;
+                const int maxcells = n < kSmemCells ? n : kSmemCells;
+                for (int it = 0; it < 64; it++) {
+                    double prod = 1.0;
+                    for (int a = 0; a < 3; a++) {
+                        double ga = floor(ext[a] / h) + 1.0;
+                        g[a] = ga > 2000000.0 ? 2000000 : (int)ga;
+                        prod *= ga;
+                    }
+                    if (prod <= (double)maxcells) break;
+                    h *= 1.2599210498948732;  // cbrt(2): halve the cell count per step
+                }
+                if ((double)g[0] * g[1] * g[2] > (double)maxcells) { g[0] = g[1] = g[2] = 1; }
+            } else if (!finite) {
+                lo3[0] = lo3[1] = lo3[2] = 0.0;
+            }
+            for (int a = 0; a < 3; a++) { s_org[a] = (T)lo3[a]; s_g[a] = g[a]; }
+            s_invh = (T)(1.0 / h);
+            cellparam[b] = CellParam{g[0], g[1], g[2], 1};
+        }
+        __syncthreads();
+        const int gx = s_g[0], gy = s_g[1], gz = s_g[2];
+        const int ncell = gx * gy * gz;
+        for (int c = tid; c <= ncell; c += kBuildThreads) counts[c] = 0;
+        __syncthreads();
+        const T ox = s_org[0], oy = s_org[1], oz = s_org[2], invh = s_invh;
+        for (int i = tid; i < n; i += kBuildThreads) {
+            const T x = pos[(lo + i) * 3], y = pos[(lo + i) * 3 + 1], z = pos[(lo + i) * 3 + 2];
+            int cx = (int)floor((x - ox) * invh), cy = (int)floor((y - oy) * invh), cz = (int)floor((z - oz) * invh);
+            cx = min(max(cx, 0), gx - 1);
+            cy = min(max(cy, 0), gy - 1);
+            cz = min(max(cz, 0), gz - 1);
+            const int c = cx + gx * (cy + gy * cz);
+            cell_of[lo + i] = c;
+            atomicAdd(&counts[c], 1);
+        }
+        __syncthreads();
+        // exclusive scan of counts[0..ncell) by warp 0: each lane owns a contiguous chunk
+        if (warp == 0) {
+            const int chunk = (ncell + 31) / 32;
+            const int c0 = lane * chunk, c1 = min(c0 + chunk, ncell);
+            int s = 0;
+            for (int c = c0; c < c1; c++) s += counts[c];
+            int incl = s;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            int run = incl - s;
+            for (int c = c0; c < c1; c++) { int t = counts[c]; counts[c] = run; run += t; }
+            if (lane == 31) counts[ncell] = incl;
+        }
+        __syncthreads();
+        int32_t *cs = cell_start + lo + b;
+        for (int c = tid; c <= ncell; c += kBuildThreads) cs[c] = counts[c];
+        __syncthreads();
+        for (int i = tid; i < n; i += kBuildThreads) {
+            const int c = cell_of[lo + i];
+            const int slot = atomicAdd(&counts[c], 1);
+            spos[lo + slot] = make_v4(pos[(lo + i) * 3], pos[(lo + i) * 3 + 1], pos[(lo + i) * 3 + 2], i);
+        }
+        __syncthreads();
+    }
+}
+
+// ------------------------------------------------------------------------------------- neighbours
+struct FillOut {
+    int64_t *row0, *row1, *mapping_batch;
+    void *distance;
+    int32_t *row0_32, *row1_32;
+};
+
+template <typename T>
+__device__ __forceinline__ void emit_edge(const FillOut &o, int64_t slot, int64_t i, int64_t j, int64_t b, T d2) {
+    o.row0[slot] = i;
+    o.row1[slot] = j;
+    if (o.mapping_batch) o.mapping_batch[slot] = b;
+    if (o.distance) ((T *)o.distance)[slot] = sqrt(d2);
+    if (o.row0_32) o.row0_32[slot] = (int32_t)i;
+    if (o.row1_32) o.row1_32[slot] = (int32_t)j;
+}
+
+template <typename T, bool FILL>
+__global__ void __launch_bounds__(kNbrWarps * 32)
+neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t N, int64_t B, T r2,
+                  int64_t max_nn, int loop, int rule, const V4<T> *__restrict__ spos,
+                  const CellParam *__restrict__ cellparam, const int32_t *__restrict__ cell_of,
+                  const int32_t *__restrict__ cell_start, int32_t *__restrict__ deg,
+                  const int64_t *__restrict__ offsets, FillOut out, int32_t *__restrict__ status) {
+    __shared__ unsigned s_mask[FILL ? kNbrWarps * (kCapBits / 32) : 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned *mask = s_mask + (FILL ? warp * (kCapBits / 32) : 0);
+    const unsigned lt = lanemask_lt();
+
+    for (int64_t i = (int64_t)blockIdx.x * kNbrWarps + warp; i < N; i += (int64_t)gridDim.x * kNbrWarps) {
+        // structure of i: the last b with ptr[b] <= i (empty structures share a start and are skipped)
+        int64_t blo = 0, bhi = B;  // invariant: ptr[blo] <= i < ptr[bhi]
+        while (bhi - blo > 1) {
+            const int64_t mid = (blo + bhi) >> 1;
+            if (ptr[mid] <= i) blo = mid; else bhi = mid;
+        }
+        const int64_t b = blo;
+        const int64_t lo = ptr[b];
+        const int n = (int)(ptr[b + 1] - lo);
+        const int il = (int)(i - lo);
+        const T xi = pos[i * 3], yi = pos[i * 3 + 1], zi = pos[i * 3 + 2];
+        const CellParam cp = cellparam[b];
+
+        int64_t kept = 0, base_off = 0;
+        if (FILL) {
+            base_off = offsets[i];
+            kept = offsets[i + 1] - base_off;
+            if (kept == 0) continue;
+        }
+        int cnt_lo = 0, cnt_hi = 0;  // COUNT: hits with j < il / j > il (per lane)
+
+        if (!cp.use_cells) {
+            int64_t emitted = 0;
+            for (int jb = 0; jb < n; jb += 32) {
+                const int j = jb + lane;
+                bool hit = false;
+                T d2 = T(0);
+                if (j < n) {
+                    const int64_t gj = lo + j;
+                    d2 = dist2_rn(xi, yi, zi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]);
+                    hit = d2 < r2;
+                }
+                if (FILL) {
+                    hit = hit && (loop || j != il);
+                    const unsigned bal = __ballot_sync(0xffffffffu, hit);
+                    const int64_t rank = emitted + __popc(bal & lt);
+                    if (hit && rank < kept) emit_edge<T>(out, base_off + rank, i, lo + j, b, d2);
+                    emitted += __popc(bal);
+                    if (emitted >= kept) break;
+                } else if (hit) {
+                    cnt_lo += (j < il);
+                    cnt_hi += (j > il);
+                }
+            }
+        } else {
+            const int gx = cp.gx, gy = cp.gy, gz = cp.gz;
+            const int c = cell_of[i];
+            const int cx = c % gx, cy = (c / gx) % gy, cz = c / (gx * gy);
+            const int x0 = max(cx - 1, 0), x1 = min(cx + 1, gx - 1);
+            const int32_t *cs = cell_start + lo + b;
+            const V4<T> *sp = spos + lo;
+            const int nwin = FILL ? (n + kCapBits - 1) / kCapBits : 1;
+            int64_t emitted = 0;
+            for (int win = 0; win < nwin; win++) {
+                const int wbase = win * kCapBits;
+                const int wbits = FILL ? min(kCapBits, n - wbase) : 0;
+                const int nwords = (wbits + 31) >> 5;
+                if (FILL) {
+                    for (int w = lane; w < nwords; w += 32) mask[w] = 0u;
+                    __syncwarp();
+                }
+                for (int dz = -1; dz <= 1; dz++) {
+                    const int zz = cz + dz;
+                    if (zz < 0 || zz >= gz) continue;
+                    for (int dy = -1; dy <= 1; dy++) {
+                        const int yy = cy + dy;
+                        if (yy < 0 || yy >= gy) continue;
+                        const int rowbase = gx * (yy + gy * zz);
+                        const int k0 = cs[rowbase + x0], k1 = cs[rowbase + x1 + 1];
+                        for (int k = k0 + lane; k < k1; k += 32) {
+                            const V4<T> p = sp[k];
+                            const int j = idx_of(p);
+                            const T d2 = dist2_rn(xi, yi, zi, p.x, p.y, p.z);
+                            if (d2 < r2) {
+                                if (FILL) {
+                                    const int jw = j - wbase;
+                                    if ((loop || j != il) && jw >= 0 && jw < wbits)
+                                        atomicOr(&mask[jw >> 5], 1u << (jw & 31));
+                                } else {
+                                    cnt_lo += (j < il);
+                                    cnt_hi += (j > il);
+                                }
+                            }
+                        }
+                    }
+                }
+                if (FILL) {
+                    __syncwarp();
+                    for (int w0 = 0; w0 < nwords; w0 += 32) {
+                        const int w = w0 + lane;
+                        unsigned bits = w < nwords ? mask[w] : 0u;
+                        const int cbits = __popc(bits);
+                        int incl = cbits;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                            if (lane >= o) incl += t;
+                        }
+                        const int total = __shfl_sync(0xffffffffu, incl, 31);
+                        int64_t rank = emitted + (incl - cbits);
+                        while (bits && rank < kept) {
+                            const int t = __ffs(bits) - 1;
+                            bits &= bits - 1;
+                            const int j = wbase + (w << 5) + t;
+                            T d2 = T(0);
+                            if (out.distance) {
+                                const int64_t gj = lo + j;
+                                d2 = dist2_rn(xi, yi, zi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]);
+                            }
+                            emit_edge<T>(out, base_off + rank, i, lo + j, b, d2);
+                            rank++;
+                        }
+                        emitted += total;
+                        if (emitted >= kept) break;
+                    }
+                    __syncwarp();
+                    if (emitted >= kept) break;
+                }
+            }
+        }
+
+        if (!FILL) {
+            const int64_t nlo = warp_sum(cnt_lo), nhi = warp_sum(cnt_hi);
+            const int self_hit = dist2_rn(xi, yi, zi, xi, yi, zi) < r2 ? 1 : 0;
+            int64_t total, k;
+            if (loop) {
+                total = nlo + nhi + self_hit;
+                k = total < max_nn ? total : max_nn;
+            } else if (rule == MLCGB_RULE_CLUSTER && self_hit) {
+                total = nlo + nhi;
+                if (nlo >= max_nn + 1) k = max_nn + 1;
+                else k = total < max_nn ? total : max_nn;
+            } else {
+                total = nlo + nhi;
+                k = total < max_nn ? total : max_nn;
+            }
+            if (lane == 0) {
+                deg[i] = (int32_t)k;
+                if (k < total) atomicOr(status, (int)kTruncated);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------- scan
+__device__ __forceinline__ int64_t block_exclusive_scan(int64_t v, int64_t *s_warp, int64_t *total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int64_t incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int64_t t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int64_t w = lane < nwarp ? s_warp[lane] : 0;
+        int64_t wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int64_t t = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += t;
+        }
+        if (lane < nwarp) s_warp[lane] = wi - w;
+        if (lane == 31) s_warp[32] = wi;
+    }
+    __syncthreads();
+    const int64_t r = s_warp[warp] + incl - v;
+    if (total) *total = s_warp[32];
+    __syncthreads();
+    return r;
+}
+
+__global__ void __launch_bounds__(kScanBlock) scan_block_sums_kernel(const int32_t *deg, int64_t N, int64_t *bsum) {
+    __shared__ int64_t s_warp[33];
+    const int64_t i = (int64_t)blockIdx.x * kScanBlock + threadIdx.x;
+    int64_t total;
+    block_exclusive_scan(i < N ? (int64_t)deg[i] : 0, s_warp, &total);
+    if (threadIdx.x == 0) bsum[blockIdx.x] = total;
+}
+
+__global__ void __launch_bounds__(kScanBlock) scan_of_sums_kernel(int64_t *bsum, int64_t nb, int64_t *grand_total) {
+    __shared__ int64_t s_warp[33];
+    int64_t carry = 0;
+    for (int64_t c0 = 0; c0 < nb; c0 += kScanBlock) {
+        const int64_t k = c0 + threadIdx.x;
+        const int64_t v = k < nb ? bsum[k] : 0;
+        int64_t total;
+        const int64_t ex = block_exclusive_scan(v, s_warp, &total);
+        if (k < nb) bsum[k] = carry + ex;
+        carry += total;
+    }
+    if (threadIdx.x == 0) *grand_total = carry;
+}
+
+__global__ void __launch_bounds__(kScanBlock)
+scan_apply_kernel(const int32_t *deg, int64_t N, const int64_t *bsum, int64_t *offsets) {
+    __shared__ int64_t s_warp[33];
+    const int64_t i = (int64_t)blockIdx.x * kScanBlock + threadIdx.x;
+    const int64_t ex = block_exclusive_scan(i < N ? (int64_t)deg[i] : 0, s_warp, nullptr);
+    if (i < N) offsets[i] = bsum[blockIdx.x] + ex;
+}
+
+__global__ void batch_to_ptr_kernel(const int64_t *__restrict__ batch, int64_t N, int64_t B, int64_t *__restrict__ ptr) {
+    const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b > B) return;
+    int64_t lo = 0, hi = N;  // first index with batch[idx] >= b
+    while (lo < hi) {
+        const int64_t mid = (lo + hi) >> 1;
+        if (batch[mid] < b) lo = mid + 1; else hi = mid;
+    }
+    ptr[b] = lo;
+}
+
+__global__ void edge_twin_kernel(const int32_t *__restrict__ row0, const int32_t *__restrict__ row1,
+                                 const int64_t *__restrict__ offsets, int64_t E, int64_t N, int32_t *__restrict__ twin,
+                                 int32_t *__restrict__ status) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x) {
+        const int a = row0[e], b = row1[e];
+        int32_t t = -1;
+        if (a >= 0 && a < N && b >= 0 && b < N) {
+            int64_t lo = offsets[b], hi = offsets[b + 1];  // first k in b's segment with row1[k] >= a
+            while (lo < hi) {
+                const int64_t mid = (lo + hi) >> 1;
+                if (row1[mid] < a) lo = mid + 1; else hi = mid;
+            }
+            if (lo < offsets[b + 1] && row1[lo] == a) t = (int32_t)lo;
+        } else {
+            atomicOr(status, (int)kBadIndex);
+        }
+        if (t < 0) atomicOr(status, (int)kAsymmetric);
+        twin[e] = t;
+    }
+}
+
+template <typename T>
+static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn,
+                         int loop, int rule, void *ws, size_t ws_bytes, int dtype, int32_t *deg, int64_t *offsets,
+                         FillOut out, int32_t *status, cudaStream_t st) {
+    const WsLayout L = ws_layout(N, B, dtype);
+    if (ws_bytes < L.total) return MLCGB_E_WORKSPACE;
+    char *w = (char *)ws;
+    const T *pos = (const T *)pos_;
+    auto *spos = (V4<T> *)(w + L.spos);
+    auto *cellparam = (CellParam *)(w + L.cellparam);
+    auto *cell_of = (int32_t *)(w + L.cell_of);
+    auto *cell_start = (int32_t *)(w + L.cell_start);
+    auto *bsum = (int64_t *)(w + L.bsum);
+    const T r2 = (T)(r * r);
+    const int nbr_grid = grid_for(N, kNbrWarps, 32);
+    if (!fill) {
+        build_cells_kernel<T><<<grid_for(B, 1, 8), kBuildThreads, 0, st>>>(pos, ptr, B, (T)r, spos, cellparam, cell_of, cell_start);
+        neighbours_kernel<T, false><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
+                                                                         cell_of, cell_start, deg, nullptr, out, status);
+        const int64_t nb = (N + kScanBlock - 1) / kScanBlock;
+        scan_block_sums_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum);
+        scan_of_sums_kernel<<<1, kScanBlock, 0, st>>>(bsum, nb, offsets + N);
+        scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum, offsets);
+    } else {
+        neighbours_kernel<T, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
+                                                                        cell_of, cell_start, nullptr, offsets, out, status);
+    }
+    return check_launch();
+}
+
+}  // namespace mlcgb
+
+using namespace mlcgb;
+
+extern "C" {
+
+int mlcgb_batch_to_ptr(const int64_t *batch, int64_t N, int64_t B, int64_t *ptr, void *stream) {
+    if (N < 0 || B < 0 || !ptr || (N > 0 && !batch)) return MLCGB_E_ARG;
+    batch_to_ptr_kernel<<<(unsigned)((B + 1 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(batch, N, B, ptr);
+    return check_launch();
+}
+
+size_t mlcgb_radius_workspace_bytes(int64_t N, int64_t B, int dtype) {
+    if (N < 0 || B < 0) return 0;
+    return ws_layout(N, B, dtype).total;
+}
+
+int mlcgb_radius_count(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn, int loop,
+                       int rule, void *workspace, size_t workspace_bytes, int32_t *deg, int64_t *offsets, int32_t *status,
+                       void *stream) {
+    if (N < 0 || B < 0 || max_nn < 0 || !offsets || !status || !ptr || !workspace) return MLCGB_E_ARG;
+    if (N >= (int64_t)1 << 31) return MLCGB_E_LIMIT;
+    if (rule != MLCGB_RULE_NATIVE && rule != MLCGB_RULE_CLUSTER) return MLCGB_E_ARG;
+    if (N == 0) {
+        cudaMemsetAsync(offsets, 0, sizeof(int64_t), (cudaStream_t)stream);
+        return check_launch();
+    }
+    if (!pos || !deg || B == 0) return MLCGB_E_ARG;
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        return radius_launch<scalar_t>(false, pos, ptr, N, B, r, max_nn, loop, rule, workspace, workspace_bytes, dtype, deg,
+                                       offsets, FillOut{}, status, (cudaStream_t)stream);
+    });
+}
+
+int mlcgb_radius_fill(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int loop,
+                      const void *workspace, size_t workspace_bytes, const int64_t *offsets, int64_t E, int64_t *edge_index,
+                      void *distance, int64_t *mapping_batch, int32_t *row0_i32, int32_t *row1_i32, int32_t *status,
+                      void *stream) {
+    if (N < 0 || B < 0 || E < 0 || !offsets || !status || !ptr || !workspace) return MLCGB_E_ARG;
+    if (E == 0 || N == 0) return MLCGB_OK;
+    if (!pos || !edge_index) return MLCGB_E_ARG;
+    FillOut out{edge_index, edge_index + E, mapping_batch, distance, row0_i32, row1_i32};
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        return radius_launch<scalar_t>(true, pos, ptr, N, B, r, 0, loop, 0, const_cast<void *>(workspace), workspace_bytes, dtype,
+                                       nullptr, const_cast<int64_t *>(offsets), out, status, (cudaStream_t)stream);
+    });
+}
+
+int mlcgb_edge_twin(const int32_t *row0, const int32_t *row1, const int64_t *offsets, int64_t E, int64_t N, int32_t *twin,
+                    int32_t *status, void *stream) {
+    if (E < 0 || N < 0 || !status) return MLCGB_E_ARG;
+    if (E == 0) return MLCGB_OK;
+    if (!row0 || !row1 || !offsets || !twin) return MLCGB_E_ARG;
+    edge_twin_kernel<<<grid_for(E, 256), 256, 0, (cudaStream_t)stream>>>(row0, row1, offsets, E, N, twin, status);
+    return check_launch();
+}
+
+}  // extern "C"

@@ -1,0 +1,145 @@
+"""Radius-graph front end with mlcg's call signatures and neighbour-list dictionary format.
+
+Mirrors ``src/mlcg/neighbor_list/neighbor_list.py`` (``atomic_data2neighbor_list`` :27-102,
+``make_neighbor_list`` :105-163, ``validate_neighborlist`` :170-202), the ``radius_graph`` call made at
+``src/mlcg/neighbor_list/torch_impl.py:216-224`` and the native op ``radius_distance``
+(``src/opt_radius/mlcg_opt_radius/radius.py:187-199``).  Non-periodic structures only.
+"""
+from typing import Dict, Mapping, Optional, Tuple
+
+import torch
+
+from .autograd import EdgePlan, attach_plan, edge_distances
+from .backend import STATUS_TRUNCATED, get_backend
+
+RULE_NATIVE, RULE_CLUSTER = 0, 1
+PLAN_KEY = "_mlcgb_plan"
+
+
+def _as_3d(x: torch.Tensor) -> torch.Tensor:
+    """Zero-pad 1-D / 2-D points to three coordinates (adding +0.0 leaves the squared distance unchanged)."""
+    if x.dim() != 2 or not 1 <= x.shape[1] <= 3:
+        raise ValueError("positions must be [N, dim] with dim in 1..3")
+    if x.shape[1] == 3:
+        return x
+    return torch.cat([x, x.new_zeros(x.shape[0], 3 - x.shape[1])], dim=1)
+
+
+def _structure_ptr(x, batch, batch_size):
+    be = get_backend()
+    N = x.shape[0]
+    if batch is None:
+        return torch.tensor([0, N], dtype=torch.int64, device=x.device)
+    if batch.numel() != N:
+        raise ValueError("batch must have one entry per point")
+    if batch_size is None:
+        batch_size = int(batch[-1]) + 1 if N > 0 else 1   # sorted batch vector: last entry is the maximum
+    return be.batch_to_ptr(batch.to(torch.int64), batch_size)
+
+
+def _graph(x, r, ptr, loop, max_num_neighbors, rule, want_distance=False):
+    be = get_backend()
+    res = be.radius_graph(_as_3d(x), ptr, r, max_num_neighbors, loop, rule, want_distance=want_distance)
+    truncated = bool(res["status"] & STATUS_TRUNCATED)
+    plan = EdgePlan.from_centre_sorted(res["row0"], res["row1"], res["offsets"], x.shape[0], symmetric=not truncated)
+    attach_plan(res["edge_index"], plan)
+    res["plan"], res["truncated"] = plan, truncated
+    return res
+
+
+def radius_graph(x: torch.Tensor, r: float, batch: Optional[torch.Tensor] = None, loop: bool = False,
+                 max_num_neighbors: int = 32, flow: str = "source_to_target", num_workers: int = 1,
+                 batch_size: Optional[int] = None) -> torch.Tensor:
+    """Same call and result as ``torch_cluster.radius_graph`` (torch_impl.py:216-224 passes
+    ``flow="target_to_source"``: row 0 = centre, row 1 = neighbour, centre-major, neighbours ascending)."""
+    assert flow in ("source_to_target", "target_to_source")
+    res = _graph(x, r, _structure_ptr(x, batch, batch_size), loop, max_num_neighbors, RULE_CLUSTER)
+    ei = res["edge_index"]
+    if flow == "target_to_source":
+        return ei
+    out = ei.flip(0)
+    return out
+
+
+def radius_cuda(x: torch.Tensor, ptr_x: Optional[torch.Tensor], r: float, max_num_neighbors: int, ignore_same_index: bool,
+                exclude_pair_xs: Optional[torch.Tensor] = None, ptr_exclude_pair_xs: Optional[torch.Tensor] = None
+                ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``mlcg::radius_cuda`` (radius.cu:197-307): returns ``(edge_index [2,E], distance [E])``."""
+    if exclude_pair_xs is not None and exclude_pair_xs.numel() > 0 and ptr_exclude_pair_xs is not None and int(ptr_exclude_pair_xs[-1]) > 0:
+        raise NotImplementedError("excluded pairs are not supported by this build of radius_cuda")
+    if not x.is_cuda:
+        raise RuntimeError("x must be CUDA tensor")
+    if ptr_x is None:
+        ptr_x = torch.tensor([0, x.shape[0]], dtype=torch.int64, device=x.device)
+    res = _graph(x, r, ptr_x.to(torch.int64), not ignore_same_index, max_num_neighbors, RULE_NATIVE, want_distance=True)
+    return res["edge_index"], res["distance"]
+
+
+def radius_distance(x: torch.Tensor, r: float, batch: Optional[torch.Tensor] = None, loop: bool = False,
+                    max_num_neighbors: int = 32, batch_size: Optional[int] = None,
+                    exclude_pair_indices: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``mlcg_opt_radius.radius.radius_distance`` (radius.py:187-199): ``(distance, edge_index)``."""
+    if exclude_pair_indices is not None and exclude_pair_indices.numel() > 0:
+        raise NotImplementedError("excluded pairs are not supported by this build of radius_distance")
+    if x.numel() == 0:
+        return x.new_zeros(0), torch.empty(2, 0, dtype=torch.long, device=x.device)
+    res = _graph(x, r, _structure_ptr(x, batch, batch_size), loop, max_num_neighbors, RULE_NATIVE)
+    # the distance goes through the differentiable geometry operators, so that derivatives of any
+    # order with respect to x exist (the reference hand-writes two orders, radius.py:123-158)
+    return edge_distances(_as_3d(x), res["plan"]), res["edge_index"]
+
+
+def make_neighbor_list(tag: str, order: int, index_mapping: torch.Tensor, mapping_batch: Optional[torch.Tensor] = None,
+                       cell_shifts: Optional[torch.Tensor] = None, rcut: Optional[float] = None,
+                       self_interaction: Optional[bool] = None) -> Dict:
+    """neighbor_list.py:105-163 — same keys, same checks."""
+    if index_mapping.shape[0] != order:
+        raise RuntimeError(f"index_mapping shape does not match the order:{index_mapping.shape[0]} != {order}")
+    if mapping_batch is None:
+        mapping_batch = torch.zeros((index_mapping.shape[1],) if len(index_mapping) > 0 else (0,), dtype=torch.long)
+    plan = getattr(index_mapping, "_mlcgb_plan", None)
+    im = torch.as_tensor(index_mapping, dtype=torch.long)
+    if plan is not None:
+        attach_plan(im, plan)
+    return dict(tag=tag, order=order, index_mapping=im, cell_shifts=cell_shifts, rcut=rcut,
+                self_interaction=self_interaction, mapping_batch=mapping_batch)
+
+
+def validate_neighborlist(inp: Mapping) -> bool:
+    """neighbor_list.py:170-202."""
+    keys = {"tag", "order", "index_mapping", "cell_shifts", "rcut", "self_interaction", "mapping_batch"}
+    if isinstance(inp, Mapping) and keys.issubset(inp.keys()):
+        if isinstance(inp["tag"], str) and isinstance(inp["order"], int) and torch.is_tensor(inp["index_mapping"]):
+            return True
+    return False
+
+
+def atomic_data2neighbor_list(data, rcut: float, self_interaction: bool = False, max_num_neighbors: int = 1000,
+                              nls_distance_method: str = "custom_kernel") -> Dict:
+    """neighbor_list.py:27-102 for non-periodic data; every supported method name runs the same
+    sm_100a kernel (there is no alternative back end in this package)."""
+    rcut = float(rcut)
+    if nls_distance_method not in ("torch", "custom_kernel", "nvalchemi_naive", "nvalchemi_cell", "nvalchemi_raw"):
+        raise ValueError(f"Method {nls_distance_method} not supported for nls-distance computation ")
+    pbc = getattr(data, "pbc", None)
+    if pbc is not None and bool(torch.any(pbc)):
+        raise NotImplementedError("periodic structures are outside the scope of mlcg_b200's radius graph")
+    pos = data.pos
+    batch = getattr(data, "batch", None)
+    if batch is None:
+        batch = torch.zeros(pos.shape[0], dtype=torch.long, device=pos.device)
+    n_atoms = getattr(data, "n_atoms", None)
+    if n_atoms is not None and torch.is_tensor(n_atoms) and n_atoms.dim() == 1:
+        # structure boundaries without a device->host read of batch[-1]
+        ptr = torch.zeros(n_atoms.numel() + 1, dtype=torch.int64, device=pos.device)
+        torch.cumsum(n_atoms.to(device=pos.device, dtype=torch.int64), 0, out=ptr[1:])
+    else:
+        ptr = _structure_ptr(pos, batch, None)
+    res = _graph(pos, rcut, ptr, self_interaction, max_num_neighbors, RULE_CLUSTER)
+    mapping = res["edge_index"]
+    # The reference asserts batch[mapping[0]] == batch[mapping[1]] here (a device->host sync,
+    # neighbor_list.py:89-91); the kernel only ever pairs points of one structure, by construction.
+    cell_shifts = torch.zeros((mapping.shape[1], 3), dtype=pos.dtype, device=pos.device)
+    return make_neighbor_list(tag=f"nonbounded rc:{rcut} order:{mapping.shape[0]}", order=mapping.shape[0], index_mapping=mapping,
+                              mapping_batch=res["mapping_batch"], cell_shifts=cell_shifts, rcut=rcut,
+                              self_interaction=self_interaction)

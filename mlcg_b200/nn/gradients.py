@@ -1,0 +1,80 @@
+"""Energy -> force wrappers with mlcg's names and output layout (src/mlcg/nn/gradients.py)."""
+from typing import Any, List, Sequence
+
+import torch
+
+from ..data import ENERGY_KEY, FORCE_KEY
+
+
+class GradientsOut(torch.nn.Module):
+    """forces = -d(sum of energies)/d(pos); the graph of that derivative is kept in training mode so the
+    force loss can be differentiated again (gradients.py:191-230)."""
+
+    _targets = {FORCE_KEY: ENERGY_KEY}
+
+    def __init__(self, model: torch.nn.Module, targets: str = FORCE_KEY):
+        super().__init__()
+        self.model = model
+        self.name = self.model.name
+        self.targets = [targets] if isinstance(targets, str) else list(targets) if isinstance(targets, Sequence) else []
+        assert any(k in GradientsOut._targets for k in self.targets), f"targets={self.targets} should be any of {GradientsOut._targets}"
+
+    def forward(self, data):
+        data.pos.requires_grad_(True)
+        data = self.model(data)
+        if FORCE_KEY in self.targets:
+            y = data.out[ENERGY_KEY] if self.name == "SumOut" else data.out[self.name][ENERGY_KEY]
+            dy_dr = torch.autograd.grad(y.sum(), data.pos, create_graph=self.training)[0]
+            if self.name == "SumOut":
+                data.out[FORCE_KEY] = -dy_dr
+            else:
+                data.out[self.name][FORCE_KEY] = -dy_dr
+        data.pos = data.pos.detach()
+        return data
+
+    def neighbor_list(self, **kwargs: Any):
+        return self.model.neighbor_list(**kwargs)
+
+
+class SumOut(torch.nn.Module):
+    """Runs each component model and adds up the targets (gradients.py:59-117)."""
+
+    name: str = "SumOut"
+
+    def __init__(self, models: torch.nn.ModuleDict, targets: List[str] = None):
+        super().__init__()
+        self.targets = [ENERGY_KEY, FORCE_KEY] if targets is None else targets
+        self.models = models
+
+    def forward(self, data):
+        for target in self.targets:
+            data.out[target] = 0.00
+        for name in self.models.keys():
+            data = self.models[name](data)
+            for target in self.targets:
+                data.out[target] += data.out[name][target]
+        return data
+
+    def neighbor_list(self, **kwargs):
+        nl = {}
+        for _, model in self.models.items():
+            nl.update(**model.neighbor_list(**kwargs))
+        return nl
+
+
+class EnergyOut(torch.nn.Module):
+    """Copies a model's energy to the top level of ``data.out`` (gradients.py:126-156)."""
+
+    name: str = "EnergyOut"
+
+    def __init__(self, model: torch.nn.Module, targets: List[str] = None):
+        super().__init__()
+        self.targets = [ENERGY_KEY] if targets is None else targets
+        self.model = model
+        self.name = self.model.name
+
+    def forward(self, data):
+        data = self.model(data)
+        for target in self.targets:
+            data.out[target] = data.out[self.name][target]
+        return data

@@ -1,0 +1,44 @@
+"""MLP with mlcg's constructor and ``layers.{i}`` parameter names (src/mlcg/nn/mlp.py:7-58)."""
+from typing import List
+
+import torch
+
+from ..autograd import MatmulNT
+
+
+def init_xavier_uniform(module: torch.nn.Module, zero_bias: bool = True) -> None:
+    """Xavier-uniform weights, zero bias, Linear layers only (src/mlcg/nn/_module_init.py:4-28)."""
+    if isinstance(module, torch.nn.Linear):
+        torch.nn.init.xavier_uniform_(module.weight)
+        if module.bias is not None and zero_bias:
+            torch.nn.init.constant_(module.bias, 0.0)
+
+
+class MLP(torch.nn.Module):
+    def __init__(self, layer_widths: List[int] = None, activation_func: torch.nn.Module = torch.nn.Tanh(), last_bias: bool = True):
+        super().__init__()
+        if layer_widths is None:
+            layer_widths = [10, 10, 1]
+        layers = []
+        for w_in, w_out in zip(layer_widths[:-2], layer_widths[1:-1]):
+            layers += [torch.nn.Linear(w_in, w_out, bias=True), activation_func]
+        layers.append(torch.nn.Linear(layer_widths[-2], layer_widths[-1], bias=last_bias))
+        self.layers = torch.nn.Sequential(*layers)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        for layer in self.layers:
+            init_xavier_uniform(layer)
+
+    def forward(self, x, data=None):
+        return self.layers(x)
+
+    def forward_edges(self, x: torch.Tensor) -> torch.Tensor:
+        """Same function as :meth:`forward`, with every Linear layer run by this package's GEMM kernels
+        (used for the edge-sized filter network, where the row count is the number of edges)."""
+        for layer in self.layers:
+            if isinstance(layer, torch.nn.Linear):
+                x = MatmulNT.apply(x, layer.weight, layer.bias)
+            else:
+                x = layer(x)
+        return x

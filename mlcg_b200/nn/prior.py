@@ -1,0 +1,252 @@
+"""Prior energy terms with mlcg's class names, constructor arguments and buffers
+(src/mlcg/nn/prior/harmonic.py, repulsion.py, fourier_series.py, base.py).
+
+``forward(data)`` evaluates one fused kernel per prior that returns the per-structure energies and keeps
+dE/dpos for the backward pass, so ``GradientsOut`` gets forces from a single multiply.  In training
+mode (``create_graph=True`` upstream) the same terms are evaluated with differentiable torch
+operations, because the analytic-gradient kernel carries no second derivative.
+"""
+from typing import Dict, Final
+
+import torch
+
+from ..backend import get_backend
+
+KIND_BOND, KIND_ANGLE, KIND_DIHEDRAL, KIND_REPULSION = 0, 1, 2, 3
+_PARAM_CACHE = "_mlcgb_prior_params"
+
+
+class _PriorEnergy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, pos, kind, mapping, mapping_batch, params, batch, B):
+        energy, grad = get_backend().prior_terms(kind, pos, mapping, mapping_batch, params, B, want_grad=True)
+        ctx.save_for_backward(grad, batch)
+        return energy
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        grad, batch = ctx.saved_tensors
+        return g.index_select(0, batch).unsqueeze(-1) * grad, None, None, None, None, None, None
+
+
+def _num_structures(data) -> int:
+    n_atoms = getattr(data, "n_atoms", None)
+    if n_atoms is not None and torch.is_tensor(n_atoms) and n_atoms.dim() == 1:
+        return int(n_atoms.numel())
+    return int(data.batch[-1]) + 1
+
+
+def _table_from_statistics(statistics: Dict, order: int, field: str) -> torch.Tensor:
+    keys = torch.tensor(list(statistics.keys()), dtype=torch.long)
+    types = torch.unique(keys.flatten())
+    assert types.min() >= 0
+    table = torch.zeros(tuple([int(types.max()) + 1] * order))
+    for key, val in statistics.items():
+        table[key] = val[field]
+    return table
+
+
+# differentiable torch restatements of the features, used only when second derivatives are needed
+def _distances(pos, m):
+    return (pos[m[1]] - pos[m[0]]).norm(p=2, dim=1)
+
+
+def _angles_cos(pos, m):
+    a, b = pos[m[0]] - pos[m[1]], pos[m[2]] - pos[m[1]]
+    return (a * b).sum(dim=1) / a.norm(p=2, dim=1) / b.norm(p=2, dim=1)
+
+
+def _torsions(pos, m):
+    b1, b2, b3 = pos[m[1]] - pos[m[0]], pos[m[2]] - pos[m[1]], pos[m[3]] - pos[m[2]]
+    b1, b2, b3 = (v / v.norm(p=2, dim=1)[:, None] for v in (b1, b2, b3))
+    n1, n2 = torch.cross(b1, b2, dim=1), torch.cross(b2, b3, dim=1)
+    m1 = torch.cross(n1, b2, dim=1)
+    return torch.atan2(-(m1 * n2).sum(-1), (n1 * n2).sum(-1))
+
+
+class _Prior(torch.nn.Module):
+    """base.py:66-141: a prior reads ``data.neighbor_list[self.name]`` and writes ``data.out[self.name]["energy"]``."""
+
+    kind = None
+
+    def _params(self, data) -> torch.Tensor:
+        raise NotImplementedError
+
+    def _energy_terms(self, pos, mapping, params) -> torch.Tensor:
+        raise NotImplementedError
+
+    def _interaction_types(self, data):
+        mapping = data.neighbor_list[self.name]["index_mapping"]
+        return tuple(data.atom_types[mapping[i]] for i in range(self.order))
+
+    def _cached_params(self, data) -> torch.Tensor:
+        """[P, M] per-term parameters; the index lists and bead types are static, so they are gathered once
+        per data object and kept next to the neighbour list (what mlcg's StaticPrior specialisation does,
+        src/mlcg/simulation/specialize_prior.py:49-59)."""
+        nl = data.neighbor_list[self.name]
+        cache = nl.setdefault(_PARAM_CACHE, {})
+        key = (self.name, data.pos.dtype, data.pos.device)
+        if key not in cache:
+            cache[key] = self._params(data).to(data.pos.dtype).contiguous()
+        return cache[key]
+
+    def forward(self, data):
+        nl = data.neighbor_list[self.name]
+        mapping, mapping_batch = nl["index_mapping"], nl["mapping_batch"]
+        B = _num_structures(data)
+        params = self._cached_params(data)
+        if self.training and torch.is_grad_enabled():
+            y = self._energy_terms(data.pos, mapping, params)
+            energy = torch.zeros(B, dtype=y.dtype, device=y.device).index_add_(0, mapping_batch, y)
+        else:
+            energy = _PriorEnergy.apply(data.pos, self.kind, mapping, mapping_batch, params, data.batch, B)
+        data.out[self.name] = {"energy": energy}
+        return data
+
+
+class Harmonic(_Prior):
+    """k (x - x0)^2 + V0, no factor one half (harmonic.py:22-120)."""
+
+    def __init__(self, statistics: Dict, name: str, order: int) -> None:
+        super().__init__()
+        self.allowed_interaction_keys = list(statistics.keys())
+        self.name, self.order = name, order
+        self.register_buffer("x_0", _table_from_statistics(statistics, order, "x_0"))
+        self.register_buffer("k", _table_from_statistics(statistics, order, "k"))
+
+    def data2parameters(self, data):
+        t = self._interaction_types(data)
+        params = {"x0": self.x_0[t].flatten(), "k": self.k[t].flatten()}
+        params["V0"] = torch.zeros_like(params["x0"])
+        return params
+
+    def _params(self, data):
+        p = self.data2parameters(data)
+        return torch.stack([p["x0"], p["k"]])
+
+    @staticmethod
+    def compute(x, x0, k, V0=0):
+        return k * (x - x0) ** 2 + V0
+
+
+class HarmonicBonds(Harmonic):
+    name: Final[str] = "bonds"
+    _order = 2
+    kind = KIND_BOND
+
+    def __init__(self, statistics) -> None:
+        super().__init__(statistics, HarmonicBonds.name, order=2)
+
+    def _energy_terms(self, pos, mapping, params):
+        return Harmonic.compute(_distances(pos, mapping), params[0], params[1])
+
+    @staticmethod
+    def compute_features(pos, mapping, pbc=None, cell=None, batch=None):
+        return _distances(pos, mapping)
+
+
+class HarmonicAngles(Harmonic):
+    """k (cos(theta) - x0)^2: x0 is a cosine (harmonic.py:245-297)."""
+
+    name: Final[str] = "angles"
+    _order = 3
+    kind = KIND_ANGLE
+
+    def __init__(self, statistics) -> None:
+        super().__init__(statistics, HarmonicAngles.name, order=3)
+
+    def _energy_terms(self, pos, mapping, params):
+        return Harmonic.compute(_angles_cos(pos, mapping), params[0], params[1])
+
+    @staticmethod
+    def compute_features(pos, mapping, pbc=None, cell=None, batch=None):
+        return _angles_cos(pos, mapping)
+
+
+class Repulsion(_Prior):
+    """(sigma / d)^6 over the pair list as given (repulsion.py:14-140)."""
+
+    name: Final[str] = "repulsion"
+    _neighbor_list_name = "fully connected"
+    kind = KIND_REPULSION
+
+    def __init__(self, statistics: Dict) -> None:
+        super().__init__()
+        self.allowed_interaction_keys = list(statistics.keys())
+        self.order = 2
+        self.register_buffer("sigma", _table_from_statistics(statistics, 2, "sigma"))
+
+    def _params(self, data):
+        return self.sigma[self._interaction_types(data)].flatten().unsqueeze(0)
+
+    def _energy_terms(self, pos, mapping, params):
+        return Repulsion.compute(_distances(pos, mapping), params[0])
+
+    @staticmethod
+    def compute_features(pos, mapping, pbc=None, cell=None, batch=None):
+        return _distances(pos, mapping)
+
+    @staticmethod
+    def compute(x, sigma):
+        rr = (sigma / x) * (sigma / x)
+        return rr * rr * rr
+
+
+class FourierSeries(_Prior):
+    """v0 + sum_n k1_n sin(n theta) + k2_n cos(n theta) (fourier_series.py:16-198)."""
+
+    kind = KIND_DIHEDRAL
+
+    def __init__(self, statistics: Dict, name: str = "", n_degs: int = 6, order: int = 4) -> None:
+        super().__init__()
+        self.allowed_interaction_keys = list(statistics.keys())
+        self.order, self.name, self.n_degs = order, name, n_degs
+        self.k1_names = ["k1_" + str(i) for i in range(1, n_degs + 1)]
+        self.k2_names = ["k2_" + str(i) for i in range(1, n_degs + 1)]
+        keys = torch.tensor(list(statistics.keys()), dtype=torch.long)
+        sizes = tuple([int(torch.unique(keys.flatten()).max()) + 1] * order)
+        k1, k2, v_0 = torch.zeros(n_degs, *sizes), torch.zeros(n_degs, *sizes), torch.zeros(*sizes)
+        for key, val in statistics.items():
+            for i in range(n_degs):
+                k1[i][key] = val["k1s"][self.k1_names[i]]
+                k2[i][key] = val["k2s"][self.k2_names[i]]
+            v_0[key] = val["v_0"]
+        self.register_buffer("k1s", k1)
+        self.register_buffer("k2s", k2)
+        self.register_buffer("v_0", v_0)
+
+    def data2parameters(self, data):
+        t = self._interaction_types(data)
+        k1s = torch.vstack([self.k1s[i][t] for i in range(self.n_degs)]).t()
+        k2s = torch.vstack([self.k2s[i][t] for i in range(self.n_degs)]).t()
+        return {"k1s": k1s, "k2s": k2s, "v_0": self.v_0[t].view(-1, 1)}
+
+    def _params(self, data):
+        p = self.data2parameters(data)
+        return torch.cat([p["v_0"].t(), p["k1s"].t(), p["k2s"].t()], dim=0)   # rows: v0, k1_1..k1_n, k2_1..k2_n
+
+    def _energy_terms(self, pos, mapping, params):
+        n = self.n_degs
+        return FourierSeries.compute(_torsions(pos, mapping), params[0], params[1:1 + n].t(), params[1 + n:1 + 2 * n].t())
+
+    @staticmethod
+    def compute(theta, v_0, k1s, k2s):
+        n_degs = torch.arange(1, k1s.shape[1] + 1, dtype=theta.dtype, device=theta.device)
+        angles = theta.view(-1, 1) * n_degs.view(1, -1)
+        V = k1s * torch.sin(angles) + k2s * torch.cos(angles)
+        if v_0.ndim > 1:
+            v_0 = v_0[:, 0]
+        return V.sum(dim=1) + v_0
+
+
+class Dihedral(FourierSeries):
+    name: Final[str] = "dihedrals"
+    _order: Final[int] = 4
+
+    def __init__(self, statistics: Dict, n_degs: int = 3, name: str = "dihedrals") -> None:
+        super().__init__(statistics, name=name, n_degs=n_degs, order=self._order)
+
+    @staticmethod
+    def compute_features(pos, mapping, pbc=None, cell=None, batch=None):
+        return _torsions(pos, mapping)

@@ -1,0 +1,109 @@
+"""Radial bases with mlcg's class names, constructor arguments and parameter names
+(src/mlcg/nn/radial_basis/gaussian.py, exp_normal.py, base.py)."""
+from typing import Union
+
+import torch
+from torch import nn
+
+from ..autograd import RbfExpand
+from ..backend import RbfSpec
+from .cutoff import CosineCutoff, IdentityCutoff, _Cutoff, cutoff_kind
+
+
+class _RadialBasis(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.cutoff = None
+
+    def check_cutoff(self):
+        if self.cutoff.cutoff_upper < self.cutoff.cutoff_lower:
+            raise ValueError("Upper cutoff {} is less than lower cutoff {}".format(self.cutoff.cutoff_upper, self.cutoff.cutoff_lower))
+
+    def _resolve_cutoff(self, cutoff, default_cls):
+        if isinstance(cutoff, (float, int)):
+            return default_cls(0, cutoff)
+        if isinstance(cutoff, _Cutoff) or cutoff_kind(cutoff) is not None:
+            return cutoff
+        raise TypeError("Supplied cutoff {} is neither a number nor a _Cutoff instance.".format(cutoff))
+
+    def _kernel_ok(self, dist: torch.Tensor) -> bool:
+        """The fused kernel treats the basis parameters as constants and knows two envelopes."""
+        # (in eval mode only position gradients are taken, as in GradientsOut with create_graph=False)
+        frozen = not self.training or not torch.is_grad_enabled() or not any(p.requires_grad for p in self.parameters())
+        return frozen and cutoff_kind(self.cutoff) is not None and dist.dim() == 1
+
+
+class GaussianBasis(_RadialBasis):
+    """exp(coeff (d - offset_k)^2) * envelope(d), gaussian.py:9-102."""
+
+    def __init__(self, cutoff: Union[int, float, _Cutoff], num_rbf: int = 50, trainable: bool = False):
+        super().__init__()
+        self.cutoff = self._resolve_cutoff(cutoff, IdentityCutoff)
+        self.check_cutoff()
+        self.num_rbf, self.trainable = num_rbf, trainable
+        offset, coeff = self._initial_params()
+        if trainable:
+            self.register_parameter("coeff", nn.Parameter(coeff))
+            self.register_parameter("offset", nn.Parameter(offset))
+        else:
+            self.register_buffer("coeff", coeff)
+            self.register_buffer("offset", offset)
+
+    def _initial_params(self):
+        offset = torch.linspace(self.cutoff.cutoff_lower, self.cutoff.cutoff_upper, self.num_rbf)
+        return offset, -0.5 / (offset[1] - offset[0]) ** 2
+
+    def reset_parameters(self):
+        offset, coeff = self._initial_params()
+        self.offset.data.copy_(offset)
+        self.coeff.data.copy_(coeff)
+
+    def spec(self) -> RbfSpec:
+        c = self.cutoff
+        return RbfSpec(0, self.num_rbf, cutoff_kind(c), float(c.cutoff_lower), float(c.cutoff_upper), 0.0, self.offset, self.coeff)
+
+    def forward(self, dist: torch.Tensor) -> torch.Tensor:
+        if self._kernel_ok(dist):
+            return RbfExpand.apply(dist, self.spec(), 0)
+        dist = dist.unsqueeze(-1)
+        return torch.exp(self.coeff * torch.pow(dist - self.offset, 2)) * self.cutoff(dist)
+
+
+class ExpNormalBasis(_RadialBasis):
+    """envelope(d) * exp(-beta_k (exp(alpha (lower - d)) - mean_k)^2), exp_normal.py:9-124."""
+
+    def __init__(self, cutoff: Union[int, float, _Cutoff], num_rbf: int = 50, trainable: bool = True):
+        super().__init__()
+        self.cutoff = self._resolve_cutoff(cutoff, CosineCutoff)
+        self.check_cutoff()
+        self.num_rbf, self.trainable = num_rbf, trainable
+        self.alpha = 5.0 / (self.cutoff.cutoff_upper - self.cutoff.cutoff_lower)
+        means, betas = self._initial_params()
+        if trainable:
+            self.register_parameter("means", nn.Parameter(means))
+            self.register_parameter("betas", nn.Parameter(betas))
+        else:
+            self.register_buffer("means", means)
+            self.register_buffer("betas", betas)
+
+    def _initial_params(self):
+        start = torch.exp(torch.scalar_tensor(-self.cutoff.cutoff_upper + self.cutoff.cutoff_lower))
+        means = torch.linspace(start, 1, self.num_rbf)
+        betas = torch.tensor([(2 / self.num_rbf * (1 - start)) ** -2] * self.num_rbf)
+        return means, betas
+
+    def reset_parameters(self):
+        means, betas = self._initial_params()
+        self.means.data.copy_(means)
+        self.betas.data.copy_(betas)
+
+    def spec(self) -> RbfSpec:
+        c = self.cutoff
+        return RbfSpec(1, self.num_rbf, cutoff_kind(c), float(c.cutoff_lower), float(c.cutoff_upper), float(self.alpha), self.means, self.betas)
+
+    def forward(self, dist: torch.Tensor) -> torch.Tensor:
+        if self._kernel_ok(dist):
+            return RbfExpand.apply(dist, self.spec(), 0)
+        dist = dist.unsqueeze(-1)
+        inner = torch.exp(self.alpha * (-dist + self.cutoff.cutoff_lower)) - self.means
+        return self.cutoff(dist) * torch.exp(-self.betas * inner ** 2)

@@ -1,0 +1,181 @@
+"""SchNet with mlcg's classes, constructor arguments, attribute names and ``state_dict`` keys
+(src/mlcg/nn/schnet.py), computing through this package's sm_100a kernels.
+
+``SchNet`` :32-192, ``InteractionBlock`` :195-262, ``CFConv`` :265-368, ``StandardSchNet`` :371-475.
+"""
+import warnings
+from typing import Final, List
+
+import torch
+
+from ..autograd import SegIn, SegmentSum, edge_distances, plan_of
+from ..backend import get_backend
+from ..data import ENERGY_KEY
+from ..neighbor_list import atomic_data2neighbor_list, validate_neighborlist
+from .mlp import MLP, init_xavier_uniform
+
+_SYM = "_mlcgb_symmetric"   # tag on edge tensors that are functions of the (symmetric) distance only
+
+
+def _tag_symmetric(t: torch.Tensor, flag: bool) -> torch.Tensor:
+    setattr(t, _SYM, flag)
+    return t
+
+
+class CFConv(torch.nn.Module):
+    """Continuous-filter convolution (schnet.py:265-368): ``lin2( sum_j lin1(x)_j * W_ij )`` with
+    ``W = filter_network(rbf) * cutoff(d)``.  Same constructor and sub-module names as the reference,
+    which derives from PyG's ``MessagePassing``; the aggregation here is an ordered segmented sum."""
+
+    def __init__(self, filter_network: torch.nn.Module, cutoff: torch.nn.Module, in_channels: int = 128, out_channels: int = 128,
+                 num_filters: int = 128, aggr: str = "add"):
+        super().__init__()
+        if aggr != "add":
+            raise NotImplementedError("mlcg_b200.CFConv implements aggr='add' (the only scheme mlcg's SchNet uses)")
+        self.aggr = aggr
+        self.lin1 = torch.nn.Linear(in_channels, num_filters, bias=False)
+        self.lin2 = torch.nn.Linear(num_filters, out_channels)
+        self.filter_network = filter_network
+        self.cutoff = cutoff
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        self.filter_network.reset_parameters()
+        init_xavier_uniform(self.lin1)
+        init_xavier_uniform(self.lin2)
+
+    def filters(self, edge_weight: torch.Tensor, edge_attr: torch.Tensor) -> torch.Tensor:
+        """W[E, F] (schnet.py:340-341)."""
+        C = self.cutoff(edge_weight)
+        net = self.filter_network
+        h = net.forward_edges(edge_attr) if isinstance(net, MLP) else net(edge_attr)
+        return h * C.view(-1, 1)
+
+    def forward(self, x: torch.Tensor, edge_index: torch.Tensor, edge_weight: torch.Tensor, edge_attr: torch.Tensor) -> torch.Tensor:
+        plan = plan_of(edge_index, x.shape[0])
+        symmetric = bool(getattr(edge_weight, _SYM, False) and getattr(edge_attr, _SYM, False))
+        W = self.filters(edge_weight, edge_attr)
+        x = self.lin1(x)
+        x = SegIn.apply(x, W, plan, symmetric)      # x_j = x[edge_index[0]], summed at edge_index[1]
+        return self.lin2(x)
+
+    def message(self, x_j: torch.Tensor, W: torch.Tensor) -> torch.Tensor:
+        return x_j * W
+
+
+class InteractionBlock(torch.nn.Module):
+    """CFConv -> activation -> Linear (schnet.py:195-262)."""
+
+    def __init__(self, cfconv_layer: torch.nn.Module, hidden_channels: int = 128, activation: torch.nn.Module = torch.nn.Tanh()):
+        super().__init__()
+        self.conv = cfconv_layer
+        self.activation = activation
+        self.lin = torch.nn.Linear(hidden_channels, hidden_channels)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        self.conv.reset_parameters()
+        init_xavier_uniform(self.lin)
+
+    def forward(self, x, edge_index, edge_weight, edge_attr, *args):
+        return self.lin(self.activation(self.conv(x, edge_index, edge_weight, edge_attr)))
+
+
+class SchNet(torch.nn.Module):
+    """schnet.py:32-192.  ``forward(data)`` fills ``data.out["SchNet"]["energy"]`` with one energy per structure."""
+
+    name: Final[str] = "SchNet"
+
+    def __init__(self, embedding_layer: torch.nn.Module, interaction_blocks: List[torch.nn.Module], rbf_layer: torch.nn.Module,
+                 output_network: torch.nn.Module, self_interaction: bool = False, max_num_neighbors: int = 1000,
+                 nls_distance_method: str = "custom_kernel"):
+        super().__init__()
+        self.embedding_layer = embedding_layer
+        self.rbf_layer = rbf_layer
+        self.max_num_neighbors = max_num_neighbors
+        if self_interaction:
+            raise NotImplementedError("The option `self_interaction` did not have function due to a bug. It only exists for compatibility and should stay `False`.")
+        self.self_interaction = self_interaction
+        if isinstance(interaction_blocks, list):
+            self.interaction_blocks = torch.nn.Sequential(*interaction_blocks)
+        elif isinstance(interaction_blocks, InteractionBlock):
+            self.interaction_blocks = torch.nn.Sequential(interaction_blocks)
+        else:
+            raise RuntimeError("interaction_blocks must be a single InteractionBlock or a list of InteractionBlocks.")
+        self.nls_distance_method = nls_distance_method
+        self.output_network = output_network
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        self.embedding_layer.reset_parameters()
+        self.rbf_layer.reset_parameters()
+        for block in self.interaction_blocks:
+            block.reset_parameters()
+        self.output_network.reset_parameters()
+
+    def is_nl_compatible(self, nl) -> bool:
+        # (the reference reads ``self.cutoff`` here, which SchNet never sets, schnet.py:164-173; the
+        #  intended comparison is with the radial basis' upper cutoff)
+        return bool(validate_neighborlist(nl) and nl["order"] == 2 and nl["self_interaction"] is False
+                    and nl["rcut"] == self.rbf_layer.cutoff.cutoff_upper)
+
+    def neighbor_list(self, data, rcut: float, max_num_neighbors: int = 1000) -> dict:
+        if not hasattr(self, "nls_distance_method"):
+            self.nls_distance_method = "custom_kernel"
+        return {SchNet.name: atomic_data2neighbor_list(data, rcut, self_interaction=False, max_num_neighbors=max_num_neighbors,
+                                                       nls_distance_method=self.nls_distance_method)}
+
+    def _structure_ptr(self, data):
+        n_atoms = getattr(data, "n_atoms", None)
+        if n_atoms is not None and torch.is_tensor(n_atoms) and n_atoms.dim() == 1:
+            ptr = torch.zeros(n_atoms.numel() + 1, dtype=torch.int64, device=data.pos.device)
+            torch.cumsum(n_atoms.to(device=data.pos.device, dtype=torch.int64), 0, out=ptr[1:])
+            return ptr
+        return get_backend().batch_to_ptr(data.batch, int(data.batch[-1]) + 1)
+
+    def forward(self, data):
+        x = self.embedding_layer(data.atom_types)
+        neighbor_list = data.neighbor_list.get(self.name)
+        if not self.is_nl_compatible(neighbor_list):
+            neighbor_list = self.neighbor_list(data, self.rbf_layer.cutoff.cutoff_upper, self.max_num_neighbors)[self.name]
+        edge_index = neighbor_list["index_mapping"]
+        cell_shifts = neighbor_list["cell_shifts"]
+        if cell_shifts is not None and cell_shifts.numel() > 0 and bool(torch.any(cell_shifts != 0)):
+            raise NotImplementedError("periodic cell shifts are outside the scope of mlcg_b200")
+        plan = plan_of(edge_index, data.pos.shape[0])
+        distances = _tag_symmetric(edge_distances(data.pos, plan), plan.symmetric)
+        rbf_expansion = _tag_symmetric(self.rbf_layer(distances), plan.symmetric)
+        num_batch = None
+        for block in self.interaction_blocks:
+            x = x + block(x, edge_index, distances, rbf_expansion, num_batch, data.batch)
+        energy = self.output_network(x, data)
+        energy = SegmentSum.apply(energy, self._structure_ptr(data), data.batch).flatten()
+        data.out[self.name] = {ENERGY_KEY: energy}
+        return data
+
+
+class StandardSchNet(SchNet):
+    """Convenience constructor (schnet.py:371-475): same arguments, same defaults."""
+
+    def __init__(self, rbf_layer: torch.nn.Module, cutoff: torch.nn.Module, output_hidden_layer_widths: List[int],
+                 hidden_channels: int = 128, embedding_size: int = 100, num_filters: int = 128, num_interactions: int = 3,
+                 activation: torch.nn.Module = torch.nn.Tanh(), max_num_neighbors: int = 1000, aggr: str = "add",
+                 nls_distance_method: str = "custom_kernel"):
+        if num_interactions < 1:
+            raise ValueError("At least one interaction block must be specified")
+        if cutoff.cutoff_lower != rbf_layer.cutoff.cutoff_lower:
+            warnings.warn("Cutoff function lower cutoff, {}, and radial basis function  lower cutoff, {}, do not match.".format(
+                cutoff.cutoff_lower, rbf_layer.cutoff.cutoff_lower))
+        if cutoff.cutoff_upper != rbf_layer.cutoff.cutoff_upper:
+            warnings.warn("Cutoff function upper cutoff, {}, and radial basis function  upper cutoff, {}, do not match.".format(
+                cutoff.cutoff_upper, rbf_layer.cutoff.cutoff_upper))
+        embedding_layer = torch.nn.Embedding(embedding_size, hidden_channels)
+        blocks = []
+        for _ in range(num_interactions):
+            filter_network = MLP(layer_widths=[rbf_layer.num_rbf, num_filters, num_filters], activation_func=activation, last_bias=False)
+            cfconv = CFConv(filter_network, cutoff=cutoff, num_filters=num_filters, in_channels=hidden_channels,
+                            out_channels=hidden_channels, aggr=aggr)
+            blocks.append(InteractionBlock(cfconv, hidden_channels, activation))
+        output_network = MLP([hidden_channels] + output_hidden_layer_widths + [1], activation_func=activation, last_bias=False)
+        super().__init__(embedding_layer, blocks, rbf_layer, output_network, max_num_neighbors=max_num_neighbors,
+                         nls_distance_method=nls_distance_method)

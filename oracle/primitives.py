@@ -1,0 +1,130 @@
+"""TEST INFRASTRUCTURE — plain-torch CPU restatements of the kernel primitives (not shipped).
+
+:class:`OracleBackend` has the same methods as ``mlcg_b200.backend.CudaBackend``.  The test-suite uses
+it in two ways: as the checker the CUDA kernels are compared against (same inputs, ``-m gpu``), and,
+substituted through ``mlcg_b200.backend.set_backend``, to exercise the host-side autograd wiring on a
+machine without a GPU.  It is never selected by the package itself.
+"""
+import numpy as np
+import torch
+
+from . import radius_ref, schnet_ref
+
+
+def _expand_segments(ptr):
+    counts = (ptr[1:] - ptr[:-1]).to(torch.int64)
+    return torch.repeat_interleave(torch.arange(counts.numel(), device=ptr.device), counts)
+
+
+class OracleBackend:
+    name = "oracle"
+
+    # ------------------------------------------------------------------ radius graph
+    def batch_to_ptr(self, batch, B):
+        return torch.from_numpy(radius_ref.batch_to_ptr(batch.cpu().numpy(), B)).to(batch.device)
+
+    def radius_graph(self, pos, ptr, r, max_num_neighbors, loop, rule, want_distance=False, want_batch=True):
+        p = pos.detach().cpu().numpy()
+        rule_name = "cluster" if int(rule) == 1 else "native"
+        ei, dist = radius_ref.radius_graph_c(p, ptr.cpu().numpy(), r, max_num_neighbors, loop, rule_name, with_distance=True)
+        N = p.shape[0]
+        deg = np.bincount(ei[0], minlength=N)
+        offsets = np.zeros(N + 1, dtype=np.int64)
+        np.cumsum(deg, out=offsets[1:])
+        # truncated: any centre that would have had more neighbours without the cap
+        full = radius_ref.radius_graph_c(p, ptr.cpu().numpy(), r, max(N, 1) + 1, loop, rule_name)
+        status = 1 if full.shape[1] != ei.shape[1] else 0
+        dev = pos.device
+        ei_t = torch.from_numpy(ei).to(dev)
+        seg = torch.from_numpy(np.searchsorted(ptr.cpu().numpy(), ei[0], side="right") - 1).to(dev)
+        return dict(edge_index=ei_t, distance=torch.from_numpy(dist).to(dev) if want_distance else None,
+                    mapping_batch=seg if want_batch else None, row0=ei_t[0].to(torch.int32), row1=ei_t[1].to(torch.int32),
+                    offsets=torch.from_numpy(offsets).to(dev), status=status)
+
+    def edge_twin(self, row0, row1, offsets, N):
+        E = row0.numel()
+        key = row0.to(torch.int64) * N + row1.to(torch.int64)
+        rkey = row1.to(torch.int64) * N + row0.to(torch.int64)
+        pos = torch.searchsorted(key, rkey).clamp(max=max(E - 1, 0))
+        found = key[pos] == rkey if E else torch.zeros(0, dtype=torch.bool)
+        twin = torch.where(found, pos, torch.full_like(pos, -1)).to(torch.int32)
+        status = torch.zeros(4, dtype=torch.int32)
+        if E and not bool(found.all()):
+            status[0] = 4
+        return twin, status
+
+    # ------------------------------------------------------------------ geometry
+    def edge_diff(self, pos, row0, row1):
+        return pos[row1.long()] - pos[row0.long()]
+
+    def node_scatter_diff(self, g, ptr_in, perm_in, ptr_out, perm_out, N):
+        gi = g if perm_in is None else g[perm_in.long()]
+        go = g if perm_out is None else g[perm_out.long()]
+        out = torch.zeros((N, 3), dtype=g.dtype)
+        out.index_add_(0, _expand_segments(ptr_in), gi)
+        out.index_add_(0, _expand_segments(ptr_out), -go)
+        return out
+
+    # ------------------------------------------------------------------ radial basis
+    @staticmethod
+    def _phi(d, spec):
+        cut = {"cutoff": "cosine" if spec.cutoff_kind == 1 else "identity", "lower": spec.lower, "upper": spec.upper}
+        s = {"kind": "gaussian" if spec.kind == 0 else "expnormal", "rbf_cutoff": cut}
+        sd = {"rbf_layer.offset": spec.p0.detach().to(d.dtype), "rbf_layer.coeff": spec.p1.detach().to(d.dtype).reshape(-1)[0],
+              "rbf_layer.means": spec.p0.detach().to(d.dtype), "rbf_layer.betas": spec.p1.detach().to(d.dtype).reshape(-1)}
+        return schnet_ref.radial_basis(d, s, sd)
+
+    def rbf_expand(self, d, spec, order):
+        """order-th derivative by nested automatic differentiation of the oracle expression."""
+        d = d.detach().clone().requires_grad_(True)
+        with torch.enable_grad():
+            cur = self._phi(d, spec)
+            for _ in range(order):
+                cols = [torch.autograd.grad(cur[:, k].sum(), d, create_graph=True)[0] for k in range(cur.shape[1])]
+                cur = torch.stack(cols, dim=1)
+        return cur.detach()
+
+    def rbf_contract(self, d, G, spec, order):
+        return (G.detach() * self.rbf_expand(d, spec, order)).sum(dim=1)
+
+    # ------------------------------------------------------------------ CFConv primitives
+    def seg_mul_sum(self, a, V, ptr, nbr, eperm, N):
+        Vp = V if eperm is None else V[eperm.long()]
+        out = torch.zeros((N, V.shape[1]), dtype=V.dtype)
+        return out.index_add_(0, _expand_segments(ptr), a[nbr.long()] * Vp)
+
+    def edge_mul(self, a, b, ia, ib):
+        return a[ia.long()] * b[ib.long()]
+
+    def gemm(self, mode, A, B, bias=None):
+        if mode == 0:
+            C = A @ B.t()
+            return C + bias if bias is not None else C
+        if mode == 1:
+            return A @ B
+        return A.t() @ B
+
+    def segment_sum(self, x, ptr):
+        out = torch.zeros(ptr.numel() - 1, dtype=x.dtype)
+        return out.index_add_(0, _expand_segments(ptr), x)
+
+    # ------------------------------------------------------------------ priors
+    def prior_terms(self, kind, pos, mapping, mapping_batch, params, B, want_grad=True):
+        p = pos.detach().clone().requires_grad_(True)
+        with torch.enable_grad():
+            if kind == 0:
+                y = params[1] * (schnet_ref.edge_distances(p, mapping) - params[0]) ** 2
+            elif kind == 1:
+                y = params[1] * (schnet_ref.angles_cos(p, mapping) - params[0]) ** 2
+            elif kind == 2:
+                n = (params.shape[0] - 1) // 2
+                th = schnet_ref.torsions(p, mapping)
+                y = params[0].clone()
+                for i in range(1, n + 1):
+                    y = y + params[i] * torch.sin(i * th) + params[n + i] * torch.cos(i * th)
+            else:
+                rr = (params[0] / schnet_ref.edge_distances(p, mapping)) ** 2
+                y = rr * rr * rr
+            e = schnet_ref.index_sum(y, mapping_batch, B)
+            g = torch.autograd.grad(e.sum(), p)[0] if want_grad else None
+        return e.detach(), g

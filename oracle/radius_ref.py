@@ -1,0 +1,136 @@
+"""TEST INFRASTRUCTURE — CPU oracle for the radius graph (not shipped, not measured as product).
+
+Two independent restatements of the same rule, used to pin each other:
+
+* :func:`radius_graph_numpy` — vectorised numpy, all pairs of one structure at a time;
+* :func:`radius_graph_c` — ``radius_ref.c`` compiled with ``-ffp-contract=off`` and OpenMP.
+
+The rule follows ``src/opt_radius/mlcg_opt_radius/radius.cu:106-141`` (strict ``<`` on the squared
+distance, optional self exclusion, the first ``max_num_neighbors`` hits in index order) and, for
+``rule="cluster"``, the ``max_num_neighbors + 1``-then-drop-self behaviour of
+``torch_cluster.radius_graph`` 1.6.3 as called from ``src/mlcg/neighbor_list/torch_impl.py:216-224``
+with ``flow="target_to_source"`` (row 0 = centre, row 1 = neighbour).
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libradius_ref.so")
+_SRC = os.path.join(_HERE, "radius_ref.c")
+RULES = {"native": 0, "cluster": 1}
+
+
+def build(force: bool = False) -> str:
+    """Compile ``radius_ref.c`` next to itself; returns the path of the shared object."""
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(_SRC):
+        subprocess.check_call(
+            ["gcc", "-O2", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC", "-o", _SO, _SRC, "-lm"]
+        )
+    return _SO
+
+
+_lib = None
+
+
+def _load():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(build())
+        i64p = ctypes.POINTER(ctypes.c_int64)
+        for name, fp in (("f32", ctypes.c_float), ("f64", ctypes.c_double)):
+            cnt = getattr(_lib, f"radius_ref_{name}_count")
+            cnt.restype = ctypes.c_int64
+            cnt.argtypes = [ctypes.POINTER(fp), i64p, ctypes.c_int64, ctypes.c_double, ctypes.c_int64,
+                            ctypes.c_int, ctypes.c_int, i64p]
+            fill = getattr(_lib, f"radius_ref_{name}_fill")
+            fill.restype = None
+            fill.argtypes = [ctypes.POINTER(fp), i64p, ctypes.c_int64, ctypes.c_double, ctypes.c_int64,
+                             ctypes.c_int, ctypes.c_int, i64p, i64p, i64p, ctypes.POINTER(fp)]
+        _lib.exclusion_pair_to_ptr_ref.restype = ctypes.c_int
+        _lib.exclusion_pair_to_ptr_ref.argtypes = [i64p, ctypes.c_int64, ctypes.c_int64, i64p, i64p]
+    return _lib
+
+
+def _ptr_of(a, ctype):
+    return a.ctypes.data_as(ctypes.POINTER(ctype))
+
+
+def batch_to_ptr(batch: np.ndarray, num_structures=None) -> np.ndarray:
+    """``ptr[b]`` = first index whose batch id is >= b (radius.py:64-75 uses bucketize for this)."""
+    batch = np.asarray(batch, dtype=np.int64)
+    B = int(batch.max()) + 1 if num_structures is None else int(num_structures)
+    return np.searchsorted(batch, np.arange(B + 1), side="left").astype(np.int64)
+
+
+def radius_graph_c(pos, ptr, r, max_num_neighbors=1000, loop=False, rule="cluster", with_distance=False):
+    """Edges ``[2, E]`` int64 (and distances) from the compiled oracle. ``pos`` is float32 or float64."""
+    lib = _load()
+    pos = np.ascontiguousarray(pos)
+    assert pos.ndim == 2 and pos.shape[1] == 3 and pos.dtype in (np.float32, np.float64)
+    tag, ct = ("f32", ctypes.c_float) if pos.dtype == np.float32 else ("f64", ctypes.c_double)
+    ptr = np.ascontiguousarray(ptr, dtype=np.int64)
+    B, N = len(ptr) - 1, pos.shape[0]
+    deg = np.zeros(N, dtype=np.int64)
+    E = getattr(lib, f"radius_ref_{tag}_count")(
+        _ptr_of(pos, ct), _ptr_of(ptr, ctypes.c_int64), B, float(r), int(max_num_neighbors), int(loop),
+        RULES[rule], _ptr_of(deg, ctypes.c_int64))
+    off = np.zeros(N + 1, dtype=np.int64)
+    np.cumsum(deg, out=off[1:])
+    ei = np.empty((2, E), dtype=np.int64)
+    dist = np.empty(E, dtype=pos.dtype)
+    getattr(lib, f"radius_ref_{tag}_fill")(
+        _ptr_of(pos, ct), _ptr_of(ptr, ctypes.c_int64), B, float(r), int(max_num_neighbors), int(loop),
+        RULES[rule], _ptr_of(off, ctypes.c_int64), _ptr_of(ei[0], ctypes.c_int64),
+        _ptr_of(ei[1], ctypes.c_int64), _ptr_of(dist, ct))
+    return (ei, dist) if with_distance else ei
+
+
+def radius_graph_numpy(pos, ptr, r, max_num_neighbors=1000, loop=False, rule="cluster", with_distance=False):
+    """Same rule, all pairs of one structure at a time with separately rounded numpy operations."""
+    pos = np.asarray(pos)
+    T = pos.dtype.type
+    r2 = T(float(r) * float(r))
+    rows0, rows1, dists = [], [], []
+    for b in range(len(ptr) - 1):
+        lo, hi = int(ptr[b]), int(ptr[b + 1])
+        p = pos[lo:hi]
+        d = p[None, :, :] - p[:, None, :]          # d[i, j] = pos[j] - pos[i]
+        sq = d * d
+        d2 = (sq[..., 0] + sq[..., 1]) + sq[..., 2]
+        hit = d2 < r2
+        n = hi - lo
+        eye = np.eye(n, dtype=bool)
+        if loop:
+            counted, cap = hit, max_num_neighbors
+        elif rule == "cluster":
+            counted, cap = hit, max_num_neighbors + 1   # self counts towards the cap ...
+        else:
+            counted, cap = hit & ~eye, max_num_neighbors
+        rank = np.cumsum(counted, axis=1)               # 1-based rank of each counted hit
+        keep = counted & (rank <= cap)
+        if not loop:
+            keep &= ~eye                                # ... and is dropped afterwards
+        i, j = np.nonzero(keep)
+        rows0.append(i + lo)
+        rows1.append(j + lo)
+        dists.append(np.sqrt(d2[i, j]))
+    ei = np.stack([np.concatenate(rows0), np.concatenate(rows1)]).astype(np.int64) if rows0 else np.zeros((2, 0), np.int64)
+    if with_distance:
+        return ei, (np.concatenate(dists) if dists else np.zeros(0, pos.dtype))
+    return ei
+
+
+def exclusion_pair_to_ptr(pairs, num_nodes):
+    """``exclusion_pairs.cpp:7-62``: pairs ``[2, P]`` (x, y) -> xs sorted by (y, x), CSR pointer over y."""
+    lib = _load()
+    pairs = np.ascontiguousarray(pairs, dtype=np.int64)
+    P = pairs.shape[1]
+    xs = np.empty(P, dtype=np.int64)
+    y_ptr = np.empty(num_nodes + 1, dtype=np.int64)
+    rc = lib.exclusion_pair_to_ptr_ref(_ptr_of(pairs, ctypes.c_int64), P, int(num_nodes),
+                                       _ptr_of(xs, ctypes.c_int64), _ptr_of(y_ptr, ctypes.c_int64))
+    assert rc == 0
+    return xs, y_ptr

@@ -1,0 +1,73 @@
+"""Shared builders for the tests: models from golden cases, synthetic chains, prior set-ups."""
+import itertools
+
+import torch
+
+import mlcg_b200
+from mlcg_b200 import nn as bnn
+
+
+def schnet_from_case(case, dtype=None, device="cpu", trainable=None):
+    """mlcg_b200 StandardSchNet with the architecture and weights of a golden case."""
+    cut = bnn.CosineCutoff(0.0, case["upper"])
+    trainable = ("rbf_layer.means" in case.get("param_grads", {})) if trainable is None else trainable
+    rbf = bnn.GaussianBasis(cut, case["R"], trainable=trainable) if case["kind"] == "gaussian" else bnn.ExpNormalBasis(cut, case["R"], trainable=trainable)
+    emb = case["state_dict"]["embedding_layer.weight"].shape[0]
+    model = bnn.StandardSchNet(rbf, cut, [case["H"]], hidden_channels=case["H"], embedding_size=emb, num_filters=case["H"],
+                               num_interactions=case["L"])
+    model = model.to(case["pos"].dtype)          # cast first: loading float64 weights into float32 would round them
+    model.load_state_dict(case["state_dict"])
+    dtype = case["pos"].dtype if dtype is None else dtype
+    return model.to(device=device, dtype=dtype)
+
+
+def data_from_case(case, device="cpu", dtype=None):
+    dtype = case["pos"].dtype if dtype is None else dtype
+    return mlcg_b200.AtomicData(pos=case["pos"].clone().to(device=device, dtype=dtype), atom_types=case["atom_types"].to(device),
+                                batch=case["batch"].to(device), n_atoms=torch.full((case["B"],), case["n"]).to(device), neighbor_list={})
+
+
+def random_walk_chain(n, gen, step=3.8, jitter=0.0, min_dist=None):
+    """3.8 A random walk; with ``min_dist`` a step is redrawn while the new bead is closer than that to any
+    bead except its predecessor (back-tracking five beads after 200 failures)."""
+    pos = torch.zeros(n, 3)
+    i, fails = 1, 0
+    while i < n:
+        v = torch.randn(3, generator=gen)
+        cand = pos[i - 1] + step * v / v.norm()
+        if min_dist is not None and i > 1 and bool(((pos[: i - 1] - cand).norm(dim=1) < min_dist).any()):
+            fails += 1
+            if fails > 200:
+                i, fails = max(1, i - 5), 0
+            continue
+        pos[i] = cand
+        i, fails = i + 1, 0
+    if jitter:
+        pos = pos + jitter * torch.randn(n, 3, generator=gen)
+    return pos
+
+
+def prior_setup(n, B, T, gen, min_sep=3):
+    """Chains with bonds / angles / dihedrals / repulsion lists and random parameter tables over T types."""
+    pos = torch.cat([random_walk_chain(n, gen, jitter=0.3) for _ in range(B)])
+    types_ = torch.randint(0, T, (B * n,), generator=gen)
+    batch = torch.arange(B).repeat_interleave(n)
+    idx = torch.arange(n)
+    per = {"bonds": torch.stack([idx[:-1], idx[1:]]), "angles": torch.stack([idx[:-2], idx[1:-1], idx[2:]]),
+           "dihedrals": torch.stack([idx[:-3], idx[1:-2], idx[2:-1], idx[3:]])}
+    full = torch.cartesian_prod(idx, idx).t()
+    per["repulsion"] = full[:, (full[0] - full[1]).abs() >= min_sep]
+    nls = {}
+    for k, m in per.items():
+        nls[k] = mlcg_b200.make_neighbor_list(k, m.shape[0], torch.cat([m + b * n for b in range(B)], dim=1),
+                                              torch.arange(B).repeat_interleave(m.shape[1]))
+    r = lambda: float(torch.rand(1, generator=gen))
+    bond = {k: {"k": 50 + 100 * r(), "x_0": 3.5 + 0.6 * r()} for k in itertools.product(range(T), repeat=2)}
+    ang = {k: {"k": 20 + 60 * r(), "x_0": -0.8 + r()} for k in itertools.product(range(T), repeat=3)}
+    dih = {k: {"v_0": r(), "k1s": {f"k1_{i}": r() - 0.5 for i in (1, 2, 3)}, "k2s": {f"k2_{i}": r() - 0.5 for i in (1, 2, 3)}}
+           for k in itertools.product(range(T), repeat=4)}
+    rep = {k: {"sigma": 3.0 + 2.0 * r()} for k in itertools.product(range(T), repeat=2)}
+    priors = {"bonds": bnn.HarmonicBonds(bond), "angles": bnn.HarmonicAngles(ang), "dihedrals": bnn.Dihedral(dih, n_degs=3),
+              "repulsion": bnn.Repulsion(rep)}
+    data = mlcg_b200.AtomicData(pos=pos, atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list=nls)
+    return data, priors

@@ -1,0 +1,171 @@
+"""Host-side logic on CPU: the package's modules and autograd wiring, with the kernel primitives
+replaced by their oracle restatements (``oracle/primitives.py``).  What is checked here is the
+Python layer — edge plans, operator composition, derivative formulas, module/state_dict layout —
+not the CUDA kernels (those are compared with the same oracle in the ``-m gpu`` tests)."""
+import pytest
+import torch
+
+import mlcg_b200
+from mlcg_b200 import autograd as ag
+from mlcg_b200 import backend, nn as bnn
+from oracle.primitives import OracleBackend
+
+from helpers import data_from_case, prior_setup, schnet_from_case
+
+
+@pytest.fixture(autouse=True)
+def oracle_backend():
+    old = backend.set_backend(OracleBackend())
+    yield
+    backend.set_backend(old)
+
+
+CASES = ["schnet_gaussian_f32", "schnet_expnormal_f32", "schnet_expnormal_trainable_f64"]
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_schnet_energy_forces_vs_reference(golden, name):
+    c = golden[name]
+    model = bnn.GradientsOut(schnet_from_case(c), "forces").eval()
+    out = model(data_from_case(c))
+    tol = 1e-10 if c["pos"].dtype == torch.float64 else 2e-6
+    assert torch.allclose(out.out["SchNet"]["energy"], c["energy"], rtol=tol, atol=tol)
+    assert torch.allclose(out.out["SchNet"]["forces"], c["forces"], rtol=tol, atol=10 * tol)
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_force_matching_step_vs_reference(golden, name):
+    c = golden[name]
+    net = schnet_from_case(c)
+    model = bnn.GradientsOut(net, "forces").train()
+    out = model(data_from_case(c))
+    loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], c["target_forces"])
+    loss.backward()
+    tol = 1e-9 if c["pos"].dtype == torch.float64 else 1e-5
+    assert torch.allclose(loss.detach(), c["loss"], rtol=tol)
+    grads = dict(net.named_parameters())
+    for k, g in c["param_grads"].items():
+        assert grads[k].grad is not None, k
+        assert torch.allclose(grads[k].grad, g, rtol=10 * tol, atol=tol * float(g.abs().max() + 1e-30)), k
+
+
+def test_state_dict_keys_match_reference(golden):
+    c = golden["schnet_expnormal_f32"]
+    assert set(schnet_from_case(c).state_dict().keys()) == set(c["state_dict"].keys())
+
+
+def test_neighbor_list_dictionary_format(golden):
+    c = golden["schnet_gaussian_f32"]
+    nl = mlcg_b200.atomic_data2neighbor_list(data_from_case(c), c["upper"], False, 1000)
+    assert set(nl) >= {"tag", "order", "index_mapping", "cell_shifts", "rcut", "self_interaction", "mapping_batch"}
+    assert nl["order"] == 2 and nl["rcut"] == c["upper"] and nl["self_interaction"] is False
+    assert torch.equal(nl["index_mapping"], c["edge_index"])
+    assert torch.equal(nl["mapping_batch"], c["batch"][c["edge_index"][0]])
+    assert nl["cell_shifts"].shape == (c["edge_index"].shape[1], 3) and not nl["cell_shifts"].any()
+    assert mlcg_b200.neighbor_list.validate_neighborlist(nl)
+
+
+def _plans(golden):
+    c = golden["schnet_gaussian_f32"]
+    ei = c["edge_index"]
+    N = c["pos"].shape[0]
+    sym = ag.EdgePlan.from_centre_sorted(ei[0].int(), ei[1].int(), ag._ptr_from_index(ei[0], N), N, symmetric=True)
+    perm = torch.randperm(ei.shape[1], generator=torch.Generator().manual_seed(0))
+    keep = perm[: int(0.8 * len(perm))]                   # shuffled and no longer symmetric
+    gen = ag.EdgePlan.from_edge_index(ei[:, keep].contiguous(), N)
+    return c, sym, gen
+
+
+def test_symmetric_plan_equals_general_plan(golden):
+    c, sym, _ = _plans(golden)
+    N = c["pos"].shape[0]
+    general = ag.EdgePlan.from_edge_index(c["edge_index"], N)
+    assert torch.equal(sym.ptr_in, general.ptr_in) and torch.equal(sym.perm_in, general.perm_in)
+    assert torch.equal(sym.nbr_in, general.nbr_in) and general.perm_out is None
+
+
+@pytest.mark.parametrize("which", ["symmetric", "general"])
+def test_bilinear_family_gradcheck(golden, which):
+    c, sym, gen = _plans(golden)
+    plan = sym if which == "symmetric" else gen
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn(plan.N, 3, dtype=torch.float64, generator=g, requires_grad=True)
+    b = torch.randn(plan.N, 3, dtype=torch.float64, generator=g, requires_grad=True)
+    V = torch.randn(plan.E, 3, dtype=torch.float64, generator=g, requires_grad=True)
+    for fn, args in [(lambda a, V: ag.SegIn.apply(a, V, plan, False), (a, V)), (lambda a, V: ag.SegOut.apply(a, V, plan), (a, V)),
+                     (lambda a, b: ag.EdgeMul.apply(a, b, plan), (a, b))]:
+        assert torch.autograd.gradcheck(fn, args, eps=1e-6, atol=1e-6)
+        assert torch.autograd.gradgradcheck(fn, args, eps=1e-6, atol=1e-6)
+    # SegIn against the definition: sum at row1 of a[row0] * V
+    ref = torch.zeros(plan.N, 3, dtype=torch.float64).index_add_(0, plan.row1.long(), a[plan.row0.long()] * V)
+    assert torch.allclose(ag.SegIn.apply(a, V, plan, False), ref)
+
+
+@pytest.mark.parametrize("which", ["symmetric", "general"])
+def test_distance_gradcheck(golden, which):
+    """The recipe of the reference's native-op test (test_radius.py:126-150): gradcheck and gradgradcheck."""
+    c, sym, gen = _plans(golden)
+    plan = sym if which == "symmetric" else gen
+    pos = c["pos"].double().clone().requires_grad_(True)
+    fn = lambda p: ag.edge_distances(p, plan)
+    assert torch.autograd.gradcheck(fn, (pos,), eps=1e-6, atol=1e-6)
+    assert torch.autograd.gradgradcheck(fn, (pos,), eps=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("kind", ["gaussian", "expnormal"])
+def test_rbf_operator_chain_gradcheck(kind):
+    cut = bnn.CosineCutoff(0.0, 8.0)
+    rbf = (bnn.GaussianBasis(cut, 6) if kind == "gaussian" else bnn.ExpNormalBasis(cut, 6, trainable=False)).double()
+    d = (0.5 + 7.0 * torch.rand(9, dtype=torch.float64, generator=torch.Generator().manual_seed(2))).requires_grad_(True)
+    assert torch.autograd.gradcheck(rbf, (d,), eps=1e-6, atol=1e-6)
+    assert torch.autograd.gradgradcheck(rbf, (d,), eps=1e-6, atol=1e-6)
+
+
+def test_gemm_family_gradcheck():
+    g = torch.Generator().manual_seed(3)
+    X = torch.randn(7, 4, dtype=torch.float64, generator=g, requires_grad=True)
+    W = torch.randn(5, 4, dtype=torch.float64, generator=g, requires_grad=True)
+    b = torch.randn(5, dtype=torch.float64, generator=g, requires_grad=True)
+    assert torch.autograd.gradcheck(ag.MatmulNT.apply, (X, W, b), eps=1e-6, atol=1e-6)
+    assert torch.autograd.gradgradcheck(ag.MatmulNT.apply, (X, W, b), eps=1e-6, atol=1e-6)
+
+
+def test_priors_eval_and_train_paths_vs_reference(golden):
+    c = golden["priors_f32"]
+    import itertools
+    T = c["tables"]["bonds"]["x_0"].shape[0]
+    data, priors = prior_setup(12, 2, T, torch.Generator().manual_seed(0))
+    # replace geometry, lists and tables by the golden ones
+    for k, p in priors.items():
+        p.load_state_dict(c["tables"][k])
+    for mode in ("eval", "train"):
+        for k, p in priors.items():
+            d = mlcg_b200.AtomicData(pos=c["pos"].clone(), atom_types=c["atom_types"], batch=c["batch"], n_atoms=torch.full((c["B"],), 12),
+                                     neighbor_list={k: mlcg_b200.make_neighbor_list(k, c["mappings"][k].shape[0], c["mappings"][k], c["mapping_batch"][k])})
+            m = bnn.GradientsOut(p, "forces")
+            m = m.eval() if mode == "eval" else m.train()
+            o = m(d)
+            assert torch.allclose(o.out[k]["energy"], c["energy"][k], rtol=1e-5), (mode, k)
+            f = o.out[k]["forces"].detach()
+            assert torch.allclose(f, c["forces"][k], rtol=1e-4, atol=1e-4 * float(c["forces"][k].abs().max())), (mode, k)
+
+
+def test_sumout_additivity(golden):
+    """tests/unit/nn/test_outs.py:160-166: SumOut totals equal the sum of the components (atol 1e-5 relative here)."""
+    data, priors = prior_setup(12, 3, 4, torch.Generator().manual_seed(5))
+    models = torch.nn.ModuleDict({k: bnn.GradientsOut(p, "forces") for k, p in priors.items()})
+    out = bnn.SumOut(models).eval()(data)
+    e = sum(out.out[k]["energy"] for k in priors)
+    f = sum(out.out[k]["forces"] for k in priors)
+    assert torch.allclose(out.out["energy"], e, rtol=1e-6) and torch.allclose(out.out["forces"], f, rtol=1e-6)
+
+
+def test_no_cpu_fallback():
+    """Without the test substitution the package refuses CPU tensors instead of computing on the host."""
+    backend.set_backend(None)
+    try:
+        be = backend.get_backend()
+    except Exception:
+        return  # library not built on this machine: operators cannot run at all, which is the point
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        be.edge_mul(torch.zeros(2, 4), torch.zeros(2, 4), torch.zeros(1, dtype=torch.int32), torch.zeros(1, dtype=torch.int32))
