@@ -1,0 +1,306 @@
+#!/usr/bin/env python
+"""Benchmark of the coarse-grained SchNet hot path: energy + force evaluations per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload at every N: 512 structures per GPU of a 100-bead C-alpha chain (3.8 A self-avoiding random
+walk, 20 bead types), SchNet with 3 interaction blocks, hidden = filters = 128, 128 exp-normal radial
+basis functions, 15 A cosine cutoff, float32; one step = radius graph + energy + forces for the batch.
+Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU restatement of mlcg's own PyTorch
+path (``oracle/``) on the host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "energy+force evaluations per second (structures/s), SchNet CG"
+WORKLOAD = dict(workload="cfg1: 100-bead CA chains, 512 structures/GPU, SchNet 3x(H=128,F=128), 128 expnorm RBF, rc=15A, energy+forces",
+                structures_per_gpu=512, beads=100, bead_types=20, hidden=128, filters=128, num_rbf=128, interactions=3,
+                cutoff_A=15.0, l2="flushed between steps (256 MiB write); edge tensors (>= 500 MB) exceed L2 as well")
+
+
+# ----------------------------------------------------------------------------------------- workload
+def self_avoiding_chains(B, n, gen, step=3.8, min_dist=4.0):
+    """B chains grown together: a bead is redrawn while it is closer than ``min_dist`` to any bead of its own
+    chain except its predecessor; after 200 failed draws the chain steps back five beads."""
+    pos = torch.zeros(B, n, 3)
+    i = torch.ones(B, dtype=torch.long)
+    fails = torch.zeros(B, dtype=torch.long)
+    ar = torch.arange(n)
+    while bool((i < n).any()):
+        act = (i < n).nonzero().flatten()
+        ia = i[act]
+        v = torch.randn(len(act), 3, generator=gen)
+        cand = pos[act, ia - 1] + step * v / v.norm(dim=1, keepdim=True)
+        d = (pos[act] - cand[:, None, :]).norm(dim=2)
+        considered = ar[None, :] < (ia - 1)[:, None]
+        clash = ((d < min_dist) & considered).any(dim=1)
+        ok = act[~clash]
+        pos[ok, i[ok]] = cand[~clash]
+        i[ok] += 1
+        fails[ok] = 0
+        bad = act[clash]
+        fails[bad] += 1
+        back = bad[fails[bad] > 200]
+        i[back] = torch.clamp(i[back] - 5, min=1)
+        fails[back] = 0
+    return pos.reshape(B * n, 3)
+
+
+def make_inputs(B, n, n_types, seed):
+    gen = torch.Generator().manual_seed(seed)
+    pos = self_avoiding_chains(B, n, gen)
+    types_ = torch.randint(0, n_types, (B * n,), generator=gen)
+    batch = torch.arange(B).repeat_interleave(n)
+    return pos, types_, batch
+
+
+def make_model():
+    from mlcg_b200 import nn as bnn
+    torch.manual_seed(0)
+    cut = bnn.CosineCutoff(0.0, WORKLOAD["cutoff_A"])
+    rbf = bnn.ExpNormalBasis(cut, WORKLOAD["num_rbf"], trainable=False)
+    return bnn.StandardSchNet(rbf, cut, [WORKLOAD["hidden"]], hidden_channels=WORKLOAD["hidden"], embedding_size=WORKLOAD["bead_types"],
+                              num_filters=WORKLOAD["filters"], num_interactions=WORKLOAD["interactions"])
+
+
+# ----------------------------------------------------------------------------------------- CPU legs
+def oracle_step_fn(model_sd, pos, types_, batch, B):
+    """One energy+force evaluation with the CPU oracle (radius graph included), returns (E, F)."""
+    from oracle import radius_ref, schnet_ref
+    cut = {"cutoff": "cosine", "lower": 0.0, "upper": WORKLOAD["cutoff_A"]}
+    spec = {"kind": "expnormal", "rbf_cutoff": cut, "cutoff": cut, "activation": "tanh", "num_interactions": WORKLOAD["interactions"]}
+    ptr = radius_ref.batch_to_ptr(batch.numpy(), B)
+
+    def step():
+        ei = torch.from_numpy(radius_ref.radius_graph_c(pos.numpy(), ptr, WORKLOAD["cutoff_A"], 1000, False, "cluster"))
+        e, f, _ = schnet_ref.energy_and_forces(lambda p: schnet_ref.schnet_energy(model_sd, spec, p, types_, batch, ei, B), pos)
+        return e, f
+
+    return step
+
+
+def cpu_leg(sample_B, steps, warmup):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    model = make_model()
+    sd = {k: v.detach() for k, v in model.state_dict().items()}
+    pos, types_, batch = make_inputs(sample_B, WORKLOAD["beads"], WORKLOAD["bead_types"], seed=0)
+    step = oracle_step_fn(sd, pos, types_, batch, sample_B)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    return sample_B * steps / dt, dt / steps * 1e3, cores
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample_B = 32
+    value, ms, cores = cpu_leg(sample_B, max(args.steps, 1), max(args.warmup, 1))
+    sample = f"{sample_B} structures of the same workload per step (of 512), torch CPU float32, radius graph rebuilt each step"
+    line = dict(metric=METRIC, value=value, unit="structures/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup, ms_per_step=ms,
+                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
+                config=dict(WORKLOAD, sample_structures_per_step=sample_B),
+                cpu_baseline=dict(value=value, unit="structures/s", cores=cores, kind="port", sample=sample),
+                e2e=dict(value=value, unit="structures/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for ln in out.strip().splitlines():
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None, reasons=sorted(reasons), samples=len(sm))
+
+
+# ----------------------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch.distributed as dist
+    import mlcg_b200
+    from mlcg_b200 import nn as bnn
+    from mlcg_b200.backend import KernelProfiler, get_backend
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, n = WORKLOAD["structures_per_gpu"], WORKLOAD["beads"]
+    pos_h, types_h, batch_h = make_inputs(B, n, WORKLOAD["bead_types"], seed=1000 + rank)   # every rank its own replicas
+    model = bnn.GradientsOut(make_model().to(dev), "forces").eval()
+    be = get_backend()
+    n_atoms = torch.full((B,), n, device=dev)
+    pos_d, types_d, batch_d = pos_h.to(dev), types_h.to(dev), batch_h.to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step_resident():
+        data = mlcg_b200.AtomicData(pos=pos_d.clone(), atom_types=types_d, batch=batch_d, n_atoms=n_atoms)
+        out = model(data)
+        return out.out["SchNet"]["energy"], out.out["SchNet"]["forces"]
+
+    pin = lambda t: t.pin_memory()
+    pos_p, types_p, batch_p = pin(pos_h), pin(types_h), pin(batch_h)
+
+    def step_e2e():
+        data = mlcg_b200.AtomicData(pos=pos_p.to(dev, non_blocking=True), atom_types=types_p.to(dev, non_blocking=True),
+                                    batch=batch_p.to(dev, non_blocking=True), n_atoms=n_atoms)
+        out = model(data)
+        return out.out["SchNet"]["energy"].cpu(), out.out["SchNet"]["forces"].cpu()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    torch.cuda.synchronize()
+    n_edges = int(be.radius_graph(pos_d, torch.arange(B + 1, device=dev) * n, WORKLOAD["cutoff_A"], 1000, False, 1)["edge_index"].shape[1])
+
+    # ---- timed region: K steps, device time per step (L2 flushed outside the event pair), kernels profiled live
+    prof = KernelProfiler()
+    be.profiler = prof
+    clocks = ClockSampler(local)
+    clocks.start()
+    barrier()
+    pairs = []
+    for _ in range(args.steps):
+        flush.fill_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step_resident()
+        b.record()
+        pairs.append((a, b))
+    barrier()
+    ms_total = sum(a.elapsed_time(b) for a, b in pairs)
+    stats = prof.summary()
+    be.profiler = None
+    clk = clocks.stop()
+
+    # ---- end to end through the public API: pinned host inputs in, energies and forces back to the host
+    step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_e2e()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+
+    t = torch.tensor([ms_total, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms = float(t[0]), float(t[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    hbm_peak = peaks.get("hbm_gbs", 6650.0)
+    tf_peak = peaks.get("bf16_tflops_sustained", 1400.0)
+    peak_src = "measured" if peaks else "fallback"
+    top = max(stats.items(), key=lambda kv: kv[1]["ms"])
+    name, st = top
+    per_launch_ms = st["ms"] / max(st["calls"], 1)
+    if name == "gemm":
+        achieved = st["flops"] / max(st["ms"], 1e-9) / 1e9            # TFLOP/s
+        roof = dict(kernel="gemm_kernel<float> (filter-network GEMMs, fp32 FMA)", bound="tensor", achieved=achieved, peak=tf_peak,
+                    unit="TFLOP/s", frac=achieved / tf_peak, traffic=None, peak_source=f"{peak_src} bf16 sustained", avg_launch_ms=per_launch_ms)
+    else:
+        achieved = st["bytes"] / max(st["ms"], 1e-9) / 1e6            # GB/s
+        roof = dict(kernel=name, bound="hbm", achieved=achieved, peak=hbm_peak, unit="GB/s", frac=achieved / hbm_peak, traffic=None,
+                    peak_source=f"{peak_src} copy bandwidth", avg_launch_ms=per_launch_ms)
+    kernels = {k: dict(calls=v["calls"], ms_per_step=v["ms"] / args.steps,
+                       GBps=(v["bytes"] / v["ms"] / 1e6 if v["ms"] > 0 else None),
+                       TFLOPs=(v["flops"] / v["ms"] / 1e9 if v["ms"] > 0 and v["flops"] else None)) for k, v in sorted(stats.items(), key=lambda kv: -kv[1]["ms"])}
+
+    cpu = None
+    if world == 1 or True:
+        sample_B = 32
+        v, ms, cores = cpu_leg(sample_B, 3, 1)
+        cpu = dict(value=v, unit="structures/s", cores=cores, kind="port",
+                   sample=f"{sample_B} structures of the same workload per step, 3 steps after 1 warm-up, torch CPU float32 + C radius oracle")
+
+    value = world * B * args.steps / (ms_total / 1e3)
+    h2d = pos_h.numel() * 4 + types_h.numel() * 8 + batch_h.numel() * 8
+    d2h = B * 4 + pos_h.numel() * 4
+    line = dict(metric=METRIC, value=value, unit="structures/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+                ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(WORKLOAD, edges_per_gpu=n_edges, global_structures=world * B, parallelism=f"replicas x{world}, no collective"),
+                e2e=dict(value=world * B * args.steps / (e2e_ms / 1e3), unit="structures/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+                gpu_launches=prof.total_launches, roofline=roof, cpu_baseline=cpu, clocks=clk, kernels=kernels,
+                edges_per_s=world * n_edges * args.steps / (ms_total / 1e3))
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -52,11 +52,94 @@ def _dt(t: torch.Tensor) -> int:
         raise TypeError(f"mlcg_b200: unsupported dtype {t.dtype}; use float32 or float64") from None
 
 
+class KernelProfiler:
+    """Per-operator launch counts, device time (CUDA events on the launching stream) and algorithmic work.
+
+    Attach with ``get_backend().profiler = KernelProfiler()``; ``summary()`` synchronises and returns
+    ``{name: {"calls", "launches", "ms", "bytes", "flops"}}``."""
+
+    def __init__(self, time_kernels: bool = True):
+        self.time_kernels = time_kernels
+        self.records = []      # (name, start_event, end_event)
+        self.stats = {}
+
+    def begin(self, name, launches, nbytes, flops):
+        st = self.stats.setdefault(name, {"calls": 0, "launches": 0, "ms": 0.0, "bytes": 0, "flops": 0})
+        st["calls"] += 1
+        st["launches"] += launches
+        st["bytes"] += int(nbytes)
+        st["flops"] += int(flops)
+        if not self.time_kernels:
+            return None
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        return ev
+
+    def end(self, name, start):
+        if start is None:
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.records.append((name, start, ev))
+
+    def summary(self):
+        torch.cuda.synchronize()
+        for name, a, b in self.records:
+            self.stats[name]["ms"] += a.elapsed_time(b)
+        self.records = []
+        return self.stats
+
+    @property
+    def total_launches(self):
+        return sum(v["launches"] for v in self.stats.values())
+
+
 class CudaBackend:
     name = "cuda"
 
     def __init__(self):
         self.lib = _lib.load()
+        self.profiler = None
+
+    def _run(self, name, fn, args, what=None, launches=1, nbytes=0, flops=0):
+        prof = self.profiler
+        ev = prof.begin(name, launches, nbytes, flops) if prof is not None else None
+        _lib.check(fn(*args), what or name)
+        if prof is not None:
+            prof.end(name, ev)
+
+    @staticmethod
+    def _work(name, v):
+        """Algorithmic bytes / flops and kernel launches of one call (index tensors counted at their stored width)."""
+        es = lambda t: t.element_size()
+        if name == "radius_count":
+            return dict(launches=5, nbytes=v["N"] * (12 + 4 + 8) + v["B"] * 8)
+        if name == "radius_fill":
+            return dict(launches=1, nbytes=16 * v["E"] + 20 * v["N"])       # [2,E] int64 written, pos + structure ids read
+        if name == "seg_mul_sum":
+            V, a = v["V"], v["a"]
+            return dict(nbytes=V.numel() * es(V) + V.shape[0] * 4 + (a.numel() + v["N"] * v["F"]) * es(V) + v["N"] * 8,
+                        flops=2 * V.numel())
+        if name == "edge_mul":
+            a = v["a"]
+            return dict(nbytes=v["E"] * v["F"] * es(a) + v["E"] * 8 + 2 * a.numel() * es(a), flops=v["E"] * v["F"])
+        if name == "gemm":
+            A = v["A"]
+            M, N, K = v["M"], v["N"], v["K"]
+            return dict(launches=2 if v["wsb"] else 1, nbytes=(M * K + N * K + M * N) * es(A), flops=2 * M * N * K)
+        if name in ("rbf_expand", "rbf_contract"):
+            d = v["d"]
+            R = v["spec"].num_rbf
+            return dict(nbytes=d.numel() * es(d) * (R + 1 + (1 if name == "rbf_contract" else 0)), flops=d.numel() * R * 20)
+        if name == "edge_diff":
+            return dict(nbytes=v["E"] * (8 + 3 * es(v["pos"])) + v["pos"].numel() * es(v["pos"]))
+        if name == "node_scatter_diff":
+            g = v["g"]
+            return dict(nbytes=2 * g.numel() * es(g) + g.shape[0] * 4 + v["N"] * (16 + 3 * es(g)))
+        if name == "prior_terms":
+            m = v["mapping"]
+            return dict(nbytes=m.numel() * 8 + v["M"] * 8 + v["params"].numel() * es(v["params"]) + 2 * v["pos"].numel() * es(v["pos"]))
+        return {}
 
     # ------------------------------------------------------------------ radius graph
     def batch_to_ptr(self, batch: torch.Tensor, B: int) -> torch.Tensor:
@@ -64,7 +147,7 @@ class CudaBackend:
         batch = batch.contiguous()
         ptr = torch.empty(B + 1, dtype=torch.int64, device=batch.device)
         with torch.cuda.device(batch.device):
-            _lib.check(self.lib.mlcgb_batch_to_ptr(_ptr(batch), batch.numel(), B, _ptr(ptr), _stream()), "batch_to_ptr")
+            self._run("batch_to_ptr", self.lib.mlcgb_batch_to_ptr, (_ptr(batch), batch.numel(), B, _ptr(ptr), _stream(),), **self._work("batch_to_ptr", locals()))
         return ptr
 
     def radius_graph(self, pos, ptr, r, max_num_neighbors, loop, rule, want_distance=False, want_batch=True):
@@ -79,8 +162,8 @@ class CudaBackend:
             deg = torch.empty(max(N, 1), dtype=torch.int32, device=dev)
             offsets = torch.empty(N + 1, dtype=torch.int64, device=dev)
             status = torch.zeros(4, dtype=torch.int32, device=dev)
-            _lib.check(self.lib.mlcgb_radius_count(_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(max_num_neighbors), int(loop), int(rule),
-                                                   _ptr(ws), ws_bytes, _ptr(deg), _ptr(offsets), _ptr(status), _stream()), "radius_count")
+            self._run("radius_count", self.lib.mlcgb_radius_count, (_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(max_num_neighbors), int(loop), int(rule),
+                                                   _ptr(ws), ws_bytes, _ptr(deg), _ptr(offsets), _ptr(status), _stream(),), **self._work("radius_count", locals()))
             tail = torch.stack([offsets[N], status[0].to(torch.int64)]).cpu()   # the one host read: E and the status word
             E, st = int(tail[0]), int(tail[1])
             ei = torch.empty((2, E), dtype=torch.int64, device=dev)
@@ -88,8 +171,8 @@ class CudaBackend:
             mb = torch.empty(E, dtype=torch.int64, device=dev) if want_batch else None
             r0 = torch.empty(E, dtype=torch.int32, device=dev)
             r1 = torch.empty(E, dtype=torch.int32, device=dev)
-            _lib.check(self.lib.mlcgb_radius_fill(_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(loop), _ptr(ws), ws_bytes, _ptr(offsets), E,
-                                                  _ptr(ei), _ptr(dist), _ptr(mb), _ptr(r0), _ptr(r1), _ptr(status), _stream()), "radius_fill")
+            self._run("radius_fill", self.lib.mlcgb_radius_fill, (_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(loop), _ptr(ws), ws_bytes, _ptr(offsets), E,
+                                                  _ptr(ei), _ptr(dist), _ptr(mb), _ptr(r0), _ptr(r1), _ptr(status), _stream(),), **self._work("radius_fill", locals()))
         return dict(edge_index=ei, distance=dist, mapping_batch=mb, row0=r0, row1=r1, offsets=offsets, status=st)
 
     def edge_twin(self, row0, row1, offsets, N):
@@ -99,7 +182,7 @@ class CudaBackend:
         twin = torch.empty(E, dtype=torch.int32, device=row0.device)
         status = torch.zeros(4, dtype=torch.int32, device=row0.device)
         with torch.cuda.device(row0.device):
-            _lib.check(self.lib.mlcgb_edge_twin(_ptr(row0), _ptr(row1), _ptr(offsets), E, N, _ptr(twin), _ptr(status), _stream()), "edge_twin")
+            self._run("edge_twin", self.lib.mlcgb_edge_twin, (_ptr(row0), _ptr(row1), _ptr(offsets), E, N, _ptr(twin), _ptr(status), _stream(),), **self._work("edge_twin", locals()))
         return twin, status
 
     # ------------------------------------------------------------------ geometry
@@ -110,7 +193,7 @@ class CudaBackend:
         out = torch.empty((E, 3), dtype=pos.dtype, device=pos.device)
         status = torch.zeros(4, dtype=torch.int32, device=pos.device)
         with torch.cuda.device(pos.device):
-            _lib.check(self.lib.mlcgb_edge_diff(_ptr(pos), _dt(pos), _ptr(row0), _ptr(row1), E, pos.shape[0], _ptr(out), _ptr(status), _stream()), "edge_diff")
+            self._run("edge_diff", self.lib.mlcgb_edge_diff, (_ptr(pos), _dt(pos), _ptr(row0), _ptr(row1), E, pos.shape[0], _ptr(out), _ptr(status), _stream(),), **self._work("edge_diff", locals()))
         return out
 
     def node_scatter_diff(self, g, ptr_in, perm_in, ptr_out, perm_out, N):
@@ -118,8 +201,8 @@ class CudaBackend:
         g = g.contiguous()
         out = torch.empty((N, 3), dtype=g.dtype, device=g.device)
         with torch.cuda.device(g.device):
-            _lib.check(self.lib.mlcgb_node_scatter_diff(_ptr(g), _dt(g), _ptr(ptr_in), _ptr(perm_in), _ptr(ptr_out), _ptr(perm_out), N,
-                                                        g.shape[0], _ptr(out), _stream()), "node_scatter_diff")
+            self._run("node_scatter_diff", self.lib.mlcgb_node_scatter_diff, (_ptr(g), _dt(g), _ptr(ptr_in), _ptr(perm_in), _ptr(ptr_out), _ptr(perm_out), N,
+                                                        g.shape[0], _ptr(out), _stream(),), **self._work("node_scatter_diff", locals()))
         return out
 
     # ------------------------------------------------------------------ radial basis
@@ -135,7 +218,7 @@ class CudaBackend:
         s, keep = self._spec(spec, d.dtype)
         out = torch.empty((d.numel(), spec.num_rbf), dtype=d.dtype, device=d.device)
         with torch.cuda.device(d.device):
-            _lib.check(self.lib.mlcgb_rbf_expand(_ptr(d), _dt(d), d.numel(), ctypes.byref(s), order, _ptr(out), _stream()), "rbf_expand")
+            self._run("rbf_expand", self.lib.mlcgb_rbf_expand, (_ptr(d), _dt(d), d.numel(), ctypes.byref(s), order, _ptr(out), _stream(),), **self._work("rbf_expand", locals()))
         return out
 
     def rbf_contract(self, d, G, spec: RbfSpec, order: int):
@@ -144,7 +227,7 @@ class CudaBackend:
         s, keep = self._spec(spec, d.dtype)
         out = torch.empty(d.numel(), dtype=d.dtype, device=d.device)
         with torch.cuda.device(d.device):
-            _lib.check(self.lib.mlcgb_rbf_contract(_ptr(d), _ptr(G), _dt(d), d.numel(), ctypes.byref(s), order, _ptr(out), _stream()), "rbf_contract")
+            self._run("rbf_contract", self.lib.mlcgb_rbf_contract, (_ptr(d), _ptr(G), _dt(d), d.numel(), ctypes.byref(s), order, _ptr(out), _stream(),), **self._work("rbf_contract", locals()))
         return out
 
     # ------------------------------------------------------------------ CFConv primitives
@@ -154,7 +237,7 @@ class CudaBackend:
         F = V.shape[1]
         out = torch.empty((N, F), dtype=V.dtype, device=V.device)
         with torch.cuda.device(V.device):
-            _lib.check(self.lib.mlcgb_seg_mul_sum(_ptr(a), _ptr(V), _dt(V), _ptr(ptr), _ptr(nbr), _ptr(eperm), N, V.shape[0], F, _ptr(out), _stream()), "seg_mul_sum")
+            self._run("seg_mul_sum", self.lib.mlcgb_seg_mul_sum, (_ptr(a), _ptr(V), _dt(V), _ptr(ptr), _ptr(nbr), _ptr(eperm), N, V.shape[0], F, _ptr(out), _stream(),), **self._work("seg_mul_sum", locals()))
         return out
 
     def edge_mul(self, a, b, ia, ib):
@@ -163,7 +246,7 @@ class CudaBackend:
         E, F = ia.numel(), a.shape[1]
         out = torch.empty((E, F), dtype=a.dtype, device=a.device)
         with torch.cuda.device(a.device):
-            _lib.check(self.lib.mlcgb_edge_mul(_ptr(a), _ptr(b), _dt(a), _ptr(ia), _ptr(ib), E, F, _ptr(out), _stream()), "edge_mul")
+            self._run("edge_mul", self.lib.mlcgb_edge_mul, (_ptr(a), _ptr(b), _dt(a), _ptr(ia), _ptr(ib), E, F, _ptr(out), _stream(),), **self._work("edge_mul", locals()))
         return out
 
     # ------------------------------------------------------------------ GEMM
@@ -184,7 +267,7 @@ class CudaBackend:
             ws = torch.empty(wsb, dtype=torch.uint8, device=A.device) if wsb else None
             if bias is not None:
                 bias = bias.contiguous()
-            _lib.check(self.lib.mlcgb_gemm(mode, _ptr(A), _ptr(B), _ptr(bias), dt, M, N, K, _ptr(C), _ptr(ws), wsb, _stream()), "gemm")
+            self._run("gemm", self.lib.mlcgb_gemm, (mode, _ptr(A), _ptr(B), _ptr(bias), dt, M, N, K, _ptr(C), _ptr(ws), wsb, _stream(),), **self._work("gemm", locals()))
         return C
 
     def segment_sum(self, x, ptr):
@@ -193,7 +276,7 @@ class CudaBackend:
         B = ptr.numel() - 1
         out = torch.empty(B, dtype=x.dtype, device=x.device)
         with torch.cuda.device(x.device):
-            _lib.check(self.lib.mlcgb_segment_sum(_ptr(x), _dt(x), _ptr(ptr), B, _ptr(out), _stream()), "segment_sum")
+            self._run("segment_sum", self.lib.mlcgb_segment_sum, (_ptr(x), _dt(x), _ptr(ptr), B, _ptr(out), _stream(),), **self._work("segment_sum", locals()))
         return out
 
     # ------------------------------------------------------------------ priors
@@ -206,8 +289,8 @@ class CudaBackend:
         grad = torch.zeros((N, 3), dtype=pos.dtype, device=pos.device) if want_grad else None
         status = torch.zeros(4, dtype=torch.int32, device=pos.device)
         with torch.cuda.device(pos.device):
-            _lib.check(self.lib.mlcgb_prior_terms(kind, _ptr(pos), _dt(pos), _ptr(mapping), _ptr(mapping_batch), _ptr(params), params.shape[0], M, N, B,
-                                                  _ptr(energy), _ptr(grad), _ptr(status), _stream()), "prior_terms")
+            self._run("prior_terms", self.lib.mlcgb_prior_terms, (kind, _ptr(pos), _dt(pos), _ptr(mapping), _ptr(mapping_batch), _ptr(params), params.shape[0], M, N, B,
+                                                  _ptr(energy), _ptr(grad), _ptr(status), _stream(),), **self._work("prior_terms", locals()))
         return energy, grad
 
 

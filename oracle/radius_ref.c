@@ -90,9 +90,10 @@ DEFINE_ORACLE(radius_ref_f64, double, sqrt)
 
 /*
  * exclusion_pairs.cpp:7-62 — sort pairs (x, y) by (y, x), return the xs and a CSR
- * pointer over y of length num_nodes+1. Worked example from the comment at
- * exclusion_pairs.cpp:16-18:
- *   pairs [(2,1),(1,2),(3,2),(2,2),(2,3)], num_nodes 4 -> xs [2,1,3,2,2], ptr [0,1,4,5,5]
+ * pointer over y of length num_nodes+1, indexed by 0-based node as radius.cu:122-123 reads it.
+ * For the input of the comment at exclusion_pairs.cpp:16-18, pairs [(2,1),(1,2),(3,2),(2,2),(2,3)]
+ * with num_nodes 4, the code gives xs [2,1,2,3,2], ptr [0,0,1,4,5] (the numbers printed in that
+ * comment are not what the code below it computes; the code is followed here).
  */
 typedef struct { int64_t x, y; } pair_t;
 static int pair_cmp(const void *a, const void *b) {

@@ -1,0 +1,154 @@
+"""Each CUDA primitive, through the C ABI, against its oracle restatement on the same seeded inputs."""
+import numpy as np
+import pytest
+import torch
+
+from mlcg_b200 import autograd as ag
+from mlcg_b200.backend import RbfSpec, get_backend
+from oracle.primitives import OracleBackend
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+ORA = OracleBackend()
+
+
+def tol(dtype):
+    return dict(rtol=1e-12, atol=1e-12) if dtype == torch.float64 else dict(rtol=2e-5, atol=2e-6)
+
+
+def random_graph(N, deg, gen):
+    """Symmetric-free random multigraph sorted by row0, plus its plan on CPU (built with torch ops)."""
+    E = N * deg
+    row0 = torch.sort(torch.randint(0, N, (E,), generator=gen)).values
+    row1 = torch.randint(0, N, (E,), generator=gen)
+    return torch.stack([row0, row1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("F", [128, 32, 20, 7, 1])
+def test_seg_mul_sum_and_edge_mul(dtype, F):
+    gen = torch.Generator().manual_seed(F)
+    N = 300
+    ei = random_graph(N, 9, gen)
+    plan = ag.EdgePlan.from_edge_index(ei, N)
+    a = torch.randn(N, F, dtype=dtype, generator=gen)
+    V = torch.randn(ei.shape[1], F, dtype=dtype, generator=gen)
+    be = get_backend()
+    for ptr, nbr, perm in [(plan.ptr_in, plan.nbr_in, plan.perm_in), (plan.ptr_out, plan.nbr_out, plan.perm_out)]:
+        want = ORA.seg_mul_sum(a, V, ptr, nbr, perm, N)
+        got = be.seg_mul_sum(a.to(DEV), V.to(DEV), ptr.to(DEV), nbr.to(DEV), None if perm is None else perm.to(DEV), N)
+        assert torch.allclose(got.cpu(), want, rtol=1e-5 if dtype == torch.float32 else 1e-12, atol=1e-5 if dtype == torch.float32 else 1e-12)
+    want = ORA.edge_mul(a, a * 2, plan.row0, plan.row1)
+    got = be.edge_mul(a.to(DEV), (a * 2).to(DEV), plan.row0.to(DEV), plan.row1.to(DEV))
+    assert torch.equal(got.cpu(), want)
+    # run-to-run reproducibility of the ordered sum
+    again = be.seg_mul_sum(a.to(DEV), V.to(DEV), plan.ptr_in.to(DEV), plan.nbr_in.to(DEV), plan.perm_in.to(DEV), N)
+    again2 = be.seg_mul_sum(a.to(DEV), V.to(DEV), plan.ptr_in.to(DEV), plan.nbr_in.to(DEV), plan.perm_in.to(DEV), N)
+    assert torch.equal(again, again2)
+
+
+def test_seg_mul_sum_empty_segments_and_no_edges():
+    be = get_backend()
+    N, F = 5, 8
+    ptr = torch.tensor([0, 0, 3, 3, 3, 4], device=DEV)
+    nbr = torch.tensor([1, 2, 4, 0], dtype=torch.int32, device=DEV)
+    a = torch.arange(N * F, dtype=torch.float32, device=DEV).view(N, F)
+    V = torch.ones(4, F, device=DEV)
+    out = be.seg_mul_sum(a, V, ptr, nbr, None, N)
+    assert torch.equal(out[0], torch.zeros(F, device=DEV)) and torch.equal(out[1], a[1] + a[2] + a[4]) and torch.equal(out[4], a[0])
+    z = be.seg_mul_sum(a, torch.zeros(0, F, device=DEV), torch.zeros(N + 1, dtype=torch.int64, device=DEV),
+                       torch.zeros(0, dtype=torch.int32, device=DEV), None, N)
+    assert not z.any()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_edge_geometry(dtype):
+    gen = torch.Generator().manual_seed(0)
+    N = 200
+    ei = random_graph(N, 6, gen)
+    plan = ag.EdgePlan.from_edge_index(ei, N)
+    pos = torch.randn(N, 3, dtype=dtype, generator=gen)
+    g = torch.randn(ei.shape[1], 3, dtype=dtype, generator=gen)
+    be = get_backend()
+    assert torch.equal(be.edge_diff(pos.to(DEV), plan.row0.to(DEV), plan.row1.to(DEV)).cpu(), ORA.edge_diff(pos, plan.row0, plan.row1))
+    got = be.node_scatter_diff(g.to(DEV), plan.ptr_in.to(DEV), plan.perm_in.to(DEV), plan.ptr_out.to(DEV), None, N)
+    assert torch.allclose(got.cpu(), ORA.node_scatter_diff(g, plan.ptr_in, plan.perm_in, plan.ptr_out, None, N), **tol(dtype))
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+@pytest.mark.parametrize("cutoff_kind,lower", [(1, 0.0), (1, 1.5), (0, 0.0)])
+@pytest.mark.parametrize("order", [0, 1, 2, 3])
+def test_rbf_derivatives_float64(kind, cutoff_kind, lower, order):
+    """Taylor-arithmetic kernel vs nested automatic differentiation of the oracle expression."""
+    from oracle import schnet_ref
+    upper, R = 9.0, 12
+    p0, p1 = (schnet_ref.gaussian_params(lower, upper, R, torch.float64) if kind == 0 else schnet_ref.expnormal_params(lower, upper, R, torch.float64))
+    spec = RbfSpec(kind, R, cutoff_kind, lower, upper, 5.0 / (upper - lower), p0, p1.reshape(-1))
+    d = torch.linspace(0.3, 10.0, 57, dtype=torch.float64)
+    want = ORA.rbf_expand(d, spec, order)
+    spec_gpu = RbfSpec(kind, R, cutoff_kind, lower, upper, 5.0 / (upper - lower), p0.to(DEV), p1.reshape(-1).to(DEV))
+    got = get_backend().rbf_expand(d.to(DEV), spec_gpu, order).cpu()
+    scale = float(want.abs().max()) + 1e-30
+    assert torch.allclose(got, want, rtol=1e-9, atol=1e-11 * scale)
+    G = torch.randn(57, R, dtype=torch.float64, generator=torch.Generator().manual_seed(1))
+    got_c = get_backend().rbf_contract(d.to(DEV), G.to(DEV), spec_gpu, order).cpu()
+    assert torch.allclose(got_c, (G * want).sum(1), rtol=1e-9, atol=1e-10 * scale)
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+def test_rbf_float32_matches_reference_expression(kind):
+    from oracle import schnet_ref
+    upper, R = 15.0, 128
+    p0, p1 = (schnet_ref.gaussian_params(0.0, upper, R) if kind == 0 else schnet_ref.expnormal_params(0.0, upper, R))
+    spec = RbfSpec(kind, R, 1, 0.0, upper, 5.0 / upper, p0, p1.reshape(-1))
+    d = torch.rand(2000, generator=torch.Generator().manual_seed(0)) * 16.0
+    want = ORA.rbf_expand(d, spec, 0)
+    got = get_backend().rbf_expand(d.to(DEV), RbfSpec(kind, R, 1, 0.0, upper, 5.0 / upper, p0.to(DEV), p1.reshape(-1).to(DEV)), 0).cpu()
+    assert torch.allclose(got, want, rtol=1e-5, atol=2e-6)
+    assert not got[d >= upper].any()                       # envelope is exactly zero at and beyond the cutoff
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("M,N,K", [(1000, 128, 128), (333, 128, 50), (77, 20, 33), (5, 1, 3), (4096, 128, 128)])
+def test_gemm_modes(dtype, M, N, K):
+    gen = torch.Generator().manual_seed(M + N + K)
+    be = get_backend()
+    t = dict(rtol=1e-11, atol=1e-11) if dtype == torch.float64 else dict(rtol=1e-4, atol=1e-4)
+    X, W, b = torch.randn(M, K, dtype=dtype, generator=gen), torch.randn(N, K, dtype=dtype, generator=gen), torch.randn(N, dtype=dtype, generator=gen)
+    assert torch.allclose(be.gemm(0, X.to(DEV), W.to(DEV), b.to(DEV)).cpu(), (X.double() @ W.double().t() + b.double()).to(dtype), **t)
+    assert torch.allclose(be.gemm(0, X.to(DEV), W.to(DEV)).cpu(), (X.double() @ W.double().t()).to(dtype), **t)
+    G = torch.randn(M, N, dtype=dtype, generator=gen)
+    assert torch.allclose(be.gemm(1, G.to(DEV), W.to(DEV)).cpu(), (G.double() @ W.double()).to(dtype), **t)
+    t2 = dict(rtol=1e-10, atol=1e-10) if dtype == torch.float64 else dict(rtol=2e-4, atol=2e-3)
+    assert torch.allclose(be.gemm(2, G.to(DEV), X.to(DEV)).cpu(), (G.double().t() @ X.double()).to(dtype), **t2)
+
+
+def test_gemm_weight_gradient_over_many_edges_is_reproducible():
+    gen = torch.Generator().manual_seed(0)
+    G, X = torch.randn(200000, 128, generator=gen).to(DEV), torch.randn(200000, 128, generator=gen).to(DEV)
+    be = get_backend()
+    a, b = be.gemm(2, G, X), be.gemm(2, G, X)
+    assert torch.equal(a, b)
+    assert torch.allclose(a.cpu(), (G.double().t() @ X.double()).float().cpu(), rtol=1e-3, atol=0.05)
+
+
+def test_segment_sum():
+    x = torch.randn(1000, dtype=torch.float64, generator=torch.Generator().manual_seed(0))
+    ptr = torch.tensor([0, 0, 10, 500, 500, 1000])
+    assert torch.allclose(get_backend().segment_sum(x.to(DEV), ptr.to(DEV)).cpu(), ORA.segment_sum(x, ptr))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_prior_terms(dtype):
+    from helpers import prior_setup
+    data, priors = prior_setup(30, 5, 4, torch.Generator().manual_seed(0))
+    pos = data.pos.to(dtype)
+    for kind, name in enumerate(["bonds", "angles", "dihedrals", "repulsion"]):
+        p = priors[name]
+        nl = data.neighbor_list[name]
+        params = p._params(data).to(dtype)
+        e_ref, g_ref = ORA.prior_terms(kind, pos, nl["index_mapping"], nl["mapping_batch"], params, 5)
+        e, g = get_backend().prior_terms(kind, pos.to(DEV), nl["index_mapping"].to(DEV), nl["mapping_batch"].to(DEV), params.to(DEV), 5)
+        rt = 1e-10 if dtype == torch.float64 else 2e-5
+        assert torch.allclose(e.cpu(), e_ref, rtol=rt), name
+        assert torch.allclose(g.cpu(), g_ref, rtol=10 * rt, atol=rt * float(g_ref.abs().max())), name

@@ -1,0 +1,139 @@
+"""The SchNet energy / force path on the GPU against the reference fixtures and the CPU oracle.
+
+Tolerances are the ones the build targets for float32: energies 1e-5 relative, forces 1e-4 kcal/mol/A absolute."""
+import numpy as np
+import pytest
+import torch
+
+import mlcg_b200
+from mlcg_b200 import nn as bnn
+from oracle import radius_ref, schnet_ref
+
+from helpers import data_from_case, prior_setup, random_walk_chain, schnet_from_case
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+E_RTOL, F_ATOL = 1e-5, 1e-4
+CASES = ["schnet_gaussian_f32", "schnet_expnormal_f32", "schnet_expnormal_trainable_f64"]
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_golden_energy_forces(golden, name):
+    c = golden[name]
+    model = bnn.GradientsOut(schnet_from_case(c, device=DEV), "forces").eval()
+    out = model(data_from_case(c, device=DEV))
+    f64 = c["pos"].dtype == torch.float64
+    assert torch.allclose(out.out["SchNet"]["energy"].cpu(), c["energy"], rtol=1e-10 if f64 else E_RTOL, atol=1e-10 if f64 else 1e-5)
+    assert torch.allclose(out.out["SchNet"]["forces"].cpu(), c["forces"], rtol=0, atol=1e-9 if f64 else F_ATOL)
+
+
+@pytest.mark.parametrize("name", CASES)
+def test_golden_force_matching_gradients(golden, name):
+    c = golden[name]
+    net = schnet_from_case(c, device=DEV)
+    out = bnn.GradientsOut(net, "forces").train()(data_from_case(c, device=DEV))
+    loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], c["target_forces"].to(DEV))
+    loss.backward()
+    f64 = c["pos"].dtype == torch.float64
+    assert torch.allclose(loss.detach().cpu(), c["loss"], rtol=1e-9 if f64 else 1e-5)
+    grads = dict(net.named_parameters())
+    for k, g in c["param_grads"].items():
+        tol_ = 1e-8 if f64 else 1e-4
+        assert torch.allclose(grads[k].grad.cpu(), g, rtol=tol_, atol=tol_ * float(g.abs().max() + 1e-30)), k
+
+
+def _make(kind, B, n, n_types, upper, R, H, L, seed, min_dist=None, jitter=0.0):
+    torch.manual_seed(seed)
+    cut = bnn.CosineCutoff(0.0, upper)
+    rbf = bnn.GaussianBasis(cut, R) if kind == "gaussian" else bnn.ExpNormalBasis(cut, R, trainable=False)
+    model = bnn.StandardSchNet(rbf, cut, [H], hidden_channels=H, embedding_size=n_types, num_filters=H, num_interactions=L)
+    gen = torch.Generator().manual_seed(seed)
+    pos = torch.cat([random_walk_chain(n, gen, jitter=jitter, min_dist=min_dist) for _ in range(B)])
+    types_ = torch.randint(0, n_types, (B * n,), generator=gen)
+    return model, pos, types_, torch.arange(B).repeat_interleave(n)
+
+
+def _oracle(model, kind, upper, L, pos, types_, batch, B):
+    cut = {"cutoff": "cosine", "lower": 0.0, "upper": upper}
+    spec = {"kind": kind, "rbf_cutoff": cut, "cutoff": cut, "activation": "tanh", "num_interactions": L}
+    sd = {k: v.detach().cpu() for k, v in model.state_dict().items()}
+    ei = torch.from_numpy(radius_ref.radius_graph_c(pos.numpy(), radius_ref.batch_to_ptr(batch.numpy(), B), upper, 1000, False, "cluster"))
+    e, f, _ = schnet_ref.energy_and_forces(lambda p: schnet_ref.schnet_energy(sd, spec, p, types_, batch, ei, B), pos)
+    return e, f, ei
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(kind="gaussian", B=64, n=10, n_types=10, upper=30.0, R=50, H=128, L=2, jitter=0.3),            # the CPU-runnable configuration
+    dict(kind="expnormal", B=24, n=100, n_types=20, upper=15.0, R=128, H=128, L=3, min_dist=4.0),       # 100-bead chains, 3 blocks
+    dict(kind="expnormal", B=8, n=268, n_types=20, upper=12.0, R=128, H=128, L=3),                      # simulation-size chains
+])
+def test_full_shape_models_vs_oracle(cfg):
+    kind, B, n, upper, L = cfg["kind"], cfg["B"], cfg["n"], cfg["upper"], cfg["L"]
+    model, pos, types_, batch = _make(kind, B, n, cfg["n_types"], upper, cfg["R"], cfg["H"], L, 0, cfg.get("min_dist"), cfg.get("jitter", 0.0))
+    e_ref, f_ref, ei = _oracle(model, kind, upper, L, pos, types_, batch, B)
+    data = mlcg_b200.AtomicData(pos=pos.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV), n_atoms=torch.full((B,), n).to(DEV))
+    out = bnn.GradientsOut(model.to(DEV), "forces").eval()(data)
+    assert torch.allclose(out.out["SchNet"]["energy"].cpu(), e_ref, rtol=E_RTOL, atol=E_RTOL * float(e_ref.abs().max()))
+    assert float((out.out["SchNet"]["forces"].cpu() - f_ref).abs().max()) < F_ATOL
+
+
+def test_gradcheck_on_device_float64():
+    """First and second derivatives of the whole energy w.r.t. positions, CUDA kernels in float64."""
+    model, pos, types_, batch = _make("expnormal", 2, 7, 4, 9.0, 6, 8, 2, 1, jitter=0.2)
+    model = model.double().to(DEV)
+    B, n = 2, 7
+
+    def energy(p):
+        data = mlcg_b200.AtomicData(pos=p, atom_types=types_.to(DEV), batch=batch.to(DEV), n_atoms=torch.full((B,), n).to(DEV))
+        return model(data).out["SchNet"]["energy"]
+
+    p = pos.double().to(DEV).requires_grad_(True)
+    assert torch.autograd.gradcheck(energy, (p,), eps=1e-6, atol=1e-6, nondet_tol=1e-9)
+    assert torch.autograd.gradgradcheck(energy, (p,), eps=1e-6, atol=1e-5, nondet_tol=1e-9)
+
+
+def test_forces_are_reproducible_run_to_run():
+    model, pos, types_, batch = _make("expnormal", 8, 100, 20, 15.0, 64, 64, 2, 3, min_dist=4.0)
+    m = bnn.GradientsOut(model.to(DEV), "forces").eval()
+    mk = lambda: mlcg_b200.AtomicData(pos=pos.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV), n_atoms=torch.full((8,), 100).to(DEV))
+    a, b = m(mk()), m(mk())
+    assert torch.equal(a.out["SchNet"]["forces"], b.out["SchNet"]["forces"]) and torch.equal(a.out["SchNet"]["energy"], b.out["SchNet"]["energy"])
+
+
+def test_truncated_neighbour_list_uses_general_plan():
+    """max_num_neighbors below the real degree: the graph stops being symmetric and the general edge plan must agree with the oracle."""
+    model, pos, types_, batch = _make("gaussian", 4, 40, 5, 12.0, 20, 32, 2, 4, jitter=0.2)
+    model.max_num_neighbors = 6
+    sd = {k: v.detach() for k, v in model.state_dict().items()}
+    cut = {"cutoff": "cosine", "lower": 0.0, "upper": 12.0}
+    spec = {"kind": "gaussian", "rbf_cutoff": cut, "cutoff": cut, "activation": "tanh", "num_interactions": 2}
+    ei = torch.from_numpy(radius_ref.radius_graph_c(pos.numpy(), radius_ref.batch_to_ptr(batch.numpy(), 4), 12.0, 6, False, "cluster"))
+    e_ref, f_ref, _ = schnet_ref.energy_and_forces(lambda p: schnet_ref.schnet_energy(sd, spec, p, types_, batch, ei, 4), pos)
+    data = mlcg_b200.AtomicData(pos=pos.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV), n_atoms=torch.full((4,), 40).to(DEV))
+    out = bnn.GradientsOut(model.to(DEV), "forces").eval()(data)
+    assert torch.equal(out.neighbor_list["SchNet"]["index_mapping"].cpu(), ei) if "SchNet" in out.neighbor_list else True
+    assert torch.allclose(out.out["SchNet"]["energy"].cpu(), e_ref, rtol=E_RTOL, atol=1e-5)
+    assert float((out.out["SchNet"]["forces"].cpu() - f_ref).abs().max()) < F_ATOL
+
+
+def test_priors_and_sumout_on_device(golden):
+    c = golden["priors_f32"]
+    data, priors = prior_setup(12, 2, c["tables"]["bonds"]["x_0"].shape[0], torch.Generator().manual_seed(0))
+    for k, p in priors.items():
+        p.load_state_dict(c["tables"][k])
+    for mode in ("eval", "train"):
+        for k, p in priors.items():
+            d = mlcg_b200.AtomicData(pos=c["pos"].clone().to(DEV), atom_types=c["atom_types"].to(DEV), batch=c["batch"].to(DEV),
+                                     n_atoms=torch.full((c["B"],), 12).to(DEV),
+                                     neighbor_list={k: mlcg_b200.make_neighbor_list(k, c["mappings"][k].shape[0], c["mappings"][k].to(DEV), c["mapping_batch"][k].to(DEV))})
+            m = bnn.GradientsOut(p.to(DEV), "forces")
+            o = (m.eval() if mode == "eval" else m.train())(d)
+            assert torch.allclose(o.out[k]["energy"].cpu(), c["energy"][k], rtol=2e-5), (mode, k)
+            assert torch.allclose(o.out[k]["forces"].detach().cpu(), c["forces"][k], rtol=1e-4, atol=1e-4 * float(c["forces"][k].abs().max())), (mode, k)
+
+
+def test_extension_is_the_compute_path():
+    """The operators resolve to the CUDA back end of libmlcg_b200.so, not to a substitute."""
+    from mlcg_b200 import _lib, backend
+    be = backend.get_backend()
+    assert be.name == "cuda" and be.lib is _lib.load()

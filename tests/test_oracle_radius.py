@@ -1,0 +1,55 @@
+"""The two radius-graph oracles against each other and against hand-checkable cases."""
+import numpy as np
+import pytest
+
+from oracle import radius_ref
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("rule", ["native", "cluster"])
+@pytest.mark.parametrize("loop", [False, True])
+@pytest.mark.parametrize("max_nn", [2, 5, 1000])
+def test_c_equals_numpy(dtype, rule, loop, max_nn):
+    rng = np.random.default_rng(0)
+    sizes = [0, 17, 1, 40, 0, 33]
+    ptr = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    pos = (rng.random((ptr[-1], 3)) * 6).astype(dtype)
+    a, da = radius_ref.radius_graph_c(pos, ptr, 2.0, max_nn, loop, rule, with_distance=True)
+    b, db = radius_ref.radius_graph_numpy(pos, ptr, 2.0, max_nn, loop, rule, with_distance=True)
+    assert np.array_equal(a, b) and np.array_equal(da, db)
+    assert np.all(np.diff(a[0]) >= 0)                           # centre-major
+    same = a[0][1:] == a[0][:-1]
+    assert np.all(a[1][1:][same] > a[1][:-1][same])             # neighbours ascending
+
+
+def test_strict_cutoff_on_a_lattice():
+    """Integer lattice, integer cutoff: pairs at exactly r are excluded (strict <, radius.cu:134)."""
+    g = np.stack(np.meshgrid(*[np.arange(4)] * 3, indexing="ij"), -1).reshape(-1, 3).astype(np.float32)
+    ei = radius_ref.radius_graph_c(g, np.array([0, 64]), 1.0, 1000, False, "cluster")
+    assert ei.shape[1] == 0
+    ei = radius_ref.radius_graph_c(g, np.array([0, 64]), 1.0000001, 1000, False, "cluster")
+    assert ei.shape[1] == 2 * 3 * 4 * 4 * 3                     # axis neighbours only
+    assert radius_ref.radius_graph_c(g, np.array([0, 64]), 0.0, 1000, True, "native").shape[1] == 0  # r = 0: nothing, not even loops
+
+
+def test_truncation_rules_differ_only_when_self_is_not_reached():
+    # five collinear points, all within range; max_nn = 2
+    pos = np.zeros((5, 3), np.float32)
+    pos[:, 0] = np.arange(5) * 0.1
+    nat = radius_ref.radius_graph_c(pos, np.array([0, 5]), 1.0, 2, False, "native")
+    clu = radius_ref.radius_graph_c(pos, np.array([0, 5]), 1.0, 2, False, "cluster")
+    deg_n, deg_c = np.bincount(nat[0], minlength=5), np.bincount(clu[0], minlength=5)
+    assert deg_n.tolist() == [2, 2, 2, 2, 2]
+    assert deg_c.tolist() == [2, 2, 2, 3, 3]                    # centres 3, 4 have >= 3 lower neighbours: self never reached
+    assert clu[1][clu[0] == 4].tolist() == [0, 1, 2]
+
+
+def test_exclusion_pair_worked_example():
+    """The input of the example in the comment at exclusion_pairs.cpp:16-18, with the result the CODE below
+    that comment produces (two stable sorts -> ordered by (y, x); pointer indexed by 0-based node, which is
+    how radius.cu:122-123 reads it).  The comment's own numbers ([2,1,3,2,2] / [0,1,4,5,5]) do not follow
+    from the code: they leave x unsorted inside y = 2 and index the pointer from node 1."""
+    pairs = np.array([[2, 1, 3, 2, 2], [1, 2, 2, 2, 3]])
+    xs, ptr = radius_ref.exclusion_pair_to_ptr(pairs, 4)
+    assert xs.tolist() == [2, 1, 2, 3, 2]
+    assert ptr.tolist() == [0, 0, 1, 4, 5]
