@@ -269,7 +269,7 @@ def run_ours(args):
                        TFLOPs=(v["flops"] / v["ms"] / 1e9 if v["ms"] > 0 and v["flops"] else None)) for k, v in sorted(stats.items(), key=lambda kv: -kv[1]["ms"])}
 
     cpu = None
-    if world == 1 or True:
+    if not args.no_cpu:
         sample_B = 32
         v, ms, cores = cpu_leg(sample_B, 3, 1)
         cpu = dict(value=v, unit="structures/s", cores=cores, kind="port",
@@ -295,7 +295,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--structures", type=int, default=None, help="structures per GPU (default 512; smaller values are for profiler captures)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
     args = ap.parse_args()
+    if args.structures:
+        WORKLOAD["structures_per_gpu"] = args.structures
+        WORKLOAD["workload"] += f" [REDUCED to {args.structures} structures/GPU: not the benchmark configuration]"
     if args.impl == "reference":
         run_reference(args)
     else:
