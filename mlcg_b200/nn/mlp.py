@@ -33,12 +33,19 @@ class MLP(torch.nn.Module):
     def forward(self, x, data=None):
         return self.layers(x)
 
-    def forward_edges(self, x: torch.Tensor) -> torch.Tensor:
+    def forward_edges(self, x: torch.Tensor, frozen: bool = False) -> torch.Tensor:
         """Same function as :meth:`forward`, with every Linear layer run by this package's GEMM kernels
-        (used for the edge-sized filter network, where the row count is the number of edges)."""
+        (used for the edge-sized filter network, where the row count is the number of edges).
+
+        ``frozen=True`` takes the weights out of the autograd graph.  A custom autograd function is told
+        which of its inputs *require* a gradient, not which gradients the caller asked for, so with live
+        weights the edge-sized weight-gradient GEMMs would run even when only forces are wanted."""
         for layer in self.layers:
             if isinstance(layer, torch.nn.Linear):
-                x = MatmulNT.apply(x, layer.weight, layer.bias)
+                w, b = layer.weight, layer.bias
+                if frozen:
+                    w, b = w.detach(), (None if b is None else b.detach())
+                x = MatmulNT.apply(x, w, b)
             else:
                 x = layer(x)
         return x

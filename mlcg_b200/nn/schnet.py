@@ -48,7 +48,9 @@ class CFConv(torch.nn.Module):
         """W[E, F] (schnet.py:340-341)."""
         C = self.cutoff(edge_weight)
         net = self.filter_network
-        h = net.forward_edges(edge_attr) if isinstance(net, MLP) else net(edge_attr)
+        # eval mode evaluates energies and forces only (GradientsOut uses create_graph=False there), so the
+        # filter weights are constants; training mode keeps them differentiable to second order
+        h = net.forward_edges(edge_attr, frozen=not self.training) if isinstance(net, MLP) else net(edge_attr)
         return h * C.view(-1, 1)
 
     def forward(self, x: torch.Tensor, edge_index: torch.Tensor, edge_weight: torch.Tensor, edge_attr: torch.Tensor) -> torch.Tensor:
