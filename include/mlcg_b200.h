@@ -3,7 +3,8 @@
  *
  * Conventions
  *   - Every pointer is a DEVICE pointer unless the comment says "host". The library never allocates,
- *     frees or synchronises: the caller owns inputs, outputs and workspaces and passes the stream.
+ *     frees or synchronises (one entry point, mlcgb_radius_graph_static, waits for its stream once and says so):
+ *     the caller owns inputs, outputs and workspaces and passes the stream.
  *   - `dtype`: 0 = float32, 1 = float64 (the type of positions and of every floating tensor of a call).
  *   - Node tensors are row-major [N, F]; edge tensors are row-major [E, F]; index rows are contiguous.
  *   - Return value: 0 on success, a negative MLCGB_E_* code otherwise (mlcgb_strerror gives the text).
@@ -65,6 +66,25 @@ int mlcgb_radius_fill(const void *pos, int dtype, const int64_t *ptr, int64_t N,
                       void *distance /* [E] or NULL */, int64_t *mapping_batch /* [E] or NULL */,
                       int32_t *row0_i32 /* [E] or NULL */, int32_t *row1_i32 /* [E] or NULL */, int32_t *status,
                       void *stream);
+
+/* Radius graph in one call that allocates nothing.  No counterpart in the reference (mlcg sizes its
+ * outputs with torch and a host read, src/opt_radius/mlcg_opt_radius/radius.cu:236-241,288-292); it exists
+ * for callers that may not allocate device memory at the point of the call: a force routine invoked from
+ * inside another program's integration loop, a plug-in whose host owns all of the GPU's memory, a thread
+ * that must stay off the allocator's locks.  The cell-list scratch is a fixed 3 MiB array inside the
+ * library image (every GPU that loads the library holds it until the process exits); the limits are
+ * N <= 65536 points and B <= 8192 structures, and larger inputs return MLCGB_E_LIMIT.
+ *   deg[N], offsets[N+1] and edge_index[2, capacity] are the caller's; row 0 starts at edge_index, row 1 at
+ *   edge_index + capacity; *n_edges_host (a HOST pointer) receives the number of edges, also when it
+ *   exceeds `capacity`, in which case nothing is written to edge_index and MLCGB_E_LIMIT is returned.
+ * The call waits for the stream once (to read the edge count).  The first call on each device looks up
+ * the scratch address; make that first call outside any stream capture.  All calls on a device share
+ * the scratch: calls that may overlap on the GPU (different streams or threads) race on it and must be
+ * serialised by the caller.  Nothing in the scratch has to start at zero and nothing is kept between calls. */
+int mlcgb_radius_graph_static(const void *pos /* [N,3] */, int dtype, const int64_t *ptr /* [B+1] */, int64_t N, int64_t B,
+                              double r, int64_t max_num_neighbors, int loop, int rule, int32_t *deg /* [N] */,
+                              int64_t *offsets /* [N+1] */, int64_t capacity, int64_t *edge_index /* [2,capacity] */,
+                              int64_t *n_edges_host /* host */, int32_t *status, void *stream);
 
 /* For each edge (a,b) of a centre-sorted list, the position of (b,a); -1 and status bit 2 if absent.
  * No reference counterpart: PyG aggregates at edge_index[1] with atomics (src/mlcg/nn/schnet.py:346);

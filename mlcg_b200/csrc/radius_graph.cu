@@ -527,3 +527,72 @@ int mlcgb_edge_twin(const int32_t *row0, const int32_t *row1, const int64_t *off
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Radius graph for callers that cannot allocate device memory.
+//
+// The two-call path above takes its workspace from the caller (the Python wrapper gets it from torch's
+// caching allocator).  Code that runs where no allocator may be called — a force callback inside
+// another engine's time-step loop, a plug-in whose host forbids cudaMalloc after start-up, a thread
+// that must not take the allocator's locks — uses this single call instead: the cell-list scratch
+// lives in a fixed array that is part of the library image, and inputs and outputs stay the caller's.
+// ------------------------------------------------------------------------------------------------
+namespace mlcgb {
+constexpr int64_t kStaticMaxPoints = 65536;
+constexpr int64_t kStaticMaxStructures = 8192;
+constexpr size_t kStaticScratchBytes = (size_t)3 << 20;   // >= ws_layout(65536, 8192, float64).total
+static __device__ __align__(256) unsigned char g_radius_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void *g_scratch_addr[kMaxDevices] = {nullptr};
+
+// The array's name is only a host-side handle; the device address has to be asked for, once per
+// device, with that device current.
+static int static_scratch_address(void **out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return MLCGB_E_ARG;
+    if (!g_scratch_addr[dev]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_radius_scratch);
+        if (e != cudaSuccess || !p) {
+            g_last_cuda_error = (int)e;
+            return MLCGB_E_LAUNCH;
+        }
+        g_scratch_addr[dev] = p;
+    }
+    *out = g_scratch_addr[dev];
+    return MLCGB_OK;
+}
+}  // namespace mlcgb
+
+extern "C" int mlcgb_radius_graph_static(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r,
+                                         int64_t max_nn, int loop, int rule, int32_t *deg, int64_t *offsets, int64_t capacity,
+                                         int64_t *edge_index, int64_t *n_edges_host, int32_t *status, void *stream) {
+    if (N < 0 || B < 0 || max_nn < 0 || capacity < 0 || !offsets || !status || !ptr || !n_edges_host) return MLCGB_E_ARG;
+    if (dtype != MLCGB_F32 && dtype != MLCGB_F64) return MLCGB_E_ARG;
+    if (N > kStaticMaxPoints || B > kStaticMaxStructures) return MLCGB_E_LIMIT;   // beyond the built-in scratch
+    if (ws_layout(N, B, dtype).total > kStaticScratchBytes) return MLCGB_E_LIMIT;
+    void *scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    auto st = (cudaStream_t)stream;
+    *n_edges_host = 0;
+    int rc = mlcgb_radius_count(pos, dtype, ptr, N, B, r, max_nn, loop, rule, scratch, kStaticScratchBytes, deg, offsets, status, stream);
+    if (rc != MLCGB_OK) return rc;
+    int64_t E = 0;
+    cudaError_t e = cudaMemcpyAsync(&E, offsets + N, sizeof(int64_t), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+        g_last_cuda_error = (int)e;
+        return MLCGB_E_LAUNCH;
+    }
+    *n_edges_host = E;
+    if (E > capacity) return MLCGB_E_LIMIT;   // the caller's edge buffer is too small; n_edges_host says how many are needed
+    if (E == 0 || N == 0) return MLCGB_OK;
+    if (!pos || !edge_index) return MLCGB_E_ARG;
+    // rows of the caller's [2, capacity] buffer
+    FillOut out{edge_index, edge_index + capacity, nullptr, nullptr, nullptr, nullptr};
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        return radius_launch<scalar_t>(true, pos, ptr, N, B, r, 0, loop, 0, scratch, kStaticScratchBytes, dtype, nullptr, offsets, out,
+                                       status, st);
+    });
+}
