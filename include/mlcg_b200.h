@@ -153,6 +153,19 @@ size_t mlcgb_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, int
 int mlcgb_gemm(int mode, const void *A, const void *B, const void *bias /* [N] or NULL */, int dtype, int64_t M,
                int64_t N, int64_t K, void *C, void *workspace, size_t workspace_bytes, void *stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Fused filter network on the tensor cores (tcgen05 / TMEM):
+ *   W[e,:] = ( tanh( phi(d_e) A1^T + b1 ) A2^T ) * C(d_e)
+ * i.e. rbf_layer -> filter_network -> cutoff of CFConv.forward, src/mlcg/nn/schnet.py:340-341 with the
+ * basis of src/mlcg/nn/radial_basis/*.py evaluated in the GEMM prologue.  float32 in / out, F = 128,
+ * R <= 128, tanh activation.  precision 0: fp32-equivalent products (fp16 hi/lo pairs, three tensor-core
+ * products per GEMM, fp32 accumulation); precision 1: bf16 operands, one product.
+ * status bit 3 is set if a tensor-core wait ran out (the output is then incomplete).
+ * ---------------------------------------------------------------------------------------------- */
+int mlcgb_filter_forward(const void *d /* [E] */, int64_t E, const mlcgb_rbf_spec *rbf /* host */, int conv_cutoff_kind,
+                         double conv_lower, double conv_upper, const void *A1 /* [F,R] */, const void *b1 /* [F] */,
+                         const void *A2 /* [F,F] */, int64_t F, int precision, void *W /* [E,F] */, int32_t *status, void *stream);
+
 /* out[b] = sum_{n in [ptr[b],ptr[b+1])} x[n]  — the per-structure energy sum, src/mlcg/nn/schnet.py:158 */
 int mlcgb_segment_sum(const void *x /* [N] */, int dtype, const int64_t *ptr /* [B+1] */, int64_t B, void *out /* [B] */,
                       void *stream);

@@ -270,6 +270,24 @@ class CudaBackend:
             self._run("gemm", self.lib.mlcgb_gemm, (mode, _ptr(A), _ptr(B), _ptr(bias), dt, M, N, K, _ptr(C), _ptr(ws), wsb, _stream(),), **self._work("gemm", locals()))
         return C
 
+    # ------------------------------------------------------------------ fused filter network (tensor cores)
+    def filter_forward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, precision=0):
+        """W[E,F] = (tanh(phi(d) A1^T + b1) A2^T) * C(d); float32, F = 128, R <= 128."""
+        _need_cuda(d, A1, b1, A2, spec.p0, spec.p1)
+        if d.dtype != torch.float32:
+            raise TypeError("filter_forward is a float32 kernel")
+        d, A1, b1, A2 = d.contiguous(), A1.detach().contiguous(), b1.detach().contiguous(), A2.detach().contiguous()
+        s, keep = self._spec(spec, d.dtype)
+        E, F = d.numel(), A2.shape[0]
+        W = torch.empty((E, F), dtype=d.dtype, device=d.device)
+        status = torch.zeros(4, dtype=torch.int32, device=d.device)
+        with torch.cuda.device(d.device):
+            self._run("filter_forward", self.lib.mlcgb_filter_forward,
+                      (_ptr(d), E, ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
+                       int(precision), _ptr(W), _ptr(status), _stream()),
+                      nbytes=E * (4 * F + 4), flops=2 * E * F * (spec.num_rbf + F))
+        return W, status
+
     def segment_sum(self, x, ptr):
         _need_cuda(x, ptr)
         x = x.contiguous()

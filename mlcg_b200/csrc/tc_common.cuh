@@ -1,0 +1,206 @@
+// sm_100a tensor-core plumbing shared by the fused filter-network kernels: shared-memory operand
+// layout (K-major, 128-byte swizzle), UMMA descriptors, tcgen05.mma / commit / ld / st, TMEM
+// allocation, bounded mbarrier waits.
+//
+// Operand tiles hold 2-byte elements (bf16 or fp16).  A [rows][K] tile is stored as K/64 "atoms";
+// one atom is [rows][64 elements] = rows x 128 bytes, rows grouped by 8 (1024 bytes per group), and
+// inside a group the 16-byte chunk index of a row is XOR-ed with the row index modulo 8.  That is
+// the canonical K-major SWIZZLE_128B layout the tensor core reads through a matrix descriptor with
+// stride-byte-offset 1024; the same bytes can be read as an MN-major operand (rows = K index) with
+// leading-byte-offset = the atom size.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "common.cuh"
+
+namespace mlcgb {
+namespace tc {
+
+constexpr int kRows = 128;                       // tile rows (M of the MMA, edges per tile)
+constexpr int kAtomBytes = kRows * 128;          // one 64-element column block of a 128-row tile
+constexpr uint32_t kSpinLimit = 1u << 22;        // bounded wait on an mbarrier
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// byte offset of the 16-byte chunk holding elements [k0, k0+8) of row r (k0 a multiple of 8)
+__device__ __forceinline__ uint32_t chunk_offset(int r, int k0) {
+    const int atom = k0 >> 6, chunk = (k0 & 63) >> 3;
+    return (uint32_t)(atom * kAtomBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4));
+}
+// byte offset of a single 2-byte element (used when filling the weight tiles)
+__device__ __forceinline__ uint32_t elem_offset(int r, int k) { return chunk_offset(r, k & ~7) + ((k & 7) << 1); }
+
+// ---- matrix descriptors --------------------------------------------------------------------------
+// bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+// [46,48) version (1 on sm_100), [61,64) layout type (2 = 128-byte swizzle)
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// the same storage read with rows as the K index and the 64-element blocks along N (MN-major)
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(kAtomBytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// descriptor of K-step ks (16 elements) of a K-major tile
+__device__ __forceinline__ uint64_t kstep_kmajor(uint64_t base, int ks) {
+    return base + (uint64_t)(((ks >> 2) * kAtomBytes + (ks & 3) * 32) >> 4);
+}
+// descriptor of K-step ks (16 rows) of an MN-major tile
+__device__ __forceinline__ uint64_t kstep_mnmajor(uint64_t base, int ks) { return base + (uint64_t)((ks * 16 * 128) >> 4); }
+
+// instruction descriptor: fp32 accumulate, A/B format fmt (0 = fp16, 1 = bf16), M = 128, N = 128
+__device__ __forceinline__ uint32_t instr_desc(int fmt, int b_mn_major) {
+    return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)b_mn_major << 16) | ((128u >> 3) << 17) |
+           ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint32_t bar_saddr) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_saddr) : "memory");
+}
+
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar_saddr, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_saddr), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// Waits for the phase with the given parity; gives up after kSpinLimit polls and returns false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar_saddr, uint32_t parity) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(bar_saddr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// ---- tensor memory ---------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_saddr, uint32_t ncols) {   // one full warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_saddr), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free(uint32_t taddr, uint32_t ncols) {         // the same warp
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// 32 consecutive columns of this thread's TMEM lane (lane = 32*(warp%4) + laneid): v[j] = D[row][col0 + j]
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// ---- packing 8 fp32 values into one 16-byte operand chunk --------------------------------------------
+// SPLIT = false: bf16, one chunk.  SPLIT = true: fp16 "high" chunk plus the fp16 rounding of the remainder
+// ("low" chunk); high + low carries ~22 significant bits, and hi*hi + hi*lo + lo*hi reproduces an fp32 product.
+template <bool SPLIT>
+__device__ __forceinline__ void pack8(const float (&x)[8], uint4 &hi, uint4 &lo) {
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if (SPLIT) {
+            const __half a = __float2half_rn(x[2 * i]), b = __float2half_rn(x[2 * i + 1]);
+            const __half ar = __float2half_rn(x[2 * i] - __half2float(a)), br = __float2half_rn(x[2 * i + 1] - __half2float(b));
+            h[i] = (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
+            l[i] = (uint32_t)__half_as_ushort(ar) | ((uint32_t)__half_as_ushort(br) << 16);
+        } else {
+            const __nv_bfloat16 a = __float2bfloat16_rn(x[2 * i]), b = __float2bfloat16_rn(x[2 * i + 1]);
+            h[i] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+            l[i] = 0u;
+        }
+    }
+    hi = make_uint4(h[0], h[1], h[2], h[3]);
+    lo = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
+// Fill a [128][Kpad] weight tile (and its low part) from a row-major fp32 matrix src[rows][K], scaled by `scale`.
+template <bool SPLIT>
+__device__ __forceinline__ void load_weight_tile(uint8_t *hi, uint8_t *lo, const float *__restrict__ src, int rows, int K, int Kpad,
+                                                 float scale) {
+    for (int idx = threadIdx.x; idx < kRows * Kpad; idx += blockDim.x) {
+        const int n = idx / Kpad, k = idx - n * Kpad;
+        const float w = (n < rows && k < K) ? src[(int64_t)n * K + k] * scale : 0.f;
+        const uint32_t off = elem_offset(n, k);
+        if (SPLIT) {
+            const __half a = __float2half_rn(w);
+            *reinterpret_cast<__half *>(hi + off) = a;
+            *reinterpret_cast<__half *>(lo + off) = __float2half_rn(w - __half2float(a));
+        } else {
+            *reinterpret_cast<__nv_bfloat16 *>(hi + off) = __float2bfloat16_rn(w);
+        }
+    }
+}
+
+// One GEMM D[128x128] (+)= A[128xK] * B^T over ksteps K-steps, issued by the calling thread.
+// SPLIT: three products per step (hi*hi, hi*lo, lo*hi).  B is K-major (b_mn = 0) or MN-major (b_mn = 1).
+template <bool SPLIT>
+__device__ __forceinline__ void issue_gemm(uint32_t tmem_d, uint32_t a_hi, uint32_t a_lo, uint32_t b_hi, uint32_t b_lo, int ksteps,
+                                           int b_mn) {
+    const uint32_t idesc = instr_desc(SPLIT ? 0 : 1, b_mn);
+    const uint64_t dah = desc_kmajor(a_hi), dal = desc_kmajor(a_lo);
+    const uint64_t dbh = b_mn ? desc_mnmajor(b_hi) : desc_kmajor(b_hi), dbl = b_mn ? desc_mnmajor(b_lo) : desc_kmajor(b_lo);
+    for (int ks = 0; ks < ksteps; ks++) {
+        const uint64_t ah = kstep_kmajor(dah, ks), al = kstep_kmajor(dal, ks);
+        const uint64_t bh = b_mn ? kstep_mnmajor(dbh, ks) : kstep_kmajor(dbh, ks);
+        const uint64_t bl = b_mn ? kstep_mnmajor(dbl, ks) : kstep_kmajor(dbl, ks);
+        mma_f16(tmem_d, ah, bh, idesc, ks > 0 ? 1u : 0u);
+        if (SPLIT) {
+            mma_f16(tmem_d, ah, bl, idesc, 1u);
+            mma_f16(tmem_d, al, bh, idesc, 1u);
+        }
+    }
+}
+
+}  // namespace tc
+}  // namespace mlcgb

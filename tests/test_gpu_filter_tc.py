@@ -1,0 +1,60 @@
+"""The fused tensor-core filter network against the oracle expression (float64 evaluation of the same float32 inputs)."""
+import pytest
+import torch
+
+from mlcg_b200.backend import RbfSpec, get_backend
+from oracle import schnet_ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def reference(d, kind, upper, R, A1, b1, A2):
+    cut = {"cutoff": "cosine", "lower": 0.0, "upper": upper}
+    spec = {"kind": kind, "rbf_cutoff": cut}
+    p0, p1 = (schnet_ref.gaussian_params(0.0, upper, R) if kind == "gaussian" else schnet_ref.expnormal_params(0.0, upper, R))
+    sd = {"rbf_layer.offset": p0.double(), "rbf_layer.coeff": p1.double(), "rbf_layer.means": p0.double(), "rbf_layer.betas": p1.double()}
+    dd = d.double()
+    rbf = schnet_ref.radial_basis(dd, spec, sd)
+    h = torch.tanh(rbf @ A1.double().t() + b1.double())
+    return (h @ A2.double().t()) * schnet_ref.cosine_cutoff(dd, 0.0, upper).view(-1, 1), p0, p1
+
+
+@pytest.mark.parametrize("kind,R,upper", [("expnormal", 128, 15.0), ("gaussian", 50, 30.0), ("expnormal", 64, 12.0), ("gaussian", 100, 10.0)])
+@pytest.mark.parametrize("E", [1, 127, 128, 1000, 40000])
+@pytest.mark.parametrize("precision", [0, 1])
+def test_filter_forward(kind, R, upper, E, precision):
+    gen = torch.Generator().manual_seed(E + R)
+    F = 128
+    d = torch.rand(E, generator=gen) * (upper * 1.05) + 0.5
+    lim1, lim2 = (6.0 / (R + F)) ** 0.5, (6.0 / (2 * F)) ** 0.5
+    A1 = (torch.rand(F, R, generator=gen) * 2 - 1) * lim1
+    A2 = (torch.rand(F, F, generator=gen) * 2 - 1) * lim2
+    b1 = torch.randn(F, generator=gen) * 0.1
+    want, p0, p1 = reference(d, kind, upper, R, A1, b1, A2)
+    spec = RbfSpec(0 if kind == "gaussian" else 1, R, 1, 0.0, upper, 5.0 / upper, p0.to(DEV), p1.reshape(-1).to(DEV))
+    W, status = get_backend().filter_forward(d.to(DEV), spec, 1, 0.0, upper, A1.to(DEV), b1.to(DEV), A2.to(DEV), precision)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    err = float((W.cpu().double() - want).abs().max())
+    scale = float(want.abs().max()) + 1e-30
+    if precision == 0:
+        assert err < 3e-6 * max(scale, 1.0), (err, scale)        # float32-equivalent
+    else:
+        assert err < 3e-2 * max(scale, 1.0), (err, scale)        # bf16 operands
+    assert not W[d.to(DEV) >= upper].any()                        # envelope: exactly zero beyond the cutoff
+
+
+def test_filter_forward_is_row_independent():
+    """A row of W depends on its own distance only: the same distance gives the same bits wherever it sits."""
+    gen = torch.Generator().manual_seed(0)
+    d = torch.rand(5000, generator=gen) * 14 + 0.5
+    d2 = torch.cat([d.flip(0), d[:100]])
+    R, F, upper = 128, 128, 15.0
+    p0, p1 = schnet_ref.expnormal_params(0.0, upper, R)
+    spec = RbfSpec(1, R, 1, 0.0, upper, 5.0 / upper, p0.to(DEV), p1.to(DEV))
+    A1, A2, b1 = torch.randn(F, R, generator=gen) * 0.1, torch.randn(F, F, generator=gen) * 0.1, torch.zeros(F)
+    be = get_backend()
+    Wa, _ = be.filter_forward(d.to(DEV), spec, 1, 0.0, upper, A1.to(DEV), b1.to(DEV), A2.to(DEV), 0)
+    Wb, _ = be.filter_forward(d2.to(DEV), spec, 1, 0.0, upper, A1.to(DEV), b1.to(DEV), A2.to(DEV), 0)
+    assert torch.equal(Wa.flip(0), Wb[:5000]) and torch.equal(Wa[:100], Wb[5000:])
