@@ -166,6 +166,16 @@ int mlcgb_filter_forward(const void *d /* [E] */, int64_t E, const mlcgb_rbf_spe
                          double conv_lower, double conv_upper, const void *A1 /* [F,R] */, const void *b1 /* [F] */,
                          const void *A2 /* [F,F] */, int64_t F, int precision, void *W /* [E,F] */, int32_t *status, void *stream);
 
+/* Backward of the above with respect to the distance, fused with the message product:
+ *   gd[e] = sum_f gW[e,f] * dW[e,f]/dd_e,  gW[e,:] = xl[row0[e],:] * gagg[row1[e],:]
+ * (the gradient CFConv's aggregation, src/mlcg/nn/schnet.py:346,350-368, sends back to its filters).
+ * Recomputes the forward per tile; four tensor-core GEMMs per tile; nothing edge-sized is read or
+ * written in HBM except d, the two index rows and gd. */
+int mlcgb_filter_backward(const void *d, int64_t E, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower,
+                          double conv_upper, const void *A1, const void *b1, const void *A2, int64_t F, int precision,
+                          const int32_t *row0, const int32_t *row1, const void *xl /* [N,F] */, const void *gagg /* [N,F] */,
+                          int64_t N, void *gd /* [E] */, int32_t *status, void *stream);
+
 /* out[b] = sum_{n in [ptr[b],ptr[b+1])} x[n]  — the per-structure energy sum, src/mlcg/nn/schnet.py:158 */
 int mlcgb_segment_sum(const void *x /* [N] */, int dtype, const int64_t *ptr /* [B+1] */, int64_t B, void *out /* [B] */,
                       void *stream);

@@ -49,9 +49,9 @@ __device__ __forceinline__ uint64_t kstep_kmajor(uint64_t base, int ks) {
 // descriptor of K-step ks (16 rows) of an MN-major tile
 __device__ __forceinline__ uint64_t kstep_mnmajor(uint64_t base, int ks) { return base + (uint64_t)((ks * 16 * 128) >> 4); }
 
-// instruction descriptor: fp32 accumulate, A/B format fmt (0 = fp16, 1 = bf16), M = 128, N = 128
-__device__ __forceinline__ uint32_t instr_desc(int fmt, int b_mn_major) {
-    return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)b_mn_major << 16) | ((128u >> 3) << 17) |
+// instruction descriptor: fp32 accumulate, A/B format fmt (0 = fp16, 1 = bf16), M = 128, N = n (multiple of 16)
+__device__ __forceinline__ uint32_t instr_desc(int fmt, int b_mn_major, int n) {
+    return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)b_mn_major << 16) | (((uint32_t)n >> 3) << 17) |
            ((128u >> 4) << 24);
 }
 
@@ -182,12 +182,12 @@ __device__ __forceinline__ void load_weight_tile(uint8_t *hi, uint8_t *lo, const
     }
 }
 
-// One GEMM D[128x128] (+)= A[128xK] * B^T over ksteps K-steps, issued by the calling thread.
+// One GEMM D[128 x n] = A[128 x K] * B over ksteps K-steps of 16, issued by the calling thread.
 // SPLIT: three products per step (hi*hi, hi*lo, lo*hi).  B is K-major (b_mn = 0) or MN-major (b_mn = 1).
 template <bool SPLIT>
 __device__ __forceinline__ void issue_gemm(uint32_t tmem_d, uint32_t a_hi, uint32_t a_lo, uint32_t b_hi, uint32_t b_lo, int ksteps,
-                                           int b_mn) {
-    const uint32_t idesc = instr_desc(SPLIT ? 0 : 1, b_mn);
+                                           int b_mn, int n = 128) {
+    const uint32_t idesc = instr_desc(SPLIT ? 0 : 1, b_mn, n);
     const uint64_t dah = desc_kmajor(a_hi), dal = desc_kmajor(a_lo);
     const uint64_t dbh = b_mn ? desc_mnmajor(b_hi) : desc_kmajor(b_hi), dbl = b_mn ? desc_mnmajor(b_lo) : desc_kmajor(b_lo);
     for (int ks = 0; ks < ksteps; ks++) {
@@ -200,6 +200,15 @@ __device__ __forceinline__ void issue_gemm(uint32_t tmem_d, uint32_t a_hi, uint3
             mma_f16(tmem_d, al, bh, idesc, 1u);
         }
     }
+}
+
+// Power-of-two factor that brings a row whose largest magnitude is `rmax` to [8, 16): exact to apply and to
+// undo, keeps fp16 operands far from overflow and their low parts out of the subnormal range.
+__device__ __forceinline__ float row_scale(float rmax) {
+    if (!(rmax > 0.f) || !isfinite(rmax)) return 1.f;
+    int ex = (int)((__float_as_uint(rmax) >> 23) & 0xffu) - 126;   // rmax = m * 2^ex, m in [0.5, 1)
+    ex = ex < -100 ? -100 : (ex > 100 ? 100 : ex);
+    return __uint_as_float((uint32_t)(127 + 4 - ex) << 23);
 }
 
 }  // namespace tc

@@ -14,7 +14,7 @@ def reference(d, kind, upper, R, A1, b1, A2):
     spec = {"kind": kind, "rbf_cutoff": cut}
     p0, p1 = (schnet_ref.gaussian_params(0.0, upper, R) if kind == "gaussian" else schnet_ref.expnormal_params(0.0, upper, R))
     sd = {"rbf_layer.offset": p0.double(), "rbf_layer.coeff": p1.double(), "rbf_layer.means": p0.double(), "rbf_layer.betas": p1.double()}
-    dd = d.double()
+    dd = d if d.dtype == torch.float64 else d.double()
     rbf = schnet_ref.radial_basis(dd, spec, sd)
     h = torch.tanh(rbf @ A1.double().t() + b1.double())
     return (h @ A2.double().t()) * schnet_ref.cosine_cutoff(dd, 0.0, upper).view(-1, 1), p0, p1
@@ -58,3 +58,34 @@ def test_filter_forward_is_row_independent():
     Wa, _ = be.filter_forward(d.to(DEV), spec, 1, 0.0, upper, A1.to(DEV), b1.to(DEV), A2.to(DEV), 0)
     Wb, _ = be.filter_forward(d2.to(DEV), spec, 1, 0.0, upper, A1.to(DEV), b1.to(DEV), A2.to(DEV), 0)
     assert torch.equal(Wa.flip(0), Wb[:5000]) and torch.equal(Wa[:100], Wb[5000:])
+
+
+@pytest.mark.parametrize("kind,R,upper", [("expnormal", 128, 15.0), ("gaussian", 50, 30.0)])
+@pytest.mark.parametrize("E", [100, 5000])
+@pytest.mark.parametrize("precision", [0, 1])
+@pytest.mark.parametrize("gscale", [1.0, 1e4, 1e-6])
+def test_filter_backward(kind, R, upper, E, precision, gscale):
+    """gd = d/dd sum(gW * W(d)) with gW = xl[row0] * gagg[row1]; checked against autograd of the float64 oracle."""
+    gen = torch.Generator().manual_seed(E + R)
+    F, N = 128, 300
+    d = torch.rand(E, generator=gen) * (upper * 1.02) + 0.5
+    lim1, lim2 = (6.0 / (R + F)) ** 0.5, (6.0 / (2 * F)) ** 0.5
+    A1 = (torch.rand(F, R, generator=gen) * 2 - 1) * lim1
+    A2 = (torch.rand(F, F, generator=gen) * 2 - 1) * lim2
+    b1 = torch.randn(F, generator=gen) * 0.1
+    row0 = torch.randint(0, N, (E,), generator=gen).int()
+    row1 = torch.randint(0, N, (E,), generator=gen).int()
+    xl = torch.randn(N, F, generator=gen)
+    gagg = torch.randn(N, F, generator=gen) * gscale
+    gW = (xl[row0.long()] * gagg[row1.long()]).double()
+    dd = d.double().requires_grad_(True)
+    W, p0, p1 = reference(dd, kind, upper, R, A1, b1, A2)
+    (want,) = torch.autograd.grad((gW * W).sum(), dd)
+    spec = RbfSpec(0 if kind == "gaussian" else 1, R, 1, 0.0, upper, 5.0 / upper, p0.to(DEV), p1.reshape(-1).to(DEV))
+    gd, status = get_backend().filter_backward(d.to(DEV), spec, 1, 0.0, upper, A1.to(DEV), b1.to(DEV), A2.to(DEV), row0.to(DEV), row1.to(DEV),
+                                               xl.to(DEV), gagg.to(DEV), precision)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    err = float((gd.cpu().double() - want).abs().max())
+    scale = float(want.abs().max()) + 1e-30
+    assert err < (2e-5 if precision == 0 else 5e-2) * scale, (err, scale)
