@@ -274,3 +274,38 @@ class SegmentSum(torch.autograd.Function):
     def backward(ctx, g):
         (batch,) = ctx.saved_tensors
         return g.index_select(0, batch).reshape(ctx.shape), None, None
+
+
+# ------------------------------------------------------------------------------- fused eval path
+class FusedFilterConv(torch.autograd.Function):
+    """agg = SegIn(xl, W(d)) with W(d) = (tanh(phi(d) A1^T + b1) A2^T) C(d) produced by the tensor-core kernel.
+
+    First-order only (energies and forces): the backward returns the gradients with respect to ``xl`` and
+    ``d`` and is not itself differentiable; training mode uses the composable operators above instead."""
+
+    @staticmethod
+    def forward(ctx, xl, d, A1, b1, A2, plan: EdgePlan, spec: RbfSpec, conv_cut, precision: int):
+        be = get_backend()
+        W, status = be.filter_forward(d, spec, conv_cut[0], conv_cut[1], conv_cut[2], A1, b1, A2, precision)
+        be.defer_status(status, "fused filter network (forward)")
+        if plan.symmetric:   # W[e] == W[reverse(e)] bit for bit: read the grouping by row1 as the grouping by row0
+            agg = be.seg_mul_sum(xl, W, plan.ptr_out, plan.nbr_out, plan.perm_out, plan.N)
+        else:
+            agg = be.seg_mul_sum(xl, W, plan.ptr_in, plan.nbr_in, plan.perm_in, plan.N)
+        ctx.plan, ctx.spec, ctx.conv_cut, ctx.precision = plan, spec, conv_cut, precision
+        ctx.save_for_backward(xl, d, W, A1, b1, A2)
+        return agg
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        xl, d, W, A1, b1, A2 = ctx.saved_tensors
+        plan, be = ctx.plan, get_backend()
+        g = g.contiguous()
+        gxl = be.seg_mul_sum(g, W, plan.ptr_out, plan.nbr_out, plan.perm_out, plan.N) if ctx.needs_input_grad[0] else None
+        gd = None
+        if ctx.needs_input_grad[1]:
+            gd, status = be.filter_backward(d, ctx.spec, ctx.conv_cut[0], ctx.conv_cut[1], ctx.conv_cut[2], A1, b1, A2, plan.row0, plan.row1,
+                                            xl, g, ctx.precision)
+            be.defer_status(status, "fused filter network (backward)")
+        return gxl, gd, None, None, None, None, None, None, None

@@ -100,6 +100,23 @@ class CudaBackend:
     def __init__(self):
         self.lib = _lib.load()
         self.profiler = None
+        self._pending = []      # (status tensor, what) of kernels whose status word has not been read yet
+
+    def defer_status(self, status, what):
+        """Remember a kernel's status word; it is read together with the next unavoidable host read (the edge
+        count of the next radius graph) or by :meth:`check_pending`, so the hot path gains no synchronisation."""
+        self._pending.append((status, what))
+        if len(self._pending) > 256:
+            self.check_pending()
+
+    def check_pending(self):
+        pending, self._pending = self._pending, []
+        if not pending:
+            return
+        words = torch.stack([s[0] for s, _ in pending]).cpu().tolist()
+        for w, (_, what) in zip(words, pending):
+            if w & 8:
+                raise RuntimeError(f"mlcg_b200: {what}: a tensor-core wait ran out; results are incomplete")
 
     def _run(self, name, fn, args, what=None, launches=1, nbytes=0, flops=0):
         prof = self.profiler
@@ -164,8 +181,13 @@ class CudaBackend:
             status = torch.zeros(4, dtype=torch.int32, device=dev)
             self._run("radius_count", self.lib.mlcgb_radius_count, (_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(max_num_neighbors), int(loop), int(rule),
                                                    _ptr(ws), ws_bytes, _ptr(deg), _ptr(offsets), _ptr(status), _stream(),), **self._work("radius_count", locals()))
-            tail = torch.stack([offsets[N], status[0].to(torch.int64)]).cpu()   # the one host read: E and the status word
+            pend, self._pending = self._pending, []
+            extra = [s[0].to(torch.int64) for s, _ in pend]
+            tail = torch.stack([offsets[N], status[0].to(torch.int64)] + extra).cpu().tolist()   # the one host read
             E, st = int(tail[0]), int(tail[1])
+            for w, (_, what) in zip(tail[2:], pend):
+                if w & 8:
+                    raise RuntimeError(f"mlcg_b200: {what}: a tensor-core wait ran out; results are incomplete")
             ei = torch.empty((2, E), dtype=torch.int64, device=dev)
             dist = torch.empty(E, dtype=pos.dtype, device=dev) if want_distance else None
             mb = torch.empty(E, dtype=torch.int64, device=dev) if want_batch else None

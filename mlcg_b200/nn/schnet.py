@@ -8,11 +8,26 @@ from typing import Final, List
 
 import torch
 
-from ..autograd import SegIn, SegmentSum, edge_distances, plan_of
+from ..autograd import FusedFilterConv, SegIn, SegmentSum, edge_distances, plan_of
 from ..backend import get_backend
 from ..data import ENERGY_KEY
 from ..neighbor_list import atomic_data2neighbor_list, validate_neighborlist
+from .cutoff import cutoff_kind
 from .mlp import MLP, init_xavier_uniform
+
+FILTER_PRECISIONS = {"fp32": 0, "bf16": 1}
+
+
+class LazyRadialBasis:
+    """Stands for ``rbf_layer(distances)`` without computing it.  In eval mode the fused tensor-core kernel
+    evaluates the basis inside its GEMM prologue, so the ``[E, R]`` expansion never has to exist; a consumer
+    that does need it calls :meth:`materialize`."""
+
+    def __init__(self, distances: torch.Tensor, rbf_layer: torch.nn.Module, symmetric: bool):
+        self.distances, self.rbf_layer, self.symmetric = distances, rbf_layer, symmetric
+
+    def materialize(self) -> torch.Tensor:
+        return _tag_symmetric(self.rbf_layer(self.distances), self.symmetric)
 
 _SYM = "_mlcgb_symmetric"   # tag on edge tensors that are functions of the (symmetric) distance only
 
@@ -37,12 +52,31 @@ class CFConv(torch.nn.Module):
         self.lin2 = torch.nn.Linear(num_filters, out_channels)
         self.filter_network = filter_network
         self.cutoff = cutoff
+        self.filter_precision = "fp32"   # "bf16": filter GEMMs with bf16 operands (eval mode only)
         self.reset_parameters()
 
     def reset_parameters(self):
         self.filter_network.reset_parameters()
         init_xavier_uniform(self.lin1)
         init_xavier_uniform(self.lin2)
+
+    def fused_spec(self, rbf_layer):
+        """The tensor-core kernel covers: eval mode, tanh filter MLP [R, 128, 128] with a bias on the first
+        layer only, R <= 128, Gaussian / exp-normal basis with cosine or identity envelopes, float32."""
+        net = self.filter_network
+        if self.training or not isinstance(net, MLP) or len(net.layers) != 3 or not hasattr(rbf_layer, "spec"):
+            return None
+        l0, act, l2 = net.layers
+        if not (isinstance(l0, torch.nn.Linear) and isinstance(l2, torch.nn.Linear) and isinstance(act, torch.nn.Tanh)):
+            return None
+        if l0.bias is None or l2.bias is not None or l0.out_features != 128 or l2.out_features != 128 or l0.in_features > 128:
+            return None
+        if l0.weight.dtype != torch.float32 or not l0.weight.is_cuda:
+            return None
+        ck, rk = cutoff_kind(self.cutoff), cutoff_kind(rbf_layer.cutoff)
+        if ck is None or rk is None or (ck == 1 and self.cutoff.cutoff_lower < 0):
+            return None
+        return rbf_layer.spec(), (ck, float(self.cutoff.cutoff_lower), float(self.cutoff.cutoff_upper) if ck == 1 else 1.0)
 
     def filters(self, edge_weight: torch.Tensor, edge_attr: torch.Tensor) -> torch.Tensor:
         """W[E, F] (schnet.py:340-341)."""
@@ -55,6 +89,15 @@ class CFConv(torch.nn.Module):
 
     def forward(self, x: torch.Tensor, edge_index: torch.Tensor, edge_weight: torch.Tensor, edge_attr: torch.Tensor) -> torch.Tensor:
         plan = plan_of(edge_index, x.shape[0])
+        if isinstance(edge_attr, LazyRadialBasis):
+            fused = self.fused_spec(edge_attr.rbf_layer) if x.dtype == torch.float32 and edge_attr.symmetric == plan.symmetric else None
+            if fused is not None:
+                net = self.filter_network.layers
+                xl = self.lin1(x)
+                agg = FusedFilterConv.apply(xl, edge_weight, net[0].weight.detach(), net[0].bias.detach(), net[2].weight.detach(), plan,
+                                            fused[0], fused[1], FILTER_PRECISIONS[self.filter_precision])
+                return self.lin2(agg)
+            edge_attr = edge_attr.materialize()
         symmetric = bool(getattr(edge_weight, _SYM, False) and getattr(edge_attr, _SYM, False))
         W = self.filters(edge_weight, edge_attr)
         x = self.lin1(x)
@@ -146,7 +189,13 @@ class SchNet(torch.nn.Module):
             raise NotImplementedError("periodic cell shifts are outside the scope of mlcg_b200")
         plan = plan_of(edge_index, data.pos.shape[0])
         distances = _tag_symmetric(edge_distances(data.pos, plan), plan.symmetric)
-        rbf_expansion = _tag_symmetric(self.rbf_layer(distances), plan.symmetric)
+        lazy_ok = (not self.training and distances.dtype == torch.float32 and
+                   all(type(b) is InteractionBlock and type(b.conv) is CFConv and b.conv.fused_spec(self.rbf_layer) is not None
+                       for b in self.interaction_blocks))
+        if lazy_ok:
+            rbf_expansion = LazyRadialBasis(distances, self.rbf_layer, plan.symmetric)
+        else:
+            rbf_expansion = _tag_symmetric(self.rbf_layer(distances), plan.symmetric)
         num_batch = None
         for block in self.interaction_blocks:
             x = x + block(x, edge_index, distances, rbf_expansion, num_batch, data.batch)
@@ -181,3 +230,13 @@ class StandardSchNet(SchNet):
         output_network = MLP([hidden_channels] + output_hidden_layer_widths + [1], activation_func=activation, last_bias=False)
         super().__init__(embedding_layer, blocks, rbf_layer, output_network, max_num_neighbors=max_num_neighbors,
                          nls_distance_method=nls_distance_method)
+
+
+def set_filter_precision(model: torch.nn.Module, precision: str) -> torch.nn.Module:
+    """``"fp32"`` (default: fp32-equivalent tensor-core products) or ``"bf16"`` for every CFConv of ``model``."""
+    if precision not in FILTER_PRECISIONS:
+        raise ValueError(f"precision must be one of {sorted(FILTER_PRECISIONS)}")
+    for m in model.modules():
+        if isinstance(m, CFConv):
+            m.filter_precision = precision
+    return model

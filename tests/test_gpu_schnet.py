@@ -142,3 +142,34 @@ def test_extension_is_the_compute_path():
     from mlcg_b200 import _lib, backend
     be = backend.get_backend()
     assert be.name == "cuda" and be.lib is _lib.load()
+
+
+def test_eval_mode_uses_the_fused_tensor_core_path_and_matches_the_composed_operators():
+    """Same model, same inputs: eval mode (fused tcgen05 kernels) against training mode (composable operators)."""
+    from mlcg_b200.backend import KernelProfiler, get_backend
+    model, pos, types_, batch = _make("expnormal", 16, 100, 20, 15.0, 128, 128, 3, 5, min_dist=4.0)
+    model = model.to(DEV)
+    mk = lambda: mlcg_b200.AtomicData(pos=pos.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV), n_atoms=torch.full((16,), 100).to(DEV))
+    be = get_backend()
+    be.profiler = KernelProfiler(time_kernels=False)
+    fused = bnn.GradientsOut(model, "forces").eval()(mk())
+    names = set(be.profiler.stats)
+    be.profiler = None
+    assert {"filter_forward", "filter_backward"} <= names and "gemm" not in names
+    composed = bnn.GradientsOut(model, "forces").train()(mk())
+    get_backend().check_pending()
+    assert torch.allclose(fused.out["SchNet"]["energy"], composed.out["SchNet"]["energy"].detach(), rtol=E_RTOL, atol=1e-5)
+    assert float((fused.out["SchNet"]["forces"] - composed.out["SchNet"]["forces"].detach()).abs().max()) < F_ATOL
+
+
+def test_bf16_filter_mode_force_accuracy():
+    """bf16 filter GEMMs: forces within 1e-2 relative RMS of the float32 reference."""
+    model, pos, types_, batch = _make("expnormal", 16, 100, 20, 15.0, 128, 128, 3, 6, min_dist=4.0)
+    e_ref, f_ref, _ = _oracle(model, "expnormal", 15.0, 3, pos, types_, batch, 16)
+    bnn.set_filter_precision(model, "bf16")
+    data = mlcg_b200.AtomicData(pos=pos.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV), n_atoms=torch.full((16,), 100).to(DEV))
+    out = bnn.GradientsOut(model.to(DEV), "forces").eval()(data)
+    f = out.out["SchNet"]["forces"].cpu()
+    rel_rms = float(((f - f_ref) ** 2).mean().sqrt() / (f_ref ** 2).mean().sqrt())
+    assert rel_rms < 1e-2, rel_rms
+    assert torch.allclose(out.out["SchNet"]["energy"].detach().cpu(), e_ref, rtol=2e-2, atol=2e-2 * float(e_ref.abs().max()))
