@@ -17,9 +17,10 @@
 namespace mlcgb {
 
 constexpr int kF = 128;                 // filters / hidden width of the filter network
-constexpr int kTcThreads = 256;         // thread t: row t % 128, column half t / 128
+constexpr int kTcThreads = 512;         // thread t: row t % 128 of the tile, 32-column quarter t / 128
 constexpr float kWScale = 64.f;         // power-of-two operand scalings keep the fp16 "low" parts normal
 constexpr float kActScale = 16.f;
+constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
 
 struct FilterFwdParams {
     const float *d;      // [E]
@@ -37,7 +38,9 @@ template <bool SPLIT>
 struct FilterSmem {
     static constexpr int kTile = SPLIT ? 2 * 32768 : 32768;   // one 128x128 operand tile (hi [+ lo])
     static constexpr int kA = 0, kB1 = kTile, kB2 = 2 * kTile, kMisc = 3 * kTile;
-    static constexpr int kTotal = kMisc + 4096 + 1024;        // + misc (bias, barrier, exchange buffers) + alignment slack
+    // misc: bias [128] f32 | basis table [128] float2 | exchange [4][128] f32 x2 | barrier, TMEM slot, error flag
+    static constexpr int kBias = 0, kTable = 512, kRed = 1536, kRed2 = 3584, kBar = 5632;
+    static constexpr int kTotal = kMisc + 6144 + 1024;        // + alignment slack
 };
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -45,6 +48,120 @@ __device__ __forceinline__ float tanh_fast(float x) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// tanh to ~2e-7 absolute: 1 - 2/(e^{2|x|} + 1) with the sign restored
+__device__ __forceinline__ float tanh_acc(float x) {
+    const float t = ex2_fast(fminf(fabsf(x), 15.f) * (2.f * kLog2e));
+    return copysignf(1.f - __fdividef(2.f, t + 1.f), x);
+}
+
+// Per-edge part of the basis: value t(d) the basis functions are centred on and its derivative.
+//   Gaussian:   g_k = exp(coeff (d - offset_k)^2)                 t = d,                 t' = 1
+//   exp-normal: g_k = exp(-beta_k (u - mean_k)^2), u = exp(alpha (lower - d)):  t = u,   t' = -alpha u
+// The table holds (centre_k, s_k) with g_k = 2^(s_k (t - centre_k)^2).
+__device__ __forceinline__ void edge_arg(float d, const RbfDev<float> &s, float &t, float &dt) {
+    if (s.kind == 0) {
+        t = d;
+        dt = 1.f;
+    } else {
+        t = expf(s.alpha * (-d + s.lower));
+        dt = -s.alpha * t;
+    }
+}
+
+// Shared set-up of both kernels: weight tiles, bias, basis table, barrier, tensor memory.
+template <bool SPLIT>
+__device__ __forceinline__ uint32_t filter_setup(const FilterFwdParams &p, uint8_t *smem, int Kpad1, uint32_t tmem_cols) {
+    using namespace tc;
+    using L = FilterSmem<SPLIT>;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const float wscale = SPLIT ? kWScale : 1.f;
+    load_weight_tile<SPLIT>(smem + L::kB1, smem + L::kB1 + 32768, p.A1, kF, p.rbf.R, Kpad1, wscale);
+    load_weight_tile<SPLIT>(smem + L::kB2, smem + L::kB2 + 32768, p.A2, kF, kF, kF, wscale);
+    float *s_b1 = reinterpret_cast<float *>(smem + L::kMisc + L::kBias);
+    float2 *s_tab = reinterpret_cast<float2 *>(smem + L::kMisc + L::kTable);
+    if (tid < kF) {
+        s_b1[tid] = p.b1[tid];
+        float c = 0.f, sc = 0.f;
+        if (tid < p.rbf.R) {
+            c = p.rbf.p0[tid];
+            sc = (p.rbf.kind == 0 ? p.rbf.p1[0] : -p.rbf.p1[tid]) * kLog2e;
+        }
+        s_tab[tid] = make_float2(c, sc);
+    }
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar);
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(s_bar + 1);
+    int *s_err = reinterpret_cast<int *>(s_tmem + 1);
+    if (tid == 0) {
+        mbar_init(smem_u32(s_bar), 1);
+        *s_err = 0;
+    }
+    __syncwarp();
+    if (warp == 0) tmem_alloc(smem_u32(s_tmem), tmem_cols);
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    return *s_tmem;
+}
+
+// this thread's 32 columns of phi (scaled) -> A operand; columns at or beyond R are zero
+template <bool SPLIT>
+__device__ __forceinline__ void write_phi(uint8_t *sA_hi, uint8_t *sA_lo, const float2 *s_tab, int r, int col0, int R, float t, float amp) {
+    using namespace tc;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        float x[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int k = col0 + c * 8 + j;
+            const float2 cs = s_tab[k];
+            const float v = t - cs.x;
+            x[j] = k < R ? amp * ex2_fast(cs.y * v * v) : 0.f;
+        }
+        uint4 hi, lo;
+        pack8<SPLIT>(x, hi, lo);
+        const uint32_t off = chunk_offset(r, col0 + c * 8);
+        *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
+        if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
+    }
+}
+
+template <bool SPLIT>
+__device__ __forceinline__ void write_row32(uint8_t *sA_hi, uint8_t *sA_lo, int r, int col0, const float (&v)[32], float scale) {
+    using namespace tc;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        float x[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) x[j] = v[c * 8 + j] * scale;
+        uint4 hi, lo;
+        pack8<SPLIT>(x, hi, lo);
+        const uint32_t off = chunk_offset(r, col0 + c * 8);
+        *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
+        if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
+    }
+}
+
+// one GEMM issued by thread 0 and awaited by every thread; leaves the tile loop if the wait runs out
+#define MLCGB_RUN_GEMM(TCOL, BOFF, KSTEPS, BMN, NN)                                                           \
+    fence_async_smem();                                                                                       \
+    tc_fence_before();                                                                                        \
+    __syncthreads();                                                                                          \
+    if (tid == 0) {                                                                                           \
+        tc_fence_after();                                                                                     \
+        issue_gemm<SPLIT>(tmem + (TCOL), a_hi, a_lo, smem_u32(smem + (BOFF)), smem_u32(smem + (BOFF) + 32768), (KSTEPS), (BMN), (NN)); \
+        mma_commit(bar);                                                                                      \
+    }                                                                                                         \
+    if (!mbar_wait(bar, phase)) *s_err = 1;                                                                   \
+    phase ^= 1;                                                                                               \
+    tc_fence_after();                                                                                         \
+    __syncthreads();                                                                                          \
+    if (*s_err) break;
 
 template <bool SPLIT>
 __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_tc_kernel(FilterFwdParams p) {
@@ -53,36 +170,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_tc_kernel(FilterFwdP
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t *sA_hi = smem + L::kA, *sA_lo = sA_hi + 32768;
-    uint8_t *sB1_hi = smem + L::kB1, *sB1_lo = sB1_hi + 32768;
-    uint8_t *sB2_hi = smem + L::kB2, *sB2_lo = sB2_hi + 32768;
-    float *s_b1 = reinterpret_cast<float *>(smem + L::kMisc);
-    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_b1 + kF);
-    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(s_bar + 1);
-    int *s_err = reinterpret_cast<int *>(s_tmem + 1);
+    const float *s_b1 = reinterpret_cast<const float *>(smem + L::kMisc + L::kBias);
+    const float2 *s_tab = reinterpret_cast<const float2 *>(smem + L::kMisc + L::kTable);
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar);
+    int *s_err = reinterpret_cast<int *>(reinterpret_cast<uint32_t *>(s_bar + 1) + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    const int r = tid & 127, ch = tid >> 7;            // row of the tile, column half
+    const int r = tid & 127, col0 = (tid >> 7) * 32;   // row of the tile, first of this thread's 32 columns
     const int R = p.rbf.R;
     const int Kpad1 = R <= 64 ? 64 : 128;
     const float wscale = SPLIT ? kWScale : 1.f, ascale = SPLIT ? kActScale : 1.f;
     const float unscale = 1.f / (wscale * ascale);
 
-    load_weight_tile<SPLIT>(sB1_hi, sB1_lo, p.A1, kF, R, Kpad1, wscale);
-    load_weight_tile<SPLIT>(sB2_hi, sB2_lo, p.A2, kF, kF, kF, wscale);
-    if (tid < kF) s_b1[tid] = p.b1[tid];
-    const uint32_t bar = smem_u32(s_bar);
-    if (tid == 0) {
-        mbar_init(bar, 1);
-        *s_err = 0;
-    }
-    __syncwarp();
-    if (warp == 0) tmem_alloc(smem_u32(s_tmem), 256);
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *s_tmem;
+    const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 256);
     const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 TMEM lanes
+    const uint32_t a_hi = smem_u32(sA_hi), a_lo = smem_u32(sA_lo), bar = smem_u32(s_bar);
     uint32_t phase = 0;
 
     const int64_t ntiles = (p.E + kRows - 1) / kRows;
@@ -91,78 +193,30 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_tc_kernel(FilterFwdP
         const bool live = e < p.E;
         const float de = live ? p.d[e] : 1.f;
 
-        // ---- A operand of GEMM 1: phi_k(d) for this thread's 64 columns
-        if (ch * 64 < Kpad1) {
-            const Jet<float, 0> env = envelope_jet<float, 0>(de, p.rbf);
-            const Jet<float, 0> ej = edge_jet<float, 0>(de, p.rbf);
-#pragma unroll 2
-            for (int c = 0; c < 8; c++) {
-                float x[8];
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const int k = ch * 64 + c * 8 + j;
-                    x[j] = k < R ? ascale * phi_deriv<float, 0>(ej, env, k, p.rbf) : 0.f;
-                }
-                uint4 hi, lo;
-                pack8<SPLIT>(x, hi, lo);
-                const uint32_t off = chunk_offset(r, ch * 64 + c * 8);
-                *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
-                if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
-            }
+        // ---- A operand of GEMM 1: phi_k(d) for this thread's columns;  Z = phi A1^T
+        if (col0 < Kpad1) {
+            float t, dt;
+            edge_arg(de, p.rbf, t, dt);
+            write_phi<SPLIT>(sA_hi, sA_lo, s_tab, r, col0, R, t, ascale * envelope_jet<float, 0>(de, p.rbf).c[0]);
         }
-        fence_async_smem();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-            issue_gemm<SPLIT>(tmem, smem_u32(sA_hi), smem_u32(sA_lo), smem_u32(sB1_hi), smem_u32(sB1_lo), Kpad1 / 16, 0);
-            mma_commit(bar);
-        }
-        if (!mbar_wait(bar, phase)) *s_err = 1;
-        phase ^= 1;
-        tc_fence_after();
-        __syncthreads();
-        if (*s_err) break;
+        MLCGB_RUN_GEMM(0, L::kB1, Kpad1 / 16, 0, 128)
 
-        // ---- epilogue 1: h = tanh(z + b1) -> A operand of GEMM 2 (GEMM 1 has finished reading sA)
-#pragma unroll 1
-        for (int half = 0; half < 2; half++) {
-            const int col0 = ch * 64 + half * 32;
+        // ---- epilogue 1: h = tanh(z + b1) -> A operand of GEMM 2 (GEMM 1 has finished reading sA);  Y = h A2^T
+        {
             float v[32];
             tmem_ld32(t_lane + col0, v);
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                float x[8];
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const float z = v[c * 8 + j] * unscale + s_b1[col0 + c * 8 + j];
-                    x[j] = ascale * (SPLIT ? tanhf(z) : tanh_fast(z));
-                }
-                uint4 hi, lo;
-                pack8<SPLIT>(x, hi, lo);
-                const uint32_t off = chunk_offset(r, col0 + c * 8);
-                *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
-                if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
+            for (int j = 0; j < 32; j++) {
+                const float z = fmaf(v[j], unscale, s_b1[col0 + j]);
+                v[j] = SPLIT ? tanh_acc(z) : tanh_fast(z);
             }
+            write_row32<SPLIT>(sA_hi, sA_lo, r, col0, v, ascale);
         }
-        fence_async_smem();
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-            issue_gemm<SPLIT>(tmem + 128, smem_u32(sA_hi), smem_u32(sA_lo), smem_u32(sB2_hi), smem_u32(sB2_lo), kF / 16, 0);
-            mma_commit(bar);
-        }
-        if (!mbar_wait(bar, phase)) *s_err = 1;
-        phase ^= 1;
-        tc_fence_after();
-        __syncthreads();
-        if (*s_err) break;
+        MLCGB_RUN_GEMM(128, L::kB2, kF / 16, 0, 128)
 
         // ---- epilogue 2: W = y * C(d)
-        const float C = envelope_jet<float, 0>(de, p.conv).c[0] * unscale;
-#pragma unroll 1
-        for (int half = 0; half < 2; half++) {
-            const int col0 = ch * 64 + half * 32;
+        {
+            const float C = envelope_jet<float, 0>(de, p.conv).c[0] * unscale;
             float v[32];
             tmem_ld32(t_lane + 128 + col0, v);
             if (live) {
@@ -198,7 +252,6 @@ static int filter_fwd_launch(const FilterFwdParams &p, cudaStream_t st) {
     return check_launch();
 }
 
-
 // ------------------------------------------------------------------------------------------------
 // Backward of the fused filter network + message product with respect to the distance:
 //
@@ -226,56 +279,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t *sA_hi = smem + L::kA, *sA_lo = sA_hi + 32768;
-    uint8_t *sB1_hi = smem + L::kB1, *sB1_lo = sB1_hi + 32768;
-    uint8_t *sB2_hi = smem + L::kB2, *sB2_lo = sB2_hi + 32768;
-    float *s_b1 = reinterpret_cast<float *>(smem + L::kMisc);
-    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_b1 + kF);
-    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(s_bar + 1);
-    int *s_err = reinterpret_cast<int *>(s_tmem + 1);
-    float *s_red = reinterpret_cast<float *>(smem + L::kMisc + 1024);   // [2][128] exchange between the two column halves
-    float *s_red2 = s_red + 256;
+    const float *s_b1 = reinterpret_cast<const float *>(smem + L::kMisc + L::kBias);
+    const float2 *s_tab = reinterpret_cast<const float2 *>(smem + L::kMisc + L::kTable);
+    float *s_red = reinterpret_cast<float *>(smem + L::kMisc + L::kRed);     // [4][128] exchange between column quarters
+    float *s_red2 = reinterpret_cast<float *>(smem + L::kMisc + L::kRed2);
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar);
+    int *s_err = reinterpret_cast<int *>(reinterpret_cast<uint32_t *>(s_bar + 1) + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    const int r = tid & 127, ch = tid >> 7;
+    const int r = tid & 127, qt = tid >> 7, col0 = qt * 32;
     const int R = p.rbf.R;
     const int Kpad1 = R <= 64 ? 64 : 128;
     const float wscale = SPLIT ? kWScale : 1.f, ascale = SPLIT ? kActScale : 1.f;
     const float unscale = 1.f / (wscale * ascale);
 
-    load_weight_tile<SPLIT>(sB1_hi, sB1_lo, p.A1, kF, R, Kpad1, wscale);
-    load_weight_tile<SPLIT>(sB2_hi, sB2_lo, p.A2, kF, kF, kF, wscale);
-    if (tid < kF) s_b1[tid] = p.b1[tid];
-    const uint32_t bar = smem_u32(s_bar);
-    if (tid == 0) {
-        mbar_init(bar, 1);
-        *s_err = 0;
-    }
-    __syncwarp();
-    if (warp == 0) tmem_alloc(smem_u32(s_tmem), 512);
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *s_tmem;
+    const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 512);
     const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t a_hi = smem_u32(sA_hi), a_lo = smem_u32(sA_lo);
+    const uint32_t a_hi = smem_u32(sA_hi), a_lo = smem_u32(sA_lo), bar = smem_u32(s_bar);
     uint32_t phase = 0;
-
-// one GEMM issued by thread 0 and awaited by everybody; leaves the loop if the wait runs out
-#define RUN_GEMM(TCOL, BHI, BLO, KSTEPS, BMN, NN)                                         \
-    fence_async_smem();                                                                   \
-    tc_fence_before();                                                                    \
-    __syncthreads();                                                                      \
-    if (tid == 0) {                                                                       \
-        tc_fence_after();                                                                 \
-        issue_gemm<SPLIT>(tmem + (TCOL), a_hi, a_lo, smem_u32(BHI), smem_u32(BLO), (KSTEPS), (BMN), (NN)); \
-        mma_commit(bar);                                                                  \
-    }                                                                                     \
-    if (!mbar_wait(bar, phase)) *s_err = 1;                                               \
-    phase ^= 1;                                                                           \
-    tc_fence_after();                                                                     \
-    __syncthreads();                                                                      \
-    if (*s_err) break;
 
     const int64_t ntiles = (p.E + kRows - 1) / kRows;
     for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
@@ -283,62 +304,33 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
         const bool live = e < p.E;
         const float de = live ? p.d[e] : 1.f;
         const int64_t i0 = live ? q.row0[e] : 0, i1 = live ? q.row1[e] : 0;
+        float t, dt;
+        edge_arg(de, p.rbf, t, dt);
         const Jet<float, 1> env = envelope_jet<float, 1>(de, p.rbf);
-        const Jet<float, 1> ej = edge_jet<float, 1>(de, p.rbf);
-        const Jet<float, 0> env0{{env.c[0]}}, ej0{{ej.c[0]}};
 
         // ---- step 1: phi -> A operand, Z = phi A1^T
-        if (ch * 64 < Kpad1) {
-#pragma unroll 2
-            for (int c = 0; c < 8; c++) {
-                float x[8];
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const int k = ch * 64 + c * 8 + j;
-                    x[j] = k < R ? ascale * phi_deriv<float, 0>(ej0, env0, k, p.rbf) : 0.f;
-                }
-                uint4 hi, lo;
-                pack8<SPLIT>(x, hi, lo);
-                const uint32_t off = chunk_offset(r, ch * 64 + c * 8);
-                *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
-                if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
-            }
-        }
-        RUN_GEMM(0, sB1_hi, sB1_lo, Kpad1 / 16, 0, 128)
+        if (col0 < Kpad1) write_phi<SPLIT>(sA_hi, sA_lo, s_tab, r, col0, R, t, ascale * env.c[0]);
+        MLCGB_RUN_GEMM(0, L::kB1, Kpad1 / 16, 0, 128)
 
         // ---- step 2: h = tanh(z + b1): kept in tensor memory (over z) and written as the A operand; Y = h A2^T
-#pragma unroll 1
-        for (int half = 0; half < 2; half++) {
-            const int col0 = ch * 64 + half * 32;
+        {
             float v[32];
             tmem_ld32(t_lane + col0, v);
 #pragma unroll
             for (int j = 0; j < 32; j++) {
-                const float z = v[j] * unscale + s_b1[col0 + j];
-                v[j] = SPLIT ? tanhf(z) : tanh_fast(z);
+                const float z = fmaf(v[j], unscale, s_b1[col0 + j]);
+                v[j] = SPLIT ? tanh_acc(z) : tanh_fast(z);
             }
             tmem_st32(t_lane + col0, v);
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                float x[8];
-#pragma unroll
-                for (int j = 0; j < 8; j++) x[j] = ascale * v[c * 8 + j];
-                uint4 hi, lo;
-                pack8<SPLIT>(x, hi, lo);
-                const uint32_t off = chunk_offset(r, col0 + c * 8);
-                *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
-                if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
-            }
+            write_row32<SPLIT>(sA_hi, sA_lo, r, col0, v, ascale);
         }
-        RUN_GEMM(128, sB2_hi, sB2_lo, kF / 16, 0, 128)
+        MLCGB_RUN_GEMM(128, L::kB2, kF / 16, 0, 128)
 
         // ---- step 3: gW from the two gathered node rows; gC = sum gW*y; gy = gW*C -> A operand; GH = gy A2
         const Jet<float, 1> cj = envelope_jet<float, 1>(de, p.conv);
-        float g[64];
+        float g[32];
         float gC = 0.f, rmax = 0.f;
-#pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const int col0 = ch * 64 + half * 32;
+        {
             float v[32];
             tmem_ld32(t_lane + 128 + col0, v);
             const float4 *xa = reinterpret_cast<const float4 *>(q.xl + i0 * kF + col0);
@@ -349,95 +341,76 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
                 const float gw[4] = {a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w};
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const float t = live ? gw[j] : 0.f;
-                    gC = fmaf(t, v[4 * w + j] * unscale, gC);
-                    const float gy = t * cj.c[0];
-                    g[half * 32 + 4 * w + j] = gy;
+                    const float tt = live ? gw[j] : 0.f;
+                    gC = fmaf(tt, v[4 * w + j], gC);
+                    const float gy = tt * cj.c[0];
+                    g[4 * w + j] = gy;
                     rmax = fmaxf(rmax, fabsf(gy));
                 }
             }
         }
-        s_red[ch * 128 + r] = rmax;
-        s_red2[ch * 128 + r] = gC;
+        s_red[qt * 128 + r] = rmax;
+        s_red2[qt * 128 + r] = gC * unscale;
         __syncthreads();
-        gC = s_red2[r] + s_red2[128 + r];
-        const float sc3 = SPLIT ? row_scale(fmaxf(s_red[r], s_red[128 + r])) : 1.f;
-#pragma unroll
-        for (int c = 0; c < 8; c++) {
-            float x[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) x[j] = g[c * 8 + j] * sc3;
-            uint4 hi, lo;
-            pack8<SPLIT>(x, hi, lo);
-            const uint32_t off = chunk_offset(r, ch * 64 + c * 8);
-            *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
-            if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
-        }
-        RUN_GEMM(256, sB2_hi, sB2_lo, kF / 16, 1, 128)
+        gC = (s_red2[r] + s_red2[128 + r]) + (s_red2[256 + r] + s_red2[384 + r]);
+        const float sc3 = SPLIT ? row_scale(fmaxf(fmaxf(s_red[r], s_red[128 + r]), fmaxf(s_red[256 + r], s_red[384 + r]))) : 1.f;
+        write_row32<SPLIT>(sA_hi, sA_lo, r, col0, g, sc3);
+        MLCGB_RUN_GEMM(256, L::kB2, kF / 16, 1, 128)
 
         // ---- step 4: gz = gh (1 - h^2) -> A operand; GPHI = gz A1
-        const float inv3 = 1.f / (sc3 * wscale);
-        rmax = 0.f;
+        {
+            const float inv3 = 1.f / (sc3 * wscale);
+            rmax = 0.f;
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const int col0 = ch * 64 + half * 32;
-            float v[32], h[32];
-            tmem_ld32(t_lane + 256 + col0, v);
-            tmem_ld32(t_lane + col0, h);
+            for (int half = 0; half < 2; half++) {
+                float v[16], h[16];
+                tmem_ld16(t_lane + 256 + col0 + half * 16, v);
+                tmem_ld16(t_lane + col0 + half * 16, h);
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
-                const float gz = v[j] * inv3 * (1.f - h[j] * h[j]);
-                g[half * 32 + j] = gz;
-                rmax = fmaxf(rmax, fabsf(gz));
+                for (int j = 0; j < 16; j++) {
+                    const float gz = v[j] * inv3 * fmaf(-h[j], h[j], 1.f);
+                    g[half * 16 + j] = gz;
+                    rmax = fmaxf(rmax, fabsf(gz));
+                }
             }
         }
-        __syncthreads();            // everyone has read s_red of step 3
-        s_red[ch * 128 + r] = rmax;
+        s_red[qt * 128 + r] = rmax;      // (step 3's values were consumed before the barriers of GEMM 3)
         __syncthreads();
-        const float sc4 = SPLIT ? row_scale(fmaxf(s_red[r], s_red[128 + r])) : 1.f;
-#pragma unroll
-        for (int c = 0; c < 8; c++) {
-            float x[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) x[j] = g[c * 8 + j] * sc4;
-            uint4 hi, lo;
-            pack8<SPLIT>(x, hi, lo);
-            const uint32_t off = chunk_offset(r, ch * 64 + c * 8);
-            *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
-            if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
-        }
-        RUN_GEMM(384, sB1_hi, sB1_lo, kF / 16, 1, Kpad1)
+        const float sc4 = SPLIT ? row_scale(fmaxf(fmaxf(s_red[r], s_red[128 + r]), fmaxf(s_red[256 + r], s_red[384 + r]))) : 1.f;
+        write_row32<SPLIT>(sA_hi, sA_lo, r, col0, g, sc4);
+        MLCGB_RUN_GEMM(384, L::kB1, kF / 16, 1, Kpad1)
 
-        // ---- step 5: gd = sum_r gphi_r phi'_r(d) + gC C'(d)
+        // ---- step 5: gd = sum_r gphi_r phi'_r(d) + gC C'(d),  phi'_k = g_k (env' + env 2 ln2 s_k (t - c_k) t')
         float acc = 0.f;
-        if (ch * 64 < Kpad1) {
-#pragma unroll 1
-            for (int half = 0; half < 2; half++) {
-                const int col0 = ch * 64 + half * 32;
-                float v[32];
-                tmem_ld32(t_lane + 384 + col0, v);
-#pragma unroll 4
-                for (int j = 0; j < 32; j++) {
-                    const int k = col0 + j;
-                    if (k < R) acc = fmaf(v[j], phi_deriv<float, 1>(ej, env, k, p.rbf), acc);
-                }
+        if (col0 < Kpad1) {
+            float v[32];
+            tmem_ld32(t_lane + 384 + col0, v);
+            const float e0 = env.c[0], e1 = env.c[1], two = 2.f * kLn2 * dt;
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const int k = col0 + j;
+                const float2 cs = s_tab[k];
+                const float u = t - cs.x;
+                const float gk = ex2_fast(cs.y * u * u);
+                const float dphi = gk * fmaf(e0 * two, cs.y * u, e1);
+                if (k < R) acc = fmaf(v[j], dphi, acc);
             }
             acc *= 1.f / (sc4 * wscale);
         }
-        if (ch == 0) acc = fmaf(gC, cj.c[1], acc);
-        __syncthreads();            // s_red of step 4 has been read by everyone
-        s_red[ch * 128 + r] = acc;
+        if (qt == 0) acc = fmaf(gC, cj.c[1], acc);
+        s_red2[qt * 128 + r] = acc;      // (step 3's values were consumed before the barriers of GEMM 3)
         tc_fence_before();
         __syncthreads();
-        if (ch == 0 && live) q.gd[e] = s_red[r] + s_red[128 + r];
+        if (qt == 0 && live) q.gd[e] = (s_red2[r] + s_red2[128 + r]) + (s_red2[256 + r] + s_red2[384 + r]);
+        // the next tile's first exchange through s_red / s_red2 comes after several more barriers
     }
-#undef RUN_GEMM
 
     if (*s_err && tid == 0) atomicOr(p.status, 8);
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_free(tmem, 512);
 }
+#undef MLCGB_RUN_GEMM
 
 template <bool SPLIT>
 static int filter_bwd_launch(const FilterBwdParams &q, cudaStream_t st) {

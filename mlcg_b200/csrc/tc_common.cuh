@@ -124,6 +124,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
 }
 
+// 16 consecutive columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
+}
+
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -150,13 +165,14 @@ __device__ __forceinline__ void pack8(const float (&x)[8], uint4 &hi, uint4 &lo)
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         if (SPLIT) {
-            const __half a = __float2half_rn(x[2 * i]), b = __float2half_rn(x[2 * i + 1]);
-            const __half ar = __float2half_rn(x[2 * i] - __half2float(a)), br = __float2half_rn(x[2 * i + 1] - __half2float(b));
-            h[i] = (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
-            l[i] = (uint32_t)__half_as_ushort(ar) | ((uint32_t)__half_as_ushort(br) << 16);
+            const __half2 a = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+            const float2 b = __half22float2(a);
+            const __half2 c = __floats2half2_rn(x[2 * i] - b.x, x[2 * i + 1] - b.y);
+            h[i] = *reinterpret_cast<const uint32_t *>(&a);
+            l[i] = *reinterpret_cast<const uint32_t *>(&c);
         } else {
-            const __nv_bfloat16 a = __float2bfloat16_rn(x[2 * i]), b = __float2bfloat16_rn(x[2 * i + 1]);
-            h[i] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+            const __nv_bfloat162 a = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+            h[i] = *reinterpret_cast<const uint32_t *>(&a);
             l[i] = 0u;
         }
     }
