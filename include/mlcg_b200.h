@@ -105,6 +105,16 @@ int mlcgb_node_scatter_diff(const void *g /* [E,3] */, int dtype, const int64_t 
                             const int64_t *ptr_out, const int32_t *perm_out, int64_t N, int64_t E,
                             void *out /* [N,3] */, void *stream);
 
+/* The same distance in one kernel, d[e] = |pos[row1[e]] - pos[row0[e]]|, and its first derivative
+ * gpos[n] = sum_{e: row1=n} (g_e/d_e) dr_e - sum_{e: row0=n} (g_e/d_e) dr_e (ordered, no atomics): the force path
+ * of energy/force evaluation, where nothing has to be differentiated a second time. */
+int mlcgb_edge_distance(const void *pos, int dtype, const int32_t *row0, const int32_t *row1, int64_t E, int64_t N,
+                        void *d /* [E] */, int32_t *status, void *stream);
+int mlcgb_edge_distance_backward(const void *pos, const void *g /* [E] */, const void *d /* [E] */, int dtype,
+                                 const int32_t *row0, const int32_t *row1, const int64_t *ptr_in, const int32_t *perm_in,
+                                 const int64_t *ptr_out, const int32_t *perm_out, int64_t N, int64_t E, void *gpos /* [N,3] */,
+                                 void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Radial basis times cutoff envelope, and its derivatives with respect to the distance.
  * GaussianBasis.forward src/mlcg/nn/radial_basis/gaussian.py:83-102, ExpNormalBasis.forward

@@ -33,6 +33,8 @@ SIGNATURES = {
                                           ctypes.POINTER(c_i64), c_vp, c_vp]),
     "mlcgb_edge_twin": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "mlcgb_edge_diff": (c_int, [c_vp, c_int, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "mlcgb_edge_distance": (c_int, [c_vp, c_int, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "mlcgb_edge_distance_backward": (c_int, [c_vp, c_vp, c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp]),
     "mlcgb_node_scatter_diff": (c_int, [c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp]),
     "mlcgb_rbf_expand": (c_int, [c_vp, c_int, c_i64, ctypes.POINTER(RbfSpecStruct), c_int, c_vp, c_vp]),
     "mlcgb_rbf_contract": (c_int, [c_vp, c_vp, c_int, c_i64, ctypes.POINTER(RbfSpecStruct), c_int, c_vp, c_vp]),

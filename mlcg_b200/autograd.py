@@ -169,6 +169,24 @@ def edge_distances(pos: torch.Tensor, plan: EdgePlan) -> torch.Tensor:
     return EdgeDiff.apply(pos, plan).norm(p=2, dim=1)
 
 
+class EdgeDistanceOnce(torch.autograd.Function):
+    """Distances in one kernel with a hand-written first derivative (energy / force evaluation only; the
+    composable :func:`edge_distances` serves anything that differentiates twice)."""
+
+    @staticmethod
+    def forward(ctx, pos, plan: EdgePlan):
+        d = get_backend().edge_distance(pos, plan.row0, plan.row1)
+        ctx.plan = plan
+        ctx.save_for_backward(pos, d)
+        return d
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        pos, d = ctx.saved_tensors
+        return get_backend().edge_distance_backward(pos, g, d, ctx.plan), None
+
+
 # ------------------------------------------------------------------------------- radial basis
 MAX_RBF_ORDER = 3
 

@@ -100,12 +100,14 @@ class CudaBackend:
     def __init__(self):
         self.lib = _lib.load()
         self.profiler = None
+        self._status = {}
         self._pending = []      # (status tensor, what) of kernels whose status word has not been read yet
 
     def defer_status(self, status, what):
         """Remember a kernel's status word; it is read together with the next unavoidable host read (the edge
         count of the next radius graph) or by :meth:`check_pending`, so the hot path gains no synchronisation."""
-        self._pending.append((status, what))
+        if not any(s is status for s, _ in self._pending):
+            self._pending.append((status, what))
         if len(self._pending) > 256:
             self.check_pending()
 
@@ -218,6 +220,35 @@ class CudaBackend:
             self._run("edge_diff", self.lib.mlcgb_edge_diff, (_ptr(pos), _dt(pos), _ptr(row0), _ptr(row1), E, pos.shape[0], _ptr(out), _ptr(status), _stream(),), **self._work("edge_diff", locals()))
         return out
 
+    def _sticky_status(self, dev):
+        """One status array per device for kernels whose status is only ever checked lazily (bits accumulate)."""
+        st = self._status.get(dev)
+        if st is None:
+            st = self._status[dev] = torch.zeros(4, dtype=torch.int32, device=dev)
+        return st
+
+    def edge_distance(self, pos, row0, row1):
+        _need_cuda(pos, row0, row1)
+        pos = pos.contiguous()
+        E = row0.numel()
+        out = torch.empty(E, dtype=pos.dtype, device=pos.device)
+        with torch.cuda.device(pos.device):
+            self._run("edge_distance", self.lib.mlcgb_edge_distance,
+                      (_ptr(pos), _dt(pos), _ptr(row0), _ptr(row1), E, pos.shape[0], _ptr(out), _ptr(self._sticky_status(pos.device)), _stream()),
+                      nbytes=E * (8 + pos.element_size()) + pos.numel() * pos.element_size())
+        return out
+
+    def edge_distance_backward(self, pos, g, d, plan):
+        _need_cuda(pos, g, d)
+        pos, g, d = pos.contiguous(), g.contiguous(), d.contiguous()
+        out = torch.empty_like(pos)
+        with torch.cuda.device(pos.device):
+            self._run("edge_distance_backward", self.lib.mlcgb_edge_distance_backward,
+                      (_ptr(pos), _ptr(g), _ptr(d), _dt(pos), _ptr(plan.row0), _ptr(plan.row1), _ptr(plan.ptr_in), _ptr(plan.perm_in),
+                       _ptr(plan.ptr_out), _ptr(plan.perm_out), plan.N, plan.E, _ptr(out), _stream()),
+                      nbytes=2 * plan.E * (16 + 2 * pos.element_size()) + 2 * pos.numel() * pos.element_size())
+        return out
+
     def node_scatter_diff(self, g, ptr_in, perm_in, ptr_out, perm_out, N):
         _need_cuda(g)
         g = g.contiguous()
@@ -302,7 +333,7 @@ class CudaBackend:
         s, keep = self._spec(spec, d.dtype)
         E, F = d.numel(), A2.shape[0]
         W = torch.empty((E, F), dtype=d.dtype, device=d.device)
-        status = torch.zeros(4, dtype=torch.int32, device=d.device)
+        status = self._sticky_status(d.device)
         with torch.cuda.device(d.device):
             self._run("filter_forward", self.lib.mlcgb_filter_forward,
                       (_ptr(d), E, ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
@@ -318,7 +349,7 @@ class CudaBackend:
         s, keep = self._spec(spec, d.dtype)
         E, F = d.numel(), A2.shape[0]
         gd = torch.empty(E, dtype=d.dtype, device=d.device)
-        status = torch.zeros(4, dtype=torch.int32, device=d.device)
+        status = self._sticky_status(d.device)
         with torch.cuda.device(d.device):
             self._run("filter_backward", self.lib.mlcgb_filter_backward,
                       (_ptr(d), E, ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,

@@ -156,6 +156,56 @@ node_scatter_diff_kernel(const T *__restrict__ g, const int64_t *__restrict__ pt
     }
 }
 
+
+// d[e] = |pos[row1] - pos[row0]|  (compute_distances, internal_coordinates.py:72-100, in one kernel)
+template <typename T>
+__global__ void edge_distance_kernel(const T *__restrict__ pos, const int32_t *__restrict__ row0,
+                                     const int32_t *__restrict__ row1, int64_t E, int64_t N, T *__restrict__ d,
+                                     int32_t *__restrict__ status) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t a = row0[e], b = row1[e];
+        if (a < 0 || a >= N || b < 0 || b >= N) {
+            atomicOr(status, (int)kBadIndex);
+            d[e] = T(0);
+            continue;
+        }
+        const T dx = pos[b * 3] - pos[a * 3], dy = pos[b * 3 + 1] - pos[a * 3 + 1], dz = pos[b * 3 + 2] - pos[a * 3 + 2];
+        d[e] = sqrt(dx * dx + dy * dy + dz * dz);
+    }
+}
+
+// gpos[n] = sum_{e: row1(e)=n} (g_e/d_e) dr_e - sum_{e: row0(e)=n} (g_e/d_e) dr_e,  dr_e = pos[row1] - pos[row0]
+// one warp per node, ordered, no atomics
+template <typename T>
+__global__ void __launch_bounds__(256)
+edge_distance_bwd_kernel(const T *__restrict__ pos, const T *__restrict__ g, const T *__restrict__ d,
+                         const int32_t *__restrict__ row0, const int32_t *__restrict__ row1,
+                         const int64_t *__restrict__ ptr_in, const int32_t *__restrict__ perm_in,
+                         const int64_t *__restrict__ ptr_out, const int32_t *__restrict__ perm_out, int64_t N,
+                         T *__restrict__ gpos) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t n = warp; n < N; n += nwarps) {
+        T s0 = T(0), s1 = T(0), s2 = T(0);
+        for (int pass = 0; pass < 2; pass++) {
+            const int64_t *ptr = pass ? ptr_out : ptr_in;
+            const int32_t *perm = pass ? perm_out : perm_in;
+            const T sign = pass ? T(-1) : T(1);
+            for (int64_t k = ptr[n] + lane; k < ptr[n + 1]; k += 32) {
+                const int64_t e = perm ? (int64_t)perm[k] : k;
+                const int64_t a = row0[e], b = row1[e];
+                const T w = sign * g[e] / d[e];
+                s0 = fma(w, pos[b * 3] - pos[a * 3], s0);
+                s1 = fma(w, pos[b * 3 + 1] - pos[a * 3 + 1], s1);
+                s2 = fma(w, pos[b * 3 + 2] - pos[a * 3 + 2], s2);
+            }
+        }
+        s0 = warp_sum(s0); s1 = warp_sum(s1); s2 = warp_sum(s2);
+        if (lane == 0) { gpos[n * 3] = s0; gpos[n * 3 + 1] = s1; gpos[n * 3 + 2] = s2; }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 segment_sum_kernel(const T *__restrict__ x, const int64_t *__restrict__ ptr, int64_t B, T *__restrict__ out) {
@@ -252,6 +302,30 @@ int mlcgb_segment_sum(const void *x, int dtype, const int64_t *ptr, int64_t B, v
     if (!x || !ptr || !out) return MLCGB_E_ARG;
     return MLCGB_DISPATCH_DTYPE(dtype, [&] {
         segment_sum_kernel<scalar_t><<<grid_for(B * 32, 256), 256, 0, (cudaStream_t)stream>>>((const scalar_t *)x, ptr, B, (scalar_t *)out);
+        return check_launch();
+    });
+}
+
+int mlcgb_edge_distance(const void *pos, int dtype, const int32_t *row0, const int32_t *row1, int64_t E, int64_t N, void *d,
+                        int32_t *status, void *stream) {
+    if (E < 0 || N < 0 || !status) return MLCGB_E_ARG;
+    if (E == 0) return MLCGB_OK;
+    if (!pos || !row0 || !row1 || !d) return MLCGB_E_ARG;
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        edge_distance_kernel<scalar_t><<<grid_for(E, 256), 256, 0, (cudaStream_t)stream>>>((const scalar_t *)pos, row0, row1, E, N, (scalar_t *)d, status);
+        return check_launch();
+    });
+}
+
+int mlcgb_edge_distance_backward(const void *pos, const void *g, const void *d, int dtype, const int32_t *row0, const int32_t *row1,
+                                 const int64_t *ptr_in, const int32_t *perm_in, const int64_t *ptr_out, const int32_t *perm_out,
+                                 int64_t N, int64_t E, void *gpos, void *stream) {
+    if (N < 0 || E < 0) return MLCGB_E_ARG;
+    if (N == 0) return MLCGB_OK;
+    if (!ptr_in || !ptr_out || !gpos || (E > 0 && (!pos || !g || !d || !row0 || !row1))) return MLCGB_E_ARG;
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        edge_distance_bwd_kernel<scalar_t><<<grid_for(N * 32, 256), 256, 0, (cudaStream_t)stream>>>(
+            (const scalar_t *)pos, (const scalar_t *)g, (const scalar_t *)d, row0, row1, ptr_in, perm_in, ptr_out, perm_out, N, (scalar_t *)gpos);
         return check_launch();
     });
 }

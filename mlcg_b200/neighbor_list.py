@@ -140,6 +140,8 @@ def atomic_data2neighbor_list(data, rcut: float, self_interaction: bool = False,
     # The reference asserts batch[mapping[0]] == batch[mapping[1]] here (a device->host sync,
     # neighbor_list.py:89-91); the kernel only ever pairs points of one structure, by construction.
     cell_shifts = torch.zeros((mapping.shape[1], 3), dtype=pos.dtype, device=pos.device)
-    return make_neighbor_list(tag=f"nonbounded rc:{rcut} order:{mapping.shape[0]}", order=mapping.shape[0], index_mapping=mapping,
-                              mapping_batch=res["mapping_batch"], cell_shifts=cell_shifts, rcut=rcut,
-                              self_interaction=self_interaction)
+    nl = make_neighbor_list(tag=f"nonbounded rc:{rcut} order:{mapping.shape[0]}", order=mapping.shape[0], index_mapping=mapping,
+                            mapping_batch=res["mapping_batch"], cell_shifts=cell_shifts, rcut=rcut,
+                            self_interaction=self_interaction)
+    nl["_mlcgb_zero_shifts"] = True
+    return nl

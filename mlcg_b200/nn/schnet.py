@@ -8,7 +8,7 @@ from typing import Final, List
 
 import torch
 
-from ..autograd import FusedFilterConv, SegIn, SegmentSum, edge_distances, plan_of
+from ..autograd import EdgeDistanceOnce, FusedFilterConv, SegIn, SegmentSum, edge_distances, plan_of
 from ..backend import get_backend
 from ..data import ENERGY_KEY
 from ..neighbor_list import atomic_data2neighbor_list, validate_neighborlist
@@ -185,10 +185,15 @@ class SchNet(torch.nn.Module):
             neighbor_list = self.neighbor_list(data, self.rbf_layer.cutoff.cutoff_upper, self.max_num_neighbors)[self.name]
         edge_index = neighbor_list["index_mapping"]
         cell_shifts = neighbor_list["cell_shifts"]
-        if cell_shifts is not None and cell_shifts.numel() > 0 and bool(torch.any(cell_shifts != 0)):
+        if (not neighbor_list.get("_mlcgb_zero_shifts", False) and cell_shifts is not None and cell_shifts.numel() > 0
+                and bool(torch.any(cell_shifts != 0))):   # (a host read; lists built by this package are known to be shift-free)
             raise NotImplementedError("periodic cell shifts are outside the scope of mlcg_b200")
         plan = plan_of(edge_index, data.pos.shape[0])
-        distances = _tag_symmetric(edge_distances(data.pos, plan), plan.symmetric)
+        if self.training:
+            distances = edge_distances(data.pos, plan)          # differentiable to any order
+        else:
+            distances = EdgeDistanceOnce.apply(data.pos, plan)  # one kernel forward, one backward
+        distances = _tag_symmetric(distances, plan.symmetric)
         lazy_ok = (not self.training and distances.dtype == torch.float32 and
                    all(type(b) is InteractionBlock and type(b.conv) is CFConv and b.conv.fused_spec(self.rbf_layer) is not None
                        for b in self.interaction_blocks))

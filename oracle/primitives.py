@@ -57,6 +57,13 @@ class OracleBackend:
     def edge_diff(self, pos, row0, row1):
         return pos[row1.long()] - pos[row0.long()]
 
+    def edge_distance(self, pos, row0, row1):
+        return (pos[row1.long()] - pos[row0.long()]).norm(p=2, dim=1)
+
+    def edge_distance_backward(self, pos, g, d, plan):
+        w = (g / d).unsqueeze(-1) * (pos[plan.row1.long()] - pos[plan.row0.long()])
+        return self.node_scatter_diff(w, plan.ptr_in, plan.perm_in, plan.ptr_out, plan.perm_out, plan.N)
+
     def node_scatter_diff(self, g, ptr_in, perm_in, ptr_out, perm_out, N):
         gi = g if perm_in is None else g[perm_in.long()]
         go = g if perm_out is None else g[perm_out.long()]

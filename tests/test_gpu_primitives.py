@@ -152,3 +152,26 @@ def test_prior_terms(dtype):
         rt = 1e-10 if dtype == torch.float64 else 2e-5
         assert torch.allclose(e.cpu(), e_ref, rtol=rt), name
         assert torch.allclose(g.cpu(), g_ref, rtol=10 * rt, atol=rt * float(g_ref.abs().max())), name
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_edge_distance_and_its_backward(dtype):
+    gen = torch.Generator().manual_seed(7)
+    N = 150
+    ei = random_graph(N, 8, gen)
+    ei = ei[:, ei[0] != ei[1]]
+    plan = ag.EdgePlan.from_edge_index(ei, N)
+    pos = torch.randn(N, 3, dtype=dtype, generator=gen) * 3
+    g = torch.randn(ei.shape[1], dtype=dtype, generator=gen)
+    be = get_backend()
+    d = be.edge_distance(pos.to(DEV), plan.row0.to(DEV), plan.row1.to(DEV))
+    assert torch.allclose(d.cpu(), ORA.edge_distance(pos, plan.row0, plan.row1), **tol(dtype))
+    import copy
+    gplan = copy.copy(plan)
+    for f in ("row0", "row1", "ptr_in", "perm_in", "ptr_out", "nbr_in", "nbr_out"):
+        setattr(gplan, f, getattr(plan, f).to(DEV))
+    gplan.perm_out = None if plan.perm_out is None else plan.perm_out.to(DEV)
+    got = be.edge_distance_backward(pos.to(DEV), g.to(DEV), d, gplan)
+    p = pos.clone().requires_grad_(True)
+    (want,) = torch.autograd.grad((ORA.edge_distance(p, plan.row0, plan.row1) * g).sum(), p)
+    assert torch.allclose(got.cpu(), want, rtol=1e-4 if dtype == torch.float32 else 1e-10, atol=1e-4 if dtype == torch.float32 else 1e-10)
