@@ -160,6 +160,68 @@ class ClockSampler:
         return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None, reasons=sorted(reasons), samples=len(sm))
 
 
+
+# ----------------------------------------------------------------------------------------- other kernel families
+def time_cuda(fn, iters=5, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return statistics.median(ts)
+
+
+def extra_measurements(dev, hbm_peak):
+    """Kernel families that the headline step exercises only lightly, at the sizes of the other configurations:
+    the stand-alone radius graph (256 x 4000 points, 60 A cube, 10 A cutoff) and the prior terms of the simulation
+    configuration (1024 x 268 beads).  Device time, CUDA events; inputs are far larger than L2."""
+    import mlcg_b200
+    from mlcg_b200 import nn as bnn
+    from mlcg_b200.backend import get_backend
+    be = get_backend()
+    out = {}
+    gen = torch.Generator().manual_seed(0)
+    B, n = 256, 4000
+    pos = (torch.rand(B * n, 3, generator=gen) * 60.0).to(dev)
+    ptr = torch.arange(B + 1, device=dev) * n
+    res = be.radius_graph(pos, ptr, 10.0, 1000, False, 1)
+    E = int(res["edge_index"].shape[1])
+    del res
+    ms = time_cuda(lambda: be.radius_graph(pos, ptr, 10.0, 1000, False, 1), iters=5, warm=1)
+    nbytes = 16 * E + 20 * B * n
+    out["radius_graph_256x4000"] = dict(edges=E, ms=ms, edges_per_s=E / (ms / 1e3), algorithmic_GBps=nbytes / ms / 1e6,
+                                        frac_of_hbm=nbytes / ms / 1e6 / hbm_peak,
+                                        note="count + scan + host read of E + fill, allocation of the outputs included; "
+                                             "algorithmic bytes = 16 B/edge written + 20 B/point read")
+    del pos
+    # priors of the simulation configuration
+    Bp, npb = 1024, 268
+    idx = torch.arange(npb, device=dev)
+    full = torch.cartesian_prod(idx, idx).t()
+    lists = {"bonds": torch.stack([idx[:-1], idx[1:]]), "angles": torch.stack([idx[:-2], idx[1:-1], idx[2:]]),
+             "dihedrals": torch.stack([idx[:-3], idx[1:-2], idx[2:-1], idx[3:]]), "repulsion": full[:, (full[0] - full[1]).abs() >= 3]}
+    ppos = torch.cumsum(torch.nn.functional.normalize(torch.randn(Bp, npb, 3, generator=gen), dim=2) * 3.8, dim=1).reshape(-1, 3).to(dev)
+    offs = (torch.arange(Bp, device=dev) * npb)
+    n_par = {"bonds": 2, "angles": 2, "dihedrals": 7, "repulsion": 1}
+    for kind, name in enumerate(["bonds", "angles", "dihedrals", "repulsion"]):
+        m = lists[name]
+        M = m.shape[1] * Bp
+        mapping = (m[:, None, :] + offs[None, :, None]).reshape(m.shape[0], M).contiguous()
+        mb = torch.arange(Bp, device=dev).repeat_interleave(m.shape[1])
+        params = torch.rand(n_par[name], M, device=dev) + (3.0 if name in ("bonds", "repulsion") else 0.0)
+        ms = time_cuda(lambda: be.prior_terms(kind, ppos, mapping, mb, params, Bp), iters=5, warm=1)
+        nbytes = M * (8 * m.shape[0] + 8 + 4 * n_par[name]) + 2 * ppos.numel() * 4
+        out[f"prior_{name}_1024x268"] = dict(terms=M, ms=ms, terms_per_s=M / (ms / 1e3), algorithmic_GBps=nbytes / ms / 1e6,
+                                             frac_of_hbm=nbytes / ms / 1e6 / hbm_peak)
+        del mapping, mb, params
+    return out
+
 # ----------------------------------------------------------------------------------------- GPU arm
 def run_ours(args):
     import torch.distributed as dist
@@ -287,6 +349,15 @@ def run_ours(args):
         cpu = dict(value=v, unit="structures/s", cores=cores, kind="port",
                    sample=f"{sample_B} structures of the same workload per step, 3 steps after 1 warm-up, torch CPU float32 + C radius oracle")
 
+    extras = None
+    if not args.no_extras:
+        try:
+            del flush
+            torch.cuda.empty_cache()
+            extras = extra_measurements(dev, hbm_peak)
+        except Exception as exc:   # the headline line is still printed
+            extras = {"error": repr(exc)}
+
     value = world * B * args.steps / (ms_total / 1e3)
     h2d = pos_h.numel() * 4 + types_h.numel() * 8 + batch_h.numel() * 8
     d2h = B * 4 + pos_h.numel() * 4
@@ -294,7 +365,7 @@ def run_ours(args):
                 ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
                 config=dict(WORKLOAD, edges_per_gpu=n_edges, global_structures=world * B, parallelism=f"replicas x{world}, no collective"),
                 e2e=dict(value=world * B * args.steps / (e2e_ms / 1e3), unit="structures/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
-                gpu_launches=prof.total_launches, roofline=roof, cfconv_roofline=cfconv, cpu_baseline=cpu, clocks=clk, kernels=kernels,
+                gpu_launches=prof.total_launches, roofline=roof, cfconv_roofline=cfconv, other_kernels=extras, cpu_baseline=cpu, clocks=clk, kernels=kernels,
                 edges_per_s=world * n_edges * args.steps / (ms_total / 1e3))
     print(json.dumps(line))
     if world > 1:
@@ -308,6 +379,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--structures", type=int, default=None, help="structures per GPU (default 512; smaller values are for profiler captures)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the stand-alone radius-graph and prior-kernel measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
     args = ap.parse_args()
     if args.structures:
