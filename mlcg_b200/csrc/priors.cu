@@ -21,6 +21,25 @@ template <typename T> __device__ __forceinline__ void atomic_add3(T *g, int64_t 
     atomicAdd(g + i * 3 + 2, v.z);
 }
 
+// Adds v into g[i] with one atomic per run of consecutive lanes that share the same index i (pair lists are
+// usually grouped by their first index, so a warp holds one or two runs).  Every lane of the warp must call this;
+// lanes without a contribution pass i = -1.
+template <typename T>
+__device__ __forceinline__ void run_add3(T *g, int64_t i, V3<T> v, int lane) {
+    const int64_t prev = __shfl_up_sync(0xffffffffu, i, 1);
+    const bool head = lane == 0 || prev != i;
+    const unsigned heads = __ballot_sync(0xffffffffu, head);
+    // end of this lane's run = position of the next head above it
+    const unsigned above = lane == 31 ? 0u : (heads >> (lane + 1));
+    const int run_end = above ? lane + __ffs(above) : 32;   // exclusive
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const T x = __shfl_down_sync(0xffffffffu, v.x, o), y = __shfl_down_sync(0xffffffffu, v.y, o), z = __shfl_down_sync(0xffffffffu, v.z, o);
+        if (lane + o < run_end) { v.x += x; v.y += y; v.z += z; }
+    }
+    if (head && i >= 0) atomic_add3(g, i, v);
+}
+
 template <typename T, int KIND>
 __global__ void __launch_bounds__(256)
 prior_kernel(const T *__restrict__ pos, const int64_t *__restrict__ mapping, const int64_t *__restrict__ mapping_batch,
@@ -46,6 +65,7 @@ prior_kernel(const T *__restrict__ pos, const int64_t *__restrict__ mapping, con
             if (!valid) atomicOr(status, (int)kBadIndex);
         }
         T e = T(0);
+        V3<T> g0{T(0), T(0), T(0)};   // pair terms: gradient on the first index, reduced over runs below
         if (valid) {
             if (KIND == 0 || KIND == 3) {
                 const V3<T> dr = sub(ld3(pos, idx[1]), ld3(pos, idx[0]));
@@ -64,7 +84,7 @@ prior_kernel(const T *__restrict__ pos, const int64_t *__restrict__ mapping, con
                 if (grad) {
                     const V3<T> g1 = scale(dr, dEdd / d);
                     atomic_add3(grad, idx[1], g1);
-                    atomic_add3(grad, idx[0], scale(g1, T(-1)));
+                    g0 = scale(g1, T(-1));
                 }
             } else if (KIND == 1) {
                 const V3<T> p1 = ld3(pos, idx[1]);
@@ -118,6 +138,7 @@ prior_kernel(const T *__restrict__ pos, const int64_t *__restrict__ mapping, con
                 }
             }
         }
+        if ((KIND == 0 || KIND == 3) && grad) run_add3(grad, valid ? idx[0] : (int64_t)-1, g0, lane);
         // energy: one atomic per warp when the whole warp sits in one structure
         const int64_t mb0 = __shfl_sync(0xffffffffu, mb, 0);
         const bool same = __all_sync(0xffffffffu, !valid || mb == mb0);

@@ -35,7 +35,7 @@ __device__ __forceinline__ double4 make_v4(double x, double y, double z, int i) 
 }
 
 struct WsLayout {
-    size_t spos, cellparam, cell_of, cell_start, bsum, total;
+    size_t spos, cellparam, cell_of, cell_start, struct_of, bsum, total;
 };
 static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 static WsLayout ws_layout(int64_t N, int64_t B, int dtype) {
@@ -46,6 +46,7 @@ static WsLayout ws_layout(int64_t N, int64_t B, int dtype) {
     L.cellparam = o;   o += align256((size_t)B * sizeof(CellParam));
     L.cell_of = o;     o += align256((size_t)N * 4);
     L.cell_start = o;  o += align256((size_t)(N + B) * 4);
+    L.struct_of = o;   o += align256((size_t)N * 4);
     L.bsum = o;        o += align256((size_t)((N + kScanBlock - 1) / kScanBlock + 1) * 8);
     L.total = o;
     return L;
@@ -56,7 +57,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBuildThreads)
 build_cells_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, T rcut,
                    V4<T> *__restrict__ spos, CellParam *__restrict__ cellparam, int32_t *__restrict__ cell_of,
-                   int32_t *__restrict__ cell_start) {
+                   int32_t *__restrict__ cell_start, int32_t *__restrict__ struct_of) {
     __shared__ int counts[kSmemCells + 1];
     __shared__ T red[6][kBuildThreads / 32];
     __shared__ T s_org[3];
@@ -67,6 +68,7 @@ build_cells_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, i
     for (int64_t b = blockIdx.x; b < B; b += gridDim.x) {
         const int64_t lo = ptr[b];
         const int64_t n64 = ptr[b + 1] - lo;
+        for (int64_t i = tid; i < n64; i += kBuildThreads) struct_of[lo + i] = (int32_t)b;   // structure of every point
         if (n64 <= kBruteMax) {
             if (tid == 0) cellparam[b] = CellParam{0, 0, 0, 0};
             continue;
@@ -196,7 +198,7 @@ __global__ void __launch_bounds__(kNbrWarps * 32)
 neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t N, int64_t B, T r2,
                   int64_t max_nn, int loop, int rule, const V4<T> *__restrict__ spos,
                   const CellParam *__restrict__ cellparam, const int32_t *__restrict__ cell_of,
-                  const int32_t *__restrict__ cell_start, int32_t *__restrict__ deg,
+                  const int32_t *__restrict__ cell_start, const int32_t *__restrict__ struct_of, int32_t *__restrict__ deg,
                   const int64_t *__restrict__ offsets, FillOut out, int32_t *__restrict__ status) {
     __shared__ unsigned s_mask[FILL ? kNbrWarps * (kCapBits / 32) : 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -204,13 +206,7 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
     const unsigned lt = lanemask_lt();
 
     for (int64_t i = (int64_t)blockIdx.x * kNbrWarps + warp; i < N; i += (int64_t)gridDim.x * kNbrWarps) {
-        // structure of i: the last b with ptr[b] <= i (empty structures share a start and are skipped)
-        int64_t blo = 0, bhi = B;  // invariant: ptr[blo] <= i < ptr[bhi]
-        while (bhi - blo > 1) {
-            const int64_t mid = (blo + bhi) >> 1;
-            if (ptr[mid] <= i) blo = mid; else bhi = mid;
-        }
-        const int64_t b = blo;
+        const int64_t b = struct_of[i];
         const int64_t lo = ptr[b];
         const int n = (int)(ptr[b + 1] - lo);
         const int il = (int)(i - lo);
@@ -265,30 +261,40 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
                     for (int w = lane; w < nwords; w += 32) mask[w] = 0u;
                     __syncwarp();
                 }
-                for (int dz = -1; dz <= 1; dz++) {
-                    const int zz = cz + dz;
-                    if (zz < 0 || zz >= gz) continue;
-                    for (int dy = -1; dy <= 1; dy++) {
-                        const int yy = cy + dy;
-                        if (yy < 0 || yy >= gy) continue;
+                // lanes 0-8 fetch the candidate run of one (dy, dz) row each, so the nine pairs of cell-start
+                // reads are in flight together; every lane then keeps two loads per row in flight
+                int rk0 = 0, rk1 = 0;
+                if (lane < 9) {
+                    const int yy = cy + lane % 3 - 1, zz = cz + lane / 3 - 1;
+                    if (yy >= 0 && yy < gy && zz >= 0 && zz < gz) {
                         const int rowbase = gx * (yy + gy * zz);
-                        const int k0 = cs[rowbase + x0], k1 = cs[rowbase + x1 + 1];
-                        for (int k = k0 + lane; k < k1; k += 32) {
-                            const V4<T> p = sp[k];
-                            const int j = idx_of(p);
-                            const T d2 = dist2_rn(xi, yi, zi, p.x, p.y, p.z);
-                            if (d2 < r2) {
-                                if (FILL) {
-                                    const int jw = j - wbase;
-                                    if ((loop || j != il) && jw >= 0 && jw < wbits)
-                                        atomicOr(&mask[jw >> 5], 1u << (jw & 31));
-                                } else {
-                                    cnt_lo += (j < il);
-                                    cnt_hi += (j > il);
-                                }
-                            }
+                        rk0 = cs[rowbase + x0];
+                        rk1 = cs[rowbase + x1 + 1];
+                    }
+                }
+                auto test = [&](const V4<T> &p) {
+                    const int j = idx_of(p);
+                    const T d2 = dist2_rn(xi, yi, zi, p.x, p.y, p.z);
+                    if (d2 < r2) {
+                        if (FILL) {
+                            const int jw = j - wbase;
+                            if ((loop || j != il) && jw >= 0 && jw < wbits) atomicOr(&mask[jw >> 5], 1u << (jw & 31));
+                        } else {
+                            cnt_lo += (j < il);
+                            cnt_hi += (j > il);
                         }
                     }
+                };
+#pragma unroll
+                for (int row = 0; row < 9; row++) {
+                    const int k0 = __shfl_sync(0xffffffffu, rk0, row), k1 = __shfl_sync(0xffffffffu, rk1, row);
+                    const int ka = k0 + lane, kb = ka + 32;
+                    V4<T> pa, pb;
+                    if (ka < k1) pa = sp[ka];
+                    if (kb < k1) pb = sp[kb];
+                    if (ka < k1) test(pa);
+                    if (kb < k1) test(pb);
+                    for (int k = kb + 32; k < k1; k += 32) test(sp[k]);
                 }
                 if (FILL) {
                     __syncwarp();
@@ -451,20 +457,21 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
     auto *cellparam = (CellParam *)(w + L.cellparam);
     auto *cell_of = (int32_t *)(w + L.cell_of);
     auto *cell_start = (int32_t *)(w + L.cell_start);
+    auto *struct_of = (int32_t *)(w + L.struct_of);
     auto *bsum = (int64_t *)(w + L.bsum);
     const T r2 = (T)(r * r);
     const int nbr_grid = grid_for(N, kNbrWarps, 32);
     if (!fill) {
-        build_cells_kernel<T><<<grid_for(B, 1, 8), kBuildThreads, 0, st>>>(pos, ptr, B, (T)r, spos, cellparam, cell_of, cell_start);
+        build_cells_kernel<T><<<grid_for(B, 1, 8), kBuildThreads, 0, st>>>(pos, ptr, B, (T)r, spos, cellparam, cell_of, cell_start, struct_of);
         neighbours_kernel<T, false><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
-                                                                         cell_of, cell_start, deg, nullptr, out, status);
+                                                                         cell_of, cell_start, struct_of, deg, nullptr, out, status);
         const int64_t nb = (N + kScanBlock - 1) / kScanBlock;
         scan_block_sums_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum);
         scan_of_sums_kernel<<<1, kScanBlock, 0, st>>>(bsum, nb, offsets + N);
         scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum, offsets);
     } else {
         neighbours_kernel<T, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
-                                                                        cell_of, cell_start, nullptr, offsets, out, status);
+                                                                        cell_of, cell_start, struct_of, nullptr, offsets, out, status);
     }
     return check_launch();
 }
