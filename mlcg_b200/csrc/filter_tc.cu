@@ -18,8 +18,7 @@ namespace mlcgb {
 
 constexpr int kF = 128;                 // filters / hidden width of the filter network
 constexpr int kTcThreads = 512;         // thread t: row t % 128 of the tile, 32-column quarter t / 128
-constexpr float kWScale = 64.f;         // power-of-two operand scalings keep the fp16 "low" parts normal
-constexpr float kActScale = 16.f;
+constexpr float kWScale = 64.f;         // power-of-two weight scaling keeps the fp16 "low" parts of the weights normal
 constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
 
 struct FilterFwdParams {
@@ -38,9 +37,11 @@ template <bool SPLIT>
 struct FilterSmem {
     static constexpr int kTile = SPLIT ? 2 * 32768 : 32768;   // one 128x128 operand tile (hi [+ lo])
     static constexpr int kA = 0, kB1 = kTile, kB2 = 2 * kTile, kMisc = 3 * kTile;
-    // misc: bias [128] f32 | basis table [128] float2 | exchange [4][128] f32 x2 | barrier, TMEM slot, error flag
-    static constexpr int kBias = 0, kTable = 512, kRed = 1536, kRed2 = 3584, kBar = 5632;
-    static constexpr int kTotal = kMisc + 6144 + 1024;        // + alignment slack
+    // misc: bias, scaled bias [2][128] f32 | basis table [128] float2 | exchange [4][128] f32 x2 | barrier, TMEM slot, error flag
+    static constexpr int kBias = 0, kTable = 1024, kRed = 2048, kRed2 = 4096, kBar = 6144;
+    // 64 KB fp32 staging tile for coalesced global traffic: over the A operand where that is 64 KB, else its own region
+    static constexpr int kStage = SPLIT ? kA : kMisc + 7168;
+    static constexpr int kTotal = kMisc + 7168 + (SPLIT ? 0 : 65536) + 1024;        // + alignment slack
 };
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -48,21 +49,21 @@ __device__ __forceinline__ float tanh_fast(float x) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float rcp_fast(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float ex2_fast(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// tanh to ~2e-7 absolute: 1 - 2/(e^{2|x|} + 1) with the sign restored
-__device__ __forceinline__ float tanh_acc(float x) {
-    const float t = ex2_fast(fminf(fabsf(x), 15.f) * (2.f * kLog2e));
-    return copysignf(1.f - __fdividef(2.f, t + 1.f), x);
-}
-
 // Per-edge part of the basis: value t(d) the basis functions are centred on and its derivative.
 //   Gaussian:   g_k = exp(coeff (d - offset_k)^2)                 t = d,                 t' = 1
 //   exp-normal: g_k = exp(-beta_k (u - mean_k)^2), u = exp(alpha (lower - d)):  t = u,   t' = -alpha u
-// The table holds (centre_k, s_k) with g_k = 2^(s_k (t - centre_k)^2).
+// The table holds (c_k, w_k) with g_k = 2^(-w_k (t - c_k)^2), w_k = width_k log2(e)
+// (widths are positive: -coeff for the Gaussian, beta_k for the exp-normal basis).
 __device__ __forceinline__ void edge_arg(float d, const RbfDev<float> &s, float &t, float &dt) {
     if (s.kind == 0) {
         t = d;
@@ -86,12 +87,13 @@ __device__ __forceinline__ uint32_t filter_setup(const FilterFwdParams &p, uint8
     float2 *s_tab = reinterpret_cast<float2 *>(smem + L::kMisc + L::kTable);
     if (tid < kF) {
         s_b1[tid] = p.b1[tid];
-        float c = 0.f, sc = 0.f;
+        float c = 1e4f, w = 1.f;                       // beyond R: 2^(-(t - 1e4)^2) = 0
         if (tid < p.rbf.R) {
             c = p.rbf.p0[tid];
-            sc = (p.rbf.kind == 0 ? p.rbf.p1[0] : -p.rbf.p1[tid]) * kLog2e;
+            w = (p.rbf.kind == 0 ? -p.rbf.p1[0] : p.rbf.p1[tid]) * kLog2e;
         }
-        s_tab[tid] = make_float2(c, sc);
+        s_tab[tid] = make_float2(c, w);
+        s_b1[kF + tid] = p.b1[tid] * (2.f * kLog2e);    // bias pre-multiplied for the exp2-based tanh
     }
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar);
     uint32_t *s_tmem = reinterpret_cast<uint32_t *>(s_bar + 1);
@@ -109,25 +111,40 @@ __device__ __forceinline__ uint32_t filter_setup(const FilterFwdParams &p, uint8
     return *s_tmem;
 }
 
-// this thread's 32 columns of phi (scaled) -> A operand; columns at or beyond R are zero
+// this thread's 32 columns of phi -> A operand: phi_k = amp * g_k = 2^(log2(amp) - w_k (t - c_k)^2)
 template <bool SPLIT>
-__device__ __forceinline__ void write_phi(uint8_t *sA_hi, uint8_t *sA_lo, const float2 *s_tab, int r, int col0, int R, float t, float amp) {
+__device__ __forceinline__ void write_phi(uint8_t *sA_hi, uint8_t *sA_lo, const float2 *s_tab, int r, int col0, float t, float log2amp) {
     using namespace tc;
 #pragma unroll
     for (int c = 0; c < 4; c++) {
         float x[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            const int k = col0 + c * 8 + j;
-            const float2 cs = s_tab[k];
-            const float v = t - cs.x;
-            x[j] = k < R ? amp * ex2_fast(cs.y * v * v) : 0.f;
+            const float2 cw = s_tab[col0 + c * 8 + j];
+            const float u = t - cw.x;
+            x[j] = ex2_fast(fmaf(-cw.y * u, u, log2amp));
         }
         uint4 hi, lo;
         pack8<SPLIT>(x, hi, lo);
         const uint32_t off = chunk_offset(r, col0 + c * 8);
         *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
         if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
+    }
+}
+
+// h = tanh(z) for this thread's 32 accumulator values, z = v * unscale + b1, through exp2: tanh z = sign(z) (1 - 2/(2^{|zz|} + 1)),
+// zz = 2 log2(e) z  (2^{|zz|} overflowing to inf gives exactly 1)
+template <bool SPLIT>
+__device__ __forceinline__ void tanh_row32(float (&v)[32], const float *s_b1s, int col0, float unscale2) {
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        const float zz = fmaf(v[j], unscale2, s_b1s[col0 + j]);
+        if (SPLIT) {
+            const float tt = ex2_fast(fabsf(zz));
+            v[j] = copysignf(fmaf(-2.f, rcp_fast(tt + 1.f), 1.f), zz);
+        } else {
+            v[j] = tanh_fast(zz * (0.5f * kLn2));
+        }
     }
 }
 
@@ -145,6 +162,12 @@ __device__ __forceinline__ void write_row32(uint8_t *sA_hi, uint8_t *sA_lo, int 
         *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
         if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
     }
+}
+
+// fp32 staging tile [128 rows][32 chunks of 16 B], chunk index XOR-ed with (row & 7): a thread writing its own
+// row and a warp reading one whole row are both free of bank conflicts
+__device__ __forceinline__ float4 *stage_chunk(uint8_t *stage, int row, int chunk) {
+    return reinterpret_cast<float4 *>(stage + row * 512 + ((chunk ^ (row & 7)) << 4));
 }
 
 // one GEMM issued by thread 0 and awaited by every thread; leaves the tile loop if the wait runs out
@@ -170,6 +193,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_tc_kernel(FilterFwdP
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t *sA_hi = smem + L::kA, *sA_lo = sA_hi + 32768;
+    uint8_t *stage = smem + L::kStage;
     const float *s_b1 = reinterpret_cast<const float *>(smem + L::kMisc + L::kBias);
     const float2 *s_tab = reinterpret_cast<const float2 *>(smem + L::kMisc + L::kTable);
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar);
@@ -179,8 +203,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_tc_kernel(FilterFwdP
     const int r = tid & 127, col0 = (tid >> 7) * 32;   // row of the tile, first of this thread's 32 columns
     const int R = p.rbf.R;
     const int Kpad1 = R <= 64 ? 64 : 128;
-    const float wscale = SPLIT ? kWScale : 1.f, ascale = SPLIT ? kActScale : 1.f;
-    const float unscale = 1.f / (wscale * ascale);
+    const float wscale = SPLIT ? kWScale : 1.f;
+    const float unscale = 1.f / wscale;
 
     const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 256);
     const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 TMEM lanes
@@ -197,7 +221,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_tc_kernel(FilterFwdP
         if (col0 < Kpad1) {
             float t, dt;
             edge_arg(de, p.rbf, t, dt);
-            write_phi<SPLIT>(sA_hi, sA_lo, s_tab, r, col0, R, t, ascale * envelope_jet<float, 0>(de, p.rbf).c[0]);
+            write_phi<SPLIT>(sA_hi, sA_lo, s_tab, r, col0, t, log2f(envelope_jet<float, 0>(de, p.rbf).c[0]));
         }
         MLCGB_RUN_GEMM(0, L::kB1, Kpad1 / 16, 0, 128)
 
@@ -205,28 +229,32 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_tc_kernel(FilterFwdP
         {
             float v[32];
             tmem_ld32(t_lane + col0, v);
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-                const float z = fmaf(v[j], unscale, s_b1[col0 + j]);
-                v[j] = SPLIT ? tanh_acc(z) : tanh_fast(z);
-            }
-            write_row32<SPLIT>(sA_hi, sA_lo, r, col0, v, ascale);
+            tanh_row32<SPLIT>(v, s_b1 + kF, col0, unscale * (2.f * kLog2e));
+            write_row32<SPLIT>(sA_hi, sA_lo, r, col0, v, 1.f);
         }
         MLCGB_RUN_GEMM(128, L::kB2, kF / 16, 0, 128)
 
-        // ---- epilogue 2: W = y * C(d)
+        // ---- epilogue 2: W = y * C(d), staged through shared memory so that each warp writes whole 512-byte rows
         {
             const float C = envelope_jet<float, 0>(de, p.conv).c[0] * unscale;
             float v[32];
             tmem_ld32(t_lane + 128 + col0, v);
-            if (live) {
-                float4 *dst = reinterpret_cast<float4 *>(p.W + e * kF + col0);
 #pragma unroll
-                for (int q = 0; q < 8; q++) dst[q] = make_float4(v[4 * q] * C, v[4 * q + 1] * C, v[4 * q + 2] * C, v[4 * q + 3] * C);
-            }
+            for (int q = 0; q < 8; q++)
+                *stage_chunk(stage, r, (col0 >> 2) + q) = make_float4(v[4 * q] * C, v[4 * q + 1] * C, v[4 * q + 2] * C, v[4 * q + 3] * C);
         }
         tc_fence_before();
-        __syncthreads();   // TMEM and sA are reused by the next tile
+        __syncthreads();
+        {
+            const int lane = tid & 31;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int row = warp * 8 + i;
+                const int64_t er = tile * kRows + row;
+                if (er < p.E) __stcs(reinterpret_cast<float4 *>(p.W + er * kF) + lane, *stage_chunk(stage, row, lane));
+            }
+        }
+        __syncthreads();   // staging (= the A operand in the split mode) and TMEM are reused by the next tile
     }
 
     if (*s_err && tid == 0) atomicOr(p.status, 8);
@@ -279,6 +307,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t *sA_hi = smem + L::kA, *sA_lo = sA_hi + 32768;
+    uint8_t *stage = smem + L::kStage;   // free whenever no GEMM is reading the A operand
     const float *s_b1 = reinterpret_cast<const float *>(smem + L::kMisc + L::kBias);
     const float2 *s_tab = reinterpret_cast<const float2 *>(smem + L::kMisc + L::kTable);
     float *s_red = reinterpret_cast<float *>(smem + L::kMisc + L::kRed);     // [4][128] exchange between column quarters
@@ -290,8 +319,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
     const int r = tid & 127, qt = tid >> 7, col0 = qt * 32;
     const int R = p.rbf.R;
     const int Kpad1 = R <= 64 ? 64 : 128;
-    const float wscale = SPLIT ? kWScale : 1.f, ascale = SPLIT ? kActScale : 1.f;
-    const float unscale = 1.f / (wscale * ascale);
+    const float wscale = SPLIT ? kWScale : 1.f;
+    const float unscale = 1.f / wscale;
 
     const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 512);
     const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -309,20 +338,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
         const Jet<float, 1> env = envelope_jet<float, 1>(de, p.rbf);
 
         // ---- step 1: phi -> A operand, Z = phi A1^T
-        if (col0 < Kpad1) write_phi<SPLIT>(sA_hi, sA_lo, s_tab, r, col0, R, t, ascale * env.c[0]);
+        if (col0 < Kpad1) write_phi<SPLIT>(sA_hi, sA_lo, s_tab, r, col0, t, log2f(env.c[0]));
         MLCGB_RUN_GEMM(0, L::kB1, Kpad1 / 16, 0, 128)
 
         // ---- step 2: h = tanh(z + b1): kept in tensor memory (over z) and written as the A operand; Y = h A2^T
         {
             float v[32];
             tmem_ld32(t_lane + col0, v);
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-                const float z = fmaf(v[j], unscale, s_b1[col0 + j]);
-                v[j] = SPLIT ? tanh_acc(z) : tanh_fast(z);
-            }
+            tanh_row32<SPLIT>(v, s_b1 + kF, col0, unscale * (2.f * kLog2e));
             tmem_st32(t_lane + col0, v);
-            write_row32<SPLIT>(sA_hi, sA_lo, r, col0, v, ascale);
+            write_row32<SPLIT>(sA_hi, sA_lo, r, col0, v, 1.f);
         }
         MLCGB_RUN_GEMM(128, L::kB2, kF / 16, 0, 128)
 
@@ -331,19 +356,30 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
         float g[32];
         float gC = 0.f, rmax = 0.f;
         {
+            // gW = xl[row0] * gagg[row1] for this warp's 32 rows x 32 columns, fetched four rows per instruction
+            // (eight lanes cover 128 contiguous bytes of a node row) and turned row-per-lane through shared memory
+            const int lane = tid & 31, sub = lane >> 3, cc = (col0 >> 2) + (lane & 7);
+#pragma unroll
+            for (int it = 0; it < 8; it++) {
+                const int rl = it * 4 + sub;
+                const int64_t j0 = __shfl_sync(0xffffffffu, i0, rl), j1 = __shfl_sync(0xffffffffu, i1, rl);
+                const int lv = __shfl_sync(0xffffffffu, (int)live, rl);
+                const float4 a = __ldg(reinterpret_cast<const float4 *>(q.xl + j0 * kF) + cc);
+                const float4 b = __ldg(reinterpret_cast<const float4 *>(q.gagg + j1 * kF) + cc);
+                const float m = lv ? 1.f : 0.f;
+                *stage_chunk(stage, (r & ~31) + rl, cc) = make_float4(a.x * b.x * m, a.y * b.y * m, a.z * b.z * m, a.w * b.w * m);
+            }
+            __syncwarp();
             float v[32];
             tmem_ld32(t_lane + 128 + col0, v);
-            const float4 *xa = reinterpret_cast<const float4 *>(q.xl + i0 * kF + col0);
-            const float4 *ga = reinterpret_cast<const float4 *>(q.gagg + i1 * kF + col0);
 #pragma unroll
             for (int w = 0; w < 8; w++) {
-                const float4 a = __ldg(xa + w), b = __ldg(ga + w);
-                const float gw[4] = {a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w};
+                const float4 gw4 = *stage_chunk(stage, r, (col0 >> 2) + w);
+                const float gw[4] = {gw4.x, gw4.y, gw4.z, gw4.w};
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const float tt = live ? gw[j] : 0.f;
-                    gC = fmaf(tt, v[4 * w + j], gC);
-                    const float gy = tt * cj.c[0];
+                    gC = fmaf(gw[j], v[4 * w + j], gC);
+                    const float gy = gw[j] * cj.c[0];
                     g[4 * w + j] = gy;
                     rmax = fmaxf(rmax, fabsf(gy));
                 }
@@ -380,20 +416,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
         write_row32<SPLIT>(sA_hi, sA_lo, r, col0, g, sc4);
         MLCGB_RUN_GEMM(384, L::kB1, kF / 16, 1, Kpad1)
 
-        // ---- step 5: gd = sum_r gphi_r phi'_r(d) + gC C'(d),  phi'_k = g_k (env' + env 2 ln2 s_k (t - c_k) t')
+        // ---- step 5: gd = sum_r gphi_r phi'_r(d) + gC C'(d),  phi'_k = g_k (env' - env 2 ln2 w_k (t - c_k) t')
         float acc = 0.f;
         if (col0 < Kpad1) {
             float v[32];
             tmem_ld32(t_lane + 384 + col0, v);
-            const float e0 = env.c[0], e1 = env.c[1], two = 2.f * kLn2 * dt;
+            const float e0 = env.c[0], e1 = env.c[1], m2 = -2.f * kLn2 * dt * e0;
 #pragma unroll
             for (int j = 0; j < 32; j++) {
-                const int k = col0 + j;
-                const float2 cs = s_tab[k];
-                const float u = t - cs.x;
-                const float gk = ex2_fast(cs.y * u * u);
-                const float dphi = gk * fmaf(e0 * two, cs.y * u, e1);
-                if (k < R) acc = fmaf(v[j], dphi, acc);
+                const float2 cw = s_tab[col0 + j];
+                const float u = t - cw.x, wu = cw.y * u;
+                const float gk = ex2_fast(-wu * u);
+                acc = fmaf(v[j], gk * fmaf(m2, wu, e1), acc);            // columns at or beyond R: gk = 0
             }
             acc *= 1.f / (sc4 * wscale);
         }
