@@ -263,6 +263,145 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_tc_kernel(FilterFwdP
     if (warp == 0) tmem_free(tmem, 256);
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Forward, pipelined: the A operands (phi, h) live in tensor memory instead of shared memory, which
+// leaves room for two tiles in flight.  TMEM columns: D1 [0,128) | D2 [128,256) | A of even tiles
+// [256,384) | A of odd tiles [384,512) (fp16 hi in the first 64 columns of an A block, lo in the last 64).
+// While GEMM 1 of tile i runs the threads store W of tile i-1; while GEMM 2 of tile i runs they evaluate
+// the radial basis of tile i+1.
+// ------------------------------------------------------------------------------------------------
+template <bool SPLIT>
+__global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFwdParams p) {
+    using namespace tc;
+    using L = FilterSmem<SPLIT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *stage = smem + L::kA;                       // the A region of the layout is free here: 64 KB (split) ...
+    if (!SPLIT) stage = smem + L::kStage;                // ... or the separate staging region
+    const float *s_b1 = reinterpret_cast<const float *>(smem + L::kMisc + L::kBias);
+    const float2 *s_tab = reinterpret_cast<const float2 *>(smem + L::kMisc + L::kTable);
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar);
+    uint64_t *s_bar2 = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar + 64);
+    int *s_err = reinterpret_cast<int *>(reinterpret_cast<uint32_t *>(s_bar + 1) + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = tid & 127, col0 = (tid >> 7) * 32;
+    const int R = p.rbf.R;
+    const int Kpad1 = R <= 64 ? 64 : 128;
+    const float wscale = SPLIT ? kWScale : 1.f;
+    const float unscale = 1.f / wscale;
+
+    const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 512);
+    if (tid == 0) mbar_init(smem_u32(s_bar2), 1);
+    __syncthreads();
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t t_lane = tmem + lane_off;
+    const uint32_t bar1 = smem_u32(s_bar), bar2 = smem_u32(s_bar2);
+    const uint32_t b1_hi = smem_u32(smem + L::kB1), b1_lo = b1_hi + 32768, b2_hi = smem_u32(smem + L::kB2), b2_lo = b2_hi + 32768;
+    uint32_t ph1 = 0, ph2 = 0;
+    bool failed = false;
+
+    const int64_t ntiles = (p.E + kRows - 1) / kRows;
+    const int64_t first = blockIdx.x, step = gridDim.x;
+
+    auto load_d = [&](int64_t tile) { const int64_t e = tile * kRows + r; return e < p.E ? p.d[e] : 1.f; };
+    auto basis_to_tmem = [&](float de, uint32_t ta) {          // phi_k(d) for this thread's 32 columns -> A operand
+        if (col0 < Kpad1) {
+            float t, dt;
+            edge_arg(de, p.rbf, t, dt);
+            const float l2a = log2f(envelope_jet<float, 0>(de, p.rbf).c[0]);
+            float x[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const float2 cw = s_tab[col0 + j];
+                const float u = t - cw.x;
+                x[j] = ex2_fast(fmaf(-cw.y * u, u, l2a));
+            }
+            store_a_tmem<SPLIT>(ta + lane_off, col0, x, 1.f);
+        }
+        tmem_wait_st();
+    };
+    auto store_w = [&](int64_t tile, float de) {               // W = y * C(d): D2 -> shared-memory stage -> whole rows
+        const float C = envelope_jet<float, 0>(de, p.conv).c[0] * unscale;
+        float v[32];
+        tmem_ld32(t_lane + 128 + col0, v);
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+            *stage_chunk(stage, r, (col0 >> 2) + q) = make_float4(v[4 * q] * C, v[4 * q + 1] * C, v[4 * q + 2] * C, v[4 * q + 3] * C);
+        tc_fence_before();
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int row = warp * 8 + i;
+            const int64_t er = tile * kRows + row;
+            if (er < p.E) __stcs(reinterpret_cast<float4 *>(p.W + er * kF) + lane, *stage_chunk(stage, row, lane));
+        }
+    };
+
+    float de = 0.f, de_prev = 0.f;
+    if (first < ntiles) {
+        de = load_d(first);
+        basis_to_tmem(de, tmem + 256);
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            issue_gemm_ts<SPLIT>(tmem, tmem + 256, b1_hi, b1_lo, Kpad1 / 16, 0, 128);
+            mma_commit(bar1);
+        }
+    }
+    int s = 0;
+    for (int64_t tile = first; tile < ntiles; tile += step, s ^= 1) {
+        const uint32_t ta = tmem + 256 + s * 128, ta_next = tmem + 256 + (s ^ 1) * 128;
+        // (a) GEMM 1 of this tile is running: write out W of the previous tile
+        if (tile != first) store_w(tile - step, de_prev);
+        // (b) h = tanh(z + b1) -> A operand (over phi, which GEMM 1 has finished reading), then GEMM 2
+        if (!mbar_wait(bar1, ph1)) failed = true;
+        ph1 ^= 1;
+        tc_fence_after();
+        {
+            float v[32];
+            tmem_ld32(t_lane + col0, v);
+            tanh_row32<SPLIT>(v, s_b1 + kF, col0, unscale * (2.f * kLog2e));
+            store_a_tmem<SPLIT>(ta + lane_off, col0, v, 1.f);
+            tmem_wait_st();
+        }
+        tc_fence_before();
+        __syncthreads();                                         // also: every thread is done with the stage of (a)
+        if (tid == 0) {
+            tc_fence_after();
+            issue_gemm_ts<SPLIT>(tmem + 128, ta, b2_hi, b2_lo, kF / 16, 0, 128);
+            mma_commit(bar2);
+        }
+        // (c) GEMM 2 is running: radial basis of the next tile into the other A block
+        const int64_t next = tile + step;
+        de_prev = de;
+        if (next < ntiles) {
+            de = load_d(next);
+            basis_to_tmem(de, ta_next);
+        }
+        if (!mbar_wait(bar2, ph2)) failed = true;
+        ph2 ^= 1;
+        tc_fence_after();
+        if (failed) s_err[0] = 1;
+        tc_fence_before();
+        __syncthreads();
+        if (s_err[0]) break;
+        if (next < ntiles && tid == 0) {                          // GEMM 1 of the next tile (D1 was consumed in (b))
+            tc_fence_after();
+            issue_gemm_ts<SPLIT>(tmem, ta_next, b1_hi, b1_lo, Kpad1 / 16, 0, 128);
+            mma_commit(bar1);
+        }
+        if (next >= ntiles) store_w(tile, de_prev);               // last tile of this CTA
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (s_err[0] && tid == 0) atomicOr(p.status, 8);
+    if (warp == 0) tmem_free(tmem, 512);
+}
+
 template <bool SPLIT>
 static int filter_fwd_launch(const FilterFwdParams &p, cudaStream_t st) {
     using L = FilterSmem<SPLIT>;
@@ -270,13 +409,13 @@ static int filter_fwd_launch(const FilterFwdParams &p, cudaStream_t st) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(filter_fwd_tc_kernel<SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
+        if (cudaFuncSetAttribute(filter_fwd_pipe_kernel<SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
             return check_launch();
         configured[dev] = true;
     }
     const int64_t ntiles = (p.E + tc::kRows - 1) / tc::kRows;
     const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
-    filter_fwd_tc_kernel<SPLIT><<<grid, kTcThreads, L::kTotal, st>>>(p);
+    filter_fwd_pipe_kernel<SPLIT><<<grid, kTcThreads, L::kTotal, st>>>(p);
     return check_launch();
 }
 

@@ -218,6 +218,75 @@ __device__ __forceinline__ void issue_gemm(uint32_t tmem_d, uint32_t a_hi, uint3
     }
 }
 
+// ---- A operand in tensor memory -----------------------------------------------------------------------
+// For 16-bit operands the tensor core can read A straight from TMEM: lane = row, each 32-bit column holds two
+// consecutive K elements (even k in the low half), so a K-step of 16 spans 8 columns.
+__device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// 32 fp32 values of one row (K range [k0, k0+32)) -> 16 packed columns of the high part (and of the low part)
+template <bool SPLIT>
+__device__ __forceinline__ void pack32(const float (&x)[32], float scale, uint32_t (&hi)[16], uint32_t (&lo)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const float a0 = x[2 * i] * scale, a1 = x[2 * i + 1] * scale;
+        if (SPLIT) {
+            const __half2 a = __floats2half2_rn(a0, a1);
+            const float2 b = __half22float2(a);
+            const __half2 c = __floats2half2_rn(a0 - b.x, a1 - b.y);
+            hi[i] = *reinterpret_cast<const uint32_t *>(&a);
+            lo[i] = *reinterpret_cast<const uint32_t *>(&c);
+        } else {
+            const __nv_bfloat162 a = __floats2bfloat162_rn(a0, a1);
+            hi[i] = *reinterpret_cast<const uint32_t *>(&a);
+            lo[i] = 0u;
+        }
+    }
+}
+
+// write this thread's 32 K-elements of its row into the TMEM A operand (hi block at ta, lo block 64 columns further)
+template <bool SPLIT>
+__device__ __forceinline__ void store_a_tmem(uint32_t ta_lane, int k0, const float (&x)[32], float scale) {
+    uint32_t hi[16], lo[16];
+    pack32<SPLIT>(x, scale, hi, lo);
+    tmem_st16(ta_lane + (k0 >> 1), hi);
+    if (SPLIT) tmem_st16(ta_lane + 64 + (k0 >> 1), lo);
+}
+
+// GEMM with the A operand in tensor memory (hi at ta, lo at ta + 64 columns)
+template <bool SPLIT>
+__device__ __forceinline__ void issue_gemm_ts(uint32_t tmem_d, uint32_t ta, uint32_t b_hi, uint32_t b_lo, int ksteps, int b_mn, int n = 128) {
+    const uint32_t idesc = instr_desc(SPLIT ? 0 : 1, b_mn, n);
+    const uint64_t dbh = b_mn ? desc_mnmajor(b_hi) : desc_kmajor(b_hi), dbl = b_mn ? desc_mnmajor(b_lo) : desc_kmajor(b_lo);
+    for (int ks = 0; ks < ksteps; ks++) {
+        const uint64_t bh = b_mn ? kstep_mnmajor(dbh, ks) : kstep_kmajor(dbh, ks);
+        const uint64_t bl = b_mn ? kstep_mnmajor(dbl, ks) : kstep_kmajor(dbl, ks);
+        mma_f16_ts(tmem_d, ta + ks * 8, bh, idesc, ks > 0 ? 1u : 0u);
+        if (SPLIT) {
+            mma_f16_ts(tmem_d, ta + ks * 8, bl, idesc, 1u);
+            mma_f16_ts(tmem_d, ta + 64 + ks * 8, bh, idesc, 1u);
+        }
+    }
+}
+
 // Power-of-two factor that brings a row whose largest magnitude is `rmax` to [8, 16): exact to apply and to
 // undo, keeps fp16 operands far from overflow and their low parts out of the subnormal range.
 __device__ __forceinline__ float row_scale(float rmax) {
