@@ -2,11 +2,11 @@
 //
 //   W[e,:] = ( tanh( phi(d_e) A1^T + b1 ) A2^T ) * C(d_e)            src/mlcg/nn/schnet.py:340-341
 //
-// One persistent CTA per SM walks 128-edge tiles.  Per tile: the radial basis is evaluated straight
-// into the A operand in shared memory (it never exists in HBM), GEMM 1 accumulates in tensor memory,
-// its epilogue (bias, tanh) writes the hidden activations back to shared memory as the A operand of
-// GEMM 2, and the second epilogue applies the cutoff envelope and stores W.  Weights are converted
-// once per CTA and stay resident in shared memory.
+// One persistent CTA per SM (512 threads: thread = one tile row x 32 columns) walks 128-edge tiles.  The
+// radial basis is evaluated straight into the A operand (it never exists in HBM); A operands live in
+// tensor memory (fp16 pairs packed two per 32-bit column), accumulators too; the weight tiles are
+// converted once per CTA and stay in shared memory (K-major, 128-byte swizzle), and serve the backward
+// GEMMs as MN-major operands.  W leaves through a swizzled shared-memory stage as whole 512-byte rows.
 //
 // Precision modes.  0: every fp32 value is carried as an fp16 pair (value = hi + lo, ~22 bits) and
 // each GEMM runs hi*hi + hi*lo + lo*hi with fp32 accumulation — the products an fp32 GEMM forms, at
@@ -111,27 +111,6 @@ __device__ __forceinline__ uint32_t filter_setup(const FilterFwdParams &p, uint8
     return *s_tmem;
 }
 
-// this thread's 32 columns of phi -> A operand: phi_k = amp * g_k = 2^(log2(amp) - w_k (t - c_k)^2)
-template <bool SPLIT>
-__device__ __forceinline__ void write_phi(uint8_t *sA_hi, uint8_t *sA_lo, const float2 *s_tab, int r, int col0, float t, float log2amp) {
-    using namespace tc;
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-        float x[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const float2 cw = s_tab[col0 + c * 8 + j];
-            const float u = t - cw.x;
-            x[j] = ex2_fast(fmaf(-cw.y * u, u, log2amp));
-        }
-        uint4 hi, lo;
-        pack8<SPLIT>(x, hi, lo);
-        const uint32_t off = chunk_offset(r, col0 + c * 8);
-        *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
-        if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
-    }
-}
-
 // h = tanh(z) for this thread's 32 accumulator values, z = v * unscale + b1, through exp2: tanh z = sign(z) (1 - 2/(2^{|zz|} + 1)),
 // zz = 2 log2(e) z  (2^{|zz|} overflowing to inf gives exactly 1)
 template <bool SPLIT>
@@ -148,121 +127,11 @@ __device__ __forceinline__ void tanh_row32(float (&v)[32], const float *s_b1s, i
     }
 }
 
-template <bool SPLIT>
-__device__ __forceinline__ void write_row32(uint8_t *sA_hi, uint8_t *sA_lo, int r, int col0, const float (&v)[32], float scale) {
-    using namespace tc;
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-        float x[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) x[j] = v[c * 8 + j] * scale;
-        uint4 hi, lo;
-        pack8<SPLIT>(x, hi, lo);
-        const uint32_t off = chunk_offset(r, col0 + c * 8);
-        *reinterpret_cast<uint4 *>(sA_hi + off) = hi;
-        if (SPLIT) *reinterpret_cast<uint4 *>(sA_lo + off) = lo;
-    }
-}
-
 // fp32 staging tile [128 rows][32 chunks of 16 B], chunk index XOR-ed with (row & 7): a thread writing its own
 // row and a warp reading one whole row are both free of bank conflicts
 __device__ __forceinline__ float4 *stage_chunk(uint8_t *stage, int row, int chunk) {
     return reinterpret_cast<float4 *>(stage + row * 512 + ((chunk ^ (row & 7)) << 4));
 }
-
-// one GEMM issued by thread 0 and awaited by every thread; leaves the tile loop if the wait runs out
-#define MLCGB_RUN_GEMM(TCOL, BOFF, KSTEPS, BMN, NN)                                                           \
-    fence_async_smem();                                                                                       \
-    tc_fence_before();                                                                                        \
-    __syncthreads();                                                                                          \
-    if (tid == 0) {                                                                                           \
-        tc_fence_after();                                                                                     \
-        issue_gemm<SPLIT>(tmem + (TCOL), a_hi, a_lo, smem_u32(smem + (BOFF)), smem_u32(smem + (BOFF) + 32768), (KSTEPS), (BMN), (NN)); \
-        mma_commit(bar);                                                                                      \
-    }                                                                                                         \
-    if (!mbar_wait(bar, phase)) *s_err = 1;                                                                   \
-    phase ^= 1;                                                                                               \
-    tc_fence_after();                                                                                         \
-    __syncthreads();                                                                                          \
-    if (*s_err) break;
-
-template <bool SPLIT>
-__global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_tc_kernel(FilterFwdParams p) {
-    using namespace tc;
-    using L = FilterSmem<SPLIT>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t *sA_hi = smem + L::kA, *sA_lo = sA_hi + 32768;
-    uint8_t *stage = smem + L::kStage;
-    const float *s_b1 = reinterpret_cast<const float *>(smem + L::kMisc + L::kBias);
-    const float2 *s_tab = reinterpret_cast<const float2 *>(smem + L::kMisc + L::kTable);
-    uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar);
-    int *s_err = reinterpret_cast<int *>(reinterpret_cast<uint32_t *>(s_bar + 1) + 1);
-
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int r = tid & 127, col0 = (tid >> 7) * 32;   // row of the tile, first of this thread's 32 columns
-    const int R = p.rbf.R;
-    const int Kpad1 = R <= 64 ? 64 : 128;
-    const float wscale = SPLIT ? kWScale : 1.f;
-    const float unscale = 1.f / wscale;
-
-    const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 256);
-    const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 TMEM lanes
-    const uint32_t a_hi = smem_u32(sA_hi), a_lo = smem_u32(sA_lo), bar = smem_u32(s_bar);
-    uint32_t phase = 0;
-
-    const int64_t ntiles = (p.E + kRows - 1) / kRows;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const int64_t e = tile * kRows + r;
-        const bool live = e < p.E;
-        const float de = live ? p.d[e] : 1.f;
-
-        // ---- A operand of GEMM 1: phi_k(d) for this thread's columns;  Z = phi A1^T
-        if (col0 < Kpad1) {
-            float t, dt;
-            edge_arg(de, p.rbf, t, dt);
-            write_phi<SPLIT>(sA_hi, sA_lo, s_tab, r, col0, t, log2f(envelope_jet<float, 0>(de, p.rbf).c[0]));
-        }
-        MLCGB_RUN_GEMM(0, L::kB1, Kpad1 / 16, 0, 128)
-
-        // ---- epilogue 1: h = tanh(z + b1) -> A operand of GEMM 2 (GEMM 1 has finished reading sA);  Y = h A2^T
-        {
-            float v[32];
-            tmem_ld32(t_lane + col0, v);
-            tanh_row32<SPLIT>(v, s_b1 + kF, col0, unscale * (2.f * kLog2e));
-            write_row32<SPLIT>(sA_hi, sA_lo, r, col0, v, 1.f);
-        }
-        MLCGB_RUN_GEMM(128, L::kB2, kF / 16, 0, 128)
-
-        // ---- epilogue 2: W = y * C(d), staged through shared memory so that each warp writes whole 512-byte rows
-        {
-            const float C = envelope_jet<float, 0>(de, p.conv).c[0] * unscale;
-            float v[32];
-            tmem_ld32(t_lane + 128 + col0, v);
-#pragma unroll
-            for (int q = 0; q < 8; q++)
-                *stage_chunk(stage, r, (col0 >> 2) + q) = make_float4(v[4 * q] * C, v[4 * q + 1] * C, v[4 * q + 2] * C, v[4 * q + 3] * C);
-        }
-        tc_fence_before();
-        __syncthreads();
-        {
-            const int lane = tid & 31;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int row = warp * 8 + i;
-                const int64_t er = tile * kRows + row;
-                if (er < p.E) __stcs(reinterpret_cast<float4 *>(p.W + er * kF) + lane, *stage_chunk(stage, row, lane));
-            }
-        }
-        __syncthreads();   // staging (= the A operand in the split mode) and TMEM are reused by the next tile
-    }
-
-    if (*s_err && tid == 0) atomicOr(p.status, 8);
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) tmem_free(tmem, 256);
-}
-
 
 // ------------------------------------------------------------------------------------------------
 // Forward, pipelined: the A operands (phi, h) live in tensor memory instead of shared memory, which
@@ -438,23 +307,28 @@ struct FilterBwdParams {
     float *gd;               // [E]
 };
 
+// ------------------------------------------------------------------------------------------------
+// Backward, pipelined.  A operands (phi, h, gy, gz) go through one 128-column block of tensor memory;
+// accumulators: T0 = Z then h (fp32) | T1 = Y then GH | T2 = GPHI.  Work placed under the GEMMs:
+// the gather of gW under GEMM 2, the basis derivatives under GEMM 4, the final reduction and the store
+// of gd under GEMM 1 of the next tile.
+// ------------------------------------------------------------------------------------------------
 template <bool SPLIT>
-__global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdParams q) {
+__global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBwdParams q) {
     using namespace tc;
     using L = FilterSmem<SPLIT>;
     const FilterFwdParams &p = q.f;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t *sA_hi = smem + L::kA, *sA_lo = sA_hi + 32768;
-    uint8_t *stage = smem + L::kStage;   // free whenever no GEMM is reading the A operand
+    uint8_t *stage = SPLIT ? smem + L::kA : smem + L::kStage;
     const float *s_b1 = reinterpret_cast<const float *>(smem + L::kMisc + L::kBias);
     const float2 *s_tab = reinterpret_cast<const float2 *>(smem + L::kMisc + L::kTable);
-    float *s_red = reinterpret_cast<float *>(smem + L::kMisc + L::kRed);     // [4][128] exchange between column quarters
+    float *s_red = reinterpret_cast<float *>(smem + L::kMisc + L::kRed);
     float *s_red2 = reinterpret_cast<float *>(smem + L::kMisc + L::kRed2);
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar);
     int *s_err = reinterpret_cast<int *>(reinterpret_cast<uint32_t *>(s_bar + 1) + 1);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = tid & 127, qt = tid >> 7, col0 = qt * 32;
     const int R = p.rbf.R;
     const int Kpad1 = R <= 64 ? 64 : 128;
@@ -462,42 +336,85 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
     const float unscale = 1.f / wscale;
 
     const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 512);
-    const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t a_hi = smem_u32(sA_hi), a_lo = smem_u32(sA_lo), bar = smem_u32(s_bar);
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t t_lane = tmem + lane_off;
+    const uint32_t T0 = 0, T1 = 128, T2 = 256, TA = 384;
+    const uint32_t bar = smem_u32(s_bar);
+    const uint32_t b1_hi = smem_u32(smem + L::kB1), b1_lo = b1_hi + 32768, b2_hi = smem_u32(smem + L::kB2), b2_lo = b2_hi + 32768;
     uint32_t phase = 0;
+    bool failed = false;
+
+    // issue one GEMM (A in tensor memory) after everybody's operand stores are visible
+#define ISSUE(TCOL, BHI, BLO, KSTEPS, BMN, NN)                                                  \
+    tc_fence_before();                                                                          \
+    __syncthreads();                                                                            \
+    if (tid == 0) {                                                                             \
+        tc_fence_after();                                                                       \
+        issue_gemm_ts<SPLIT>(tmem + (TCOL), tmem + TA, (BHI), (BLO), (KSTEPS), (BMN), (NN));    \
+        mma_commit(bar);                                                                        \
+    }
+#define AWAIT()                                   \
+    if (!mbar_wait(bar, phase)) failed = true;    \
+    phase ^= 1;                                   \
+    tc_fence_after();
+
+    struct EdgeScalars { float t, dt, e0, e1; };
+    auto scalars = [&](float de) {
+        EdgeScalars s;
+        edge_arg(de, p.rbf, s.t, s.dt);
+        const Jet<float, 1> env = envelope_jet<float, 1>(de, p.rbf);
+        s.e0 = env.c[0];
+        s.e1 = env.c[1];
+        return s;
+    };
+    auto basis_to_tmem = [&](const EdgeScalars &es) {
+        if (col0 < Kpad1) {
+            const float l2a = log2f(es.e0);
+            float x[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const float2 cw = s_tab[col0 + j];
+                const float u = es.t - cw.x;
+                x[j] = ex2_fast(fmaf(-cw.y * u, u, l2a));
+            }
+            store_a_tmem<SPLIT>(tmem + TA + lane_off, col0, x, 1.f);
+        }
+        tmem_wait_st();
+    };
 
     const int64_t ntiles = (p.E + kRows - 1) / kRows;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int64_t first = blockIdx.x, step = gridDim.x;
+    float de = 1.f;
+    EdgeScalars es{};
+    if (first < ntiles) {
+        const int64_t e = first * kRows + r;
+        de = e < p.E ? p.d[e] : 1.f;
+        es = scalars(de);
+        basis_to_tmem(es);
+        ISSUE(T0, b1_hi, b1_lo, Kpad1 / 16, 0, 128)
+    }
+    for (int64_t tile = first; tile < ntiles; tile += step) {
         const int64_t e = tile * kRows + r;
         const bool live = e < p.E;
-        const float de = live ? p.d[e] : 1.f;
         const int64_t i0 = live ? q.row0[e] : 0, i1 = live ? q.row1[e] : 0;
-        float t, dt;
-        edge_arg(de, p.rbf, t, dt);
-        const Jet<float, 1> env = envelope_jet<float, 1>(de, p.rbf);
+        const Jet<float, 1> cj = envelope_jet<float, 1>(de, p.conv);
 
-        // ---- step 1: phi -> A operand, Z = phi A1^T
-        if (col0 < Kpad1) write_phi<SPLIT>(sA_hi, sA_lo, s_tab, r, col0, t, log2f(env.c[0]));
-        MLCGB_RUN_GEMM(0, L::kB1, Kpad1 / 16, 0, 128)
-
-        // ---- step 2: h = tanh(z + b1): kept in tensor memory (over z) and written as the A operand; Y = h A2^T
+        // ---- GEMM 1 done: h = tanh(z + b1) kept in T0 (fp32) and written as the A operand; issue Y = h A2^T
+        AWAIT()
         {
             float v[32];
-            tmem_ld32(t_lane + col0, v);
+            tmem_ld32(t_lane + T0 + col0, v);
             tanh_row32<SPLIT>(v, s_b1 + kF, col0, unscale * (2.f * kLog2e));
-            tmem_st32(t_lane + col0, v);
-            write_row32<SPLIT>(sA_hi, sA_lo, r, col0, v, 1.f);
+            tmem_st32(t_lane + T0 + col0, v);
+            store_a_tmem<SPLIT>(tmem + TA + lane_off, col0, v, 1.f);
+            tmem_wait_st();
         }
-        MLCGB_RUN_GEMM(128, L::kB2, kF / 16, 0, 128)
+        ISSUE(T1, b2_hi, b2_lo, kF / 16, 0, 128)
 
-        // ---- step 3: gW from the two gathered node rows; gC = sum gW*y; gy = gW*C -> A operand; GH = gy A2
-        const Jet<float, 1> cj = envelope_jet<float, 1>(de, p.conv);
-        float g[32];
-        float gC = 0.f, rmax = 0.f;
+        // ---- under GEMM 2: gW = xl[row0] * gagg[row1] for this warp's 32 rows x 32 columns, four rows per instruction,
+        //      turned row-per-lane through shared memory
         {
-            // gW = xl[row0] * gagg[row1] for this warp's 32 rows x 32 columns, fetched four rows per instruction
-            // (eight lanes cover 128 contiguous bytes of a node row) and turned row-per-lane through shared memory
-            const int lane = tid & 31, sub = lane >> 3, cc = (col0 >> 2) + (lane & 7);
+            const int sub = lane >> 3, cc = (col0 >> 2) + (lane & 7);
 #pragma unroll
             for (int it = 0; it < 8; it++) {
                 const int rl = it * 4 + sub;
@@ -509,8 +426,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
                 *stage_chunk(stage, (r & ~31) + rl, cc) = make_float4(a.x * b.x * m, a.y * b.y * m, a.z * b.z * m, a.w * b.w * m);
             }
             __syncwarp();
+        }
+        AWAIT()
+
+        // ---- gC = sum gW*y; gy = gW*C -> A operand (row-scaled); issue GH = gy A2 (over Y)
+        float g[32];
+        float gC = 0.f, rmax = 0.f;
+        {
             float v[32];
-            tmem_ld32(t_lane + 128 + col0, v);
+            tmem_ld32(t_lane + T1 + col0, v);
 #pragma unroll
             for (int w = 0; w < 8; w++) {
                 const float4 gw4 = *stage_chunk(stage, r, (col0 >> 2) + w);
@@ -529,18 +453,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
         __syncthreads();
         gC = (s_red2[r] + s_red2[128 + r]) + (s_red2[256 + r] + s_red2[384 + r]);
         const float sc3 = SPLIT ? row_scale(fmaxf(fmaxf(s_red[r], s_red[128 + r]), fmaxf(s_red[256 + r], s_red[384 + r]))) : 1.f;
-        write_row32<SPLIT>(sA_hi, sA_lo, r, col0, g, sc3);
-        MLCGB_RUN_GEMM(256, L::kB2, kF / 16, 1, 128)
+        store_a_tmem<SPLIT>(tmem + TA + lane_off, col0, g, sc3);
+        tmem_wait_st();
+        ISSUE(T1, b2_hi, b2_lo, kF / 16, 1, 128)
+        AWAIT()
 
-        // ---- step 4: gz = gh (1 - h^2) -> A operand; GPHI = gz A1
+        // ---- gz = gh (1 - h^2) -> A operand (row-scaled); issue GPHI = gz A1
         {
             const float inv3 = 1.f / (sc3 * wscale);
             rmax = 0.f;
 #pragma unroll
             for (int half = 0; half < 2; half++) {
                 float v[16], h[16];
-                tmem_ld16(t_lane + 256 + col0 + half * 16, v);
-                tmem_ld16(t_lane + col0 + half * 16, h);
+                tmem_ld16(t_lane + T1 + col0 + half * 16, v);
+                tmem_ld16(t_lane + T0 + col0 + half * 16, h);
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     const float gz = v[j] * inv3 * fmaf(-h[j], h[j], 1.f);
@@ -549,41 +475,72 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_tc_kernel(FilterBwdP
                 }
             }
         }
-        s_red[qt * 128 + r] = rmax;      // (step 3's values were consumed before the barriers of GEMM 3)
+        s_red[qt * 128 + r] = rmax;
         __syncthreads();
         const float sc4 = SPLIT ? row_scale(fmaxf(fmaxf(s_red[r], s_red[128 + r]), fmaxf(s_red[256 + r], s_red[384 + r]))) : 1.f;
-        write_row32<SPLIT>(sA_hi, sA_lo, r, col0, g, sc4);
-        MLCGB_RUN_GEMM(384, L::kB1, kF / 16, 1, Kpad1)
+        store_a_tmem<SPLIT>(tmem + TA + lane_off, col0, g, sc4);
+        tmem_wait_st();
+        ISSUE(T2, b1_hi, b1_lo, kF / 16, 1, Kpad1)
 
-        // ---- step 5: gd = sum_r gphi_r phi'_r(d) + gC C'(d),  phi'_k = g_k (env' - env 2 ln2 w_k (t - c_k) t')
-        float acc = 0.f;
+        // ---- under GEMM 4: basis derivatives phi'_k = g_k (env' - env 2 ln2 w_k (t - c_k) t') for this thread's columns
         if (col0 < Kpad1) {
-            float v[32];
-            tmem_ld32(t_lane + 384 + col0, v);
-            const float e0 = env.c[0], e1 = env.c[1], m2 = -2.f * kLn2 * dt * e0;
+            const float m2 = -2.f * kLn2 * es.dt * es.e0;
 #pragma unroll
             for (int j = 0; j < 32; j++) {
                 const float2 cw = s_tab[col0 + j];
-                const float u = t - cw.x, wu = cw.y * u;
-                const float gk = ex2_fast(-wu * u);
-                acc = fmaf(v[j], gk * fmaf(m2, wu, e1), acc);            // columns at or beyond R: gk = 0
+                const float u = es.t - cw.x, wu = cw.y * u;
+                g[j] = ex2_fast(-wu * u) * fmaf(m2, wu, es.e1);      // columns at or beyond R: exactly 0
             }
-            acc *= 1.f / (sc4 * wscale);
         }
-        if (qt == 0) acc = fmaf(gC, cj.c[1], acc);
-        s_red2[qt * 128 + r] = acc;      // (step 3's values were consumed before the barriers of GEMM 3)
+        const float gC_dC = gC * cj.c[1], inv4 = 1.f / (sc4 * wscale);
+        // scalars of the next tile
+        const int64_t next = tile + step;
+        float de_next = 1.f;
+        EdgeScalars es_next{};
+        if (next < ntiles) {
+            const int64_t en = next * kRows + r;
+            de_next = en < p.E ? p.d[en] : 1.f;
+            es_next = scalars(de_next);
+        }
+        AWAIT()
+        if (failed) s_err[0] = 1;
+
+        // ---- next tile's basis -> A operand (GEMM 4 has consumed gz), issue its GEMM 1 (T0's h was consumed above)
+        if (next < ntiles) basis_to_tmem(es_next);
+        tc_fence_before();
+        __syncthreads();
+        if (s_err[0]) break;
+        if (next < ntiles && tid == 0) {
+            tc_fence_after();
+            issue_gemm_ts<SPLIT>(tmem + T0, tmem + TA, b1_hi, b1_lo, Kpad1 / 16, 0, 128);
+            mma_commit(bar);
+        }
+
+        // ---- under the next GEMM 1: gd = sum_r gphi_r phi'_r(d) + gC C'(d)
+        float acc = 0.f;
+        if (col0 < Kpad1) {
+            float v[32];
+            tmem_ld32(t_lane + T2 + col0, v);
+#pragma unroll
+            for (int j = 0; j < 32; j++) acc = fmaf(v[j], g[j], acc);
+            acc *= inv4;
+        }
+        if (qt == 0) acc += gC_dC;
+        s_red2[qt * 128 + r] = acc;
         tc_fence_before();
         __syncthreads();
         if (qt == 0 && live) q.gd[e] = (s_red2[r] + s_red2[128 + r]) + (s_red2[256 + r] + s_red2[384 + r]);
-        // the next tile's first exchange through s_red / s_red2 comes after several more barriers
+        de = de_next;
+        es = es_next;
     }
+#undef ISSUE
+#undef AWAIT
 
-    if (*s_err && tid == 0) atomicOr(p.status, 8);
     tc_fence_before();
     __syncthreads();
+    if (s_err[0] && tid == 0) atomicOr(p.status, 8);
     if (warp == 0) tmem_free(tmem, 512);
 }
-#undef MLCGB_RUN_GEMM
 
 template <bool SPLIT>
 static int filter_bwd_launch(const FilterBwdParams &q, cudaStream_t st) {
@@ -592,13 +549,13 @@ static int filter_bwd_launch(const FilterBwdParams &q, cudaStream_t st) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(filter_bwd_tc_kernel<SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
+        if (cudaFuncSetAttribute(filter_bwd_pipe_kernel<SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
             return check_launch();
         configured[dev] = true;
     }
     const int64_t ntiles = (q.f.E + tc::kRows - 1) / tc::kRows;
     const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
-    filter_bwd_tc_kernel<SPLIT><<<grid, kTcThreads, L::kTotal, st>>>(q);
+    filter_bwd_pipe_kernel<SPLIT><<<grid, kTcThreads, L::kTotal, st>>>(q);
     return check_launch();
 }
 
