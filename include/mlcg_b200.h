@@ -163,6 +163,15 @@ size_t mlcgb_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, int
 int mlcgb_gemm(int mode, const void *A, const void *B, const void *bias /* [N] or NULL */, int dtype, int64_t M,
                int64_t N, int64_t K, void *C, void *workspace, size_t workspace_bytes, void *stream);
 
+/* The same three GEMMs on the tensor cores (tcgen05, fp16 hi/lo pairs, three products per GEMM, fp32
+ * accumulation in tensor memory): float32 only, the two weight-sized dimensions at most 128 (modes 0/1: N, K <= 128,
+ * M = edges; mode 2: M, N <= 128, K = edges).  mlcgb_gemm_tc_supported tells whether a shape qualifies;
+ * status bit 3 reports a tensor-core wait that ran out. */
+int mlcgb_gemm_tc_supported(int mode, int64_t M, int64_t N, int64_t K);
+size_t mlcgb_gemm_tc_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K);
+int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int64_t M, int64_t N, int64_t K, void *C,
+                  void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Fused filter network on the tensor cores (tcgen05 / TMEM):
  *   W[e,:] = ( tanh( phi(d_e) A1^T + b1 ) A2^T ) * C(d_e)

@@ -101,6 +101,7 @@ class CudaBackend:
         self.lib = _lib.load()
         self.profiler = None
         self._status = {}
+        self.tensor_core_gemm = True   # float32 GEMMs of qualifying shape run on tcgen05 (fp32-equivalent products)
         self._pending = []      # (status tensor, what) of kernels whose status word has not been read yet
 
     def defer_status(self, status, what):
@@ -315,6 +316,17 @@ class CudaBackend:
             (K, M), N = A.shape, B.shape[1]
         dt = _dt(A)
         C = torch.empty((M, N), dtype=A.dtype, device=A.device)
+        if self.tensor_core_gemm and dt == 0 and min(M, N, K) > 0 and self.lib.mlcgb_gemm_tc_supported(mode, M, N, K):
+            with torch.cuda.device(A.device):
+                wsb = self.lib.mlcgb_gemm_tc_workspace_bytes(mode, M, N, K)
+                ws = torch.empty(wsb, dtype=torch.uint8, device=A.device) if wsb else None
+                if bias is not None:
+                    bias = bias.contiguous()
+                status = self._sticky_status(A.device)
+                self._run("gemm_tc", self.lib.mlcgb_gemm_tc, (mode, _ptr(A), _ptr(B), _ptr(bias), M, N, K, _ptr(C), _ptr(ws), wsb, _ptr(status), _stream()),
+                          launches=2 if wsb else 1, nbytes=(M * K + N * K + M * N) * 4, flops=2 * M * N * K)
+                self.defer_status(status, "tensor-core GEMM")
+            return C
         with torch.cuda.device(A.device):
             wsb = self.lib.mlcgb_gemm_workspace_bytes(mode, M, N, K, dt)
             ws = torch.empty(wsb, dtype=torch.uint8, device=A.device) if wsb else None

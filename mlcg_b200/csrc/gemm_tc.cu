@@ -1,0 +1,343 @@
+// Edge-sized GEMMs of the filter network on the sm_100a tensor cores, fp32-equivalent.
+//
+// The composable (training) path needs plain GEMMs whose tall dimension is the edge count and whose
+// other two dimensions are the widths of the filter network (128 and at most 128):
+//   NT  C[E,N] = A[E,K] B[N,K]^T (+ bias)     forward of a Linear layer
+//   NN  C[E,N] = A[E,K] B[K,N]                gradient w.r.t. the layer input
+//   TN  C[M,N] = A[E,M]^T B[E,N]              gradient w.r.t. the weight (contraction over edges)
+// Every fp32 operand is carried as an fp16 pair (hi + lo, ~22 bits) and each product runs as
+// hi*hi + hi*lo + lo*hi with fp32 accumulation in tensor memory, like the fused eval-mode kernels.
+// Rows of A (NT/NN) are scaled by a power of two so that their largest magnitude sits in [8,16);
+// TN scales each 128-edge tile of A and of B by one power of two and accumulates the tiles in registers.
+#include "tc_common.cuh"
+
+namespace mlcgb {
+
+constexpr int kGT = 512;   // threads: thread = (row of the tile, 32-column quarter)
+
+struct GemmTcSmem {
+    static constexpr int kB = 0;                 // operand tile hi | lo (2 x 32 KB)
+    static constexpr int kStageA = 65536;        // fp32 stage 64 KB
+    static constexpr int kStageB = 131072;       // fp32 stage 64 KB (TN only)
+    static constexpr int kMisc = 196608;         // exchange [4][128] f32, bias [128], barrier, TMEM slot, flags
+    static constexpr int kTotal = kMisc + 4096 + 1024;
+};
+
+__device__ __forceinline__ float4 *gstage(uint8_t *stage, int row, int chunk) {
+    return reinterpret_cast<float4 *>(stage + row * 512 + ((chunk ^ (row & 7)) << 4));
+}
+__device__ __forceinline__ float *gstage_elem(uint8_t *stage, int row, int col) {
+    return reinterpret_cast<float *>(stage + row * 512 + ((((col >> 2) ^ (row & 7)) << 4) | ((col & 3) << 2)));
+}
+
+// rows [row0, row0+128) x cols [0, ncols) of a row-major [nrows_total, ncols] fp32 matrix -> stage, zero-filled
+// outside; whole rows are read by consecutive lanes
+__device__ __forceinline__ void load_tile_to_stage(uint8_t *stage, const float *__restrict__ src, int64_t row0, int64_t nrows_total,
+                                                   int ncols) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool vec = (ncols & 3) == 0 && ((uintptr_t)src & 15) == 0;
+#pragma unroll 1
+    for (int i = 0; i < 8; i++) {
+        const int row = warp * 8 + i;
+        const int64_t gr = row0 + row;
+        if (vec) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (gr < nrows_total && lane * 4 < ncols) v = __ldcs(reinterpret_cast<const float4 *>(src + gr * ncols) + lane);
+            *gstage(stage, row, lane) = v;
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int col = lane + 32 * c;
+                *gstage_elem(stage, row, col) = (gr < nrows_total && col < ncols) ? src[gr * ncols + col] : 0.f;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ NT / NN
+template <int MODE>   // 0 NT, 1 NN
+__global__ void __launch_bounds__(kGT, 1)
+gemm_tc_rows_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int64_t E, int N, int K,
+                    float *__restrict__ C, int32_t *__restrict__ status) {
+    using namespace tc;
+    using L = GemmTcSmem;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *sB_hi = smem + L::kB, *sB_lo = sB_hi + 32768, *stage = smem + L::kStageA;
+    float *s_red = reinterpret_cast<float *>(smem + L::kMisc);
+    float *s_bias = s_red + 512;
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_bias + 128);
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(s_bar + 1);
+    int *s_err = reinterpret_cast<int *>(s_tmem + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = tid & 127, qt = tid >> 7, col0 = qt * 32;
+    constexpr float kWS = 64.f;
+    // operand tile of the weight: NT: rows = n, K-major;  NN: rows = k, read as an MN-major operand
+    const int wrows = MODE == 0 ? N : K, wcols = MODE == 0 ? K : N;
+    const int wpad = wcols <= 64 ? 64 : 128;
+    load_weight_tile<true>(sB_hi, sB_lo, B, wrows, wcols, wpad, kWS);
+    if (tid < 128) s_bias[tid] = (bias && tid < N) ? bias[tid] : 0.f;
+    const uint32_t bar = smem_u32(s_bar);
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        *s_err = 0;
+    }
+    __syncwarp();
+    if (warp == 0) tmem_alloc(smem_u32(s_tmem), 256);
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const int ksteps = MODE == 0 ? wpad / 16 : (K + 15) / 16;
+    const int nmma = MODE == 0 ? 128 : wpad;
+    uint32_t phase = 0;
+
+    const int64_t ntiles = (E + kRows - 1) / kRows;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        load_tile_to_stage(stage, A, tile * kRows, E, K);
+        __syncthreads();
+        float x[32];
+        float rmax = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const float4 v = *gstage(stage, r, (col0 >> 2) + w);
+            x[4 * w] = v.x; x[4 * w + 1] = v.y; x[4 * w + 2] = v.z; x[4 * w + 3] = v.w;
+            rmax = fmaxf(fmaxf(rmax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        }
+        s_red[qt * 128 + r] = rmax;
+        __syncthreads();
+        const float sc = row_scale(fmaxf(fmaxf(s_red[r], s_red[128 + r]), fmaxf(s_red[256 + r], s_red[384 + r])));
+        if (col0 < ksteps * 16) store_a_tmem<true>(tmem + 128 + lane_off, col0, x, sc);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            issue_gemm_ts<true>(tmem, tmem + 128, smem_u32(sB_hi), smem_u32(sB_lo), ksteps, MODE, nmma);
+            mma_commit(bar);
+        }
+        if (!mbar_wait(bar, phase)) *s_err = 1;
+        phase ^= 1;
+        tc_fence_after();
+        if (col0 < nmma) {
+            float v[32];
+            tmem_ld32(tmem + lane_off + col0, v);
+            const float inv = 1.f / (sc * kWS);
+#pragma unroll
+            for (int w = 0; w < 8; w++)
+                *gstage(stage, r, (col0 >> 2) + w) = make_float4(fmaf(v[4 * w], inv, s_bias[col0 + 4 * w]), fmaf(v[4 * w + 1], inv, s_bias[col0 + 4 * w + 1]),
+                                                                 fmaf(v[4 * w + 2], inv, s_bias[col0 + 4 * w + 2]), fmaf(v[4 * w + 3], inv, s_bias[col0 + 4 * w + 3]));
+        }
+        tc_fence_before();
+        __syncthreads();
+        if (*s_err) break;
+        const bool vec = (N & 3) == 0 && ((uintptr_t)C & 15) == 0;
+#pragma unroll 1
+        for (int i = 0; i < 8; i++) {
+            const int row = warp * 8 + i;
+            const int64_t gr = tile * kRows + row;
+            if (gr >= E) continue;
+            if (vec) {
+                if (lane * 4 < N) __stcs(reinterpret_cast<float4 *>(C + gr * N) + lane, *gstage(stage, row, lane));
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int col = lane + 32 * c;
+                    if (col < N) C[gr * N + col] = *gstage_elem(stage, row, col);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*s_err && tid == 0) atomicOr(status, 8);
+    if (warp == 0) tmem_free(tmem, 256);
+}
+
+// ------------------------------------------------------------------------------------------------ TN
+__device__ __forceinline__ float block_max_512(float v, float *s_red) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float m = s_red[0];
+#pragma unroll
+    for (int i = 1; i < 16; i++) m = fmaxf(m, s_red[i]);
+    __syncthreads();
+    return m;
+}
+
+__global__ void __launch_bounds__(kGT, 1)
+gemm_tc_tn_kernel(const float *__restrict__ A, const float *__restrict__ B, int64_t E, int M, int N, float *__restrict__ partial,
+                  int32_t *__restrict__ status) {
+    using namespace tc;
+    using L = GemmTcSmem;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *sB_hi = smem + L::kB, *sB_lo = sB_hi + 32768, *stageA = smem + L::kStageA, *stageB = smem + L::kStageB;
+    float *s_red = reinterpret_cast<float *>(smem + L::kMisc);
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_red + 640);
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(s_bar + 1);
+    int *s_err = reinterpret_cast<int *>(s_tmem + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int r = tid & 127, qt = tid >> 7, col0 = qt * 32;   // r: output row m (TMEM lane); col0: edge sub-range / output column range
+    const int npad = N <= 64 ? 64 : 128;
+    const uint32_t bar = smem_u32(s_bar);
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        *s_err = 0;
+    }
+    __syncwarp();
+    if (warp == 0) tmem_alloc(smem_u32(s_tmem), 256);
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t phase = 0;
+    float acc[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) acc[j] = 0.f;
+
+    const int64_t ntiles = (E + kRows - 1) / kRows;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        load_tile_to_stage(stageA, A, tile * kRows, E, M);
+        load_tile_to_stage(stageB, B, tile * kRows, E, N);
+        __syncthreads();
+        // A operand: lane = output row m, K = edge: x[j] = A[edge col0 + j][m]
+        float x[32];
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            x[j] = *gstage_elem(stageA, col0 + j, r);
+            amax = fmaxf(amax, fabsf(x[j]));
+        }
+        float bmax = 0.f;
+        for (int idx = tid; idx < kRows * 32; idx += kGT) {
+            const float4 v = *reinterpret_cast<const float4 *>(stageB + idx * 16);
+            bmax = fmaxf(fmaxf(bmax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        }
+        const float sa = row_scale(block_max_512(amax, s_red));
+        const float sb = row_scale(block_max_512(bmax, s_red));
+        store_a_tmem<true>(tmem + 128 + lane_off, col0, x, sa);
+        // B operand tile [edge rows][n cols], read MN-major
+        for (int idx = tid; idx < kRows * npad; idx += kGT) {
+            const int er = idx / npad, n = idx - er * npad;
+            const float w = *gstage_elem(stageB, er, n) * sb;
+            const uint32_t off = elem_offset(er, n);
+            const __half a = __float2half_rn(w);
+            *reinterpret_cast<__half *>(sB_hi + off) = a;
+            *reinterpret_cast<__half *>(sB_lo + off) = __float2half_rn(w - __half2float(a));
+        }
+        tmem_wait_st();
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            issue_gemm_ts<true>(tmem, tmem + 128, smem_u32(sB_hi), smem_u32(sB_lo), kRows / 16, 1, npad);
+            mma_commit(bar);
+        }
+        if (!mbar_wait(bar, phase)) *s_err = 1;
+        phase ^= 1;
+        tc_fence_after();
+        if (col0 < npad) {
+            float v[32];
+            tmem_ld32(tmem + lane_off + col0, v);
+            const float inv = 1.f / (sa * sb);
+#pragma unroll
+            for (int j = 0; j < 32; j++) acc[j] = fmaf(v[j], inv, acc[j]);
+        }
+        tc_fence_before();
+        __syncthreads();
+        if (*s_err) break;
+    }
+    // this CTA's partial [M][N]
+    if (r < M)
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            if (col0 + j < N) partial[((int64_t)blockIdx.x * M + r) * N + col0 + j] = acc[j];
+    tc_fence_before();
+    __syncthreads();
+    if (*s_err && tid == 0) atomicOr(status, 8);
+    if (warp == 0) tmem_free(tmem, 256);
+}
+
+__global__ void gemm_tc_reduce_kernel(const float *__restrict__ partial, int64_t MN, int parts, float *__restrict__ C) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < MN; i += (int64_t)gridDim.x * blockDim.x) {
+        float s = 0.f;
+        for (int z = 0; z < parts; z++) s += partial[(int64_t)z * MN + i];
+        C[i] = s;
+    }
+}
+
+static int tn_parts(int64_t K) {
+    const int64_t ntiles = (K + tc::kRows - 1) / tc::kRows;
+    return (int)(ntiles < kNumSM ? (ntiles < 1 ? 1 : ntiles) : kNumSM);
+}
+
+template <typename Kern>
+static int set_smem(Kern kern, bool *done) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !done[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmTcSmem::kTotal) != cudaSuccess) return check_launch();
+        done[dev] = true;
+    }
+    return MLCGB_OK;
+}
+
+}  // namespace mlcgb
+
+using namespace mlcgb;
+
+extern "C" {
+
+int mlcgb_gemm_tc_supported(int mode, int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (mode == 0 || mode == 1) return N <= 128 && K <= 128;   // M = edges
+    if (mode == 2) return M <= 128 && N <= 128;                // K = edges
+    return 0;
+}
+
+size_t mlcgb_gemm_tc_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K) {
+    if (mode != 2 || !mlcgb_gemm_tc_supported(mode, M, N, K)) return 0;
+    return (size_t)tn_parts(K) * (size_t)M * (size_t)N * sizeof(float);
+}
+
+int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int64_t M, int64_t N, int64_t K, void *C, void *workspace,
+                  size_t workspace_bytes, int32_t *status, void *stream) {
+    if (!A || !B || !C || !status) return MLCGB_E_ARG;
+    if (!mlcgb_gemm_tc_supported(mode, M, N, K)) return MLCGB_E_LIMIT;
+    auto st = (cudaStream_t)stream;
+    static bool c0[64] = {false}, c1[64] = {false}, c2[64] = {false};
+    if (mode == 0 || mode == 1) {
+        const int64_t ntiles = (M + tc::kRows - 1) / tc::kRows;
+        const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
+        if (mode == 0) {
+            if (int rc = set_smem(gemm_tc_rows_kernel<0>, c0)) return rc;
+            gemm_tc_rows_kernel<0><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, (const float *)bias, M, (int)N, (int)K, (float *)C, status);
+        } else {
+            if (int rc = set_smem(gemm_tc_rows_kernel<1>, c1)) return rc;
+            gemm_tc_rows_kernel<1><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, nullptr, M, (int)N, (int)K, (float *)C, status);
+        }
+        return check_launch();
+    }
+    const int parts = tn_parts(K);
+    if (!workspace || workspace_bytes < (size_t)parts * M * N * sizeof(float)) return MLCGB_E_WORKSPACE;
+    if (int rc = set_smem(gemm_tc_tn_kernel, c2)) return rc;
+    gemm_tc_tn_kernel<<<parts, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, K, (int)M, (int)N, (float *)workspace, status);
+    gemm_tc_reduce_kernel<<<grid_for(M * N, 256), 256, 0, st>>>((const float *)workspace, M * N, parts, (float *)C);
+    return check_launch();
+}
+
+}  // extern "C"

@@ -175,3 +175,32 @@ def test_edge_distance_and_its_backward(dtype):
     p = pos.clone().requires_grad_(True)
     (want,) = torch.autograd.grad((ORA.edge_distance(p, plan.row0, plan.row1) * g).sum(), p)
     assert torch.allclose(got.cpu(), want, rtol=1e-4 if dtype == torch.float32 else 1e-10, atol=1e-4 if dtype == torch.float32 else 1e-10)
+
+
+@pytest.mark.parametrize("M,N,K", [(1000, 128, 128), (333, 128, 50), (5000, 50, 128), (128, 128, 128), (77, 64, 33), (40000, 128, 128)])
+@pytest.mark.parametrize("heavy_tail", [False, True])
+def test_tensor_core_gemm_matches_float64(M, N, K, heavy_tail):
+    """The tcgen05 GEMMs (fp16 hi/lo pairs) against float64 products, rows spanning many orders of magnitude."""
+    gen = torch.Generator().manual_seed(M + N + K)
+    be = get_backend()
+    assert be.tensor_core_gemm
+    rows = torch.exp(torch.randn(M, 1, generator=gen) * (6.0 if heavy_tail else 0.0))
+    X = torch.randn(M, K, generator=gen) * rows
+    W = torch.randn(N, K, generator=gen) * 0.1
+    b = torch.randn(N, generator=gen)
+    def rel(got, want):
+        return float(((got.cpu().double() - want).abs() / (want.abs().amax(dim=1, keepdim=True) + 1e-30)).max())
+    want = X.double() @ W.double().t() + b.double()
+    assert rel(be.gemm(0, X.to(DEV), W.to(DEV), b.to(DEV)), want) < 5e-6
+    G = torch.randn(M, N, generator=gen) * rows
+    assert rel(be.gemm(1, G.to(DEV), W.to(DEV)), G.double() @ W.double()) < 5e-6
+    want_t = G.double().t() @ X.double()
+    got_t = be.gemm(2, G.to(DEV), X.to(DEV)).cpu().double()
+    assert float((got_t - want_t).abs().max()) < 2e-5 * float(want_t.abs().max())
+    get_backend().check_pending()
+    # and the CUDA-core kernel gives the same answers when the tensor-core route is switched off
+    be.tensor_core_gemm = False
+    try:
+        assert rel(be.gemm(0, X.to(DEV), W.to(DEV), b.to(DEV)), want) < 5e-6
+    finally:
+        be.tensor_core_gemm = True

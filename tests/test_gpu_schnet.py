@@ -173,3 +173,33 @@ def test_bf16_filter_mode_force_accuracy():
     rel_rms = float(((f - f_ref) ** 2).mean().sqrt() / (f_ref ** 2).mean().sqrt())
     assert rel_rms < 1e-2, rel_rms
     assert torch.allclose(out.out["SchNet"]["energy"].detach().cpu(), e_ref, rtol=2e-2, atol=2e-2 * float(e_ref.abs().max()))
+
+
+def test_force_matching_gradients_full_width_vs_oracle():
+    """Second-order pass at the real layer widths (128 filters, 128 RBF: the tensor-core GEMMs are on this path):
+    gradient of the force-matching loss w.r.t. every parameter against the CPU oracle in float64."""
+    model, pos, types_, batch = _make("expnormal", 6, 40, 8, 12.0, 128, 128, 2, 9, min_dist=4.0)
+    B, n = 6, 40
+    target = torch.randn(pos.shape, generator=torch.Generator().manual_seed(1))
+    cut = {"cutoff": "cosine", "lower": 0.0, "upper": 12.0}
+    spec = {"kind": "expnormal", "rbf_cutoff": cut, "cutoff": cut, "activation": "tanh", "num_interactions": 2}
+    sd = {k: (v.detach().double().requires_grad_(True) if v.is_floating_point() else v) for k, v in model.state_dict().items()}
+    ei = torch.from_numpy(radius_ref.radius_graph_c(pos.numpy(), radius_ref.batch_to_ptr(batch.numpy(), B), 12.0, 1000, False, "cluster"))
+    _, f, _ = schnet_ref.energy_and_forces(lambda p: schnet_ref.schnet_energy(sd, spec, p, types_, batch, ei, B), pos.double(), create_graph=True)
+    loss_ref = torch.nn.functional.mse_loss(f, target.double())
+    loss_ref.backward()
+    net = model.to(DEV)
+    out = bnn.GradientsOut(net, "forces").train()(mlcg_b200.AtomicData(pos=pos.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV),
+                                                                        n_atoms=torch.full((B,), n).to(DEV)))
+    loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], target.to(DEV))
+    loss.backward()
+    from mlcg_b200.backend import get_backend
+    get_backend().check_pending()
+    assert abs(float(loss) - float(loss_ref)) < 1e-4 * abs(float(loss_ref))
+    for k, p in net.named_parameters():
+        if p.grad is None:
+            continue
+        g_ref = sd[k].grad
+        assert g_ref is not None, k
+        err = float((p.grad.cpu().double() - g_ref).abs().max())
+        assert err < 2e-4 * float(g_ref.abs().max()) + 1e-7, (k, err, float(g_ref.abs().max()))
