@@ -115,14 +115,21 @@ __device__ __forceinline__ uint32_t filter_setup(const FilterFwdParams &p, uint8
 // zz = 2 log2(e) z  (2^{|zz|} overflowing to inf gives exactly 1)
 template <bool SPLIT>
 __device__ __forceinline__ void tanh_row32(float (&v)[32], const float *s_b1s, int col0, float unscale2) {
+    const float4 *b4 = reinterpret_cast<const float4 *>(s_b1s + col0);
 #pragma unroll
-    for (int j = 0; j < 32; j++) {
-        const float zz = fmaf(v[j], unscale2, s_b1s[col0 + j]);
-        if (SPLIT) {
-            const float tt = ex2_fast(fabsf(zz));
-            v[j] = copysignf(fmaf(-2.f, rcp_fast(tt + 1.f), 1.f), zz);
-        } else {
-            v[j] = tanh_fast(zz * (0.5f * kLn2));
+    for (int q = 0; q < 8; q++) {
+        const float4 bq = b4[q];
+        const float bb[4] = {bq.x, bq.y, bq.z, bq.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int j = 4 * q + i;
+            const float zz = fmaf(v[j], unscale2, bb[i]);
+            if (SPLIT) {
+                const float tt = ex2_fast(fabsf(zz));
+                v[j] = copysignf(fmaf(-2.f, rcp_fast(tt + 1.f), 1.f), zz);
+            } else {
+                v[j] = tanh_fast(zz * (0.5f * kLn2));
+            }
         }
     }
 }
@@ -181,11 +188,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFw
             edge_arg(de, p.rbf, t, dt);
             const float l2a = log2f(envelope_jet<float, 0>(de, p.rbf).c[0]);
             float x[32];
+            const float4 *tab4 = reinterpret_cast<const float4 *>(s_tab + col0);   // two (centre, width) pairs per 128-bit read
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
-                const float2 cw = s_tab[col0 + j];
-                const float u = t - cw.x;
-                x[j] = ex2_fast(fmaf(-cw.y * u, u, l2a));
+            for (int j = 0; j < 16; j++) {
+                const float4 cw = tab4[j];
+                const float u0 = t - cw.x, u1 = t - cw.z;
+                x[2 * j] = ex2_fast(fmaf(-cw.y * u0, u0, l2a));
+                x[2 * j + 1] = ex2_fast(fmaf(-cw.w * u1, u1, l2a));
             }
             store_a_tmem<SPLIT>(ta + lane_off, col0, x, 1.f);
         }
@@ -371,11 +380,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
         if (col0 < Kpad1) {
             const float l2a = log2f(es.e0);
             float x[32];
+            const float4 *tab4 = reinterpret_cast<const float4 *>(s_tab + col0);
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
-                const float2 cw = s_tab[col0 + j];
-                const float u = es.t - cw.x;
-                x[j] = ex2_fast(fmaf(-cw.y * u, u, l2a));
+            for (int j = 0; j < 16; j++) {
+                const float4 cw = tab4[j];
+                const float u0 = es.t - cw.x, u1 = es.t - cw.z;
+                x[2 * j] = ex2_fast(fmaf(-cw.y * u0, u0, l2a));
+                x[2 * j + 1] = ex2_fast(fmaf(-cw.w * u1, u1, l2a));
             }
             store_a_tmem<SPLIT>(tmem + TA + lane_off, col0, x, 1.f);
         }
@@ -485,11 +496,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
         // ---- under GEMM 4: basis derivatives phi'_k = g_k (env' - env 2 ln2 w_k (t - c_k) t') for this thread's columns
         if (col0 < Kpad1) {
             const float m2 = -2.f * kLn2 * es.dt * es.e0;
+            const float4 *tab4 = reinterpret_cast<const float4 *>(s_tab + col0);
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
-                const float2 cw = s_tab[col0 + j];
-                const float u = es.t - cw.x, wu = cw.y * u;
-                g[j] = ex2_fast(-wu * u) * fmaf(m2, wu, es.e1);      // columns at or beyond R: exactly 0
+            for (int j = 0; j < 16; j++) {
+                const float4 cw = tab4[j];
+                const float u0 = es.t - cw.x, wu0 = cw.y * u0, u1 = es.t - cw.z, wu1 = cw.w * u1;
+                g[2 * j] = ex2_fast(-wu0 * u0) * fmaf(m2, wu0, es.e1);      // columns at or beyond R: exactly 0
+                g[2 * j + 1] = ex2_fast(-wu1 * u1) * fmaf(m2, wu1, es.e1);
             }
         }
         const float gC_dC = gC * cj.c[1], inv4 = 1.f / (sc4 * wscale);

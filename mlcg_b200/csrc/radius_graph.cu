@@ -201,8 +201,10 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
                   const int32_t *__restrict__ cell_start, const int32_t *__restrict__ struct_of, int32_t *__restrict__ deg,
                   const int64_t *__restrict__ offsets, FillOut out, int32_t *__restrict__ status) {
     __shared__ unsigned s_mask[FILL ? kNbrWarps * (kCapBits / 32) : 1];
+    __shared__ unsigned short s_list[FILL ? kNbrWarps * 1024 : 1];   // per warp: bit positions of one 32-word chunk
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned *mask = s_mask + (FILL ? warp * (kCapBits / 32) : 0);
+    unsigned short *list = s_list + (FILL ? warp * 1024 : 0);
     const unsigned lt = lanemask_lt();
 
     for (int64_t i = (int64_t)blockIdx.x * kNbrWarps + warp; i < N; i += (int64_t)gridDim.x * kNbrWarps) {
@@ -309,19 +311,27 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
                             if (lane >= o) incl += t;
                         }
                         const int total = __shfl_sync(0xffffffffu, incl, 31);
-                        int64_t rank = emitted + (incl - cbits);
-                        while (bits && rank < kept) {
+                        // compact the set bits of these 32 words into a dense list in shared memory ...
+                        int pos_in = incl - cbits;
+                        while (bits) {
                             const int t = __ffs(bits) - 1;
                             bits &= bits - 1;
-                            const int j = wbase + (w << 5) + t;
+                            list[pos_in++] = (unsigned short)(((w - w0) << 5) + t);
+                        }
+                        __syncwarp();
+                        // ... and write the edges with consecutive lanes on consecutive slots
+                        const int64_t room = kept - emitted;
+                        const int take = (int64_t)total < room ? total : (int)room;
+                        for (int t = lane; t < take; t += 32) {
+                            const int j = wbase + (w0 << 5) + (int)list[t];
                             T d2 = T(0);
                             if (out.distance) {
                                 const int64_t gj = lo + j;
                                 d2 = dist2_rn(xi, yi, zi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]);
                             }
-                            emit_edge<T>(out, base_off + rank, i, lo + j, b, d2);
-                            rank++;
+                            emit_edge<T>(out, base_off + emitted + t, i, lo + j, b, d2);
                         }
+                        __syncwarp();
                         emitted += total;
                         if (emitted >= kept) break;
                     }
