@@ -206,7 +206,7 @@ def extra_measurements(dev, hbm_peak):
     full = torch.cartesian_prod(idx, idx).t()
     lists = {"bonds": torch.stack([idx[:-1], idx[1:]]), "angles": torch.stack([idx[:-2], idx[1:-1], idx[2:]]),
              "dihedrals": torch.stack([idx[:-3], idx[1:-2], idx[2:-1], idx[3:]]), "repulsion": full[:, (full[0] - full[1]).abs() >= 3]}
-    ppos = torch.cumsum(torch.nn.functional.normalize(torch.randn(Bp, npb, 3, generator=gen), dim=2) * 3.8, dim=1).reshape(-1, 3).to(dev)
+    ppos = self_avoiding_chains(Bp, npb, gen).to(dev)    # 3.8 A walk, no two beads closer than 4 A
     offs = (torch.arange(Bp, device=dev) * npb)
     n_par = {"bonds": 2, "angles": 2, "dihedrals": 7, "repulsion": 1}
     for kind, name in enumerate(["bonds", "angles", "dihedrals", "repulsion"]):
@@ -220,6 +220,56 @@ def extra_measurements(dev, hbm_peak):
         out[f"prior_{name}_1024x268"] = dict(terms=M, ms=ms, terms_per_s=M / (ms / 1e3), algorithmic_GBps=nbytes / ms / 1e6,
                                              frac_of_hbm=nbytes / ms / 1e6 / hbm_peak)
         del mapping, mb, params
+    # Langevin dynamics of the simulation configuration: 1024 replicas x 268 beads, SchNet (3 blocks, 12 A) + the four
+    # priors, BAOAB, graph rebuilt every step
+    from mlcg_b200.simulation import LangevinSimulation
+    import itertools
+    T = 20
+    torch.manual_seed(0)
+    cut = bnn.CosineCutoff(0.0, 12.0)
+    net = bnn.StandardSchNet(bnn.ExpNormalBasis(cut, 128, trainable=False), cut, [128], hidden_channels=128, embedding_size=T,
+                             num_filters=128, num_interactions=3)
+    stats2 = lambda d: {k: d for k in itertools.product(range(1), repeat=2)}
+    pri = {"bonds": bnn.HarmonicBonds({(0, 0): {"k": 100.0, "x_0": 3.8}}), "angles": bnn.HarmonicAngles({(0, 0, 0): {"k": 50.0, "x_0": float(torch.cos(torch.tensor(1.9)))}}),
+           "dihedrals": bnn.Dihedral({(0, 0, 0, 0): {"v_0": 0.0, "k1s": {"k1_1": 0.3, "k1_2": -0.2, "k1_3": 0.1}, "k2s": {"k2_1": 0.2, "k2_2": 0.1, "k2_3": -0.1}}}),
+           "repulsion": bnn.Repulsion({(0, 0): {"sigma": 4.0}})}
+    models = {"SchNet": bnn.GradientsOut(net, "forces")}
+    models.update({k: bnn.GradientsOut(p, "forces") for k, p in pri.items()})
+    model = bnn.SumOut(torch.nn.ModuleDict(models)).eval().to(dev)
+    nls = {}
+    for name in ["bonds", "angles", "dihedrals", "repulsion"]:
+        m = lists[name]
+        M = m.shape[1] * Bp
+        nls[name] = mlcg_b200.make_neighbor_list(name, m.shape[0], (m[:, None, :] + offs[None, :, None]).reshape(m.shape[0], M).contiguous(),
+                                                 torch.arange(Bp, device=dev).repeat_interleave(m.shape[1]))
+    class _Data(mlcg_b200.AtomicData):
+        pass
+    data = _Data(pos=ppos.clone(), atom_types=torch.randint(0, T, (Bp * npb,), generator=gen).to(dev), batch=torch.arange(Bp, device=dev).repeat_interleave(npb),
+                 n_atoms=torch.full((Bp,), npb, device=dev), neighbor_list=nls)
+    # priors use bead type 0 tables: give them a type vector of zeros through their cached parameters
+    zero_types = torch.zeros(Bp * npb, dtype=torch.long, device=dev)
+    real_types = data.atom_types
+    data.atom_types = zero_types
+    for name, p in pri.items():
+        p._cached_params(data)
+    data.atom_types = real_types
+    sim = LangevinSimulation(model, dt=0.002, friction=1.0, beta=1.0 / (0.0019872041 * 300), rng=torch.Generator(device=dev).manual_seed(0))
+    sim.attach(data, torch.full((Bp * npb,), 12.0 / 418.39, device=dev))
+    pot, forces = sim.calculate_potential_and_forces(sim.data)
+    for _ in range(2):
+        _, pot, forces = sim.timestep(sim.data, forces)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    nsteps = 5
+    a.record()
+    for _ in range(nsteps):
+        _, pot, forces = sim.timestep(sim.data, forces)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / nsteps
+    out["langevin_1024x268"] = dict(ms_per_md_step=ms, md_steps_per_s=1e3 / ms, replica_steps_per_s=Bp * 1e3 / ms, finite=bool(torch.isfinite(pot).all()),
+                                    note="SchNet (3 blocks, 128 expnorm RBF, 12 A) + bonds/angles/dihedrals/repulsion(|i-j|>=3), BAOAB dt=2 fs, "
+                                         "radius graph rebuilt every step, 1024 replicas on one GPU")
     return out
 
 # ----------------------------------------------------------------------------------------- GPU arm

@@ -213,6 +213,17 @@ int mlcgb_prior_terms(int kind, const void *pos /* [N,3] */, int dtype, const in
                       const void *params, int n_params, int64_t M, int64_t N, int64_t B, void *energy /* [B] */,
                       void *grad /* [N,3] or NULL */, int32_t *status, void *stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * BAOAB Langevin step around the force evaluation, LangevinSimulation.timestep,
+ * src/mlcg/simulation/langevin.py:100-144.  x, v are updated in place; `noise` holds the normal deviates
+ * (drawn by the caller, so the random stream is the reference's); beta_mass_ratio[n] = sqrt(1/(beta_n m_n))
+ * (langevin.py:176-180); vscale = exp(-dt*friction), noisescale = sqrt(1 - vscale^2) (langevin.py:74-76).
+ * ---------------------------------------------------------------------------------------------- */
+int mlcgb_langevin_first_half(void *x /* [N,3] */, void *v /* [N,3] */, const void *f /* [N,3] */, const void *masses /* [N] */,
+                              const void *beta_mass_ratio /* [N] */, const void *noise /* [N,3] */, int dtype, int64_t N, double dt,
+                              double vscale, double noisescale, void *stream);
+int mlcgb_langevin_second_half(void *v, const void *f, const void *masses, int dtype, int64_t N, double dt, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -49,6 +49,8 @@ SIGNATURES = {
     "mlcgb_filter_backward": (c_int, [c_vp, c_i64, ctypes.POINTER(RbfSpecStruct), c_int, c_dbl, c_dbl, c_vp, c_vp, c_vp, c_i64, c_int,
                                       c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
     "mlcgb_segment_sum": (c_int, [c_vp, c_int, c_vp, c_i64, c_vp, c_vp]),
+    "mlcgb_langevin_first_half": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_dbl, c_dbl, c_dbl, c_vp]),
+    "mlcgb_langevin_second_half": (c_int, [c_vp, c_vp, c_vp, c_int, c_i64, c_dbl, c_vp]),
     "mlcgb_prior_terms": (c_int, [c_int, c_vp, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
 }
 

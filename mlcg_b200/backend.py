@@ -378,6 +378,25 @@ class CudaBackend:
             self._run("segment_sum", self.lib.mlcgb_segment_sum, (_ptr(x), _dt(x), _ptr(ptr), B, _ptr(out), _stream(),), **self._work("segment_sum", locals()))
         return out
 
+    # ------------------------------------------------------------------ Langevin integrator
+    def langevin_first_half(self, x, v, f, masses, beta_mass_ratio, noise, dt, vscale, noisescale):
+        """In place on x and v (both contiguous [N,3])."""
+        _need_cuda(x, v, f, masses, beta_mass_ratio, noise)
+        assert x.is_contiguous() and v.is_contiguous()
+        f, noise = f.contiguous(), noise.contiguous()
+        with torch.cuda.device(x.device):
+            self._run("langevin_first_half", self.lib.mlcgb_langevin_first_half,
+                      (_ptr(x), _ptr(v), _ptr(f), _ptr(masses), _ptr(beta_mass_ratio), _ptr(noise), _dt(x), x.shape[0], float(dt), float(vscale),
+                       float(noisescale), _stream()), nbytes=6 * x.numel() * x.element_size())
+
+    def langevin_second_half(self, v, f, masses, dt):
+        _need_cuda(v, f, masses)
+        assert v.is_contiguous()
+        f = f.contiguous()
+        with torch.cuda.device(v.device):
+            self._run("langevin_second_half", self.lib.mlcgb_langevin_second_half, (_ptr(v), _ptr(f), _ptr(masses), _dt(v), v.shape[0], float(dt), _stream()),
+                      nbytes=3 * v.numel() * v.element_size())
+
     # ------------------------------------------------------------------ priors
     def prior_terms(self, kind, pos, mapping, mapping_batch, params, B, want_grad=True):
         """Returns (energy[B], dE/dpos[N,3] | None)."""

@@ -115,6 +115,18 @@ class OracleBackend:
         out = torch.zeros(ptr.numel() - 1, dtype=x.dtype)
         return out.index_add_(0, _expand_segments(ptr), x)
 
+    # ------------------------------------------------------------------ Langevin integrator (langevin.py:100-144)
+    def langevin_first_half(self, x, v, f, masses, beta_mass_ratio, noise, dt, vscale, noisescale):
+        vn = v + 0.5 * dt * f / masses[:, None]
+        xn = x + vn * dt * 0.5
+        vn = vn * vscale + noisescale * (beta_mass_ratio[:, None] * noise)
+        xn = xn + vn * dt * 0.5
+        x.copy_(xn)
+        v.copy_(vn)
+
+    def langevin_second_half(self, v, f, masses, dt):
+        v.copy_(v + 0.5 * dt * f / masses[:, None])
+
     # ------------------------------------------------------------------ priors
     def prior_terms(self, kind, pos, mapping, mapping_batch, params, B, want_grad=True):
         p = pos.detach().clone().requires_grad_(True)
