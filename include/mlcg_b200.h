@@ -181,19 +181,24 @@ int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int6
  * products per GEMM, fp32 accumulation); precision 1: bf16 operands, one product.
  * status bit 3 is set if a tensor-core wait ran out (the output is then incomplete).
  * ---------------------------------------------------------------------------------------------- */
-int mlcgb_filter_forward(const void *d /* [E] */, int64_t E, const mlcgb_rbf_spec *rbf /* host */, int conv_cutoff_kind,
+int mlcgb_filter_forward(const void *d /* [.] */, int64_t rows, const int32_t *sel /* [rows] or NULL */,
+                         const int32_t *twin /* [E] or NULL */, const mlcgb_rbf_spec *rbf /* host */, int conv_cutoff_kind,
                          double conv_lower, double conv_upper, const void *A1 /* [F,R] */, const void *b1 /* [F] */,
                          const void *A2 /* [F,F] */, int64_t F, int precision, void *W /* [E,F] */, int32_t *status, void *stream);
+/* `rows` = E and sel = twin = NULL: row k is edge k.  For a symmetric edge list the filter of an edge equals that of its
+ * reverse (same distance), so the caller may pass one edge per unordered pair in `sel` (rows = E/2) together with the
+ * reverse-edge map `twin` (mlcgb_edge_twin): each computed row is then written to both edges, and the backward below
+ * sums the two directions' incoming gradients and returns the pair's gradient on the selected edge (zero on its twin). */
 
 /* Backward of the above with respect to the distance, fused with the message product:
  *   gd[e] = sum_f gW[e,f] * dW[e,f]/dd_e,  gW[e,:] = xl[row0[e],:] * gagg[row1[e],:]
  * (the gradient CFConv's aggregation, src/mlcg/nn/schnet.py:346,350-368, sends back to its filters).
  * Recomputes the forward per tile; four tensor-core GEMMs per tile; nothing edge-sized is read or
  * written in HBM except d, the two index rows and gd. */
-int mlcgb_filter_backward(const void *d, int64_t E, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower,
-                          double conv_upper, const void *A1, const void *b1, const void *A2, int64_t F, int precision,
-                          const int32_t *row0, const int32_t *row1, const void *xl /* [N,F] */, const void *gagg /* [N,F] */,
-                          int64_t N, void *gd /* [E] */, int32_t *status, void *stream);
+int mlcgb_filter_backward(const void *d, int64_t rows, const int32_t *sel, const int32_t *twin, const mlcgb_rbf_spec *rbf,
+                          int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1, const void *A2,
+                          int64_t F, int precision, const int32_t *row0, const int32_t *row1, const void *xl /* [N,F] */,
+                          const void *gagg /* [N,F] */, int64_t N, void *gd /* [E] */, int32_t *status, void *stream);
 
 /* out[b] = sum_{n in [ptr[b],ptr[b+1])} x[n]  — the per-structure energy sum, src/mlcg/nn/schnet.py:158 */
 int mlcgb_segment_sum(const void *x /* [N] */, int dtype, const int64_t *ptr /* [B+1] */, int64_t B, void *out /* [B] */,

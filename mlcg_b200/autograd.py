@@ -37,6 +37,16 @@ class EdgePlan:
     perm_in: torch.Tensor              # int32 [E]
     nbr_in: torch.Tensor               # int32 [E]  row0 in that grouping
     symmetric: bool = False            # every edge has its reverse, and perm_in maps an edge to it
+    _half: Optional[torch.Tensor] = None
+
+    def half_selection(self) -> Optional[torch.Tensor]:
+        """One edge per unordered pair (row0 < row1) of a symmetric, loop-free list; None if that does not apply."""
+        if not self.symmetric or self.E % 2:
+            return None
+        if self._half is None:
+            # exactly E/2 edges have row0 < row1, so the size is known without reading the device
+            self._half = torch.nonzero_static(self.row0 < self.row1, size=self.E // 2).flatten().to(torch.int32)
+        return self._half
 
     @staticmethod
     def from_centre_sorted(row0, row1, offsets, N, symmetric: bool) -> "EdgePlan":
@@ -304,7 +314,9 @@ class FusedFilterConv(torch.autograd.Function):
     @staticmethod
     def forward(ctx, xl, d, A1, b1, A2, plan: EdgePlan, spec: RbfSpec, conv_cut, precision: int):
         be = get_backend()
-        W, status = be.filter_forward(d, spec, conv_cut[0], conv_cut[1], conv_cut[2], A1, b1, A2, precision)
+        sel = plan.half_selection()         # symmetric list: W[e] = W[reverse(e)], evaluate each pair once
+        twin = plan.perm_in if sel is not None else None
+        W, status = be.filter_forward(d, spec, conv_cut[0], conv_cut[1], conv_cut[2], A1, b1, A2, precision, sel, twin)
         be.defer_status(status, "fused filter network (forward)")
         if plan.symmetric:   # W[e] == W[reverse(e)] bit for bit: read the grouping by row1 as the grouping by row0
             agg = be.seg_mul_sum(xl, W, plan.ptr_out, plan.nbr_out, plan.perm_out, plan.N)
@@ -323,7 +335,8 @@ class FusedFilterConv(torch.autograd.Function):
         gxl = be.seg_mul_sum(g, W, plan.ptr_out, plan.nbr_out, plan.perm_out, plan.N) if ctx.needs_input_grad[0] else None
         gd = None
         if ctx.needs_input_grad[1]:
+            sel = plan.half_selection()     # d(e) and d(reverse(e)) are the same distance: one gradient per pair
             gd, status = be.filter_backward(d, ctx.spec, ctx.conv_cut[0], ctx.conv_cut[1], ctx.conv_cut[2], A1, b1, A2, plan.row0, plan.row1,
-                                            xl, g, ctx.precision)
+                                            xl, g, ctx.precision, sel, plan.perm_in if sel is not None else None)
             be.defer_status(status, "fused filter network (backward)")
         return gxl, gd, None, None, None, None, None, None, None

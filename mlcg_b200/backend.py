@@ -336,35 +336,39 @@ class CudaBackend:
         return C
 
     # ------------------------------------------------------------------ fused filter network (tensor cores)
-    def filter_forward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, precision=0):
-        """W[E,F] = (tanh(phi(d) A1^T + b1) A2^T) * C(d); float32, F = 128, R <= 128."""
+    def filter_forward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, precision=0, sel=None, twin=None):
+        """W[E,F] = (tanh(phi(d) A1^T + b1) A2^T) * C(d); float32, F = 128, R <= 128.
+        ``sel`` / ``twin``: compute one row per unordered pair and write it to both edges (symmetric edge lists)."""
         _need_cuda(d, A1, b1, A2, spec.p0, spec.p1)
         if d.dtype != torch.float32:
             raise TypeError("filter_forward is a float32 kernel")
         d, A1, b1, A2 = d.contiguous(), A1.detach().contiguous(), b1.detach().contiguous(), A2.detach().contiguous()
         s, keep = self._spec(spec, d.dtype)
         E, F = d.numel(), A2.shape[0]
+        rows = E if sel is None else sel.numel()
         W = torch.empty((E, F), dtype=d.dtype, device=d.device)
         status = self._sticky_status(d.device)
         with torch.cuda.device(d.device):
             self._run("filter_forward", self.lib.mlcgb_filter_forward,
-                      (_ptr(d), E, ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
+                      (_ptr(d), rows, _ptr(sel), _ptr(twin), ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
                        int(precision), _ptr(W), _ptr(status), _stream()),
                       nbytes=E * (4 * F + 4), flops=2 * E * F * (spec.num_rbf + F))
         return W, status
 
-    def filter_backward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, row0, row1, xl, gagg, precision=0):
+    def filter_backward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, row0, row1, xl, gagg, precision=0,
+                        sel=None, twin=None):
         """gd[E] = sum_f (xl[row0] * gagg[row1])_f * dW_f/dd."""
         _need_cuda(d, A1, b1, A2, row0, row1, xl, gagg)
         d, A1, b1, A2 = d.contiguous(), A1.detach().contiguous(), b1.detach().contiguous(), A2.detach().contiguous()
         xl, gagg = xl.detach().contiguous(), gagg.detach().contiguous()
         s, keep = self._spec(spec, d.dtype)
         E, F = d.numel(), A2.shape[0]
+        rows = E if sel is None else sel.numel()
         gd = torch.empty(E, dtype=d.dtype, device=d.device)
         status = self._sticky_status(d.device)
         with torch.cuda.device(d.device):
             self._run("filter_backward", self.lib.mlcgb_filter_backward,
-                      (_ptr(d), E, ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
+                      (_ptr(d), rows, _ptr(sel), _ptr(twin), ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
                        int(precision), _ptr(row0), _ptr(row1), _ptr(xl), _ptr(gagg), xl.shape[0], _ptr(gd), _ptr(status), _stream()),
                       nbytes=E * 16 + 2 * xl.numel() * 4, flops=2 * E * F * 2 * (spec.num_rbf + F))
         return gd, status

@@ -23,7 +23,9 @@ constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
 
 struct FilterFwdParams {
     const float *d;      // [E]
-    int64_t E;
+    int64_t E;           // rows to process: all edges, or one edge per unordered pair when `sel` is given
+    const int32_t *sel;  // [E] edge handled by row k (NULL: k itself)
+    const int32_t *twin; // reverse edge of each edge (NULL: none); with `sel`, results go to both edges of a pair
     RbfDev<float> rbf;   // basis and its envelope
     RbfDev<float> conv;  // only cutoff_kind / lower / upper are used: the CFConv cutoff C(d)
     const float *A1;     // [kF][R]
@@ -181,7 +183,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFw
     const int64_t ntiles = (p.E + kRows - 1) / kRows;
     const int64_t first = blockIdx.x, step = gridDim.x;
 
-    auto load_d = [&](int64_t tile) { const int64_t e = tile * kRows + r; return e < p.E ? p.d[e] : 1.f; };
+    auto load_d = [&](int64_t tile) {
+        const int64_t k = tile * kRows + r;
+        return k < p.E ? p.d[p.sel ? (int64_t)p.sel[k] : k] : 1.f;
+    };
     auto basis_to_tmem = [&](float de, uint32_t ta) {          // phi_k(d) for this thread's 32 columns -> A operand
         if (col0 < Kpad1) {
             float t, dt;
@@ -212,8 +217,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFw
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const int row = warp * 8 + i;
-            const int64_t er = tile * kRows + row;
-            if (er < p.E) __stcs(reinterpret_cast<float4 *>(p.W + er * kF) + lane, *stage_chunk(stage, row, lane));
+            const int64_t kr = tile * kRows + row;
+            if (kr < p.E) {
+                const int64_t er = p.sel ? (int64_t)p.sel[kr] : kr;
+                const float4 w4 = *stage_chunk(stage, row, lane);
+                __stcs(reinterpret_cast<float4 *>(p.W + er * kF) + lane, w4);
+                if (p.sel && p.twin) __stcs(reinterpret_cast<float4 *>(p.W + (int64_t)p.twin[er] * kF) + lane, w4);   // same distance, same filter
+            }
         }
     };
 
@@ -398,15 +408,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
     float de = 1.f;
     EdgeScalars es{};
     if (first < ntiles) {
-        const int64_t e = first * kRows + r;
-        de = e < p.E ? p.d[e] : 1.f;
+        const int64_t k = first * kRows + r;
+        de = k < p.E ? p.d[p.sel ? (int64_t)p.sel[k] : k] : 1.f;
         es = scalars(de);
         basis_to_tmem(es);
         ISSUE(T0, b1_hi, b1_lo, Kpad1 / 16, 0, 128)
     }
     for (int64_t tile = first; tile < ntiles; tile += step) {
-        const int64_t e = tile * kRows + r;
-        const bool live = e < p.E;
+        const int64_t krow = tile * kRows + r;
+        const bool live = krow < p.E;
+        const int64_t e = live ? (p.sel ? (int64_t)p.sel[krow] : krow) : 0;
+        const bool paired = p.sel && p.twin;      // one row per unordered pair: both directions' gW are summed
         const int64_t i0 = live ? q.row0[e] : 0, i1 = live ? q.row1[e] : 0;
         const Jet<float, 1> cj = envelope_jet<float, 1>(de, p.conv);
 
@@ -434,7 +446,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
                 const float4 a = __ldg(reinterpret_cast<const float4 *>(q.xl + j0 * kF) + cc);
                 const float4 b = __ldg(reinterpret_cast<const float4 *>(q.gagg + j1 * kF) + cc);
                 const float m = lv ? 1.f : 0.f;
-                *stage_chunk(stage, (r & ~31) + rl, cc) = make_float4(a.x * b.x * m, a.y * b.y * m, a.z * b.z * m, a.w * b.w * m);
+                float4 gw = make_float4(a.x * b.x * m, a.y * b.y * m, a.z * b.z * m, a.w * b.w * m);
+                if (paired) {   // the reverse edge: xl[row1] * gagg[row0]
+                    const float4 a2 = __ldg(reinterpret_cast<const float4 *>(q.xl + j1 * kF) + cc);
+                    const float4 b2 = __ldg(reinterpret_cast<const float4 *>(q.gagg + j0 * kF) + cc);
+                    gw.x = fmaf(a2.x * b2.x, m, gw.x); gw.y = fmaf(a2.y * b2.y, m, gw.y);
+                    gw.z = fmaf(a2.z * b2.z, m, gw.z); gw.w = fmaf(a2.w * b2.w, m, gw.w);
+                }
+                *stage_chunk(stage, (r & ~31) + rl, cc) = gw;
             }
             __syncwarp();
         }
@@ -511,8 +530,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
         float de_next = 1.f;
         EdgeScalars es_next{};
         if (next < ntiles) {
-            const int64_t en = next * kRows + r;
-            de_next = en < p.E ? p.d[en] : 1.f;
+            const int64_t kn = next * kRows + r;
+            de_next = kn < p.E ? p.d[p.sel ? (int64_t)p.sel[kn] : kn] : 1.f;
             es_next = scalars(de_next);
         }
         AWAIT()
@@ -542,7 +561,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
         s_red2[qt * 128 + r] = acc;
         tc_fence_before();
         __syncthreads();
-        if (qt == 0 && live) q.gd[e] = (s_red2[r] + s_red2[128 + r]) + (s_red2[256 + r] + s_red2[384 + r]);
+        if (qt == 0 && live) {
+            q.gd[e] = (s_red2[r] + s_red2[128 + r]) + (s_red2[256 + r] + s_red2[384 + r]);
+            if (paired) q.gd[p.twin[e]] = 0.f;   // the pair's whole gradient is carried by one of its two edges
+        }
         de = de_next;
         es = es_next;
     }
@@ -576,9 +598,9 @@ static int filter_bwd_launch(const FilterBwdParams &q, cudaStream_t st) {
 
 using namespace mlcgb;
 
-extern "C" int mlcgb_filter_forward(const void *d, int64_t E, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower,
-                                    double conv_upper, const void *A1, const void *b1, const void *A2, int64_t F, int precision,
-                                    void *W, int32_t *status, void *stream) {
+extern "C" int mlcgb_filter_forward(const void *d, int64_t E, const int32_t *sel, const int32_t *twin, const mlcgb_rbf_spec *rbf,
+                                    int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1,
+                                    const void *A2, int64_t F, int precision, void *W, int32_t *status, void *stream) {
     if (int rc = check_spec(rbf, 0)) return rc;
     if (E < 0 || !status || (precision != 0 && precision != 1) || (conv_cutoff_kind != 0 && conv_cutoff_kind != 1)) return MLCGB_E_ARG;
     if (F != kF || rbf->num_rbf > 128) return MLCGB_E_LIMIT;
@@ -587,6 +609,8 @@ extern "C" int mlcgb_filter_forward(const void *d, int64_t E, const mlcgb_rbf_sp
     FilterFwdParams p;
     p.d = (const float *)d;
     p.E = E;
+    p.sel = sel;
+    p.twin = twin;
     p.rbf = to_dev<float>(rbf);
     p.conv = p.rbf;
     p.conv.cutoff_kind = conv_cutoff_kind;
@@ -600,10 +624,10 @@ extern "C" int mlcgb_filter_forward(const void *d, int64_t E, const mlcgb_rbf_sp
     return precision == 0 ? filter_fwd_launch<true>(p, (cudaStream_t)stream) : filter_fwd_launch<false>(p, (cudaStream_t)stream);
 }
 
-extern "C" int mlcgb_filter_backward(const void *d, int64_t E, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower,
-                                     double conv_upper, const void *A1, const void *b1, const void *A2, int64_t F, int precision,
-                                     const int32_t *row0, const int32_t *row1, const void *xl, const void *gagg, int64_t N, void *gd,
-                                     int32_t *status, void *stream) {
+extern "C" int mlcgb_filter_backward(const void *d, int64_t E, const int32_t *sel, const int32_t *twin, const mlcgb_rbf_spec *rbf,
+                                     int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1,
+                                     const void *A2, int64_t F, int precision, const int32_t *row0, const int32_t *row1, const void *xl,
+                                     const void *gagg, int64_t N, void *gd, int32_t *status, void *stream) {
     if (int rc = check_spec(rbf, 1)) return rc;
     if (E < 0 || N < 0 || !status || (precision != 0 && precision != 1) || (conv_cutoff_kind != 0 && conv_cutoff_kind != 1)) return MLCGB_E_ARG;
     if (F != kF || rbf->num_rbf > 128) return MLCGB_E_LIMIT;
@@ -612,6 +636,8 @@ extern "C" int mlcgb_filter_backward(const void *d, int64_t E, const mlcgb_rbf_s
     FilterBwdParams q;
     q.f.d = (const float *)d;
     q.f.E = E;
+    q.f.sel = sel;
+    q.f.twin = twin;
     q.f.rbf = to_dev<float>(rbf);
     q.f.conv = q.f.rbf;
     q.f.conv.cutoff_kind = conv_cutoff_kind;
