@@ -14,6 +14,22 @@ def init_xavier_uniform(module: torch.nn.Module, zero_bias: bool = True) -> None
             torch.nn.init.constant_(module.bias, 0.0)
 
 
+def linear(layer: torch.nn.Linear, x: torch.Tensor, frozen: bool) -> torch.Tensor:
+    """``layer(x)`` through this package's GEMM kernels; ``frozen`` takes weight and bias out of the autograd graph."""
+    w, b = layer.weight, layer.bias
+    if frozen:
+        w, b = w.detach(), (None if b is None else b.detach())
+    return MatmulNT.apply(x, w, b)
+
+
+def node_linear(layer: torch.nn.Linear, x: torch.Tensor, training: bool) -> torch.Tensor:
+    """Node-sized Linear layers: in eval mode (forces only) on the tensor-core GEMM when the widths allow, else torch."""
+    if (not training and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and layer.in_features <= 128
+            and layer.out_features <= 128):
+        return linear(layer, x, frozen=True)
+    return layer(x)
+
+
 class MLP(torch.nn.Module):
     def __init__(self, layer_widths: List[int] = None, activation_func: torch.nn.Module = torch.nn.Tanh(), last_bias: bool = True):
         super().__init__()
@@ -31,6 +47,8 @@ class MLP(torch.nn.Module):
             init_xavier_uniform(layer)
 
     def forward(self, x, data=None):
+        if not self.training and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2:
+            return self.forward_edges(x, frozen=True)     # eval: fp32-equivalent tensor-core GEMMs, weights as constants
         return self.layers(x)
 
     def forward_edges(self, x: torch.Tensor, frozen: bool = False) -> torch.Tensor:
@@ -42,10 +60,7 @@ class MLP(torch.nn.Module):
         weights the edge-sized weight-gradient GEMMs would run even when only forces are wanted."""
         for layer in self.layers:
             if isinstance(layer, torch.nn.Linear):
-                w, b = layer.weight, layer.bias
-                if frozen:
-                    w, b = w.detach(), (None if b is None else b.detach())
-                x = MatmulNT.apply(x, w, b)
+                x = linear(layer, x, frozen)
             else:
                 x = layer(x)
         return x

@@ -13,7 +13,7 @@ from ..backend import get_backend
 from ..data import ENERGY_KEY
 from ..neighbor_list import atomic_data2neighbor_list, validate_neighborlist
 from .cutoff import cutoff_kind
-from .mlp import MLP, init_xavier_uniform
+from .mlp import MLP, init_xavier_uniform, node_linear
 
 FILTER_PRECISIONS = {"fp32": 0, "bf16": 1}
 
@@ -93,10 +93,10 @@ class CFConv(torch.nn.Module):
             fused = self.fused_spec(edge_attr.rbf_layer) if x.dtype == torch.float32 and edge_attr.symmetric == plan.symmetric else None
             if fused is not None:
                 net = self.filter_network.layers
-                xl = self.lin1(x)
+                xl = node_linear(self.lin1, x, self.training)
                 agg = FusedFilterConv.apply(xl, edge_weight, net[0].weight.detach(), net[0].bias.detach(), net[2].weight.detach(), plan,
                                             fused[0], fused[1], FILTER_PRECISIONS[self.filter_precision])
-                return self.lin2(agg)
+                return node_linear(self.lin2, agg, self.training)
             edge_attr = edge_attr.materialize()
         symmetric = bool(getattr(edge_weight, _SYM, False) and getattr(edge_attr, _SYM, False))
         W = self.filters(edge_weight, edge_attr)
@@ -123,7 +123,7 @@ class InteractionBlock(torch.nn.Module):
         init_xavier_uniform(self.lin)
 
     def forward(self, x, edge_index, edge_weight, edge_attr, *args):
-        return self.lin(self.activation(self.conv(x, edge_index, edge_weight, edge_attr)))
+        return node_linear(self.lin, self.activation(self.conv(x, edge_index, edge_weight, edge_attr)), self.training)
 
 
 class SchNet(torch.nn.Module):
