@@ -54,6 +54,25 @@ __device__ __forceinline__ void load_tile_to_stage(uint8_t *stage, const float *
     }
 }
 
+// The same, asynchronously (cp.async, 16 bytes per lane) for rows whose length is a multiple of four floats: used to
+// fetch the next tile while the current one is processed.  Out-of-range chunks are zero-filled by the copy itself.
+__device__ __forceinline__ void prefetch_tile_to_stage(uint8_t *stage, const float *__restrict__ src, int64_t row0, int64_t nrows_total,
+                                                       int ncols) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int row = warp * 8 + i;
+        const int64_t gr = row0 + row;
+        const bool ok = gr < nrows_total && lane * 4 < ncols;
+        const float *g = ok ? src + gr * ncols + lane * 4 : src;
+        const uint32_t dst = tc::smem_u32(gstage(stage, row, lane));
+        const int nbytes = ok ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(g), "r"(nbytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void wait_prefetch() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // ------------------------------------------------------------------------------------------------ NT / NN
 template <int MODE>   // 0 NT, 1 NN
 __global__ void __launch_bounds__(kGT, 1)
@@ -63,7 +82,8 @@ gemm_tc_rows_kernel(const float *__restrict__ A, const float *__restrict__ B, co
     using L = GemmTcSmem;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t *sB_hi = smem + L::kB, *sB_lo = sB_hi + 32768, *stage = smem + L::kStageA;
+    uint8_t *sB_hi = smem + L::kB, *sB_lo = sB_hi + 32768;
+    uint8_t *stages[2] = {smem + L::kStageA, smem + L::kStageB};   // input tiles, double-buffered; outputs reuse the current one
     float *s_red = reinterpret_cast<float *>(smem + L::kMisc);
     float *s_bias = s_red + 512;
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_bias + 128);
@@ -96,9 +116,20 @@ gemm_tc_rows_kernel(const float *__restrict__ A, const float *__restrict__ B, co
     uint32_t phase = 0;
 
     const int64_t ntiles = (E + kRows - 1) / kRows;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        load_tile_to_stage(stage, A, tile * kRows, E, K);
-        __syncthreads();
+    const bool async_in = (K & 3) == 0 && ((uintptr_t)A & 15) == 0;
+    int sidx = 0;
+    if (async_in && blockIdx.x < ntiles) prefetch_tile_to_stage(stages[0], A, (int64_t)blockIdx.x * kRows, E, K);
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, sidx ^= 1) {
+        uint8_t *stage = stages[sidx];
+        if (async_in) {
+            wait_prefetch();
+            __syncthreads();          // this tile has landed; the other stage was fully consumed one iteration ago
+            const int64_t next = tile + gridDim.x;
+            if (next < ntiles) prefetch_tile_to_stage(stages[sidx ^ 1], A, next * kRows, E, K);
+        } else {
+            load_tile_to_stage(stage, A, tile * kRows, E, K);
+            __syncthreads();
+        }
         float x[32];
         float rmax = 0.f;
 #pragma unroll
