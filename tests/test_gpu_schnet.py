@@ -203,3 +203,27 @@ def test_force_matching_gradients_full_width_vs_oracle():
         assert g_ref is not None, k
         err = float((p.grad.cpu().double() - g_ref).abs().max())
         assert err < 2e-4 * float(g_ref.abs().max()) + 1e-7, (k, err, float(g_ref.abs().max()))
+
+
+def test_ragged_batch_with_isolated_beads_and_no_edges():
+    """Structures of different sizes, a single-bead structure, and a batch with no edge at all (cutoff below every distance)."""
+    torch.manual_seed(0)
+    sizes = [1, 17, 3, 60, 1, 128]
+    gen = torch.Generator().manual_seed(2)
+    pos = torch.cat([random_walk_chain(n, gen, jitter=0.2) for n in sizes])
+    N, B = sum(sizes), len(sizes)
+    types_ = torch.randint(0, 6, (N,), generator=gen)
+    batch = torch.arange(B).repeat_interleave(torch.tensor(sizes))
+    for upper in (9.0, 0.01):
+        cut = bnn.CosineCutoff(0.0, upper)
+        model = bnn.StandardSchNet(bnn.ExpNormalBasis(cut, 128, trainable=False), cut, [128], hidden_channels=128, embedding_size=6,
+                                   num_filters=128, num_interactions=2)
+        e_ref, f_ref, ei = _oracle(model, "expnormal", upper, 2, pos, types_, batch, B)
+        data = mlcg_b200.AtomicData(pos=pos.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV), n_atoms=torch.tensor(sizes).to(DEV))
+        out = bnn.GradientsOut(model.to(DEV), "forces").eval()(data)
+        assert (upper < 1.0) == (ei.shape[1] == 0)   # the second pass has no edge at all
+        assert torch.allclose(out.out["SchNet"]["energy"].detach().cpu(), e_ref, rtol=E_RTOL, atol=1e-5)
+        assert float((out.out["SchNet"]["forces"].cpu() - f_ref).abs().max()) < F_ATOL
+        tr = bnn.GradientsOut(model, "forces").train()(mlcg_b200.AtomicData(pos=pos.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV),
+                                                                             n_atoms=torch.tensor(sizes).to(DEV)))
+        assert float((tr.out["SchNet"]["forces"].detach().cpu() - f_ref).abs().max()) < F_ATOL
