@@ -1,8 +1,9 @@
-// sm_100a tensor-core plumbing shared by the fused filter-network kernels: shared-memory operand
-// layout (K-major, 128-byte swizzle), UMMA descriptors, tcgen05.mma / commit / ld / st, TMEM
-// allocation, bounded mbarrier waits.
+// sm_100a tensor-core plumbing shared by the fused filter-network kernels and the tensor-core GEMMs:
+// shared-memory layout of the B (weight) operand (K-major, 128-byte swizzle), UMMA descriptors,
+// tcgen05.mma with the A operand in tensor memory, commit / ld / st, TMEM allocation, bounded mbarrier waits,
+// fp16 hi/lo packing.
 //
-// Operand tiles hold 2-byte elements (bf16 or fp16).  A [rows][K] tile is stored as K/64 "atoms";
+// Weight tiles hold 2-byte elements (bf16 or fp16).  A [rows][K] tile is stored as K/64 "atoms";
 // one atom is [rows][64 elements] = rows x 128 bytes, rows grouped by 8 (1024 bytes per group), and
 // inside a group the 16-byte chunk index of a row is XOR-ed with the row index modulo 8.  That is
 // the canonical K-major SWIZZLE_128B layout the tensor core reads through a matrix descriptor with
@@ -53,17 +54,6 @@ __device__ __forceinline__ uint64_t kstep_mnmajor(uint64_t base, int ks) { retur
 __device__ __forceinline__ uint32_t instr_desc(int fmt, int b_mn_major, int n) {
     return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)b_mn_major << 16) | (((uint32_t)n >> 3) << 17) |
            ((128u >> 4) << 24);
-}
-
-__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
-        "}\n" ::"r"(tmem_d),
-        "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
-        : "memory");
 }
 
 __device__ __forceinline__ void mma_commit(uint32_t bar_saddr) {
@@ -156,30 +146,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// ---- packing 8 fp32 values into one 16-byte operand chunk --------------------------------------------
-// SPLIT = false: bf16, one chunk.  SPLIT = true: fp16 "high" chunk plus the fp16 rounding of the remainder
-// ("low" chunk); high + low carries ~22 significant bits, and hi*hi + hi*lo + lo*hi reproduces an fp32 product.
-template <bool SPLIT>
-__device__ __forceinline__ void pack8(const float (&x)[8], uint4 &hi, uint4 &lo) {
-    uint32_t h[4], l[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        if (SPLIT) {
-            const __half2 a = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
-            const float2 b = __half22float2(a);
-            const __half2 c = __floats2half2_rn(x[2 * i] - b.x, x[2 * i + 1] - b.y);
-            h[i] = *reinterpret_cast<const uint32_t *>(&a);
-            l[i] = *reinterpret_cast<const uint32_t *>(&c);
-        } else {
-            const __nv_bfloat162 a = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
-            h[i] = *reinterpret_cast<const uint32_t *>(&a);
-            l[i] = 0u;
-        }
-    }
-    hi = make_uint4(h[0], h[1], h[2], h[3]);
-    lo = make_uint4(l[0], l[1], l[2], l[3]);
-}
-
 // Fill a [128][Kpad] weight tile (and its low part) from a row-major fp32 matrix src[rows][K], scaled by `scale`.
 template <bool SPLIT>
 __device__ __forceinline__ void load_weight_tile(uint8_t *hi, uint8_t *lo, const float *__restrict__ src, int rows, int K, int Kpad,
@@ -194,26 +160,6 @@ __device__ __forceinline__ void load_weight_tile(uint8_t *hi, uint8_t *lo, const
             *reinterpret_cast<__half *>(lo + off) = __float2half_rn(w - __half2float(a));
         } else {
             *reinterpret_cast<__nv_bfloat16 *>(hi + off) = __float2bfloat16_rn(w);
-        }
-    }
-}
-
-// One GEMM D[128 x n] = A[128 x K] * B over ksteps K-steps of 16, issued by the calling thread.
-// SPLIT: three products per step (hi*hi, hi*lo, lo*hi).  B is K-major (b_mn = 0) or MN-major (b_mn = 1).
-template <bool SPLIT>
-__device__ __forceinline__ void issue_gemm(uint32_t tmem_d, uint32_t a_hi, uint32_t a_lo, uint32_t b_hi, uint32_t b_lo, int ksteps,
-                                           int b_mn, int n = 128) {
-    const uint32_t idesc = instr_desc(SPLIT ? 0 : 1, b_mn, n);
-    const uint64_t dah = desc_kmajor(a_hi), dal = desc_kmajor(a_lo);
-    const uint64_t dbh = b_mn ? desc_mnmajor(b_hi) : desc_kmajor(b_hi), dbl = b_mn ? desc_mnmajor(b_lo) : desc_kmajor(b_lo);
-    for (int ks = 0; ks < ksteps; ks++) {
-        const uint64_t ah = kstep_kmajor(dah, ks), al = kstep_kmajor(dal, ks);
-        const uint64_t bh = b_mn ? kstep_mnmajor(dbh, ks) : kstep_kmajor(dbh, ks);
-        const uint64_t bl = b_mn ? kstep_mnmajor(dbl, ks) : kstep_kmajor(dbl, ks);
-        mma_f16(tmem_d, ah, bh, idesc, ks > 0 ? 1u : 0u);
-        if (SPLIT) {
-            mma_f16(tmem_d, ah, bl, idesc, 1u);
-            mma_f16(tmem_d, al, bh, idesc, 1u);
         }
     }
 }
