@@ -369,14 +369,14 @@ def run_ours(args):
     name, st = top
     per_launch_ms = st["ms"] / max(st["calls"], 1)
     tensor_kernels = {"gemm": "gemm_kernel<float> (filter-network GEMMs, fp32 FMA)",
-                      "filter_forward": "filter_fwd_tc_kernel (tcgen05: RBF prologue, 2 GEMMs, tanh, cutoff)",
-                      "filter_backward": "filter_bwd_tc_kernel (tcgen05: recompute + 4 GEMMs per tile, gather of gW)"}
+                      "filter_forward": "filter_fwd_pipe_kernel (tcgen05: RBF prologue, 2 GEMMs, tanh, cutoff; one row per unordered pair)",
+                      "filter_backward": "filter_bwd_pipe_kernel (tcgen05: recompute + 4 GEMMs per tile, gather of gW; one row per unordered pair)"}
     if name in tensor_kernels:
         achieved = st["flops"] / max(st["ms"], 1e-9) / 1e9            # TFLOP/s of algorithmic (fp32-equivalent) flops
         roof = dict(kernel=tensor_kernels[name], bound="tensor", achieved=achieved, peak=tf_peak, unit="TFLOP/s", frac=achieved / tf_peak,
                     traffic=None, peak_source=f"{peak_src} bf16 sustained", avg_launch_ms=per_launch_ms,
-                    note="algorithmic flops 2*E*F*(R+F) per forward GEMM pair; the fp32-equivalent mode issues three fp16 products per "
-                         "algorithmic product, so tensor-pipe work is 3x this figure")
+                    note="algorithmic flops 2*F*(R+F) per evaluated row and GEMM pair (rows = E/2 on a symmetric edge list); the fp32-equivalent "
+                         "mode issues three fp16 products per algorithmic product, so tensor-pipe work is 3x this figure")
     else:
         achieved = st["bytes"] / max(st["ms"], 1e-9) / 1e6            # GB/s
         roof = dict(kernel=name, bound="hbm", achieved=achieved, peak=hbm_peak, unit="GB/s", frac=achieved / hbm_peak, traffic=None,
@@ -385,7 +385,7 @@ def run_ours(args):
     cfconv = None
     if seg and seg["ms"] > 0:
         gbs = seg["bytes"] / seg["ms"] / 1e6
-        cfconv = dict(kernel="seg_mul_sum_kernel<float,32,true> (CFConv gather * filter, segmented sum)", bound="hbm", achieved=gbs,
+        cfconv = dict(kernel="seg_mul_sum_kernel<float,32,true,true> (CFConv gather * filter, segmented sum; filters stored once per pair)", bound="hbm", achieved=gbs,
                       peak=hbm_peak, unit="GB/s", frac=gbs / hbm_peak, edges_per_s=seg["calls"] * n_edges / (seg["ms"] / 1e3),
                       avg_launch_ms=seg["ms"] / seg["calls"])
     kernels = {k: dict(calls=v["calls"], ms_per_step=v["ms"] / args.steps,

@@ -92,6 +92,12 @@ int mlcgb_radius_graph_static(const void *pos /* [N,3] */, int dtype, const int6
 int mlcgb_edge_twin(const int32_t *row0, const int32_t *row1, const int64_t *offsets, int64_t E, int64_t N,
                     int32_t *twin /* [E] */, int32_t *status, void *stream);
 
+/* pair_of[sel[k]] = pair_of[twin[sel[k]]] = k for k < P: the row that holds a pair's filter when the filters of a
+ * symmetric list are stored once per unordered pair (mlcgb_filter_forward with `sel` and no `twin`); passed to
+ * mlcgb_seg_mul_sum as `eperm`.  No reference counterpart. */
+int mlcgb_pair_index(const int32_t *sel /* [P] */, const int32_t *twin /* [E] */, int64_t P, int32_t *pair_of /* [E] */,
+                     void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Edge geometry.  compute_distances, src/mlcg/geometry/internal_coordinates.py:72-100, split into
  * its linear part dr = pos[row1] - pos[row0] and that part's transpose (used by every derivative).
@@ -184,11 +190,14 @@ int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int6
 int mlcgb_filter_forward(const void *d /* [.] */, int64_t rows, const int32_t *sel /* [rows] or NULL */,
                          const int32_t *twin /* [E] or NULL */, const mlcgb_rbf_spec *rbf /* host */, int conv_cutoff_kind,
                          double conv_lower, double conv_upper, const void *A1 /* [F,R] */, const void *b1 /* [F] */,
-                         const void *A2 /* [F,F] */, int64_t F, int precision, void *W /* [E,F] */, int32_t *status, void *stream);
+                         const void *A2 /* [F,F] */, int64_t F, int precision, void *W /* [E,F] or [rows,F] */, int32_t *status,
+                         void *stream);
 /* `rows` = E and sel = twin = NULL: row k is edge k.  For a symmetric edge list the filter of an edge equals that of its
- * reverse (same distance), so the caller may pass one edge per unordered pair in `sel` (rows = E/2) together with the
- * reverse-edge map `twin` (mlcgb_edge_twin): each computed row is then written to both edges, and the backward below
- * sums the two directions' incoming gradients and returns the pair's gradient on the selected edge (zero on its twin). */
+ * reverse (same distance), so the caller may pass one edge per unordered pair in `sel` (rows = E/2).  With the
+ * reverse-edge map `twin` (mlcgb_edge_twin) each computed row is written to both edges of W[E,F]; without it W has
+ * `rows` rows and row k holds the filter of edge sel[k] and of its reverse (half the HBM traffic; the aggregation then
+ * reads W through mlcgb_pair_index).  The backward below, given `sel` and `twin`, sums the two directions' incoming
+ * gradients and returns the pair's gradient on the selected edge (zero on its twin). */
 
 /* Backward of the above with respect to the distance, fused with the message product:
  *   gd[e] = sum_f gW[e,f] * dW[e,f]/dd_e,  gW[e,:] = xl[row0[e],:] * gagg[row1[e],:]

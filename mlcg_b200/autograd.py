@@ -37,26 +37,37 @@ class EdgePlan:
     perm_in: torch.Tensor              # int32 [E]
     nbr_in: torch.Tensor               # int32 [E]  row0 in that grouping
     symmetric: bool = False            # every edge has its reverse, and perm_in maps an edge to it
+    loops: bool = False                # the list may hold edges (i, i)
     _half: Optional[torch.Tensor] = None
+    _pair_of: Optional[torch.Tensor] = None
 
     def half_selection(self) -> Optional[torch.Tensor]:
         """One edge per unordered pair (row0 < row1) of a symmetric, loop-free list; None if that does not apply."""
-        if not self.symmetric or self.E % 2:
+        if not self.symmetric or self.loops or self.E % 2:
             return None
         if self._half is None:
             # exactly E/2 edges have row0 < row1, so the size is known without reading the device
             self._half = torch.nonzero_static(self.row0 < self.row1, size=self.E // 2).flatten().to(torch.int32)
         return self._half
 
+    def pair_index(self) -> Optional[torch.Tensor]:
+        """For every edge the position of its unordered pair in :meth:`half_selection`; None if that does not apply."""
+        sel = self.half_selection()
+        if sel is None:
+            return None
+        if self._pair_of is None:
+            self._pair_of = get_backend().pair_index(sel, self.perm_in)
+        return self._pair_of
+
     @staticmethod
-    def from_centre_sorted(row0, row1, offsets, N, symmetric: bool) -> "EdgePlan":
+    def from_centre_sorted(row0, row1, offsets, N, symmetric: bool, loops: bool = False) -> "EdgePlan":
         """Edges sorted by (row0, row1) as the radius graph emits them."""
         be = get_backend()
         E = row0.numel()
         if symmetric:
             twin, _ = be.edge_twin(row0, row1, offsets, N)
             # the k-th edge grouped by row1 is the reverse of the k-th edge grouped by row0
-            return EdgePlan(N, E, row0, row1, offsets, None, row1, offsets, twin, row1, True)
+            return EdgePlan(N, E, row0, row1, offsets, None, row1, offsets, twin, row1, True, loops)
         return EdgePlan._general(row0, row1, N, ptr_out=offsets, perm_out=None)
 
     @staticmethod
@@ -308,18 +319,20 @@ class SegmentSum(torch.autograd.Function):
 class FusedFilterConv(torch.autograd.Function):
     """agg = SegIn(xl, W(d)) with W(d) = (tanh(phi(d) A1^T + b1) A2^T) C(d) produced by the tensor-core kernel.
 
+    On a symmetric edge list W[e] = W[reverse(e)] (same distance): the filters are evaluated and stored once per
+    unordered pair and both aggregations read them through the edge -> pair index.
+
     First-order only (energies and forces): the backward returns the gradients with respect to ``xl`` and
     ``d`` and is not itself differentiable; training mode uses the composable operators above instead."""
 
     @staticmethod
     def forward(ctx, xl, d, A1, b1, A2, plan: EdgePlan, spec: RbfSpec, conv_cut, precision: int):
         be = get_backend()
-        sel = plan.half_selection()         # symmetric list: W[e] = W[reverse(e)], evaluate each pair once
-        twin = plan.perm_in if sel is not None else None
-        W, status = be.filter_forward(d, spec, conv_cut[0], conv_cut[1], conv_cut[2], A1, b1, A2, precision, sel, twin)
+        sel = plan.half_selection()
+        W, status = be.filter_forward(d, spec, conv_cut[0], conv_cut[1], conv_cut[2], A1, b1, A2, precision, sel, None)
         be.defer_status(status, "fused filter network (forward)")
-        if plan.symmetric:   # W[e] == W[reverse(e)] bit for bit: read the grouping by row1 as the grouping by row0
-            agg = be.seg_mul_sum(xl, W, plan.ptr_out, plan.nbr_out, plan.perm_out, plan.N)
+        if sel is not None:   # W[pair]; grouping by row1 read as the grouping by row0 of the reversed edges
+            agg = be.seg_mul_sum(xl, W, plan.ptr_out, plan.nbr_out, plan.pair_index(), plan.N)
         else:
             agg = be.seg_mul_sum(xl, W, plan.ptr_in, plan.nbr_in, plan.perm_in, plan.N)
         ctx.plan, ctx.spec, ctx.conv_cut, ctx.precision = plan, spec, conv_cut, precision
@@ -332,10 +345,12 @@ class FusedFilterConv(torch.autograd.Function):
         xl, d, W, A1, b1, A2 = ctx.saved_tensors
         plan, be = ctx.plan, get_backend()
         g = g.contiguous()
-        gxl = be.seg_mul_sum(g, W, plan.ptr_out, plan.nbr_out, plan.perm_out, plan.N) if ctx.needs_input_grad[0] else None
+        sel = plan.half_selection()
+        gxl = None
+        if ctx.needs_input_grad[0]:
+            gxl = be.seg_mul_sum(g, W, plan.ptr_out, plan.nbr_out, plan.pair_index() if sel is not None else plan.perm_out, plan.N)
         gd = None
-        if ctx.needs_input_grad[1]:
-            sel = plan.half_selection()     # d(e) and d(reverse(e)) are the same distance: one gradient per pair
+        if ctx.needs_input_grad[1]:     # d(e) and d(reverse(e)) are the same distance: one gradient per pair
             gd, status = be.filter_backward(d, ctx.spec, ctx.conv_cut[0], ctx.conv_cut[1], ctx.conv_cut[2], A1, b1, A2, plan.row0, plan.row1,
                                             xl, g, ctx.precision, sel, plan.perm_in if sel is not None else None)
             be.defer_status(status, "fused filter network (backward)")

@@ -210,6 +210,14 @@ class CudaBackend:
             self._run("edge_twin", self.lib.mlcgb_edge_twin, (_ptr(row0), _ptr(row1), _ptr(offsets), E, N, _ptr(twin), _ptr(status), _stream(),), **self._work("edge_twin", locals()))
         return twin, status
 
+    def pair_index(self, sel, twin):
+        """pair_of[e] = k for the k-th selected edge and for its reverse."""
+        _need_cuda(sel, twin)
+        pair_of = torch.empty(twin.numel(), dtype=torch.int32, device=twin.device)
+        with torch.cuda.device(twin.device):
+            self._run("pair_index", self.lib.mlcgb_pair_index, (_ptr(sel), _ptr(twin), sel.numel(), _ptr(pair_of), _stream(),), nbytes=12 * sel.numel())
+        return pair_of
+
     # ------------------------------------------------------------------ geometry
     def edge_diff(self, pos, row0, row1):
         _need_cuda(pos, row0, row1)
@@ -338,7 +346,8 @@ class CudaBackend:
     # ------------------------------------------------------------------ fused filter network (tensor cores)
     def filter_forward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, precision=0, sel=None, twin=None):
         """W[E,F] = (tanh(phi(d) A1^T + b1) A2^T) * C(d); float32, F = 128, R <= 128.
-        ``sel`` / ``twin``: compute one row per unordered pair and write it to both edges (symmetric edge lists)."""
+        ``sel`` / ``twin``: compute one row per unordered pair and write it to both edges (symmetric edge lists);
+        ``sel`` alone: W has one row per selected edge, in the order of ``sel``."""
         _need_cuda(d, A1, b1, A2, spec.p0, spec.p1)
         if d.dtype != torch.float32:
             raise TypeError("filter_forward is a float32 kernel")
@@ -346,13 +355,13 @@ class CudaBackend:
         s, keep = self._spec(spec, d.dtype)
         E, F = d.numel(), A2.shape[0]
         rows = E if sel is None else sel.numel()
-        W = torch.empty((E, F), dtype=d.dtype, device=d.device)
+        W = torch.empty((E if (sel is None or twin is not None) else rows, F), dtype=d.dtype, device=d.device)
         status = self._sticky_status(d.device)
         with torch.cuda.device(d.device):
             self._run("filter_forward", self.lib.mlcgb_filter_forward,
                       (_ptr(d), rows, _ptr(sel), _ptr(twin), ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
                        int(precision), _ptr(W), _ptr(status), _stream()),
-                      nbytes=E * (4 * F + 4), flops=2 * E * F * (spec.num_rbf + F))
+                      nbytes=W.shape[0] * 4 * F + 4 * rows, flops=2 * rows * F * (spec.num_rbf + F))
         return W, status
 
     def filter_backward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, row0, row1, xl, gagg, precision=0,
@@ -370,7 +379,7 @@ class CudaBackend:
             self._run("filter_backward", self.lib.mlcgb_filter_backward,
                       (_ptr(d), rows, _ptr(sel), _ptr(twin), ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
                        int(precision), _ptr(row0), _ptr(row1), _ptr(xl), _ptr(gagg), xl.shape[0], _ptr(gd), _ptr(status), _stream()),
-                      nbytes=E * 16 + 2 * xl.numel() * 4, flops=2 * E * F * 2 * (spec.num_rbf + F))
+                      nbytes=E * 16 + 2 * xl.numel() * 4, flops=2 * rows * F * 2 * (spec.num_rbf + F))
         return gd, status
 
     def segment_sum(self, x, ptr):

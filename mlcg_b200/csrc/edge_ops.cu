@@ -37,7 +37,10 @@ __device__ __forceinline__ void st_stream(double2 *p, const double2 &v) { __stcs
 
 // ------------------------------------------------------------------------------- seg_mul_sum
 // One group of G lanes per destination row; G*W elements per pass over the feature dimension.
-template <typename T, int G, bool VEC>
+// PERM: rows of V are picked through eperm.  Such rows may be shared between destination rows (a filter stored once
+// per pair of a symmetric list is read from both ends), so they are loaded with the default cache policy and the
+// second reader finds them in L2; rows read in order are read once and loaded with the streaming hint.
+template <typename T, int G, bool VEC, bool PERM>
 __global__ void __launch_bounds__(256)
 seg_mul_sum_kernel(const T *__restrict__ a, const T *__restrict__ V, const int64_t *__restrict__ ptr,
                    const int32_t *__restrict__ nbr, const int32_t *__restrict__ eperm, int64_t N, int64_t F,
@@ -58,11 +61,12 @@ seg_mul_sum_kernel(const T *__restrict__ a, const T *__restrict__ V, const int64
                     int64_t e[4];
                     int32_t j[4];
 #pragma unroll
-                    for (int u = 0; u < 4; u++) { j[u] = nbr[k + u]; e[u] = eperm ? (int64_t)eperm[k + u] : k + u; }
+                    for (int u = 0; u < 4; u++) { j[u] = nbr[k + u]; e[u] = PERM ? (int64_t)eperm[k + u] : k + u; }
                     VT v[4], x[4];
 #pragma unroll
                     for (int u = 0; u < 4; u++) {
-                        v[u] = ld_stream(reinterpret_cast<const VT *>(V + e[u] * F) + c);
+                        const VT *vp = reinterpret_cast<const VT *>(V + e[u] * F) + c;
+                        v[u] = PERM ? __ldg(vp) : ld_stream(vp);
                         x[u] = __ldg(reinterpret_cast<const VT *>(a + (int64_t)j[u] * F) + c);
                     }
                     vfma(acc0, x[0], v[0]);
@@ -71,8 +75,9 @@ seg_mul_sum_kernel(const T *__restrict__ a, const T *__restrict__ V, const int64
                     vfma(acc1, x[3], v[3]);
                 }
                 for (; k < k1; k++) {
-                    const int64_t e = eperm ? (int64_t)eperm[k] : k;
-                    const VT v = ld_stream(reinterpret_cast<const VT *>(V + e * F) + c);
+                    const int64_t e = PERM ? (int64_t)eperm[k] : k;
+                    const VT *vp = reinterpret_cast<const VT *>(V + e * F) + c;
+                    const VT v = PERM ? __ldg(vp) : ld_stream(vp);
                     const VT x = __ldg(reinterpret_cast<const VT *>(a + (int64_t)nbr[k] * F) + c);
                     vfma(acc0, x, v);
                 }
@@ -86,7 +91,7 @@ seg_mul_sum_kernel(const T *__restrict__ a, const T *__restrict__ V, const int64
             } else {
                 T acc = T(0);
                 for (int64_t k = k0; k < k1; k++) {
-                    const int64_t e = eperm ? (int64_t)eperm[k] : k;
+                    const int64_t e = PERM ? (int64_t)eperm[k] : k;
                     acc = fma(a[(int64_t)nbr[k] * F + c], V[e * F + c], acc);
                 }
                 out[n * F + c] = acc;
@@ -229,9 +234,12 @@ static int seg_mul_sum_launch(const void *a, const void *V, const int64_t *ptr, 
     int G = 32;
     while (G > 1 && G / 2 >= Fv) G /= 2;  // smallest power of two >= Fv, capped at a warp
     const int grid = grid_for(N * G, 256, 16);
-#define LAUNCH(GG)                                                                                                           \
-    if (vec) seg_mul_sum_kernel<T, GG, true><<<grid, 256, 0, st>>>((const T *)a, (const T *)V, ptr, nbr, eperm, N, F, (T *)out); \
-    else seg_mul_sum_kernel<T, GG, false><<<grid, 256, 0, st>>>((const T *)a, (const T *)V, ptr, nbr, eperm, N, F, (T *)out)
+#define LAUNCH2(GG, VV)                                                                                                              \
+    if (eperm) seg_mul_sum_kernel<T, GG, VV, true><<<grid, 256, 0, st>>>((const T *)a, (const T *)V, ptr, nbr, eperm, N, F, (T *)out);  \
+    else seg_mul_sum_kernel<T, GG, VV, false><<<grid, 256, 0, st>>>((const T *)a, (const T *)V, ptr, nbr, eperm, N, F, (T *)out)
+#define LAUNCH(GG)                \
+    if (vec) { LAUNCH2(GG, true); } \
+    else { LAUNCH2(GG, false); }
     switch (G) {
         case 32: LAUNCH(32); break;
         case 16: LAUNCH(16); break;
@@ -241,6 +249,7 @@ static int seg_mul_sum_launch(const void *a, const void *V, const int64_t *ptr, 
         default: LAUNCH(1); break;
     }
 #undef LAUNCH
+#undef LAUNCH2
     return check_launch();
 }
 

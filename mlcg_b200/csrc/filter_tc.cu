@@ -26,6 +26,7 @@ struct FilterFwdParams {
     int64_t E;           // rows to process: all edges, or one edge per unordered pair when `sel` is given
     const int32_t *sel;  // [E] edge handled by row k (NULL: k itself)
     const int32_t *twin; // reverse edge of each edge (NULL: none); with `sel`, results go to both edges of a pair
+                         // (forward with `sel` alone: W has E rows, row k is the filter of edge sel[k])
     RbfDev<float> rbf;   // basis and its envelope
     RbfDev<float> conv;  // only cutoff_kind / lower / upper are used: the CFConv cutoff C(d)
     const float *A1;     // [kF][R]
@@ -219,7 +220,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFw
             const int row = warp * 8 + i;
             const int64_t kr = tile * kRows + row;
             if (kr < p.E) {
-                const int64_t er = p.sel ? (int64_t)p.sel[kr] : kr;
+                const int64_t er = (p.sel && p.twin) ? (int64_t)p.sel[kr] : kr;   // sel without twin: one row per pair, in order
                 const float4 w4 = *stage_chunk(stage, row, lane);
                 __stcs(reinterpret_cast<float4 *>(p.W + er * kF) + lane, w4);
                 if (p.sel && p.twin) __stcs(reinterpret_cast<float4 *>(p.W + (int64_t)p.twin[er] * kF) + lane, w4);   // same distance, same filter

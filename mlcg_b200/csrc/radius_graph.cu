@@ -455,6 +455,17 @@ __global__ void edge_twin_kernel(const int32_t *__restrict__ row0, const int32_t
     }
 }
 
+// pair_of[e] = k for the k-th selected edge and for its reverse
+__global__ void pair_index_kernel(const int32_t *__restrict__ sel, const int32_t *__restrict__ twin, int64_t P,
+                                  int32_t *__restrict__ pair_of) {
+    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < P; k += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t e = sel[k];
+        pair_of[e] = (int32_t)k;
+        const int32_t t = twin[e];
+        if (t >= 0) pair_of[t] = (int32_t)k;
+    }
+}
+
 template <typename T>
 static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn,
                          int loop, int rule, void *ws, size_t ws_bytes, int dtype, int32_t *deg, int64_t *offsets,
@@ -540,6 +551,14 @@ int mlcgb_edge_twin(const int32_t *row0, const int32_t *row1, const int64_t *off
     if (E == 0) return MLCGB_OK;
     if (!row0 || !row1 || !offsets || !twin) return MLCGB_E_ARG;
     edge_twin_kernel<<<grid_for(E, 256), 256, 0, (cudaStream_t)stream>>>(row0, row1, offsets, E, N, twin, status);
+    return check_launch();
+}
+
+int mlcgb_pair_index(const int32_t *sel, const int32_t *twin, int64_t P, int32_t *pair_of, void *stream) {
+    if (P < 0) return MLCGB_E_ARG;
+    if (P == 0) return MLCGB_OK;
+    if (!sel || !twin || !pair_of) return MLCGB_E_ARG;
+    pair_index_kernel<<<grid_for(P, 256), 256, 0, (cudaStream_t)stream>>>(sel, twin, P, pair_of);
     return check_launch();
 }
 

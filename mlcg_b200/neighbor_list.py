@@ -41,7 +41,7 @@ def _graph(x, r, ptr, loop, max_num_neighbors, rule, want_distance=False):
     be = get_backend()
     res = be.radius_graph(_as_3d(x), ptr, r, max_num_neighbors, loop, rule, want_distance=want_distance)
     truncated = bool(res["status"] & STATUS_TRUNCATED)
-    plan = EdgePlan.from_centre_sorted(res["row0"], res["row1"], res["offsets"], x.shape[0], symmetric=not truncated)
+    plan = EdgePlan.from_centre_sorted(res["row0"], res["row1"], res["offsets"], x.shape[0], symmetric=not truncated, loops=bool(loop))
     attach_plan(res["edge_index"], plan)
     res["plan"], res["truncated"] = plan, truncated
     return res

@@ -53,6 +53,13 @@ class OracleBackend:
             status[0] = 4
         return twin, status
 
+    def pair_index(self, sel, twin):
+        pair_of = torch.full((twin.numel(),), -1, dtype=torch.int32)
+        k = torch.arange(sel.numel(), dtype=torch.int32)
+        pair_of[sel.long()] = k
+        pair_of[twin[sel.long()].long()] = k
+        return pair_of
+
     # ------------------------------------------------------------------ geometry
     def edge_diff(self, pos, row0, row1):
         return pos[row1.long()] - pos[row0.long()]

@@ -4,6 +4,7 @@ import torch
 
 from mlcg_b200.backend import RbfSpec, get_backend
 from oracle import schnet_ref
+from oracle.primitives import OracleBackend
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -113,6 +114,16 @@ def test_pair_mode_equals_per_edge_mode():
     W_full, _ = be.filter_forward(d, spec, 1, 0.0, upper, A1, b1, A2, 0)
     W_pair, _ = be.filter_forward(d, spec, 1, 0.0, upper, A1, b1, A2, 0, sel, plan.perm_in)
     assert torch.equal(W_full, W_pair)
+    # one stored row per pair, read by both edges through the pair index
+    W_half, _ = be.filter_forward(d, spec, 1, 0.0, upper, A1, b1, A2, 0, sel)
+    pair_of = plan.pair_index()
+    assert W_half.shape[0] * 2 == plan.E
+    assert torch.equal(pair_of.cpu(), OracleBackend().pair_index(sel.cpu(), plan.perm_in.cpu()))
+    assert torch.equal(W_half[pair_of.long()], W_full)
+    xs = torch.randn(B * n, F, generator=gen).to(DEV)
+    agg_full = be.seg_mul_sum(xs, W_full, plan.ptr_out, plan.nbr_out, None, plan.N)
+    agg_half = be.seg_mul_sum(xs, W_half, plan.ptr_out, plan.nbr_out, pair_of, plan.N)
+    assert torch.equal(agg_full, agg_half)
     xl, gagg = torch.randn(B * n, F, generator=gen).to(DEV), torch.randn(B * n, F, generator=gen).to(DEV)
     g_full, _ = be.filter_backward(d, spec, 1, 0.0, upper, A1, b1, A2, plan.row0, plan.row1, xl, gagg, 0)
     g_pair, _ = be.filter_backward(d, spec, 1, 0.0, upper, A1, b1, A2, plan.row0, plan.row1, xl, gagg, 0, sel, plan.perm_in)
