@@ -11,6 +11,10 @@
 // Precision modes.  0: every fp32 value is carried as an fp16 pair (value = hi + lo, ~22 bits) and
 // each GEMM runs hi*hi + hi*lo + lo*hi with fp32 accumulation — the products an fp32 GEMM forms, at
 // half-precision tensor-core rate.  1: operands rounded to bf16, one product, tanh.approx.
+#include <cuda.h>
+
+#include <cstring>
+
 #include "rbf_device.cuh"
 #include "tc_common.cuh"
 
@@ -39,12 +43,14 @@ struct FilterFwdParams {
 template <bool SPLIT>
 struct FilterSmem {
     static constexpr int kTile = SPLIT ? 2 * 32768 : 32768;   // one 128x128 operand tile (hi [+ lo])
-    static constexpr int kA = 0, kB1 = kTile, kB2 = 2 * kTile, kMisc = 3 * kTile;
+    static constexpr int kStageBytes = 65536;                 // fp32 staging tile: 128 rows of 512 B
+    static constexpr int kASize = SPLIT ? kStageBytes : kTile;
+    static constexpr int kA = 0, kB1 = kASize, kB2 = kASize + kTile, kMisc = kASize + 2 * kTile;
     // misc: bias, scaled bias [2][128] f32 | basis table [128] float2 | exchange [4][128] f32 x2 | barrier, TMEM slot, error flag
     static constexpr int kBias = 0, kTable = 1024, kRed = 2048, kRed2 = 4096, kBar = 6144;
-    // 64 KB fp32 staging tile for coalesced global traffic: over the A operand where that is 64 KB, else its own region
+    // fp32 staging tile for coalesced global traffic: in the A region (free when the A operands live in TMEM) or its own
     static constexpr int kStage = SPLIT ? kA : kMisc + 7168;
-    static constexpr int kTotal = kMisc + 7168 + (SPLIT ? 0 : 65536) + 1024;        // + alignment slack
+    static constexpr int kTotal = kMisc + 7168 + (SPLIT ? 0 : kStageBytes) + 1024;   // + alignment slack
 };
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -116,11 +122,11 @@ __device__ __forceinline__ uint32_t filter_setup(const FilterFwdParams &p, uint8
 
 // h = tanh(z) for this thread's 32 accumulator values, z = v * unscale + b1, through exp2: tanh z = sign(z) (1 - 2/(2^{|zz|} + 1)),
 // zz = 2 log2(e) z  (2^{|zz|} overflowing to inf gives exactly 1)
-template <bool SPLIT>
-__device__ __forceinline__ void tanh_row32(float (&v)[32], const float *s_b1s, int col0, float unscale2) {
+template <bool SPLIT, int NC = 32>
+__device__ __forceinline__ void tanh_row32(float (&v)[NC], const float *s_b1s, int col0, float unscale2) {
     const float4 *b4 = reinterpret_cast<const float4 *>(s_b1s + col0);
 #pragma unroll
-    for (int q = 0; q < 8; q++) {
+    for (int q = 0; q < NC / 4; q++) {
         const float4 bq = b4[q];
         const float bb[4] = {bq.x, bq.y, bq.z, bq.w};
 #pragma unroll
@@ -143,6 +149,17 @@ __device__ __forceinline__ float4 *stage_chunk(uint8_t *stage, int row, int chun
     return reinterpret_cast<float4 *>(stage + row * 512 + ((chunk ^ (row & 7)) << 4));
 }
 
+// One 32-column x 128-row box of the staging tile (128-byte swizzle) to rows [y, y+128) of the [rows][128] fp32 tensor
+// the map describes; rows past the end of the tensor are clipped by the copy engine.
+__device__ __forceinline__ void tensor_store_box(const CUtensorMap *map, int x, int y, const uint8_t *src_box) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x),
+                 "r"(y), "r"(tc::smem_u32(src_box))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ------------------------------------------------------------------------------------------------
 // Forward, pipelined: the A operands (phi, h) live in tensor memory instead of shared memory, which
 // leaves room for two tiles in flight.  TMEM columns: D1 [0,128) | D2 [128,256) | A of even tiles
@@ -150,13 +167,15 @@ __device__ __forceinline__ float4 *stage_chunk(uint8_t *stage, int row, int chun
 // While GEMM 1 of tile i runs the threads store W of tile i-1; while GEMM 2 of tile i runs they evaluate
 // the radial basis of tile i+1.
 // ------------------------------------------------------------------------------------------------
-template <bool SPLIT>
-__global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFwdParams p) {
+template <bool SPLIT, int NT>
+__global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams p, const __grid_constant__ CUtensorMap wmap, int use_map) {
+    constexpr int NC = 128 * 128 / NT;      // columns per thread: 32 with 512 threads (1024 threads x 16 columns measured no faster)
+    constexpr int RPW = 128 * 32 / NT;      // rows each warp writes out: 8 or 4
     using namespace tc;
     using L = FilterSmem<SPLIT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t *stage = smem + L::kA;                       // the A region of the layout is free here: 64 KB (split) ...
+    uint8_t *stage = smem + L::kA;                       // the A region of the layout is free here (split) ...
     if (!SPLIT) stage = smem + L::kStage;                // ... or the separate staging region
     const float *s_b1 = reinterpret_cast<const float *>(smem + L::kMisc + L::kBias);
     const float2 *s_tab = reinterpret_cast<const float2 *>(smem + L::kMisc + L::kTable);
@@ -165,7 +184,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFw
     int *s_err = reinterpret_cast<int *>(reinterpret_cast<uint32_t *>(s_bar + 1) + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int r = tid & 127, col0 = (tid >> 7) * 32;
+    const int r = tid & 127, col0 = (tid >> 7) * NC;
     const int R = p.rbf.R;
     const int Kpad1 = R <= 64 ? 64 : 128;
     const float wscale = SPLIT ? kWScale : 1.f;
@@ -188,36 +207,61 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFw
         const int64_t k = tile * kRows + r;
         return k < p.E ? p.d[p.sel ? (int64_t)p.sel[k] : k] : 1.f;
     };
-    auto basis_to_tmem = [&](float de, uint32_t ta) {          // phi_k(d) for this thread's 32 columns -> A operand
+    const bool same_env = p.conv.cutoff_kind == p.rbf.cutoff_kind && p.conv.lower == p.rbf.lower && p.conv.upper == p.rbf.upper;
+    // phi_k(d) for this thread's columns -> A operand; returns the CFConv cutoff C(d) of the row (the envelope of the basis
+    // when both use the same cutoff, as SchNet builds them)
+    auto basis_to_tmem = [&](float de, uint32_t ta) {
+        const float env = envelope_jet<float, 0>(de, p.rbf).c[0];
         if (col0 < Kpad1) {
             float t, dt;
             edge_arg(de, p.rbf, t, dt);
-            const float l2a = log2f(envelope_jet<float, 0>(de, p.rbf).c[0]);
-            float x[32];
+            const float l2a = log2f(env);
+            float x[NC];
             const float4 *tab4 = reinterpret_cast<const float4 *>(s_tab + col0);   // two (centre, width) pairs per 128-bit read
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
+            for (int j = 0; j < NC / 2; j++) {
                 const float4 cw = tab4[j];
                 const float u0 = t - cw.x, u1 = t - cw.z;
                 x[2 * j] = ex2_fast(fmaf(-cw.y * u0, u0, l2a));
                 x[2 * j + 1] = ex2_fast(fmaf(-cw.w * u1, u1, l2a));
             }
-            store_a_tmem<SPLIT>(ta + lane_off, col0, x, 1.f);
+            store_a_tmem_cols<SPLIT, NC>(ta + lane_off, col0, x, 1.f);
         }
         tmem_wait_st();
+        return same_env ? env : envelope_jet<float, 0>(de, p.conv).c[0];
     };
-    auto store_w = [&](int64_t tile, float de) {               // W = y * C(d): D2 -> shared-memory stage -> whole rows
-        const float C = envelope_jet<float, 0>(de, p.conv).c[0] * unscale;
-        float v[32];
-        tmem_ld32(t_lane + 128 + col0, v);
+    // W = y * C(d): D2 -> shared-memory stage -> global memory.  With a tensor map (rows written in order) the stage is four
+    // 32-column boxes in the 128-byte swizzle and one thread hands them to the copy engine, which drains them while the
+    // CTA goes on; otherwise (rows scattered to an edge and its reverse) warps copy whole 512-byte rows themselves.
+    auto store_w = [&](int64_t tile, float C) {
+        C *= unscale;
+        float v[NC];
+        tmem_ld_cols<NC>(t_lane + 128 + col0, v);
+        if (use_map) {
+            uint8_t *box_row = stage + (col0 >> 5) * 16384 + r * 128;
+            const int chunk0 = (col0 & 31) >> 2;
 #pragma unroll
-        for (int q = 0; q < 8; q++)
+            for (int q = 0; q < NC / 4; q++)
+                *reinterpret_cast<float4 *>(box_row + (((chunk0 + q) ^ (r & 7)) << 4)) =
+                    make_float4(v[4 * q] * C, v[4 * q + 1] * C, v[4 * q + 2] * C, v[4 * q + 3] * C);
+            fence_async_smem();                                 // the copy engine reads the stage through the async proxy
+            tc_fence_before();
+            __syncthreads();
+            if (tid == 0) {
+#pragma unroll
+                for (int b = 0; b < 4; b++) tensor_store_box(&wmap, 32 * b, (int)(tile * kRows), stage + b * 16384);
+                bulk_commit();
+            }
+            return;
+        }
+#pragma unroll
+        for (int q = 0; q < NC / 4; q++)
             *stage_chunk(stage, r, (col0 >> 2) + q) = make_float4(v[4 * q] * C, v[4 * q + 1] * C, v[4 * q + 2] * C, v[4 * q + 3] * C);
         tc_fence_before();
         __syncthreads();
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int row = warp * 8 + i;
+        for (int i = 0; i < RPW; i++) {
+            const int row = warp * RPW + i;
             const int64_t kr = tile * kRows + row;
             if (kr < p.E) {
                 const int64_t er = (p.sel && p.twin) ? (int64_t)p.sel[kr] : kr;   // sel without twin: one row per pair, in order
@@ -228,10 +272,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFw
         }
     };
 
-    float de = 0.f, de_prev = 0.f;
+    float c_cur = 0.f, c_prev = 0.f;
     if (first < ntiles) {
-        de = load_d(first);
-        basis_to_tmem(de, tmem + 256);
+        c_cur = basis_to_tmem(load_d(first), tmem + 256);
         tc_fence_before();
         __syncthreads();
         if (tid == 0) {
@@ -244,18 +287,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFw
     for (int64_t tile = first; tile < ntiles; tile += step, s ^= 1) {
         const uint32_t ta = tmem + 256 + s * 128, ta_next = tmem + 256 + (s ^ 1) * 128;
         // (a) GEMM 1 of this tile is running: write out W of the previous tile
-        if (tile != first) store_w(tile - step, de_prev);
+        if (tile != first) store_w(tile - step, c_prev);
         // (b) h = tanh(z + b1) -> A operand (over phi, which GEMM 1 has finished reading), then GEMM 2
         if (!mbar_wait(bar1, ph1)) failed = true;
         ph1 ^= 1;
         tc_fence_after();
         {
-            float v[32];
-            tmem_ld32(t_lane + col0, v);
-            tanh_row32<SPLIT>(v, s_b1 + kF, col0, unscale * (2.f * kLog2e));
-            store_a_tmem<SPLIT>(ta + lane_off, col0, v, 1.f);
+            float v[NC];
+            tmem_ld_cols<NC>(t_lane + col0, v);
+            tanh_row32<SPLIT, NC>(v, s_b1 + kF, col0, unscale * (2.f * kLog2e));
+            store_a_tmem_cols<SPLIT, NC>(ta + lane_off, col0, v, 1.f);
             tmem_wait_st();
         }
+        bulk_wait_read();                                        // the copies of (a) have read the stage
         tc_fence_before();
         __syncthreads();                                         // also: every thread is done with the stage of (a)
         if (tid == 0) {
@@ -265,11 +309,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFw
         }
         // (c) GEMM 2 is running: radial basis of the next tile into the other A block
         const int64_t next = tile + step;
-        de_prev = de;
-        if (next < ntiles) {
-            de = load_d(next);
-            basis_to_tmem(de, ta_next);
-        }
+        c_prev = c_cur;
+        if (next < ntiles) c_cur = basis_to_tmem(load_d(next), ta_next);
         if (!mbar_wait(bar2, ph2)) failed = true;
         ph2 ^= 1;
         tc_fence_after();
@@ -282,13 +323,41 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_fwd_pipe_kernel(FilterFw
             issue_gemm_ts<SPLIT>(tmem, ta_next, b1_hi, b1_lo, Kpad1 / 16, 0, 128);
             mma_commit(bar1);
         }
-        if (next >= ntiles) store_w(tile, de_prev);               // last tile of this CTA
+        if (next >= ntiles) store_w(tile, c_prev);                // last tile of this CTA
     }
 
+    bulk_wait_all();
     tc_fence_before();
     __syncthreads();
     if (s_err[0] && tid == 0) atomicOr(p.status, 8);
     if (warp == 0) tmem_free(tmem, 512);
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda)
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                      const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TensorMapEncodeFn tensor_map_encoder() {
+    static TensorMapEncodeFn fn = [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) != cudaSuccess || res != cudaDriverEntryPointSuccess)
+            ptr = nullptr;
+        return (TensorMapEncodeFn)ptr;
+    }();
+    return fn;
+}
+
+// Map of W[rows][128] fp32 for stores of 32-column x 128-row boxes in the 128-byte swizzle.
+static bool make_w_map(CUtensorMap *map, float *W, int64_t rows) {
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (!enc || rows < tc::kRows || (uintptr_t)W % 16 != 0) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)kF, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)kF * sizeof(float)};
+    const cuuint32_t box[2] = {32, (cuuint32_t)tc::kRows};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, W, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <bool SPLIT>
@@ -298,13 +367,17 @@ static int filter_fwd_launch(const FilterFwdParams &p, cudaStream_t st) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(filter_fwd_pipe_kernel<SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
+        if (cudaFuncSetAttribute(filter_fwd_pipe_kernel<SPLIT, kTcThreads>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess)
             return check_launch();
         configured[dev] = true;
     }
+    // rows written in order (no scatter to reverse edges): the copy engine stores the tiles
+    CUtensorMap wmap;
+    memset(&wmap, 0, sizeof(wmap));
+    const int use_map = !(p.sel && p.twin) && make_w_map(&wmap, p.W, p.E) ? 1 : 0;
     const int64_t ntiles = (p.E + tc::kRows - 1) / tc::kRows;
     const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
-    filter_fwd_pipe_kernel<SPLIT><<<grid, kTcThreads, L::kTotal, st>>>(p);
+    filter_fwd_pipe_kernel<SPLIT, kTcThreads><<<grid, kTcThreads, L::kTotal, st>>>(p, wmap, use_map);
     return check_launch();
 }
 

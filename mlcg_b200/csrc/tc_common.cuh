@@ -217,6 +217,48 @@ __device__ __forceinline__ void store_a_tmem(uint32_t ta_lane, int k0, const flo
     if (SPLIT) tmem_st16(ta_lane + 64 + (k0 >> 1), lo);
 }
 
+
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+        : "memory");
+}
+
+// N = 32 or 16 columns per thread
+template <int N> __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float (&v)[N]);
+template <> __device__ __forceinline__ void tmem_ld_cols<32>(uint32_t taddr, float (&v)[32]) { tmem_ld32(taddr, v); }
+template <> __device__ __forceinline__ void tmem_ld_cols<16>(uint32_t taddr, float (&v)[16]) { tmem_ld16(taddr, v); }
+
+// N fp32 values of one row (K range [k0, k0+N)) -> N/2 packed columns of the A operand in TMEM (hi block at ta, lo block 64
+// columns further)
+template <bool SPLIT, int N>
+__device__ __forceinline__ void store_a_tmem_cols(uint32_t ta_lane, int k0, const float (&x)[N], float scale) {
+    uint32_t hi[N / 2], lo[N / 2];
+#pragma unroll
+    for (int i = 0; i < N / 2; i++) {
+        const float a0 = x[2 * i] * scale, a1 = x[2 * i + 1] * scale;
+        if (SPLIT) {
+            const __half2 a = __floats2half2_rn(a0, a1);
+            const float2 b = __half22float2(a);
+            const __half2 c = __floats2half2_rn(a0 - b.x, a1 - b.y);
+            hi[i] = *reinterpret_cast<const uint32_t *>(&a);
+            lo[i] = *reinterpret_cast<const uint32_t *>(&c);
+        } else {
+            const __nv_bfloat162 a = __floats2bfloat162_rn(a0, a1);
+            hi[i] = *reinterpret_cast<const uint32_t *>(&a);
+            lo[i] = 0u;
+        }
+    }
+    if constexpr (N == 32) {
+        tmem_st16(ta_lane + (k0 >> 1), hi);
+        if (SPLIT) tmem_st16(ta_lane + 64 + (k0 >> 1), lo);
+    } else {
+        tmem_st8(ta_lane + (k0 >> 1), hi);
+        if (SPLIT) tmem_st8(ta_lane + 64 + (k0 >> 1), lo);
+    }
+}
+
 // GEMM with the A operand in tensor memory (hi at ta, lo at ta + 64 columns)
 template <bool SPLIT>
 __device__ __forceinline__ void issue_gemm_ts(uint32_t tmem_d, uint32_t ta, uint32_t b_hi, uint32_t b_lo, int ksteps, int b_mn, int n = 128) {
