@@ -451,14 +451,36 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
     phase ^= 1;                                   \
     tc_fence_after();
 
-    struct EdgeScalars { float t, dt, e0, e1; };
+    // per-row scalars: basis argument and its derivative, envelope of the basis and its derivative, CFConv cutoff C(d) and
+    // C'(d) (the envelope again when both use the same cutoff, as SchNet builds them)
+    const bool same_env = p.conv.cutoff_kind == p.rbf.cutoff_kind && p.conv.lower == p.rbf.lower && p.conv.upper == p.rbf.upper;
+    struct EdgeScalars { float t, dt, e0, e1, c0, c1; };
     auto scalars = [&](float de) {
         EdgeScalars s;
         edge_arg(de, p.rbf, s.t, s.dt);
         const Jet<float, 1> env = envelope_jet<float, 1>(de, p.rbf);
         s.e0 = env.c[0];
         s.e1 = env.c[1];
+        if (same_env) {
+            s.c0 = s.e0;
+            s.c1 = s.e1;
+        } else {
+            const Jet<float, 1> cj = envelope_jet<float, 1>(de, p.conv);
+            s.c0 = cj.c[0];
+            s.c1 = cj.c[1];
+        }
         return s;
+    };
+    // row of the tile -> edge and its two nodes (0 for rows past the end)
+    struct RowIdx { int64_t e; int32_t i0, i1; bool live; };
+    auto row_index = [&](int64_t tile) {
+        RowIdx x;
+        const int64_t krow = tile * kRows + r;
+        x.live = krow < p.E;
+        x.e = x.live ? (p.sel ? (int64_t)p.sel[krow] : krow) : 0;
+        x.i0 = x.live ? q.row0[x.e] : 0;
+        x.i1 = x.live ? q.row1[x.e] : 0;
+        return x;
     };
     auto basis_to_tmem = [&](const EdgeScalars &es) {
         if (col0 < Kpad1) {
@@ -479,22 +501,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
 
     const int64_t ntiles = (p.E + kRows - 1) / kRows;
     const int64_t first = blockIdx.x, step = gridDim.x;
-    float de = 1.f;
     EdgeScalars es{};
+    RowIdx ri{0, 0, 0, false};
+    const bool paired = p.sel && p.twin;          // one row per unordered pair: both directions' gW are summed
     if (first < ntiles) {
-        const int64_t k = first * kRows + r;
-        de = k < p.E ? p.d[p.sel ? (int64_t)p.sel[k] : k] : 1.f;
-        es = scalars(de);
+        ri = row_index(first);
+        es = scalars(ri.live ? p.d[ri.e] : 1.f);
         basis_to_tmem(es);
         ISSUE(T0, b1_hi, b1_lo, Kpad1 / 16, 0, 128)
     }
     for (int64_t tile = first; tile < ntiles; tile += step) {
-        const int64_t krow = tile * kRows + r;
-        const bool live = krow < p.E;
-        const int64_t e = live ? (p.sel ? (int64_t)p.sel[krow] : krow) : 0;
-        const bool paired = p.sel && p.twin;      // one row per unordered pair: both directions' gW are summed
-        const int64_t i0 = live ? q.row0[e] : 0, i1 = live ? q.row1[e] : 0;
-        const Jet<float, 1> cj = envelope_jet<float, 1>(de, p.conv);
+        const bool live = ri.live;
+        const int64_t e = ri.e;
+        const int64_t i0 = ri.i0, i1 = ri.i1;
 
         // ---- GEMM 1 done: h = tanh(z + b1) kept in T0 (fp32) and written as the A operand; issue Y = h A2^T
         AWAIT()
@@ -546,7 +565,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     gC = fmaf(gw[j], v[4 * w + j], gC);
-                    const float gy = gw[j] * cj.c[0];
+                    const float gy = gw[j] * es.c0;
                     g[4 * w + j] = gy;
                     rmax = fmaxf(rmax, fabsf(gy));
                 }
@@ -560,6 +579,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
         store_a_tmem<SPLIT>(tmem + TA + lane_off, col0, g, sc3);
         tmem_wait_st();
         ISSUE(T1, b2_hi, b2_lo, kF / 16, 1, 128)
+        // under GEMM 3: indices and per-row scalars of the next tile
+        const int64_t next = tile + step;
+        EdgeScalars es_next{};
+        RowIdx ri_next{0, 0, 0, false};
+        if (next < ntiles) {
+            ri_next = row_index(next);
+            es_next = scalars(ri_next.live ? p.d[ri_next.e] : 1.f);
+        }
         AWAIT()
 
         // ---- gz = gh (1 - h^2) -> A operand (row-scaled); issue GPHI = gz A1
@@ -598,16 +625,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
                 g[2 * j + 1] = ex2_fast(-wu1 * u1) * fmaf(m2, wu1, es.e1);
             }
         }
-        const float gC_dC = gC * cj.c[1], inv4 = 1.f / (sc4 * wscale);
-        // scalars of the next tile
-        const int64_t next = tile + step;
-        float de_next = 1.f;
-        EdgeScalars es_next{};
-        if (next < ntiles) {
-            const int64_t kn = next * kRows + r;
-            de_next = kn < p.E ? p.d[p.sel ? (int64_t)p.sel[kn] : kn] : 1.f;
-            es_next = scalars(de_next);
-        }
+        const float gC_dC = gC * es.c1, inv4 = 1.f / (sc4 * wscale);
         AWAIT()
         if (failed) s_err[0] = 1;
 
@@ -639,8 +657,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
             q.gd[e] = (s_red2[r] + s_red2[128 + r]) + (s_red2[256 + r] + s_red2[384 + r]);
             if (paired) q.gd[p.twin[e]] = 0.f;   // the pair's whole gradient is carried by one of its two edges
         }
-        de = de_next;
         es = es_next;
+        ri = ri_next;
     }
 #undef ISSUE
 #undef AWAIT
