@@ -11,12 +11,9 @@
 // Precision modes.  0: every fp32 value is carried as an fp16 pair (value = hi + lo, ~22 bits) and
 // each GEMM runs hi*hi + hi*lo + lo*hi with fp32 accumulation — the products an fp32 GEMM forms, at
 // half-precision tensor-core rate.  1: operands rounded to bf16, one product, tanh.approx.
-#include <cuda.h>
-
-#include <cstring>
-
 #include "rbf_device.cuh"
 #include "tc_common.cuh"
+#include "tensor_map.cuh"
 
 namespace mlcgb {
 
@@ -149,17 +146,6 @@ __device__ __forceinline__ float4 *stage_chunk(uint8_t *stage, int row, int chun
     return reinterpret_cast<float4 *>(stage + row * 512 + ((chunk ^ (row & 7)) << 4));
 }
 
-// One 32-column x 128-row box of the staging tile (128-byte swizzle) to rows [y, y+128) of the [rows][128] fp32 tensor
-// the map describes; rows past the end of the tensor are clipped by the copy engine.
-__device__ __forceinline__ void tensor_store_box(const CUtensorMap *map, int x, int y, const uint8_t *src_box) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x),
-                 "r"(y), "r"(tc::smem_u32(src_box))
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
 // ------------------------------------------------------------------------------------------------
 // Forward, pipelined: the A operands (phi, h) live in tensor memory instead of shared memory, which
 // leaves room for two tiles in flight.  TMEM columns: D1 [0,128) | D2 [128,256) | A of even tiles
@@ -238,12 +224,10 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
         float v[NC];
         tmem_ld_cols<NC>(t_lane + 128 + col0, v);
         if (use_map) {
-            uint8_t *box_row = stage + (col0 >> 5) * 16384 + r * 128;
             const int chunk0 = (col0 & 31) >> 2;
 #pragma unroll
             for (int q = 0; q < NC / 4; q++)
-                *reinterpret_cast<float4 *>(box_row + (((chunk0 + q) ^ (r & 7)) << 4)) =
-                    make_float4(v[4 * q] * C, v[4 * q + 1] * C, v[4 * q + 2] * C, v[4 * q + 3] * C);
+                *box_chunk(stage, col0 >> 5, r, chunk0 + q) = make_float4(v[4 * q] * C, v[4 * q + 1] * C, v[4 * q + 2] * C, v[4 * q + 3] * C);
             fence_async_smem();                                 // the copy engine reads the stage through the async proxy
             tc_fence_before();
             __syncthreads();
@@ -299,7 +283,7 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
             store_a_tmem_cols<SPLIT, NC>(ta + lane_off, col0, v, 1.f);
             tmem_wait_st();
         }
-        bulk_wait_read();                                        // the copies of (a) have read the stage
+        bulk_wait_read<0>();                                     // the copies of (a) have read the stage
         tc_fence_before();
         __syncthreads();                                         // also: every thread is done with the stage of (a)
         if (tid == 0) {
@@ -333,33 +317,6 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
     if (warp == 0) tmem_free(tmem, 512);
 }
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda)
-typedef CUresult (*TensorMapEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                      const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static TensorMapEncodeFn tensor_map_encoder() {
-    static TensorMapEncodeFn fn = [] {
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult res;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) != cudaSuccess || res != cudaDriverEntryPointSuccess)
-            ptr = nullptr;
-        return (TensorMapEncodeFn)ptr;
-    }();
-    return fn;
-}
-
-// Map of W[rows][128] fp32 for stores of 32-column x 128-row boxes in the 128-byte swizzle.
-static bool make_w_map(CUtensorMap *map, float *W, int64_t rows) {
-    TensorMapEncodeFn enc = tensor_map_encoder();
-    if (!enc || rows < tc::kRows || (uintptr_t)W % 16 != 0) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)kF, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)kF * sizeof(float)};
-    const cuuint32_t box[2] = {32, (cuuint32_t)tc::kRows};
-    const cuuint32_t estr[2] = {1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, W, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <bool SPLIT>
 static int filter_fwd_launch(const FilterFwdParams &p, cudaStream_t st) {
     using L = FilterSmem<SPLIT>;
@@ -373,8 +330,7 @@ static int filter_fwd_launch(const FilterFwdParams &p, cudaStream_t st) {
     }
     // rows written in order (no scatter to reverse edges): the copy engine stores the tiles
     CUtensorMap wmap;
-    memset(&wmap, 0, sizeof(wmap));
-    const int use_map = !(p.sel && p.twin) && make_w_map(&wmap, p.W, p.E) ? 1 : 0;
+    const int use_map = (make_rows_map(&wmap, p.W, p.E, kF) && !(p.sel && p.twin)) ? 1 : 0;
     const int64_t ntiles = (p.E + tc::kRows - 1) / tc::kRows;
     const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
     filter_fwd_pipe_kernel<SPLIT, kTcThreads><<<grid, kTcThreads, L::kTotal, st>>>(p, wmap, use_map);

@@ -10,6 +10,7 @@
 // Rows of A (NT/NN) are scaled by a power of two so that their largest magnitude sits in [8,16);
 // TN scales each 128-edge tile of A and of B by one power of two and accumulates the tiles in registers.
 #include "tc_common.cuh"
+#include "tensor_map.cuh"
 
 namespace mlcgb {
 
@@ -189,6 +190,128 @@ gemm_tc_rows_kernel(const float *__restrict__ A, const float *__restrict__ B, co
     if (warp == 0) tmem_free(tmem, 256);
 }
 
+// ------------------------------------------------------------------------------------------------ NT / NN, pipelined
+// Fast path of the two row-wise modes (K and N multiples of four, 16-byte aligned A and C, at least one full tile):
+//  * input tiles arrive in one shared-memory stage by cp.async (whole rows per warp); the copy of tile i+2 is issued
+//    as soon as tile i+1 has been read out of the stage;
+//  * two operand blocks and two accumulators in tensor memory: the conversion of tile i+1 (row scale, fp16 hi/lo, store
+//    to TMEM) and its MMAs are issued before the epilogue of tile i, so the tensor core works under both;
+//  * the output tile goes to a second stage (32-column boxes, 128-byte swizzle) and leaves through tensor stores that
+//    drain while the next tile is processed.
+template <int MODE>   // 0 NT, 1 NN
+__global__ void __launch_bounds__(kGT, 1)
+gemm_tc_rows_pipe_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int64_t E, int N, int K,
+                         const __grid_constant__ CUtensorMap cmap, int32_t *__restrict__ status) {
+    using namespace tc;
+    using L = GemmTcSmem;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *sB_hi = smem + L::kB, *sB_lo = sB_hi + 32768;
+    uint8_t *s_in = smem + L::kStageA, *s_out = smem + L::kStageB;
+    float *s_red = reinterpret_cast<float *>(smem + L::kMisc);
+    float *s_bias = s_red + 512;
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_bias + 128);   // two barriers, one per accumulator
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(s_bar + 2);
+    int *s_err = reinterpret_cast<int *>(s_tmem + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int r = tid & 127, qt = tid >> 7, col0 = qt * 32;
+    constexpr float kWS = 64.f;
+    const int64_t ntiles = (E + kRows - 1) / kRows;
+    const int64_t step = gridDim.x, t0 = blockIdx.x;
+    if (t0 < ntiles) prefetch_tile_to_stage(s_in, A, t0 * kRows, E, K);      // under the set-up below
+    const int wrows = MODE == 0 ? N : K, wcols = MODE == 0 ? K : N;
+    const int wpad = wcols <= 64 ? 64 : 128;
+    load_weight_tile<true>(sB_hi, sB_lo, B, wrows, wcols, wpad, kWS);
+    if (tid < 128) s_bias[tid] = (bias && tid < N) ? bias[tid] : 0.f;
+    const uint32_t bar0 = smem_u32(s_bar);
+    if (tid == 0) {
+        mbar_init(bar0, 1);
+        mbar_init(bar0 + 8, 1);
+        *s_err = 0;
+    }
+    __syncwarp();
+    if (warp == 0) tmem_alloc(smem_u32(s_tmem), 512);
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;                 // accumulators at columns [0,128) [128,256), operands at [256,384) [384,512)
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const int ksteps = MODE == 0 ? wpad / 16 : (K + 15) / 16;
+    const int nmma = MODE == 0 ? 128 : wpad;
+    const uint32_t b_hi = smem_u32(sB_hi), b_lo = smem_u32(sB_lo);
+    uint32_t phase_bits = 0;          // bit b: parity the next wait on barrier b looks for
+
+    // the tile that has landed in the input stage: row scale, operand store, MMAs into accumulator `buf`; then the copy of
+    // tile `following` (if any) into the stage.  Returns the row's scale.
+    auto convert_issue = [&](int buf, int64_t following) {
+        wait_prefetch();
+        __syncthreads();
+        float x[32];
+        float rmax = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const float4 v = *gstage(s_in, r, (col0 >> 2) + w);
+            x[4 * w] = v.x; x[4 * w + 1] = v.y; x[4 * w + 2] = v.z; x[4 * w + 3] = v.w;
+            rmax = fmaxf(fmaxf(rmax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+        }
+        s_red[qt * 128 + r] = rmax;
+        __syncthreads();                            // also: everybody has read the stage
+        if (following < ntiles) prefetch_tile_to_stage(s_in, A, following * kRows, E, K);
+        const float sc = row_scale(fmaxf(fmaxf(s_red[r], s_red[128 + r]), fmaxf(s_red[256 + r], s_red[384 + r])));
+        const uint32_t ta = tmem + 256 + buf * 128;
+        if (col0 < ksteps * 16) store_a_tmem<true>(ta + lane_off, col0, x, sc);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            issue_gemm_ts<true>(tmem + buf * 128, ta, b_hi, b_lo, ksteps, MODE, nmma);
+            mma_commit(bar0 + 8 * buf);
+        }
+        return sc;
+    };
+
+    float sc_cur = 1.f;
+    if (t0 < ntiles) sc_cur = convert_issue(0, t0 + step);
+    int buf = 0;
+    const int nboxes = (N + 31) >> 5;
+    for (int64_t tile = t0; tile < ntiles; tile += step, buf ^= 1) {
+        float sc_next = 1.f;
+        if (tile + step < ntiles) sc_next = convert_issue(buf ^ 1, tile + 2 * step);
+        if (!mbar_wait(bar0 + 8 * buf, (phase_bits >> buf) & 1u)) *s_err = 1;
+        phase_bits ^= 1u << buf;
+        tc_fence_after();
+        if (tid == 0) bulk_wait_read<0>();          // the stores of the previous tile have read the output stage
+        __syncthreads();
+        if (col0 < nmma) {
+            float v[32];
+            tmem_ld32(tmem + buf * 128 + lane_off + col0, v);
+            const float inv = 1.f / (sc_cur * kWS);
+#pragma unroll
+            for (int w = 0; w < 8; w++)
+                *box_chunk(s_out, qt, r, w) = make_float4(fmaf(v[4 * w], inv, s_bias[col0 + 4 * w]), fmaf(v[4 * w + 1], inv, s_bias[col0 + 4 * w + 1]),
+                                                          fmaf(v[4 * w + 2], inv, s_bias[col0 + 4 * w + 2]), fmaf(v[4 * w + 3], inv, s_bias[col0 + 4 * w + 3]));
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();
+        if (*s_err) break;
+        if (tid == 0) {
+            for (int b = 0; b < nboxes; b++) tensor_store_box(&cmap, 32 * b, (int)(tile * kRows), s_out + b * 16384);
+            bulk_commit();
+        }
+        sc_cur = sc_next;
+    }
+    wait_prefetch();
+    bulk_wait_all();
+    tc_fence_before();
+    __syncthreads();
+    if (*s_err && tid == 0) atomicOr(status, 8);
+    if (warp == 0) tmem_free(tmem, 512);
+}
+
 // ------------------------------------------------------------------------------------------------ TN
 __device__ __forceinline__ float block_max_512(float v, float *s_red) {
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
@@ -354,6 +477,18 @@ int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int6
     if (mode == 0 || mode == 1) {
         const int64_t ntiles = (M + tc::kRows - 1) / tc::kRows;
         const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
+        CUtensorMap cmap;
+        if ((K & 3) == 0 && ((uintptr_t)A & 15) == 0 && make_rows_map(&cmap, (float *)C, M, N)) {   // pipelined fast path
+            static bool p0[64] = {false}, p1[64] = {false};
+            if (mode == 0) {
+                if (int rc = set_smem(gemm_tc_rows_pipe_kernel<0>, p0)) return rc;
+                gemm_tc_rows_pipe_kernel<0><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, (const float *)bias, M, (int)N, (int)K, cmap, status);
+            } else {
+                if (int rc = set_smem(gemm_tc_rows_pipe_kernel<1>, p1)) return rc;
+                gemm_tc_rows_pipe_kernel<1><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, nullptr, M, (int)N, (int)K, cmap, status);
+            }
+            return check_launch();
+        }
         if (mode == 0) {
             if (int rc = set_smem(gemm_tc_rows_kernel<0>, c0)) return rc;
             gemm_tc_rows_kernel<0><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, (const float *)bias, M, (int)N, (int)K, (float *)C, status);

@@ -147,20 +147,52 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
 }
 
 // Fill a [128][Kpad] weight tile (and its low part) from a row-major fp32 matrix src[rows][K], scaled by `scale`.
+// Four consecutive K elements of a row are 8 contiguous bytes of the swizzled tile, so with K % 4 == 0 and a 16-byte
+// aligned source every thread moves float4 -> 8 bytes, with all its loads issued before the first conversion.
 template <bool SPLIT>
 __device__ __forceinline__ void load_weight_tile(uint8_t *hi, uint8_t *lo, const float *__restrict__ src, int rows, int K, int Kpad,
                                                  float scale) {
-    for (int idx = threadIdx.x; idx < kRows * Kpad; idx += blockDim.x) {
-        const int n = idx / Kpad, k = idx - n * Kpad;
-        const float w = (n < rows && k < K) ? src[(int64_t)n * K + k] * scale : 0.f;
+    auto put4 = [&](int n, int k, float4 w) {
         const uint32_t off = elem_offset(n, k);
         if (SPLIT) {
-            const __half a = __float2half_rn(w);
-            *reinterpret_cast<__half *>(hi + off) = a;
-            *reinterpret_cast<__half *>(lo + off) = __float2half_rn(w - __half2float(a));
+            const __half2 a0 = __floats2half2_rn(w.x * scale, w.y * scale), a1 = __floats2half2_rn(w.z * scale, w.w * scale);
+            const float2 f0 = __half22float2(a0), f1 = __half22float2(a1);
+            const __half2 c0 = __floats2half2_rn(w.x * scale - f0.x, w.y * scale - f0.y), c1 = __floats2half2_rn(w.z * scale - f1.x, w.w * scale - f1.y);
+            *reinterpret_cast<uint2 *>(hi + off) = make_uint2(*reinterpret_cast<const uint32_t *>(&a0), *reinterpret_cast<const uint32_t *>(&a1));
+            *reinterpret_cast<uint2 *>(lo + off) = make_uint2(*reinterpret_cast<const uint32_t *>(&c0), *reinterpret_cast<const uint32_t *>(&c1));
         } else {
-            *reinterpret_cast<__nv_bfloat16 *>(hi + off) = __float2bfloat16_rn(w);
+            const __nv_bfloat162 a0 = __floats2bfloat162_rn(w.x * scale, w.y * scale), a1 = __floats2bfloat162_rn(w.z * scale, w.w * scale);
+            *reinterpret_cast<uint2 *>(hi + off) = make_uint2(*reinterpret_cast<const uint32_t *>(&a0), *reinterpret_cast<const uint32_t *>(&a1));
         }
+    };
+    const int qpr = Kpad >> 2, nquads = kRows * qpr;          // quads per row, quads in the tile
+    if ((K & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        constexpr int kBatch = 8;
+        for (int base = threadIdx.x; base < nquads; base += kBatch * blockDim.x) {
+            float4 w[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; u++) {
+                const int qd = base + u * blockDim.x;
+                const int n = qd / qpr, k = (qd - n * qpr) << 2;
+                w[u] = (qd < nquads && n < rows && k < K) ? __ldg(reinterpret_cast<const float4 *>(src + (int64_t)n * K + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; u++) {
+                const int qd = base + u * blockDim.x;
+                if (qd < nquads) {
+                    const int n = qd / qpr;
+                    put4(n, (qd - n * qpr) << 2, w[u]);
+                }
+            }
+        }
+        return;
+    }
+    for (int qd = threadIdx.x; qd < nquads; qd += blockDim.x) {
+        const int n = qd / qpr, k = (qd - n * qpr) << 2;
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) v[j] = (n < rows && k + j < K) ? src[(int64_t)n * K + k + j] : 0.f;
+        put4(n, k, make_float4(v[0], v[1], v[2], v[3]));
     }
 }
 
