@@ -178,6 +178,16 @@ size_t mlcgb_gemm_tc_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K);
 int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int64_t M, int64_t N, int64_t K, void *C,
                   void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
 
+/* Modes 0 and 1 of the above with the elementwise step that follows the Linear layer in an interaction block fused into
+ * the store of C (src/mlcg/nn/schnet.py:252-262: activation after CFConv, Linear, and the residual sum at
+ * schnet.py:150; their derivatives in the force pass).  `epilogue`:
+ *   0  C = A op(B) + bias                      1  C = tanh(A op(B) + bias)
+ *   2  C = A op(B) + bias + aux                3  C = (A op(B) + bias) * (1 - aux^2)      (aux = tanh output)
+ * `aux` is [M,N] like C (NULL for 0 and 1); C may alias aux.  Needs M >= 128, N and K multiples of four and 16-byte aligned
+ * A, C and aux; MLCGB_E_LIMIT otherwise (use mlcgb_gemm_tc and separate elementwise steps). */
+int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias, const void *aux, int epilogue, int64_t M,
+                        int64_t N, int64_t K, void *C, int32_t *status, void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Fused filter network on the tensor cores (tcgen05 / TMEM):
  *   W[e,:] = ( tanh( phi(d_e) A1^T + b1 ) A2^T ) * C(d_e)

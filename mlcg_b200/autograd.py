@@ -355,3 +355,49 @@ class FusedFilterConv(torch.autograd.Function):
                                             xl, g, ctx.precision, sel, plan.perm_in if sel is not None else None)
             be.defer_status(status, "fused filter network (backward)")
         return gxl, gd, None, None, None, None, None, None, None
+
+
+class FusedInteraction(torch.autograd.Function):
+    """One interaction block with its residual sum, eval mode (schnet.py:150, 252-262, 340-350):
+
+        x_new = x + lin( tanh( lin2( CFConv_aggregate( lin1(x), W(d) ) ) ) )
+
+    Ten kernel launches forward and backward together and no elementwise kernel: the activation, its derivative and
+    both residual sums are epilogues of the tensor-core GEMMs.  First-order only, weights are constants."""
+
+    @staticmethod
+    def forward(ctx, x, d, W1, fA1, fb1, fA2, W2, b2, W3, b3, plan: EdgePlan, spec: RbfSpec, conv_cut, precision: int):
+        be = get_backend()
+        x = x.contiguous()
+        xl = be.gemm(0, x, W1)
+        sel = plan.half_selection()
+        W, status = be.filter_forward(d, spec, conv_cut[0], conv_cut[1], conv_cut[2], fA1, fb1, fA2, precision, sel, None)
+        be.defer_status(status, "fused filter network (forward)")
+        if sel is not None:
+            agg = be.seg_mul_sum(xl, W, plan.ptr_out, plan.nbr_out, plan.pair_index(), plan.N)
+        else:
+            agg = be.seg_mul_sum(xl, W, plan.ptr_in, plan.nbr_in, plan.perm_in, plan.N)
+        a = be.gemm_fused(0, agg, W2, b2, None, be.EPI_TANH)
+        out = be.gemm_fused(0, a, W3, b3, x, be.EPI_ADD)
+        ctx.plan, ctx.spec, ctx.conv_cut, ctx.precision = plan, spec, conv_cut, precision
+        ctx.save_for_backward(xl, d, W, a, W1, fA1, fb1, fA2, W2, W3)
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        xl, d, W, a, W1, fA1, fb1, fA2, W2, W3 = ctx.saved_tensors
+        plan, be = ctx.plan, get_backend()
+        g = g.contiguous()
+        gy = be.gemm_fused(1, g, W3, None, a, be.EPI_TANH_GRAD)        # through lin and the activation
+        gagg = be.gemm(1, gy, W2)
+        sel = plan.half_selection()
+        gx = gd = None
+        if ctx.needs_input_grad[0]:
+            gxl = be.seg_mul_sum(gagg, W, plan.ptr_out, plan.nbr_out, plan.pair_index() if sel is not None else plan.perm_out, plan.N)
+            gx = be.gemm_fused(1, gxl, W1, None, g, be.EPI_ADD)        # through lin1, plus the residual branch
+        if ctx.needs_input_grad[1]:
+            gd, status = be.filter_backward(d, ctx.spec, ctx.conv_cut[0], ctx.conv_cut[1], ctx.conv_cut[2], fA1, fb1, fA2, plan.row0, plan.row1,
+                                            xl, gagg, ctx.precision, sel, plan.perm_in if sel is not None else None)
+            be.defer_status(status, "fused filter network (backward)")
+        return (gx, gd) + (None,) * 12

@@ -343,6 +343,35 @@ class CudaBackend:
             self._run("gemm", self.lib.mlcgb_gemm, (mode, _ptr(A), _ptr(B), _ptr(bias), dt, M, N, K, _ptr(C), _ptr(ws), wsb, _stream(),), **self._work("gemm", locals()))
         return C
 
+    EPI_NONE, EPI_TANH, EPI_ADD, EPI_TANH_GRAD = 0, 1, 2, 3
+
+    def gemm_fused_ok(self, mode: int, A, B) -> bool:
+        """Whether :meth:`gemm_fused` takes these operands (float32, >= 128 rows, widths multiples of four and <= 128)."""
+        if not (self.tensor_core_gemm and A.is_cuda and A.dtype == torch.float32 and A.dim() == 2 and B.dim() == 2):
+            return False
+        M, K = A.shape
+        N = B.shape[0] if mode == 0 else B.shape[1]
+        return M >= 128 and K % 4 == 0 and N % 4 == 0 and bool(self.lib.mlcgb_gemm_tc_supported(mode, M, N, K))
+
+    def gemm_fused(self, mode: int, A, B, bias=None, aux=None, epilogue: int = 0):
+        """Row-wise tensor-core GEMM (mode 0: A B^T + bias, mode 1: A B) with the elementwise step that follows it:
+        1 tanh, 2 ``+ aux``, 3 ``* (1 - aux**2)``."""
+        _need_cuda(A, B, bias, aux)
+        A, B = A.contiguous(), B.detach().contiguous()
+        M, K = A.shape
+        N = B.shape[0] if mode == 0 else B.shape[1]
+        C = torch.empty((M, N), dtype=A.dtype, device=A.device)
+        if bias is not None:
+            bias = bias.detach().contiguous()
+        if aux is not None:
+            aux = aux.contiguous()
+        status = self._sticky_status(A.device)
+        with torch.cuda.device(A.device):
+            self._run("gemm_tc", self.lib.mlcgb_gemm_tc_fused, (mode, _ptr(A), _ptr(B), _ptr(bias), _ptr(aux), int(epilogue), M, N, K, _ptr(C), _ptr(status), _stream()),
+                      nbytes=(M * K + N * K + M * N * (2 if aux is not None else 1)) * 4, flops=2 * M * N * K)
+        self.defer_status(status, "tensor-core GEMM")
+        return C
+
     # ------------------------------------------------------------------ fused filter network (tensor cores)
     def filter_forward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, precision=0, sel=None, twin=None):
         """W[E,F] = (tanh(phi(d) A1^T + b1) A2^T) * C(d); float32, F = 128, R <= 128.

@@ -72,6 +72,23 @@ __device__ __forceinline__ void prefetch_tile_to_stage(uint8_t *stage, const flo
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
+// rows [row0, row0+128) of a row-major [nrows_total, ncols] fp32 matrix (ncols a multiple of four) -> 32-column boxes in
+// the 128-byte swizzle, asynchronously; whole rows are read by consecutive lanes
+__device__ __forceinline__ void prefetch_tile_to_boxes(uint8_t *stage, const float *__restrict__ src, int64_t row0, int64_t nrows_total,
+                                                       int ncols) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int row = warp * 8 + i;
+        const int64_t gr = row0 + row;
+        const bool ok = gr < nrows_total && lane * 4 < ncols;
+        const float *g = ok ? src + gr * ncols + lane * 4 : src;
+        const uint32_t dst = tc::smem_u32(box_chunk(stage, lane >> 3, row, lane & 7));
+        const int nbytes = ok ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(g), "r"(nbytes) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
 __device__ __forceinline__ void wait_prefetch() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------------------------ NT / NN
@@ -198,10 +215,13 @@ gemm_tc_rows_kernel(const float *__restrict__ A, const float *__restrict__ B, co
 //    to TMEM) and its MMAs are issued before the epilogue of tile i, so the tensor core works under both;
 //  * the output tile goes to a second stage (32-column boxes, 128-byte swizzle) and leaves through tensor stores that
 //    drain while the next tile is processed.
+// Epilogues (EPI): 0 none; 1 tanh; 2 + aux; 3 * (1 - aux^2), the derivative of tanh given its output.  `aux` is a matrix
+// shaped like C; its tile is copied into the output stage while the next tile is converted and combined there.
+enum { kEpiNone = 0, kEpiTanh = 1, kEpiAdd = 2, kEpiTanhGrad = 3 };
 template <int MODE>   // 0 NT, 1 NN
 __global__ void __launch_bounds__(kGT, 1)
 gemm_tc_rows_pipe_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int64_t E, int N, int K,
-                         const __grid_constant__ CUtensorMap cmap, int32_t *__restrict__ status) {
+                         const float *__restrict__ aux, int epi, const __grid_constant__ CUtensorMap cmap, int32_t *__restrict__ status) {
     using namespace tc;
     using L = GemmTcSmem;
     extern __shared__ uint8_t smem_raw[];
@@ -279,20 +299,39 @@ gemm_tc_rows_pipe_kernel(const float *__restrict__ A, const float *__restrict__ 
     const int nboxes = (N + 31) >> 5;
     for (int64_t tile = t0; tile < ntiles; tile += step, buf ^= 1) {
         float sc_next = 1.f;
+        const bool with_aux = epi == kEpiAdd || epi == kEpiTanhGrad;
+        if (with_aux) {                             // the aux tile travels to the output stage under the conversion below
+            if (tid == 0) bulk_wait_read<0>();      // the stores of the previous tile have read the output stage
+            __syncthreads();
+            prefetch_tile_to_boxes(s_out, aux, tile * kRows, E, N);
+        }
         if (tile + step < ntiles) sc_next = convert_issue(buf ^ 1, tile + 2 * step);
         if (!mbar_wait(bar0 + 8 * buf, (phase_bits >> buf) & 1u)) *s_err = 1;
         phase_bits ^= 1u << buf;
         tc_fence_after();
-        if (tid == 0) bulk_wait_read<0>();          // the stores of the previous tile have read the output stage
+        if (with_aux) wait_prefetch();              // (also waits for the input tile just requested)
+        else if (tid == 0) bulk_wait_read<0>();
         __syncthreads();
         if (col0 < nmma) {
             float v[32];
             tmem_ld32(tmem + buf * 128 + lane_off + col0, v);
             const float inv = 1.f / (sc_cur * kWS);
 #pragma unroll
-            for (int w = 0; w < 8; w++)
-                *box_chunk(s_out, qt, r, w) = make_float4(fmaf(v[4 * w], inv, s_bias[col0 + 4 * w]), fmaf(v[4 * w + 1], inv, s_bias[col0 + 4 * w + 1]),
-                                                          fmaf(v[4 * w + 2], inv, s_bias[col0 + 4 * w + 2]), fmaf(v[4 * w + 3], inv, s_bias[col0 + 4 * w + 3]));
+            for (int w = 0; w < 8; w++) {
+                float4 o = make_float4(fmaf(v[4 * w], inv, s_bias[col0 + 4 * w]), fmaf(v[4 * w + 1], inv, s_bias[col0 + 4 * w + 1]),
+                                       fmaf(v[4 * w + 2], inv, s_bias[col0 + 4 * w + 2]), fmaf(v[4 * w + 3], inv, s_bias[col0 + 4 * w + 3]));
+                float4 *slot = box_chunk(s_out, qt, r, w);
+                if (epi == kEpiTanh) {
+                    o = make_float4(tanh_ex2(o.x), tanh_ex2(o.y), tanh_ex2(o.z), tanh_ex2(o.w));
+                } else if (epi == kEpiAdd) {
+                    const float4 a4 = *slot;
+                    o = make_float4(o.x + a4.x, o.y + a4.y, o.z + a4.z, o.w + a4.w);
+                } else if (epi == kEpiTanhGrad) {
+                    const float4 a4 = *slot;
+                    o = make_float4(o.x * fmaf(-a4.x, a4.x, 1.f), o.y * fmaf(-a4.y, a4.y, 1.f), o.z * fmaf(-a4.z, a4.z, 1.f), o.w * fmaf(-a4.w, a4.w, 1.f));
+                }
+                *slot = o;
+            }
         }
         fence_async_smem();
         tc_fence_before();
@@ -450,11 +489,42 @@ static int set_smem(Kern kern, bool *done) {
     return MLCGB_OK;
 }
 
+// Pipelined row-wise kernel; MLCGB_E_LIMIT when its conditions on shape and alignment do not hold.
+static int rows_pipe_launch(int mode, const void *A, const void *B, const void *bias, const void *aux, int epi, int64_t M, int64_t N, int64_t K,
+                            void *C, int32_t *status, cudaStream_t st) {
+    CUtensorMap cmap;
+    if ((K & 3) != 0 || ((uintptr_t)A & 15) != 0 || (aux && ((uintptr_t)aux & 15) != 0) || !make_rows_map(&cmap, (float *)C, M, N)) return MLCGB_E_LIMIT;
+    const int64_t ntiles = (M + tc::kRows - 1) / tc::kRows;
+    const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
+    static bool p0[64] = {false}, p1[64] = {false};
+    if (mode == 0) {
+        if (int rc = set_smem(gemm_tc_rows_pipe_kernel<0>, p0)) return rc;
+        gemm_tc_rows_pipe_kernel<0><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, (const float *)bias, M, (int)N, (int)K,
+                                                                           (const float *)aux, epi, cmap, status);
+    } else {
+        if (int rc = set_smem(gemm_tc_rows_pipe_kernel<1>, p1)) return rc;
+        gemm_tc_rows_pipe_kernel<1><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, (const float *)bias, M, (int)N, (int)K,
+                                                                           (const float *)aux, epi, cmap, status);
+    }
+    return check_launch();
+}
+
 }  // namespace mlcgb
 
 using namespace mlcgb;
 
 extern "C" {
+
+int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias, const void *aux, int epilogue, int64_t M, int64_t N,
+                        int64_t K, void *C, int32_t *status, void *stream) {
+    if ((mode != 0 && mode != 1) || epilogue < 0 || epilogue > 3 || !status) return MLCGB_E_ARG;
+    if ((epilogue == kEpiAdd || epilogue == kEpiTanhGrad) && !aux) return MLCGB_E_ARG;
+    if (!mlcgb_gemm_tc_supported(mode, M, N, K)) return MLCGB_E_LIMIT;
+    if (M == 0) return MLCGB_OK;
+    if (!A || !B || !C) return MLCGB_E_ARG;
+    return rows_pipe_launch(mode, A, B, bias, aux, epilogue, M, N, K, C, status, (cudaStream_t)stream);
+}
+
 
 int mlcgb_gemm_tc_supported(int mode, int64_t M, int64_t N, int64_t K) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -477,18 +547,8 @@ int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int6
     if (mode == 0 || mode == 1) {
         const int64_t ntiles = (M + tc::kRows - 1) / tc::kRows;
         const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
-        CUtensorMap cmap;
-        if ((K & 3) == 0 && ((uintptr_t)A & 15) == 0 && make_rows_map(&cmap, (float *)C, M, N)) {   // pipelined fast path
-            static bool p0[64] = {false}, p1[64] = {false};
-            if (mode == 0) {
-                if (int rc = set_smem(gemm_tc_rows_pipe_kernel<0>, p0)) return rc;
-                gemm_tc_rows_pipe_kernel<0><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, (const float *)bias, M, (int)N, (int)K, cmap, status);
-            } else {
-                if (int rc = set_smem(gemm_tc_rows_pipe_kernel<1>, p1)) return rc;
-                gemm_tc_rows_pipe_kernel<1><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, nullptr, M, (int)N, (int)K, cmap, status);
-            }
-            return check_launch();
-        }
+        const int rc = rows_pipe_launch(mode, A, B, bias, nullptr, kEpiNone, M, N, K, C, status, st);
+        if (rc != MLCGB_E_LIMIT) return rc;            // else: shapes or alignment the pipelined kernel does not take
         if (mode == 0) {
             if (int rc = set_smem(gemm_tc_rows_kernel<0>, c0)) return rc;
             gemm_tc_rows_kernel<0><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, (const float *)bias, M, (int)N, (int)K, (float *)C, status);

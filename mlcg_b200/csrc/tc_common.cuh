@@ -307,6 +307,16 @@ __device__ __forceinline__ void issue_gemm_ts(uint32_t tmem_d, uint32_t ta, uint
     }
 }
 
+// tanh through exp2: tanh z = sign(z) (1 - 2 / (2^{2 log2(e) |z|} + 1)); 2^x overflowing to inf gives exactly 1.
+// Two special-function operations, about 1e-6 relative accuracy.
+__device__ __forceinline__ float tanh_ex2(float z) {
+    const float zz = z * 2.8853900817779268f;
+    float t, rr;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fabsf(zz)));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rr) : "f"(t + 1.f));
+    return copysignf(fmaf(-2.f, rr, 1.f), zz);
+}
+
 // Power-of-two factor that brings a row whose largest magnitude is `rmax` to [8, 16): exact to apply and to
 // undo, keeps fp16 operands far from overflow and their low parts out of the subnormal range.
 __device__ __forceinline__ float row_scale(float rmax) {

@@ -8,7 +8,7 @@ from typing import Final, List
 
 import torch
 
-from ..autograd import EdgeDistanceOnce, FusedFilterConv, SegIn, SegmentSum, edge_distances, plan_of
+from ..autograd import EdgeDistanceOnce, FusedFilterConv, FusedInteraction, SegIn, SegmentSum, edge_distances, plan_of
 from ..backend import get_backend
 from ..data import ENERGY_KEY
 from ..neighbor_list import atomic_data2neighbor_list, validate_neighborlist
@@ -125,6 +125,26 @@ class InteractionBlock(torch.nn.Module):
     def forward(self, x, edge_index, edge_weight, edge_attr, *args):
         return node_linear(self.lin, self.activation(self.conv(x, edge_index, edge_weight, edge_attr)), self.training)
 
+    def forward_residual(self, x, edge_index, edge_weight, edge_attr, *args):
+        """``x + self(x, ...)`` (the sum at schnet.py:150).  In eval mode, when the block has the standard layout — a CFConv the
+        fused filter kernel covers, tanh, 128-wide Linear layers — the whole expression runs as one autograd node whose GEMMs
+        carry the activation and the sums as epilogues."""
+        conv = self.conv
+        if (not self.training and type(conv) is CFConv and isinstance(edge_attr, LazyRadialBasis) and isinstance(self.activation, torch.nn.Tanh)
+                and x.dtype == torch.float32 and x.is_cuda and conv.lin1.bias is None and conv.lin2.bias is not None and self.lin.bias is not None):
+            plan = plan_of(edge_index, x.shape[0])
+            fused = conv.fused_spec(edge_attr.rbf_layer) if edge_attr.symmetric == plan.symmetric else None
+            be = get_backend()
+            if (fused is not None and be.gemm_fused_ok(0, x, conv.lin1.weight) and conv.lin1.out_features == 128
+                    and be.gemm_fused_ok(0, x, self.lin.weight) and conv.lin2.in_features == 128 and conv.lin2.out_features == self.lin.in_features
+                    and self.lin.out_features == x.shape[1] and conv.lin2.out_features % 4 == 0 and conv.lin2.out_features <= 128):
+                net = conv.filter_network.layers
+                return FusedInteraction.apply(x, edge_weight, conv.lin1.weight.detach(), net[0].weight.detach(), net[0].bias.detach(),
+                                              net[2].weight.detach(), conv.lin2.weight.detach(), conv.lin2.bias.detach(),
+                                              self.lin.weight.detach(), self.lin.bias.detach(), plan, fused[0], fused[1],
+                                              FILTER_PRECISIONS[conv.filter_precision])
+        return x + self(x, edge_index, edge_weight, edge_attr, *args)
+
 
 class SchNet(torch.nn.Module):
     """schnet.py:32-192.  ``forward(data)`` fills ``data.out["SchNet"]["energy"]`` with one energy per structure."""
@@ -203,7 +223,10 @@ class SchNet(torch.nn.Module):
             rbf_expansion = _tag_symmetric(self.rbf_layer(distances), plan.symmetric)
         num_batch = None
         for block in self.interaction_blocks:
-            x = x + block(x, edge_index, distances, rbf_expansion, num_batch, data.batch)
+            if type(block) is InteractionBlock:
+                x = block.forward_residual(x, edge_index, distances, rbf_expansion, num_batch, data.batch)
+            else:
+                x = x + block(x, edge_index, distances, rbf_expansion, num_batch, data.batch)
         energy = self.output_network(x, data)
         energy = SegmentSum.apply(energy, self._structure_ptr(data), data.batch).flatten()
         data.out[self.name] = {ENERGY_KEY: energy}

@@ -204,3 +204,27 @@ def test_tensor_core_gemm_matches_float64(M, N, K, heavy_tail):
         assert rel(be.gemm(0, X.to(DEV), W.to(DEV), b.to(DEV)), want) < 5e-6
     finally:
         be.tensor_core_gemm = True
+
+
+@pytest.mark.parametrize("M,N,K", [(1000, 128, 128), (128, 128, 128), (5003, 64, 128), (700, 128, 64)])
+def test_tensor_core_gemm_fused_epilogues(M, N, K):
+    """The epilogues of the pipelined row-wise GEMM (tanh, + aux, * (1 - aux^2)) against float64, both operand layouts."""
+    gen = torch.Generator().manual_seed(M + N + K)
+    be = get_backend()
+    X = torch.randn(M, K, generator=gen)
+    W = torch.randn(N, K, generator=gen) * 0.1          # mode 0: X W^T
+    V = torch.randn(K, N, generator=gen) * 0.1          # mode 1: X V
+    b = torch.randn(N, generator=gen) * 0.5
+    aux = torch.tanh(torch.randn(M, N, generator=gen))
+    assert be.gemm_fused_ok(0, X.to(DEV), W.to(DEV)) and be.gemm_fused_ok(1, X.to(DEV), V.to(DEV))
+    lin0 = X.double() @ W.double().t() + b.double()
+    lin1 = X.double() @ V.double()
+    a64 = aux.double()
+    cases = [(0, W, b, None, be.EPI_NONE, lin0), (0, W, b, None, be.EPI_TANH, torch.tanh(lin0)), (0, W, b, aux, be.EPI_ADD, lin0 + a64),
+             (0, W, b, aux, be.EPI_TANH_GRAD, lin0 * (1 - a64 * a64)), (1, V, None, None, be.EPI_NONE, lin1),
+             (1, V, None, aux, be.EPI_ADD, lin1 + a64), (1, V, None, aux, be.EPI_TANH_GRAD, lin1 * (1 - a64 * a64))]
+    for mode, B, bias, ax, epi, want in cases:
+        got = be.gemm_fused(mode, X.to(DEV), B.to(DEV), None if bias is None else bias.to(DEV), None if ax is None else ax.to(DEV), epi)
+        err = float((got.cpu().double() - want).abs().max())
+        assert err < 5e-6 * max(1.0, float(want.abs().max())), (mode, epi, err)
+    get_backend().check_pending()
