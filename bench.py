@@ -329,18 +329,19 @@ def run_ours(args):
             b.record()
             pairs.append((a, b))
         barrier()
-        return sum(a.elapsed_time(b) for a, b in pairs)
+        return [a.elapsed_time(b) for a, b in pairs]
 
     clocks = ClockSampler(local)
     clocks.start()
     barrier()
-    ms_total = timed_steps()
+    step_ms = timed_steps()
+    ms_total = sum(step_ms)
     # ---- the same K steps once more with a CUDA-event pair around every launch of the library (the per-kernel
     # durations behind `roofline` and `kernels`); kept out of the region above because ~170 event records per step
     # cost the host about as much as the launches themselves
     prof = KernelProfiler()
     be.profiler = prof
-    ms_profiled = timed_steps()
+    ms_profiled = sum(timed_steps())
     stats = prof.summary()
     be.profiler = None
     clk = clocks.stop()
@@ -391,10 +392,16 @@ def run_ours(args):
     seg = stats.get("seg_mul_sum")
     cfconv = None
     if seg and seg["ms"] > 0:
-        gbs = seg["bytes"] / seg["ms"] / 1e6
+        # algorithmic bytes of the CFConv aggregation per edge: the filter row (4F), the [2,E] int64 indices (16) and the node
+        # tensors read and written once (8F N/E); what the kernel really moves is less, because it reads one filter row per
+        # unordered pair and int32 indices (`unique_GBps`)
+        F, n_nodes = WORKLOAD["filters"], B * n
+        per_edge = 4 * F + 16 + 8 * F * n_nodes / n_edges
+        edges_per_s = seg["calls"] * n_edges / (seg["ms"] / 1e3)
+        gbs = per_edge * edges_per_s / 1e9
         cfconv = dict(kernel="seg_mul_sum_kernel<float,32,true,true> (CFConv gather * filter, segmented sum; filters stored once per pair)", bound="hbm", achieved=gbs,
-                      peak=hbm_peak, unit="GB/s", frac=gbs / hbm_peak, edges_per_s=seg["calls"] * n_edges / (seg["ms"] / 1e3),
-                      avg_launch_ms=seg["ms"] / seg["calls"])
+                      peak=hbm_peak, unit="GB/s", frac=gbs / hbm_peak, edges_per_s=edges_per_s, bytes_per_edge=per_edge,
+                      unique_GBps=seg["bytes"] / seg["ms"] / 1e6, avg_launch_ms=seg["ms"] / seg["calls"])
     kernels = {k: dict(calls=v["calls"], ms_per_step=v["ms"] / args.steps,
                        GBps=(v["bytes"] / v["ms"] / 1e6 if v["ms"] > 0 else None),
                        TFLOPs=(v["flops"] / v["ms"] / 1e9 if v["ms"] > 0 and v["flops"] else None)) for k, v in sorted(stats.items(), key=lambda kv: -kv[1]["ms"])}
@@ -422,7 +429,8 @@ def run_ours(args):
                 ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
                 config=dict(WORKLOAD, edges_per_gpu=n_edges, global_structures=world * B, parallelism=f"replicas x{world}, no collective"),
                 e2e=dict(value=world * B * args.steps / (e2e_ms / 1e3), unit="structures/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
-                gpu_launches=prof.total_launches, ms_per_step_with_kernel_events=ms_profiled / args.steps, roofline=roof, cfconv_roofline=cfconv, other_kernels=extras, cpu_baseline=cpu, clocks=clk, kernels=kernels,
+                gpu_launches=prof.total_launches, ms_per_step_median=sorted(step_ms)[len(step_ms) // 2], ms_per_step_min=min(step_ms),
+                ms_per_step_with_kernel_events=ms_profiled / args.steps, roofline=roof, cfconv_roofline=cfconv, other_kernels=extras, cpu_baseline=cpu, clocks=clk, kernels=kernels,
                 edges_per_s=world * n_edges * args.steps / (ms_total / 1e3))
     print(json.dumps(line))
     if world > 1:
@@ -432,8 +440,8 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--structures", type=int, default=None, help="structures per GPU (default 512; smaller values are for profiler captures)")
     ap.add_argument("--no-extras", action="store_true", help="skip the stand-alone radius-graph and prior-kernel measurements")
