@@ -365,6 +365,9 @@ def run_ours(args):
             dist.destroy_process_group()
         return
 
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels on this workload, from the
+    # Nsight Compute capture summarised under profiles/ (full-size launches; scaled by the row count for other sizes)
+    ncu_traffic = {"filter_backward": 75.1e6, "filter_forward": 230.5e6, "seg_mul_sum": 343.3e6, "gemm_tc": 39.0e6}
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -382,12 +385,13 @@ def run_ours(args):
     if name in tensor_kernels:
         achieved = st["flops"] / max(st["ms"], 1e-9) / 1e9            # TFLOP/s of algorithmic (fp32-equivalent) flops
         roof = dict(kernel=tensor_kernels[name], bound="tensor", achieved=achieved, peak=tf_peak, unit="TFLOP/s", frac=achieved / tf_peak,
-                    traffic=None, peak_source=f"{peak_src} bf16 sustained", avg_launch_ms=per_launch_ms,
+                    traffic=ncu_traffic.get(name, 0) * B / 512 or None, peak_source=f"{peak_src} bf16 sustained", avg_launch_ms=per_launch_ms,
                     note="algorithmic flops 2*F*(R+F) per evaluated row and GEMM pair (rows = E/2 on a symmetric edge list); the fp32-equivalent "
                          "mode issues three fp16 products per algorithmic product, so tensor-pipe work is 3x this figure")
     else:
         achieved = st["bytes"] / max(st["ms"], 1e-9) / 1e6            # GB/s
-        roof = dict(kernel=name, bound="hbm", achieved=achieved, peak=hbm_peak, unit="GB/s", frac=achieved / hbm_peak, traffic=None,
+        roof = dict(kernel=name, bound="hbm", achieved=achieved, peak=hbm_peak, unit="GB/s", frac=achieved / hbm_peak,
+                    traffic=ncu_traffic.get(name, 0) * B / 512 or None,
                     peak_source=f"{peak_src} copy bandwidth", avg_launch_ms=per_launch_ms)
     seg = stats.get("seg_mul_sum")
     cfconv = None
@@ -401,7 +405,7 @@ def run_ours(args):
         gbs = per_edge * edges_per_s / 1e9
         cfconv = dict(kernel="seg_mul_sum_kernel<float,32,true,true> (CFConv gather * filter, segmented sum; filters stored once per pair)", bound="hbm", achieved=gbs,
                       peak=hbm_peak, unit="GB/s", frac=gbs / hbm_peak, edges_per_s=edges_per_s, bytes_per_edge=per_edge,
-                      unique_GBps=seg["bytes"] / seg["ms"] / 1e6, avg_launch_ms=seg["ms"] / seg["calls"])
+                      unique_GBps=seg["bytes"] / seg["ms"] / 1e6, traffic=ncu_traffic["seg_mul_sum"] * B / 512, avg_launch_ms=seg["ms"] / seg["calls"])
     kernels = {k: dict(calls=v["calls"], ms_per_step=v["ms"] / args.steps,
                        GBps=(v["bytes"] / v["ms"] / 1e6 if v["ms"] > 0 else None),
                        TFLOPs=(v["flops"] / v["ms"] / 1e9 if v["ms"] > 0 and v["flops"] else None)) for k, v in sorted(stats.items(), key=lambda kv: -kv[1]["ms"])}
