@@ -67,6 +67,20 @@ int mlcgb_radius_fill(const void *pos, int dtype, const int64_t *ptr, int64_t N,
                       int32_t *row0_i32 /* [E] or NULL */, int32_t *row1_i32 /* [E] or NULL */, int32_t *status,
                       void *stream);
 
+/* The same two calls with excluded pairs, the last two arguments of mlcg::radius_cuda
+ * (src/opt_radius/mlcg_opt_radius/radius.cu:112-133,197-203): exclude_pair_xs[ptr_exclude_pair_xs[i] ..
+ * ptr_exclude_pair_xs[i+1]) lists, in ascending order, the points that centre i must not get as neighbours — the
+ * layout mlcg::exclusion_pair_to_ptr produces (exclusion_pairs.cpp:7-62).  Neighbour cap as in radius.cu (the first
+ * max_num_neighbors non-excluded hits by index).  Both pointers NULL: no exclusions. */
+int mlcgb_radius_count_excl(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r,
+                            int64_t max_num_neighbors, int loop, const int64_t *exclude_pair_xs,
+                            const int64_t *ptr_exclude_pair_xs /* [N+1] */, void *workspace, size_t workspace_bytes,
+                            int32_t *deg, int64_t *offsets, int32_t *status, void *stream);
+int mlcgb_radius_fill_excl(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int loop,
+                           const int64_t *exclude_pair_xs, const int64_t *ptr_exclude_pair_xs, const void *workspace,
+                           size_t workspace_bytes, const int64_t *offsets, int64_t E, int64_t *edge_index, void *distance,
+                           int64_t *mapping_batch, int32_t *row0_i32, int32_t *row1_i32, int32_t *status, void *stream);
+
 /* Radius graph in one call that allocates nothing.  No counterpart in the reference (mlcg sizes its
  * outputs with torch and a host read, src/opt_radius/mlcg_opt_radius/radius.cu:236-241,288-292); it exists
  * for callers that may not allocate device memory at the point of the call: a force routine invoked from

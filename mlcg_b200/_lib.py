@@ -29,6 +29,9 @@ SIGNATURES = {
     "mlcgb_radius_workspace_bytes": (c_sz, [c_i64, c_i64, c_int]),
     "mlcgb_radius_count": (c_int, [c_vp, c_int, c_vp, c_i64, c_i64, c_dbl, c_i64, c_int, c_int, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]),
     "mlcgb_radius_fill": (c_int, [c_vp, c_int, c_vp, c_i64, c_i64, c_dbl, c_int, c_vp, c_sz, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "mlcgb_radius_count_excl": (c_int, [c_vp, c_int, c_vp, c_i64, c_i64, c_dbl, c_i64, c_int, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]),
+    "mlcgb_radius_fill_excl": (c_int, [c_vp, c_int, c_vp, c_i64, c_i64, c_dbl, c_int, c_vp, c_vp, c_vp, c_sz, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp,
+                                       c_vp, c_vp]),
     "mlcgb_radius_graph_static": (c_int, [c_vp, c_int, c_vp, c_i64, c_i64, c_dbl, c_i64, c_int, c_int, c_vp, c_vp, c_i64, c_vp,
                                           ctypes.POINTER(c_i64), c_vp, c_vp]),
     "mlcgb_edge_twin": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),

@@ -170,9 +170,16 @@ class CudaBackend:
             self._run("batch_to_ptr", self.lib.mlcgb_batch_to_ptr, (_ptr(batch), batch.numel(), B, _ptr(ptr), _stream(),), **self._work("batch_to_ptr", locals()))
         return ptr
 
-    def radius_graph(self, pos, ptr, r, max_num_neighbors, loop, rule, want_distance=False, want_batch=True):
-        """Returns dict(edge_index[2,E] i64, distance|None, mapping_batch|None, row0, row1 (i32), offsets[N+1] i64, status int)."""
+    def radius_graph(self, pos, ptr, r, max_num_neighbors, loop, rule, want_distance=False, want_batch=True, exclude=None):
+        """Returns dict(edge_index[2,E] i64, distance|None, mapping_batch|None, row0, row1 (i32), offsets[N+1] i64, status int).
+        ``exclude``: ``(exclude_pair_xs, ptr_exclude_pair_xs)`` int64 as ``mlcg::radius_cuda`` takes them (rule "native" only)."""
         _need_cuda(pos, ptr)
+        if exclude is not None:
+            if int(rule) != 0:
+                raise ValueError("excluded pairs go with the neighbour cap of radius.cu (rule 0)")
+            ex_xs, ex_ptr = (t.to(device=pos.device, dtype=torch.int64).contiguous() for t in exclude)
+            if ex_ptr.numel() != pos.shape[0] + 1:
+                raise ValueError("ptr_exclude_pair_xs must have one entry per point plus one")
         pos = pos.detach().contiguous()
         N, B, dev = pos.shape[0], ptr.numel() - 1, pos.device
         dt = _dt(pos)
@@ -182,8 +189,13 @@ class CudaBackend:
             deg = torch.empty(max(N, 1), dtype=torch.int32, device=dev)
             offsets = torch.empty(N + 1, dtype=torch.int64, device=dev)
             status = torch.zeros(4, dtype=torch.int32, device=dev)
-            self._run("radius_count", self.lib.mlcgb_radius_count, (_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(max_num_neighbors), int(loop), int(rule),
-                                                   _ptr(ws), ws_bytes, _ptr(deg), _ptr(offsets), _ptr(status), _stream(),), **self._work("radius_count", locals()))
+            if exclude is None:
+                self._run("radius_count", self.lib.mlcgb_radius_count, (_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(max_num_neighbors), int(loop), int(rule),
+                                                       _ptr(ws), ws_bytes, _ptr(deg), _ptr(offsets), _ptr(status), _stream(),), **self._work("radius_count", locals()))
+            else:
+                self._run("radius_count", self.lib.mlcgb_radius_count_excl, (_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(max_num_neighbors), int(loop),
+                                                       _ptr(ex_xs), _ptr(ex_ptr), _ptr(ws), ws_bytes, _ptr(deg), _ptr(offsets), _ptr(status), _stream(),),
+                          **self._work("radius_count", locals()))
             pend, self._pending = self._pending, []
             extra = [s[0].to(torch.int64) for s, _ in pend]
             tail = torch.stack([offsets[N], status[0].to(torch.int64)] + extra).cpu().tolist()   # the one host read
@@ -196,8 +208,13 @@ class CudaBackend:
             mb = torch.empty(E, dtype=torch.int64, device=dev) if want_batch else None
             r0 = torch.empty(E, dtype=torch.int32, device=dev)
             r1 = torch.empty(E, dtype=torch.int32, device=dev)
-            self._run("radius_fill", self.lib.mlcgb_radius_fill, (_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(loop), _ptr(ws), ws_bytes, _ptr(offsets), E,
-                                                  _ptr(ei), _ptr(dist), _ptr(mb), _ptr(r0), _ptr(r1), _ptr(status), _stream(),), **self._work("radius_fill", locals()))
+            if exclude is None:
+                self._run("radius_fill", self.lib.mlcgb_radius_fill, (_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(loop), _ptr(ws), ws_bytes, _ptr(offsets), E,
+                                                      _ptr(ei), _ptr(dist), _ptr(mb), _ptr(r0), _ptr(r1), _ptr(status), _stream(),), **self._work("radius_fill", locals()))
+            else:
+                self._run("radius_fill", self.lib.mlcgb_radius_fill_excl, (_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(loop), _ptr(ex_xs), _ptr(ex_ptr), _ptr(ws), ws_bytes,
+                                                      _ptr(offsets), E, _ptr(ei), _ptr(dist), _ptr(mb), _ptr(r0), _ptr(r1), _ptr(status), _stream(),),
+                          **self._work("radius_fill", locals()))
         return dict(edge_index=ei, distance=dist, mapping_batch=mb, row0=r0, row1=r1, offsets=offsets, status=st)
 
     def edge_twin(self, row0, row1, offsets, N):

@@ -193,13 +193,28 @@ __device__ __forceinline__ void emit_edge(const FillOut &o, int64_t slot, int64_
     if (o.row1_32) o.row1_32[slot] = (int32_t)j;
 }
 
+// Pairs never to be listed (radius.cu:112-133): xs[ptr[i] .. ptr[i+1]) holds, in ascending order, the neighbours that
+// centre i must not get.  Both pointers NULL: nothing is excluded.
+struct Exclusion {
+    const int64_t *xs = nullptr, *ptr = nullptr;
+};
+__device__ __forceinline__ bool is_excluded(const int64_t *__restrict__ xs, int64_t e0, int64_t e1, int64_t j) {
+    while (e0 < e1) {                                  // binary search in the centre's sorted segment
+        const int64_t mid = (e0 + e1) >> 1;
+        const int64_t v = xs[mid];
+        if (v == j) return true;
+        if (v < j) e0 = mid + 1; else e1 = mid;
+    }
+    return false;
+}
+
 template <typename T, bool FILL>
 __global__ void __launch_bounds__(kNbrWarps * 32)
 neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t N, int64_t B, T r2,
                   int64_t max_nn, int loop, int rule, const V4<T> *__restrict__ spos,
                   const CellParam *__restrict__ cellparam, const int32_t *__restrict__ cell_of,
                   const int32_t *__restrict__ cell_start, const int32_t *__restrict__ struct_of, int32_t *__restrict__ deg,
-                  const int64_t *__restrict__ offsets, FillOut out, int32_t *__restrict__ status) {
+                  const int64_t *__restrict__ offsets, FillOut out, Exclusion ex, int32_t *__restrict__ status) {
     __shared__ unsigned s_mask[FILL ? kNbrWarps * (kCapBits / 32) : 1];
     __shared__ unsigned short s_list[FILL ? kNbrWarps * 1024 : 1];   // per warp: bit positions of one 32-word chunk
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -212,6 +227,7 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
         const int64_t lo = ptr[b];
         const int n = (int)(ptr[b + 1] - lo);
         const int il = (int)(i - lo);
+        const int64_t ex0 = ex.ptr ? ex.ptr[i] : 0, ex1 = ex.ptr ? ex.ptr[i + 1] : 0;   // this centre's excluded neighbours
         const T xi = pos[i * 3], yi = pos[i * 3 + 1], zi = pos[i * 3 + 2];
         const CellParam cp = cellparam[b];
 
@@ -232,7 +248,7 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
                 if (j < n) {
                     const int64_t gj = lo + j;
                     d2 = dist2_rn(xi, yi, zi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]);
-                    hit = d2 < r2;
+                    hit = d2 < r2 && !(ex1 > ex0 && is_excluded(ex.xs, ex0, ex1, gj));
                 }
                 if (FILL) {
                     hit = hit && (loop || j != il);
@@ -277,7 +293,7 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
                 auto test = [&](const V4<T> &p) {
                     const int j = idx_of(p);
                     const T d2 = dist2_rn(xi, yi, zi, p.x, p.y, p.z);
-                    if (d2 < r2) {
+                    if (d2 < r2 && !(ex1 > ex0 && is_excluded(ex.xs, ex0, ex1, lo + j))) {
                         if (FILL) {
                             const int jw = j - wbase;
                             if ((loop || j != il) && jw >= 0 && jw < wbits) atomicOr(&mask[jw >> 5], 1u << (jw & 31));
@@ -343,7 +359,7 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
 
         if (!FILL) {
             const int64_t nlo = warp_sum(cnt_lo), nhi = warp_sum(cnt_hi);
-            const int self_hit = dist2_rn(xi, yi, zi, xi, yi, zi) < r2 ? 1 : 0;
+            const int self_hit = (dist2_rn(xi, yi, zi, xi, yi, zi) < r2 && !(ex1 > ex0 && is_excluded(ex.xs, ex0, ex1, i))) ? 1 : 0;
             int64_t total, k;
             if (loop) {
                 total = nlo + nhi + self_hit;
@@ -469,7 +485,7 @@ __global__ void pair_index_kernel(const int32_t *__restrict__ sel, const int32_t
 template <typename T>
 static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn,
                          int loop, int rule, void *ws, size_t ws_bytes, int dtype, int32_t *deg, int64_t *offsets,
-                         FillOut out, int32_t *status, cudaStream_t st) {
+                         FillOut out, int32_t *status, cudaStream_t st, Exclusion ex = Exclusion{}) {
     const WsLayout L = ws_layout(N, B, dtype);
     if (ws_bytes < L.total) return MLCGB_E_WORKSPACE;
     char *w = (char *)ws;
@@ -485,14 +501,14 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
     if (!fill) {
         build_cells_kernel<T><<<grid_for(B, 1, 8), kBuildThreads, 0, st>>>(pos, ptr, B, (T)r, spos, cellparam, cell_of, cell_start, struct_of);
         neighbours_kernel<T, false><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
-                                                                         cell_of, cell_start, struct_of, deg, nullptr, out, status);
+                                                                         cell_of, cell_start, struct_of, deg, nullptr, out, ex, status);
         const int64_t nb = (N + kScanBlock - 1) / kScanBlock;
         scan_block_sums_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum);
         scan_of_sums_kernel<<<1, kScanBlock, 0, st>>>(bsum, nb, offsets + N);
         scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum, offsets);
     } else {
         neighbours_kernel<T, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
-                                                                        cell_of, cell_start, struct_of, nullptr, offsets, out, status);
+                                                                        cell_of, cell_start, struct_of, nullptr, offsets, out, ex, status);
     }
     return check_launch();
 }
@@ -514,9 +530,9 @@ size_t mlcgb_radius_workspace_bytes(int64_t N, int64_t B, int dtype) {
     return ws_layout(N, B, dtype).total;
 }
 
-int mlcgb_radius_count(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn, int loop,
-                       int rule, void *workspace, size_t workspace_bytes, int32_t *deg, int64_t *offsets, int32_t *status,
-                       void *stream) {
+static int radius_count_impl(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn, int loop,
+                             int rule, void *workspace, size_t workspace_bytes, int32_t *deg, int64_t *offsets, int32_t *status,
+                             void *stream, Exclusion ex) {
     if (N < 0 || B < 0 || max_nn < 0 || !offsets || !status || !ptr || !workspace) return MLCGB_E_ARG;
     if (N >= (int64_t)1 << 31) return MLCGB_E_LIMIT;
     if (rule != MLCGB_RULE_NATIVE && rule != MLCGB_RULE_CLUSTER) return MLCGB_E_ARG;
@@ -527,7 +543,37 @@ int mlcgb_radius_count(const void *pos, int dtype, const int64_t *ptr, int64_t N
     if (!pos || !deg || B == 0) return MLCGB_E_ARG;
     return MLCGB_DISPATCH_DTYPE(dtype, [&] {
         return radius_launch<scalar_t>(false, pos, ptr, N, B, r, max_nn, loop, rule, workspace, workspace_bytes, dtype, deg,
-                                       offsets, FillOut{}, status, (cudaStream_t)stream);
+                                       offsets, FillOut{}, status, (cudaStream_t)stream, ex);
+    });
+}
+
+int mlcgb_radius_count(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn, int loop,
+                       int rule, void *workspace, size_t workspace_bytes, int32_t *deg, int64_t *offsets, int32_t *status,
+                       void *stream) {
+    return radius_count_impl(pos, dtype, ptr, N, B, r, max_nn, loop, rule, workspace, workspace_bytes, deg, offsets, status, stream, Exclusion{});
+}
+
+int mlcgb_radius_count_excl(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn, int loop,
+                            const int64_t *exclude_pair_xs, const int64_t *ptr_exclude_pair_xs, void *workspace, size_t workspace_bytes,
+                            int32_t *deg, int64_t *offsets, int32_t *status, void *stream) {
+    if (!exclude_pair_xs != !ptr_exclude_pair_xs) return MLCGB_E_ARG;
+    Exclusion ex;
+    ex.xs = exclude_pair_xs;
+    ex.ptr = ptr_exclude_pair_xs;
+    return radius_count_impl(pos, dtype, ptr, N, B, r, max_nn, loop, MLCGB_RULE_NATIVE, workspace, workspace_bytes, deg, offsets, status, stream, ex);
+}
+
+static int radius_fill_impl(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int loop,
+                            const void *workspace, size_t workspace_bytes, const int64_t *offsets, int64_t E, int64_t *edge_index,
+                            void *distance, int64_t *mapping_batch, int32_t *row0_i32, int32_t *row1_i32, int32_t *status,
+                            void *stream, Exclusion ex) {
+    if (N < 0 || B < 0 || E < 0 || !offsets || !status || !ptr || !workspace) return MLCGB_E_ARG;
+    if (E == 0 || N == 0) return MLCGB_OK;
+    if (!pos || !edge_index) return MLCGB_E_ARG;
+    FillOut out{edge_index, edge_index + E, mapping_batch, distance, row0_i32, row1_i32};
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        return radius_launch<scalar_t>(true, pos, ptr, N, B, r, 0, loop, 0, const_cast<void *>(workspace), workspace_bytes, dtype,
+                                       nullptr, const_cast<int64_t *>(offsets), out, status, (cudaStream_t)stream, ex);
     });
 }
 
@@ -535,14 +581,20 @@ int mlcgb_radius_fill(const void *pos, int dtype, const int64_t *ptr, int64_t N,
                       const void *workspace, size_t workspace_bytes, const int64_t *offsets, int64_t E, int64_t *edge_index,
                       void *distance, int64_t *mapping_batch, int32_t *row0_i32, int32_t *row1_i32, int32_t *status,
                       void *stream) {
-    if (N < 0 || B < 0 || E < 0 || !offsets || !status || !ptr || !workspace) return MLCGB_E_ARG;
-    if (E == 0 || N == 0) return MLCGB_OK;
-    if (!pos || !edge_index) return MLCGB_E_ARG;
-    FillOut out{edge_index, edge_index + E, mapping_batch, distance, row0_i32, row1_i32};
-    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
-        return radius_launch<scalar_t>(true, pos, ptr, N, B, r, 0, loop, 0, const_cast<void *>(workspace), workspace_bytes, dtype,
-                                       nullptr, const_cast<int64_t *>(offsets), out, status, (cudaStream_t)stream);
-    });
+    return radius_fill_impl(pos, dtype, ptr, N, B, r, loop, workspace, workspace_bytes, offsets, E, edge_index, distance, mapping_batch,
+                            row0_i32, row1_i32, status, stream, Exclusion{});
+}
+
+int mlcgb_radius_fill_excl(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int loop,
+                           const int64_t *exclude_pair_xs, const int64_t *ptr_exclude_pair_xs, const void *workspace,
+                           size_t workspace_bytes, const int64_t *offsets, int64_t E, int64_t *edge_index, void *distance,
+                           int64_t *mapping_batch, int32_t *row0_i32, int32_t *row1_i32, int32_t *status, void *stream) {
+    if (!exclude_pair_xs != !ptr_exclude_pair_xs) return MLCGB_E_ARG;
+    Exclusion ex;
+    ex.xs = exclude_pair_xs;
+    ex.ptr = ptr_exclude_pair_xs;
+    return radius_fill_impl(pos, dtype, ptr, N, B, r, loop, workspace, workspace_bytes, offsets, E, edge_index, distance, mapping_batch,
+                            row0_i32, row1_i32, status, stream, ex);
 }
 
 int mlcgb_edge_twin(const int32_t *row0, const int32_t *row1, const int64_t *offsets, int64_t E, int64_t N, int32_t *twin,

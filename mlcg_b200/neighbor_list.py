@@ -37,11 +37,13 @@ def _structure_ptr(x, batch, batch_size):
     return be.batch_to_ptr(batch.to(torch.int64), batch_size)
 
 
-def _graph(x, r, ptr, loop, max_num_neighbors, rule, want_distance=False):
+def _graph(x, r, ptr, loop, max_num_neighbors, rule, want_distance=False, exclude=None):
     be = get_backend()
-    res = be.radius_graph(_as_3d(x), ptr, r, max_num_neighbors, loop, rule, want_distance=want_distance)
+    res = be.radius_graph(_as_3d(x), ptr, r, max_num_neighbors, loop, rule, want_distance=want_distance, exclude=exclude)
     truncated = bool(res["status"] & STATUS_TRUNCATED)
-    plan = EdgePlan.from_centre_sorted(res["row0"], res["row1"], res["offsets"], x.shape[0], symmetric=not truncated, loops=bool(loop))
+    # an exclusion list need not hold both directions of a pair: such a graph is not taken to be symmetric
+    plan = EdgePlan.from_centre_sorted(res["row0"], res["row1"], res["offsets"], x.shape[0], symmetric=not truncated and exclude is None,
+                                       loops=bool(loop))
     attach_plan(res["edge_index"], plan)
     res["plan"], res["truncated"] = plan, truncated
     return res
@@ -64,26 +66,50 @@ def radius_graph(x: torch.Tensor, r: float, batch: Optional[torch.Tensor] = None
 def radius_cuda(x: torch.Tensor, ptr_x: Optional[torch.Tensor], r: float, max_num_neighbors: int, ignore_same_index: bool,
                 exclude_pair_xs: Optional[torch.Tensor] = None, ptr_exclude_pair_xs: Optional[torch.Tensor] = None
                 ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``mlcg::radius_cuda`` (radius.cu:197-307): returns ``(edge_index [2,E], distance [E])``."""
-    if exclude_pair_xs is not None and exclude_pair_xs.numel() > 0 and ptr_exclude_pair_xs is not None and int(ptr_exclude_pair_xs[-1]) > 0:
-        raise NotImplementedError("excluded pairs are not supported by this build of radius_cuda")
+    """``mlcg::radius_cuda`` (radius.cu:197-307): returns ``(edge_index [2,E], distance [E])``.  ``exclude_pair_xs`` /
+    ``ptr_exclude_pair_xs`` as :func:`exclusion_pair_to_ptr` returns them: centre ``i`` never gets a neighbour listed in
+    ``exclude_pair_xs[ptr_exclude_pair_xs[i]:ptr_exclude_pair_xs[i+1]]`` (radius.cu:112-133)."""
     if not x.is_cuda:
         raise RuntimeError("x must be CUDA tensor")
+    if (exclude_pair_xs is None) != (ptr_exclude_pair_xs is None):
+        raise RuntimeError("exclude_pair_xs and ptr_exclude_pair_xs go together")
+    exclude = None
+    if exclude_pair_xs is not None and exclude_pair_xs.numel() > 0:
+        exclude = (exclude_pair_xs, ptr_exclude_pair_xs)
     if ptr_x is None:
         ptr_x = torch.tensor([0, x.shape[0]], dtype=torch.int64, device=x.device)
-    res = _graph(x, r, ptr_x.to(torch.int64), not ignore_same_index, max_num_neighbors, RULE_NATIVE, want_distance=True)
+    res = _graph(x, r, ptr_x.to(torch.int64), not ignore_same_index, max_num_neighbors, RULE_NATIVE, want_distance=True, exclude=exclude)
     return res["edge_index"], res["distance"]
+
+
+def exclusion_pair_to_ptr(exc_pair_index: torch.Tensor, num_nodes: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``mlcg::exclusion_pair_to_ptr`` (exclusion_pairs.cpp:7-62): pairs ``[2, P]`` of ``(x, y)`` -> the ``x`` sorted by
+    ``(y, x)`` and a pointer of length ``num_nodes + 1`` over ``y``.  Runs where the pairs live (the reference copies them to
+    the host and back); torch's stable sort and bincount do the work."""
+    if exc_pair_index.dtype != torch.int64 or exc_pair_index.dim() != 2 or exc_pair_index.shape[0] != 2:
+        raise RuntimeError("exc_pair_index must be an int64 tensor of shape [2, P]")
+    xs, ys = exc_pair_index[0], exc_pair_index[1]
+    if xs.numel() and (int(ys.min()) < 0 or int(ys.max()) >= num_nodes):
+        raise RuntimeError("pair index out of range")
+    order = torch.argsort(xs, stable=True)
+    order = order[torch.argsort(ys[order], stable=True)]
+    y_ptr = torch.zeros(num_nodes + 1, dtype=torch.int64, device=exc_pair_index.device)
+    if xs.numel():
+        y_ptr[1:] = torch.cumsum(torch.bincount(ys, minlength=num_nodes), 0)
+    return xs[order].contiguous(), y_ptr
 
 
 def radius_distance(x: torch.Tensor, r: float, batch: Optional[torch.Tensor] = None, loop: bool = False,
                     max_num_neighbors: int = 32, batch_size: Optional[int] = None,
                     exclude_pair_indices: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``mlcg_opt_radius.radius.radius_distance`` (radius.py:187-199): ``(distance, edge_index)``."""
-    if exclude_pair_indices is not None and exclude_pair_indices.numel() > 0:
-        raise NotImplementedError("excluded pairs are not supported by this build of radius_distance")
+    """``mlcg_opt_radius.radius.radius_distance`` (radius.py:187-199, :50-90): ``(distance, edge_index)``;
+    ``exclude_pair_indices`` is a ``[2, P]`` tensor of ``(x, y)`` pairs: ``y`` never gets ``x`` as a neighbour."""
     if x.numel() == 0:
         return x.new_zeros(0), torch.empty(2, 0, dtype=torch.long, device=x.device)
-    res = _graph(x, r, _structure_ptr(x, batch, batch_size), loop, max_num_neighbors, RULE_NATIVE)
+    exclude = None
+    if exclude_pair_indices is not None and exclude_pair_indices.numel() > 0:
+        exclude = exclusion_pair_to_ptr(exclude_pair_indices.to(x.device), x.shape[0])
+    res = _graph(x, r, _structure_ptr(x, batch, batch_size), loop, max_num_neighbors, RULE_NATIVE, exclude=exclude)
     # the distance goes through the differentiable geometry operators, so that derivatives of any
     # order with respect to x exist (the reference hand-writes two orders, radius.py:123-158)
     return edge_distances(_as_3d(x), res["plan"]), res["edge_index"]

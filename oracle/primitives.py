@@ -23,16 +23,21 @@ class OracleBackend:
     def batch_to_ptr(self, batch, B):
         return torch.from_numpy(radius_ref.batch_to_ptr(batch.cpu().numpy(), B)).to(batch.device)
 
-    def radius_graph(self, pos, ptr, r, max_num_neighbors, loop, rule, want_distance=False, want_batch=True):
+    def radius_graph(self, pos, ptr, r, max_num_neighbors, loop, rule, want_distance=False, want_batch=True, exclude=None):
         p = pos.detach().cpu().numpy()
         rule_name = "cluster" if int(rule) == 1 else "native"
-        ei, dist = radius_ref.radius_graph_c(p, ptr.cpu().numpy(), r, max_num_neighbors, loop, rule_name, with_distance=True)
         N = p.shape[0]
+        if exclude is None:
+            graph = lambda cap, **kw: radius_ref.radius_graph_c(p, ptr.cpu().numpy(), r, cap, loop, rule_name, **kw)
+        else:
+            ex = tuple(t.cpu().numpy() for t in exclude)
+            graph = lambda cap, **kw: radius_ref.radius_graph_numpy(p, ptr.cpu().numpy(), r, cap, loop, rule_name, exclude=ex, **kw)
+        ei, dist = graph(max_num_neighbors, with_distance=True)
         deg = np.bincount(ei[0], minlength=N)
         offsets = np.zeros(N + 1, dtype=np.int64)
         np.cumsum(deg, out=offsets[1:])
         # truncated: any centre that would have had more neighbours without the cap
-        full = radius_ref.radius_graph_c(p, ptr.cpu().numpy(), r, max(N, 1) + 1, loop, rule_name)
+        full = graph(max(N, 1) + 1)
         status = 1 if full.shape[1] != ei.shape[1] else 0
         dev = pos.device
         ei_t = torch.from_numpy(ei).to(dev)

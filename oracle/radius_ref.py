@@ -88,9 +88,13 @@ def radius_graph_c(pos, ptr, r, max_num_neighbors=1000, loop=False, rule="cluste
     return (ei, dist) if with_distance else ei
 
 
-def radius_graph_numpy(pos, ptr, r, max_num_neighbors=1000, loop=False, rule="cluster", with_distance=False):
-    """Same rule, all pairs of one structure at a time with separately rounded numpy operations."""
+def radius_graph_numpy(pos, ptr, r, max_num_neighbors=1000, loop=False, rule="cluster", with_distance=False, exclude=None):
+    """Same rule, all pairs of one structure at a time with separately rounded numpy operations.
+
+    ``exclude = (xs, y_ptr)`` as :func:`exclusion_pair_to_ptr` returns them (rule "native" only): centre ``i`` never gets a
+    neighbour listed in ``xs[y_ptr[i]:y_ptr[i+1]]``, and excluded points do not count towards the cap (radius.cu:122-141)."""
     pos = np.asarray(pos)
+    assert exclude is None or rule == "native"
     T = pos.dtype.type
     r2 = T(float(r) * float(r))
     rows0, rows1, dists = [], [], []
@@ -103,6 +107,12 @@ def radius_graph_numpy(pos, ptr, r, max_num_neighbors=1000, loop=False, rule="cl
         hit = d2 < r2
         n = hi - lo
         eye = np.eye(n, dtype=bool)
+        if exclude is not None:
+            xs, y_ptr = exclude
+            for i in range(lo, hi):
+                for x in xs[int(y_ptr[i]):int(y_ptr[i + 1])]:
+                    if lo <= x < hi:
+                        hit[i - lo, int(x) - lo] = False
         if loop:
             counted, cap = hit, max_num_neighbors
         elif rule == "cluster":

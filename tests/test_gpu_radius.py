@@ -159,3 +159,40 @@ def test_full_size_standalone_configuration_properties():
         want = radius_ref.radius_graph_c(pos[b * n:(b + 1) * n], np.array([0, n], np.int64), 10.0, 1000, False, "cluster") + b * n
         lo, hi = int(off[b * n]), int(off[(b + 1) * n])
         assert np.array_equal(ei[:, lo:hi].cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("loop", [False, True])
+@pytest.mark.parametrize("max_nn", [4, 1000])
+def test_excluded_pairs(dtype, loop, max_nn):
+    """`mlcg::radius_cuda` with exclusion lists (radius.cu:112-141): brute-force and cell-list structures, with and without
+    the neighbour cap, self pairs among the exclusions."""
+    from mlcg_b200.neighbor_list import exclusion_pair_to_ptr, radius_cuda, radius_distance
+    rng = np.random.default_rng(11)
+    sizes = [0, 30, 1, 600, 130]
+    ptr = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    pos = (rng.random((ptr[-1], 3)) * 11).astype(dtype)
+    xs_l, ys_l = [], []
+    for b in range(len(sizes)):
+        lo, hi = int(ptr[b]), int(ptr[b + 1])
+        if hi > lo:
+            m = 4 * (hi - lo)
+            xs_l.append(rng.integers(lo, hi, m)); ys_l.append(rng.integers(lo, hi, m))
+    # plus the bonded neighbours of every point, as a topology would list them
+    idx = np.arange(ptr[-1] - 1)
+    xs_l += [idx, idx + 1]; ys_l += [idx + 1, idx]
+    pairs = np.stack([np.concatenate(xs_l), np.concatenate(ys_l)]).astype(np.int64)
+    txs, tptr = exclusion_pair_to_ptr(torch.from_numpy(pairs).to(DEV), int(ptr[-1]))
+    oxs, optr = radius_ref.exclusion_pair_to_ptr(pairs, int(ptr[-1]))
+    assert np.array_equal(txs.cpu().numpy(), oxs) and np.array_equal(tptr.cpu().numpy(), optr)
+    want, wdist = radius_ref.radius_graph_numpy(pos, ptr, 3.0, max_nn, loop, "native", with_distance=True, exclude=(oxs, optr))
+    x = torch.as_tensor(pos, device=DEV)
+    ei, dist = radius_cuda(x, torch.as_tensor(ptr, device=DEV), 3.0, max_nn, not loop, txs, tptr)
+    assert np.array_equal(ei.cpu().numpy(), want) and np.array_equal(dist.cpu().numpy(), wdist)
+    banned = set(zip(pairs[1].tolist(), pairs[0].tolist()))
+    assert not any((i, j) in banned for i, j in zip(want[0].tolist(), want[1].tolist()))
+    # the Python-level entry point builds the lists itself
+    batch = torch.as_tensor(np.repeat(np.arange(len(sizes)), sizes), device=DEV)
+    d2, ei2 = radius_distance(x, 3.0, batch, loop, max_nn, len(sizes), torch.from_numpy(pairs).to(DEV))
+    assert np.array_equal(ei2.cpu().numpy(), want)
+    assert np.allclose(d2.detach().cpu().numpy(), wdist, rtol=1e-6 if dtype == np.float32 else 1e-12)

@@ -53,3 +53,56 @@ def test_exclusion_pair_worked_example():
     xs, ptr = radius_ref.exclusion_pair_to_ptr(pairs, 4)
     assert xs.tolist() == [2, 1, 2, 3, 2]
     assert ptr.tolist() == [0, 0, 1, 4, 5]
+
+
+def _random_exclusions(rng, ptr, per_point, both_directions):
+    """Pairs (x, y) inside structures, `per_point` of them per point on average, some of them (i, i)."""
+    xs, ys = [], []
+    for b in range(len(ptr) - 1):
+        lo, hi = int(ptr[b]), int(ptr[b + 1])
+        if hi - lo < 1:
+            continue
+        m = (hi - lo) * per_point
+        x, y = rng.integers(lo, hi, m), rng.integers(lo, hi, m)
+        xs.append(x); ys.append(y)
+        if both_directions:
+            xs.append(y); ys.append(x)
+    pairs = np.unique(np.stack([np.concatenate(xs), np.concatenate(ys)]), axis=1)     # the kernel's search wants no duplicates? it does not care
+    return pairs.astype(np.int64)
+
+
+@pytest.mark.parametrize("loop", [False, True])
+@pytest.mark.parametrize("max_nn", [3, 1000])
+def test_excluded_pairs_oracle(loop, max_nn):
+    """Exclusions (radius.cu:122-141): without a cap the graph is the plain graph minus the excluded pairs; with a cap the
+    excluded points do not use up places."""
+    rng = np.random.default_rng(5)
+    sizes = [0, 17, 1, 40]
+    ptr = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    pos = (rng.random((ptr[-1], 3)) * 5).astype(np.float32)
+    pairs = _random_exclusions(rng, ptr, 3, False)
+    xs, y_ptr = radius_ref.exclusion_pair_to_ptr(pairs, int(ptr[-1]))
+    plain = radius_ref.radius_graph_numpy(pos, ptr, 2.0, 10 ** 6, loop, "native")
+    got = radius_ref.radius_graph_numpy(pos, ptr, 2.0, max_nn, loop, "native", exclude=(xs, y_ptr))
+    banned = set(zip(pairs[1].tolist(), pairs[0].tolist()))                     # (centre y, neighbour x)
+    want = [(i, j) for i, j in zip(plain[0].tolist(), plain[1].tolist()) if (i, j) not in banned]
+    if max_nn < 1000:
+        kept, seen = [], {}
+        for i, j in want:
+            if seen.get(i, 0) < max_nn:
+                kept.append((i, j)); seen[i] = seen.get(i, 0) + 1
+        want = kept
+    assert list(zip(got[0].tolist(), got[1].tolist())) == want
+
+
+def test_exclusion_pair_to_ptr_torch_version_matches_the_c_restatement():
+    import torch
+    from mlcg_b200.neighbor_list import exclusion_pair_to_ptr
+    rng = np.random.default_rng(2)
+    for n, p in [(4, 5), (50, 400), (7, 0), (1, 3)]:
+        pairs = rng.integers(0, n, (2, p)).astype(np.int64)
+        xs, y_ptr = radius_ref.exclusion_pair_to_ptr(pairs, n)
+        txs, tptr = exclusion_pair_to_ptr(torch.from_numpy(pairs), n)
+        assert txs.tolist() == xs.tolist() and tptr.tolist() == y_ptr.tolist()
+    xs, y_ptr = exclusion_pair_to_ptr(torch.tensor([[2, 1, 3, 2, 2], [1, 2, 2, 2, 3]]), 4)
+    assert xs.tolist() == [2, 1, 2, 3, 2] and y_ptr.tolist() == [0, 0, 1, 4, 5]
