@@ -465,6 +465,180 @@ gemm_tc_tn_kernel(const float *__restrict__ A, const float *__restrict__ B, int6
     if (warp == 0) tmem_free(tmem, 256);
 }
 
+// ------------------------------------------------------------------------------------------------ TN, pipelined
+// C[M,N] = A[E,M]^T B[E,N], the contraction runs over the edges.  Per 128-edge tile:
+//  * A operand (lane = output row m, K = edge): every thread reads its 32 values A[e][m] straight from global memory —
+//    for one edge the 128 threads of a lane quarter read 128 consecutive floats;
+//  * B operand (rows = edges, read MN-major): float4 per thread from global memory, converted to fp16 hi/lo and written
+//    as 8-byte pieces of the swizzled operand tile;
+//  * both are scaled by one power of two per tile (largest magnitude to [8,16)), so every tile has its own scale and
+//    its product is read out of tensor memory and added to an fp32 accumulator tile in shared memory;
+//  * two operand buffers (TMEM for A, shared memory for B) and two accumulators: the loads and conversion of tile i+1
+//    run under the MMAs of tile i.
+// Needs N % 4 == 0 and a 16-byte aligned B; the one-tile-at-a-time kernel below takes everything else.
+struct GemmTnSmem {
+    static constexpr int kB0 = 0, kB1 = 65536;        // operand tiles hi | lo, two buffers
+    static constexpr int kAcc = 131072;               // fp32 accumulators [128][128], chunk-swizzled
+    static constexpr int kMisc = 196608;
+    static constexpr int kTotal = kMisc + 1024 + 1024;
+};
+
+__global__ void __launch_bounds__(kGT, 1)
+gemm_tc_tn_pipe_kernel(const float *__restrict__ A, const float *__restrict__ B, int64_t E, int M, int N, float *__restrict__ partial,
+                       int32_t *__restrict__ status) {
+    using namespace tc;
+    using L = GemmTnSmem;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *s_acc = smem + L::kAcc;
+    float2 *s_red = reinterpret_cast<float2 *>(smem + L::kMisc);          // [16] per-warp maxima of (A, B)
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + 256);
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(s_bar + 2);
+    int *s_err = reinterpret_cast<int *>(s_tmem + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = tid & 127, qt = tid >> 7, col0 = qt * 32;   // r: output row m (TMEM lane); col0: edge sub-range / output columns
+    const int npad = N <= 64 ? 64 : 128;
+    const int qpr = npad >> 2;                                  // float4 pieces per row of the B tile
+    const uint32_t bar0 = smem_u32(s_bar);
+    if (tid == 0) {
+        mbar_init(bar0, 1);
+        mbar_init(bar0 + 8, 1);
+        *s_err = 0;
+    }
+#pragma unroll
+    for (int w = 0; w < 8; w++) *gstage(s_acc, r, (col0 >> 2) + w) = make_float4(0.f, 0.f, 0.f, 0.f);
+    __syncwarp();
+    if (warp == 0) tmem_alloc(smem_u32(s_tmem), 512);
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;                 // accumulators [0,128) [128,256); A operands [256,384) [384,512)
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t phase_bits = 0;
+
+    const int64_t ntiles = (E + kRows - 1) / kRows;
+    const int64_t step = gridDim.x;
+    float xa[32];
+    float4 xb[8];
+    auto load_tile = [&](int64_t tile) {
+        const int64_t e0 = tile * kRows;
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const int64_t e = e0 + col0 + j;
+            xa[j] = (e < E && r < M) ? __ldg(A + e * M + r) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = tid + u * kGT;
+            const int er = idx / qpr, n4 = (idx - er * qpr) << 2;
+            const int64_t e = e0 + er;
+            xb[u] = (er < kRows && e < E && n4 < N) ? __ldg(reinterpret_cast<const float4 *>(B + e * N + n4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    // scales, operand stores and MMAs of the tile held in xa / xb into buffer `buf`; returns 1 / (sa sb)
+    auto convert_issue = [&](int buf) {
+        float amax = 0.f, bmax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; j++) amax = fmaxf(amax, fabsf(xa[j]));
+#pragma unroll
+        for (int u = 0; u < 8; u++) bmax = fmaxf(fmaxf(bmax, fmaxf(fabsf(xb[u].x), fabsf(xb[u].y))), fmaxf(fabsf(xb[u].z), fabsf(xb[u].w)));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
+        }
+        if (lane == 0) s_red[warp] = make_float2(amax, bmax);
+        __syncthreads();
+        if (*s_err) return -1.f;      // written before this barrier, so every thread takes the same branch
+#pragma unroll
+        for (int w = 0; w < 16; w++) {
+            const float2 m = s_red[w];
+            amax = fmaxf(amax, m.x);
+            bmax = fmaxf(bmax, m.y);
+        }
+        const float sa = row_scale(amax), sb = row_scale(bmax);
+        const uint32_t ta = tmem + 256 + buf * 128;
+        store_a_tmem<true>(ta + lane_off, col0, xa, sa);
+        uint8_t *b_hi = smem + (buf ? L::kB1 : L::kB0), *b_lo = b_hi + 32768;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = tid + u * kGT;
+            const int er = idx / qpr, n4 = (idx - er * qpr) << 2;
+            if (er < kRows) {
+                const float4 w = make_float4(xb[u].x * sb, xb[u].y * sb, xb[u].z * sb, xb[u].w * sb);
+                const uint32_t off = elem_offset(er, n4);
+                const __half2 a0 = __floats2half2_rn(w.x, w.y), a1 = __floats2half2_rn(w.z, w.w);
+                const float2 f0 = __half22float2(a0), f1 = __half22float2(a1);
+                const __half2 c0 = __floats2half2_rn(w.x - f0.x, w.y - f0.y), c1 = __floats2half2_rn(w.z - f1.x, w.w - f1.y);
+                *reinterpret_cast<uint2 *>(b_hi + off) = make_uint2(*reinterpret_cast<const uint32_t *>(&a0), *reinterpret_cast<const uint32_t *>(&a1));
+                *reinterpret_cast<uint2 *>(b_lo + off) = make_uint2(*reinterpret_cast<const uint32_t *>(&c0), *reinterpret_cast<const uint32_t *>(&c1));
+            }
+        }
+        tmem_wait_st();
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            issue_gemm_ts<true>(tmem + buf * 128, ta, smem_u32(b_hi), smem_u32(b_lo), kRows / 16, 1, npad);
+            mma_commit(bar0 + 8 * buf);
+        }
+        return 1.f / (sa * sb);
+    };
+    // product of the tile in accumulator `buf` -> shared-memory accumulator
+    auto collect = [&](int buf, float inv) {
+        if (!mbar_wait(bar0 + 8 * buf, (phase_bits >> buf) & 1u)) *s_err = 1;
+        phase_bits ^= 1u << buf;
+        tc_fence_after();
+        if (col0 < npad) {
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                float v[16];
+                tmem_ld16(tmem + buf * 128 + lane_off + col0 + half * 16, v);
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    float4 *slot = gstage(s_acc, r, (col0 >> 2) + half * 4 + w);
+                    float4 a4 = *slot;
+                    a4.x = fmaf(v[4 * w], inv, a4.x); a4.y = fmaf(v[4 * w + 1], inv, a4.y);
+                    a4.z = fmaf(v[4 * w + 2], inv, a4.z); a4.w = fmaf(v[4 * w + 3], inv, a4.w);
+                    *slot = a4;
+                }
+            }
+        }
+        tc_fence_before();
+    };
+
+    const int64_t t0 = blockIdx.x;
+    float inv_prev = 0.f;
+    int buf = 0;
+    if (t0 < ntiles) load_tile(t0);
+    for (int64_t tile = t0; tile < ntiles; tile += step, buf ^= 1) {
+        const float inv_cur = convert_issue(buf);
+        if (inv_cur < 0.f) break;                                   // a wait ran out (all threads leave together)
+        if (tile + step < ntiles) load_tile(tile + step);           // in flight under the MMAs just issued
+        if (tile != t0) collect(buf ^ 1, inv_prev);
+        inv_prev = inv_cur;
+    }
+    __syncthreads();
+    if (t0 < ntiles && !*s_err) collect(buf ^ 1, inv_prev);
+    __syncthreads();
+    if (r < M)
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const float4 a4 = *gstage(s_acc, r, (col0 >> 2) + w);
+            const float o[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (col0 + 4 * w + j < N) partial[((int64_t)blockIdx.x * M + r) * N + col0 + 4 * w + j] = o[j];
+        }
+    tc_fence_before();
+    __syncthreads();
+    if (*s_err && tid == 0) atomicOr(status, 8);
+    if (warp == 0) tmem_free(tmem, 512);
+}
+
 __global__ void gemm_tc_reduce_kernel(const float *__restrict__ partial, int64_t MN, int parts, float *__restrict__ C) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < MN; i += (int64_t)gridDim.x * blockDim.x) {
         float s = 0.f;
@@ -560,8 +734,19 @@ int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int6
     }
     const int parts = tn_parts(K);
     if (!workspace || workspace_bytes < (size_t)parts * M * N * sizeof(float)) return MLCGB_E_WORKSPACE;
-    if (int rc = set_smem(gemm_tc_tn_kernel, c2)) return rc;
-    gemm_tc_tn_kernel<<<parts, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, K, (int)M, (int)N, (float *)workspace, status);
+    if ((N & 3) == 0 && ((uintptr_t)B & 15) == 0) {
+        static bool c3[64] = {false};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !c3[dev]) {
+            if (cudaFuncSetAttribute(gemm_tc_tn_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmTnSmem::kTotal) != cudaSuccess) return check_launch();
+            c3[dev] = true;
+        }
+        gemm_tc_tn_pipe_kernel<<<parts, kGT, GemmTnSmem::kTotal, st>>>((const float *)A, (const float *)B, K, (int)M, (int)N, (float *)workspace, status);
+    } else {
+        if (int rc = set_smem(gemm_tc_tn_kernel, c2)) return rc;
+        gemm_tc_tn_kernel<<<parts, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, K, (int)M, (int)N, (float *)workspace, status);
+    }
     gemm_tc_reduce_kernel<<<grid_for(M * N, 256), 256, 0, st>>>((const float *)workspace, M * N, parts, (float *)C);
     return check_launch();
 }

@@ -52,3 +52,26 @@ class AtomicData:
     @property
     def num_structures(self):
         return None if self.n_atoms is None else int(self.n_atoms.numel())
+
+
+def collate(data_list):
+    """Structures -> one batch, the way torch_geometric collates mlcg's ``AtomicData`` (src/mlcg/data/atomic_data.py,
+    src/mlcg/simulation/base.py:621-626): positions and types concatenated, ``batch`` numbered in list order, every
+    neighbour list's ``index_mapping`` shifted by the structure's first node and concatenated, ``mapping_batch`` filled in."""
+    pos = torch.cat([d.pos for d in data_list])
+    types = torch.cat([d.atom_types for d in data_list])
+    sizes = [d.pos.shape[0] for d in data_list]
+    dev = pos.device
+    batch = torch.repeat_interleave(torch.arange(len(data_list), device=dev), torch.tensor(sizes, device=dev))
+    first = [0]
+    for n in sizes[:-1]:
+        first.append(first[-1] + n)
+    nls = {}
+    for tag in data_list[0].neighbor_list:
+        parts = [d.neighbor_list[tag] for d in data_list]
+        im = torch.cat([p["index_mapping"] + off for p, off in zip(parts, first)], dim=1)
+        mb = torch.cat([torch.full((p["index_mapping"].shape[1],), b, dtype=torch.long, device=dev) for b, p in enumerate(parts)])
+        shifts = None if parts[0].get("cell_shifts") is None else torch.cat([p["cell_shifts"] for p in parts])
+        nls[tag] = dict(tag=parts[0]["tag"], order=parts[0]["order"], index_mapping=im, cell_shifts=shifts, rcut=parts[0].get("rcut"),
+                        self_interaction=parts[0].get("self_interaction"), mapping_batch=mb)
+    return AtomicData(pos=pos, atom_types=types, batch=batch, n_atoms=torch.tensor(sizes, device=dev), neighbor_list=nls)

@@ -224,7 +224,8 @@ class FourierSeries(_Prior):
 
     def _params(self, data):
         p = self.data2parameters(data)
-        return torch.cat([p["v_0"].t(), p["k1s"].t(), p["k2s"].t()], dim=0)   # rows: v0, k1_1..k1_n, k2_1..k2_n
+        v_0 = p["v_0"][:, :1]            # (a merged prior pads v_0 to the width of the series; only column 0 counts)
+        return torch.cat([v_0.t(), p["k1s"].t(), p["k2s"].t()], dim=0)   # rows: v0, k1_1..k1_n, k2_1..k2_n
 
     def _energy_terms(self, pos, mapping, params):
         n = self.n_degs

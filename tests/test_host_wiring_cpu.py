@@ -169,3 +169,48 @@ def test_no_cpu_fallback():
         return  # library not built on this machine: operators cannot run at all, which is the point
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         be.edge_mul(torch.zeros(2, 4), torch.zeros(2, 4), torch.zeros(1, dtype=torch.int32), torch.zeros(1, dtype=torch.int32))
+
+
+def test_condensed_priors_give_the_same_energies_and_forces():
+    """src/mlcg/simulation/specialize_prior.py:75-206: several priors of one class merged into one Static prior over the
+    concatenated index lists; the total energy and forces of a collated batch do not change."""
+    import itertools
+    from mlcg_b200.data import collate
+    from mlcg_b200.specialize_prior import StaticPrior, condense_all_priors_for_simulation
+    gen = torch.Generator().manual_seed(9)
+    T, n, B = 3, 11, 3
+    r = lambda: float(torch.rand(1, generator=gen))
+    tab2 = lambda: {k: {"k": 50 + 100 * r(), "x_0": 3.5 + 0.6 * r()} for k in itertools.product(range(T), repeat=2)}
+    tab3 = {k: {"k": 20 + 60 * r(), "x_0": -0.8 + r()} for k in itertools.product(range(T), repeat=3)}
+    def tab4(nd):
+        return {k: {"v_0": r(), "k1s": {f"k1_{i}": r() - 0.5 for i in range(1, nd + 1)}, "k2s": {f"k2_{i}": r() - 0.5 for i in range(1, nd + 1)}}
+                for k in itertools.product(range(T), repeat=4)}
+    priors = {"bonds_even": bnn.HarmonicBonds(tab2()), "bonds_odd": bnn.HarmonicBonds(tab2()), "angles": bnn.HarmonicAngles(tab3),
+              "dih_short": bnn.Dihedral(tab4(2), n_degs=2, name="dih_short"), "dih_long": bnn.Dihedral(tab4(3), n_degs=3, name="dih_long"),
+              "repulsion": bnn.Repulsion({k: {"sigma": 3.0 + 2.0 * r()} for k in itertools.product(range(T), repeat=2)})}
+    for k, p in priors.items():
+        p.name = k
+    idx = torch.arange(n)
+    bonds = torch.stack([idx[:-1], idx[1:]])
+    full = torch.cartesian_prod(idx, idx).t()
+    per = {"bonds_even": bonds[:, ::2], "bonds_odd": bonds[:, 1::2], "angles": torch.stack([idx[:-2], idx[1:-1], idx[2:]]),
+           "dih_short": torch.stack([idx[:-3], idx[1:-2], idx[2:-1], idx[3:]])[:, :4],
+           "dih_long": torch.stack([idx[:-3], idx[1:-2], idx[2:-1], idx[3:]])[:, 4:], "repulsion": full[:, (full[0] - full[1]).abs() >= 3]}
+    from helpers import random_walk_chain
+    data_list = []
+    for b in range(B):
+        nls = {k: mlcg_b200.make_neighbor_list(k, m.shape[0], m.clone()) for k, m in per.items()}
+        data_list.append(mlcg_b200.AtomicData(pos=random_walk_chain(n, gen, jitter=0.3), atom_types=torch.randint(0, T, (n,), generator=gen),
+                                              neighbor_list=nls))
+    model = bnn.SumOut(torch.nn.ModuleDict({k: bnn.GradientsOut(p, "forces") for k, p in priors.items()})).eval()
+    ref = model(collate(data_list))
+    cmodel, cdata = condense_all_priors_for_simulation(model, data_list)
+    assert set(cmodel.models.keys()) == {"bonds", "angles", "dihedrals", "repulsion"}
+    assert all(isinstance(cmodel.models[k].model, StaticPrior) for k in ("bonds", "angles", "dihedrals"))
+    assert set(cdata[0].neighbor_list.keys()) == {"bonds", "angles", "dihedrals", "repulsion"}
+    out = cmodel.eval()(collate(cdata))
+    assert torch.allclose(out.out["energy"], ref.out["energy"], rtol=1e-5)
+    assert torch.allclose(out.out["forces"], ref.out["forces"], rtol=1e-4, atol=1e-4 * float(ref.out["forces"].abs().max()))
+    # and a second pass finds nothing left to merge
+    again, _ = condense_all_priors_for_simulation(cmodel, cdata)
+    assert set(again.models.keys()) == set(cmodel.models.keys())
