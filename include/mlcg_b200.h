@@ -192,6 +192,12 @@ size_t mlcgb_gemm_tc_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K);
 int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int64_t M, int64_t N, int64_t K, void *C,
                   void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
 
+/* Mode 2 together with the column sums of A: C[M,N] = A[K,M]^T B[K,N], colsum[M] = sum_k A[k,:] — the weight and bias
+ * gradients of one Linear layer (torch.nn.Linear's backward) from one pass over the incoming gradient A.  Needs N % 4 == 0
+ * and a 16-byte aligned B (MLCGB_E_LIMIT otherwise); workspace as for mode 2. */
+int mlcgb_gemm_tc_tn_colsum(const void *A, const void *B, int64_t K, int64_t M, int64_t N, void *C, void *colsum /* [M] */,
+                            void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+
 /* Modes 0 and 1 of the above with the elementwise step that follows the Linear layer in an interaction block fused into
  * the store of C (src/mlcg/nn/schnet.py:252-262: activation after CFConv, Linear, and the residual sum at
  * schnet.py:150; their derivatives in the force pass).  `epilogue`:
@@ -232,6 +238,14 @@ int mlcgb_filter_backward(const void *d, int64_t rows, const int32_t *sel, const
                           int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1, const void *A2,
                           int64_t F, int precision, const int32_t *row0, const int32_t *row1, const void *xl /* [N,F] */,
                           const void *gagg /* [N,F] */, int64_t N, void *gd /* [E] */, int32_t *status, void *stream);
+
+/* The product of the filter network's output with the per-edge cutoff, W = net(rbf) * C[:, None]
+ * (src/mlcg/nn/schnet.py:341), and the contraction its derivatives need:
+ *   row_scale: out[e,:] = a[e,:] * c[e]          row_dot: out[e] = sum_f a[e,f] * b[e,f] */
+int mlcgb_row_scale(const void *a /* [E,F] */, const void *c /* [E] */, int dtype, int64_t E, int64_t F, void *out /* [E,F] */,
+                    void *stream);
+int mlcgb_row_dot(const void *a /* [E,F] */, const void *b /* [E,F] */, int dtype, int64_t E, int64_t F, void *out /* [E] */,
+                  void *stream);
 
 /* out[b] = sum_{n in [ptr[b],ptr[b+1])} x[n]  — the per-structure energy sum, src/mlcg/nn/schnet.py:158 */
 int mlcgb_segment_sum(const void *x /* [N] */, int dtype, const int64_t *ptr /* [B+1] */, int64_t B, void *out /* [B] */,

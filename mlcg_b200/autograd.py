@@ -244,8 +244,41 @@ class RbfContract(torch.autograd.Function):
     def backward(ctx, gs):
         d, G = ctx.saved_tensors
         gd = gs * RbfContract.apply(d, G, ctx.spec, ctx.order + 1) if ctx.needs_input_grad[0] else None
-        gG = gs.unsqueeze(-1) * RbfExpand.apply(d, ctx.spec, ctx.order) if ctx.needs_input_grad[1] else None
+        gG = RowScale.apply(RbfExpand.apply(d, ctx.spec, ctx.order), gs) if ctx.needs_input_grad[1] else None
         return gd, gG, None, None
+
+
+# ------------------------------------------------------------------------------- per-edge scalar x edge row
+class RowScale(torch.autograd.Function):
+    """out[e,:] = a[e,:] * c[e] (``net(rbf) * C[:, None]``, schnet.py:341); closed under differentiation with RowDot."""
+
+    @staticmethod
+    def forward(ctx, a, c):
+        ctx.save_for_backward(a, c)
+        return get_backend().row_scale(a, c)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, c = ctx.saved_tensors
+        ga = RowScale.apply(g, c) if ctx.needs_input_grad[0] else None
+        gc = RowDot.apply(g, a) if ctx.needs_input_grad[1] else None
+        return ga, gc
+
+
+class RowDot(torch.autograd.Function):
+    """out[e] = sum_f a[e,f] * b[e,f]."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return get_backend().row_dot(a, b)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        ga = RowScale.apply(b, g) if ctx.needs_input_grad[0] else None
+        gb = RowScale.apply(a, g) if ctx.needs_input_grad[1] else None
+        return ga, gb
 
 
 # ------------------------------------------------------------------------------- GEMM family
@@ -262,8 +295,11 @@ class MatmulNT(torch.autograd.Function):
     def backward(ctx, gY):
         X, W = ctx.saved_tensors
         gX = MatmulNN.apply(gY, W) if ctx.needs_input_grad[0] else None
-        gW = MatmulTN.apply(gY, X) if ctx.needs_input_grad[1] else None
-        gb = gY.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        if ctx.has_bias and ctx.needs_input_grad[2] and ctx.needs_input_grad[1]:
+            gW, gb = MatmulTNColsum.apply(gY, X)          # one pass over gY for both
+        else:
+            gW = MatmulTN.apply(gY, X) if ctx.needs_input_grad[1] else None
+            gb = gY.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return gX, gW, gb
 
 
@@ -281,6 +317,22 @@ class MatmulNN(torch.autograd.Function):
         gG = MatmulNT.apply(gZ, W) if ctx.needs_input_grad[0] else None
         gW = MatmulTN.apply(G, gZ) if ctx.needs_input_grad[1] else None
         return gG, gW
+
+
+class MatmulTNColsum(torch.autograd.Function):
+    """(P, s) = (G^T X, sum over rows of G): the weight and bias gradients of a Linear layer."""
+
+    @staticmethod
+    def forward(ctx, G, X):
+        ctx.save_for_backward(G, X)
+        return get_backend().gemm_tn_colsum(G, X)
+
+    @staticmethod
+    def backward(ctx, gP, gs):
+        G, X = ctx.saved_tensors
+        gG = MatmulNT.apply(X, gP, gs) if ctx.needs_input_grad[0] else None    # X gP^T + gs broadcast over the rows
+        gX = MatmulNN.apply(G, gP) if ctx.needs_input_grad[1] else None
+        return gG, gX
 
 
 class MatmulTN(torch.autograd.Function):

@@ -328,6 +328,27 @@ class CudaBackend:
             self._run("edge_mul", self.lib.mlcgb_edge_mul, (_ptr(a), _ptr(b), _dt(a), _ptr(ia), _ptr(ib), E, F, _ptr(out), _stream(),), **self._work("edge_mul", locals()))
         return out
 
+    def row_scale(self, a, c):
+        """out[e,:] = a[e,:] * c[e]."""
+        _need_cuda(a, c)
+        a, c = a.contiguous(), c.contiguous()
+        E, F = a.shape
+        out = torch.empty_like(a)
+        with torch.cuda.device(a.device):
+            self._run("row_scale", self.lib.mlcgb_row_scale, (_ptr(a), _ptr(c), _dt(a), E, F, _ptr(out), _stream(),), nbytes=(2 * a.numel() + E) * a.element_size())
+        return out
+
+    def row_dot(self, a, b):
+        """out[e] = sum_f a[e,f] * b[e,f]."""
+        _need_cuda(a, b)
+        a, b = a.contiguous(), b.contiguous()
+        E, F = a.shape
+        out = torch.empty(E, dtype=a.dtype, device=a.device)
+        with torch.cuda.device(a.device):
+            self._run("row_dot", self.lib.mlcgb_row_dot, (_ptr(a), _ptr(b), _dt(a), E, F, _ptr(out), _stream(),), nbytes=(2 * a.numel() + E) * a.element_size(),
+                      flops=2 * a.numel())
+        return out
+
     # ------------------------------------------------------------------ GEMM
     def gemm(self, mode: int, A, B, bias=None):
         """mode 0: A[M,K] B[N,K]^T (+bias); 1: A[M,K] B[K,N]; 2: A[K,M]^T B[K,N]."""
@@ -359,6 +380,25 @@ class CudaBackend:
                 bias = bias.contiguous()
             self._run("gemm", self.lib.mlcgb_gemm, (mode, _ptr(A), _ptr(B), _ptr(bias), dt, M, N, K, _ptr(C), _ptr(ws), wsb, _stream(),), **self._work("gemm", locals()))
         return C
+
+    def gemm_tn_colsum(self, G, X):
+        """(G^T X, column sums of G): weight and bias gradient of a Linear layer in one pass over G (contraction over rows)."""
+        _need_cuda(G, X)
+        G, X = G.contiguous(), X.contiguous()
+        (K, M), N = G.shape, X.shape[1]
+        if (self.tensor_core_gemm and G.dtype == torch.float32 and min(M, N, K) > 0 and N % 4 == 0 and X.data_ptr() % 16 == 0
+                and self.lib.mlcgb_gemm_tc_supported(2, M, N, K)):
+            C = torch.empty((M, N), dtype=G.dtype, device=G.device)
+            cs = torch.empty(M, dtype=G.dtype, device=G.device)
+            with torch.cuda.device(G.device):
+                wsb = self.lib.mlcgb_gemm_tc_workspace_bytes(2, M, N, K)
+                ws = torch.empty(wsb, dtype=torch.uint8, device=G.device)
+                status = self._sticky_status(G.device)
+                self._run("gemm_tc", self.lib.mlcgb_gemm_tc_tn_colsum, (_ptr(G), _ptr(X), K, M, N, _ptr(C), _ptr(cs), _ptr(ws), wsb, _ptr(status), _stream()),
+                          launches=3, nbytes=(M * K + N * K + M * N) * 4, flops=2 * M * N * K)
+                self.defer_status(status, "tensor-core GEMM")
+            return C, cs
+        return self.gemm(2, G, X), G.sum(0)
 
     EPI_NONE, EPI_TANH, EPI_ADD, EPI_TANH_GRAD = 0, 1, 2, 3
 

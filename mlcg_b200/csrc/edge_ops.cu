@@ -225,6 +225,54 @@ segment_sum_kernel(const T *__restrict__ x, const int64_t *__restrict__ ptr, int
     }
 }
 
+// ---------------------------------------------------------------------------- per-edge scalar times edge row
+// out[e,:] = a[e,:] * c[e]   (W = net(rbf) * C[:,None], schnet.py:341, and every derivative of that product)
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+row_scale_kernel(const T *__restrict__ a, const T *__restrict__ c, int64_t E, int64_t F, T *__restrict__ out) {
+    using VT = typename VecIO<T>::V;
+    constexpr int W = VEC ? VecIO<T>::W : 1;
+    const int64_t Fv = F / W, total = E * Fv;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e = t / Fv;
+        const T s = c[e];
+        if (VEC) {
+            VT v = ld_stream(reinterpret_cast<const VT *>(a) + t);
+            if constexpr (sizeof(T) == 4) v = make_float4(v.x * s, v.y * s, v.z * s, v.w * s);
+            else v = make_double2(v.x * s, v.y * s);
+            reinterpret_cast<VT *>(out)[t] = v;
+        } else {
+            out[t] = a[t] * s;
+        }
+    }
+}
+
+// out[e] = sum_f a[e,f] * b[e,f]: one warp per row, fixed-shape shuffle reduction
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+row_dot_kernel(const T *__restrict__ a, const T *__restrict__ b, int64_t E, int64_t F, T *__restrict__ out) {
+    using VT = typename VecIO<T>::V;
+    constexpr int W = VEC ? VecIO<T>::W : 1;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t Fv = F / W;
+    for (int64_t e = warp; e < E; e += nwarps) {
+        T s = T(0);
+        for (int64_t k = lane; k < Fv; k += 32) {
+            if (VEC) {
+                const VT x = ld_stream(reinterpret_cast<const VT *>(a + e * F) + k), y = ld_stream(reinterpret_cast<const VT *>(b + e * F) + k);
+                if constexpr (sizeof(T) == 4) s = fmaf(x.w, y.w, fmaf(x.z, y.z, fmaf(x.y, y.y, fmaf(x.x, y.x, s))));
+                else s = fma(x.y, y.y, fma(x.x, y.x, s));
+            } else {
+                s = fma(a[e * F + k], b[e * F + k], s);
+            }
+        }
+        s = warp_sum(s);
+        if (lane == 0) out[e] = s;
+    }
+}
+
 template <typename T>
 static int seg_mul_sum_launch(const void *a, const void *V, const int64_t *ptr, const int32_t *nbr, const int32_t *eperm,
                               int64_t N, int64_t F, void *out, cudaStream_t st) {
@@ -311,6 +359,34 @@ int mlcgb_segment_sum(const void *x, int dtype, const int64_t *ptr, int64_t B, v
     if (!x || !ptr || !out) return MLCGB_E_ARG;
     return MLCGB_DISPATCH_DTYPE(dtype, [&] {
         segment_sum_kernel<scalar_t><<<grid_for(B * 32, 256), 256, 0, (cudaStream_t)stream>>>((const scalar_t *)x, ptr, B, (scalar_t *)out);
+        return check_launch();
+    });
+}
+
+int mlcgb_row_scale(const void *a, const void *c, int dtype, int64_t E, int64_t F, void *out, void *stream) {
+    if (E < 0 || F <= 0) return MLCGB_E_ARG;
+    if (E == 0) return MLCGB_OK;
+    if (!a || !c || !out) return MLCGB_E_ARG;
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        constexpr int W = VecIO<scalar_t>::W;
+        const bool vec = (F % W == 0) && ((uintptr_t)a % 16 == 0) && ((uintptr_t)out % 16 == 0);
+        const int grid = grid_for(E * (vec ? F / W : F), 256, 32);
+        if (vec) row_scale_kernel<scalar_t, true><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)c, E, F, (scalar_t *)out);
+        else row_scale_kernel<scalar_t, false><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)c, E, F, (scalar_t *)out);
+        return check_launch();
+    });
+}
+
+int mlcgb_row_dot(const void *a, const void *b, int dtype, int64_t E, int64_t F, void *out, void *stream) {
+    if (E < 0 || F <= 0) return MLCGB_E_ARG;
+    if (E == 0) return MLCGB_OK;
+    if (!a || !b || !out) return MLCGB_E_ARG;
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        constexpr int W = VecIO<scalar_t>::W;
+        const bool vec = (F % W == 0) && ((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0);
+        const int grid = grid_for(E * 32, 256, 32);
+        if (vec) row_dot_kernel<scalar_t, true><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)b, E, F, (scalar_t *)out);
+        else row_dot_kernel<scalar_t, false><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)b, E, F, (scalar_t *)out);
         return check_launch();
     });
 }

@@ -485,7 +485,7 @@ struct GemmTnSmem {
 
 __global__ void __launch_bounds__(kGT, 1)
 gemm_tc_tn_pipe_kernel(const float *__restrict__ A, const float *__restrict__ B, int64_t E, int M, int N, float *__restrict__ partial,
-                       int32_t *__restrict__ status) {
+                       float *__restrict__ colsum_partial /* [gridDim.x][M] or NULL: column sums of A */, int32_t *__restrict__ status) {
     using namespace tc;
     using L = GemmTnSmem;
     extern __shared__ uint8_t smem_raw[];
@@ -522,6 +522,7 @@ gemm_tc_tn_pipe_kernel(const float *__restrict__ A, const float *__restrict__ B,
     const int64_t step = gridDim.x;
     float xa[32];
     float4 xb[8];
+    float csum = 0.f;                               // this thread's share of sum_e A[e][r]
     auto load_tile = [&](int64_t tile) {
         const int64_t e0 = tile * kRows;
 #pragma unroll
@@ -541,7 +542,10 @@ gemm_tc_tn_pipe_kernel(const float *__restrict__ A, const float *__restrict__ B,
     auto convert_issue = [&](int buf) {
         float amax = 0.f, bmax = 0.f;
 #pragma unroll
-        for (int j = 0; j < 32; j++) amax = fmaxf(amax, fabsf(xa[j]));
+        for (int j = 0; j < 32; j++) {
+            amax = fmaxf(amax, fabsf(xa[j]));
+            csum += xa[j];
+        }
 #pragma unroll
         for (int u = 0; u < 8; u++) bmax = fmaxf(fmaxf(bmax, fmaxf(fabsf(xb[u].x), fabsf(xb[u].y))), fmaxf(fabsf(xb[u].z), fabsf(xb[u].w)));
 #pragma unroll
@@ -633,6 +637,13 @@ gemm_tc_tn_pipe_kernel(const float *__restrict__ A, const float *__restrict__ B,
             for (int j = 0; j < 4; j++)
                 if (col0 + 4 * w + j < N) partial[((int64_t)blockIdx.x * M + r) * N + col0 + 4 * w + j] = o[j];
         }
+    if (colsum_partial) {                           // the four edge sub-ranges of each output row, in a fixed order
+        float *s_cs = reinterpret_cast<float *>(s_acc);
+        __syncthreads();
+        s_cs[qt * 128 + r] = csum;
+        __syncthreads();
+        if (qt == 0 && r < M) colsum_partial[(int64_t)blockIdx.x * M + r] = (s_cs[r] + s_cs[128 + r]) + (s_cs[256 + r] + s_cs[384 + r]);
+    }
     tc_fence_before();
     __syncthreads();
     if (*s_err && tid == 0) atomicOr(status, 8);
@@ -700,6 +711,27 @@ int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias
 }
 
 
+int mlcgb_gemm_tc_tn_colsum(const void *A, const void *B, int64_t K, int64_t M, int64_t N, void *C, void *colsum, void *workspace,
+                            size_t workspace_bytes, int32_t *status, void *stream) {
+    if (!A || !B || !C || !colsum || !status) return MLCGB_E_ARG;
+    if (!mlcgb_gemm_tc_supported(2, M, N, K) || (N & 3) != 0 || ((uintptr_t)B & 15) != 0) return MLCGB_E_LIMIT;
+    const int parts = tn_parts(K);
+    if (!workspace || workspace_bytes < (size_t)parts * M * (N + 1) * sizeof(float)) return MLCGB_E_WORKSPACE;
+    auto st = (cudaStream_t)stream;
+    static bool done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !done[dev]) {
+        if (cudaFuncSetAttribute(gemm_tc_tn_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmTnSmem::kTotal) != cudaSuccess) return check_launch();
+        done[dev] = true;
+    }
+    float *part = (float *)workspace, *cpart = part + (size_t)parts * M * N;
+    gemm_tc_tn_pipe_kernel<<<parts, kGT, GemmTnSmem::kTotal, st>>>((const float *)A, (const float *)B, K, (int)M, (int)N, part, cpart, status);
+    gemm_tc_reduce_kernel<<<grid_for(M * N, 256), 256, 0, st>>>(part, M * N, parts, (float *)C);
+    gemm_tc_reduce_kernel<<<grid_for(M, 256), 256, 0, st>>>(cpart, M, parts, (float *)colsum);
+    return check_launch();
+}
+
 int mlcgb_gemm_tc_supported(int mode, int64_t M, int64_t N, int64_t K) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (mode == 0 || mode == 1) return N <= 128 && K <= 128;   // M = edges
@@ -709,7 +741,7 @@ int mlcgb_gemm_tc_supported(int mode, int64_t M, int64_t N, int64_t K) {
 
 size_t mlcgb_gemm_tc_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K) {
     if (mode != 2 || !mlcgb_gemm_tc_supported(mode, M, N, K)) return 0;
-    return (size_t)tn_parts(K) * (size_t)M * (size_t)N * sizeof(float);
+    return (size_t)tn_parts(K) * (size_t)M * (size_t)(N + 1) * sizeof(float);   // partial products, and partial column sums
 }
 
 int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int64_t M, int64_t N, int64_t K, void *C, void *workspace,
@@ -742,7 +774,7 @@ int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int6
             if (cudaFuncSetAttribute(gemm_tc_tn_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmTnSmem::kTotal) != cudaSuccess) return check_launch();
             c3[dev] = true;
         }
-        gemm_tc_tn_pipe_kernel<<<parts, kGT, GemmTnSmem::kTotal, st>>>((const float *)A, (const float *)B, K, (int)M, (int)N, (float *)workspace, status);
+        gemm_tc_tn_pipe_kernel<<<parts, kGT, GemmTnSmem::kTotal, st>>>((const float *)A, (const float *)B, K, (int)M, (int)N, (float *)workspace, nullptr, status);
     } else {
         if (int rc = set_smem(gemm_tc_tn_kernel, c2)) return rc;
         gemm_tc_tn_kernel<<<parts, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, K, (int)M, (int)N, (float *)workspace, status);

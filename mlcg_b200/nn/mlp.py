@@ -23,10 +23,10 @@ def linear(layer: torch.nn.Linear, x: torch.Tensor, frozen: bool) -> torch.Tenso
 
 
 def node_linear(layer: torch.nn.Linear, x: torch.Tensor, training: bool) -> torch.Tensor:
-    """Node-sized Linear layers: in eval mode (forces only) on the tensor-core GEMM when the widths allow, else torch."""
-    if (not training and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and layer.in_features <= 128
-            and layer.out_features <= 128):
-        return linear(layer, x, frozen=True)
+    """Node-sized Linear layers on the tensor-core GEMMs when the widths allow, else torch.  In eval mode (forces only) the
+    weights are constants; in training mode they stay in the graph (the operators are differentiable to any order)."""
+    if x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and layer.in_features <= 128 and layer.out_features <= 128:
+        return linear(layer, x, frozen=not training)
     return layer(x)
 
 
@@ -47,8 +47,9 @@ class MLP(torch.nn.Module):
             init_xavier_uniform(layer)
 
     def forward(self, x, data=None):
-        if not self.training and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2:
-            return self.forward_edges(x, frozen=True)     # eval: fp32-equivalent tensor-core GEMMs, weights as constants
+        if x.is_cuda and x.dtype == torch.float32 and x.dim() == 2:
+            # fp32-equivalent tensor-core GEMMs; in eval mode the weights are constants, in training they stay in the graph
+            return self.forward_edges(x, frozen=not self.training)
         return self.layers(x)
 
     def forward_edges(self, x: torch.Tensor, frozen: bool = False) -> torch.Tensor:

@@ -8,7 +8,7 @@ from typing import Final, List
 
 import torch
 
-from ..autograd import EdgeDistanceOnce, FusedFilterConv, FusedInteraction, SegIn, SegmentSum, edge_distances, plan_of
+from ..autograd import EdgeDistanceOnce, FusedFilterConv, FusedInteraction, RowScale, SegIn, SegmentSum, edge_distances, plan_of
 from ..backend import get_backend
 from ..data import ENERGY_KEY
 from ..neighbor_list import atomic_data2neighbor_list, validate_neighborlist
@@ -85,7 +85,7 @@ class CFConv(torch.nn.Module):
         # eval mode evaluates energies and forces only (GradientsOut uses create_graph=False there), so the
         # filter weights are constants; training mode keeps them differentiable to second order
         h = net.forward_edges(edge_attr, frozen=not self.training) if isinstance(net, MLP) else net(edge_attr)
-        return h * C.view(-1, 1)
+        return RowScale.apply(h, C.reshape(-1)) if h.dim() == 2 and C.numel() == h.shape[0] else h * C.view(-1, 1)
 
     def forward(self, x: torch.Tensor, edge_index: torch.Tensor, edge_weight: torch.Tensor, edge_attr: torch.Tensor) -> torch.Tensor:
         plan = plan_of(edge_index, x.shape[0])
@@ -100,9 +100,9 @@ class CFConv(torch.nn.Module):
             edge_attr = edge_attr.materialize()
         symmetric = bool(getattr(edge_weight, _SYM, False) and getattr(edge_attr, _SYM, False))
         W = self.filters(edge_weight, edge_attr)
-        x = self.lin1(x)
+        x = node_linear(self.lin1, x, self.training)
         x = SegIn.apply(x, W, plan, symmetric)      # x_j = x[edge_index[0]], summed at edge_index[1]
-        return self.lin2(x)
+        return node_linear(self.lin2, x, self.training)
 
     def message(self, x_j: torch.Tensor, W: torch.Tensor) -> torch.Tensor:
         return x_j * W

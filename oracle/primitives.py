@@ -115,6 +115,15 @@ class OracleBackend:
     def edge_mul(self, a, b, ia, ib):
         return a[ia.long()] * b[ib.long()]
 
+    def gemm_tn_colsum(self, G, X):
+        return G.t() @ X, G.sum(0)
+
+    def row_scale(self, a, c):
+        return a * c.unsqueeze(-1)
+
+    def row_dot(self, a, b):
+        return (a * b).sum(dim=1)
+
     def gemm(self, mode, A, B, bias=None):
         if mode == 0:
             C = A @ B.t()

@@ -228,3 +228,26 @@ def test_tensor_core_gemm_fused_epilogues(M, N, K):
         err = float((got.cpu().double() - want).abs().max())
         assert err < 5e-6 * max(1.0, float(want.abs().max())), (mode, epi, err)
     get_backend().check_pending()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("E,F", [(1000, 128), (37, 50), (0, 128), (5000, 64)])
+def test_row_scale_and_row_dot(dtype, E, F):
+    gen = torch.Generator().manual_seed(E + F)
+    a, b, c = torch.randn(E, F, generator=gen, dtype=dtype), torch.randn(E, F, generator=gen, dtype=dtype), torch.randn(E, generator=gen, dtype=dtype)
+    be = get_backend()
+    assert torch.equal(be.row_scale(a.to(DEV), c.to(DEV)).cpu(), ORA.row_scale(a, c))
+    tol = 1e-5 if dtype == torch.float32 else 1e-13
+    assert torch.allclose(be.row_dot(a.to(DEV), b.to(DEV)).cpu(), ORA.row_dot(a, b), rtol=tol, atol=tol * F ** 0.5)
+
+
+@pytest.mark.parametrize("K,M,N", [(40000, 128, 128), (1000, 128, 64), (333, 1, 128), (129, 64, 128)])
+def test_weight_and_bias_gradient_in_one_pass(K, M, N):
+    gen = torch.Generator().manual_seed(K + M + N)
+    G = torch.randn(K, M, generator=gen) * torch.exp(torch.randn(K, 1, generator=gen))
+    X = torch.randn(K, N, generator=gen)
+    P, s = get_backend().gemm_tn_colsum(G.to(DEV), X.to(DEV))
+    want_P, want_s = G.double().t() @ X.double(), G.double().sum(0)
+    assert float((P.cpu().double() - want_P).abs().max()) < 2e-5 * float(want_P.abs().max())
+    assert float((s.cpu().double() - want_s).abs().max()) < 1e-5 * float(G.abs().sum(0).max())
+    get_backend().check_pending()
