@@ -36,7 +36,8 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    return torch.cuda.current_stream().cuda_stream
+    """Raw handle of torch's current stream on the current device."""
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
 def _need_cuda(*ts):
@@ -128,9 +129,11 @@ class CudaBackend:
         if prof is not None:
             prof.end(name, ev)
 
-    @staticmethod
-    def _work(name, v):
-        """Algorithmic bytes / flops and kernel launches of one call (index tensors counted at their stored width)."""
+    def _work(self, name, v):
+        """Algorithmic bytes / flops and kernel launches of one call (index tensors counted at their stored width); only
+        worked out while a profiler is attached."""
+        if self.profiler is None:
+            return {}
         es = lambda t: t.element_size()
         if name == "radius_count":
             return dict(launches=5, nbytes=v["N"] * (12 + 4 + 8) + v["B"] * 8)
