@@ -411,7 +411,7 @@ def run_ours(args):
                        TFLOPs=(v["flops"] / v["ms"] / 1e9 if v["ms"] > 0 and v["flops"] else None)) for k, v in sorted(stats.items(), key=lambda kv: -kv[1]["ms"])}
 
     cpu = None
-    if not args.no_cpu:
+    if not args.no_cpu and world == 1:        # the CPU leg is timed at N = 1 only (other ranks would share the host cores)
         sample_B = 32
         v, ms, cores = cpu_leg(sample_B, 3, 1)
         cpu = dict(value=v, unit="structures/s", cores=cores, kind="port",
