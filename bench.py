@@ -420,9 +420,17 @@ def run_ours(args):
     extras = None
     if not args.no_extras:
         try:
+            # the same step with the filter-network GEMMs on bf16 operands (forces within 1e-2 relative RMS of the fp32 mode)
+            bnn.set_filter_precision(model, "bf16")
+            for _ in range(3):
+                step_resident()
+            bf16_ms = timed_steps()
+            bnn.set_filter_precision(model, "fp32")
             del flush
             torch.cuda.empty_cache()
             extras = extra_measurements(dev, hbm_peak)
+            extras["bf16_filter_mode"] = dict(ms_per_step=sum(bf16_ms) / len(bf16_ms), structures_per_s=B / (sum(bf16_ms) / len(bf16_ms) / 1e3),
+                                              note="same workload, filter-network GEMMs with bf16 operands (one product, tanh.approx)")
         except Exception as exc:   # the headline line is still printed
             extras = {"error": repr(exc)}
 
