@@ -11,6 +11,8 @@
 // Precision modes.  0: every fp32 value is carried as an fp16 pair (value = hi + lo, ~22 bits) and
 // each GEMM runs hi*hi + hi*lo + lo*hi with fp32 accumulation — the products an fp32 GEMM forms, at
 // half-precision tensor-core rate.  1: operands rounded to bf16, one product, tanh.approx.
+#include <type_traits>
+
 #include "rbf_device.cuh"
 #include "tc_common.cuh"
 #include "tensor_map.cuh"
@@ -492,26 +494,41 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
         ISSUE(T1, b2_hi, b2_lo, kF / 16, 0, 128)
 
         // ---- under GEMM 2: gW = xl[row0] * gagg[row1] for this warp's 32 rows x 32 columns, four rows per instruction,
-        //      turned row-per-lane through shared memory
+        //      turned row-per-lane through shared memory; the loads of four instructions' worth of rows are issued together
         {
             const int sub = lane >> 3, cc = (col0 >> 2) + (lane & 7);
+            auto gather = [&](auto paired_tag) {
+                constexpr bool kPaired = decltype(paired_tag)::value;
 #pragma unroll
-            for (int it = 0; it < 8; it++) {
-                const int rl = it * 4 + sub;
-                const int64_t j0 = __shfl_sync(0xffffffffu, i0, rl), j1 = __shfl_sync(0xffffffffu, i1, rl);
-                const int lv = __shfl_sync(0xffffffffu, (int)live, rl);
-                const float4 a = __ldg(reinterpret_cast<const float4 *>(q.xl + j0 * kF) + cc);
-                const float4 b = __ldg(reinterpret_cast<const float4 *>(q.gagg + j1 * kF) + cc);
-                const float m = lv ? 1.f : 0.f;
-                float4 gw = make_float4(a.x * b.x * m, a.y * b.y * m, a.z * b.z * m, a.w * b.w * m);
-                if (paired) {   // the reverse edge: xl[row1] * gagg[row0]
-                    const float4 a2 = __ldg(reinterpret_cast<const float4 *>(q.xl + j1 * kF) + cc);
-                    const float4 b2 = __ldg(reinterpret_cast<const float4 *>(q.gagg + j0 * kF) + cc);
-                    gw.x = fmaf(a2.x * b2.x, m, gw.x); gw.y = fmaf(a2.y * b2.y, m, gw.y);
-                    gw.z = fmaf(a2.z * b2.z, m, gw.z); gw.w = fmaf(a2.w * b2.w, m, gw.w);
+                for (int half = 0; half < 2; half++) {
+                    float4 a[4], b[4], a2[4], b2[4];
+                    float m[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int rl = (half * 4 + u) * 4 + sub;
+                        const int64_t j0 = __shfl_sync(0xffffffffu, i0, rl), j1 = __shfl_sync(0xffffffffu, i1, rl);
+                        m[u] = __shfl_sync(0xffffffffu, (int)live, rl) ? 1.f : 0.f;
+                        a[u] = __ldg(reinterpret_cast<const float4 *>(q.xl + j0 * kF) + cc);
+                        b[u] = __ldg(reinterpret_cast<const float4 *>(q.gagg + j1 * kF) + cc);
+                        if (kPaired) {   // the reverse edge: xl[row1] * gagg[row0]
+                            a2[u] = __ldg(reinterpret_cast<const float4 *>(q.xl + j1 * kF) + cc);
+                            b2[u] = __ldg(reinterpret_cast<const float4 *>(q.gagg + j0 * kF) + cc);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int rl = (half * 4 + u) * 4 + sub;
+                        float4 gw = make_float4(a[u].x * b[u].x * m[u], a[u].y * b[u].y * m[u], a[u].z * b[u].z * m[u], a[u].w * b[u].w * m[u]);
+                        if (kPaired) {
+                            gw.x = fmaf(a2[u].x * b2[u].x, m[u], gw.x); gw.y = fmaf(a2[u].y * b2[u].y, m[u], gw.y);
+                            gw.z = fmaf(a2[u].z * b2[u].z, m[u], gw.z); gw.w = fmaf(a2[u].w * b2[u].w, m[u], gw.w);
+                        }
+                        *stage_chunk(stage, (r & ~31) + rl, cc) = gw;
+                    }
                 }
-                *stage_chunk(stage, (r & ~31) + rl, cc) = gw;
-            }
+            };
+            if (paired) gather(std::true_type{});
+            else gather(std::false_type{});
             __syncwarp();
         }
         AWAIT()
