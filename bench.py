@@ -109,7 +109,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample_B = 32
+    sample_B = 128
     value, ms, cores = cpu_leg(sample_B, max(args.steps, 1), max(args.warmup, 1))
     sample = f"{sample_B} structures of the same workload per step (of 512), torch CPU float32, radius graph rebuilt each step"
     line = dict(metric=METRIC, value=value, unit="structures/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup, ms_per_step=ms,
@@ -412,10 +412,10 @@ def run_ours(args):
 
     cpu = None
     if not args.no_cpu and world == 1:        # the CPU leg is timed at N = 1 only (other ranks would share the host cores)
-        sample_B = 32
-        v, ms, cores = cpu_leg(sample_B, 3, 1)
+        sample_B = 128
+        v, ms, cores = cpu_leg(sample_B, 16, 1)     # about 10 s of host work
         cpu = dict(value=v, unit="structures/s", cores=cores, kind="port",
-                   sample=f"{sample_B} structures of the same workload per step, 3 steps after 1 warm-up, torch CPU float32 + C radius oracle")
+                   sample=f"{sample_B} structures of the same workload per step, 16 steps after 1 warm-up, torch CPU float32 + C radius oracle")
 
     extras = None
     if not args.no_extras:
