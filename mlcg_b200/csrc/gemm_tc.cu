@@ -658,9 +658,13 @@ __global__ void gemm_tc_reduce_kernel(const float *__restrict__ partial, int64_t
     }
 }
 
+// CTAs of the TN kernels (each writes one [M,N] partial): one per SM for edge-sized contractions; for short ones at least
+// four tiles per CTA, so that the set-up and the reduction over partials do not outweigh the tiles
 static int tn_parts(int64_t K) {
     const int64_t ntiles = (K + tc::kRows - 1) / tc::kRows;
-    return (int)(ntiles < kNumSM ? (ntiles < 1 ? 1 : ntiles) : kNumSM);
+    int64_t parts = (ntiles + 3) / 4;
+    if (parts > kNumSM) parts = kNumSM;
+    return (int)(parts < 1 ? 1 : parts);
 }
 
 template <typename Kern>

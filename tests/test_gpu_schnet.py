@@ -227,3 +227,36 @@ def test_ragged_batch_with_isolated_beads_and_no_edges():
         tr = bnn.GradientsOut(model, "forces").train()(mlcg_b200.AtomicData(pos=pos.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV),
                                                                              n_atoms=torch.tensor(sizes).to(DEV)))
         assert float((tr.out["SchNet"]["forces"].detach().cpu() - f_ref).abs().max()) < F_ATOL
+
+
+def test_condensed_priors_on_the_device():
+    """Merged Static priors (specialize_prior.py) through the CUDA prior kernel: same totals as the separate priors."""
+    import itertools
+    from mlcg_b200.data import collate
+    from mlcg_b200.specialize_prior import condense_all_priors_for_simulation
+    from helpers import random_walk_chain
+    gen = torch.Generator().manual_seed(4)
+    T, n, B = 3, 40, 6
+    r = lambda: float(torch.rand(1, generator=gen))
+    tab2 = lambda: {k: {"k": 50 + 100 * r(), "x_0": 3.5 + 0.6 * r()} for k in itertools.product(range(T), repeat=2)}
+    def tab4(nd):
+        return {k: {"v_0": r(), "k1s": {f"k1_{i}": r() - 0.5 for i in range(1, nd + 1)}, "k2s": {f"k2_{i}": r() - 0.5 for i in range(1, nd + 1)}}
+                for k in itertools.product(range(T), repeat=4)}
+    priors = {"bonds_even": bnn.HarmonicBonds(tab2()), "bonds_odd": bnn.HarmonicBonds(tab2()),
+              "dih_short": bnn.Dihedral(tab4(2), n_degs=2, name="dih_short"), "dih_long": bnn.Dihedral(tab4(3), n_degs=3, name="dih_long")}
+    for k, p in priors.items():
+        p.name = k
+    idx = torch.arange(n)
+    bonds = torch.stack([idx[:-1], idx[1:]])
+    dih = torch.stack([idx[:-3], idx[1:-2], idx[2:-1], idx[3:]])
+    per = {"bonds_even": bonds[:, ::2], "bonds_odd": bonds[:, 1::2], "dih_short": dih[:, :10], "dih_long": dih[:, 10:]}
+    data_list = [mlcg_b200.AtomicData(pos=random_walk_chain(n, gen, jitter=0.3), atom_types=torch.randint(0, T, (n,), generator=gen),
+                                      neighbor_list={k: mlcg_b200.make_neighbor_list(k, m.shape[0], m.clone()) for k, m in per.items()})
+                 for _ in range(B)]
+    model = bnn.SumOut(torch.nn.ModuleDict({k: bnn.GradientsOut(p, "forces") for k, p in priors.items()})).eval().to(DEV)
+    ref = model(collate(data_list).to(DEV))
+    cmodel, cdata = condense_all_priors_for_simulation(model.cpu(), data_list)
+    out = cmodel.eval().to(DEV)(collate(cdata).to(DEV))
+    assert set(cmodel.models.keys()) == {"bonds", "dihedrals"}
+    assert torch.allclose(out.out["energy"], ref.out["energy"], rtol=1e-5)
+    assert torch.allclose(out.out["forces"], ref.out["forces"], rtol=1e-4, atol=1e-4 * float(ref.out["forces"].abs().max()))
