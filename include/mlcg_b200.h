@@ -186,7 +186,8 @@ int mlcgb_gemm(int mode, const void *A, const void *B, const void *bias /* [N] o
 /* The same three GEMMs on the tensor cores (tcgen05, fp16 hi/lo pairs, three products per GEMM, fp32
  * accumulation in tensor memory): float32 only, the two weight-sized dimensions at most 128 (modes 0/1: N, K <= 128,
  * M = edges; mode 2: M, N <= 128, K = edges).  mlcgb_gemm_tc_supported tells whether a shape qualifies;
- * status bit 3 reports a tensor-core wait that ran out. */
+ * status bit 3 reports a tensor-core wait that ran out, bit 4 a weight beyond the range of the fp16-pair operands
+ * (|w| > 512: the result is then not to be used; mlcgb_gemm computes such layers on the CUDA cores). */
 int mlcgb_gemm_tc_supported(int mode, int64_t M, int64_t N, int64_t K);
 size_t mlcgb_gemm_tc_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K);
 int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int64_t M, int64_t N, int64_t K, void *C,
@@ -215,7 +216,8 @@ int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias
  * basis of src/mlcg/nn/radial_basis/*.py evaluated in the GEMM prologue.  float32 in / out, F = 128,
  * R <= 128, tanh activation.  precision 0: fp32-equivalent products (fp16 hi/lo pairs, three tensor-core
  * products per GEMM, fp32 accumulation); precision 1: bf16 operands, one product.
- * status bit 3 is set if a tensor-core wait ran out (the output is then incomplete).
+ * status bit 3 is set if a tensor-core wait ran out (the output is then incomplete), bit 4 if a weight of the filter
+ * network is beyond the range of the fp16-pair operands (|w| > 512, precision 0).
  * ---------------------------------------------------------------------------------------------- */
 int mlcgb_filter_forward(const void *d /* [.] */, int64_t rows, const int32_t *sel /* [rows] or NULL */,
                          const int32_t *twin /* [E] or NULL */, const mlcgb_rbf_spec *rbf /* host */, int conv_cutoff_kind,

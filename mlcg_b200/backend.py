@@ -46,6 +46,15 @@ def _need_cuda(*ts):
             raise RuntimeError("mlcg_b200 operators run on CUDA tensors only (there is no CPU fallback)")
 
 
+def _raise_for_status(word: int, what: str) -> None:
+    """Status bits the tensor-core kernels set (read lazily, with the next unavoidable host read)."""
+    if word & 8:
+        raise RuntimeError(f"mlcg_b200: {what}: a tensor-core wait ran out; results are incomplete")
+    if word & 16:
+        raise RuntimeError(f"mlcg_b200: {what}: a weight is beyond the range of the fp16-pair tensor-core operands (|w| > 512); "
+                           "set mlcg_b200.backend.get_backend().tensor_core_gemm = False to run these layers on the CUDA cores")
+
+
 def _dt(t: torch.Tensor) -> int:
     try:
         return _DT[t.dtype]
@@ -119,8 +128,7 @@ class CudaBackend:
             return
         words = torch.stack([s[0] for s, _ in pending]).cpu().tolist()
         for w, (_, what) in zip(words, pending):
-            if w & 8:
-                raise RuntimeError(f"mlcg_b200: {what}: a tensor-core wait ran out; results are incomplete")
+            _raise_for_status(w, what)
 
     def _run(self, name, fn, args, what=None, launches=1, nbytes=0, flops=0):
         prof = self.profiler
@@ -204,8 +212,7 @@ class CudaBackend:
             tail = torch.stack([offsets[N], status[0].to(torch.int64)] + extra).cpu().tolist()   # the one host read
             E, st = int(tail[0]), int(tail[1])
             for w, (_, what) in zip(tail[2:], pend):
-                if w & 8:
-                    raise RuntimeError(f"mlcg_b200: {what}: a tensor-core wait ran out; results are incomplete")
+                _raise_for_status(w, what)
             ei = torch.empty((2, E), dtype=torch.int64, device=dev)
             dist = torch.empty(E, dtype=pos.dtype, device=dev) if want_distance else None
             mb = torch.empty(E, dtype=torch.int64, device=dev) if want_batch else None

@@ -89,8 +89,9 @@ __device__ __forceinline__ uint32_t filter_setup(const FilterFwdParams &p, uint8
     using L = FilterSmem<SPLIT>;
     const int tid = threadIdx.x, warp = tid >> 5;
     const float wscale = SPLIT ? kWScale : 1.f;
-    load_weight_tile<SPLIT>(smem + L::kB1, smem + L::kB1 + 32768, p.A1, kF, p.rbf.R, Kpad1, wscale);
-    load_weight_tile<SPLIT>(smem + L::kB2, smem + L::kB2 + 32768, p.A2, kF, kF, kF, wscale);
+    const bool over1 = load_weight_tile<SPLIT>(smem + L::kB1, smem + L::kB1 + 32768, p.A1, kF, p.rbf.R, Kpad1, wscale);
+    const bool over2 = load_weight_tile<SPLIT>(smem + L::kB2, smem + L::kB2 + 32768, p.A2, kF, kF, kF, wscale);
+    if ((over1 || over2) && blockIdx.x == 0) atomicOr(p.status, (int)kWeightRange);
     float *s_b1 = reinterpret_cast<float *>(smem + L::kMisc + L::kBias);
     float2 *s_tab = reinterpret_cast<float2 *>(smem + L::kMisc + L::kTable);
     if (tid < kF) {

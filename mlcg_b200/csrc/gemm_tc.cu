@@ -114,7 +114,7 @@ gemm_tc_rows_kernel(const float *__restrict__ A, const float *__restrict__ B, co
     // operand tile of the weight: NT: rows = n, K-major;  NN: rows = k, read as an MN-major operand
     const int wrows = MODE == 0 ? N : K, wcols = MODE == 0 ? K : N;
     const int wpad = wcols <= 64 ? 64 : 128;
-    load_weight_tile<true>(sB_hi, sB_lo, B, wrows, wcols, wpad, kWS);
+    if (load_weight_tile<true>(sB_hi, sB_lo, B, wrows, wcols, wpad, kWS) && blockIdx.x == 0) atomicOr(status, (int)kWeightRange);
     if (tid < 128) s_bias[tid] = (bias && tid < N) ? bias[tid] : 0.f;
     const uint32_t bar = smem_u32(s_bar);
     if (tid == 0) {
@@ -242,7 +242,7 @@ gemm_tc_rows_pipe_kernel(const float *__restrict__ A, const float *__restrict__ 
     if (t0 < ntiles) prefetch_tile_to_stage(s_in, A, t0 * kRows, E, K);      // under the set-up below
     const int wrows = MODE == 0 ? N : K, wcols = MODE == 0 ? K : N;
     const int wpad = wcols <= 64 ? 64 : 128;
-    load_weight_tile<true>(sB_hi, sB_lo, B, wrows, wcols, wpad, kWS);
+    if (load_weight_tile<true>(sB_hi, sB_lo, B, wrows, wcols, wpad, kWS) && blockIdx.x == 0) atomicOr(status, (int)kWeightRange);
     if (tid < 128) s_bias[tid] = (bias && tid < N) ? bias[tid] : 0.f;
     const uint32_t bar0 = smem_u32(s_bar);
     if (tid == 0) {

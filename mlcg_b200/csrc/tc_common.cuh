@@ -149,10 +149,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
 // Fill a [128][Kpad] weight tile (and its low part) from a row-major fp32 matrix src[rows][K], scaled by `scale`.
 // Four consecutive K elements of a row are 8 contiguous bytes of the swizzled tile, so with K % 4 == 0 and a 16-byte
 // aligned source every thread moves float4 -> 8 bytes, with all its loads issued before the first conversion.
+// Returns true if this thread saw a scaled weight too large for a 16-bit operand (|w * scale| > 32768 with fp16 pairs):
+// the caller reports it through its status word instead of computing with infinities.
 template <bool SPLIT>
-__device__ __forceinline__ void load_weight_tile(uint8_t *hi, uint8_t *lo, const float *__restrict__ src, int rows, int K, int Kpad,
+__device__ __forceinline__ bool load_weight_tile(uint8_t *hi, uint8_t *lo, const float *__restrict__ src, int rows, int K, int Kpad,
                                                  float scale) {
+    float wmax = 0.f;
     auto put4 = [&](int n, int k, float4 w) {
+        wmax = fmaxf(fmaxf(wmax, fmaxf(fabsf(w.x), fabsf(w.y))), fmaxf(fabsf(w.z), fabsf(w.w)));
         const uint32_t off = elem_offset(n, k);
         if (SPLIT) {
             const __half2 a0 = __floats2half2_rn(w.x * scale, w.y * scale), a1 = __floats2half2_rn(w.z * scale, w.w * scale);
@@ -185,7 +189,7 @@ __device__ __forceinline__ void load_weight_tile(uint8_t *hi, uint8_t *lo, const
                 }
             }
         }
-        return;
+        return SPLIT && !(wmax * scale <= 32768.f);
     }
     for (int qd = threadIdx.x; qd < nquads; qd += blockDim.x) {
         const int n = qd / qpr, k = (qd - n * qpr) << 2;
@@ -194,6 +198,7 @@ __device__ __forceinline__ void load_weight_tile(uint8_t *hi, uint8_t *lo, const
         for (int j = 0; j < 4; j++) v[j] = (n < rows && k + j < K) ? src[(int64_t)n * K + k + j] : 0.f;
         put4(n, k, make_float4(v[0], v[1], v[2], v[3]));
     }
+    return SPLIT && !(wmax * scale <= 32768.f);     // (also true for NaN weights)
 }
 
 // ---- A operand in tensor memory -----------------------------------------------------------------------

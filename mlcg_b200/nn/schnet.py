@@ -66,6 +66,8 @@ class CFConv(torch.nn.Module):
         net = self.filter_network
         if self.training or not isinstance(net, MLP) or len(net.layers) != 3 or not hasattr(rbf_layer, "spec"):
             return None
+        if not getattr(get_backend(), "tensor_core_gemm", False):     # the switch that sends every GEMM to the CUDA cores
+            return None
         l0, act, l2 = net.layers
         if not (isinstance(l0, torch.nn.Linear) and isinstance(l2, torch.nn.Linear) and isinstance(act, torch.nn.Tanh)):
             return None

@@ -132,3 +132,36 @@ def test_pair_mode_equals_per_edge_mode():
     total_pair = g_pair + g_pair[tw]
     assert bool((g_pair[tw[sel.long()]] == 0).all())
     assert float((total_full - total_pair).abs().max()) < 2e-5 * float(total_full.abs().max())
+
+
+def test_weights_beyond_the_fp16_pair_range_are_reported():
+    """|w| > 512 cannot be carried by the scaled fp16 operand pairs: the kernel says so through its status word, and with
+    the tensor-core route switched off the same model evaluates on the CUDA cores."""
+    from mlcg_b200 import nn as bnn
+    import mlcg_b200
+    gen = torch.Generator().manual_seed(0)
+    torch.manual_seed(0)
+    cut = bnn.CosineCutoff(0.0, 8.0)
+    net = bnn.StandardSchNet(bnn.ExpNormalBasis(cut, 32, trainable=False), cut, [128], hidden_channels=128, embedding_size=5,
+                             num_filters=128, num_interactions=1).to(DEV)
+    with torch.no_grad():
+        net.interaction_blocks[0].conv.filter_network.layers[0].weight[3, 5] = 2000.0
+    model = bnn.GradientsOut(net, "forces").eval()
+    B, n = 8, 20
+    v = torch.randn(B, n, 3, generator=gen)
+    pos = torch.cumsum(3.8 * v / v.norm(dim=2, keepdim=True), dim=1).reshape(B * n, 3).to(DEV)
+    mk = lambda: mlcg_b200.AtomicData(pos=pos.clone(), atom_types=torch.randint(0, 5, (B * n,), generator=gen).to(DEV),
+                                      batch=torch.arange(B).repeat_interleave(n).to(DEV), n_atoms=torch.full((B,), n).to(DEV))
+    be = get_backend()
+    be.check_pending()
+    model(mk())
+    with pytest.raises(RuntimeError, match="range of the fp16-pair"):
+        be.check_pending()
+    be._status.clear()                    # the sticky status word keeps its bits: start from a clean one
+    be.tensor_core_gemm = False
+    try:
+        out = model(mk())
+        be.check_pending()
+        assert bool(torch.isfinite(out.out["SchNet"]["forces"]).all())
+    finally:
+        be.tensor_core_gemm = True
