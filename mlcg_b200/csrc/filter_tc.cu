@@ -421,6 +421,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
     // per-row scalars: basis argument and its derivative, envelope of the basis and its derivative, CFConv cutoff C(d) and
     // C'(d) (the envelope again when both use the same cutoff, as SchNet builds them)
     const bool same_env = p.conv.cutoff_kind == p.rbf.cutoff_kind && p.conv.lower == p.rbf.lower && p.conv.upper == p.rbf.upper;
+    // The four column quarters of a row sit in warps w, w+4, w+8, w+12: exchanges between them (row maxima, row sums) need only
+    // those 128 threads, on a named barrier of their own (ids 1-4; every such exchange is separated from the next use of its
+    // shared-memory slots by a CTA-wide barrier of the GEMM issue).
+    auto row_group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + (warp & 3)) : "memory"); };
     struct EdgeScalars { float t, dt, e0, e1, c0, c1; };
     auto scalars = [&](float de) {
         EdgeScalars s;
@@ -555,7 +559,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
         }
         s_red[qt * 128 + r] = rmax;
         s_red2[qt * 128 + r] = gC * unscale;
-        __syncthreads();
+        row_group_sync();
         gC = (s_red2[r] + s_red2[128 + r]) + (s_red2[256 + r] + s_red2[384 + r]);
         const float sc3 = SPLIT ? row_scale(fmaxf(fmaxf(s_red[r], s_red[128 + r]), fmaxf(s_red[256 + r], s_red[384 + r]))) : 1.f;
         store_a_tmem<SPLIT>(tmem + TA + lane_off, col0, g, sc3);
@@ -589,7 +593,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
             }
         }
         s_red[qt * 128 + r] = rmax;
-        __syncthreads();
+        row_group_sync();
         const float sc4 = SPLIT ? row_scale(fmaxf(fmaxf(s_red[r], s_red[128 + r]), fmaxf(s_red[256 + r], s_red[384 + r]))) : 1.f;
         store_a_tmem<SPLIT>(tmem + TA + lane_off, col0, g, sc4);
         tmem_wait_st();
@@ -634,7 +638,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
         if (qt == 0) acc += gC_dC;
         s_red2[qt * 128 + r] = acc;
         tc_fence_before();
-        __syncthreads();
+        row_group_sync();
         if (qt == 0 && live) {
             q.gd[e] = (s_red2[r] + s_red2[128 + r]) + (s_red2[256 + r] + s_red2[384 + r]);
             if (paired) q.gd[p.twin[e]] = 0.f;   // the pair's whole gradient is carried by one of its two edges
