@@ -208,7 +208,8 @@ __device__ __forceinline__ bool is_excluded(const int64_t *__restrict__ xs, int6
     return false;
 }
 
-template <typename T, bool FILL>
+// EXCL: compiled with the exclusion test (kept out of the plain kernels, whose inner loop is issue-bound)
+template <typename T, bool FILL, bool EXCL>
 __global__ void __launch_bounds__(kNbrWarps * 32)
 neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t N, int64_t B, T r2,
                   int64_t max_nn, int loop, int rule, const V4<T> *__restrict__ spos,
@@ -227,7 +228,7 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
         const int64_t lo = ptr[b];
         const int n = (int)(ptr[b + 1] - lo);
         const int il = (int)(i - lo);
-        const int64_t ex0 = ex.ptr ? ex.ptr[i] : 0, ex1 = ex.ptr ? ex.ptr[i + 1] : 0;   // this centre's excluded neighbours
+        const int64_t ex0 = EXCL ? ex.ptr[i] : 0, ex1 = EXCL ? ex.ptr[i + 1] : 0;   // this centre's excluded neighbours
         const T xi = pos[i * 3], yi = pos[i * 3 + 1], zi = pos[i * 3 + 2];
         const CellParam cp = cellparam[b];
 
@@ -248,7 +249,7 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
                 if (j < n) {
                     const int64_t gj = lo + j;
                     d2 = dist2_rn(xi, yi, zi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]);
-                    hit = d2 < r2 && !(ex1 > ex0 && is_excluded(ex.xs, ex0, ex1, gj));
+                    hit = d2 < r2 && !(EXCL && ex1 > ex0 && is_excluded(ex.xs, ex0, ex1, gj));
                 }
                 if (FILL) {
                     hit = hit && (loop || j != il);
@@ -293,7 +294,7 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
                 auto test = [&](const V4<T> &p) {
                     const int j = idx_of(p);
                     const T d2 = dist2_rn(xi, yi, zi, p.x, p.y, p.z);
-                    if (d2 < r2 && !(ex1 > ex0 && is_excluded(ex.xs, ex0, ex1, lo + j))) {
+                    if (d2 < r2 && !(EXCL && ex1 > ex0 && is_excluded(ex.xs, ex0, ex1, lo + j))) {
                         if (FILL) {
                             const int jw = j - wbase;
                             if ((loop || j != il) && jw >= 0 && jw < wbits) atomicOr(&mask[jw >> 5], 1u << (jw & 31));
@@ -359,7 +360,7 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
 
         if (!FILL) {
             const int64_t nlo = warp_sum(cnt_lo), nhi = warp_sum(cnt_hi);
-            const int self_hit = (dist2_rn(xi, yi, zi, xi, yi, zi) < r2 && !(ex1 > ex0 && is_excluded(ex.xs, ex0, ex1, i))) ? 1 : 0;
+            const int self_hit = (dist2_rn(xi, yi, zi, xi, yi, zi) < r2 && !(EXCL && ex1 > ex0 && is_excluded(ex.xs, ex0, ex1, i))) ? 1 : 0;
             int64_t total, k;
             if (loop) {
                 total = nlo + nhi + self_hit;
@@ -500,15 +501,23 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
     const int nbr_grid = grid_for(N, kNbrWarps, 32);
     if (!fill) {
         build_cells_kernel<T><<<grid_for(B, 1, 8), kBuildThreads, 0, st>>>(pos, ptr, B, (T)r, spos, cellparam, cell_of, cell_start, struct_of);
-        neighbours_kernel<T, false><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
-                                                                         cell_of, cell_start, struct_of, deg, nullptr, out, ex, status);
+        if (ex.ptr)
+            neighbours_kernel<T, false, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
+                                                                                   cell_of, cell_start, struct_of, deg, nullptr, out, ex, status);
+        else
+            neighbours_kernel<T, false, false><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
+                                                                                    cell_of, cell_start, struct_of, deg, nullptr, out, ex, status);
         const int64_t nb = (N + kScanBlock - 1) / kScanBlock;
         scan_block_sums_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum);
         scan_of_sums_kernel<<<1, kScanBlock, 0, st>>>(bsum, nb, offsets + N);
         scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum, offsets);
     } else {
-        neighbours_kernel<T, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
-                                                                        cell_of, cell_start, struct_of, nullptr, offsets, out, ex, status);
+        if (ex.ptr)
+            neighbours_kernel<T, true, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
+                                                                                  cell_of, cell_start, struct_of, nullptr, offsets, out, ex, status);
+        else
+            neighbours_kernel<T, true, false><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
+                                                                                   cell_of, cell_start, struct_of, nullptr, offsets, out, ex, status);
     }
     return check_launch();
 }
