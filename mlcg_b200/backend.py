@@ -127,8 +127,17 @@ class CudaBackend:
         if not pending:
             return
         words = torch.stack([s[0] for s, _ in pending]).cpu().tolist()
-        for w, (_, what) in zip(words, pending):
-            _raise_for_status(w, what)
+        self._raise_pending(words, pending)
+
+    @staticmethod
+    def _raise_pending(words, pending):
+        """Raise for the first status word that reports a failure; the words are cleared first, so one failure is reported
+        once and later evaluations start clean."""
+        bad = [(w, what) for w, (_, what) in zip(words, pending) if w & (8 | 16)]
+        if bad:
+            for st, _ in pending:
+                st.zero_()
+            _raise_for_status(*bad[0])
 
     def _run(self, name, fn, args, what=None, launches=1, nbytes=0, flops=0):
         prof = self.profiler
@@ -211,8 +220,7 @@ class CudaBackend:
             extra = [s[0].to(torch.int64) for s, _ in pend]
             tail = torch.stack([offsets[N], status[0].to(torch.int64)] + extra).cpu().tolist()   # the one host read
             E, st = int(tail[0]), int(tail[1])
-            for w, (_, what) in zip(tail[2:], pend):
-                _raise_for_status(w, what)
+            self._raise_pending(tail[2:], pend)
             ei = torch.empty((2, E), dtype=torch.int64, device=dev)
             dist = torch.empty(E, dtype=pos.dtype, device=dev) if want_distance else None
             mb = torch.empty(E, dtype=torch.int64, device=dev) if want_batch else None
