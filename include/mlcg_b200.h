@@ -213,7 +213,7 @@ int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias
  * Fused filter network on the tensor cores (tcgen05 / TMEM):
  *   W[e,:] = ( tanh( phi(d_e) A1^T + b1 ) A2^T ) * C(d_e)
  * i.e. rbf_layer -> filter_network -> cutoff of CFConv.forward, src/mlcg/nn/schnet.py:340-341 with the
- * basis of src/mlcg/nn/radial_basis/*.py evaluated in the GEMM prologue.  float32 in / out, F = 128,
+ * basis of src/mlcg/nn/radial_basis (gaussian.py, exp_normal.py) evaluated in the GEMM prologue.  float32 in / out, F = 128,
  * R <= 128, tanh activation.  precision 0: fp32-equivalent products (fp16 hi/lo pairs, three tensor-core
  * products per GEMM, fp32 accumulation); precision 1: bf16 operands, one product.
  * status bit 3 is set if a tensor-core wait ran out (the output is then incomplete), bit 4 if a weight of the filter
