@@ -40,6 +40,24 @@ def _stream():
     return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def _on(device):
+    """Device guard for a launch: a real ``torch.cuda.device`` only when ``device`` is not the current one."""
+    if device.index is None or device.index == torch._C._cuda_getDevice():
+        return _NO_GUARD
+    return torch.cuda.device(device)
+
+
 def _need_cuda(*ts):
     for t in ts:
         if t is not None and not t.is_cuda:
@@ -117,7 +135,7 @@ class CudaBackend:
     def defer_status(self, status, what):
         """Remember a kernel's status word; it is read together with the next unavoidable host read (the edge
         count of the next radius graph) or by :meth:`check_pending`, so the hot path gains no synchronisation."""
-        if not any(s is status for s, _ in self._pending):
+        if not self._pending or (self._pending[-1][0] is not status and not any(s is status for s, _ in self._pending)):
             self._pending.append((status, what))
         if len(self._pending) > 256:
             self.check_pending()
@@ -186,7 +204,7 @@ class CudaBackend:
         _need_cuda(batch)
         batch = batch.contiguous()
         ptr = torch.empty(B + 1, dtype=torch.int64, device=batch.device)
-        with torch.cuda.device(batch.device):
+        with _on(batch.device):
             self._run("batch_to_ptr", self.lib.mlcgb_batch_to_ptr, (_ptr(batch), batch.numel(), B, _ptr(ptr), _stream(),), **self._work("batch_to_ptr", locals()))
         return ptr
 
@@ -203,7 +221,7 @@ class CudaBackend:
         pos = pos.detach().contiguous()
         N, B, dev = pos.shape[0], ptr.numel() - 1, pos.device
         dt = _dt(pos)
-        with torch.cuda.device(dev):
+        with _on(dev):
             ws_bytes = self.lib.mlcgb_radius_workspace_bytes(N, B, dt)
             ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
             deg = torch.empty(max(N, 1), dtype=torch.int32, device=dev)
@@ -241,7 +259,7 @@ class CudaBackend:
         E = row0.numel()
         twin = torch.empty(E, dtype=torch.int32, device=row0.device)
         status = torch.zeros(4, dtype=torch.int32, device=row0.device)
-        with torch.cuda.device(row0.device):
+        with _on(row0.device):
             self._run("edge_twin", self.lib.mlcgb_edge_twin, (_ptr(row0), _ptr(row1), _ptr(offsets), E, N, _ptr(twin), _ptr(status), _stream(),), **self._work("edge_twin", locals()))
         return twin, status
 
@@ -249,7 +267,7 @@ class CudaBackend:
         """pair_of[e] = k for the k-th selected edge and for its reverse."""
         _need_cuda(sel, twin)
         pair_of = torch.empty(twin.numel(), dtype=torch.int32, device=twin.device)
-        with torch.cuda.device(twin.device):
+        with _on(twin.device):
             self._run("pair_index", self.lib.mlcgb_pair_index, (_ptr(sel), _ptr(twin), sel.numel(), _ptr(pair_of), _stream(),), nbytes=12 * sel.numel())
         return pair_of
 
@@ -260,7 +278,7 @@ class CudaBackend:
         E = row0.numel()
         out = torch.empty((E, 3), dtype=pos.dtype, device=pos.device)
         status = torch.zeros(4, dtype=torch.int32, device=pos.device)
-        with torch.cuda.device(pos.device):
+        with _on(pos.device):
             self._run("edge_diff", self.lib.mlcgb_edge_diff, (_ptr(pos), _dt(pos), _ptr(row0), _ptr(row1), E, pos.shape[0], _ptr(out), _ptr(status), _stream(),), **self._work("edge_diff", locals()))
         return out
 
@@ -276,7 +294,7 @@ class CudaBackend:
         pos = pos.contiguous()
         E = row0.numel()
         out = torch.empty(E, dtype=pos.dtype, device=pos.device)
-        with torch.cuda.device(pos.device):
+        with _on(pos.device):
             self._run("edge_distance", self.lib.mlcgb_edge_distance,
                       (_ptr(pos), _dt(pos), _ptr(row0), _ptr(row1), E, pos.shape[0], _ptr(out), _ptr(self._sticky_status(pos.device)), _stream()),
                       nbytes=E * (8 + pos.element_size()) + pos.numel() * pos.element_size())
@@ -286,7 +304,7 @@ class CudaBackend:
         _need_cuda(pos, g, d)
         pos, g, d = pos.contiguous(), g.contiguous(), d.contiguous()
         out = torch.empty_like(pos)
-        with torch.cuda.device(pos.device):
+        with _on(pos.device):
             self._run("edge_distance_backward", self.lib.mlcgb_edge_distance_backward,
                       (_ptr(pos), _ptr(g), _ptr(d), _dt(pos), _ptr(plan.row0), _ptr(plan.row1), _ptr(plan.ptr_in), _ptr(plan.perm_in),
                        _ptr(plan.ptr_out), _ptr(plan.perm_out), plan.N, plan.E, _ptr(out), _stream()),
@@ -297,7 +315,7 @@ class CudaBackend:
         _need_cuda(g)
         g = g.contiguous()
         out = torch.empty((N, 3), dtype=g.dtype, device=g.device)
-        with torch.cuda.device(g.device):
+        with _on(g.device):
             self._run("node_scatter_diff", self.lib.mlcgb_node_scatter_diff, (_ptr(g), _dt(g), _ptr(ptr_in), _ptr(perm_in), _ptr(ptr_out), _ptr(perm_out), N,
                                                         g.shape[0], _ptr(out), _stream(),), **self._work("node_scatter_diff", locals()))
         return out
@@ -314,7 +332,7 @@ class CudaBackend:
         d = d.contiguous()
         s, keep = self._spec(spec, d.dtype)
         out = torch.empty((d.numel(), spec.num_rbf), dtype=d.dtype, device=d.device)
-        with torch.cuda.device(d.device):
+        with _on(d.device):
             self._run("rbf_expand", self.lib.mlcgb_rbf_expand, (_ptr(d), _dt(d), d.numel(), ctypes.byref(s), order, _ptr(out), _stream(),), **self._work("rbf_expand", locals()))
         return out
 
@@ -323,7 +341,7 @@ class CudaBackend:
         d, G = d.contiguous(), G.contiguous()
         s, keep = self._spec(spec, d.dtype)
         out = torch.empty(d.numel(), dtype=d.dtype, device=d.device)
-        with torch.cuda.device(d.device):
+        with _on(d.device):
             self._run("rbf_contract", self.lib.mlcgb_rbf_contract, (_ptr(d), _ptr(G), _dt(d), d.numel(), ctypes.byref(s), order, _ptr(out), _stream(),), **self._work("rbf_contract", locals()))
         return out
 
@@ -333,7 +351,7 @@ class CudaBackend:
         a, V = a.contiguous(), V.contiguous()
         F = V.shape[1]
         out = torch.empty((N, F), dtype=V.dtype, device=V.device)
-        with torch.cuda.device(V.device):
+        with _on(V.device):
             self._run("seg_mul_sum", self.lib.mlcgb_seg_mul_sum, (_ptr(a), _ptr(V), _dt(V), _ptr(ptr), _ptr(nbr), _ptr(eperm), N, V.shape[0], F, _ptr(out), _stream(),), **self._work("seg_mul_sum", locals()))
         return out
 
@@ -342,7 +360,7 @@ class CudaBackend:
         a, b = a.contiguous(), b.contiguous()
         E, F = ia.numel(), a.shape[1]
         out = torch.empty((E, F), dtype=a.dtype, device=a.device)
-        with torch.cuda.device(a.device):
+        with _on(a.device):
             self._run("edge_mul", self.lib.mlcgb_edge_mul, (_ptr(a), _ptr(b), _dt(a), _ptr(ia), _ptr(ib), E, F, _ptr(out), _stream(),), **self._work("edge_mul", locals()))
         return out
 
@@ -352,7 +370,7 @@ class CudaBackend:
         a, c = a.contiguous(), c.contiguous()
         E, F = a.shape
         out = torch.empty_like(a)
-        with torch.cuda.device(a.device):
+        with _on(a.device):
             self._run("row_scale", self.lib.mlcgb_row_scale, (_ptr(a), _ptr(c), _dt(a), E, F, _ptr(out), _stream(),), nbytes=(2 * a.numel() + E) * a.element_size())
         return out
 
@@ -362,7 +380,7 @@ class CudaBackend:
         a, b = a.contiguous(), b.contiguous()
         E, F = a.shape
         out = torch.empty(E, dtype=a.dtype, device=a.device)
-        with torch.cuda.device(a.device):
+        with _on(a.device):
             self._run("row_dot", self.lib.mlcgb_row_dot, (_ptr(a), _ptr(b), _dt(a), E, F, _ptr(out), _stream(),), nbytes=(2 * a.numel() + E) * a.element_size(),
                       flops=2 * a.numel())
         return out
@@ -380,9 +398,10 @@ class CudaBackend:
             (K, M), N = A.shape, B.shape[1]
         dt = _dt(A)
         C = torch.empty((M, N), dtype=A.dtype, device=A.device)
-        if self.tensor_core_gemm and dt == 0 and min(M, N, K) > 0 and self.lib.mlcgb_gemm_tc_supported(mode, M, N, K):
-            with torch.cuda.device(A.device):
-                wsb = self.lib.mlcgb_gemm_tc_workspace_bytes(mode, M, N, K)
+        tc_ok = (N <= 128 and K <= 128) if mode != 2 else (M <= 128 and N <= 128)      # what mlcgb_gemm_tc_supported tests
+        if self.tensor_core_gemm and dt == 0 and min(M, N, K) > 0 and tc_ok:
+            with _on(A.device):
+                wsb = self.lib.mlcgb_gemm_tc_workspace_bytes(mode, M, N, K) if mode == 2 else 0
                 ws = torch.empty(wsb, dtype=torch.uint8, device=A.device) if wsb else None
                 if bias is not None:
                     bias = bias.contiguous()
@@ -391,7 +410,7 @@ class CudaBackend:
                           launches=2 if wsb else 1, nbytes=(M * K + N * K + M * N) * 4, flops=2 * M * N * K)
                 self.defer_status(status, "tensor-core GEMM")
             return C
-        with torch.cuda.device(A.device):
+        with _on(A.device):
             wsb = self.lib.mlcgb_gemm_workspace_bytes(mode, M, N, K, dt)
             ws = torch.empty(wsb, dtype=torch.uint8, device=A.device) if wsb else None
             if bias is not None:
@@ -408,7 +427,7 @@ class CudaBackend:
                 and self.lib.mlcgb_gemm_tc_supported(2, M, N, K)):
             C = torch.empty((M, N), dtype=G.dtype, device=G.device)
             cs = torch.empty(M, dtype=G.dtype, device=G.device)
-            with torch.cuda.device(G.device):
+            with _on(G.device):
                 wsb = self.lib.mlcgb_gemm_tc_workspace_bytes(2, M, N, K)
                 ws = torch.empty(wsb, dtype=torch.uint8, device=G.device)
                 status = self._sticky_status(G.device)
@@ -426,7 +445,7 @@ class CudaBackend:
             return False
         M, K = A.shape
         N = B.shape[0] if mode == 0 else B.shape[1]
-        return M >= 128 and K % 4 == 0 and N % 4 == 0 and bool(self.lib.mlcgb_gemm_tc_supported(mode, M, N, K))
+        return M >= 128 and K % 4 == 0 and N % 4 == 0 and N <= 128 and K <= 128
 
     def gemm_fused(self, mode: int, A, B, bias=None, aux=None, epilogue: int = 0):
         """Row-wise tensor-core GEMM (mode 0: A B^T + bias, mode 1: A B) with the elementwise step that follows it:
@@ -441,7 +460,7 @@ class CudaBackend:
         if aux is not None:
             aux = aux.contiguous()
         status = self._sticky_status(A.device)
-        with torch.cuda.device(A.device):
+        with _on(A.device):
             self._run("gemm_tc", self.lib.mlcgb_gemm_tc_fused, (mode, _ptr(A), _ptr(B), _ptr(bias), _ptr(aux), int(epilogue), M, N, K, _ptr(C), _ptr(status), _stream()),
                       nbytes=(M * K + N * K + M * N * (2 if aux is not None else 1)) * 4, flops=2 * M * N * K)
         self.defer_status(status, "tensor-core GEMM")
@@ -461,7 +480,7 @@ class CudaBackend:
         rows = E if sel is None else sel.numel()
         W = torch.empty((E if (sel is None or twin is not None) else rows, F), dtype=d.dtype, device=d.device)
         status = self._sticky_status(d.device)
-        with torch.cuda.device(d.device):
+        with _on(d.device):
             self._run("filter_forward", self.lib.mlcgb_filter_forward,
                       (_ptr(d), rows, _ptr(sel), _ptr(twin), ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
                        int(precision), _ptr(W), _ptr(status), _stream()),
@@ -479,7 +498,7 @@ class CudaBackend:
         rows = E if sel is None else sel.numel()
         gd = torch.empty(E, dtype=d.dtype, device=d.device)
         status = self._sticky_status(d.device)
-        with torch.cuda.device(d.device):
+        with _on(d.device):
             self._run("filter_backward", self.lib.mlcgb_filter_backward,
                       (_ptr(d), rows, _ptr(sel), _ptr(twin), ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
                        int(precision), _ptr(row0), _ptr(row1), _ptr(xl), _ptr(gagg), xl.shape[0], _ptr(gd), _ptr(status), _stream()),
@@ -491,7 +510,7 @@ class CudaBackend:
         x = x.contiguous()
         B = ptr.numel() - 1
         out = torch.empty(B, dtype=x.dtype, device=x.device)
-        with torch.cuda.device(x.device):
+        with _on(x.device):
             self._run("segment_sum", self.lib.mlcgb_segment_sum, (_ptr(x), _dt(x), _ptr(ptr), B, _ptr(out), _stream(),), **self._work("segment_sum", locals()))
         return out
 
@@ -501,7 +520,7 @@ class CudaBackend:
         _need_cuda(x, v, f, masses, beta_mass_ratio, noise)
         assert x.is_contiguous() and v.is_contiguous()
         f, noise = f.contiguous(), noise.contiguous()
-        with torch.cuda.device(x.device):
+        with _on(x.device):
             self._run("langevin_first_half", self.lib.mlcgb_langevin_first_half,
                       (_ptr(x), _ptr(v), _ptr(f), _ptr(masses), _ptr(beta_mass_ratio), _ptr(noise), _dt(x), x.shape[0], float(dt), float(vscale),
                        float(noisescale), _stream()), nbytes=6 * x.numel() * x.element_size())
@@ -510,7 +529,7 @@ class CudaBackend:
         _need_cuda(v, f, masses)
         assert v.is_contiguous()
         f = f.contiguous()
-        with torch.cuda.device(v.device):
+        with _on(v.device):
             self._run("langevin_second_half", self.lib.mlcgb_langevin_second_half, (_ptr(v), _ptr(f), _ptr(masses), _dt(v), v.shape[0], float(dt), _stream()),
                       nbytes=3 * v.numel() * v.element_size())
 
@@ -523,7 +542,7 @@ class CudaBackend:
         energy = torch.zeros(B, dtype=pos.dtype, device=pos.device)
         grad = torch.zeros((N, 3), dtype=pos.dtype, device=pos.device) if want_grad else None
         status = torch.zeros(4, dtype=torch.int32, device=pos.device)
-        with torch.cuda.device(pos.device):
+        with _on(pos.device):
             self._run("prior_terms", self.lib.mlcgb_prior_terms, (kind, _ptr(pos), _dt(pos), _ptr(mapping), _ptr(mapping_batch), _ptr(params), params.shape[0], M, N, B,
                                                   _ptr(energy), _ptr(grad), _ptr(status), _stream(),), **self._work("prior_terms", locals()))
         return energy, grad

@@ -68,6 +68,22 @@ class CFConv(torch.nn.Module):
             return None
         if not getattr(get_backend(), "tensor_core_gemm", False):     # the switch that sends every GEMM to the CUDA cores
             return None
+        # the answer depends on module structure, device and dtype only: kept until one of them changes
+        rc = rbf_layer.cutoff
+        key = (id(rbf_layer), net.layers[0].weight.device, net.layers[0].weight.dtype, id(self.cutoff), id(rc),
+               getattr(self.cutoff, "cutoff_lower", None), getattr(self.cutoff, "cutoff_upper", None),
+               getattr(rc, "cutoff_lower", None), getattr(rc, "cutoff_upper", None),
+               tuple(id(m) for m in net.layers), tuple(id(t) for t in rbf_layer.parameters(recurse=False)),
+               tuple(id(t) for t in rbf_layer.buffers(recurse=False)))
+        cached = self.__dict__.get("_fused_spec_cache")
+        if cached is not None and cached[0] == key:
+            return cached[1]
+        result = self._fused_spec_uncached(rbf_layer)
+        self.__dict__["_fused_spec_cache"] = (key, result)
+        return result
+
+    def _fused_spec_uncached(self, rbf_layer):
+        net = self.filter_network
         l0, act, l2 = net.layers
         if not (isinstance(l0, torch.nn.Linear) and isinstance(l2, torch.nn.Linear) and isinstance(act, torch.nn.Tanh)):
             return None
