@@ -249,6 +249,34 @@ int mlcgb_row_scale(const void *a /* [E,F] */, const void *c /* [E] */, int dtyp
 int mlcgb_row_dot(const void *a /* [E,F] */, const void *b /* [E,F] */, int dtype, int64_t E, int64_t F, void *out /* [E] */,
                   void *stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * One interaction block per call (eval mode, symmetric edge list, float32, 128 filters):
+ *   x_new = x + lin( tanh( lin2( sum_j lin1(x)_j * W(d_ij) ) ) )     src/mlcg/nn/schnet.py:150, 252-262, 340-350
+ * forward  = mlcgb_gemm_tc_fused (lin1) -> mlcgb_filter_forward (one row per pair) -> mlcgb_seg_mul_sum ->
+ *            mlcgb_gemm_tc_fused (lin2 + tanh) -> mlcgb_gemm_tc_fused (lin + residual);
+ * backward = the force pass through the same block: gx (gradient w.r.t. x, residual branch included; skipped if NULL)
+ *            and gd (gradient w.r.t. the distances; skipped if NULL) from g = dE/dx_new.
+ * They exist so that a host pays one foreign call per block and direction: for small systems the evaluation time is the
+ * launch path.  W1 [F,H] (no bias), fA1 [F,R], fb1 [F], fA2 [F,F] the filter network, W2 [H2,F], b2, W3 [H,H2], b3.
+ * sel [P] one edge per unordered pair, pair_of [E] (mlcgb_pair_index), twin [E] (mlcgb_edge_twin), ptr_out / nbr_out the
+ * CSR of the centre-sorted list.  xl [N,F], Wp [P,F], a [N,H2] are written by the forward and read by the backward; agg,
+ * gy, gagg, gxl are scratch of the shapes [N,F], [N,H2], [N,F], [N,F].  MLCGB_E_LIMIT when N < 128 or a width is not a
+ * multiple of four / beyond 128 (use the individual entry points then).
+ * ---------------------------------------------------------------------------------------------- */
+int mlcgb_interaction_forward(const void *x, const void *d, const int64_t *ptr_out, const int32_t *nbr_out, const int32_t *sel,
+                              const int32_t *pair_of, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower,
+                              double conv_upper, const void *W1, const void *fA1, const void *fb1, const void *fA2, const void *W2,
+                              const void *b2, const void *W3, const void *b3, int64_t N, int64_t E, int64_t P, int64_t H, int64_t F,
+                              int64_t H2, int precision, void *xl, void *Wp, void *agg, void *a, void *out, int32_t *status,
+                              void *stream);
+int mlcgb_interaction_backward(const void *g, const void *a, const void *Wp, const void *xl, const void *d, const int64_t *ptr_out,
+                               const int32_t *nbr_out, const int32_t *sel, const int32_t *pair_of, const int32_t *twin,
+                               const int32_t *row0, const int32_t *row1, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind,
+                               double conv_lower, double conv_upper, const void *W1, const void *fA1, const void *fb1,
+                               const void *fA2, const void *W2, const void *W3, int64_t N, int64_t E, int64_t P, int64_t H, int64_t F,
+                               int64_t H2, int precision, void *gy, void *gagg, void *gxl, void *gx, void *gd, int32_t *status,
+                               void *stream);
+
 /* out[b] = sum_{n in [ptr[b],ptr[b+1])} x[n]  — the per-structure energy sum, src/mlcg/nn/schnet.py:158 */
 int mlcgb_segment_sum(const void *x /* [N] */, int dtype, const int64_t *ptr /* [B+1] */, int64_t B, void *out /* [B] */,
                       void *stream);

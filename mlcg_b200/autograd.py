@@ -421,6 +421,12 @@ class FusedInteraction(torch.autograd.Function):
     def forward(ctx, x, d, W1, fA1, fb1, fA2, W2, b2, W3, b3, plan: EdgePlan, spec: RbfSpec, conv_cut, precision: int):
         be = get_backend()
         x = x.contiguous()
+        ctx.plan, ctx.spec, ctx.conv_cut, ctx.precision = plan, spec, conv_cut, precision
+        if be.interaction_ok(x, plan, x.shape[1], W1.shape[0], W2.shape[0]):        # the whole block in one library call
+            d = d.contiguous()
+            out, xl, W, a = be.interaction_forward(x, d, plan, spec, conv_cut, W1, fA1, fb1, fA2, W2, b2, W3, b3, precision)
+            ctx.save_for_backward(xl, d, W, a, W1, fA1, fb1, fA2, W2, W3)
+            return out
         xl = be.gemm(0, x, W1)
         sel = plan.half_selection()
         W, status = be.filter_forward(d, spec, conv_cut[0], conv_cut[1], conv_cut[2], fA1, fb1, fA2, precision, sel, None)
@@ -441,6 +447,10 @@ class FusedInteraction(torch.autograd.Function):
         xl, d, W, a, W1, fA1, fb1, fA2, W2, W3 = ctx.saved_tensors
         plan, be = ctx.plan, get_backend()
         g = g.contiguous()
+        if be.interaction_ok(g, plan, g.shape[1], W1.shape[0], W2.shape[0]):
+            gx, gd = be.interaction_backward(g, a, W, xl, d, plan, ctx.spec, ctx.conv_cut, W1, fA1, fb1, fA2, W2, W3, ctx.precision,
+                                             ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+            return (gx, gd) + (None,) * 12
         gy = be.gemm_fused(1, g, W3, None, a, be.EPI_TANH_GRAD)        # through lin and the activation
         gagg = be.gemm(1, gy, W2)
         sel = plan.half_selection()

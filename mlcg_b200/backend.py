@@ -466,6 +466,55 @@ class CudaBackend:
         self.defer_status(status, "tensor-core GEMM")
         return C
 
+    # ------------------------------------------------------------------ one interaction block per call
+    def interaction_ok(self, x, plan, H, F, H2) -> bool:
+        """Whether the per-block entry points take this case; with a profiler attached the individual kernels are launched
+        instead, so that each is timed on its own."""
+        return (self.profiler is None and self.tensor_core_gemm and x.dtype == torch.float32 and x.shape[0] >= 128 and F == 128
+                and H <= 128 and H2 <= 128 and H % 4 == 0 and H2 % 4 == 0 and plan.half_selection() is not None)
+
+    def interaction_forward(self, x, d, plan, spec: RbfSpec, conv_cut, W1, fA1, fb1, fA2, W2, b2, W3, b3, precision):
+        """x + lin(tanh(lin2(aggregate(lin1(x), W(d))))) in one library call; returns (x_new, xl, Wp, a)."""
+        N, H = x.shape
+        W1, fA1, fb1, fA2, W2, b2, W3, b3 = (t.contiguous() for t in (W1, fA1, fb1, fA2, W2, b2, W3, b3))
+        F, H2 = W1.shape[0], W2.shape[0]
+        sel, pair_of = plan.half_selection(), plan.pair_index()
+        P, dev = sel.numel(), x.device
+        s, keep = self._spec(spec, torch.float32)
+        new = lambda *shape: torch.empty(shape, dtype=torch.float32, device=dev)
+        xl, Wp, agg, a, out = new(N, F), new(P, F), new(N, F), new(N, H2), new(N, H)
+        status = self._sticky_status(dev)
+        with _on(dev):
+            _lib.check(self.lib.mlcgb_interaction_forward(
+                _ptr(x), _ptr(d), _ptr(plan.ptr_out), _ptr(plan.nbr_out), _ptr(sel), _ptr(pair_of), ctypes.byref(s), int(conv_cut[0]),
+                float(conv_cut[1]), float(conv_cut[2]), _ptr(W1), _ptr(fA1), _ptr(fb1), _ptr(fA2), _ptr(W2), _ptr(b2), _ptr(W3), _ptr(b3),
+                N, plan.E, P, H, F, H2, int(precision), _ptr(xl), _ptr(Wp), _ptr(agg), _ptr(a), _ptr(out), _ptr(status), _stream()),
+                "interaction_forward")
+        self.defer_status(status, "interaction block (forward)")
+        return out, xl, Wp, a
+
+    def interaction_backward(self, g, a, Wp, xl, d, plan, spec: RbfSpec, conv_cut, W1, fA1, fb1, fA2, W2, W3, precision, want_gx=True, want_gd=True):
+        N, H = g.shape
+        W1, fA1, fb1, fA2, W2, W3 = (t.contiguous() for t in (W1, fA1, fb1, fA2, W2, W3))
+        F, H2 = W1.shape[0], W2.shape[0]
+        sel, pair_of = plan.half_selection(), plan.pair_index()
+        P, dev = sel.numel(), g.device
+        s, keep = self._spec(spec, torch.float32)
+        new = lambda *shape: torch.empty(shape, dtype=torch.float32, device=dev)
+        gy, gagg, gxl = new(N, H2), new(N, F), new(N, F)
+        gx = new(N, H) if want_gx else None
+        gd = new(plan.E) if want_gd else None
+        status = self._sticky_status(dev)
+        with _on(dev):
+            _lib.check(self.lib.mlcgb_interaction_backward(
+                _ptr(g), _ptr(a), _ptr(Wp), _ptr(xl), _ptr(d), _ptr(plan.ptr_out), _ptr(plan.nbr_out), _ptr(sel), _ptr(pair_of),
+                _ptr(plan.perm_in), _ptr(plan.row0), _ptr(plan.row1), ctypes.byref(s), int(conv_cut[0]), float(conv_cut[1]), float(conv_cut[2]),
+                _ptr(W1), _ptr(fA1), _ptr(fb1), _ptr(fA2), _ptr(W2), _ptr(W3), N, plan.E, P, H, F, H2, int(precision),
+                _ptr(gy), _ptr(gagg), _ptr(gxl), _ptr(gx), _ptr(gd), _ptr(status), _stream()),
+                "interaction_backward")
+        self.defer_status(status, "interaction block (backward)")
+        return gx, gd
+
     # ------------------------------------------------------------------ fused filter network (tensor cores)
     def filter_forward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, precision=0, sel=None, twin=None):
         """W[E,F] = (tanh(phi(d) A1^T + b1) A2^T) * C(d); float32, F = 128, R <= 128.

@@ -143,7 +143,7 @@ class InteractionBlock(torch.nn.Module):
     def forward(self, x, edge_index, edge_weight, edge_attr, *args):
         return node_linear(self.lin, self.activation(self.conv(x, edge_index, edge_weight, edge_attr)), self.training)
 
-    def forward_residual(self, x, edge_index, edge_weight, edge_attr, *args):
+    def forward_residual(self, x, edge_index, edge_weight, edge_attr, *args, fused=None):
         """``x + self(x, ...)`` (the sum at schnet.py:150).  In eval mode, when the block has the standard layout — a CFConv the
         fused filter kernel covers, tanh, 128-wide Linear layers — the whole expression runs as one autograd node whose GEMMs
         carry the activation and the sums as epilogues."""
@@ -151,7 +151,10 @@ class InteractionBlock(torch.nn.Module):
         if (not self.training and type(conv) is CFConv and isinstance(edge_attr, LazyRadialBasis) and isinstance(self.activation, torch.nn.Tanh)
                 and x.dtype == torch.float32 and x.is_cuda and conv.lin1.bias is None and conv.lin2.bias is not None and self.lin.bias is not None):
             plan = plan_of(edge_index, x.shape[0])
-            fused = conv.fused_spec(edge_attr.rbf_layer) if edge_attr.symmetric == plan.symmetric else None
+            if edge_attr.symmetric != plan.symmetric:
+                fused = None
+            elif fused is None:          # (SchNet.forward hands over what it already worked out)
+                fused = conv.fused_spec(edge_attr.rbf_layer)
             be = get_backend()
             if (fused is not None and be.gemm_fused_ok(0, x, conv.lin1.weight) and conv.lin1.out_features == 128
                     and be.gemm_fused_ok(0, x, self.lin.weight) and conv.lin2.in_features == 128 and conv.lin2.out_features == self.lin.in_features
@@ -232,17 +235,17 @@ class SchNet(torch.nn.Module):
         else:
             distances = EdgeDistanceOnce.apply(data.pos, plan)  # one kernel forward, one backward
         distances = _tag_symmetric(distances, plan.symmetric)
-        lazy_ok = (not self.training and distances.dtype == torch.float32 and
-                   all(type(b) is InteractionBlock and type(b.conv) is CFConv and b.conv.fused_spec(self.rbf_layer) is not None
-                       for b in self.interaction_blocks))
+        specs = [b.conv.fused_spec(self.rbf_layer) if (not self.training and type(b) is InteractionBlock and type(b.conv) is CFConv) else None
+                 for b in self.interaction_blocks]
+        lazy_ok = not self.training and distances.dtype == torch.float32 and all(s is not None for s in specs)
         if lazy_ok:
             rbf_expansion = LazyRadialBasis(distances, self.rbf_layer, plan.symmetric)
         else:
             rbf_expansion = _tag_symmetric(self.rbf_layer(distances), plan.symmetric)
         num_batch = None
-        for block in self.interaction_blocks:
+        for block, spec in zip(self.interaction_blocks, specs):
             if type(block) is InteractionBlock:
-                x = block.forward_residual(x, edge_index, distances, rbf_expansion, num_batch, data.batch)
+                x = block.forward_residual(x, edge_index, distances, rbf_expansion, num_batch, data.batch, fused=spec if lazy_ok else None)
             else:
                 x = x + block(x, edge_index, distances, rbf_expansion, num_batch, data.batch)
         energy = self.output_network(x, data)

@@ -260,3 +260,24 @@ def test_condensed_priors_on_the_device():
     assert set(cmodel.models.keys()) == {"bonds", "dihedrals"}
     assert torch.allclose(out.out["energy"], ref.out["energy"], rtol=1e-5)
     assert torch.allclose(out.out["forces"], ref.out["forces"], rtol=1e-4, atol=1e-4 * float(ref.out["forces"].abs().max()))
+
+
+def test_one_call_per_block_matches_the_individual_kernels():
+    """`mlcgb_interaction_forward` / `_backward` issue the same kernels as the per-kernel entry points: bit-identical results.
+    (With a profiler attached the package launches the kernels one by one, without it one library call per block.)"""
+    from mlcg_b200.backend import KernelProfiler, get_backend
+    model, pos, types_, batch = _make("expnormal", 8, 100, 20, 15.0, 128, 128, 3, 7, min_dist=4.0)
+    model = bnn.GradientsOut(model.to(DEV), "forces").eval()
+    mk = lambda: mlcg_b200.AtomicData(pos=pos.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV), n_atoms=torch.full((8,), 100).to(DEV))
+    be = get_backend()
+    assert be.profiler is None
+    whole = model(mk())
+    be.profiler = KernelProfiler(time_kernels=False)
+    try:
+        parts = model(mk())
+        assert {"filter_forward", "filter_backward", "seg_mul_sum", "gemm_tc"} <= set(be.profiler.stats)
+    finally:
+        be.profiler = None
+    be.check_pending()
+    assert torch.equal(whole.out["SchNet"]["energy"], parts.out["SchNet"]["energy"])
+    assert torch.equal(whole.out["SchNet"]["forces"], parts.out["SchNet"]["forces"])
