@@ -73,8 +73,7 @@ class CFConv(torch.nn.Module):
         key = (id(rbf_layer), net.layers[0].weight.device, net.layers[0].weight.dtype, id(self.cutoff), id(rc),
                getattr(self.cutoff, "cutoff_lower", None), getattr(self.cutoff, "cutoff_upper", None),
                getattr(rc, "cutoff_lower", None), getattr(rc, "cutoff_upper", None),
-               tuple(id(m) for m in net.layers), tuple(id(t) for t in rbf_layer.parameters(recurse=False)),
-               tuple(id(t) for t in rbf_layer.buffers(recurse=False)))
+               tuple(map(id, net.layers)), tuple(map(id, rbf_layer._parameters.values())), tuple(map(id, rbf_layer._buffers.values())))
         cached = self.__dict__.get("_fused_spec_cache")
         if cached is not None and cached[0] == key:
             return cached[1]
