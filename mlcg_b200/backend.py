@@ -253,12 +253,13 @@ class CudaBackend:
                           **self._work("radius_fill", locals()))
         return dict(edge_index=ei, distance=dist, mapping_batch=mb, row0=r0, row1=r1, offsets=offsets, status=st)
 
-    def edge_twin(self, row0, row1, offsets, N):
-        """twin[e] = position of the reversed edge; second value: True if every edge has one."""
+    def edge_twin(self, row0, row1, offsets, N, fresh_status: bool = False):
+        """twin[e] = position of the reversed edge; second value: the status words (bit 2: an edge without its reverse).  By default
+        the words are the backend's accumulating ones; ``fresh_status=True`` gives this call its own."""
         _need_cuda(row0)
         E = row0.numel()
         twin = torch.empty(E, dtype=torch.int32, device=row0.device)
-        status = torch.zeros(4, dtype=torch.int32, device=row0.device)
+        status = torch.zeros(4, dtype=torch.int32, device=row0.device) if fresh_status else self._sticky_status(row0.device)
         with _on(row0.device):
             self._run("edge_twin", self.lib.mlcgb_edge_twin, (_ptr(row0), _ptr(row1), _ptr(offsets), E, N, _ptr(twin), _ptr(status), _stream(),), **self._work("edge_twin", locals()))
         return twin, status

@@ -170,4 +170,5 @@ def atomic_data2neighbor_list(data, rcut: float, self_interaction: bool = False,
                             mapping_batch=res["mapping_batch"], cell_shifts=cell_shifts, rcut=rcut,
                             self_interaction=self_interaction)
     nl["_mlcgb_zero_shifts"] = True
+    nl["_mlcgb_ptr"] = ptr           # structure boundaries, for the per-structure energy sum
     return nl

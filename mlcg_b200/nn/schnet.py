@@ -248,7 +248,10 @@ class SchNet(torch.nn.Module):
             else:
                 x = x + block(x, edge_index, distances, rbf_expansion, num_batch, data.batch)
         energy = self.output_network(x, data)
-        energy = SegmentSum.apply(energy, self._structure_ptr(data), data.batch).flatten()
+        ptr = neighbor_list.get("_mlcgb_ptr")
+        if ptr is None or ptr.device != x.device or ptr[-1:].numel() == 0:
+            ptr = self._structure_ptr(data)
+        energy = SegmentSum.apply(energy, ptr, data.batch).flatten()
         data.out[self.name] = {ENERGY_KEY: energy}
         return data
 

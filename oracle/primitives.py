@@ -46,7 +46,7 @@ class OracleBackend:
                     mapping_batch=seg if want_batch else None, row0=ei_t[0].to(torch.int32), row1=ei_t[1].to(torch.int32),
                     offsets=torch.from_numpy(offsets).to(dev), status=status)
 
-    def edge_twin(self, row0, row1, offsets, N):
+    def edge_twin(self, row0, row1, offsets, N, fresh_status=False):
         E = row0.numel()
         key = row0.to(torch.int64) * N + row1.to(torch.int64)
         rkey = row1.to(torch.int64) * N + row0.to(torch.int64)

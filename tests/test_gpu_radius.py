@@ -129,7 +129,7 @@ def test_chain_configurations():
     for n, B, rc in [(10, 64, 30.0), (100, 16, 15.0), (73, 16, 10.0), (268, 8, 12.0)]:
         pos = torch.cat([random_walk_chain(n, gen, jitter=0.3) for _ in range(B)]).numpy()
         res, ei = check_against_oracle(pos, np.arange(B + 1, dtype=np.int64) * n, rc)
-        twin, st = get_backend().edge_twin(res["row0"], res["row1"], res["offsets"], len(pos))
+        twin, st = get_backend().edge_twin(res["row0"], res["row1"], res["offsets"], len(pos), fresh_status=True)
         assert int(st[0]) == 0
         t = twin.cpu().numpy()
         assert np.array_equal(ei[0][t], ei[1]) and np.array_equal(ei[1][t], ei[0])
@@ -153,7 +153,7 @@ def test_full_size_standalone_configuration_properties():
     d = p[ei[1]] - p[ei[0]]
     d2 = (d[:, 0] * d[:, 0] + d[:, 1] * d[:, 1]) + d[:, 2] * d[:, 2]
     assert bool((d2 < 100.0).all())
-    twin, st = get_backend().edge_twin(res["row0"], res["row1"], off, B * n)              # symmetric: every edge has its reverse
+    twin, st = get_backend().edge_twin(res["row0"], res["row1"], off, B * n, fresh_status=True)              # symmetric: every edge has its reverse
     assert int(st[0]) == 0
     for b in (0, 100, 255):
         want = radius_ref.radius_graph_c(pos[b * n:(b + 1) * n], np.array([0, n], np.int64), 10.0, 1000, False, "cluster") + b * n
