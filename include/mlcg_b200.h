@@ -277,6 +277,39 @@ int mlcgb_interaction_backward(const void *g, const void *a, const void *Wp, con
                                int64_t H2, int precision, void *gy, void *gagg, void *gxl, void *gx, void *gd, int32_t *status,
                                void *stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * The whole evaluation of a SchNet with the standard layout in one call: embedding, interaction blocks, output network
+ * MLP([H, head_width, 1]) with tanh, per-structure energy sum (src/mlcg/nn/schnet.py:116-162) and, if grad_pos is given,
+ * d(sum of energies)/d(pos) (what GradientsOut differentiates, src/mlcg/nn/gradients.py:191-230; forces are its negative).
+ * Same kernels as the per-block entry points; float32, symmetric centre-sorted edge list with its pair selection, pair
+ * index and reverse-edge map, N >= 128, widths multiples of four and at most 128, 128 filters (MLCGB_E_LIMIT otherwise).
+ * All weight pointers are device pointers; the two structs live on the host.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+    const void *lin1_w;                            /* [F,H], no bias       CFConv.lin1 */
+    const void *filter_w1, *filter_b1, *filter_w2; /* [F,R], [F], [F,F]    CFConv.filter_network */
+    const void *lin2_w, *lin2_b;                   /* [H2,F], [H2]         CFConv.lin2 */
+    const void *lin_w, *lin_b;                     /* [H,H2], [H]          InteractionBlock.lin */
+} mlcgb_schnet_block;
+
+typedef struct {
+    int64_t hidden, filters, conv_out, head_width; /* H, F, H2, width of the output network's hidden layer */
+    int64_t num_blocks, num_types;
+    const mlcgb_schnet_block *blocks;              /* host array [num_blocks] */
+    const void *embedding;                         /* [num_types, H] */
+    const void *head_W, *head_b;                   /* [head_width, H], [head_width] */
+    const void *head_out, *head_out_b;             /* [head_width], [1] or NULL */
+} mlcgb_schnet_weights;
+
+size_t mlcgb_schnet_eval_workspace_bytes(int64_t N, int64_t E, int64_t P, int64_t H, int64_t F, int64_t H2, int64_t head_width,
+                                         int64_t num_blocks);
+int mlcgb_schnet_eval(const void *pos /* [N,3] */, const int64_t *types /* [N] */, const int64_t *struct_ptr /* [B+1] */, int64_t N,
+                      int64_t B, const int32_t *row0, const int32_t *row1, const int64_t *offsets /* [N+1] */,
+                      const int32_t *sel /* [P] */, const int32_t *pair_of /* [E] */, const int32_t *twin /* [E] */, int64_t E,
+                      int64_t P, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper,
+                      const mlcgb_schnet_weights *weights, int precision, void *workspace, size_t workspace_bytes,
+                      void *energy /* [B] */, void *grad_pos /* [N,3] or NULL */, int32_t *status, void *stream);
+
 /* out[b] = sum_{n in [ptr[b],ptr[b+1])} x[n]  — the per-structure energy sum, src/mlcg/nn/schnet.py:158 */
 int mlcgb_segment_sum(const void *x /* [N] */, int dtype, const int64_t *ptr /* [B+1] */, int64_t B, void *out /* [B] */,
                       void *stream);

@@ -20,6 +20,20 @@ class RbfSpecStruct(ctypes.Structure):
                 ("lower", c_dbl), ("upper", c_dbl), ("alpha", c_dbl), ("p0", c_vp), ("p1", c_vp)]
 
 
+class SchnetBlockStruct(ctypes.Structure):
+    """Mirror of ``mlcgb_schnet_block``."""
+
+    _fields_ = [(n, c_vp) for n in ("lin1_w", "filter_w1", "filter_b1", "filter_w2", "lin2_w", "lin2_b", "lin_w", "lin_b")]
+
+
+class SchnetWeightsStruct(ctypes.Structure):
+    """Mirror of ``mlcgb_schnet_weights``."""
+
+    _fields_ = [("hidden", c_i64), ("filters", c_i64), ("conv_out", c_i64), ("head_width", c_i64), ("num_blocks", c_i64), ("num_types", c_i64),
+                ("blocks", ctypes.POINTER(SchnetBlockStruct)), ("embedding", c_vp), ("head_W", c_vp), ("head_b", c_vp), ("head_out", c_vp),
+                ("head_out_b", c_vp)]
+
+
 # name -> (restype, argtypes); one entry per symbol declared in include/mlcg_b200.h
 SIGNATURES = {
     "mlcgb_strerror": (ctypes.c_char_p, [c_int]),
@@ -54,6 +68,9 @@ SIGNATURES = {
     "mlcgb_gemm_tc_tn_colsum": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp]),
     "mlcgb_interaction_forward": (c_int, [c_vp] * 6 + [c_vp, c_int, c_dbl, c_dbl] + [c_vp] * 8 + [c_i64] * 6 + [c_int] + [c_vp] * 7),
     "mlcgb_interaction_backward": (c_int, [c_vp] * 12 + [c_vp, c_int, c_dbl, c_dbl] + [c_vp] * 6 + [c_i64] * 6 + [c_int] + [c_vp] * 7),
+    "mlcgb_schnet_eval_workspace_bytes": (c_sz, [c_i64] * 8),
+    "mlcgb_schnet_eval": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_int, c_dbl, c_dbl,
+                                  c_vp, c_int, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]),
     "mlcgb_gemm_tc_fused": (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "mlcgb_filter_forward": (c_int, [c_vp, c_i64, c_vp, c_vp, ctypes.POINTER(RbfSpecStruct), c_int, c_dbl, c_dbl, c_vp, c_vp, c_vp, c_i64, c_int, c_vp, c_vp, c_vp]),
     "mlcgb_filter_backward": (c_int, [c_vp, c_i64, c_vp, c_vp, ctypes.POINTER(RbfSpecStruct), c_int, c_dbl, c_dbl, c_vp, c_vp, c_vp, c_i64, c_int,

@@ -463,3 +463,23 @@ class FusedInteraction(torch.autograd.Function):
                                             xl, gagg, ctx.precision, sel, plan.perm_in if sel is not None else None)
             be.defer_status(status, "fused filter network (backward)")
         return (gx, gd) + (None,) * 12
+
+
+class SchNetEval(torch.autograd.Function):
+    """Energies of a standard SchNet with d(sum E)/d(pos) worked out in the same library call (eval mode: the force pass
+    always follows).  ``backward`` hands that gradient out, scaled per structure by the incoming gradient; it is not itself
+    differentiable."""
+
+    @staticmethod
+    def forward(ctx, pos, types, struct_ptr, batch, plan: EdgePlan, spec: RbfSpec, conv_cut, weights, precision: int):
+        energy, grad = get_backend().schnet_eval(pos.contiguous(), types, struct_ptr, plan, spec, conv_cut, weights, precision,
+                                                 want_grad=ctx.needs_input_grad[0])
+        if grad is not None:
+            ctx.save_for_backward(grad, batch)
+        return energy
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        grad, batch = ctx.saved_tensors
+        return (grad * g.index_select(0, batch).unsqueeze(-1),) + (None,) * 8

@@ -516,6 +516,29 @@ class CudaBackend:
         self.defer_status(status, "interaction block (backward)")
         return gx, gd
 
+    def schnet_eval(self, pos, types, struct_ptr, plan, spec: RbfSpec, conv_cut, weights, precision, want_grad=True):
+        """Energies [B] and d(sum of energies)/d(pos) [N,3] of a standard SchNet in one library call.  ``weights`` is what
+        :func:`mlcg_b200.nn.schnet.packed_weights` returns: ``(SchnetWeightsStruct, keep-alive objects)``."""
+        wstruct, _keep = weights
+        N, dev = pos.shape[0], pos.device
+        B = struct_ptr.numel() - 1
+        sel, pair_of = plan.half_selection(), plan.pair_index()
+        P = sel.numel()
+        s, keep = self._spec(spec, torch.float32)
+        wsb = self.lib.mlcgb_schnet_eval_workspace_bytes(N, plan.E, P, wstruct.hidden, wstruct.filters, wstruct.conv_out, wstruct.head_width,
+                                                         wstruct.num_blocks)
+        ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
+        energy = torch.empty(B, dtype=torch.float32, device=dev)
+        grad = torch.empty((N, 3), dtype=torch.float32, device=dev) if want_grad else None
+        status = self._sticky_status(dev)
+        with _on(dev):
+            _lib.check(self.lib.mlcgb_schnet_eval(
+                _ptr(pos), _ptr(types), _ptr(struct_ptr), N, B, _ptr(plan.row0), _ptr(plan.row1), _ptr(plan.ptr_out), _ptr(sel), _ptr(pair_of),
+                _ptr(plan.perm_in), plan.E, P, ctypes.byref(s), int(conv_cut[0]), float(conv_cut[1]), float(conv_cut[2]), ctypes.byref(wstruct),
+                int(precision), _ptr(ws), wsb, _ptr(energy), _ptr(grad), _ptr(status), _stream()), "schnet_eval")
+        self.defer_status(status, "SchNet evaluation")
+        return energy, grad
+
     # ------------------------------------------------------------------ fused filter network (tensor cores)
     def filter_forward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, precision=0, sel=None, twin=None):
         """W[E,F] = (tanh(phi(d) A1^T + b1) A2^T) * C(d); float32, F = 128, R <= 128.

@@ -60,3 +60,143 @@ int mlcgb_interaction_backward(const void *g, const void *a, const void *Wp, con
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// The whole SchNet evaluation — embedding, interaction blocks, output network, per-structure sum and the force pass — as
+// one kernel sequence issued from C (src/mlcg/nn/schnet.py:116-162 and its derivative, src/mlcg/nn/gradients.py:191-230).
+// ------------------------------------------------------------------------------------------------
+namespace mlcgb {
+
+__global__ void embedding_rows_kernel(const float *__restrict__ table, const int64_t *__restrict__ types, int64_t N, int64_t H, int64_t T,
+                                      float *__restrict__ x, int32_t *__restrict__ status) {
+    const int64_t Hv = H >> 2, total = N * Hv;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = t / Hv, c = t - n * Hv;
+        int64_t ty = types[n];
+        if (ty < 0 || ty >= T) {
+            atomicOr(status, (int)kBadIndex);
+            ty = 0;
+        }
+        reinterpret_cast<float4 *>(x)[t] = __ldg(reinterpret_cast<const float4 *>(table + ty * H) + c);
+    }
+}
+
+// e[n] = sum_f a[n,f] w[f] + b: the last Linear layer of the output network (one output); one warp per node
+__global__ void head_out_kernel(const float *__restrict__ a, const float *__restrict__ w, const float *__restrict__ b, int64_t N, int64_t F,
+                                float *__restrict__ e) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t n = warp; n < N; n += nwarps) {
+        float s = 0.f;
+        for (int64_t f = lane; f < F; f += 32) s = fmaf(a[n * F + f], w[f], s);
+        s = warp_sum(s);
+        if (lane == 0) e[n] = s + (b ? b[0] : 0.f);
+    }
+}
+
+// gradient of the sum of all energies with respect to the pre-activation of the output network's hidden layer:
+// gy[n,f] = w[f] * (1 - a[n,f]^2)
+__global__ void head_backward_kernel(const float *__restrict__ a, const float *__restrict__ w, int64_t N, int64_t F, float *__restrict__ gy) {
+    const int64_t total = N * F;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const float av = a[t];
+        gy[t] = w[t % F] * fmaf(-av, av, 1.f);
+    }
+}
+
+__global__ void add_inplace_kernel(float *__restrict__ y, const float *__restrict__ x, int64_t n) {
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x) y[t] += x[t];
+}
+
+static inline int64_t up4(int64_t n) { return (n + 3) & ~(int64_t)3; }
+
+struct SchnetLayout {
+    int64_t d, x[2], g[2], agg, gy, gxl, ah, en, gyh, gd, gdt, block0, block_stride, xl_off, a_off, wp_off, total;
+};
+static SchnetLayout schnet_layout(int64_t N, int64_t E, int64_t P, int64_t H, int64_t F, int64_t H2, int64_t Wh, int64_t L) {
+    SchnetLayout o;
+    int64_t at = 0;
+    auto take = [&](int64_t n) { const int64_t r = at; at += up4(n); return r; };
+    o.d = take(E);
+    o.x[0] = take(N * H); o.x[1] = take(N * H);
+    o.g[0] = take(N * H); o.g[1] = take(N * H);
+    o.agg = take(N * F); o.gy = take(N * H2); o.gxl = take(N * F);
+    o.ah = take(N * Wh); o.en = take(N); o.gyh = take(N * Wh);
+    o.gd = take(E); o.gdt = take(E);
+    o.xl_off = 0; o.a_off = up4(N * F); o.wp_off = o.a_off + up4(N * H2);
+    o.block_stride = o.wp_off + up4(P * F);
+    o.block0 = at;
+    at += L * o.block_stride;
+    o.total = at;
+    return o;
+}
+
+}  // namespace mlcgb
+
+extern "C" {
+
+size_t mlcgb_schnet_eval_workspace_bytes(int64_t N, int64_t E, int64_t P, int64_t H, int64_t F, int64_t H2, int64_t head_width,
+                                         int64_t num_blocks) {
+    if (N < 0 || E < 0 || P < 0 || H <= 0 || F <= 0 || H2 <= 0 || head_width <= 0 || num_blocks < 0) return 0;
+    return (size_t)schnet_layout(N, E, P, H, F, H2, head_width, num_blocks).total * sizeof(float);
+}
+
+int mlcgb_schnet_eval(const void *pos, const int64_t *types, const int64_t *struct_ptr, int64_t N, int64_t B, const int32_t *row0,
+                      const int32_t *row1, const int64_t *offsets, const int32_t *sel, const int32_t *pair_of, const int32_t *twin,
+                      int64_t E, int64_t P, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper,
+                      const mlcgb_schnet_weights *w, int precision, void *workspace, size_t workspace_bytes, void *energy,
+                      void *grad_pos, int32_t *status, void *stream) {
+    if (N < 0 || B < 0 || E < 0 || P < 0 || !w || !status || !energy || !struct_ptr) return MLCGB_E_ARG;
+    if (B == 0) return MLCGB_OK;
+    const int64_t H = w->hidden, F = w->filters, H2 = w->conv_out, Wh = w->head_width, L = w->num_blocks;
+    if (N < 128 || F != 128 || H > 128 || H2 > 128 || Wh > 128 || (H & 3) || (H2 & 3) || (Wh & 3) || L < 1) return MLCGB_E_LIMIT;
+    if (!pos || !types || !offsets || !w->embedding || !w->blocks || !w->head_W || !w->head_b || !w->head_out || !workspace) return MLCGB_E_ARG;
+    if (E > 0 && (!row0 || !row1 || !sel || !pair_of || !twin || 2 * P != E)) return MLCGB_E_ARG;
+    const SchnetLayout lay = schnet_layout(N, E, P, H, F, H2, Wh, L);
+    if (workspace_bytes < (size_t)lay.total * sizeof(float)) return MLCGB_E_WORKSPACE;
+    float *ws = (float *)workspace;
+    auto st = (cudaStream_t)stream;
+    float *d = ws + lay.d;
+    int rc = mlcgb_edge_distance(pos, MLCGB_F32, row0, row1, E, N, d, status, stream);
+    if (rc) return rc;
+    embedding_rows_kernel<<<grid_for(N * (H >> 2), 256), 256, 0, st>>>((const float *)w->embedding, types, N, H, w->num_types, ws + lay.x[0], status);
+    int cur = 0;
+    for (int64_t l = 0; l < L; l++) {
+        const mlcgb_schnet_block &bw = w->blocks[l];
+        float *blk = ws + lay.block0 + l * lay.block_stride;
+        rc = mlcgb_interaction_forward(ws + lay.x[cur], d, offsets, row1, sel, pair_of, rbf, conv_cutoff_kind, conv_lower, conv_upper, bw.lin1_w,
+                                       bw.filter_w1, bw.filter_b1, bw.filter_w2, bw.lin2_w, bw.lin2_b, bw.lin_w, bw.lin_b, N, E, P, H, F, H2,
+                                       precision, blk + lay.xl_off, blk + lay.wp_off, ws + lay.agg, blk + lay.a_off, ws + lay.x[cur ^ 1], status,
+                                       stream);
+        if (rc) return rc;
+        cur ^= 1;
+    }
+    // output network: tanh(x W^T + b) . w_out (+ b_out), summed per structure
+    rc = mlcgb_gemm_tc_fused(0, ws + lay.x[cur], w->head_W, w->head_b, nullptr, 1, N, Wh, H, ws + lay.ah, status, stream);
+    if (rc) return rc;
+    head_out_kernel<<<grid_for(N * 32, 256), 256, 0, st>>>(ws + lay.ah, (const float *)w->head_out, (const float *)w->head_out_b, N, Wh, ws + lay.en);
+    rc = mlcgb_segment_sum(ws + lay.en, MLCGB_F32, struct_ptr, B, energy, stream);
+    if (rc || !grad_pos) return rc ? rc : check_launch();
+
+    // force pass: d(sum of energies)/d(pos)
+    head_backward_kernel<<<grid_for(N * Wh, 256), 256, 0, st>>>(ws + lay.ah, (const float *)w->head_out, N, Wh, ws + lay.gyh);
+    int gcur = 0;
+    rc = mlcgb_gemm_tc_fused(1, ws + lay.gyh, w->head_W, nullptr, nullptr, 0, N, H, Wh, ws + lay.g[gcur], status, stream);
+    if (rc) return rc;
+    for (int64_t l = L - 1; l >= 0; l--) {
+        const mlcgb_schnet_block &bw = w->blocks[l];
+        float *blk = ws + lay.block0 + l * lay.block_stride;
+        float *gd_l = (l == L - 1) ? ws + lay.gd : ws + lay.gdt;
+        rc = mlcgb_interaction_backward(ws + lay.g[gcur], blk + lay.a_off, blk + lay.wp_off, blk + lay.xl_off, d, offsets, row1, sel, pair_of, twin,
+                                        row0, row1, rbf, conv_cutoff_kind, conv_lower, conv_upper, bw.lin1_w, bw.filter_w1, bw.filter_b1,
+                                        bw.filter_w2, bw.lin2_w, bw.lin_w, N, E, P, H, F, H2, precision, ws + lay.gy, ws + lay.agg, ws + lay.gxl,
+                                        l > 0 ? ws + lay.g[gcur ^ 1] : nullptr, E > 0 ? gd_l : nullptr, status, stream);
+        if (rc) return rc;
+        if (l != L - 1 && E > 0) add_inplace_kernel<<<grid_for(E, 256), 256, 0, st>>>(ws + lay.gd, ws + lay.gdt, E);
+        gcur ^= 1;
+    }
+    // symmetric centre-sorted list: grouped by row0 in place, grouped by row1 through the reverse-edge map
+    return mlcgb_edge_distance_backward(pos, ws + lay.gd, d, MLCGB_F32, row0, row1, offsets, twin, offsets, nullptr, N, E, grad_pos, stream);
+}
+
+}  // extern "C"

@@ -8,7 +8,9 @@ from typing import Final, List
 
 import torch
 
-from ..autograd import EdgeDistanceOnce, FusedFilterConv, FusedInteraction, RowScale, SegIn, SegmentSum, edge_distances, plan_of
+from .. import _lib
+from ..autograd import (EdgeDistanceOnce, FusedFilterConv, FusedInteraction, RowScale, SchNetEval, SegIn, SegmentSum, edge_distances,
+                        plan_of)
 from ..backend import get_backend
 from ..data import ENERGY_KEY
 from ..neighbor_list import atomic_data2neighbor_list, validate_neighborlist
@@ -218,11 +220,69 @@ class SchNet(torch.nn.Module):
             return ptr
         return get_backend().batch_to_ptr(data.batch, int(data.batch[-1]) + 1)
 
+    # ---- whole-model evaluation in one library call (eval mode, standard layout)
+    def _whole_model_slots(self):
+        """(module, parameter name) of every tensor ``mlcgb_schnet_eval`` reads, or None if the layout is not the standard
+        one: nn.Embedding, InteractionBlock(CFConv) blocks with tanh, output network MLP([H, w, 1]) with tanh."""
+        emb, head = self.embedding_layer, self.output_network
+        if type(emb) is not torch.nn.Embedding or not isinstance(head, MLP) or len(head.layers) != 3:
+            return None
+        h0, hact, h1 = head.layers
+        if not (isinstance(h0, torch.nn.Linear) and isinstance(hact, torch.nn.Tanh) and isinstance(h1, torch.nn.Linear)):
+            return None
+        if h0.bias is None or h1.out_features != 1 or h0.in_features != emb.embedding_dim:
+            return None
+        slots = [(emb, "weight"), (h0, "weight"), (h0, "bias"), (h1, "weight"), (h1, "bias")]
+        for b in self.interaction_blocks:
+            if type(b) is not InteractionBlock or type(b.conv) is not CFConv or not isinstance(b.activation, torch.nn.Tanh):
+                return None
+            c, net = b.conv, b.conv.filter_network
+            if not isinstance(net, MLP) or len(net.layers) != 3 or c.lin1.bias is not None or c.lin2.bias is None or b.lin.bias is None:
+                return None
+            slots += [(c.lin1, "weight"), (net.layers[0], "weight"), (net.layers[0], "bias"), (net.layers[2], "weight"), (c.lin2, "weight"),
+                      (c.lin2, "bias"), (b.lin, "weight"), (b.lin, "bias")]
+        return slots
+
+    def packed_weights(self):
+        """``mlcgb_schnet_weights`` over the current parameters (rebuilt whenever a parameter's storage has moved), or None."""
+        slots = self.__dict__.get("_mlcgb_slots", False)
+        if slots is False:
+            slots = self.__dict__["_mlcgb_slots"] = self._whole_model_slots()
+        if slots is None:
+            return None
+        tensors = [m._parameters[n] for m, n in slots]
+        key = tuple(0 if t is None else t.data_ptr() for t in tensors)
+        packed = self.__dict__.get("_mlcgb_packed")
+        if packed is not None and packed[0] == key:
+            return packed[1]
+        ok = all(t is None or (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()) for t in tensors)
+        H = self.embedding_layer.embedding_dim
+        blocks = list(self.interaction_blocks)
+        F, H2, Wh = blocks[0].conv.lin1.out_features, blocks[0].conv.lin2.out_features, self.output_network.layers[0].out_features
+        ok = ok and F == 128 and all(b.conv.lin1.out_features == F and b.conv.lin2.out_features == H2 and b.conv.lin2.in_features == F
+                                     and b.lin.in_features == H2 and b.lin.out_features == H and b.conv.lin1.in_features == H for b in blocks)
+        ok = ok and all(v % 4 == 0 and v <= 128 for v in (H, H2, Wh))
+        result = None
+        if ok:
+            ptr = lambda t: None if t is None else t.data_ptr()
+            arr = (_lib.SchnetBlockStruct * len(blocks))()
+            for i in range(len(blocks)):
+                for f, t in zip(("lin1_w", "filter_w1", "filter_b1", "filter_w2", "lin2_w", "lin2_b", "lin_w", "lin_b"), tensors[5 + 8 * i: 13 + 8 * i]):
+                    setattr(arr[i], f, ptr(t))
+            ws = _lib.SchnetWeightsStruct(H, F, H2, Wh, len(blocks), self.embedding_layer.num_embeddings, arr, ptr(tensors[0]), ptr(tensors[1]),
+                                          ptr(tensors[2]), ptr(tensors[3]), ptr(tensors[4]))
+            result = (ws, (arr, tensors))
+        self.__dict__["_mlcgb_packed"] = (key, result)
+        return result
+
     def forward(self, data):
-        x = self.embedding_layer(data.atom_types)
         neighbor_list = data.neighbor_list.get(self.name)
         if not self.is_nl_compatible(neighbor_list):
             neighbor_list = self.neighbor_list(data, self.rbf_layer.cutoff.cutoff_upper, self.max_num_neighbors)[self.name]
+        fast = self._forward_whole_model(data, neighbor_list)
+        if fast is not None:
+            return fast
+        x = self.embedding_layer(data.atom_types)
         edge_index = neighbor_list["index_mapping"]
         cell_shifts = neighbor_list["cell_shifts"]
         if (not neighbor_list.get("_mlcgb_zero_shifts", False) and cell_shifts is not None and cell_shifts.numel() > 0
@@ -252,6 +312,37 @@ class SchNet(torch.nn.Module):
         if ptr is None or ptr.device != x.device or ptr[-1:].numel() == 0:
             ptr = self._structure_ptr(data)
         energy = SegmentSum.apply(energy, ptr, data.batch).flatten()
+        data.out[self.name] = {ENERGY_KEY: energy}
+        return data
+
+
+    def _forward_whole_model(self, data, neighbor_list):
+        """Eval mode, standard layout, symmetric shift-free edge list, float32 on CUDA, at least 128 beads: energies and their
+        position gradient from one library call (``mlcgb_schnet_eval``); None if any of that does not hold."""
+        be = get_backend()
+        pos = data.pos
+        if (self.training or getattr(be, "profiler", True) is not None or not getattr(be, "tensor_core_gemm", False) or not pos.is_cuda
+                or pos.dtype != torch.float32 or pos.shape[0] < 128 or not neighbor_list.get("_mlcgb_zero_shifts", False)):
+            return None
+        weights = self.packed_weights()
+        if weights is None or weights[1][1][0].device != pos.device:
+            return None
+        plan = plan_of(neighbor_list["index_mapping"], pos.shape[0])
+        if plan.half_selection() is None:
+            return None
+        specs = [b.conv.fused_spec(self.rbf_layer) for b in self.interaction_blocks]
+        if any(s is None for s in specs) or any(s[1] != specs[0][1] for s in specs[1:]):
+            return None
+        precisions = {FILTER_PRECISIONS[b.conv.filter_precision] for b in self.interaction_blocks}
+        if len(precisions) != 1:
+            return None
+        ptr = neighbor_list.get("_mlcgb_ptr")
+        if ptr is None or ptr.device != pos.device:
+            ptr = self._structure_ptr(data)
+        types = data.atom_types
+        if types.dtype != torch.int64 or not types.is_contiguous():
+            types = types.to(torch.int64).contiguous()
+        energy = SchNetEval.apply(pos, types, ptr, data.batch, plan, specs[0][0], specs[0][1], weights, precisions.pop())
         data.out[self.name] = {ENERGY_KEY: energy}
         return data
 
