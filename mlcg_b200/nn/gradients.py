@@ -20,6 +20,16 @@ class GradientsOut(torch.nn.Module):
         assert any(k in GradientsOut._targets for k in self.targets), f"targets={self.targets} should be any of {GradientsOut._targets}"
 
     def forward(self, data):
+        # eval mode: models that can hand out the energy together with its position gradient are evaluated without an
+        # autograd graph (same numbers; create_graph is False in eval mode anyway, gradients.py:191-230)
+        direct = getattr(self.model, "energy_and_gradient", None)
+        if direct is not None and not self.training and FORCE_KEY in self.targets and self.name != "SumOut":
+            res = direct(data)
+            if res is not None:
+                energy, dy_dr = res
+                data.out[self.name] = {ENERGY_KEY: energy, FORCE_KEY: -dy_dr}
+                data.pos = data.pos.detach()
+                return data
         data.pos.requires_grad_(True)
         data = self.model(data)
         if FORCE_KEY in self.targets:

@@ -91,6 +91,15 @@ class _Prior(torch.nn.Module):
             cache[key] = self._params(data).to(data.pos.dtype).contiguous()
         return cache[key]
 
+    def energy_and_gradient(self, data):
+        """(energy [B], d(sum of energies)/d(pos) [N,3]) straight from the prior kernel, without an autograd graph; None where
+        that route does not apply (training mode, tensors off the device)."""
+        if self.training or not data.pos.is_cuda:
+            return None
+        nl = data.neighbor_list[self.name]
+        return get_backend().prior_terms(self.kind, data.pos.detach(), nl["index_mapping"], nl["mapping_batch"], self._cached_params(data),
+                                         _num_structures(data), want_grad=True)
+
     def forward(self, data):
         nl = data.neighbor_list[self.name]
         mapping, mapping_batch = nl["index_mapping"], nl["mapping_batch"]

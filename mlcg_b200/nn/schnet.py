@@ -316,7 +316,28 @@ class SchNet(torch.nn.Module):
         return data
 
 
+    def energy_and_gradient(self, data):
+        """(energy [B], d(sum of energies)/d(pos) [N,3]) from one library call, without an autograd graph; None where the
+        whole-model route does not apply (see :meth:`_forward_whole_model`)."""
+        neighbor_list = data.neighbor_list.get(self.name)
+        if not self.is_nl_compatible(neighbor_list):
+            if self.training or data.pos.shape[0] < 128 or not data.pos.is_cuda or get_backend().profiler is not None:
+                return None                                    # (before paying for a neighbour list this route would not use)
+            neighbor_list = self.neighbor_list(data, self.rbf_layer.cutoff.cutoff_upper, self.max_num_neighbors)[self.name]
+        args = self._whole_model_args(data, neighbor_list)
+        if args is None:
+            return None
+        pos, types, ptr, batch, plan, spec, conv_cut, weights, precision = args
+        return get_backend().schnet_eval(pos.detach().contiguous(), types, ptr, plan, spec, conv_cut, weights, precision, want_grad=True)
+
     def _forward_whole_model(self, data, neighbor_list):
+        args = self._whole_model_args(data, neighbor_list)
+        if args is None:
+            return None
+        data.out[self.name] = {ENERGY_KEY: SchNetEval.apply(*args)}
+        return data
+
+    def _whole_model_args(self, data, neighbor_list):
         """Eval mode, standard layout, symmetric shift-free edge list, float32 on CUDA, at least 128 beads: energies and their
         position gradient from one library call (``mlcgb_schnet_eval``); None if any of that does not hold."""
         be = get_backend()
@@ -342,9 +363,7 @@ class SchNet(torch.nn.Module):
         types = data.atom_types
         if types.dtype != torch.int64 or not types.is_contiguous():
             types = types.to(torch.int64).contiguous()
-        energy = SchNetEval.apply(pos, types, ptr, data.batch, plan, specs[0][0], specs[0][1], weights, precisions.pop())
-        data.out[self.name] = {ENERGY_KEY: energy}
-        return data
+        return pos, types, ptr, data.batch, plan, specs[0][0], specs[0][1], weights, precisions.pop()
 
 
 class StandardSchNet(SchNet):

@@ -295,3 +295,29 @@ def test_whole_model_call_matches_the_individual_kernels():
     doubled = model(mk())
     assert torch.allclose(doubled.out["SchNet"]["energy"], 2.0 * e_w, rtol=1e-5, atol=1e-5 * float(e_w.abs().max()))
     assert torch.allclose(doubled.out["SchNet"]["forces"], 2.0 * f_w, rtol=1e-4, atol=2e-5)
+
+
+def test_neighbour_list_is_rebuilt_for_every_evaluation():
+    """A data object evaluated again after its positions moved gets a new radius graph (the list built on the fly is not kept
+    in the data object, src/mlcg/nn/schnet.py:134-141), on the one-call route and on the per-kernel route."""
+    from mlcg_b200.backend import KernelProfiler, get_backend
+    model, pos, types_, batch = _make("expnormal", 4, 100, 20, 15.0, 128, 128, 2, 11, min_dist=4.0)
+    model = bnn.GradientsOut(model.to(DEV), "forces").eval()
+    mk = lambda p: mlcg_b200.AtomicData(pos=p.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV), n_atoms=torch.full((4,), 100).to(DEV))
+    moved = pos.clone()
+    moved[::7] += 6.0            # changes the edge set
+    be = get_backend()
+    for profiled in (False, True):
+        be.profiler = KernelProfiler(time_kernels=False) if profiled else None
+        try:
+            data = mk(pos)
+            first = model(data).out["SchNet"]["forces"].clone()
+            assert "SchNet" not in data.neighbor_list
+            data.pos = moved.to(DEV)
+            data.out = {}
+            second = model(data).out["SchNet"]["forces"]
+            fresh = model(mk(moved)).out["SchNet"]["forces"]
+        finally:
+            be.profiler = None
+        assert torch.equal(second, fresh)
+        assert float((first - fresh).abs().max()) > 1e-3
