@@ -612,9 +612,11 @@ class CudaBackend:
         _need_cuda(pos, mapping, mapping_batch, params)
         pos, mapping, mapping_batch, params = pos.detach().contiguous(), mapping.contiguous(), mapping_batch.contiguous(), params.contiguous()
         M, N = mapping.shape[1], pos.shape[0]
-        energy = torch.zeros(B, dtype=pos.dtype, device=pos.device)
-        grad = torch.zeros((N, 3), dtype=pos.dtype, device=pos.device) if want_grad else None
-        status = torch.zeros(4, dtype=torch.int32, device=pos.device)
+        # the kernel accumulates: one zero-filled buffer holds the gradient (first, so that it stays 16-byte aligned) and the energies
+        buf = torch.zeros(3 * N + B if want_grad else B, dtype=pos.dtype, device=pos.device)
+        grad = buf[:3 * N].view(N, 3) if want_grad else None
+        energy = buf[3 * N:] if want_grad else buf
+        status = self._sticky_status(pos.device)       # (bit 1: a term with an index out of range was skipped)
         with _on(pos.device):
             self._run("prior_terms", self.lib.mlcgb_prior_terms, (kind, _ptr(pos), _dt(pos), _ptr(mapping), _ptr(mapping_batch), _ptr(params), params.shape[0], M, N, B,
                                                   _ptr(energy), _ptr(grad), _ptr(status), _stream(),), **self._work("prior_terms", locals()))

@@ -140,6 +140,34 @@ def validate_neighborlist(inp: Mapping) -> bool:
     return False
 
 
+def structure_pointer(data) -> torch.Tensor:
+    """Structure boundaries ``ptr[B+1]`` of a collated batch, from ``n_atoms`` when it is there (no device->host read)."""
+    pos = data.pos
+    n_atoms = getattr(data, "n_atoms", None)
+    if n_atoms is not None and torch.is_tensor(n_atoms) and n_atoms.dim() == 1:
+        ptr = torch.zeros(n_atoms.numel() + 1, dtype=torch.int64, device=pos.device)
+        torch.cumsum(n_atoms.to(device=pos.device, dtype=torch.int64), 0, out=ptr[1:])
+        return ptr
+    batch = getattr(data, "batch", None)
+    if batch is None:
+        batch = torch.zeros(pos.shape[0], dtype=torch.long, device=pos.device)
+    return _structure_ptr(pos, batch, None)
+
+
+def edge_plan_for(data, rcut: float, max_num_neighbors: int = 1000):
+    """Radius graph of non-periodic data as (edge plan, structure pointer), without the neighbour-list dictionary around it
+    (no ``mapping_batch``, no ``cell_shifts``): what the one-call evaluation needs and nothing else."""
+    pbc = getattr(data, "pbc", None)
+    if pbc is not None and bool(torch.any(pbc)):
+        raise NotImplementedError("periodic structures are outside the scope of mlcg_b200's radius graph")
+    ptr = structure_pointer(data)
+    be = get_backend()
+    res = be.radius_graph(_as_3d(data.pos), ptr, float(rcut), max_num_neighbors, False, RULE_CLUSTER, want_distance=False, want_batch=False)
+    truncated = bool(res["status"] & STATUS_TRUNCATED)
+    plan = EdgePlan.from_centre_sorted(res["row0"], res["row1"], res["offsets"], data.pos.shape[0], symmetric=not truncated, loops=False)
+    return plan, ptr, res["edge_index"]
+
+
 def atomic_data2neighbor_list(data, rcut: float, self_interaction: bool = False, max_num_neighbors: int = 1000,
                               nls_distance_method: str = "custom_kernel") -> Dict:
     """neighbor_list.py:27-102 for non-periodic data; every supported method name runs the same

@@ -13,7 +13,7 @@ from ..autograd import (EdgeDistanceOnce, FusedFilterConv, FusedInteraction, Row
                         plan_of)
 from ..backend import get_backend
 from ..data import ENERGY_KEY
-from ..neighbor_list import atomic_data2neighbor_list, validate_neighborlist
+from ..neighbor_list import atomic_data2neighbor_list, edge_plan_for, validate_neighborlist
 from .cutoff import cutoff_kind
 from .mlp import MLP, init_xavier_uniform, node_linear
 
@@ -318,52 +318,75 @@ class SchNet(torch.nn.Module):
 
     def energy_and_gradient(self, data):
         """(energy [B], d(sum of energies)/d(pos) [N,3]) from one library call, without an autograd graph; None where the
-        whole-model route does not apply (see :meth:`_forward_whole_model`)."""
-        neighbor_list = data.neighbor_list.get(self.name)
-        if not self.is_nl_compatible(neighbor_list):
-            if self.training or data.pos.shape[0] < 128 or not data.pos.is_cuda or get_backend().profiler is not None:
-                return None                                    # (before paying for a neighbour list this route would not use)
-            neighbor_list = self.neighbor_list(data, self.rbf_layer.cutoff.cutoff_upper, self.max_num_neighbors)[self.name]
-        args = self._whole_model_args(data, neighbor_list)
-        if args is None:
+        whole-model route does not apply (see :meth:`_whole_model_setup`)."""
+        setup = self._whole_model_setup(data.pos)
+        if setup is None:
             return None
-        pos, types, ptr, batch, plan, spec, conv_cut, weights, precision = args
-        return get_backend().schnet_eval(pos.detach().contiguous(), types, ptr, plan, spec, conv_cut, weights, precision, want_grad=True)
+        neighbor_list = data.neighbor_list.get(self.name)
+        if self.is_nl_compatible(neighbor_list):
+            if not neighbor_list.get("_mlcgb_zero_shifts", False):
+                return None
+            plan, ptr = plan_of(neighbor_list["index_mapping"], data.pos.shape[0]), neighbor_list.get("_mlcgb_ptr")
+        else:       # the graph alone: no neighbour-list dictionary, mapping_batch or cell shifts are needed on this route
+            plan, ptr, _ = edge_plan_for(data, self.rbf_layer.cutoff.cutoff_upper, self.max_num_neighbors)
+        if plan.half_selection() is None:
+            return None
+        if ptr is None or ptr.device != data.pos.device:
+            ptr = self._structure_ptr(data)
+        spec, conv_cut, weights, precision = setup
+        return get_backend().schnet_eval(data.pos.detach().contiguous(), self._types(data), ptr, plan, spec, conv_cut, weights, precision,
+                                         want_grad=True)
 
     def _forward_whole_model(self, data, neighbor_list):
-        args = self._whole_model_args(data, neighbor_list)
-        if args is None:
+        setup = self._whole_model_setup(data.pos)
+        if setup is None or not neighbor_list.get("_mlcgb_zero_shifts", False):
             return None
-        data.out[self.name] = {ENERGY_KEY: SchNetEval.apply(*args)}
+        plan = plan_of(neighbor_list["index_mapping"], data.pos.shape[0])
+        if plan.half_selection() is None:
+            return None
+        ptr = neighbor_list.get("_mlcgb_ptr")
+        if ptr is None or ptr.device != data.pos.device:
+            ptr = self._structure_ptr(data)
+        spec, conv_cut, weights, precision = setup
+        data.out[self.name] = {ENERGY_KEY: SchNetEval.apply(data.pos, self._types(data), ptr, data.batch, plan, spec, conv_cut, weights, precision)}
         return data
 
-    def _whole_model_args(self, data, neighbor_list):
-        """Eval mode, standard layout, symmetric shift-free edge list, float32 on CUDA, at least 128 beads: energies and their
-        position gradient from one library call (``mlcgb_schnet_eval``); None if any of that does not hold."""
+    @staticmethod
+    def _types(data):
+        types = data.atom_types
+        if types.dtype != torch.int64 or not types.is_contiguous():
+            types = types.to(torch.int64).contiguous()
+        return types
+
+    def _whole_model_setup(self, pos):
+        """(basis spec, CFConv cutoff, packed weights, filter precision) for ``mlcgb_schnet_eval``, or None: eval mode, no kernel
+        profiler attached, float32 positions on CUDA, at least 128 beads, standard layout with every block on the fused filter
+        kernel, one cutoff and one filter precision for all blocks.  The model-dependent part is worked out once per set of
+        parameter storages and cutoff values."""
         be = get_backend()
-        pos = data.pos
         if (self.training or getattr(be, "profiler", True) is not None or not getattr(be, "tensor_core_gemm", False) or not pos.is_cuda
-                or pos.dtype != torch.float32 or pos.shape[0] < 128 or not neighbor_list.get("_mlcgb_zero_shifts", False)):
+                or pos.dtype != torch.float32 or pos.shape[0] < 128):
             return None
         weights = self.packed_weights()
         if weights is None or weights[1][1][0].device != pos.device:
             return None
-        plan = plan_of(neighbor_list["index_mapping"], pos.shape[0])
-        if plan.half_selection() is None:
-            return None
-        specs = [b.conv.fused_spec(self.rbf_layer) for b in self.interaction_blocks]
-        if any(s is None for s in specs) or any(s[1] != specs[0][1] for s in specs[1:]):
-            return None
-        precisions = {FILTER_PRECISIONS[b.conv.filter_precision] for b in self.interaction_blocks}
-        if len(precisions) != 1:
-            return None
-        ptr = neighbor_list.get("_mlcgb_ptr")
-        if ptr is None or ptr.device != pos.device:
-            ptr = self._structure_ptr(data)
-        types = data.atom_types
-        if types.dtype != torch.int64 or not types.is_contiguous():
-            types = types.to(torch.int64).contiguous()
-        return pos, types, ptr, data.batch, plan, specs[0][0], specs[0][1], weights, precisions.pop()
+        blocks = self.interaction_blocks
+        rc = self.rbf_layer.cutoff
+        rbf = self.rbf_layer
+        key = (id(weights), id(rbf), tuple(map(id, rbf._parameters.values())), tuple(map(id, rbf._buffers.values())),
+               getattr(rc, "cutoff_lower", None), getattr(rc, "cutoff_upper", None),
+               tuple((getattr(b.conv.cutoff, "cutoff_lower", None), getattr(b.conv.cutoff, "cutoff_upper", None), b.conv.filter_precision)
+                     for b in blocks))
+        cached = self.__dict__.get("_mlcgb_setup")
+        if cached is not None and cached[0] == key:
+            return cached[1]
+        specs = [b.conv.fused_spec(self.rbf_layer) for b in blocks]
+        precisions = {FILTER_PRECISIONS[b.conv.filter_precision] for b in blocks}
+        result = None
+        if all(s is not None for s in specs) and all(s[1] == specs[0][1] for s in specs[1:]) and len(precisions) == 1:
+            result = (specs[0][0], specs[0][1], weights, precisions.pop())
+        self.__dict__["_mlcgb_setup"] = (key, result, weights)      # (keeps `weights` alive, so its id stays unique)
+        return result
 
 
 class StandardSchNet(SchNet):
