@@ -21,6 +21,30 @@ inline int check_launch() {
     return MLCGB_OK;
 }
 
+// Programmatic dependent launch: a kernel launched this way may start (on SMs the previous kernel of the stream has
+// already left) before that kernel has finished as a whole; it runs its own set-up — weight tiles, barriers, tensor-memory
+// allocation, nothing that depends on the previous kernel — and calls pdl_wait() before it touches any activation.
+// pdl_wait() returns once the previous kernel has completed and its writes are visible; it is a no-op for a plain launch.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);      // errors surface through cudaGetLastError() in check_launch()
+}
+#endif
+
 inline int grid_for(int64_t work_items, int per_block, int max_waves = 64) {
     int64_t blocks = (work_items + per_block - 1) / per_block;
     int64_t cap = (int64_t)kNumSM * max_waves;

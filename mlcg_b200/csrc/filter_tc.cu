@@ -190,6 +190,8 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
     const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 512);
     if (tid == 0) mbar_init(smem_u32(s_bar2), 1);
     __syncthreads();
+    pdl_wait();                    // set-up done (weights only); from here on the distances of the previous kernels are read
+    pdl_launch_dependents();
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t t_lane = tmem + lane_off;
     const uint32_t bar1 = smem_u32(s_bar), bar2 = smem_u32(s_bar2);
@@ -344,7 +346,7 @@ static int filter_fwd_launch(const FilterFwdParams &p, cudaStream_t st) {
     const int use_map = (make_rows_map(&wmap, p.W, p.E, kF) && !(p.sel && p.twin)) ? 1 : 0;
     const int64_t ntiles = (p.E + tc::kRows - 1) / tc::kRows;
     const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
-    filter_fwd_pipe_kernel<SPLIT, kTcThreads><<<grid, kTcThreads, L::kTotal, st>>>(p, wmap, use_map);
+    launch_pdl(filter_fwd_pipe_kernel<SPLIT, kTcThreads>, dim3(grid), dim3(kTcThreads), L::kTotal, st, p, wmap, use_map);
     return check_launch();
 }
 
@@ -396,6 +398,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
     const float unscale = 1.f / wscale;
 
     const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 512);
+    pdl_wait();                    // set-up done (weights only); everything below reads what earlier kernels wrote
+    pdl_launch_dependents();
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t t_lane = tmem + lane_off;
     const uint32_t T0 = 0, T1 = 128, T2 = 256, TA = 384;
@@ -668,7 +672,7 @@ static int filter_bwd_launch(const FilterBwdParams &q, cudaStream_t st) {
     }
     const int64_t ntiles = (q.f.E + tc::kRows - 1) / tc::kRows;
     const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
-    filter_bwd_pipe_kernel<SPLIT><<<grid, kTcThreads, L::kTotal, st>>>(q);
+    launch_pdl(filter_bwd_pipe_kernel<SPLIT>, dim3(grid), dim3(kTcThreads), L::kTotal, st, q);
     return check_launch();
 }
 

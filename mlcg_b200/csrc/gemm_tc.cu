@@ -239,7 +239,6 @@ gemm_tc_rows_pipe_kernel(const float *__restrict__ A, const float *__restrict__ 
     constexpr float kWS = 64.f;
     const int64_t ntiles = (E + kRows - 1) / kRows;
     const int64_t step = gridDim.x, t0 = blockIdx.x;
-    if (t0 < ntiles) prefetch_tile_to_stage(s_in, A, t0 * kRows, E, K);      // under the set-up below
     const int wrows = MODE == 0 ? N : K, wcols = MODE == 0 ? K : N;
     const int wpad = wcols <= 64 ? 64 : 128;
     if (load_weight_tile<true>(sB_hi, sB_lo, B, wrows, wcols, wpad, kWS) && blockIdx.x == 0) atomicOr(status, (int)kWeightRange);
@@ -256,6 +255,9 @@ gemm_tc_rows_pipe_kernel(const float *__restrict__ A, const float *__restrict__ 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();                                    // set-up done (weights only); A, aux and C belong to the kernels before
+    pdl_launch_dependents();
+    if (t0 < ntiles) prefetch_tile_to_stage(s_in, A, t0 * kRows, E, K);
     const uint32_t tmem = *s_tmem;                 // accumulators at columns [0,128) [128,256), operands at [256,384) [384,512)
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const int ksteps = MODE == 0 ? wpad / 16 : (K + 15) / 16;
@@ -688,12 +690,12 @@ static int rows_pipe_launch(int mode, const void *A, const void *B, const void *
     static bool p0[64] = {false}, p1[64] = {false};
     if (mode == 0) {
         if (int rc = set_smem(gemm_tc_rows_pipe_kernel<0>, p0)) return rc;
-        gemm_tc_rows_pipe_kernel<0><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, (const float *)bias, M, (int)N, (int)K,
-                                                                           (const float *)aux, epi, cmap, status);
+        launch_pdl(gemm_tc_rows_pipe_kernel<0>, dim3(grid), dim3(kGT), GemmTcSmem::kTotal, st, (const float *)A, (const float *)B, (const float *)bias, M,
+                   (int)N, (int)K, (const float *)aux, epi, cmap, status);
     } else {
         if (int rc = set_smem(gemm_tc_rows_pipe_kernel<1>, p1)) return rc;
-        gemm_tc_rows_pipe_kernel<1><<<grid, kGT, GemmTcSmem::kTotal, st>>>((const float *)A, (const float *)B, (const float *)bias, M, (int)N, (int)K,
-                                                                           (const float *)aux, epi, cmap, status);
+        launch_pdl(gemm_tc_rows_pipe_kernel<1>, dim3(grid), dim3(kGT), GemmTcSmem::kTotal, st, (const float *)A, (const float *)B, (const float *)bias, M,
+                   (int)N, (int)K, (const float *)aux, epi, cmap, status);
     }
     return check_launch();
 }
