@@ -70,6 +70,7 @@ namespace mlcgb {
 __global__ void embedding_rows_kernel(const float *__restrict__ table, const int64_t *__restrict__ types, int64_t N, int64_t H, int64_t T,
                                       float *__restrict__ x, int32_t *__restrict__ status) {
     const int64_t Hv = H >> 2, total = N * Hv;
+    pdl_wait();
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
         const int64_t n = t / Hv, c = t - n * Hv;
         int64_t ty = types[n];
@@ -86,6 +87,7 @@ __global__ void head_out_kernel(const float *__restrict__ a, const float *__rest
                                 float *__restrict__ e) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    pdl_wait();
     for (int64_t n = warp; n < N; n += nwarps) {
         float s = 0.f;
         for (int64_t f = lane; f < F; f += 32) s = fmaf(a[n * F + f], w[f], s);
@@ -98,6 +100,7 @@ __global__ void head_out_kernel(const float *__restrict__ a, const float *__rest
 // gy[n,f] = w[f] * (1 - a[n,f]^2)
 __global__ void head_backward_kernel(const float *__restrict__ a, const float *__restrict__ w, int64_t N, int64_t F, float *__restrict__ gy) {
     const int64_t total = N * F;
+    pdl_wait();
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
         const float av = a[t];
         gy[t] = w[t % F] * fmaf(-av, av, 1.f);
@@ -105,6 +108,7 @@ __global__ void head_backward_kernel(const float *__restrict__ a, const float *_
 }
 
 __global__ void add_inplace_kernel(float *__restrict__ y, const float *__restrict__ x, int64_t n) {
+    pdl_wait();
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x) y[t] += x[t];
 }
 
@@ -159,7 +163,7 @@ int mlcgb_schnet_eval(const void *pos, const int64_t *types, const int64_t *stru
     float *d = ws + lay.d;
     int rc = mlcgb_edge_distance(pos, MLCGB_F32, row0, row1, E, N, d, status, stream);
     if (rc) return rc;
-    embedding_rows_kernel<<<grid_for(N * (H >> 2), 256), 256, 0, st>>>((const float *)w->embedding, types, N, H, w->num_types, ws + lay.x[0], status);
+    launch_pdl(embedding_rows_kernel, dim3(grid_for(N * (H >> 2), 256)), dim3(256), 0, st, (const float *)w->embedding, types, N, H, w->num_types, ws + lay.x[0], status);
     int cur = 0;
     for (int64_t l = 0; l < L; l++) {
         const mlcgb_schnet_block &bw = w->blocks[l];
@@ -174,12 +178,12 @@ int mlcgb_schnet_eval(const void *pos, const int64_t *types, const int64_t *stru
     // output network: tanh(x W^T + b) . w_out (+ b_out), summed per structure
     rc = mlcgb_gemm_tc_fused(0, ws + lay.x[cur], w->head_W, w->head_b, nullptr, 1, N, Wh, H, ws + lay.ah, status, stream);
     if (rc) return rc;
-    head_out_kernel<<<grid_for(N * 32, 256), 256, 0, st>>>(ws + lay.ah, (const float *)w->head_out, (const float *)w->head_out_b, N, Wh, ws + lay.en);
+    launch_pdl(head_out_kernel, dim3(grid_for(N * 32, 256)), dim3(256), 0, st, (const float *)(ws + lay.ah), (const float *)w->head_out, (const float *)w->head_out_b, N, Wh, ws + lay.en);
     rc = mlcgb_segment_sum(ws + lay.en, MLCGB_F32, struct_ptr, B, energy, stream);
     if (rc || !grad_pos) return rc ? rc : check_launch();
 
     // force pass: d(sum of energies)/d(pos)
-    head_backward_kernel<<<grid_for(N * Wh, 256), 256, 0, st>>>(ws + lay.ah, (const float *)w->head_out, N, Wh, ws + lay.gyh);
+    launch_pdl(head_backward_kernel, dim3(grid_for(N * Wh, 256)), dim3(256), 0, st, (const float *)(ws + lay.ah), (const float *)w->head_out, N, Wh, ws + lay.gyh);
     int gcur = 0;
     rc = mlcgb_gemm_tc_fused(1, ws + lay.gyh, w->head_W, nullptr, nullptr, 0, N, H, Wh, ws + lay.g[gcur], status, stream);
     if (rc) return rc;
@@ -192,7 +196,7 @@ int mlcgb_schnet_eval(const void *pos, const int64_t *types, const int64_t *stru
                                         bw.filter_w2, bw.lin2_w, bw.lin_w, N, E, P, H, F, H2, precision, ws + lay.gy, ws + lay.agg, ws + lay.gxl,
                                         l > 0 ? ws + lay.g[gcur ^ 1] : nullptr, E > 0 ? gd_l : nullptr, status, stream);
         if (rc) return rc;
-        if (l != L - 1 && E > 0) add_inplace_kernel<<<grid_for(E, 256), 256, 0, st>>>(ws + lay.gd, ws + lay.gdt, E);
+        if (l != L - 1 && E > 0) launch_pdl(add_inplace_kernel, dim3(grid_for(E, 256)), dim3(256), 0, st, ws + lay.gd, (const float *)(ws + lay.gdt), E);
         gcur ^= 1;
     }
     // symmetric centre-sorted list: grouped by row0 in place, grouped by row1 through the reverse-edge map
