@@ -112,6 +112,14 @@ int mlcgb_edge_twin(const int32_t *row0, const int32_t *row1, const int64_t *off
 int mlcgb_pair_index(const int32_t *sel /* [P] */, const int32_t *twin /* [E] */, int64_t P, int32_t *pair_of /* [E] */,
                      void *stream);
 
+/* mlcgb_edge_twin, the selection of one edge per unordered pair (row0 < row1, in list order: sel[P], P = E/2) and
+ * mlcgb_pair_index in one call, for a symmetric, loop-free, centre-sorted list.  An edge without its reverse or a loop sets
+ * status bit 2 (the outputs are then not a valid plan).  No reference counterpart. */
+size_t mlcgb_pair_plan_workspace_bytes(int64_t N);
+int mlcgb_pair_plan(const int32_t *row0, const int32_t *row1, const int64_t *offsets /* [N+1] */, int64_t E, int64_t N,
+                    void *workspace, size_t workspace_bytes, int32_t *twin /* [E] */, int32_t *sel /* [E/2] */,
+                    int32_t *pair_of /* [E] */, int32_t *status, void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Edge geometry.  compute_distances, src/mlcg/geometry/internal_coordinates.py:72-100, split into
  * its linear part dr = pos[row1] - pos[row0] and that part's transpose (used by every derivative).

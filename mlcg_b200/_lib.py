@@ -49,6 +49,8 @@ SIGNATURES = {
     "mlcgb_radius_graph_static": (c_int, [c_vp, c_int, c_vp, c_i64, c_i64, c_dbl, c_i64, c_int, c_int, c_vp, c_vp, c_i64, c_vp,
                                           ctypes.POINTER(c_i64), c_vp, c_vp]),
     "mlcgb_edge_twin": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "mlcgb_pair_plan_workspace_bytes": (c_sz, [c_i64]),
+    "mlcgb_pair_plan": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "mlcgb_pair_index": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp]),
     "mlcgb_edge_diff": (c_int, [c_vp, c_int, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "mlcgb_edge_distance": (c_int, [c_vp, c_int, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),

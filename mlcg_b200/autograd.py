@@ -65,6 +65,12 @@ class EdgePlan:
         be = get_backend()
         E = row0.numel()
         if symmetric:
+            if not loops and E % 2 == 0 and E > 0 and hasattr(be, "pair_plan"):
+                # reverse-edge map, one edge per pair and the edge -> pair index from one library call
+                twin, sel, pair_of, _ = be.pair_plan(row0, row1, offsets, N)
+                plan = EdgePlan(N, E, row0, row1, offsets, None, row1, offsets, twin, row1, True, loops)
+                plan._half, plan._pair_of = sel, pair_of
+                return plan
             twin, _ = be.edge_twin(row0, row1, offsets, N)
             # the k-th edge grouped by row1 is the reverse of the k-th edge grouped by row0
             return EdgePlan(N, E, row0, row1, offsets, None, row1, offsets, twin, row1, True, loops)

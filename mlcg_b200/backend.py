@@ -264,6 +264,21 @@ class CudaBackend:
             self._run("edge_twin", self.lib.mlcgb_edge_twin, (_ptr(row0), _ptr(row1), _ptr(offsets), E, N, _ptr(twin), _ptr(status), _stream(),), **self._work("edge_twin", locals()))
         return twin, status
 
+    def pair_plan(self, row0, row1, offsets, N, fresh_status: bool = False):
+        """(twin [E], sel [E/2], pair_of [E], status words) of a symmetric, loop-free, centre-sorted list with an even number of
+        edges; status bit 2: a missing reverse edge or a loop."""
+        _need_cuda(row0)
+        E, dev = row0.numel(), row0.device
+        out = torch.empty(2 * E + E // 2, dtype=torch.int32, device=dev)
+        twin, pair_of, sel = out[:E], out[E:2 * E], out[2 * E:]
+        wsb = self.lib.mlcgb_pair_plan_workspace_bytes(N)
+        ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
+        status = torch.zeros(4, dtype=torch.int32, device=dev) if fresh_status else self._sticky_status(dev)
+        with _on(dev):
+            self._run("pair_plan", self.lib.mlcgb_pair_plan, (_ptr(row0), _ptr(row1), _ptr(offsets), E, N, _ptr(ws), wsb, _ptr(twin), _ptr(sel), _ptr(pair_of),
+                                                               _ptr(status), _stream()), launches=5, nbytes=28 * E + 20 * N)
+        return twin, sel, pair_of, status
+
     def pair_index(self, sel, twin):
         """pair_of[e] = k for the k-th selected edge and for its reverse."""
         _need_cuda(sel, twin)

@@ -483,6 +483,62 @@ __global__ void pair_index_kernel(const int32_t *__restrict__ sel, const int32_t
     }
 }
 
+// ---- pair plan of a symmetric, loop-free, centre-sorted list in one pass over the nodes, a scan and one pass over the edges.
+// In centre i's segment the neighbours ascend, so its edges with row1 > i ("upper" edges, one per unordered pair) are the
+// tail of the segment: upper[i] of them.
+__global__ void upper_count_kernel(const int32_t *__restrict__ row1, const int64_t *__restrict__ offsets, int64_t N,
+                                   int32_t *__restrict__ upper) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < N; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t lo = offsets[i], hi = offsets[i + 1];
+        const int64_t end = hi;
+        while (lo < hi) {                      // first k with row1[k] > i
+            const int64_t mid = (lo + hi) >> 1;
+            if (row1[mid] <= i) lo = mid + 1; else hi = mid;
+        }
+        upper[i] = (int32_t)(end - lo);
+    }
+}
+
+// twin[e] as edge_twin_kernel; sel[p] = e and pair_of[e] = pair_of[twin[e]] = p, p = rank of the upper edge among all
+// upper edges in list order (uoff = exclusive scan of upper)
+__global__ void pair_plan_kernel(const int32_t *__restrict__ row0, const int32_t *__restrict__ row1, const int64_t *__restrict__ offsets,
+                                 const int32_t *__restrict__ upper, const int64_t *__restrict__ uoff, int64_t E, int64_t N,
+                                 int32_t *__restrict__ twin, int32_t *__restrict__ sel, int32_t *__restrict__ pair_of,
+                                 int32_t *__restrict__ status) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x) {
+        const int a = row0[e], b = row1[e];
+        int32_t t = -1;
+        if (a >= 0 && a < N && b >= 0 && b < N) {
+            int64_t lo = offsets[b], hi = offsets[b + 1];
+            while (lo < hi) {
+                const int64_t mid = (lo + hi) >> 1;
+                if (row1[mid] < a) lo = mid + 1; else hi = mid;
+            }
+            if (lo < offsets[b + 1] && row1[lo] == a) t = (int32_t)lo;
+        } else {
+            atomicOr(status, (int)kBadIndex);
+        }
+        twin[e] = t;
+        if (t < 0 || a == b) {
+            atomicOr(status, (int)kAsymmetric);
+            pair_of[e] = 0;
+            continue;
+        }
+        if (b > a) {
+            const int64_t p = uoff[a] + (e - (offsets[a + 1] - upper[a]));
+            if (p >= (E >> 1)) {               // more upper than lower edges: not symmetric
+                atomicOr(status, (int)kAsymmetric);
+                pair_of[e] = 0;
+                continue;
+            }
+            sel[p] = (int32_t)e;
+            pair_of[e] = (int32_t)p;
+        } else {
+            pair_of[e] = (int32_t)(uoff[b] + (t - (offsets[b + 1] - upper[b])));
+        }
+    }
+}
+
 template <typename T>
 static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn,
                          int loop, int rule, void *ws, size_t ws_bytes, int dtype, int32_t *deg, int64_t *offsets,
@@ -612,6 +668,31 @@ int mlcgb_edge_twin(const int32_t *row0, const int32_t *row1, const int64_t *off
     if (E == 0) return MLCGB_OK;
     if (!row0 || !row1 || !offsets || !twin) return MLCGB_E_ARG;
     edge_twin_kernel<<<grid_for(E, 256), 256, 0, (cudaStream_t)stream>>>(row0, row1, offsets, E, N, twin, status);
+    return check_launch();
+}
+
+size_t mlcgb_pair_plan_workspace_bytes(int64_t N) {
+    if (N < 0) return 0;
+    return align256((size_t)N * 4) + align256((size_t)(N + 1) * 8) + align256((size_t)((N + kScanBlock - 1) / kScanBlock + 1) * 8);
+}
+
+int mlcgb_pair_plan(const int32_t *row0, const int32_t *row1, const int64_t *offsets, int64_t E, int64_t N, void *workspace,
+                    size_t workspace_bytes, int32_t *twin, int32_t *sel, int32_t *pair_of, int32_t *status, void *stream) {
+    if (E < 0 || N < 0 || (E & 1) || !status) return MLCGB_E_ARG;
+    if (E == 0) return MLCGB_OK;
+    if (!row0 || !row1 || !offsets || !twin || !sel || !pair_of || !workspace) return MLCGB_E_ARG;
+    if (workspace_bytes < mlcgb_pair_plan_workspace_bytes(N)) return MLCGB_E_WORKSPACE;
+    auto st = (cudaStream_t)stream;
+    char *w = (char *)workspace;
+    auto *upper = (int32_t *)w;
+    auto *uoff = (int64_t *)(w + align256((size_t)N * 4));
+    auto *bsum = (int64_t *)(w + align256((size_t)N * 4) + align256((size_t)(N + 1) * 8));
+    upper_count_kernel<<<grid_for(N, 256), 256, 0, st>>>(row1, offsets, N, upper);
+    const int64_t nb = (N + kScanBlock - 1) / kScanBlock;
+    scan_block_sums_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(upper, N, bsum);
+    scan_of_sums_kernel<<<1, kScanBlock, 0, st>>>(bsum, nb, uoff + N);
+    scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(upper, N, bsum, uoff);
+    pair_plan_kernel<<<grid_for(E, 256), 256, 0, st>>>(row0, row1, offsets, upper, uoff, E, N, twin, sel, pair_of, status);
     return check_launch();
 }
 

@@ -58,6 +58,11 @@ class OracleBackend:
             status[0] = 4
         return twin, status
 
+    def pair_plan(self, row0, row1, offsets, N, fresh_status=False):
+        twin, status = self.edge_twin(row0, row1, offsets, N)
+        sel = torch.nonzero(row0 < row1).flatten().to(torch.int32)
+        return twin, sel, self.pair_index(sel, twin), status
+
     def pair_index(self, sel, twin):
         pair_of = torch.full((twin.numel(),), -1, dtype=torch.int32)
         k = torch.arange(sel.numel(), dtype=torch.int32)

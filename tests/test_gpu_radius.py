@@ -135,6 +135,34 @@ def test_chain_configurations():
         assert np.array_equal(ei[0][t], ei[1]) and np.array_equal(ei[1][t], ei[0])
 
 
+def test_pair_plan_in_one_call():
+    """Reverse-edge map, one edge per unordered pair and the edge -> pair index from `mlcgb_pair_plan` equal the three
+    separate steps; a list that lacks a reverse edge, or holds a loop, is reported."""
+    from helpers import random_walk_chain
+    from oracle.primitives import OracleBackend
+    be, gen = get_backend(), torch.Generator().manual_seed(1)
+    for n, B, rc in [(2, 1, 30.0), (10, 64, 30.0), (268, 8, 12.0), (1500, 3, 9.0)]:
+        pos = torch.cat([random_walk_chain(n, gen, jitter=0.3) for _ in range(B)]).numpy()
+        res = run_gpu(pos, np.arange(B + 1, dtype=np.int64) * n, rc, 1000, False, "cluster")
+        r0, r1, off = res["row0"], res["row1"], res["offsets"]
+        twin, sel, pair_of, st = be.pair_plan(r0, r1, off, len(pos), fresh_status=True)
+        assert int(st[0]) == 0
+        want = OracleBackend().pair_plan(r0.cpu(), r1.cpu(), off.cpu(), len(pos))
+        for got, ref in zip((twin, sel, pair_of), want):
+            assert torch.equal(got.cpu(), ref)
+        twin2, st = be.edge_twin(r0, r1, off, len(pos), fresh_status=True)
+        assert int(st[0]) == 0 and torch.equal(twin, twin2)
+        assert torch.equal(pair_of, be.pair_index(sel, twin))
+    # drop one edge and its successor (the count stays even): the reverse of a kept edge is missing
+    keep = torch.ones(r0.numel(), dtype=torch.bool, device=r0.device)
+    keep[5:7] = False
+    r0b, r1b = r0[keep].contiguous(), r1[keep].contiguous()
+    offb = torch.zeros_like(off)
+    offb[1:] = torch.cumsum(torch.bincount(r0b.long(), minlength=len(pos)), 0)
+    *_, st = be.pair_plan(r0b, r1b, offb, len(pos), fresh_status=True)
+    assert int(st[0]) & 4
+
+
 def test_full_size_standalone_configuration_properties():
     """256 x 4000 points (65 M edges): size-independent properties on the whole output, oracle on a sample."""
     rng = np.random.default_rng(0)
