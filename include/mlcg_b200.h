@@ -114,7 +114,10 @@ int mlcgb_pair_index(const int32_t *sel /* [P] */, const int32_t *twin /* [E] */
 
 /* mlcgb_edge_twin, the selection of one edge per unordered pair (row0 < row1, in list order: sel[P], P = E/2) and
  * mlcgb_pair_index in one call, for a symmetric, loop-free, centre-sorted list.  An edge without its reverse or a loop sets
- * status bit 2 (the outputs are then not a valid plan).  No reference counterpart. */
+ * status bit 2: the outputs are then not a valid plan, but every entry written is a valid index (twin[e] = e, pair_of[e] = 0
+ * for such an edge), so that kernels already queued behind the call stay inside their arrays.  `sel` entries that no pair
+ * claims are left as they were: zero the array first if that can happen.  The edge count is read from offsets[N] on the
+ * device (E may be the larger capacity of the arrays).  No reference counterpart. */
 size_t mlcgb_pair_plan_workspace_bytes(int64_t N);
 int mlcgb_pair_plan(const int32_t *row0, const int32_t *row1, const int64_t *offsets /* [N+1] */, int64_t E, int64_t N,
                     void *workspace, size_t workspace_bytes, int32_t *twin /* [E] */, int32_t *sel /* [E/2] */,
@@ -321,6 +324,38 @@ int mlcgb_schnet_eval(const void *pos /* [N,3] */, const int64_t *types /* [N] *
 /* out[b] = sum_{n in [ptr[b],ptr[b+1])} x[n]  — the per-structure energy sum, src/mlcg/nn/schnet.py:158 */
 int mlcgb_segment_sum(const void *x /* [N] */, int dtype, const int64_t *ptr /* [B+1] */, int64_t B, void *out /* [B] */,
                       void *stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Capacity mode: the whole evaluation without a host read of the edge count, so that a molecular-dynamics step can be
+ * recorded into a CUDA graph (the reference reads the count on the host in every step, radius.cu:288).
+ *
+ * mlcgb_radius_graph_capacity = mlcgb_radius_count + mlcgb_radius_fill into buffers of `capacity` edges: offsets beyond the
+ * capacity are clamped, so at most `capacity` edges are written, and status bit 5 (32) reports the overflow (the list is
+ * then incomplete).  counts[0] = edges written, counts[1] = counts[0] / 2, both in device memory.  edge_index ([2,capacity]
+ * int64) may be NULL when only the int32 rows are wanted.
+ *
+ * The *_counted entry points take such a device-side count next to the host-side size: the host-side size is the capacity of
+ * the buffers and sizes the launch, the kernels work on min(size, *count) rows.  Index arrays must hold valid indices
+ * (e.g. zero) in their unused tail.  mlcgb_pair_plan reads the edge count from offsets[N], so it needs no extra argument.
+ * ---------------------------------------------------------------------------------------------- */
+int mlcgb_radius_graph_capacity(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn,
+                                int loop, int rule, void *workspace, size_t workspace_bytes, int32_t *deg /* [N] */,
+                                int64_t *offsets /* [N+1] */, int64_t capacity, int64_t *edge_index /* [2,capacity] or NULL */,
+                                int32_t *row0_i32 /* [capacity] */, int32_t *row1_i32 /* [capacity] */, int64_t *counts /* [2] */,
+                                int32_t *status, void *stream);
+int mlcgb_filter_forward_counted(const void *d, int64_t E, const int64_t *rows_dev, const int32_t *sel, const int32_t *twin,
+                                 const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1,
+                                 const void *b1, const void *A2, int64_t F, int precision, void *W, int32_t *status, void *stream);
+int mlcgb_filter_backward_counted(const void *d, int64_t E, const int64_t *rows_dev, const int32_t *sel, const int32_t *twin,
+                                  const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1,
+                                  const void *b1, const void *A2, int64_t F, int precision, const int32_t *row0, const int32_t *row1,
+                                  const void *xl, const void *gagg, int64_t N, void *gd, int32_t *status, void *stream);
+int mlcgb_schnet_eval_counted(const void *pos, const int64_t *types, const int64_t *struct_ptr, int64_t N, int64_t B,
+                              const int32_t *row0, const int32_t *row1, const int64_t *offsets, const int32_t *sel,
+                              const int32_t *pair_of, const int32_t *twin, int64_t E, int64_t P, const int64_t *counts /* [2] or NULL */,
+                              const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper,
+                              const mlcgb_schnet_weights *weights, int precision, void *workspace, size_t workspace_bytes,
+                              void *energy, void *grad_pos, int32_t *status, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Prior energy terms with analytic gradients.  `kind`:

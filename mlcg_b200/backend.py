@@ -68,6 +68,12 @@ def _raise_for_status(word: int, what: str) -> None:
     """Status bits the tensor-core kernels set (read lazily, with the next unavoidable host read)."""
     if word & 8:
         raise RuntimeError(f"mlcg_b200: {what}: a tensor-core wait ran out; results are incomplete")
+    if word & 32:
+        raise RuntimeError(f"mlcg_b200: {what}: the radius graph has more edges than the fixed edge capacity; results are incomplete "
+                           "(raise the capacity)")
+    if word & 4:
+        raise RuntimeError(f"mlcg_b200: {what}: the edge list is not symmetric (an edge without its reverse, e.g. after the neighbour "
+                           "cap cut a list short)")
     if word & 16:
         raise RuntimeError(f"mlcg_b200: {what}: a weight is beyond the range of the fp16-pair tensor-core operands (|w| > 512); "
                            "set mlcg_b200.backend.get_backend().tensor_core_gemm = False to run these layers on the CUDA cores")
@@ -151,7 +157,7 @@ class CudaBackend:
     def _raise_pending(words, pending):
         """Raise for the first status word that reports a failure; the words are cleared first, so one failure is reported
         once and later evaluations start clean."""
-        bad = [(w, what) for w, (_, what) in zip(words, pending) if w & (8 | 16)]
+        bad = [(w, what) for w, (_, what) in zip(words, pending) if w & (4 | 8 | 16 | 32)]
         if bad:
             for st, _ in pending:
                 st.zero_()
@@ -253,6 +259,33 @@ class CudaBackend:
                           **self._work("radius_fill", locals()))
         return dict(edge_index=ei, distance=dist, mapping_batch=mb, row0=r0, row1=r1, offsets=offsets, status=st)
 
+    def radius_graph_capacity(self, pos, ptr, r, max_num_neighbors, capacity, rows=None, rule=1):
+        """The radius graph into buffers of ``capacity`` edges without reading the edge count on the host:
+        dict(row0, row1 (int32 [capacity]), offsets [N+1], counts (int64 [2] on the device: edges, edges / 2)).  ``rows``: an int32
+        ``[2, capacity]`` buffer to reuse, whose entries are valid point indices (zeros at first).  An overflow sets bit 5 of the
+        backend's accumulating status words (reported by :meth:`check_pending`)."""
+        _need_cuda(pos, ptr)
+        pos = pos.detach().contiguous()
+        N, B, dev = pos.shape[0], ptr.numel() - 1, pos.device
+        dt = _dt(pos)
+        capacity = int(capacity)
+        if capacity < 0 or capacity % 2:
+            raise ValueError("capacity must be a non-negative even number of edges")
+        if rows is None:
+            rows = torch.zeros((2, capacity), dtype=torch.int32, device=dev)
+        with _on(dev):
+            ws_bytes = self.lib.mlcgb_radius_workspace_bytes(N, B, dt)
+            ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+            deg = torch.empty(max(N, 1), dtype=torch.int32, device=dev)
+            offsets = torch.empty(N + 1, dtype=torch.int64, device=dev)
+            counts = torch.empty(2, dtype=torch.int64, device=dev)
+            status = self._sticky_status(dev)
+            self._run("radius_graph_capacity", self.lib.mlcgb_radius_graph_capacity,
+                      (_ptr(pos), dt, _ptr(ptr), N, B, float(r), int(max_num_neighbors), 0, int(rule), _ptr(ws), ws_bytes, _ptr(deg), _ptr(offsets),
+                       capacity, None, _ptr(rows[0]), _ptr(rows[1]), _ptr(counts), _ptr(status), _stream()), launches=7, nbytes=N * 24 + capacity * 8)
+        self.defer_status(status, "radius graph with a fixed edge capacity")
+        return dict(row0=rows[0], row1=rows[1], offsets=offsets, counts=counts)
+
     def edge_twin(self, row0, row1, offsets, N, fresh_status: bool = False):
         """twin[e] = position of the reversed edge; second value: the status words (bit 2: an edge without its reverse).  By default
         the words are the backend's accumulating ones; ``fresh_status=True`` gives this call its own."""
@@ -269,7 +302,7 @@ class CudaBackend:
         edges; status bit 2: a missing reverse edge or a loop."""
         _need_cuda(row0)
         E, dev = row0.numel(), row0.device
-        out = torch.empty(2 * E + E // 2, dtype=torch.int32, device=dev)
+        out = torch.zeros(2 * E + E // 2, dtype=torch.int32, device=dev)    # (entries no edge claims stay valid indices)
         twin, pair_of, sel = out[:E], out[E:2 * E], out[2 * E:]
         wsb = self.lib.mlcgb_pair_plan_workspace_bytes(N)
         ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
@@ -531,9 +564,10 @@ class CudaBackend:
         self.defer_status(status, "interaction block (backward)")
         return gx, gd
 
-    def schnet_eval(self, pos, types, struct_ptr, plan, spec: RbfSpec, conv_cut, weights, precision, want_grad=True):
+    def schnet_eval(self, pos, types, struct_ptr, plan, spec: RbfSpec, conv_cut, weights, precision, want_grad=True, counts=None):
         """Energies [B] and d(sum of energies)/d(pos) [N,3] of a standard SchNet in one library call.  ``weights`` is what
-        :func:`mlcg_b200.nn.schnet.packed_weights` returns: ``(SchnetWeightsStruct, keep-alive objects)``."""
+        :func:`mlcg_b200.nn.schnet.packed_weights` returns: ``(SchnetWeightsStruct, keep-alive objects)``.  ``counts``: the
+        device-side (edges, pairs) of a fixed-capacity graph, whose plan is sized by the capacity."""
         wstruct, _keep = weights
         N, dev = pos.shape[0], pos.device
         B = struct_ptr.numel() - 1
@@ -547,9 +581,9 @@ class CudaBackend:
         grad = torch.empty((N, 3), dtype=torch.float32, device=dev) if want_grad else None
         status = self._sticky_status(dev)
         with _on(dev):
-            _lib.check(self.lib.mlcgb_schnet_eval(
+            _lib.check(self.lib.mlcgb_schnet_eval_counted(
                 _ptr(pos), _ptr(types), _ptr(struct_ptr), N, B, _ptr(plan.row0), _ptr(plan.row1), _ptr(plan.ptr_out), _ptr(sel), _ptr(pair_of),
-                _ptr(plan.perm_in), plan.E, P, ctypes.byref(s), int(conv_cut[0]), float(conv_cut[1]), float(conv_cut[2]), ctypes.byref(wstruct),
+                _ptr(plan.perm_in), plan.E, P, _ptr(counts), ctypes.byref(s), int(conv_cut[0]), float(conv_cut[1]), float(conv_cut[2]), ctypes.byref(wstruct),
                 int(precision), _ptr(ws), wsb, _ptr(energy), _ptr(grad), _ptr(status), _stream()), "schnet_eval")
         self.defer_status(status, "SchNet evaluation")
         return energy, grad

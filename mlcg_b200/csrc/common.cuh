@@ -8,7 +8,7 @@ namespace mlcgb {
 
 constexpr int kNumSM = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
 
-enum StatusBits : int { kTruncated = 1, kBadIndex = 2, kAsymmetric = 4, kTensorWait = 8, kWeightRange = 16 };
+enum StatusBits : int { kTruncated = 1, kBadIndex = 2, kAsymmetric = 4, kTensorWait = 8, kWeightRange = 16, kCapacity = 32 };
 
 extern thread_local int g_last_cuda_error;
 

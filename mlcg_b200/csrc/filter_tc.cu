@@ -27,6 +27,8 @@ constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
 struct FilterFwdParams {
     const float *d;      // [E]
     int64_t E;           // rows to process: all edges, or one edge per unordered pair when `sel` is given
+    const int64_t *rows_dev;  // NULL, or the row count in device memory (written by an earlier kernel on the stream): the
+                              // kernel then processes min(E, *rows_dev) rows and E only sizes the grid and the buffers
     const int32_t *sel;  // [E] edge handled by row k (NULL: k itself)
     const int32_t *twin; // reverse edge of each edge (NULL: none); with `sel`, results go to both edges of a pair
                          // (forward with `sel` alone: W has E rows, row k is the filter of edge sel[k])
@@ -38,6 +40,13 @@ struct FilterFwdParams {
     float *W;            // [E][kF]
     int32_t *status;
 };
+
+// rows the kernel works on; read after the wait on the preceding kernels
+__device__ __forceinline__ int64_t live_rows(const FilterFwdParams &p) {
+    if (!p.rows_dev) return p.E;
+    const int64_t n = *reinterpret_cast<const volatile int64_t *>(p.rows_dev);
+    return n < 0 ? 0 : (n < p.E ? n : p.E);
+}
 
 template <bool SPLIT>
 struct FilterSmem {
@@ -199,12 +208,13 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
     uint32_t ph1 = 0, ph2 = 0;
     bool failed = false;
 
-    const int64_t ntiles = (p.E + kRows - 1) / kRows;
+    const int64_t nE = live_rows(p);
+    const int64_t ntiles = (nE + kRows - 1) / kRows;
     const int64_t first = blockIdx.x, step = gridDim.x;
 
     auto load_d = [&](int64_t tile) {
         const int64_t k = tile * kRows + r;
-        return k < p.E ? p.d[p.sel ? (int64_t)p.sel[k] : k] : 1.f;
+        return k < nE ? p.d[p.sel ? (int64_t)p.sel[k] : k] : 1.f;
     };
     const bool same_env = p.conv.cutoff_kind == p.rbf.cutoff_kind && p.conv.lower == p.rbf.lower && p.conv.upper == p.rbf.upper;
     // phi_k(d) for this thread's columns -> A operand; returns the CFConv cutoff C(d) of the row (the envelope of the basis
@@ -260,7 +270,7 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
         for (int i = 0; i < RPW; i++) {
             const int row = warp * RPW + i;
             const int64_t kr = tile * kRows + row;
-            if (kr < p.E) {
+            if (kr < nE) {
                 const int64_t er = (p.sel && p.twin) ? (int64_t)p.sel[kr] : kr;   // sel without twin: one row per pair, in order
                 const float4 w4 = *stage_chunk(stage, row, lane);
                 __stcs(reinterpret_cast<float4 *>(p.W + er * kF) + lane, w4);
@@ -400,6 +410,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
     const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 512);
     pdl_wait();                    // set-up done (weights only); everything below reads what earlier kernels wrote
     pdl_launch_dependents();
+    const int64_t nE = live_rows(p);
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t t_lane = tmem + lane_off;
     const uint32_t T0 = 0, T1 = 128, T2 = 256, TA = 384;
@@ -451,7 +462,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
     auto row_index = [&](int64_t tile) {
         RowIdx x;
         const int64_t krow = tile * kRows + r;
-        x.live = krow < p.E;
+        x.live = krow < nE;
         x.e = x.live ? (p.sel ? (int64_t)p.sel[krow] : krow) : 0;
         x.i0 = x.live ? q.row0[x.e] : 0;
         x.i1 = x.live ? q.row1[x.e] : 0;
@@ -474,7 +485,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
         tmem_wait_st();
     };
 
-    const int64_t ntiles = (p.E + kRows - 1) / kRows;
+    const int64_t ntiles = (nE + kRows - 1) / kRows;
     const int64_t first = blockIdx.x, step = gridDim.x;
     EdgeScalars es{};
     RowIdx ri{0, 0, 0, false};
@@ -680,9 +691,10 @@ static int filter_bwd_launch(const FilterBwdParams &q, cudaStream_t st) {
 
 using namespace mlcgb;
 
-extern "C" int mlcgb_filter_forward(const void *d, int64_t E, const int32_t *sel, const int32_t *twin, const mlcgb_rbf_spec *rbf,
-                                    int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1,
-                                    const void *A2, int64_t F, int precision, void *W, int32_t *status, void *stream) {
+extern "C" int mlcgb_filter_forward_counted(const void *d, int64_t E, const int64_t *rows_dev, const int32_t *sel, const int32_t *twin,
+                                            const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper,
+                                            const void *A1, const void *b1, const void *A2, int64_t F, int precision, void *W,
+                                            int32_t *status, void *stream) {
     if (int rc = check_spec(rbf, 0)) return rc;
     if (E < 0 || !status || (precision != 0 && precision != 1) || (conv_cutoff_kind != 0 && conv_cutoff_kind != 1)) return MLCGB_E_ARG;
     if (F != kF || rbf->num_rbf > 128) return MLCGB_E_LIMIT;
@@ -691,6 +703,7 @@ extern "C" int mlcgb_filter_forward(const void *d, int64_t E, const int32_t *sel
     FilterFwdParams p;
     p.d = (const float *)d;
     p.E = E;
+    p.rows_dev = rows_dev;
     p.sel = sel;
     p.twin = twin;
     p.rbf = to_dev<float>(rbf);
@@ -706,10 +719,18 @@ extern "C" int mlcgb_filter_forward(const void *d, int64_t E, const int32_t *sel
     return precision == 0 ? filter_fwd_launch<true>(p, (cudaStream_t)stream) : filter_fwd_launch<false>(p, (cudaStream_t)stream);
 }
 
-extern "C" int mlcgb_filter_backward(const void *d, int64_t E, const int32_t *sel, const int32_t *twin, const mlcgb_rbf_spec *rbf,
-                                     int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1,
-                                     const void *A2, int64_t F, int precision, const int32_t *row0, const int32_t *row1, const void *xl,
-                                     const void *gagg, int64_t N, void *gd, int32_t *status, void *stream) {
+extern "C" int mlcgb_filter_forward(const void *d, int64_t E, const int32_t *sel, const int32_t *twin, const mlcgb_rbf_spec *rbf,
+                                    int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1,
+                                    const void *A2, int64_t F, int precision, void *W, int32_t *status, void *stream) {
+    return mlcgb_filter_forward_counted(d, E, nullptr, sel, twin, rbf, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, F, precision, W,
+                                        status, stream);
+}
+
+extern "C" int mlcgb_filter_backward_counted(const void *d, int64_t E, const int64_t *rows_dev, const int32_t *sel, const int32_t *twin,
+                                             const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper,
+                                             const void *A1, const void *b1, const void *A2, int64_t F, int precision,
+                                             const int32_t *row0, const int32_t *row1, const void *xl, const void *gagg, int64_t N,
+                                             void *gd, int32_t *status, void *stream) {
     if (int rc = check_spec(rbf, 1)) return rc;
     if (E < 0 || N < 0 || !status || (precision != 0 && precision != 1) || (conv_cutoff_kind != 0 && conv_cutoff_kind != 1)) return MLCGB_E_ARG;
     if (F != kF || rbf->num_rbf > 128) return MLCGB_E_LIMIT;
@@ -718,6 +739,7 @@ extern "C" int mlcgb_filter_backward(const void *d, int64_t E, const int32_t *se
     FilterBwdParams q;
     q.f.d = (const float *)d;
     q.f.E = E;
+    q.f.rows_dev = rows_dev;
     q.f.sel = sel;
     q.f.twin = twin;
     q.f.rbf = to_dev<float>(rbf);
@@ -736,4 +758,12 @@ extern "C" int mlcgb_filter_backward(const void *d, int64_t E, const int32_t *se
     q.gagg = (const float *)gagg;
     q.gd = (float *)gd;
     return precision == 0 ? filter_bwd_launch<true>(q, (cudaStream_t)stream) : filter_bwd_launch<false>(q, (cudaStream_t)stream);
+}
+
+extern "C" int mlcgb_filter_backward(const void *d, int64_t E, const int32_t *sel, const int32_t *twin, const mlcgb_rbf_spec *rbf,
+                                     int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1,
+                                     const void *A2, int64_t F, int precision, const int32_t *row0, const int32_t *row1, const void *xl,
+                                     const void *gagg, int64_t N, void *gd, int32_t *status, void *stream) {
+    return mlcgb_filter_backward_counted(d, E, nullptr, sel, twin, rbf, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, F, precision,
+                                         row0, row1, xl, gagg, N, gd, status, stream);
 }

@@ -9,12 +9,37 @@ using namespace mlcgb;
 
 extern "C" {
 
+static int interaction_forward_counted(const void *x, const void *d, const int64_t *ptr_out, const int32_t *nbr_out, const int32_t *sel,
+                                      const int32_t *pair_of, const int64_t *pairs_dev, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind,
+                                      double conv_lower, double conv_upper, const void *W1, const void *fA1, const void *fb1,
+                                      const void *fA2, const void *W2, const void *b2, const void *W3, const void *b3, int64_t N, int64_t E,
+                                      int64_t P, int64_t H, int64_t F, int64_t H2, int precision, void *xl, void *Wp, void *agg, void *a,
+                                      void *out, int32_t *status, void *stream);
+static int interaction_backward_counted(const void *g, const void *a, const void *Wp, const void *xl, const void *d, const int64_t *ptr_out,
+                                       const int32_t *nbr_out, const int32_t *sel, const int32_t *pair_of, const int32_t *twin,
+                                       const int64_t *pairs_dev, const int32_t *row0, const int32_t *row1, const mlcgb_rbf_spec *rbf,
+                                       int conv_cutoff_kind, double conv_lower, double conv_upper, const void *W1, const void *fA1,
+                                       const void *fb1, const void *fA2, const void *W2, const void *W3, int64_t N, int64_t E, int64_t P,
+                                       int64_t H, int64_t F, int64_t H2, int precision, void *gy, void *gagg, void *gxl, void *gx,
+                                       void *gd, int32_t *status, void *stream);
+
 int mlcgb_interaction_forward(const void *x, const void *d, const int64_t *ptr_out, const int32_t *nbr_out, const int32_t *sel,
                               const int32_t *pair_of, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower,
                               double conv_upper, const void *W1, const void *fA1, const void *fb1, const void *fA2, const void *W2,
                               const void *b2, const void *W3, const void *b3, int64_t N, int64_t E, int64_t P, int64_t H, int64_t F,
                               int64_t H2, int precision, void *xl, void *Wp, void *agg, void *a, void *out, int32_t *status,
                               void *stream) {
+    return interaction_forward_counted(x, d, ptr_out, nbr_out, sel, pair_of, nullptr, rbf, conv_cutoff_kind, conv_lower, conv_upper, W1,
+                                             fA1, fb1, fA2, W2, b2, W3, b3, N, E, P, H, F, H2, precision, xl, Wp, agg, a, out, status, stream);
+}
+
+// pairs_dev: NULL, or the number of pairs in device memory; P then only sizes the buffers (see mlcgb_filter_forward_counted)
+static int interaction_forward_counted(const void *x, const void *d, const int64_t *ptr_out, const int32_t *nbr_out, const int32_t *sel,
+                                      const int32_t *pair_of, const int64_t *pairs_dev, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind,
+                                      double conv_lower, double conv_upper, const void *W1, const void *fA1, const void *fb1,
+                                      const void *fA2, const void *W2, const void *b2, const void *W3, const void *b3, int64_t N, int64_t E,
+                                      int64_t P, int64_t H, int64_t F, int64_t H2, int precision, void *xl, void *Wp, void *agg, void *a,
+                                      void *out, int32_t *status, void *stream) {
     if (N < 0 || E < 0 || P < 0 || !status) return MLCGB_E_ARG;
     if (N == 0) return MLCGB_OK;
     if (!x || !ptr_out || !W1 || !W2 || !b2 || !W3 || !b3 || !xl || !agg || !a || !out) return MLCGB_E_ARG;
@@ -22,7 +47,8 @@ int mlcgb_interaction_forward(const void *x, const void *d, const int64_t *ptr_o
     if (N < 128 || (H & 3) || (F & 3) || (H2 & 3) || H > 128 || F != 128 || H2 > 128) return MLCGB_E_LIMIT;
     int rc = mlcgb_gemm_tc_fused(0, x, W1, nullptr, nullptr, 0, N, F, H, xl, status, stream);                 // lin1 (no bias)
     if (rc) return rc;
-    rc = mlcgb_filter_forward(d, P, sel, nullptr, rbf, conv_cutoff_kind, conv_lower, conv_upper, fA1, fb1, fA2, F, precision, Wp, status, stream);
+    rc = mlcgb_filter_forward_counted(d, P, pairs_dev, sel, nullptr, rbf, conv_cutoff_kind, conv_lower, conv_upper, fA1, fb1, fA2, F, precision,
+                                      Wp, status, stream);
     if (rc) return rc;
     rc = mlcgb_seg_mul_sum(xl, Wp, MLCGB_F32, ptr_out, nbr_out, pair_of, N, P, F, agg, stream);                // aggregation
     if (rc) return rc;
@@ -38,6 +64,18 @@ int mlcgb_interaction_backward(const void *g, const void *a, const void *Wp, con
                                const void *fA2, const void *W2, const void *W3, int64_t N, int64_t E, int64_t P, int64_t H, int64_t F,
                                int64_t H2, int precision, void *gy, void *gagg, void *gxl, void *gx /* or NULL */,
                                void *gd /* [E] or NULL */, int32_t *status, void *stream) {
+    return interaction_backward_counted(g, a, Wp, xl, d, ptr_out, nbr_out, sel, pair_of, twin, nullptr, row0, row1, rbf, conv_cutoff_kind,
+                                              conv_lower, conv_upper, W1, fA1, fb1, fA2, W2, W3, N, E, P, H, F, H2, precision, gy, gagg, gxl,
+                                              gx, gd, status, stream);
+}
+
+static int interaction_backward_counted(const void *g, const void *a, const void *Wp, const void *xl, const void *d, const int64_t *ptr_out,
+                                       const int32_t *nbr_out, const int32_t *sel, const int32_t *pair_of, const int32_t *twin,
+                                       const int64_t *pairs_dev, const int32_t *row0, const int32_t *row1, const mlcgb_rbf_spec *rbf,
+                                       int conv_cutoff_kind, double conv_lower, double conv_upper, const void *W1, const void *fA1,
+                                       const void *fb1, const void *fA2, const void *W2, const void *W3, int64_t N, int64_t E, int64_t P,
+                                       int64_t H, int64_t F, int64_t H2, int precision, void *gy, void *gagg, void *gxl,
+                                       void *gx /* or NULL */, void *gd /* [E] or NULL */, int32_t *status, void *stream) {
     if (N < 0 || E < 0 || P < 0 || !status) return MLCGB_E_ARG;
     if (N == 0) return MLCGB_OK;
     if (!g || !a || !xl || !ptr_out || !W1 || !W2 || !W3 || !gy || !gagg || !gxl) return MLCGB_E_ARG;
@@ -54,8 +92,8 @@ int mlcgb_interaction_backward(const void *g, const void *a, const void *Wp, con
         if (rc) return rc;
     }
     if (gd && E > 0)
-        rc = mlcgb_filter_backward(d, P, sel, twin, rbf, conv_cutoff_kind, conv_lower, conv_upper, fA1, fb1, fA2, F, precision, row0, row1,
-                                   xl, gagg, N, gd, status, stream);
+        rc = mlcgb_filter_backward_counted(d, P, pairs_dev, sel, twin, rbf, conv_cutoff_kind, conv_lower, conv_upper, fA1, fb1, fA2, F, precision,
+                                           row0, row1, xl, gagg, N, gd, status, stream);
     return rc;
 }
 
@@ -150,6 +188,21 @@ int mlcgb_schnet_eval(const void *pos, const int64_t *types, const int64_t *stru
                       int64_t E, int64_t P, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper,
                       const mlcgb_schnet_weights *w, int precision, void *workspace, size_t workspace_bytes, void *energy,
                       void *grad_pos, int32_t *status, void *stream) {
+    return mlcgb_schnet_eval_counted(pos, types, struct_ptr, N, B, row0, row1, offsets, sel, pair_of, twin, E, P, nullptr, rbf,
+                                     conv_cutoff_kind, conv_lower, conv_upper, w, precision, workspace, workspace_bytes, energy, grad_pos,
+                                     status, stream);
+}
+
+// counts: NULL, or {edges, pairs} in device memory as mlcgb_radius_graph_capacity leaves them.  E and P are then the
+// capacities of the index arrays (whose entries past the live ones must be valid node / edge indices, e.g. zero): the
+// edge-sized elementwise kernels run over the capacity, the filter kernels over the live pairs, everything else over nodes.
+int mlcgb_schnet_eval_counted(const void *pos, const int64_t *types, const int64_t *struct_ptr, int64_t N, int64_t B,
+                              const int32_t *row0, const int32_t *row1, const int64_t *offsets, const int32_t *sel,
+                              const int32_t *pair_of, const int32_t *twin, int64_t E, int64_t P, const int64_t *counts,
+                              const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper,
+                              const mlcgb_schnet_weights *w, int precision, void *workspace, size_t workspace_bytes, void *energy,
+                              void *grad_pos, int32_t *status, void *stream) {
+    const int64_t *pairs_dev = counts ? counts + 1 : nullptr;
     if (N < 0 || B < 0 || E < 0 || P < 0 || !w || !status || !energy || !struct_ptr) return MLCGB_E_ARG;
     if (B == 0) return MLCGB_OK;
     const int64_t H = w->hidden, F = w->filters, H2 = w->conv_out, Wh = w->head_width, L = w->num_blocks;
@@ -168,7 +221,7 @@ int mlcgb_schnet_eval(const void *pos, const int64_t *types, const int64_t *stru
     for (int64_t l = 0; l < L; l++) {
         const mlcgb_schnet_block &bw = w->blocks[l];
         float *blk = ws + lay.block0 + l * lay.block_stride;
-        rc = mlcgb_interaction_forward(ws + lay.x[cur], d, offsets, row1, sel, pair_of, rbf, conv_cutoff_kind, conv_lower, conv_upper, bw.lin1_w,
+        rc = interaction_forward_counted(ws + lay.x[cur], d, offsets, row1, sel, pair_of, pairs_dev, rbf, conv_cutoff_kind, conv_lower, conv_upper, bw.lin1_w,
                                        bw.filter_w1, bw.filter_b1, bw.filter_w2, bw.lin2_w, bw.lin2_b, bw.lin_w, bw.lin_b, N, E, P, H, F, H2,
                                        precision, blk + lay.xl_off, blk + lay.wp_off, ws + lay.agg, blk + lay.a_off, ws + lay.x[cur ^ 1], status,
                                        stream);
@@ -191,8 +244,8 @@ int mlcgb_schnet_eval(const void *pos, const int64_t *types, const int64_t *stru
         const mlcgb_schnet_block &bw = w->blocks[l];
         float *blk = ws + lay.block0 + l * lay.block_stride;
         float *gd_l = (l == L - 1) ? ws + lay.gd : ws + lay.gdt;
-        rc = mlcgb_interaction_backward(ws + lay.g[gcur], blk + lay.a_off, blk + lay.wp_off, blk + lay.xl_off, d, offsets, row1, sel, pair_of, twin,
-                                        row0, row1, rbf, conv_cutoff_kind, conv_lower, conv_upper, bw.lin1_w, bw.filter_w1, bw.filter_b1,
+        rc = interaction_backward_counted(ws + lay.g[gcur], blk + lay.a_off, blk + lay.wp_off, blk + lay.xl_off, d, offsets, row1, sel, pair_of, twin,
+                                        pairs_dev, row0, row1, rbf, conv_cutoff_kind, conv_lower, conv_upper, bw.lin1_w, bw.filter_w1, bw.filter_b1,
                                         bw.filter_w2, bw.lin2_w, bw.lin_w, N, E, P, H, F, H2, precision, ws + lay.gy, ws + lay.agg, ws + lay.gxl,
                                         l > 0 ? ws + lay.g[gcur ^ 1] : nullptr, E > 0 ? gd_l : nullptr, status, stream);
         if (rc) return rc;

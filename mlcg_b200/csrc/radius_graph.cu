@@ -185,8 +185,10 @@ struct FillOut {
 
 template <typename T>
 __device__ __forceinline__ void emit_edge(const FillOut &o, int64_t slot, int64_t i, int64_t j, int64_t b, T d2) {
-    o.row0[slot] = i;
-    o.row1[slot] = j;
+    if (o.row0) {
+        o.row0[slot] = i;
+        o.row1[slot] = j;
+    }
     if (o.mapping_batch) o.mapping_batch[slot] = b;
     if (o.distance) ((T *)o.distance)[slot] = sqrt(d2);
     if (o.row0_32) o.row0_32[slot] = (int32_t)i;
@@ -454,7 +456,11 @@ __global__ void batch_to_ptr_kernel(const int64_t *__restrict__ batch, int64_t N
 __global__ void edge_twin_kernel(const int32_t *__restrict__ row0, const int32_t *__restrict__ row1,
                                  const int64_t *__restrict__ offsets, int64_t E, int64_t N, int32_t *__restrict__ twin,
                                  int32_t *__restrict__ status) {
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x) {
+    // offsets[N] is the list's edge count; E may be the (larger) capacity of the buffers
+    const int64_t total = offsets[N];
+    const int64_t nE = total < E ? total : E;
+    if ((nE & 1) && blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, (int)kAsymmetric);
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < nE; e += (int64_t)gridDim.x * blockDim.x) {
         const int a = row0[e], b = row1[e];
         int32_t t = -1;
         if (a >= 0 && a < N && b >= 0 && b < N) {
@@ -505,7 +511,11 @@ __global__ void pair_plan_kernel(const int32_t *__restrict__ row0, const int32_t
                                  const int32_t *__restrict__ upper, const int64_t *__restrict__ uoff, int64_t E, int64_t N,
                                  int32_t *__restrict__ twin, int32_t *__restrict__ sel, int32_t *__restrict__ pair_of,
                                  int32_t *__restrict__ status) {
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x) {
+    // offsets[N] is the list's edge count; E may be the (larger) capacity of the buffers
+    const int64_t total = offsets[N];
+    const int64_t nE = total < E ? total : E;
+    if ((nE & 1) && blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, (int)kAsymmetric);
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < nE; e += (int64_t)gridDim.x * blockDim.x) {
         const int a = row0[e], b = row1[e];
         int32_t t = -1;
         if (a >= 0 && a < N && b >= 0 && b < N) {
@@ -518,15 +528,16 @@ __global__ void pair_plan_kernel(const int32_t *__restrict__ row0, const int32_t
         } else {
             atomicOr(status, (int)kBadIndex);
         }
-        twin[e] = t;
-        if (t < 0 || a == b) {
+        if (t < 0 || a == b) {               // not a valid plan: reported, and every index written stays inside its array
             atomicOr(status, (int)kAsymmetric);
+            twin[e] = (int32_t)e;
             pair_of[e] = 0;
             continue;
         }
+        twin[e] = t;
         if (b > a) {
             const int64_t p = uoff[a] + (e - (offsets[a + 1] - upper[a]));
-            if (p >= (E >> 1)) {               // more upper than lower edges: not symmetric
+            if (p >= (nE >> 1)) {              // more upper than lower edges: not symmetric
                 atomicOr(status, (int)kAsymmetric);
                 pair_of[e] = 0;
                 continue;
@@ -535,6 +546,23 @@ __global__ void pair_plan_kernel(const int32_t *__restrict__ row0, const int32_t
             pair_of[e] = (int32_t)p;
         } else {
             pair_of[e] = (int32_t)(uoff[b] + (t - (offsets[b + 1] - upper[b])));
+        }
+    }
+}
+
+// Capacity mode: the edge count stays on the device.  Offsets beyond the capacity of the edge buffers are clamped (the fill
+// then writes at most `capacity` edges and the overflow is reported in the status word); counts = {edges, edges / 2}.
+__global__ void clamp_offsets_kernel(int64_t *__restrict__ offsets, int64_t N, int64_t capacity, int64_t *__restrict__ counts,
+                                     int32_t *__restrict__ status) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i <= N; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t o = offsets[i];
+        if (o > capacity) {
+            offsets[i] = o = capacity;
+            if (i == N) atomicOr(status, (int)kCapacity);
+        }
+        if (i == N) {
+            counts[0] = o;
+            counts[1] = o >> 1;
         }
     }
 }
@@ -742,6 +770,24 @@ static int static_scratch_address(void **out) {
     return MLCGB_OK;
 }
 }  // namespace mlcgb
+
+extern "C" int mlcgb_radius_graph_capacity(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn,
+                                           int loop, int rule, void *workspace, size_t workspace_bytes, int32_t *deg, int64_t *offsets,
+                                           int64_t capacity, int64_t *edge_index, int32_t *row0_i32, int32_t *row1_i32,
+                                           int64_t *counts, int32_t *status, void *stream) {
+    if (capacity < 0 || !counts || (!edge_index && (!row0_i32 || !row1_i32))) return MLCGB_E_ARG;
+    if (N <= 0 || B <= 0) return MLCGB_E_ARG;
+    int rc = mlcgb_radius_count(pos, dtype, ptr, N, B, r, max_nn, loop, rule, workspace, workspace_bytes, deg, offsets, status, stream);
+    if (rc != MLCGB_OK) return rc;
+    auto st = (cudaStream_t)stream;
+    clamp_offsets_kernel<<<grid_for(N + 1, 256), 256, 0, st>>>(offsets, N, capacity, counts, status);
+    if (capacity == 0) return check_launch();
+    FillOut out{edge_index, edge_index ? edge_index + capacity : nullptr, nullptr, nullptr, row0_i32, row1_i32};
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        return radius_launch<scalar_t>(true, pos, ptr, N, B, r, 0, loop, 0, workspace, workspace_bytes, dtype, nullptr, offsets, out, status,
+                                       st);
+    });
+}
 
 extern "C" int mlcgb_radius_graph_static(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r,
                                          int64_t max_nn, int loop, int rule, int32_t *deg, int64_t *offsets, int64_t capacity,

@@ -327,6 +327,8 @@ class SchNet(torch.nn.Module):
             if not neighbor_list.get("_mlcgb_zero_shifts", False):
                 return None
             plan, ptr = plan_of(neighbor_list["index_mapping"], data.pos.shape[0]), neighbor_list.get("_mlcgb_ptr")
+        elif self.edge_capacity:
+            return self._fixed_capacity_evaluation(data, setup)
         else:       # the graph alone: no neighbour-list dictionary, mapping_batch or cell shifts are needed on this route
             plan, ptr, _ = edge_plan_for(data, self.rbf_layer.cutoff.cutoff_upper, self.max_num_neighbors)
         if plan.half_selection() is None:
@@ -336,6 +338,31 @@ class SchNet(torch.nn.Module):
         spec, conv_cut, weights, precision = setup
         return get_backend().schnet_eval(data.pos.detach().contiguous(), self._types(data), ptr, plan, spec, conv_cut, weights, precision,
                                          want_grad=True)
+
+    #: Fixed edge capacity (an even number of directed edges) for evaluations that must not read the edge count on the host,
+    #: e.g. a molecular-dynamics step recorded into a CUDA graph; None: buffers are sized by the count read in every call.
+    edge_capacity = None
+
+    def _fixed_capacity_evaluation(self, data, setup):
+        """Radius graph, pair plan and evaluation into buffers of ``edge_capacity`` edges: no device->host read anywhere.  More
+        edges than the capacity, or a list cut short by ``max_num_neighbors``, are reported by the backend's deferred status
+        check (``get_backend().check_pending()``)."""
+        from ..autograd import EdgePlan
+        from ..neighbor_list import structure_pointer, _as_3d
+        be = get_backend()
+        pos = data.pos.detach().contiguous()
+        N, cap = pos.shape[0], int(self.edge_capacity)
+        key = (N, cap, pos.device)
+        cached = self.__dict__.get("_mlcgb_rows")
+        if cached is None or cached[0] != key:       # stale entries of earlier graphs stay valid point indices for the same N
+            cached = self.__dict__["_mlcgb_rows"] = (key, torch.zeros((2, cap), dtype=torch.int32, device=pos.device))
+        ptr = structure_pointer(data)
+        res = be.radius_graph_capacity(_as_3d(pos), ptr, float(self.rbf_layer.cutoff.cutoff_upper), self.max_num_neighbors, cap, rows=cached[1])
+        twin, sel, pair_of, _ = be.pair_plan(res["row0"], res["row1"], res["offsets"], N)
+        plan = EdgePlan(N, cap, res["row0"], res["row1"], res["offsets"], None, res["row1"], res["offsets"], twin, res["row1"], True, False)
+        plan._half, plan._pair_of = sel, pair_of
+        spec, conv_cut, weights, precision = setup
+        return be.schnet_eval(pos, self._types(data), ptr, plan, spec, conv_cut, weights, precision, want_grad=True, counts=res["counts"])
 
     def _forward_whole_model(self, data, neighbor_list):
         setup = self._whole_model_setup(data.pos)
@@ -414,6 +441,15 @@ class StandardSchNet(SchNet):
         output_network = MLP([hidden_channels] + output_hidden_layer_widths + [1], activation_func=activation, last_bias=False)
         super().__init__(embedding_layer, blocks, rbf_layer, output_network, max_num_neighbors=max_num_neighbors,
                          nls_distance_method=nls_distance_method)
+
+
+def set_edge_capacity(model: torch.nn.Module, capacity) -> torch.nn.Module:
+    """Fixed edge capacity (directed edges, rounded up to an even number; None: off) for every SchNet of ``model``."""
+    capacity = None if capacity is None else (int(capacity) + 1) // 2 * 2
+    for m in model.modules():
+        if isinstance(m, SchNet):
+            m.edge_capacity = capacity
+    return model
 
 
 def set_filter_precision(model: torch.nn.Module, precision: str) -> torch.nn.Module:

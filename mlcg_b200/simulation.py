@@ -60,9 +60,61 @@ class LangevinSimulation:
         be.langevin_second_half(self.velocities, forces, self.masses, self.dt)
         return data, potential, forces
 
-    def simulate(self, n_timesteps: int):
+    def simulate(self, n_timesteps: int, save_interval: Optional[int] = None, cuda_graph: bool = False):
+        """``n_timesteps`` BAOAB steps.  ``save_interval``: positions after every that many steps are kept in a trajectory
+        buffer on the device (``self.trajectory`` ``[n_saves, N, 3]``, ``self.potentials`` ``[n_saves, B]``), where the
+        simulation is also checked for non-finite positions and for kernel status reports, as the reference does when it
+        saves (base.py:864-938) — once, at the end, without it.  ``cuda_graph``: record one step (noise, both halves of the
+        integrator, graph construction, every model and prior) into a CUDA graph and replay it; every SchNet of the model
+        needs a fixed edge capacity for that (:func:`mlcg_b200.nn.set_edge_capacity`), so that no step reads the edge count
+        on the host."""
         data = self.data
+        be = get_backend()
+        n_saves = n_timesteps // save_interval if save_interval else 0
+        if n_saves:
+            self.trajectory = torch.empty((n_saves,) + tuple(data.pos.shape), dtype=data.pos.dtype, device=data.pos.device)
+            self.potentials = None
         potential, forces = self.calculate_potential_and_forces(data)
-        for _ in range(n_timesteps):
-            data, potential, forces = self.timestep(data, forces)
+        step_graph, done = None, 0
+
+        def check():
+            be.check_pending()
+            if not bool(torch.isfinite(data.pos).all()):
+                raise RuntimeError(f"mlcg_b200: simulation blew up before step {done}: non-finite positions")
+
+        def save(k):
+            self.trajectory[k].copy_(data.pos)
+            if self.potentials is None:
+                self.potentials = torch.empty((n_saves,) + tuple(potential.shape), dtype=potential.dtype, device=potential.device)
+            self.potentials[k].copy_(potential)
+            check()
+
+        if cuda_graph and n_timesteps > 3:
+            # two plain steps first: every lazily created buffer and kernel attribute exists before the recording starts
+            forces = forces.clone()
+            for _ in range(2):
+                data, potential, f = self.timestep(data, forces)
+                forces.copy_(f)
+                done += 1
+                if save_interval and done % save_interval == 0:
+                    save(done // save_interval - 1)
+            check()
+            potential = potential.clone()
+            step_graph = torch.cuda.CUDAGraph()
+            if self.rng is not None:
+                step_graph.register_generator_state(self.rng)
+            with torch.cuda.graph(step_graph):
+                _, p, f = self.timestep(data, forces)
+                forces.copy_(f)
+                potential.copy_(p)
+            # (recording does not run the step; every step from here on is a replay)
+        while done < n_timesteps:
+            if step_graph is not None:
+                step_graph.replay()
+            else:
+                data, potential, forces = self.timestep(data, forces)
+            done += 1
+            if save_interval and done % save_interval == 0:
+                save(done // save_interval - 1)
+        check()
         return data, potential, forces

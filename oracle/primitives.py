@@ -58,6 +58,9 @@ class OracleBackend:
             status[0] = 4
         return twin, status
 
+    def check_pending(self):
+        pass            # the restatements report nothing lazily
+
     def pair_plan(self, row0, row1, offsets, N, fresh_status=False):
         twin, status = self.edge_twin(row0, row1, offsets, N)
         sel = torch.nonzero(row0 < row1).flatten().to(torch.int32)

@@ -321,3 +321,33 @@ def test_neighbour_list_is_rebuilt_for_every_evaluation():
             be.profiler = None
         assert torch.equal(second, fresh)
         assert float((first - fresh).abs().max()) > 1e-3
+
+
+def test_fixed_edge_capacity_evaluation():
+    """With a fixed edge capacity the evaluation reads nothing on the host (`mlcgb_radius_graph_capacity`, `mlcgb_pair_plan`,
+    `mlcgb_schnet_eval_counted`); energies and forces equal those of the route that reads the edge count, for capacities
+    from exactly the edge count upwards.  A capacity that is too small is reported by the deferred status check."""
+    from mlcg_b200.backend import get_backend
+    from mlcg_b200.neighbor_list import edge_plan_for
+    model, pos, types_, batch = _make("expnormal", 6, 100, 20, 15.0, 128, 128, 3, 5, min_dist=4.0)
+    model = bnn.GradientsOut(model.to(DEV), "forces").eval()
+    mk = lambda: mlcg_b200.AtomicData(pos=pos.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV), n_atoms=torch.full((6,), 100).to(DEV))
+    be = get_backend()
+    want = model(mk())
+    be.check_pending()
+    E = edge_plan_for(mk(), 15.0)[0].E
+    for cap in (E, E + 2, E + 1000, 2 * E):
+        bnn.set_edge_capacity(model, cap)
+        for _ in range(2):                      # second call: the index buffers hold the previous list
+            got = model(mk())
+        be.check_pending()
+        assert torch.equal(got.out["SchNet"]["energy"], want.out["SchNet"]["energy"])
+        assert torch.equal(got.out["SchNet"]["forces"], want.out["SchNet"]["forces"])
+    bnn.set_edge_capacity(model, E - 2)
+    model(mk())
+    with pytest.raises(RuntimeError, match="capacity"):
+        be.check_pending()
+    bnn.set_edge_capacity(model, None)
+    again = model(mk())
+    be.check_pending()
+    assert torch.equal(again.out["SchNet"]["forces"], want.out["SchNet"]["forces"])

@@ -77,3 +77,67 @@ def test_maxwell_boltzmann_moments():
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 def test_langevin_step_gpu(dtype):
     run_case("cuda:0", dtype)
+
+
+def _md_case(device, B=2, n=70, seed=5):
+    """SchNet + four priors on `B` chains of `n` beads, practically without friction (no noise enters: the integrator is
+    then deterministic, so two runs can be compared)."""
+    from mlcg_b200.data import collate
+    gen = torch.Generator().manual_seed(seed)
+    data, priors = prior_setup(n, B, 4, gen)
+    torch.manual_seed(seed)
+    cut = bnn.CosineCutoff(0.0, 12.0)
+    net = bnn.StandardSchNet(bnn.ExpNormalBasis(cut, 128, trainable=False), cut, [128], hidden_channels=128, embedding_size=4,
+                             num_filters=128, num_interactions=2)
+    models = {k: bnn.GradientsOut(p, "forces") for k, p in priors.items()}
+    models["SchNet"] = bnn.GradientsOut(net, "forces")
+    model = bnn.SumOut(torch.nn.ModuleDict(models)).eval().to(device)
+    data = data.to(device)
+    masses = torch.full((data.pos.shape[0],), 12.0 / 418.39, device=device)
+    sim = LangevinSimulation(model, dt=0.002, friction=1e-12, beta=1.0 / (0.0019872041 * 300))
+    sim.attach(data, masses, velocities=torch.zeros_like(data.pos))
+    return sim, model
+
+
+@pytest.mark.gpu
+def test_simulation_replayed_from_a_cuda_graph():
+    """One MD step recorded into a CUDA graph (fixed edge capacity: no host read in the step) and replayed gives the
+    trajectory of the step-by-step loop; the trajectory buffer holds the positions at the save points."""
+    from mlcg_b200.neighbor_list import edge_plan_for
+    steps, every = 24, 6
+    sim, model = _md_case("cuda:0")
+    assert sim.noisescale < 1e-6
+    x0 = sim.data.pos.clone()
+    sim.simulate(steps, save_interval=every)
+    traj_plain, pot_plain = sim.trajectory.clone(), sim.potentials.clone()
+    assert torch.equal(traj_plain[-1], sim.data.pos) and float((traj_plain[-1] - x0).abs().max()) > 1e-3
+
+    sim2, model2 = _md_case("cuda:0")
+    E = edge_plan_for(sim2.data, 12.0)[0].E
+    bnn.set_edge_capacity(model2, int(1.5 * E))
+    sim2.simulate(steps, save_interval=every, cuda_graph=True)
+    assert sim2.trajectory.shape == traj_plain.shape
+    assert float((sim2.trajectory - traj_plain).abs().max()) < 1e-3
+    assert torch.allclose(sim2.potentials, pot_plain, rtol=1e-4, atol=1e-2)
+    # an edge capacity that the graph outgrows is reported at the next save point
+    sim3, model3 = _md_case("cuda:0")
+    bnn.set_edge_capacity(model3, E - 2)
+    with pytest.raises(RuntimeError, match="capacity"):
+        sim3.simulate(steps, save_interval=every, cuda_graph=True)
+    backend.get_backend().check_pending()
+
+
+def test_simulation_trajectory_buffer_cpu_wiring():
+    from oracle.primitives import OracleBackend
+    old = backend.set_backend(OracleBackend())
+    try:
+        data, priors = prior_setup(14, 3, 4, torch.Generator().manual_seed(3))
+        model = bnn.SumOut(torch.nn.ModuleDict({k: bnn.GradientsOut(p, "forces") for k, p in priors.items()})).eval()
+        data.pos = data.pos.to(torch.float64)
+        sim = LangevinSimulation(model, dt=0.002, friction=1.0, beta=1.0 / (0.0019872041 * 300), rng=torch.Generator().manual_seed(1))
+        sim.attach(data, torch.ones(data.pos.shape[0], dtype=torch.float64))
+        sim.simulate(7, save_interval=3)
+        assert sim.trajectory.shape == (2, data.pos.shape[0], 3) and sim.potentials.shape == (2, 3)
+        assert bool(torch.isfinite(sim.trajectory).all()) and not torch.equal(sim.trajectory[0], sim.trajectory[1])
+    finally:
+        backend.set_backend(old)
