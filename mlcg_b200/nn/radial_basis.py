@@ -107,3 +107,67 @@ class ExpNormalBasis(_RadialBasis):
         dist = dist.unsqueeze(-1)
         inner = torch.exp(self.alpha * (-dist + self.cutoff.cutoff_lower)) - self.means
         return self.cutoff(dist) * torch.exp(-self.betas * inner ** 2)
+
+
+class SymmetricTensor(nn.Module):
+    """One learnable vector of length ``size`` per unordered pair of indices below ``N``, stored as the rows of the upper
+    triangle (regularized_basis.py:7-61); every entry starts at ``init_val``."""
+
+    def __init__(self, N: int, size: int, init_val: float = 1.0):
+        super().__init__()
+        self.N, self.size = N, size
+        self.w = nn.Parameter(torch.full((N * (N + 1) // 2, size), float(init_val)))
+        self.check_bounds = False
+
+    def enable_input_bound_check(self, enable: bool = True):
+        self.check_bounds = enable
+        return self
+
+    def forward(self, i: torch.Tensor, j: torch.Tensor) -> torch.Tensor:
+        if self.check_bounds and bool(((i >= self.N) | (j >= self.N) | (i < 0) | (j < 0)).any()):
+            raise IndexError(f"SymmetricTensor indices out of bounds [0, {self.N}): ")
+        lo, hi = torch.minimum(i, j), torch.maximum(i, j)
+        row = ((2 * self.N - lo + 1) * lo) // 2 + (hi - lo)      # rows of the upper triangle, row-major
+        return self.w[row]
+
+
+class RegularizedBasis(nn.Module):
+    """A radial basis whose functions are scaled, per pair of bead types, by learnable factors clamped to [0, 1]
+    (regularized_basis.py:63-235): ``forward(d, type_i, type_j)`` gives ``[n_basis_set, E, num_rbf]``, one scaled copy per
+    interaction block — all from one factor table, or one table per block with ``independent_regularizations``."""
+
+    def __init__(self, basis_function: _RadialBasis, types: int, n_basis_set: int, independent_regularizations: bool = False,
+                 init_val=1.0):
+        super().__init__()
+        self.basis_function = basis_function
+        self.types, self.n_basis_set = types, n_basis_set
+        self.independent_regularizations = independent_regularizations
+        self.num_rbf, self.cutoff = basis_function.num_rbf, basis_function.cutoff
+        if independent_regularizations:
+            vals = init_val if isinstance(init_val, list) else [init_val] * n_basis_set
+            self.regularization = nn.ModuleList([SymmetricTensor(types, self.num_rbf, vals[k]) for k in range(n_basis_set)])
+        else:
+            if isinstance(init_val, list):
+                if len(init_val) != 1:
+                    raise ValueError("When using shared regularization parameters, init_val should be a single float value.")
+                init_val = init_val[0]
+            self.regularization = SymmetricTensor(types, self.num_rbf, init_val)
+
+    def factors(self, type_i: torch.Tensor, type_j: torch.Tensor) -> torch.Tensor:
+        """[n_basis_set, E, num_rbf], clamped to [0, 1]."""
+        if self.independent_regularizations:
+            f = torch.stack([r(type_i, type_j) for r in self.regularization], dim=0)
+        else:
+            f = self.regularization(type_i, type_j).unsqueeze(0).expand(self.n_basis_set, -1, -1)
+        return torch.clamp(f, min=0.0, max=1.0)
+
+    def forward(self, distances: torch.Tensor, type_i: torch.Tensor, type_j: torch.Tensor) -> torch.Tensor:
+        return self.basis_function(distances).unsqueeze(0) * self.factors(type_i, type_j)
+
+    def get_regularization_parameters(self) -> torch.Tensor:
+        if self.independent_regularizations:
+            return torch.stack([r.w for r in self.regularization])
+        return self.regularization.w
+
+    def reset_parameters(self):
+        pass        # (the factors are set at construction, as in the reference)

@@ -443,6 +443,51 @@ class StandardSchNet(SchNet):
                          nls_distance_method=nls_distance_method)
 
 
+class RBFRegularizedSchNet(StandardSchNet):
+    """StandardSchNet whose radial basis is scaled per pair of bead types, with one set of factors for all interaction blocks or
+    one per block (schnet.py:676-803).  Also puts the factors into ``data.out["SchNet"]["radial_filters"]``.  The scaled basis is
+    an explicit ``[blocks, E, R]`` tensor here (the fused filter kernel evaluates the unscaled bases only), so this model runs on
+    the per-operator kernels."""
+
+    def __init__(self, rbf_layer: torch.nn.Module, cutoff: torch.nn.Module, output_hidden_layer_widths: List[int],
+                 hidden_channels: int = 128, embedding_size: int = 100, num_filters: int = 128, num_interactions: int = 3,
+                 activation: torch.nn.Module = torch.nn.Tanh(), max_num_neighbors: int = 1000, aggr: str = "add",
+                 nls_distance_method: str = "custom_kernel", independent_regularizations: bool = False):
+        from .radial_basis import RegularizedBasis
+        rbf_layer = RegularizedBasis(basis_function=rbf_layer, types=embedding_size, n_basis_set=num_interactions,
+                                     independent_regularizations=independent_regularizations)
+        super().__init__(rbf_layer=rbf_layer, cutoff=cutoff, output_hidden_layer_widths=output_hidden_layer_widths,
+                         hidden_channels=hidden_channels, embedding_size=embedding_size, num_filters=num_filters,
+                         num_interactions=num_interactions, activation=activation, max_num_neighbors=max_num_neighbors, aggr=aggr,
+                         nls_distance_method=nls_distance_method)
+
+    def energy_and_gradient(self, data):
+        return None         # no one-call route: the filters depend on the bead types of each pair
+
+    def forward(self, data):
+        neighbor_list = data.neighbor_list.get(self.name)
+        if not self.is_nl_compatible(neighbor_list):
+            neighbor_list = self.neighbor_list(data, self.rbf_layer.cutoff.cutoff_upper, self.max_num_neighbors)[self.name]
+        x = self.embedding_layer(data.atom_types)
+        edge_index = neighbor_list["index_mapping"]
+        if not neighbor_list.get("_mlcgb_zero_shifts", False):
+            cell_shifts = neighbor_list["cell_shifts"]
+            if cell_shifts is not None and cell_shifts.numel() > 0 and bool(torch.any(cell_shifts != 0)):
+                raise NotImplementedError("periodic cell shifts are outside the scope of mlcg_b200")
+        plan = plan_of(edge_index, data.pos.shape[0])
+        distances = edge_distances(data.pos, plan) if self.training else EdgeDistanceOnce.apply(data.pos, plan)
+        rbf_expansion = self.rbf_layer(distances, data.atom_types[edge_index[0]], data.atom_types[edge_index[1]])
+        for block_id, block in enumerate(self.interaction_blocks):
+            x = x + block(x, edge_index, distances, rbf_expansion[block_id], None, data.batch)
+        energy = self.output_network(x, data)
+        ptr = neighbor_list.get("_mlcgb_ptr")
+        if ptr is None or ptr.device != x.device:
+            ptr = self._structure_ptr(data)
+        energy = SegmentSum.apply(energy, ptr, data.batch).flatten()
+        data.out[self.name] = {ENERGY_KEY: energy, "radial_filters": self.rbf_layer.get_regularization_parameters()}
+        return data
+
+
 def set_edge_capacity(model: torch.nn.Module, capacity) -> torch.nn.Module:
     """Fixed edge capacity (directed edges, rounded up to an even number; None: off) for every SchNet of ``model``."""
     capacity = None if capacity is None else (int(capacity) + 1) // 2 * 2

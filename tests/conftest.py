@@ -17,3 +17,10 @@ def golden():
     import torch
 
     return torch.load(os.path.join(ROOT, "tests", "golden", "reference_vectors.pt"), weights_only=False)
+
+
+@pytest.fixture(scope="session")
+def golden_regularized():
+    import torch
+
+    return torch.load(os.path.join(ROOT, "tests", "golden", "reference_vectors_regularized.pt"), weights_only=False)

@@ -207,7 +207,54 @@ def main(ref_src):
     print("wrote", os.path.join(HERE, "reference_vectors.pt"), os.path.getsize(os.path.join(HERE, "reference_vectors.pt")), "bytes")
 
 
+def main_regularized(ref_src):
+    """`RBFRegularizedSchNet` (src/mlcg/nn/schnet.py:676-803) with shared and with per-block factors, random factors in
+    [-0.2, 1.2] so that both clamps act; written to a file of its own."""
+    install_shims(ref_src)
+    schnet = importlib.import_module("mlcg.nn.schnet")
+    from mlcg.nn.radial_basis import ExpNormalBasis
+    from mlcg.nn.cutoff import CosineCutoff
+    from mlcg.nn.gradients import GradientsOut
+    from mlcg.data.atomic_data import AtomicData
+    sys.modules["mlcg.data"].AtomicData = AtomicData
+    gen = torch.Generator().manual_seed(4321)
+    out = {}
+    for name, independent in (("shared", False), ("independent", True)):
+        torch.manual_seed(9)
+        B, n, T, upper, R, H, L = 2, 20, 4, 12.0, 16, 32, 2
+        cut = CosineCutoff(0.0, upper)
+        model = schnet.RBFRegularizedSchNet(ExpNormalBasis(cut, R, trainable=False), cut, [H], hidden_channels=H, embedding_size=T,
+                                            num_filters=H, num_interactions=L, independent_regularizations=independent)
+        with torch.no_grad():
+            for k, p in model.named_parameters():
+                if k.endswith("bias"):
+                    p.copy_(0.1 * torch.randn(p.shape, generator=gen))
+                if k.endswith(".w"):
+                    p.copy_(-0.2 + 1.4 * torch.rand(p.shape, generator=gen))
+        pos = torch.cat([chain(n, jitter=0.3, gen=gen) for _ in range(B)])
+        types_ = torch.randint(0, T, (B * n,), generator=gen)
+        batch = torch.arange(B).repeat_interleave(n)
+        mk = lambda: AtomicData(pos=pos.clone(), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list={})
+        res = GradientsOut(model, "forces").eval()(mk())
+        case = dict(independent=independent, upper=upper, R=R, H=H, L=L, T=T, B=B, n=n, pos=pos, atom_types=types_, batch=batch,
+                    state_dict={k: v.detach().clone() for k, v in model.state_dict().items()},
+                    energy=res.out["SchNet"]["energy"].detach(), forces=res.out["SchNet"]["forces"].detach(),
+                    radial_filters=res.out["SchNet"]["radial_filters"].detach().clone())
+        target = torch.randn(pos.shape, generator=gen)
+        tr = GradientsOut(model, "forces").train()
+        model.zero_grad()
+        loss = torch.nn.functional.mse_loss(tr(mk()).out["SchNet"]["forces"], target)
+        loss.backward()
+        case["target_forces"], case["loss"] = target, loss.detach()
+        case["param_grads"] = {k: p.grad.detach().clone() for k, p in model.named_parameters() if p.grad is not None}
+        out[name] = case
+        print(name, "E", case["energy"].tolist(), "loss", float(loss))
+    path = os.path.join(HERE, "reference_vectors_regularized.pt")
+    torch.save(out, path)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg>")
-    main(sys.argv[1])
+    if len(sys.argv) not in (2, 3) or (len(sys.argv) == 3 and sys.argv[2] != "regularized"):
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg> [regularized]")
+    (main_regularized if len(sys.argv) == 3 else main)(sys.argv[1])

@@ -21,6 +21,16 @@ def schnet_from_case(case, dtype=None, device="cpu", trainable=None):
     return model.to(device=device, dtype=dtype)
 
 
+def regularized_schnet_from_case(case, device="cpu"):
+    """mlcg_b200 RBFRegularizedSchNet with the architecture and weights of a golden case."""
+    cut = bnn.CosineCutoff(0.0, case["upper"])
+    model = bnn.RBFRegularizedSchNet(bnn.ExpNormalBasis(cut, case["R"], trainable=False), cut, [case["H"]], hidden_channels=case["H"],
+                                     embedding_size=case["T"], num_filters=case["H"], num_interactions=case["L"],
+                                     independent_regularizations=case["independent"])
+    model.load_state_dict(case["state_dict"])
+    return model.to(device)
+
+
 def data_from_case(case, device="cpu", dtype=None):
     dtype = case["pos"].dtype if dtype is None else dtype
     return mlcg_b200.AtomicData(pos=case["pos"].clone().to(device=device, dtype=dtype), atom_types=case["atom_types"].to(device),

@@ -10,7 +10,7 @@ from mlcg_b200 import autograd as ag
 from mlcg_b200 import backend, nn as bnn
 from oracle.primitives import OracleBackend
 
-from helpers import data_from_case, prior_setup, schnet_from_case
+from helpers import data_from_case, prior_setup, regularized_schnet_from_case, schnet_from_case
 
 
 @pytest.fixture(autouse=True)
@@ -47,6 +47,27 @@ def test_force_matching_step_vs_reference(golden, name):
     for k, g in c["param_grads"].items():
         assert grads[k].grad is not None, k
         assert torch.allclose(grads[k].grad, g, rtol=10 * tol, atol=tol * float(g.abs().max() + 1e-30)), k
+
+
+@pytest.mark.parametrize("name", ["shared", "independent"])
+def test_rbf_regularized_schnet_vs_reference(golden_regularized, name):
+    """`RBFRegularizedSchNet` (src/mlcg/nn/schnet.py:676-803): state_dict keys, energies, forces, the `radial_filters` output
+    and the gradients of a force-matching loss, factors outside [0, 1] included (both clamps act)."""
+    c = golden_regularized[name]
+    net = regularized_schnet_from_case(c)
+    assert set(net.state_dict().keys()) == set(c["state_dict"].keys())
+    out = bnn.GradientsOut(net, "forces").eval()(data_from_case(c))
+    assert torch.allclose(out.out["SchNet"]["energy"], c["energy"], rtol=2e-6, atol=2e-6)
+    assert torch.allclose(out.out["SchNet"]["forces"], c["forces"], rtol=2e-6, atol=2e-5)
+    assert torch.equal(out.out["SchNet"]["radial_filters"], c["radial_filters"])
+    out = bnn.GradientsOut(net, "forces").train()(data_from_case(c))
+    loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], c["target_forces"])
+    loss.backward()
+    assert torch.allclose(loss.detach(), c["loss"], rtol=1e-5)
+    grads = dict(net.named_parameters())
+    for k, g in c["param_grads"].items():
+        assert grads[k].grad is not None, k
+        assert torch.allclose(grads[k].grad, g, rtol=1e-4, atol=1e-5 * float(g.abs().max() + 1e-30)), k
 
 
 def test_state_dict_keys_match_reference(golden):
