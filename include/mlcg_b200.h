@@ -326,6 +326,25 @@ int mlcgb_segment_sum(const void *x /* [N] */, int dtype, const int64_t *ptr /* 
                       void *stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Radius graph of periodic structures, torch_neighbor_list_pbc + compute_images,
+ * src/mlcg/neighbor_list/torch_impl.py:102-163, 252-329: neighbours are (point j, periodic shift); per centre they are listed
+ * in the reference's order (shift triples (s1,s2,s3) in [-n_k, n_k] with s3 running fastest, points in order), cut after
+ * max_nn, the pair (j = i, zero shift) dropped afterwards unless `loop`.  cells is [B,3,3] (rows = cell vectors), repeats
+ * [B,3] int32 = n_k (zero along non-periodic directions).  Outputs: edge_index [2,E] (row 0 = centre), cell_shifts [E,3]
+ * (the shift in length units, as compute_distances adds it to pos[j]), optional distance [E] and mapping_batch [E].
+ * Two calls around one host read of offsets[N], like mlcgb_radius_count / mlcgb_radius_fill; the fill call takes the
+ * workspace as the count call left it.  Status bit 0: a centre reached max_nn.
+ * ---------------------------------------------------------------------------------------------- */
+size_t mlcgb_radius_pbc_workspace_bytes(int64_t N);
+int mlcgb_radius_pbc_count(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, const void *cells, const int32_t *repeats,
+                           double r, int64_t max_nn, int loop, void *workspace, size_t workspace_bytes, int32_t *deg, int64_t *offsets,
+                           int32_t *status, void *stream);
+int mlcgb_radius_pbc_fill(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, const void *cells, const int32_t *repeats,
+                          double r, int64_t max_nn, int loop, const void *workspace, size_t workspace_bytes, const int64_t *offsets,
+                          int64_t E, int64_t *edge_index, void *cell_shifts, void *distance /* or NULL */,
+                          int64_t *mapping_batch /* or NULL */, int32_t *status, void *stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Capacity mode: the whole evaluation without a host read of the edge count, so that a molecular-dynamics step can be
  * recorded into a CUDA graph (the reference reads the count on the host in every step, radius.cu:288).
  *

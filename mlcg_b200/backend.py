@@ -259,6 +259,36 @@ class CudaBackend:
                           **self._work("radius_fill", locals()))
         return dict(edge_index=ei, distance=dist, mapping_batch=mb, row0=r0, row1=r1, offsets=offsets, status=st)
 
+    def radius_graph_pbc(self, pos, ptr, cells, repeats, r, max_num_neighbors, loop, want_distance=False, want_batch=True):
+        """Radius graph of periodic structures: dict(edge_index [2,E] i64 (row 0 = centre), cell_shifts [E,3], distance|None,
+        mapping_batch|None, status int).  ``cells`` [B,3,3] in the dtype of ``pos``, ``repeats`` [B,3] copies per cell vector."""
+        _need_cuda(pos, ptr, cells, repeats)
+        pos = pos.detach().contiguous()
+        cells = cells.detach().to(pos.dtype).contiguous()
+        repeats = repeats.to(torch.int32).contiguous()
+        N, B, dev = pos.shape[0], ptr.numel() - 1, pos.device
+        if cells.numel() != 9 * B or repeats.numel() != 3 * B:
+            raise ValueError("cells must be [B,3,3] and repeats [B,3]")
+        dt = _dt(pos)
+        with _on(dev):
+            wsb = self.lib.mlcgb_radius_pbc_workspace_bytes(N)
+            ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
+            deg = torch.empty(max(N, 1), dtype=torch.int32, device=dev)
+            offsets = torch.empty(N + 1, dtype=torch.int64, device=dev)
+            status = torch.zeros(4, dtype=torch.int32, device=dev)
+            self._run("radius_pbc_count", self.lib.mlcgb_radius_pbc_count,
+                      (_ptr(pos), dt, _ptr(ptr), N, B, _ptr(cells), _ptr(repeats), float(r), int(max_num_neighbors), int(loop), _ptr(ws), wsb,
+                       _ptr(deg), _ptr(offsets), _ptr(status), _stream()), launches=5)
+            E, st = (int(v) for v in torch.stack([offsets[N], status[0].to(torch.int64)]).cpu().tolist())
+            ei = torch.empty((2, E), dtype=torch.int64, device=dev)
+            shifts = torch.empty((E, 3), dtype=pos.dtype, device=dev)
+            dist = torch.empty(E, dtype=pos.dtype, device=dev) if want_distance else None
+            mb = torch.empty(E, dtype=torch.int64, device=dev) if want_batch else None
+            self._run("radius_pbc_fill", self.lib.mlcgb_radius_pbc_fill,
+                      (_ptr(pos), dt, _ptr(ptr), N, B, _ptr(cells), _ptr(repeats), float(r), int(max_num_neighbors), int(loop), _ptr(ws), wsb,
+                       _ptr(offsets), E, _ptr(ei), _ptr(shifts), _ptr(dist), _ptr(mb), _ptr(status), _stream()), nbytes=E * (16 + 3 * pos.element_size()))
+        return dict(edge_index=ei, cell_shifts=shifts, distance=dist, mapping_batch=mb, offsets=offsets, status=st)
+
     def radius_graph_capacity(self, pos, ptr, r, max_num_neighbors, capacity, rows=None, rule=1):
         """The radius graph into buffers of ``capacity`` edges without reading the edge count on the host:
         dict(row0, row1 (int32 [capacity]), offsets [N+1], counts (int64 [2] on the device: edges, edges / 2)).  ``rows``: an int32

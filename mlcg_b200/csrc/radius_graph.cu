@@ -567,6 +567,108 @@ __global__ void clamp_offsets_kernel(int64_t *__restrict__ offsets, int64_t N, i
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Periodic structures (src/mlcg/neighbor_list/torch_impl.py:102-163, 252-329): the reference copies every structure
+// (2 n_k + 1) times along each periodic cell vector, n_k = ceil(rcut * |row k of the transposed inverse cell|), and runs a
+// bipartite radius search of the original points against all copies; a neighbour is (point j, shift s), listed per centre
+// in the order of the copies (shift triples with the last index running fastest, points in order inside a copy), cut after
+// max_num_neighbors, and the pair (j = i, s = 0) is dropped afterwards unless self pairs are asked for.
+// Here the copies are never built: one warp per centre walks the shift triples and tests the structure's points, 32 at a
+// time, against the centre; the copy's coordinates are pos[j] + shift, rounded once, as the reference stores them.
+// shift = (s1 * c1 + s2 * c2) + s3 * c3 per component with separately rounded products and sums — exact for a cell with
+// one non-zero entry per column (orthorhombic boxes); for a general cell a matrix-product routine may round differently.
+// ------------------------------------------------------------------------------------------------
+struct PbcOut {
+    int64_t *row0, *row1, *mapping_batch;
+    void *shifts, *distance;      // [E,3], [E]
+};
+
+template <typename T>
+__device__ __forceinline__ void shift_vector(const T *__restrict__ cell, int s1, int s2, int s3, T &sx, T &sy, T &sz) {
+    const T a = (T)s1, b = (T)s2, c = (T)s3;
+    sx = add_rn(add_rn(mul_rn(a, cell[0]), mul_rn(b, cell[3])), mul_rn(c, cell[6]));
+    sy = add_rn(add_rn(mul_rn(a, cell[1]), mul_rn(b, cell[4])), mul_rn(c, cell[7]));
+    sz = add_rn(add_rn(mul_rn(a, cell[2]), mul_rn(b, cell[5])), mul_rn(c, cell[8]));
+}
+
+template <typename T, bool FILL>
+__global__ void __launch_bounds__(256)
+radius_pbc_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, const int32_t *__restrict__ struct_of, int64_t N,
+                  const T *__restrict__ cells /* [B,3,3] */, const int32_t *__restrict__ repeats /* [B,3] */, T r2, int64_t max_nn,
+                  int loop, int32_t *__restrict__ deg, const int64_t *__restrict__ offsets, PbcOut out, int32_t *__restrict__ status) {
+    const int lane = threadIdx.x & 31;
+    const unsigned lt = lanemask_lt();
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t i = warp; i < N; i += nwarps) {
+        const int64_t b = struct_of[i];
+        const int64_t lo = ptr[b];
+        const int n = (int)(ptr[b + 1] - lo);
+        const T *cell = cells + b * 9;
+        const int n1 = repeats[b * 3], n2 = repeats[b * 3 + 1], n3 = repeats[b * 3 + 2];
+        const T xi = pos[i * 3], yi = pos[i * 3 + 1], zi = pos[i * 3 + 2];
+        int64_t kept = max_nn, base = 0;
+        if (FILL) {
+            base = offsets[i];
+            if (offsets[i + 1] == base) continue;
+        }
+        int64_t hits = 0, emitted = 0;       // hits so far in list order (self included); edges written
+        bool self_kept = false;
+        for (int s1 = -n1; s1 <= n1 && hits < kept; s1++)
+            for (int s2 = -n2; s2 <= n2 && hits < kept; s2++)
+                for (int s3 = -n3; s3 <= n3 && hits < kept; s3++) {
+                    T sx, sy, sz;
+                    shift_vector<T>(cell, s1, s2, s3, sx, sy, sz);
+                    const bool central = s1 == 0 && s2 == 0 && s3 == 0;
+                    for (int jb = 0; jb < n && hits < kept; jb += 32) {
+                        const int j = jb + lane;
+                        bool hit = false;
+                        T d2 = T(0);
+                        if (j < n) {
+                            const int64_t gj = lo + j;
+                            d2 = dist2_rn(xi, yi, zi, add_rn(pos[gj * 3], sx), add_rn(pos[gj * 3 + 1], sy), add_rn(pos[gj * 3 + 2], sz));
+                            hit = d2 < r2;
+                        }
+                        const unsigned bal = __ballot_sync(0xffffffffu, hit);
+                        const int64_t rank = hits + __popc(bal & lt);
+                        const bool in_list = hit && rank < kept;
+                        const bool is_self = central && lo + j == i;
+                        if (FILL) {
+                            const bool write = in_list && (loop || !is_self);
+                            const unsigned wbal = __ballot_sync(0xffffffffu, write);
+                            if (write) {
+                                const int64_t slot = base + emitted + __popc(wbal & lt);
+                                out.row0[slot] = i;
+                                out.row1[slot] = lo + j;
+                                if (out.mapping_batch) out.mapping_batch[slot] = b;
+                                T *sh = (T *)out.shifts + slot * 3;
+                                sh[0] = sx; sh[1] = sy; sh[2] = sz;
+                                if (out.distance) ((T *)out.distance)[slot] = sqrt(d2);
+                            }
+                            emitted += __popc(wbal);
+                        } else {
+                            self_kept = self_kept || __any_sync(0xffffffffu, in_list && is_self);
+                        }
+                        hits += __popc(bal);
+                    }
+                }
+        if (!FILL && lane == 0) {
+            const int64_t k = hits < kept ? hits : kept;
+            deg[i] = (int32_t)(k - ((self_kept && !loop) ? 1 : 0));
+            if (hits >= kept && kept > 0) {
+                // the walk stopped at the cap: whether more would have followed is not known without finishing it; the cap
+                // was reached, which is what callers need to know
+                atomicOr(status, (int)kTruncated);
+            }
+        }
+    }
+}
+
+__global__ void struct_of_kernel(const int64_t *__restrict__ ptr, int64_t B, int32_t *__restrict__ struct_of) {
+    for (int64_t b = blockIdx.x; b < B; b += gridDim.x)
+        for (int64_t i = ptr[b] + threadIdx.x; i < ptr[b + 1]; i += blockDim.x) struct_of[i] = (int32_t)b;
+}
+
 template <typename T>
 static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn,
                          int loop, int rule, void *ws, size_t ws_bytes, int dtype, int32_t *deg, int64_t *offsets,
@@ -722,6 +824,59 @@ int mlcgb_pair_plan(const int32_t *row0, const int32_t *row1, const int64_t *off
     scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(upper, N, bsum, uoff);
     pair_plan_kernel<<<grid_for(E, 256), 256, 0, st>>>(row0, row1, offsets, upper, uoff, E, N, twin, sel, pair_of, status);
     return check_launch();
+}
+
+size_t mlcgb_radius_pbc_workspace_bytes(int64_t N) {
+    if (N < 0) return 0;
+    return align256((size_t)N * 4) + align256((size_t)((N + kScanBlock - 1) / kScanBlock + 1) * 8);
+}
+
+int mlcgb_radius_pbc_count(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, const void *cells, const int32_t *repeats,
+                           double r, int64_t max_nn, int loop, void *workspace, size_t workspace_bytes, int32_t *deg, int64_t *offsets,
+                           int32_t *status, void *stream) {
+    if (N < 0 || B < 0 || max_nn < 0 || !offsets || !status || !ptr || !workspace) return MLCGB_E_ARG;
+    if (N >= (int64_t)1 << 31) return MLCGB_E_LIMIT;
+    auto st = (cudaStream_t)stream;
+    if (N == 0) {
+        cudaMemsetAsync(offsets, 0, sizeof(int64_t), st);
+        return check_launch();
+    }
+    if (!pos || !deg || !cells || !repeats || B == 0) return MLCGB_E_ARG;
+    if (workspace_bytes < mlcgb_radius_pbc_workspace_bytes(N)) return MLCGB_E_WORKSPACE;
+    auto *struct_of = (int32_t *)workspace;
+    auto *bsum = (int64_t *)((char *)workspace + align256((size_t)N * 4));
+    struct_of_kernel<<<grid_for(B, 1, 8), 256, 0, st>>>(ptr, B, struct_of);
+    int rc = MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        const scalar_t r2 = (scalar_t)(r * r);
+        radius_pbc_kernel<scalar_t, false><<<grid_for(N * 32, 256), 256, 0, st>>>((const scalar_t *)pos, ptr, struct_of, N, (const scalar_t *)cells,
+                                                                                  repeats, r2, max_nn, loop, deg, nullptr, PbcOut{}, status);
+        return MLCGB_OK;
+    });
+    if (rc) return rc;
+    const int64_t nb = (N + kScanBlock - 1) / kScanBlock;
+    scan_block_sums_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum);
+    scan_of_sums_kernel<<<1, kScanBlock, 0, st>>>(bsum, nb, offsets + N);
+    scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum, offsets);
+    return check_launch();
+}
+
+int mlcgb_radius_pbc_fill(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, const void *cells, const int32_t *repeats,
+                          double r, int64_t max_nn, int loop, const void *workspace, size_t workspace_bytes, const int64_t *offsets,
+                          int64_t E, int64_t *edge_index, void *cell_shifts, void *distance, int64_t *mapping_batch, int32_t *status,
+                          void *stream) {
+    if (N < 0 || B < 0 || E < 0 || max_nn < 0 || !offsets || !status || !ptr || !workspace) return MLCGB_E_ARG;
+    if (E == 0 || N == 0) return MLCGB_OK;
+    if (!pos || !cells || !repeats || !edge_index || !cell_shifts) return MLCGB_E_ARG;
+    if (workspace_bytes < mlcgb_radius_pbc_workspace_bytes(N)) return MLCGB_E_WORKSPACE;
+    auto st = (cudaStream_t)stream;
+    const auto *struct_of = (const int32_t *)workspace;      // as the count call left it
+    PbcOut out{edge_index, edge_index + E, mapping_batch, cell_shifts, distance};
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        const scalar_t r2 = (scalar_t)(r * r);
+        radius_pbc_kernel<scalar_t, true><<<grid_for(N * 32, 256), 256, 0, st>>>((const scalar_t *)pos, ptr, struct_of, N, (const scalar_t *)cells,
+                                                                                 repeats, r2, max_nn, loop, nullptr, offsets, out, status);
+        return check_launch();
+    });
 }
 
 int mlcgb_pair_index(const int32_t *sel, const int32_t *twin, int64_t P, int32_t *pair_of, void *stream) {

@@ -3,7 +3,8 @@
 Mirrors ``src/mlcg/neighbor_list/neighbor_list.py`` (``atomic_data2neighbor_list`` :27-102,
 ``make_neighbor_list`` :105-163, ``validate_neighborlist`` :170-202), the ``radius_graph`` call made at
 ``src/mlcg/neighbor_list/torch_impl.py:216-224`` and the native op ``radius_distance``
-(``src/opt_radius/mlcg_opt_radius/radius.py:187-199``).  Non-periodic structures only.
+(``src/opt_radius/mlcg_opt_radius/radius.py:187-199``), and ``torch_neighbor_list_pbc`` for periodic structures
+(``src/mlcg/neighbor_list/torch_impl.py:102-163, 252-329``).
 """
 from typing import Dict, Mapping, Optional, Tuple
 
@@ -154,6 +155,35 @@ def structure_pointer(data) -> torch.Tensor:
     return _structure_ptr(pos, batch, None)
 
 
+def _is_periodic(data) -> bool:
+    pbc = getattr(data, "pbc", None)
+    return pbc is not None and bool(torch.any(pbc))
+
+
+def pbc_repeats(cell: torch.Tensor, pbc: torch.Tensor, rcut: float) -> torch.Tensor:
+    """Copies of a structure along each cell vector that a search within ``rcut`` needs, as compute_images works them out
+    (torch_impl.py:113-120); zero along non-periodic directions.  ``[B,3]`` int64."""
+    cell, pbc = cell.view((-1, 3, 3)), pbc.view((-1, 3))
+    inv_distances = torch.linalg.inv(cell).transpose(2, 1).norm(2, dim=-1)
+    num_repeats = torch.ceil(rcut * inv_distances).to(torch.long)
+    return torch.where(pbc, num_repeats, torch.zeros_like(num_repeats))
+
+
+def periodic_neighbor_list(data, rcut: float, self_interaction: bool = False, max_num_neighbors: int = 1000) -> Dict:
+    """The neighbour-list dictionary of periodic structures (minimum images and beyond: every copy inside ``rcut``)."""
+    if getattr(data, "cell", None) is None:
+        raise ValueError("Periodic systems need to have a unit cell defined")
+    pos = data.pos
+    ptr = structure_pointer(data)
+    cell = data.cell.to(pos.dtype).view((-1, 3, 3))
+    res = get_backend().radius_graph_pbc(_as_3d(pos), ptr, cell, pbc_repeats(cell, data.pbc.to(pos.device), rcut), rcut, max_num_neighbors,
+                                         self_interaction)
+    mapping = res["edge_index"]
+    return make_neighbor_list(tag=f"nonbounded rc:{rcut} order:{mapping.shape[0]}", order=mapping.shape[0], index_mapping=mapping,
+                              mapping_batch=res["mapping_batch"], cell_shifts=res["cell_shifts"], rcut=rcut,
+                              self_interaction=self_interaction)
+
+
 def edge_plan_for(data, rcut: float, max_num_neighbors: int = 1000):
     """Radius graph of non-periodic data as (edge plan, structure pointer), without the neighbour-list dictionary around it
     (no ``mapping_batch``, no ``cell_shifts``): what the one-call evaluation needs and nothing else."""
@@ -175,9 +205,8 @@ def atomic_data2neighbor_list(data, rcut: float, self_interaction: bool = False,
     rcut = float(rcut)
     if nls_distance_method not in ("torch", "custom_kernel", "nvalchemi_naive", "nvalchemi_cell", "nvalchemi_raw"):
         raise ValueError(f"Method {nls_distance_method} not supported for nls-distance computation ")
-    pbc = getattr(data, "pbc", None)
-    if pbc is not None and bool(torch.any(pbc)):
-        raise NotImplementedError("periodic structures are outside the scope of mlcg_b200's radius graph")
+    if _is_periodic(data):
+        return periodic_neighbor_list(data, rcut, self_interaction, max_num_neighbors)
     pos = data.pos
     batch = getattr(data, "batch", None)
     if batch is None:

@@ -9,7 +9,7 @@ from typing import Final, List
 import torch
 
 from .. import _lib
-from ..autograd import (EdgeDistanceOnce, FusedFilterConv, FusedInteraction, RowScale, SchNetEval, SegIn, SegmentSum, edge_distances,
+from ..autograd import (EdgeDiff, EdgeDistanceOnce, FusedFilterConv, FusedInteraction, RowScale, SchNetEval, SegIn, SegmentSum, edge_distances,
                         plan_of)
 from ..backend import get_backend
 from ..data import ENERGY_KEY
@@ -285,11 +285,13 @@ class SchNet(torch.nn.Module):
         x = self.embedding_layer(data.atom_types)
         edge_index = neighbor_list["index_mapping"]
         cell_shifts = neighbor_list["cell_shifts"]
-        if (not neighbor_list.get("_mlcgb_zero_shifts", False) and cell_shifts is not None and cell_shifts.numel() > 0
-                and bool(torch.any(cell_shifts != 0))):   # (a host read; lists built by this package are known to be shift-free)
-            raise NotImplementedError("periodic cell shifts are outside the scope of mlcg_b200")
+        # (a host read; lists built by this package for non-periodic data are known to be shift-free)
+        shifted = (not neighbor_list.get("_mlcgb_zero_shifts", False) and cell_shifts is not None and cell_shifts.numel() > 0
+                   and bool(torch.any(cell_shifts != 0)))
         plan = plan_of(edge_index, data.pos.shape[0])
-        if self.training:
+        if shifted:             # periodic copies: |pos[j] + shift - pos[i]| (internal_coordinates.py:72-100)
+            distances = (EdgeDiff.apply(data.pos, plan) + cell_shifts.view(-1, 3).to(data.pos.dtype)).norm(p=2, dim=1)
+        elif self.training:
             distances = edge_distances(data.pos, plan)          # differentiable to any order
         else:
             distances = EdgeDistanceOnce.apply(data.pos, plan)  # one kernel forward, one backward
@@ -329,6 +331,8 @@ class SchNet(torch.nn.Module):
             plan, ptr = plan_of(neighbor_list["index_mapping"], data.pos.shape[0]), neighbor_list.get("_mlcgb_ptr")
         elif self.edge_capacity:
             return self._fixed_capacity_evaluation(data, setup)
+        elif getattr(data, "pbc", None) is not None and bool(torch.any(data.pbc)):
+            return None         # periodic structures: distances carry cell shifts, which the one-call route does not take
         else:       # the graph alone: no neighbour-list dictionary, mapping_batch or cell shifts are needed on this route
             plan, ptr, _ = edge_plan_for(data, self.rbf_layer.cutoff.cutoff_upper, self.max_num_neighbors)
         if plan.half_selection() is None:

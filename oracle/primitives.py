@@ -46,6 +46,16 @@ class OracleBackend:
                     mapping_batch=seg if want_batch else None, row0=ei_t[0].to(torch.int32), row1=ei_t[1].to(torch.int32),
                     offsets=torch.from_numpy(offsets).to(dev), status=status)
 
+    def radius_graph_pbc(self, pos, ptr, cells, repeats, r, max_num_neighbors, loop, want_distance=False, want_batch=True):
+        p, pt = pos.detach().cpu().numpy(), ptr.cpu().numpy()
+        # `repeats` already holds the copies per direction: a direction is periodic exactly where it is non-zero or r allows none
+        ei, shifts = radius_ref.radius_graph_pbc_numpy(p, pt, cells.detach().cpu().numpy(), repeats.cpu().numpy() > 0, r, max_num_neighbors, loop)
+        dev = pos.device
+        ei_t, sh = torch.from_numpy(ei).to(dev), torch.from_numpy(shifts).to(dev)
+        dist = ((pos[ei_t[1]] + sh) - pos[ei_t[0]]).norm(dim=1).detach() if want_distance else None
+        seg = torch.from_numpy(np.searchsorted(pt, ei[0], side="right") - 1).to(dev)
+        return dict(edge_index=ei_t, cell_shifts=sh, distance=dist, mapping_batch=seg if want_batch else None, status=0)
+
     def edge_twin(self, row0, row1, offsets, N, fresh_status=False):
         E = row0.numel()
         key = row0.to(torch.int64) * N + row1.to(torch.int64)

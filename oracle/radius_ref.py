@@ -133,6 +133,57 @@ def radius_graph_numpy(pos, ptr, r, max_num_neighbors=1000, loop=False, rule="cl
     return ei
 
 
+def pbc_repeats(cells, pbc, r):
+    """Copies per cell vector, compute_images (src/mlcg/neighbor_list/torch_impl.py:113-120): ceil(r * norm of the rows of the
+    transposed inverse cell), zero along non-periodic directions.  cells [B,3,3], pbc [B,3] bool -> [B,3] int."""
+    cells = np.asarray(cells).reshape(-1, 3, 3)
+    pbc = np.asarray(pbc).reshape(-1, 3).astype(bool)
+    recip = np.transpose(np.linalg.inv(cells), (0, 2, 1))
+    inv_d = np.sqrt((recip * recip).sum(-1))
+    rep = np.ceil(cells.dtype.type(r) * inv_d).astype(np.int64)
+    return np.where(pbc, rep, 0)
+
+
+def radius_graph_pbc_numpy(pos, ptr, cells, pbc, r, max_num_neighbors=1000, loop=False):
+    """torch_neighbor_list_pbc (torch_impl.py:252-329) restated: every structure is copied along its periodic cell vectors
+    (shift triples in cartesian-product order, last index fastest; copy = pos + shift, rounded once), the original points are
+    searched against all copies (squared distance < r*r, neighbours in the order of the copies, at most
+    ``max_num_neighbors``), the copy index is folded back to the point index, and the pair (i, i, zero shift) is dropped
+    unless ``loop``.  The shift vector is ((s1 c1 + s2 c2) + s3 c3) with separately rounded operations.
+    Returns (edge_index [2,E] with row 0 = centre, cell_shifts [E,3])."""
+    pos = np.asarray(pos)
+    T = pos.dtype.type
+    cells = np.asarray(cells, dtype=pos.dtype).reshape(-1, 3, 3)
+    reps = pbc_repeats(cells, pbc, r)
+    r2 = T(float(r) * float(r))
+    rows0, rows1, shifts_out = [], [], []
+    for b in range(len(ptr) - 1):
+        lo, hi = int(ptr[b]), int(ptr[b + 1])
+        p, n, c = pos[lo:hi], hi - lo, cells[b]
+        n1, n2, n3 = (int(v) for v in reps[b])
+        idx = np.array([(a, bb, cc) for a in range(-n1, n1 + 1) for bb in range(-n2, n2 + 1) for cc in range(-n3, n3 + 1)], dtype=np.int64)
+        sf = idx.astype(pos.dtype)
+        shifts = (sf[:, 0:1] * c[0][None, :] + sf[:, 1:2] * c[1][None, :]) + sf[:, 2:3] * c[2][None, :]     # [S,3]
+        images = (p[None, :, :] + shifts[:, None, :]).reshape(-1, 3)                                   # copy-major
+        d = images[None, :, :] - p[:, None, :]
+        sq = d * d
+        d2 = (sq[..., 0] + sq[..., 1]) + sq[..., 2]
+        hit = d2 < r2
+        keep = hit & (np.cumsum(hit, axis=1) <= max_num_neighbors)
+        i, im = np.nonzero(keep)
+        j, s = im % n, im // n
+        if not loop:
+            central = (idx[s] == 0).all(axis=1)
+            sel = ~(central & (i == j))
+            i, j, s = i[sel], j[sel], s[sel]
+        rows0.append(i + lo)
+        rows1.append(j + lo)
+        shifts_out.append(shifts[s])
+    if not rows0:
+        return np.zeros((2, 0), np.int64), np.zeros((0, 3), pos.dtype)
+    return np.stack([np.concatenate(rows0), np.concatenate(rows1)]).astype(np.int64), np.concatenate(shifts_out).astype(pos.dtype)
+
+
 def exclusion_pair_to_ptr(pairs, num_nodes):
     """``exclusion_pairs.cpp:7-62``: pairs ``[2, P]`` (x, y) -> xs sorted by (y, x), CSR pointer over y."""
     lib = _load()

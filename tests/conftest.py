@@ -24,3 +24,10 @@ def golden_regularized():
     import torch
 
     return torch.load(os.path.join(ROOT, "tests", "golden", "reference_vectors_regularized.pt"), weights_only=False)
+
+
+@pytest.fixture(scope="session")
+def golden_periodic():
+    import torch
+
+    return torch.load(os.path.join(ROOT, "tests", "golden", "reference_vectors_periodic.pt"), weights_only=False)

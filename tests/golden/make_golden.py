@@ -12,7 +12,9 @@ stand-ins that restate the published behaviour:
 * ``torch_geometric.nn.MessagePassing.propagate`` (``aggr="add"``): gather ``x[edge_index[0]]``, call
   ``message``, index-add at ``edge_index[1]``;
 * ``torch_geometric.utils.scatter(reduce="sum")``: index-add over dim 0;
-* ``torch_cluster.radius_graph``: the oracle in ``oracle/radius_ref.py`` (rule "cluster").
+* ``torch_cluster.radius_graph``: the oracle in ``oracle/radius_ref.py`` (rule "cluster");
+* ``torch_cluster.radius`` (periodic structures only): all points of the same structure within the radius, in index
+  order, cut after ``max_num_neighbors``.
 
 Everything else that runs — SchNet, CFConv, MLP, the radial bases, the cutoffs, compute_distances /
 angles / torsions, the prior classes, GradientsOut — is the reference's unmodified code.
@@ -82,6 +84,25 @@ def install_shims(ref_src: str):
         ei = torch.from_numpy(ei)
         return ei if flow == "target_to_source" else ei.flip(0)
 
+    def radius(x, y, r, batch_x=None, batch_y=None, max_num_neighbors=32, num_workers=1):
+        """torch_cluster.radius as its CUDA kernel states it: for every point of y, the points of x of the same structure
+        with squared distance < r*r (float arithmetic of the inputs' dtype), in index order, at most max_num_neighbors;
+        row 0 indexes y, row 1 indexes x."""
+        xn, yn = x.detach().numpy(), y.detach().numpy()
+        bx = batch_x.numpy() if batch_x is not None else np.zeros(len(xn), np.int64)
+        by = batch_y.numpy() if batch_y is not None else np.zeros(len(yn), np.int64)
+        r2 = xn.dtype.type(float(r) * float(r))
+        rows = [[], []]
+        for i in range(len(yn)):
+            cand = np.nonzero(bx == by[i])[0]
+            d = xn[cand] - yn[i]
+            sq = d * d
+            d2 = (sq[:, 0] + sq[:, 1]) + sq[:, 2]
+            hit = cand[d2 < r2][:max_num_neighbors]
+            rows[0].extend([i] * len(hit))
+            rows[1].extend(hit.tolist())
+        return torch.tensor(rows, dtype=torch.long).reshape(2, -1)
+
     mods = {n: types.ModuleType(n) for n in
             ["torch_geometric", "torch_geometric.nn", "torch_geometric.utils", "torch_geometric.data", "torch_cluster",
              "mdtraj", "mdtraj.core", "mdtraj.core.element", "ase", "ase.geometry", "ase.geometry.analysis", "ase.atoms",
@@ -90,7 +111,7 @@ def install_shims(ref_src: str):
     mods["torch_geometric.utils"].scatter = scatter
     mods["torch_geometric.data"].Data = Data
     mods["torch_cluster"].radius_graph = radius_graph
-    mods["torch_cluster"].radius = None
+    mods["torch_cluster"].radius = radius
     mods["mdtraj.core.element"].Element = object
     mods["ase.geometry.analysis"].Analysis = object
     mods["ase"].Atoms = object
@@ -207,6 +228,58 @@ def main(ref_src):
     print("wrote", os.path.join(HERE, "reference_vectors.pt"), os.path.getsize(os.path.join(HERE, "reference_vectors.pt")), "bytes")
 
 
+def main_periodic(ref_src):
+    """Periodic structures: `torch_neighbor_list_pbc` / `atomic_data2neighbor_list` (src/mlcg/neighbor_list/torch_impl.py:252-329,
+    neighbor_list.py:27-102) and a SchNet evaluated on them, for an orthorhombic box, a box periodic along two directions
+    only, and a sheared (triclinic) box; two structures per batch."""
+    install_shims(ref_src)
+    schnet = importlib.import_module("mlcg.nn.schnet")
+    from mlcg.nn.radial_basis import ExpNormalBasis
+    from mlcg.nn.cutoff import CosineCutoff
+    from mlcg.nn.gradients import GradientsOut
+    from mlcg.data.atomic_data import AtomicData
+    sys.modules["mlcg.data"].AtomicData = AtomicData
+    nlmod = importlib.import_module("mlcg.neighbor_list.neighbor_list")
+    gen = torch.Generator().manual_seed(777)
+    out = {}
+    boxes = {"orthorhombic": (torch.tensor([[9.0, 0, 0], [0, 11.0, 0], [0, 0, 13.0]]), [True, True, True]),
+             "slab": (torch.tensor([[9.0, 0, 0], [0, 11.0, 0], [0, 0, 13.0]]), [True, True, False]),
+             "triclinic": (torch.tensor([[9.0, 0, 0], [2.5, 10.0, 0], [1.5, -2.0, 12.0]]), [True, True, True])}
+    for name, (cell, pbc) in boxes.items():
+        torch.manual_seed(3)
+        B, n, T, upper, R, H, L = 2, 18, 4, 7.5, 16, 32, 2
+        cells = torch.stack([cell, cell * 1.1])
+        frac = torch.rand(B, n, 3, generator=gen) * 1.2 - 0.1           # some points outside the cell
+        pos = torch.einsum("bnk,bkd->bnd", frac, cells).reshape(-1, 3)
+        types_ = torch.randint(0, T, (B * n,), generator=gen)
+        batch = torch.arange(B).repeat_interleave(n)
+        mk = lambda: AtomicData(pos=pos.clone(), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list={},
+                                cell=cells.clone(), pbc=torch.tensor([pbc] * B))
+        case = dict(cells=cells, pbc=torch.tensor([pbc] * B), pos=pos, atom_types=types_, batch=batch, B=B, n=n, upper=upper, R=R, H=H, L=L, T=T)
+        for cap in (1000, 12):
+            nl_ = nlmod.atomic_data2neighbor_list(mk(), upper, self_interaction=False, max_num_neighbors=cap)
+            case[f"index_mapping_{cap}"] = nl_["index_mapping"].clone()
+            case[f"cell_shifts_{cap}"] = nl_["cell_shifts"].clone()
+            case[f"mapping_batch_{cap}"] = nl_["mapping_batch"].clone()
+        nl_self = nlmod.atomic_data2neighbor_list(mk(), upper, self_interaction=True, max_num_neighbors=1000)
+        case["index_mapping_self"], case["cell_shifts_self"] = nl_self["index_mapping"].clone(), nl_self["cell_shifts"].clone()
+        cut = CosineCutoff(0.0, upper)
+        model = schnet.StandardSchNet(ExpNormalBasis(cut, R, trainable=False), cut, [H], hidden_channels=H, embedding_size=T,
+                                      num_filters=H, num_interactions=L)
+        with torch.no_grad():
+            for k, p in model.named_parameters():
+                if k.endswith("bias"):
+                    p.copy_(0.1 * torch.randn(p.shape, generator=gen))
+        res = GradientsOut(model, "forces").eval()(mk())
+        case["state_dict"] = {k: v.detach().clone() for k, v in model.state_dict().items()}
+        case["energy"], case["forces"] = res.out["SchNet"]["energy"].detach(), res.out["SchNet"]["forces"].detach()
+        out[name] = case
+        print(name, "edges", case["index_mapping_1000"].shape[1], case["index_mapping_12"].shape[1], "E", case["energy"].tolist())
+    path = os.path.join(HERE, "reference_vectors_periodic.pt")
+    torch.save(out, path)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 def main_regularized(ref_src):
     """`RBFRegularizedSchNet` (src/mlcg/nn/schnet.py:676-803) with shared and with per-block factors, random factors in
     [-0.2, 1.2] so that both clamps act; written to a file of its own."""
@@ -255,6 +328,7 @@ def main_regularized(ref_src):
 
 
 if __name__ == "__main__":
-    if len(sys.argv) not in (2, 3) or (len(sys.argv) == 3 and sys.argv[2] != "regularized"):
-        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg> [regularized]")
-    (main_regularized if len(sys.argv) == 3 else main)(sys.argv[1])
+    extra = {"regularized": main_regularized, "periodic": main_periodic}
+    if len(sys.argv) not in (2, 3) or (len(sys.argv) == 3 and sys.argv[2] not in extra):
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg> [regularized|periodic]")
+    (extra[sys.argv[2]] if len(sys.argv) == 3 else main)(sys.argv[1])

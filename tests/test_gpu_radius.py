@@ -224,3 +224,47 @@ def test_excluded_pairs(dtype, loop, max_nn):
     d2, ei2 = radius_distance(x, 3.0, batch, loop, max_nn, len(sizes), torch.from_numpy(pairs).to(DEV))
     assert np.array_equal(ei2.cpu().numpy(), want)
     assert np.allclose(d2.detach().cpu().numpy(), wdist, rtol=1e-6 if dtype == np.float32 else 1e-12)
+
+
+@pytest.mark.parametrize("name", ["orthorhombic", "slab", "triclinic"])
+def test_periodic_graph_vs_reference_vectors(golden_periodic, name):
+    """`mlcgb_radius_pbc_count` / `_fill` against the lists the reference's torch_neighbor_list_pbc returned."""
+    from mlcg_b200.neighbor_list import atomic_data2neighbor_list
+    import mlcg_b200
+    c = golden_periodic[name]
+    mk = lambda: mlcg_b200.AtomicData(pos=c["pos"].to(DEV), atom_types=c["atom_types"].to(DEV), batch=c["batch"].to(DEV),
+                                      n_atoms=torch.full((c["B"],), c["n"]).to(DEV), cell=c["cells"].to(DEV), pbc=c["pbc"].to(DEV))
+    for key, cap, loop in (("1000", 1000, False), ("12", 12, False), ("self", 1000, True)):
+        nl = atomic_data2neighbor_list(mk(), c["upper"], self_interaction=loop, max_num_neighbors=cap)
+        assert torch.equal(nl["index_mapping"].cpu(), c[f"index_mapping_{key}"])
+        assert torch.allclose(nl["cell_shifts"].cpu(), c[f"cell_shifts_{key}"], rtol=1e-6, atol=1e-6)
+        if key != "self":
+            assert torch.equal(nl["mapping_batch"].cpu(), c[f"mapping_batch_{key}"])
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_periodic_graph_vs_oracle(dtype):
+    """Random boxes, structures of different sizes, cutoffs from a fraction of the box to more than the box (several copies
+    per direction): edges, shifts (bit for bit: same separately rounded arithmetic) and distances against the restatement."""
+    rng = np.random.default_rng(5)
+    be = get_backend()
+    for trial, (rc, cap) in enumerate([(3.0, 1000), (7.0, 1000), (10.5, 1000), (7.0, 9)]):
+        sizes = [5, 17, 24, 1, 20]
+        ptr = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+        B = len(sizes)
+        cells = np.zeros((B, 3, 3), dtype)
+        for b in range(B):
+            cells[b] = np.diag(rng.uniform(6.0, 10.0, 3)) + (rng.uniform(-1.5, 1.5, (3, 3)) if b % 2 else 0.0)
+        pbc = np.array([[True, True, True], [True, False, True], [True, True, True], [False, False, True], [True, True, False]])
+        frac = rng.uniform(-0.1, 1.1, (int(ptr[-1]), 3))
+        pos = np.concatenate([frac[ptr[b]:ptr[b + 1]] @ cells[b].astype(np.float64) for b in range(B)]).astype(dtype)
+        ei, shifts = radius_ref.radius_graph_pbc_numpy(pos, ptr, cells, pbc, rc, cap, False)
+        reps = torch.as_tensor(radius_ref.pbc_repeats(cells, pbc, rc))
+        res = be.radius_graph_pbc(torch.as_tensor(pos, device=DEV), torch.as_tensor(ptr, device=DEV), torch.as_tensor(cells, device=DEV),
+                                  reps.to(DEV), rc, cap, False, want_distance=True)
+        assert np.array_equal(res["edge_index"].cpu().numpy(), ei), trial
+        assert np.array_equal(res["cell_shifts"].cpu().numpy(), shifts), trial
+        d = np.sqrt((((pos[ei[1]] + shifts) - pos[ei[0]]) ** 2).sum(1))
+        assert np.allclose(res["distance"].cpu().numpy(), d, rtol=1e-6 if dtype == np.float32 else 1e-13, atol=1e-6 if dtype == np.float32 else 1e-12)
+        assert np.array_equal(res["mapping_batch"].cpu().numpy(), np.searchsorted(ptr, ei[0], side="right") - 1)
+        assert bool(res["status"] & 1) == (cap == 9)

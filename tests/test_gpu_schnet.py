@@ -59,6 +59,21 @@ def test_golden_rbf_regularized_schnet(golden_regularized, name):
         assert torch.allclose(grads[k].grad.cpu(), g, rtol=1e-4, atol=1e-4 * float(g.abs().max() + 1e-30)), k
 
 
+@pytest.mark.parametrize("name", ["orthorhombic", "slab", "triclinic"])
+def test_golden_periodic_structures(golden_periodic, name):
+    """SchNet on periodic structures (graph over the periodic copies, distances with cell shifts) against the reference."""
+    c = golden_periodic[name]
+    cut = bnn.CosineCutoff(0.0, c["upper"])
+    net = bnn.StandardSchNet(bnn.ExpNormalBasis(cut, c["R"], trainable=False), cut, [c["H"]], hidden_channels=c["H"], embedding_size=c["T"],
+                             num_filters=c["H"], num_interactions=c["L"])
+    net.load_state_dict(c["state_dict"])
+    data = mlcg_b200.AtomicData(pos=c["pos"].to(DEV), atom_types=c["atom_types"].to(DEV), batch=c["batch"].to(DEV),
+                                n_atoms=torch.full((c["B"],), c["n"]).to(DEV), cell=c["cells"].to(DEV), pbc=c["pbc"].to(DEV))
+    out = bnn.GradientsOut(net.to(DEV), "forces").eval()(data)
+    assert torch.allclose(out.out["SchNet"]["energy"].cpu(), c["energy"], rtol=E_RTOL, atol=1e-5)
+    assert torch.allclose(out.out["SchNet"]["forces"].cpu(), c["forces"], rtol=0, atol=F_ATOL)
+
+
 def _make(kind, B, n, n_types, upper, R, H, L, seed, min_dist=None, jitter=0.0):
     torch.manual_seed(seed)
     cut = bnn.CosineCutoff(0.0, upper)

@@ -70,6 +70,28 @@ def test_rbf_regularized_schnet_vs_reference(golden_regularized, name):
         assert torch.allclose(grads[k].grad, g, rtol=1e-4, atol=1e-5 * float(g.abs().max() + 1e-30)), k
 
 
+@pytest.mark.parametrize("name", ["orthorhombic", "slab", "triclinic"])
+def test_periodic_structures_vs_reference(golden_periodic, name):
+    """Neighbour-list dictionary of periodic structures and a SchNet evaluated on it (torch_impl.py:252-329,
+    internal_coordinates.py:72-100) against the reference's outputs."""
+    from mlcg_b200.neighbor_list import atomic_data2neighbor_list
+    c = golden_periodic[name]
+    mk = lambda: mlcg_b200.AtomicData(pos=c["pos"].clone(), atom_types=c["atom_types"], batch=c["batch"], n_atoms=torch.full((c["B"],), c["n"]),
+                                      cell=c["cells"].clone(), pbc=c["pbc"].clone())
+    for key, cap, loop in (("1000", 1000, False), ("12", 12, False)):
+        nl = atomic_data2neighbor_list(mk(), c["upper"], self_interaction=loop, max_num_neighbors=cap)
+        assert torch.equal(nl["index_mapping"], c[f"index_mapping_{key}"])
+        assert torch.allclose(nl["cell_shifts"], c[f"cell_shifts_{key}"], rtol=1e-6, atol=1e-6)
+        assert torch.equal(nl["mapping_batch"], c[f"mapping_batch_{key}"])
+    cut = bnn.CosineCutoff(0.0, c["upper"])
+    net = bnn.StandardSchNet(bnn.ExpNormalBasis(cut, c["R"], trainable=False), cut, [c["H"]], hidden_channels=c["H"], embedding_size=c["T"],
+                             num_filters=c["H"], num_interactions=c["L"])
+    net.load_state_dict(c["state_dict"])
+    out = bnn.GradientsOut(net, "forces").eval()(mk())
+    assert torch.allclose(out.out["SchNet"]["energy"], c["energy"], rtol=2e-6, atol=2e-6)
+    assert torch.allclose(out.out["SchNet"]["forces"], c["forces"], rtol=2e-6, atol=2e-5)
+
+
 def test_state_dict_keys_match_reference(golden):
     c = golden["schnet_expnormal_f32"]
     assert set(schnet_from_case(c).state_dict().keys()) == set(c["state_dict"].keys())

@@ -106,3 +106,20 @@ def test_exclusion_pair_to_ptr_torch_version_matches_the_c_restatement():
         assert txs.tolist() == xs.tolist() and tptr.tolist() == y_ptr.tolist()
     xs, y_ptr = exclusion_pair_to_ptr(torch.tensor([[2, 1, 3, 2, 2], [1, 2, 2, 2, 3]]), 4)
     assert xs.tolist() == [2, 1, 2, 3, 2] and y_ptr.tolist() == [0, 0, 1, 4, 5]
+
+
+@pytest.mark.parametrize("name", ["orthorhombic", "slab", "triclinic"])
+def test_periodic_graph_restatement_vs_reference(golden_periodic, name):
+    """`radius_graph_pbc_numpy` against what the reference's own torch_neighbor_list_pbc returned (torch_impl.py:252-329):
+    same edges in the same order with and without the neighbour cap and with self pairs kept; the shift vectors are equal bit
+    for bit for the axis-aligned boxes and to rounding for the sheared one."""
+    c = golden_periodic[name]
+    pos, ptr = c["pos"].numpy(), np.arange(c["B"] + 1, dtype=np.int64) * c["n"]
+    for key, cap, loop in (("1000", 1000, False), ("12", 12, False), ("self", 1000, True)):
+        ei, shifts = radius_ref.radius_graph_pbc_numpy(pos, ptr, c["cells"].numpy(), c["pbc"].numpy(), c["upper"], cap, loop)
+        assert np.array_equal(ei, c[f"index_mapping_{key}"].numpy())
+        want = c[f"cell_shifts_{key}"].numpy()
+        if name == "triclinic":
+            assert np.allclose(shifts, want, rtol=1e-6, atol=1e-6)
+        else:
+            assert np.array_equal(shifts, want)
