@@ -17,7 +17,7 @@ class AtomicData:
     def __init__(self, pos: torch.Tensor, atom_types: torch.Tensor, batch: torch.Tensor = None, n_atoms: torch.Tensor = None,
                  neighbor_list: Dict[str, Dict[str, Any]] = None, **extra):
         assert pos.dim() == 2 and pos.shape[1] == 3
-        if n_atoms is not None:
+        if n_atoms is not None and not n_atoms.is_cuda:      # (no device->host read for a count that lives on the device)
             assert int(torch.sum(n_atoms)) == pos.shape[0]
         self.pos = pos
         self.atom_types = atom_types
