@@ -10,6 +10,7 @@ Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU restatement o
 path (``oracle/``) on the host cores, on a bounded sample of the same workload.
 """
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -285,7 +286,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # (a rank that fails must not keep the others waiting for NCCL's default ten minutes)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     B, n = WORKLOAD["structures_per_gpu"], WORKLOAD["beads"]
     pos_h, types_h, batch_h = make_inputs(B, n, WORKLOAD["bead_types"], seed=1000 + rank)   # every rank its own replicas
     model = bnn.GradientsOut(make_model().to(dev), "forces").eval()
@@ -319,8 +321,10 @@ def run_ours(args):
         slot["done"].record()
         return slot
 
+    group = {"alive": world > 1}      # cleared once the ranks have parted: rank 0 then works on alone
+
     def barrier():
-        if world > 1:
+        if group["alive"]:
             dist.barrier()
         torch.cuda.synchronize()
 
@@ -384,9 +388,12 @@ def run_ours(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms, ms_profiled = float(t[0]), float(t[1]), float(t[2])
+    # the ranks part here: everything below is rank 0's own reporting (no collective may follow)
+    if world > 1:
+        dist.barrier()
+        group["alive"] = False
+        dist.destroy_process_group()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
         return
 
     # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels on this workload, from the
@@ -442,7 +449,7 @@ def run_ours(args):
                    sample=f"{sample_B} structures of the same workload per step, 16 steps after 1 warm-up, torch CPU float32 + C radius oracle")
 
     extras = None
-    if not args.no_extras:
+    if not args.no_extras and world == 1:      # side measurements of other kernels and configurations: single-GPU runs only
         try:
             # the same step with the filter-network GEMMs on bf16 operands (forces within 1e-2 relative RMS of the fp32 mode)
             bnn.set_filter_precision(model, "bf16")
@@ -479,8 +486,6 @@ def run_ours(args):
                 ms_per_step_with_kernel_events=ms_profiled / args.steps, roofline=roof, cfconv_roofline=cfconv, other_kernels=extras, cpu_baseline=cpu, clocks=clk, kernels=kernels,
                 edges_per_s=world * n_edges * args.steps / (ms_total / 1e3))
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def main():
