@@ -7,6 +7,7 @@ second derivatives) and the classical prior terms, behind the Python interface o
 """
 from . import nn  # noqa: F401
 from .data import AtomicData  # noqa: F401
+from .graphed import GraphedForceField  # noqa: F401
 from .neighbor_list import (atomic_data2neighbor_list, exclusion_pair_to_ptr, make_neighbor_list, radius_cuda,  # noqa: F401
                             radius_distance, radius_graph)
 

@@ -383,3 +383,26 @@ def test_fixed_edge_capacity_evaluation():
     again = model(mk())
     be.check_pending()
     assert torch.equal(again.out["SchNet"]["forces"], want.out["SchNet"]["forces"])
+
+
+def test_evaluation_replayed_from_a_cuda_graph():
+    """`GraphedForceField`: the evaluation recorded once (fixed edge capacity, no host read) and replayed for new positions
+    gives what the plain call gives for those positions, graph rebuilt inside the replay."""
+    from mlcg_b200.backend import get_backend
+    from mlcg_b200.neighbor_list import edge_plan_for
+    model, pos, types_, batch = _make("expnormal", 4, 100, 20, 15.0, 128, 128, 3, 21, min_dist=4.0)
+    model = bnn.GradientsOut(model.to(DEV), "forces").eval()
+    mk = lambda p: mlcg_b200.AtomicData(pos=p.to(DEV), atom_types=types_.to(DEV), batch=batch.to(DEV), n_atoms=torch.full((4,), 100).to(DEV))
+    E = edge_plan_for(mk(pos), 15.0)[0].E
+    moved = [pos, pos + 0.3 * torch.randn(pos.shape, generator=torch.Generator().manual_seed(1)), pos * 1.02]
+    want = []
+    for p in moved:
+        o = model(mk(p))
+        want.append((o.out["SchNet"]["energy"].clone(), o.out["SchNet"]["forces"].clone()))
+    bnn.set_edge_capacity(model, int(1.3 * E))
+    ff = mlcg_b200.GraphedForceField(model, mk(pos))
+    for p, (e_w, f_w) in zip(moved, want):
+        e, f = ff(p.to(DEV))
+        assert torch.equal(e, e_w) and torch.equal(f, f_w)
+    ff.check()
+    bnn.set_edge_capacity(model, None)
