@@ -368,7 +368,9 @@ int mlcgb_filter_forward_counted(const void *d, int64_t E, const int64_t *rows_d
 int mlcgb_filter_backward_counted(const void *d, int64_t E, const int64_t *rows_dev, const int32_t *sel, const int32_t *twin,
                                   const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1,
                                   const void *b1, const void *A2, int64_t F, int precision, const int32_t *row0, const int32_t *row1,
-                                  const void *xl, const void *gagg, int64_t N, void *gd, int32_t *status, void *stream);
+                                  const void *xl, const void *gagg, int64_t N, void *gd,
+                                  int accumulate /* 1: add to gd (same rows as the call that set it) instead of setting it */,
+                                  int32_t *status, void *stream);
 int mlcgb_schnet_eval_counted(const void *pos, const int64_t *types, const int64_t *struct_ptr, int64_t N, int64_t B,
                               const int32_t *row0, const int32_t *row1, const int64_t *offsets, const int32_t *sel,
                               const int32_t *pair_of, const int32_t *twin, int64_t E, int64_t P, const int64_t *counts /* [2] or NULL */,

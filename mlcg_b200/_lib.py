@@ -80,7 +80,7 @@ SIGNATURES = {
     "mlcgb_filter_forward_counted": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, ctypes.POINTER(RbfSpecStruct), c_int, c_dbl, c_dbl, c_vp, c_vp, c_vp, c_i64,
                                              c_int, c_vp, c_vp, c_vp]),
     "mlcgb_filter_backward_counted": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, ctypes.POINTER(RbfSpecStruct), c_int, c_dbl, c_dbl, c_vp, c_vp, c_vp, c_i64,
-                                              c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
+                                              c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_int, c_vp, c_vp]),
     "mlcgb_schnet_eval_counted": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_int, c_dbl,
                                           c_dbl, c_vp, c_int, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]),
     "mlcgb_schnet_eval": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_int, c_dbl, c_dbl,

@@ -377,6 +377,7 @@ struct FilterBwdParams {
     const int32_t *row0, *row1;
     const float *xl, *gagg;  // [N][kF]
     float *gd;               // [E]
+    int accumulate;          // 0: gd[e] is set (and the reverse edge's entry zeroed in pair mode); 1: added to what gd holds
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -655,8 +656,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
         tc_fence_before();
         row_group_sync();
         if (qt == 0 && live) {
-            q.gd[e] = (s_red2[r] + s_red2[128 + r]) + (s_red2[256 + r] + s_red2[384 + r]);
-            if (paired) q.gd[p.twin[e]] = 0.f;   // the pair's whole gradient is carried by one of its two edges
+            const float v = (s_red2[r] + s_red2[128 + r]) + (s_red2[256 + r] + s_red2[384 + r]);
+            if (q.accumulate) {
+                q.gd[e] += v;
+            } else {
+                q.gd[e] = v;
+                if (paired) q.gd[p.twin[e]] = 0.f;   // the pair's whole gradient is carried by one of its two edges
+            }
         }
         es = es_next;
         ri = ri_next;
@@ -730,7 +736,7 @@ extern "C" int mlcgb_filter_backward_counted(const void *d, int64_t E, const int
                                              const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper,
                                              const void *A1, const void *b1, const void *A2, int64_t F, int precision,
                                              const int32_t *row0, const int32_t *row1, const void *xl, const void *gagg, int64_t N,
-                                             void *gd, int32_t *status, void *stream) {
+                                             void *gd, int accumulate, int32_t *status, void *stream) {
     if (int rc = check_spec(rbf, 1)) return rc;
     if (E < 0 || N < 0 || !status || (precision != 0 && precision != 1) || (conv_cutoff_kind != 0 && conv_cutoff_kind != 1)) return MLCGB_E_ARG;
     if (F != kF || rbf->num_rbf > 128) return MLCGB_E_LIMIT;
@@ -757,6 +763,7 @@ extern "C" int mlcgb_filter_backward_counted(const void *d, int64_t E, const int
     q.xl = (const float *)xl;
     q.gagg = (const float *)gagg;
     q.gd = (float *)gd;
+    q.accumulate = accumulate ? 1 : 0;
     return precision == 0 ? filter_bwd_launch<true>(q, (cudaStream_t)stream) : filter_bwd_launch<false>(q, (cudaStream_t)stream);
 }
 
@@ -765,5 +772,5 @@ extern "C" int mlcgb_filter_backward(const void *d, int64_t E, const int32_t *se
                                      const void *A2, int64_t F, int precision, const int32_t *row0, const int32_t *row1, const void *xl,
                                      const void *gagg, int64_t N, void *gd, int32_t *status, void *stream) {
     return mlcgb_filter_backward_counted(d, E, nullptr, sel, twin, rbf, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, F, precision,
-                                         row0, row1, xl, gagg, N, gd, status, stream);
+                                         row0, row1, xl, gagg, N, gd, 0, status, stream);
 }

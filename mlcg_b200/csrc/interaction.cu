@@ -21,7 +21,7 @@ static int interaction_backward_counted(const void *g, const void *a, const void
                                        int conv_cutoff_kind, double conv_lower, double conv_upper, const void *W1, const void *fA1,
                                        const void *fb1, const void *fA2, const void *W2, const void *W3, int64_t N, int64_t E, int64_t P,
                                        int64_t H, int64_t F, int64_t H2, int precision, void *gy, void *gagg, void *gxl, void *gx,
-                                       void *gd, int32_t *status, void *stream);
+                                       void *gd, int gd_accumulate, int32_t *status, void *stream);
 
 int mlcgb_interaction_forward(const void *x, const void *d, const int64_t *ptr_out, const int32_t *nbr_out, const int32_t *sel,
                               const int32_t *pair_of, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower,
@@ -66,7 +66,7 @@ int mlcgb_interaction_backward(const void *g, const void *a, const void *Wp, con
                                void *gd /* [E] or NULL */, int32_t *status, void *stream) {
     return interaction_backward_counted(g, a, Wp, xl, d, ptr_out, nbr_out, sel, pair_of, twin, nullptr, row0, row1, rbf, conv_cutoff_kind,
                                               conv_lower, conv_upper, W1, fA1, fb1, fA2, W2, W3, N, E, P, H, F, H2, precision, gy, gagg, gxl,
-                                              gx, gd, status, stream);
+                                              gx, gd, 0, status, stream);
 }
 
 static int interaction_backward_counted(const void *g, const void *a, const void *Wp, const void *xl, const void *d, const int64_t *ptr_out,
@@ -75,7 +75,8 @@ static int interaction_backward_counted(const void *g, const void *a, const void
                                        int conv_cutoff_kind, double conv_lower, double conv_upper, const void *W1, const void *fA1,
                                        const void *fb1, const void *fA2, const void *W2, const void *W3, int64_t N, int64_t E, int64_t P,
                                        int64_t H, int64_t F, int64_t H2, int precision, void *gy, void *gagg, void *gxl,
-                                       void *gx /* or NULL */, void *gd /* [E] or NULL */, int32_t *status, void *stream) {
+                                       void *gx /* or NULL */, void *gd /* [E] or NULL */, int gd_accumulate, int32_t *status,
+                                       void *stream) {
     if (N < 0 || E < 0 || P < 0 || !status) return MLCGB_E_ARG;
     if (N == 0) return MLCGB_OK;
     if (!g || !a || !xl || !ptr_out || !W1 || !W2 || !W3 || !gy || !gagg || !gxl) return MLCGB_E_ARG;
@@ -93,7 +94,7 @@ static int interaction_backward_counted(const void *g, const void *a, const void
     }
     if (gd && E > 0)
         rc = mlcgb_filter_backward_counted(d, P, pairs_dev, sel, twin, rbf, conv_cutoff_kind, conv_lower, conv_upper, fA1, fb1, fA2, F, precision,
-                                           row0, row1, xl, gagg, N, gd, status, stream);
+                                           row0, row1, xl, gagg, N, gd, gd_accumulate, status, stream);
     return rc;
 }
 
@@ -145,15 +146,10 @@ __global__ void head_backward_kernel(const float *__restrict__ a, const float *_
     }
 }
 
-__global__ void add_inplace_kernel(float *__restrict__ y, const float *__restrict__ x, int64_t n) {
-    pdl_wait();
-    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x) y[t] += x[t];
-}
-
 static inline int64_t up4(int64_t n) { return (n + 3) & ~(int64_t)3; }
 
 struct SchnetLayout {
-    int64_t d, x[2], g[2], agg, gy, gxl, ah, en, gyh, gd, gdt, block0, block_stride, xl_off, a_off, wp_off, total;
+    int64_t d, x[2], g[2], agg, gy, gxl, ah, en, gyh, gd, block0, block_stride, xl_off, a_off, wp_off, total;
 };
 static SchnetLayout schnet_layout(int64_t N, int64_t E, int64_t P, int64_t H, int64_t F, int64_t H2, int64_t Wh, int64_t L) {
     SchnetLayout o;
@@ -164,7 +160,7 @@ static SchnetLayout schnet_layout(int64_t N, int64_t E, int64_t P, int64_t H, in
     o.g[0] = take(N * H); o.g[1] = take(N * H);
     o.agg = take(N * F); o.gy = take(N * H2); o.gxl = take(N * F);
     o.ah = take(N * Wh); o.en = take(N); o.gyh = take(N * Wh);
-    o.gd = take(E); o.gdt = take(E);
+    o.gd = take(E);
     o.xl_off = 0; o.a_off = up4(N * F); o.wp_off = o.a_off + up4(N * H2);
     o.block_stride = o.wp_off + up4(P * F);
     o.block0 = at;
@@ -243,13 +239,12 @@ int mlcgb_schnet_eval_counted(const void *pos, const int64_t *types, const int64
     for (int64_t l = L - 1; l >= 0; l--) {
         const mlcgb_schnet_block &bw = w->blocks[l];
         float *blk = ws + lay.block0 + l * lay.block_stride;
-        float *gd_l = (l == L - 1) ? ws + lay.gd : ws + lay.gdt;
+        // every block's filter kernel writes the same rows of gd (one edge per pair): the last block sets them, the others add
         rc = interaction_backward_counted(ws + lay.g[gcur], blk + lay.a_off, blk + lay.wp_off, blk + lay.xl_off, d, offsets, row1, sel, pair_of, twin,
                                         pairs_dev, row0, row1, rbf, conv_cutoff_kind, conv_lower, conv_upper, bw.lin1_w, bw.filter_w1, bw.filter_b1,
                                         bw.filter_w2, bw.lin2_w, bw.lin_w, N, E, P, H, F, H2, precision, ws + lay.gy, ws + lay.agg, ws + lay.gxl,
-                                        l > 0 ? ws + lay.g[gcur ^ 1] : nullptr, E > 0 ? gd_l : nullptr, status, stream);
+                                        l > 0 ? ws + lay.g[gcur ^ 1] : nullptr, E > 0 ? ws + lay.gd : nullptr, l != L - 1, status, stream);
         if (rc) return rc;
-        if (l != L - 1 && E > 0) launch_pdl(add_inplace_kernel, dim3(grid_for(E, 256)), dim3(256), 0, st, ws + lay.gd, (const float *)(ws + lay.gdt), E);
         gcur ^= 1;
     }
     // symmetric centre-sorted list: grouped by row0 in place, grouped by row1 through the reverse-edge map

@@ -442,6 +442,28 @@ scan_apply_kernel(const int32_t *deg, int64_t N, const int64_t *bsum, int64_t *o
     if (i < N) offsets[i] = bsum[blockIdx.x] + ex;
 }
 
+// inputs of at most one scan block: exclusive scan and grand total in one launch
+__global__ void __launch_bounds__(kScanBlock) scan_single_block_kernel(const int32_t *deg, int64_t N, int64_t *offsets) {
+    __shared__ int64_t s_warp[33];
+    const int64_t i = threadIdx.x;
+    int64_t total;
+    const int64_t ex = block_exclusive_scan(i < N ? (int64_t)deg[i] : 0, s_warp, &total);
+    if (i < N) offsets[i] = ex;
+    if (i == 0) offsets[N] = total;
+}
+
+// offsets[0..N] = exclusive scan of deg[0..N), offsets[N] = total; bsum: (N + kScanBlock - 1) / kScanBlock + 1 words of scratch
+static void launch_scan(const int32_t *deg, int64_t N, int64_t *bsum, int64_t *offsets, cudaStream_t st) {
+    const int64_t nb = (N + kScanBlock - 1) / kScanBlock;
+    if (nb <= 1) {
+        scan_single_block_kernel<<<1, kScanBlock, 0, st>>>(deg, N, offsets);
+        return;
+    }
+    scan_block_sums_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum);
+    scan_of_sums_kernel<<<1, kScanBlock, 0, st>>>(bsum, nb, offsets + N);
+    scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum, offsets);
+}
+
 __global__ void batch_to_ptr_kernel(const int64_t *__restrict__ batch, int64_t N, int64_t B, int64_t *__restrict__ ptr) {
     const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b > B) return;
@@ -456,11 +478,7 @@ __global__ void batch_to_ptr_kernel(const int64_t *__restrict__ batch, int64_t N
 __global__ void edge_twin_kernel(const int32_t *__restrict__ row0, const int32_t *__restrict__ row1,
                                  const int64_t *__restrict__ offsets, int64_t E, int64_t N, int32_t *__restrict__ twin,
                                  int32_t *__restrict__ status) {
-    // offsets[N] is the list's edge count; E may be the (larger) capacity of the buffers
-    const int64_t total = offsets[N];
-    const int64_t nE = total < E ? total : E;
-    if ((nE & 1) && blockIdx.x == 0 && threadIdx.x == 0) atomicOr(status, (int)kAsymmetric);
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < nE; e += (int64_t)gridDim.x * blockDim.x) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x) {
         const int a = row0[e], b = row1[e];
         int32_t t = -1;
         if (a >= 0 && a < N && b >= 0 && b < N) {
@@ -693,10 +711,7 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
         else
             neighbours_kernel<T, false, false><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
                                                                                     cell_of, cell_start, struct_of, deg, nullptr, out, ex, status);
-        const int64_t nb = (N + kScanBlock - 1) / kScanBlock;
-        scan_block_sums_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum);
-        scan_of_sums_kernel<<<1, kScanBlock, 0, st>>>(bsum, nb, offsets + N);
-        scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum, offsets);
+        launch_scan(deg, N, bsum, offsets, st);
     } else {
         if (ex.ptr)
             neighbours_kernel<T, true, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
@@ -818,10 +833,7 @@ int mlcgb_pair_plan(const int32_t *row0, const int32_t *row1, const int64_t *off
     auto *uoff = (int64_t *)(w + align256((size_t)N * 4));
     auto *bsum = (int64_t *)(w + align256((size_t)N * 4) + align256((size_t)(N + 1) * 8));
     upper_count_kernel<<<grid_for(N, 256), 256, 0, st>>>(row1, offsets, N, upper);
-    const int64_t nb = (N + kScanBlock - 1) / kScanBlock;
-    scan_block_sums_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(upper, N, bsum);
-    scan_of_sums_kernel<<<1, kScanBlock, 0, st>>>(bsum, nb, uoff + N);
-    scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(upper, N, bsum, uoff);
+    launch_scan(upper, N, bsum, uoff, st);
     pair_plan_kernel<<<grid_for(E, 256), 256, 0, st>>>(row0, row1, offsets, upper, uoff, E, N, twin, sel, pair_of, status);
     return check_launch();
 }
@@ -853,10 +865,7 @@ int mlcgb_radius_pbc_count(const void *pos, int dtype, const int64_t *ptr, int64
         return MLCGB_OK;
     });
     if (rc) return rc;
-    const int64_t nb = (N + kScanBlock - 1) / kScanBlock;
-    scan_block_sums_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum);
-    scan_of_sums_kernel<<<1, kScanBlock, 0, st>>>(bsum, nb, offsets + N);
-    scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum, offsets);
+    launch_scan(deg, N, bsum, offsets, st);
     return check_launch();
 }
 

@@ -268,3 +268,15 @@ def test_periodic_graph_vs_oracle(dtype):
         assert np.allclose(res["distance"].cpu().numpy(), d, rtol=1e-6 if dtype == np.float32 else 1e-13, atol=1e-6 if dtype == np.float32 else 1e-12)
         assert np.array_equal(res["mapping_batch"].cpu().numpy(), np.searchsorted(ptr, ei[0], side="right") - 1)
         assert bool(res["status"] & 1) == (cap == 9)
+
+
+def test_reverse_edge_map_of_a_list_with_self_pairs():
+    """Self pairs are their own reverse; a list with them may hold an odd number of edges and is still symmetric."""
+    pos = np.array([[0.0, 0, 0], [1.0, 0, 0], [0, 1.0, 0], [5.0, 5, 5], [0.5, 0.5, 0]], np.float32)
+    res = run_gpu(pos, np.array([0, 5], np.int64), 2.0, 1000, True, "cluster")
+    E = int(res["offsets"][-1])
+    assert E % 2 == 1
+    twin, st = get_backend().edge_twin(res["row0"], res["row1"], res["offsets"], 5, fresh_status=True)
+    assert int(st[0]) == 0
+    t = twin.long()
+    assert torch.equal(res["row0"][t], res["row1"]) and torch.equal(res["row1"][t], res["row0"])
