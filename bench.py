@@ -468,11 +468,11 @@ def run_ours(args):
     # kernels of the library per evaluation on the route the timed region takes (one library call for the model): radius graph 7
     # (cells, count, three scan kernels, clamp to the capacity, fill), reverse-edge map / pair selection / pair index 5 (count of
     # upper edges, three scan kernels, plan), distances 1, embedding 1, five per block
-    # forward, output network 3 (layer + tanh, dot product, per-structure sum), its derivative 2, five per block backward
+    # forward, output network 3 (layer + tanh, dot product, per-structure sum), its derivative 1, five per block backward
     # (three for the first block, whose input gradient nobody needs; the distance gradients of the blocks are added up by
     # the filter kernels), distance backward 1
     L = WORKLOAD["interactions"]
-    launches_timed = args.steps * (7 + 5 + 1 + 1 + 5 * L + 3 + 2 + 5 * (L - 1) + 3 + 1)
+    launches_timed = args.steps * (7 + 5 + 1 + 1 + 5 * L + 3 + 1 + 5 * (L - 1) + 3 + 1)
     value = world * B * args.steps / (ms_total / 1e3)
     h2d = pos_h.numel() * 4 + types_h.numel() * 8 + batch_h.numel() * 8
     d2h = B * 4 + pos_h.numel() * 4

@@ -215,7 +215,9 @@ int mlcgb_gemm_tc_tn_colsum(const void *A, const void *B, int64_t K, int64_t M, 
  * schnet.py:150; their derivatives in the force pass).  `epilogue`:
  *   0  C = A op(B) + bias                      1  C = tanh(A op(B) + bias)
  *   2  C = A op(B) + bias + aux                3  C = (A op(B) + bias) * (1 - aux^2)      (aux = tanh output)
- * `aux` is [M,N] like C (NULL for 0 and 1); C may alias aux.  Needs M >= 128, N and K multiples of four and 16-byte aligned
+ *   4  C = A' op(B) + bias with A'[m,k] = aux[k] * (1 - A[m,k]^2), aux a vector [K]: the derivative of a tanh layer followed
+ *      by a dot product with aux (the output network, src/mlcg/nn/schnet.py:157), applied as the input tile is read
+ * `aux` is [M,N] like C for 2 and 3 (NULL for 0 and 1); C may alias aux.  Needs M >= 128, N and K multiples of four and 16-byte aligned
  * A, C and aux; MLCGB_E_LIMIT otherwise (use mlcgb_gemm_tc and separate elementwise steps). */
 int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias, const void *aux, int epilogue, int64_t M,
                         int64_t N, int64_t K, void *C, int32_t *status, void *stream);

@@ -516,7 +516,7 @@ class CudaBackend:
             return C, cs
         return self.gemm(2, G, X), G.sum(0)
 
-    EPI_NONE, EPI_TANH, EPI_ADD, EPI_TANH_GRAD = 0, 1, 2, 3
+    EPI_NONE, EPI_TANH, EPI_ADD, EPI_TANH_GRAD, EPI_IN_TANH_GRAD_VEC = 0, 1, 2, 3, 4
 
     def gemm_fused_ok(self, mode: int, A, B) -> bool:
         """Whether :meth:`gemm_fused` takes these operands (float32, >= 128 rows, widths multiples of four and <= 128)."""
@@ -528,7 +528,8 @@ class CudaBackend:
 
     def gemm_fused(self, mode: int, A, B, bias=None, aux=None, epilogue: int = 0):
         """Row-wise tensor-core GEMM (mode 0: A B^T + bias, mode 1: A B) with the elementwise step that follows it:
-        1 tanh, 2 ``+ aux``, 3 ``* (1 - aux**2)``."""
+        1 tanh, 2 ``+ aux``, 3 ``* (1 - aux**2)``; 4 transforms the input instead: ``A <- aux[None, :] * (1 - A**2)`` with a
+        vector ``aux`` over the columns of A."""
         _need_cuda(A, B, bias, aux)
         A, B = A.contiguous(), B.detach().contiguous()
         M, K = A.shape

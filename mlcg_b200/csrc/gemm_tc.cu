@@ -217,7 +217,9 @@ gemm_tc_rows_kernel(const float *__restrict__ A, const float *__restrict__ B, co
 //    drain while the next tile is processed.
 // Epilogues (EPI): 0 none; 1 tanh; 2 + aux; 3 * (1 - aux^2), the derivative of tanh given its output.  `aux` is a matrix
 // shaped like C; its tile is copied into the output stage while the next tile is converted and combined there.
-enum { kEpiNone = 0, kEpiTanh = 1, kEpiAdd = 2, kEpiTanhGrad = 3 };
+// EPI 4 is a transform of the input instead: A[m,k] <- aux[k] * (1 - A[m,k]^2) with a vector aux[K], applied as the tile is read
+// (the derivative of a tanh layer followed by a dot product with aux, fed straight into the next GEMM).
+enum { kEpiNone = 0, kEpiTanh = 1, kEpiAdd = 2, kEpiTanhGrad = 3, kProTanhGradVec = 4 };
 template <int MODE>   // 0 NT, 1 NN
 __global__ void __launch_bounds__(kGT, 1)
 gemm_tc_rows_pipe_kernel(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias, int64_t E, int N, int K,
@@ -230,7 +232,8 @@ gemm_tc_rows_pipe_kernel(const float *__restrict__ A, const float *__restrict__ 
     uint8_t *s_in = smem + L::kStageA, *s_out = smem + L::kStageB;
     float *s_red = reinterpret_cast<float *>(smem + L::kMisc);
     float *s_bias = s_red + 512;
-    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_bias + 128);   // two barriers, one per accumulator
+    float *s_vec = s_bias + 128;                                     // input-transform vector (EPI 4)
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_vec + 128);     // two barriers, one per accumulator
     uint32_t *s_tmem = reinterpret_cast<uint32_t *>(s_bar + 2);
     int *s_err = reinterpret_cast<int *>(s_tmem + 1);
 
@@ -242,7 +245,10 @@ gemm_tc_rows_pipe_kernel(const float *__restrict__ A, const float *__restrict__ 
     const int wrows = MODE == 0 ? N : K, wcols = MODE == 0 ? K : N;
     const int wpad = wcols <= 64 ? 64 : 128;
     if (load_weight_tile<true>(sB_hi, sB_lo, B, wrows, wcols, wpad, kWS) && blockIdx.x == 0) atomicOr(status, (int)kWeightRange);
-    if (tid < 128) s_bias[tid] = (bias && tid < N) ? bias[tid] : 0.f;
+    if (tid < 128) {
+        s_bias[tid] = (bias && tid < N) ? bias[tid] : 0.f;
+        s_vec[tid] = (epi == kProTanhGradVec && tid < K) ? aux[tid] : 0.f;      // (a parameter vector, not a result of the kernels before)
+    }
     const uint32_t bar0 = smem_u32(s_bar);
     if (tid == 0) {
         mbar_init(bar0, 1);
@@ -274,7 +280,11 @@ gemm_tc_rows_pipe_kernel(const float *__restrict__ A, const float *__restrict__ 
         float rmax = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; w++) {
-            const float4 v = *gstage(s_in, r, (col0 >> 2) + w);
+            float4 v = *gstage(s_in, r, (col0 >> 2) + w);
+            if (epi == kProTanhGradVec) {
+                const float4 u = *reinterpret_cast<const float4 *>(s_vec + col0 + 4 * w);
+                v = make_float4(u.x * fmaf(-v.x, v.x, 1.f), u.y * fmaf(-v.y, v.y, 1.f), u.z * fmaf(-v.z, v.z, 1.f), u.w * fmaf(-v.w, v.w, 1.f));
+            }
             x[4 * w] = v.x; x[4 * w + 1] = v.y; x[4 * w + 2] = v.z; x[4 * w + 3] = v.w;
             rmax = fmaxf(fmaxf(rmax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
         }
@@ -684,7 +694,8 @@ static int set_smem(Kern kern, bool *done) {
 static int rows_pipe_launch(int mode, const void *A, const void *B, const void *bias, const void *aux, int epi, int64_t M, int64_t N, int64_t K,
                             void *C, int32_t *status, cudaStream_t st) {
     CUtensorMap cmap;
-    if ((K & 3) != 0 || ((uintptr_t)A & 15) != 0 || (aux && ((uintptr_t)aux & 15) != 0) || !make_rows_map(&cmap, (float *)C, M, N)) return MLCGB_E_LIMIT;
+    if ((K & 3) != 0 || ((uintptr_t)A & 15) != 0 || (aux && epi != kProTanhGradVec && ((uintptr_t)aux & 15) != 0) || !make_rows_map(&cmap, (float *)C, M, N))
+        return MLCGB_E_LIMIT;
     const int64_t ntiles = (M + tc::kRows - 1) / tc::kRows;
     const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
     static bool p0[64] = {false}, p1[64] = {false};
@@ -708,8 +719,8 @@ extern "C" {
 
 int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias, const void *aux, int epilogue, int64_t M, int64_t N,
                         int64_t K, void *C, int32_t *status, void *stream) {
-    if ((mode != 0 && mode != 1) || epilogue < 0 || epilogue > 3 || !status) return MLCGB_E_ARG;
-    if ((epilogue == kEpiAdd || epilogue == kEpiTanhGrad) && !aux) return MLCGB_E_ARG;
+    if ((mode != 0 && mode != 1) || epilogue < 0 || epilogue > 4 || !status) return MLCGB_E_ARG;
+    if ((epilogue == kEpiAdd || epilogue == kEpiTanhGrad || epilogue == kProTanhGradVec) && !aux) return MLCGB_E_ARG;
     if (!mlcgb_gemm_tc_supported(mode, M, N, K)) return MLCGB_E_LIMIT;
     if (M == 0) return MLCGB_OK;
     if (!A || !B || !C) return MLCGB_E_ARG;

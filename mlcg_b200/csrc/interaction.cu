@@ -135,21 +135,10 @@ __global__ void head_out_kernel(const float *__restrict__ a, const float *__rest
     }
 }
 
-// gradient of the sum of all energies with respect to the pre-activation of the output network's hidden layer:
-// gy[n,f] = w[f] * (1 - a[n,f]^2)
-__global__ void head_backward_kernel(const float *__restrict__ a, const float *__restrict__ w, int64_t N, int64_t F, float *__restrict__ gy) {
-    const int64_t total = N * F;
-    pdl_wait();
-    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-        const float av = a[t];
-        gy[t] = w[t % F] * fmaf(-av, av, 1.f);
-    }
-}
-
 static inline int64_t up4(int64_t n) { return (n + 3) & ~(int64_t)3; }
 
 struct SchnetLayout {
-    int64_t d, x[2], g[2], agg, gy, gxl, ah, en, gyh, gd, block0, block_stride, xl_off, a_off, wp_off, total;
+    int64_t d, x[2], g[2], agg, gy, gxl, ah, en, gd, block0, block_stride, xl_off, a_off, wp_off, total;
 };
 static SchnetLayout schnet_layout(int64_t N, int64_t E, int64_t P, int64_t H, int64_t F, int64_t H2, int64_t Wh, int64_t L) {
     SchnetLayout o;
@@ -159,7 +148,7 @@ static SchnetLayout schnet_layout(int64_t N, int64_t E, int64_t P, int64_t H, in
     o.x[0] = take(N * H); o.x[1] = take(N * H);
     o.g[0] = take(N * H); o.g[1] = take(N * H);
     o.agg = take(N * F); o.gy = take(N * H2); o.gxl = take(N * F);
-    o.ah = take(N * Wh); o.en = take(N); o.gyh = take(N * Wh);
+    o.ah = take(N * Wh); o.en = take(N);
     o.gd = take(E);
     o.xl_off = 0; o.a_off = up4(N * F); o.wp_off = o.a_off + up4(N * H2);
     o.block_stride = o.wp_off + up4(P * F);
@@ -232,9 +221,9 @@ int mlcgb_schnet_eval_counted(const void *pos, const int64_t *types, const int64
     if (rc || !grad_pos) return rc ? rc : check_launch();
 
     // force pass: d(sum of energies)/d(pos)
-    launch_pdl(head_backward_kernel, dim3(grid_for(N * Wh, 256)), dim3(256), 0, st, (const float *)(ws + lay.ah), (const float *)w->head_out, N, Wh, ws + lay.gyh);
+    // through the output network: g = (w_out * (1 - a^2)) head_W, the factor applied as the GEMM reads its input tile
     int gcur = 0;
-    rc = mlcgb_gemm_tc_fused(1, ws + lay.gyh, w->head_W, nullptr, nullptr, 0, N, H, Wh, ws + lay.g[gcur], status, stream);
+    rc = mlcgb_gemm_tc_fused(1, ws + lay.ah, w->head_W, nullptr, w->head_out, 4, N, H, Wh, ws + lay.g[gcur], status, stream);
     if (rc) return rc;
     for (int64_t l = L - 1; l >= 0; l--) {
         const mlcgb_schnet_block &bw = w->blocks[l];

@@ -223,8 +223,14 @@ def test_tensor_core_gemm_fused_epilogues(M, N, K):
     cases = [(0, W, b, None, be.EPI_NONE, lin0), (0, W, b, None, be.EPI_TANH, torch.tanh(lin0)), (0, W, b, aux, be.EPI_ADD, lin0 + a64),
              (0, W, b, aux, be.EPI_TANH_GRAD, lin0 * (1 - a64 * a64)), (1, V, None, None, be.EPI_NONE, lin1),
              (1, V, None, aux, be.EPI_ADD, lin1 + a64), (1, V, None, aux, be.EPI_TANH_GRAD, lin1 * (1 - a64 * a64))]
+    # input transform: A' = vec * (1 - A^2) with a vector over the columns of A (A = a tanh layer's output)
+    T = torch.tanh(X)
+    vec = torch.randn(K, generator=gen)
+    Tp = vec.double() * (1 - T.double() ** 2)
+    cases += [(1, V, None, vec, be.EPI_IN_TANH_GRAD_VEC, Tp @ V.double()), (0, W, b, vec, be.EPI_IN_TANH_GRAD_VEC, Tp @ W.double().t() + b.double())]
     for mode, B, bias, ax, epi, want in cases:
-        got = be.gemm_fused(mode, X.to(DEV), B.to(DEV), None if bias is None else bias.to(DEV), None if ax is None else ax.to(DEV), epi)
+        A_in = T if epi == be.EPI_IN_TANH_GRAD_VEC else X
+        got = be.gemm_fused(mode, A_in.to(DEV), B.to(DEV), None if bias is None else bias.to(DEV), None if ax is None else ax.to(DEV), epi)
         err = float((got.cpu().double() - want).abs().max())
         assert err < 5e-6 * max(1.0, float(want.abs().max())), (mode, epi, err)
     get_backend().check_pending()

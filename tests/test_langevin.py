@@ -94,7 +94,8 @@ def _md_case(device, B=2, n=70, seed=5):
     model = bnn.SumOut(torch.nn.ModuleDict(models)).eval().to(device)
     data = data.to(device)
     masses = torch.full((data.pos.shape[0],), 12.0 / 418.39, device=device)
-    sim = LangevinSimulation(model, dt=0.002, friction=1e-12, beta=1.0 / (0.0019872041 * 300))
+    # (a short time step: the comparison of two runs must not depend on how fast rounding differences grow)
+    sim = LangevinSimulation(model, dt=0.0005, friction=1e-12, beta=1.0 / (0.0019872041 * 300))
     sim.attach(data, masses, velocities=torch.zeros_like(data.pos))
     return sim, model
 
@@ -104,21 +105,23 @@ def test_simulation_replayed_from_a_cuda_graph():
     """One MD step recorded into a CUDA graph (fixed edge capacity: no host read in the step) and replayed gives the
     trajectory of the step-by-step loop; the trajectory buffer holds the positions at the save points."""
     from mlcg_b200.neighbor_list import edge_plan_for
-    steps, every = 24, 6
+    steps, every = 12, 3
     sim, model = _md_case("cuda:0")
     assert sim.noisescale < 1e-6
     x0 = sim.data.pos.clone()
     sim.simulate(steps, save_interval=every)
     traj_plain, pot_plain = sim.trajectory.clone(), sim.potentials.clone()
-    assert torch.equal(traj_plain[-1], sim.data.pos) and float((traj_plain[-1] - x0).abs().max()) > 1e-3
+    moved = float((traj_plain[-1] - x0).abs().max())
+    assert torch.equal(traj_plain[-1], sim.data.pos) and moved > 1e-4, moved
 
     sim2, model2 = _md_case("cuda:0")
     E = edge_plan_for(sim2.data, 12.0)[0].E
     bnn.set_edge_capacity(model2, int(1.5 * E))
     sim2.simulate(steps, save_interval=every, cuda_graph=True)
     assert sim2.trajectory.shape == traj_plain.shape
-    assert float((sim2.trajectory - traj_plain).abs().max()) < 1e-3
-    assert torch.allclose(sim2.potentials, pot_plain, rtol=1e-4, atol=1e-2)
+    diff = float((sim2.trajectory - traj_plain).abs().max())
+    assert diff < 1e-3 and diff < 0.05 * moved, (diff, moved)
+    assert torch.allclose(sim2.potentials, pot_plain, rtol=1e-4, atol=1e-2), (sim2.potentials, pot_plain)
     # an edge capacity that the graph outgrows is reported at the next save point
     sim3, model3 = _md_case("cuda:0")
     bnn.set_edge_capacity(model3, E - 2)
