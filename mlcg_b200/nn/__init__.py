@@ -3,4 +3,6 @@ from .gradients import EnergyOut, GradientsOut, SumOut
 from .mlp import MLP
 from .prior import Dihedral, FourierSeries, Harmonic, HarmonicAngles, HarmonicBonds, Repulsion
 from .radial_basis import ExpNormalBasis, GaussianBasis, RegularizedBasis, SymmetricTensor
-from .schnet import CFConv, InteractionBlock, RBFRegularizedSchNet, SchNet, StandardSchNet, set_edge_capacity, set_filter_precision
+from .attention import (AttentiveInteractionBlock, AttentiveInteractionBlock2, ExactAttention, FavorAttention, Nonlocalinteractionblock,  # noqa: F401
+                        Residual, Residual_MLP, ResidualStack)
+from .schnet import AttentiveSchNet, CFConv, InteractionBlock, RBFRegularizedSchNet, SchNet, StandardSchNet, set_edge_capacity, set_filter_precision

@@ -303,7 +303,8 @@ class SchNet(torch.nn.Module):
             rbf_expansion = LazyRadialBasis(distances, self.rbf_layer, plan.symmetric)
         else:
             rbf_expansion = _tag_symmetric(self.rbf_layer(distances), plan.symmetric)
-        num_batch = None
+        # (number of structures for blocks that ask for it, taken from n_atoms where that avoids reading batch[-1] on the host)
+        num_batch = None if all(type(b) is InteractionBlock for b in self.interaction_blocks) else self._num_structures(data)
         for block, spec in zip(self.interaction_blocks, specs):
             if type(block) is InteractionBlock:
                 x = block.forward_residual(x, edge_index, distances, rbf_expansion, num_batch, data.batch, fused=spec if lazy_ok else None)
@@ -367,6 +368,13 @@ class SchNet(torch.nn.Module):
         plan._half, plan._pair_of = sel, pair_of
         spec, conv_cut, weights, precision = setup
         return be.schnet_eval(pos, self._types(data), ptr, plan, spec, conv_cut, weights, precision, want_grad=True, counts=res["counts"])
+
+    @staticmethod
+    def _num_structures(data) -> int:
+        n_atoms = getattr(data, "n_atoms", None)
+        if n_atoms is not None and torch.is_tensor(n_atoms) and n_atoms.dim() == 1:
+            return int(n_atoms.numel())
+        return int(data.batch[-1]) + 1
 
     def _forward_whole_model(self, data, neighbor_list):
         setup = self._whole_model_setup(data.pos)
@@ -445,6 +453,58 @@ class StandardSchNet(SchNet):
         output_network = MLP([hidden_channels] + output_hidden_layer_widths + [1], activation_func=activation, last_bias=False)
         super().__init__(embedding_layer, blocks, rbf_layer, output_network, max_num_neighbors=max_num_neighbors,
                          nls_distance_method=nls_distance_method)
+
+
+class AttentiveSchNet(SchNet):
+    """SchNet whose interaction blocks add attention over the beads of each structure (schnet.py:478-674): same arguments and
+    sub-module names.  ``attention_version`` "normal" (`AttentiveInteractionBlock`) or "2" (`AttentiveInteractionBlock2`); the
+    attention arguments are given all together or all ``None`` (a block without the non-local part cannot be evaluated in the
+    reference either)."""
+
+    def __init__(self, rbf_layer: torch.nn.Module, cutoff: torch.nn.Module, output_hidden_layer_widths: List[int], num_features_in: int,
+                 num_features_out: int, num_residual_q: int, num_residual_k: int, num_residual_v: int, attention_block: torch.nn.Module,
+                 hidden_channels: int = 128, embedding_size: int = 100, num_filters: int = 128, num_interactions: int = 3,
+                 activation_func: torch.nn.Module = torch.nn.Tanh(), max_num_neighbors: int = 1000, layer_widths: List[int] = None,
+                 activation_first: bool = False, aggr: str = "add", attention_version: str = "normal",
+                 nls_distance_method: str = "custom_kernel"):
+        from .attention import AttentiveInteractionBlock, AttentiveInteractionBlock2, Nonlocalinteractionblock
+        layer_widths = [128, 128] if layer_widths is None else layer_widths
+        if num_interactions < 1:
+            raise ValueError("At least one interaction block must be specified")
+        if cutoff.cutoff_lower != rbf_layer.cutoff.cutoff_lower:
+            warnings.warn("Cutoff function lower cutoff, {}, and radial basis function  lower cutoff, {}, do not match.".format(
+                cutoff.cutoff_lower, rbf_layer.cutoff.cutoff_lower))
+        if cutoff.cutoff_upper != rbf_layer.cutoff.cutoff_upper:
+            warnings.warn("Cutoff function upper cutoff, {}, and radial basis function  upper cutoff, {}, do not match.".format(
+                cutoff.cutoff_upper, rbf_layer.cutoff.cutoff_upper))
+        if attention_version not in ("normal", "2"):
+            raise RuntimeError("attention_version not recognized")
+        block_cls = AttentiveInteractionBlock if attention_version == "normal" else AttentiveInteractionBlock2
+        attention_args = [num_features_in, num_features_out, num_residual_q, num_residual_k, num_residual_v, attention_block]
+        given = [a is not None for a in attention_args]
+        if any(given) and not all(given):
+            raise ValueError("To use Attention, you must specify 'num_features_in','num_features_out','num_residual_q','num_residual_k', "
+                             "'num_residual_v' and 'attention_block'")
+        embedding_layer = torch.nn.Embedding(embedding_size, hidden_channels)
+        blocks = []
+        for _ in range(num_interactions):
+            filter_network = MLP(layer_widths=[rbf_layer.num_rbf, num_filters, num_filters], activation_func=activation_func)
+            cfconv = CFConv(filter_network, cutoff=cutoff, num_filters=num_filters, in_channels=hidden_channels,
+                            out_channels=hidden_channels, aggr=aggr)
+            nonlocal_part = None
+            if all(given):
+                # (as in the reference, `layer_widths`, `activation_func` and `activation_first` do not reach the non-local part:
+                # its residual blocks are 128 wide with tanh, so the features have to be 128 wide as well)
+                nonlocal_part = Nonlocalinteractionblock(num_features_in, num_features_out, num_residual_q, num_residual_k, num_residual_v,
+                                                         attention_block)
+            blocks.append(block_cls(cfconv_layer=cfconv, hidden_channels=hidden_channels, activation_func=activation_func,
+                                    attention_block=nonlocal_part))
+        output_network = MLP([hidden_channels] + output_hidden_layer_widths + [1], activation_func=activation_func, last_bias=False)
+        super().__init__(interaction_blocks=blocks, rbf_layer=rbf_layer, embedding_layer=embedding_layer, output_network=output_network,
+                         max_num_neighbors=max_num_neighbors, nls_distance_method=nls_distance_method)
+
+    def energy_and_gradient(self, data):
+        return None         # attention mixes all beads of a structure: no one-call route
 
 
 class RBFRegularizedSchNet(StandardSchNet):

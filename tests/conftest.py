@@ -31,3 +31,10 @@ def golden_periodic():
     import torch
 
     return torch.load(os.path.join(ROOT, "tests", "golden", "reference_vectors_periodic.pt"), weights_only=False)
+
+
+@pytest.fixture(scope="session")
+def golden_attentive():
+    import torch
+
+    return torch.load(os.path.join(ROOT, "tests", "golden", "reference_vectors_attentive.pt"), weights_only=False)

@@ -280,6 +280,55 @@ def main_periodic(ref_src):
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def main_attentive(ref_src):
+    """`AttentiveSchNet` (src/mlcg/nn/schnet.py:478-674, src/mlcg/nn/attention.py): both block versions, softmax and FAVOR+
+    attention, two structures per batch (so the structure mask acts) and one (the unmasked branch)."""
+    install_shims(ref_src)
+    schnet = importlib.import_module("mlcg.nn.schnet")
+    attention = importlib.import_module("mlcg.nn.attention")
+    from mlcg.nn.radial_basis import ExpNormalBasis
+    from mlcg.nn.cutoff import CosineCutoff
+    from mlcg.nn.gradients import GradientsOut
+    from mlcg.data.atomic_data import AtomicData
+    sys.modules["mlcg.data"].AtomicData = AtomicData
+    gen = torch.Generator().manual_seed(2468)
+    out = {}
+    # (the reference's non-local part is always 128 wide, so hidden_channels has to be 128; filters and bases are kept small,
+    # and of the force-matching gradients only those of the small parameters are stored, to keep the file small)
+    for name, version, favor, B in (("normal_exact", "normal", False, 2), ("v2_favor", "2", True, 2), ("normal_favor_single", "normal", True, 1)):
+        torch.manual_seed(11)
+        n, T, upper, R, H, L, F = 16, 4, 12.0, 8, 128, 1, 32
+        cut = CosineCutoff(0.0, upper)
+        att = attention.FavorAttention(dimv=24, dimqk=H) if favor else attention.ExactAttention()
+        model = schnet.AttentiveSchNet(ExpNormalBasis(cut, R, trainable=False), cut, [16], num_features_in=H, num_features_out=H,
+                                       num_residual_q=1, num_residual_k=1, num_residual_v=1, attention_block=att, hidden_channels=H,
+                                       embedding_size=T, num_filters=F, num_interactions=L, attention_version=version)
+        with torch.no_grad():
+            for k, p in model.named_parameters():
+                if k.endswith("bias"):
+                    p.copy_(0.1 * torch.randn(p.shape, generator=gen))
+        pos = torch.cat([chain(n, jitter=0.3, gen=gen) for _ in range(B)])
+        types_ = torch.randint(0, T, (B * n,), generator=gen)
+        batch = torch.arange(B).repeat_interleave(n)
+        mk = lambda: AtomicData(pos=pos.clone(), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list={})
+        res = GradientsOut(model, "forces").eval()(mk())
+        case = dict(version=version, favor=favor, upper=upper, R=R, H=H, L=L, T=T, F=F, B=B, n=n, pos=pos, atom_types=types_,
+                    batch=batch, state_dict={k: v.detach().clone() for k, v in model.state_dict().items()},
+                    energy=res.out["SchNet"]["energy"].detach(), forces=res.out["SchNet"]["forces"].detach())
+        target = torch.randn(pos.shape, generator=gen)
+        tr = GradientsOut(model, "forces").train()
+        model.zero_grad()
+        loss = torch.nn.functional.mse_loss(tr(mk()).out["SchNet"]["forces"], target)
+        loss.backward()
+        case["target_forces"], case["loss"] = target, loss.detach()
+        case["param_grads"] = {k: p.grad.detach().clone() for k, p in model.named_parameters() if p.grad is not None and p.numel() <= 4096}
+        out[name] = case
+        print(name, "E", case["energy"].tolist(), "loss", float(loss), "params", len(case["param_grads"]))
+    path = os.path.join(HERE, "reference_vectors_attentive.pt")
+    torch.save(out, path)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 def main_regularized(ref_src):
     """`RBFRegularizedSchNet` (src/mlcg/nn/schnet.py:676-803) with shared and with per-block factors, random factors in
     [-0.2, 1.2] so that both clamps act; written to a file of its own."""
@@ -328,7 +377,7 @@ def main_regularized(ref_src):
 
 
 if __name__ == "__main__":
-    extra = {"regularized": main_regularized, "periodic": main_periodic}
+    extra = {"regularized": main_regularized, "periodic": main_periodic, "attentive": main_attentive}
     if len(sys.argv) not in (2, 3) or (len(sys.argv) == 3 and sys.argv[2] not in extra):
-        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg> [regularized|periodic]")
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg> [regularized|periodic|attentive]")
     (extra[sys.argv[2]] if len(sys.argv) == 3 else main)(sys.argv[1])

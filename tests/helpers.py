@@ -31,6 +31,19 @@ def regularized_schnet_from_case(case, device="cpu"):
     return model.to(device)
 
 
+def attentive_schnet_from_case(case, device="cpu"):
+    """mlcg_b200 AttentiveSchNet with the architecture and weights of a golden case."""
+    cut = bnn.CosineCutoff(0.0, case["upper"])
+    att = bnn.FavorAttention(dimv=case["state_dict"]["interaction_blocks.0.attention_block.attention_block.omega"].shape[1],
+                             dimqk=case["H"]) if case["favor"] else bnn.ExactAttention()
+    model = bnn.AttentiveSchNet(bnn.ExpNormalBasis(cut, case["R"], trainable=False), cut, [16], num_features_in=case["H"],
+                                num_features_out=case["H"], num_residual_q=1, num_residual_k=1, num_residual_v=1, attention_block=att,
+                                hidden_channels=case["H"], embedding_size=case["T"], num_filters=case["F"], num_interactions=case["L"],
+                                attention_version=case["version"])
+    model.load_state_dict(case["state_dict"])
+    return model.to(device)
+
+
 def data_from_case(case, device="cpu", dtype=None):
     dtype = case["pos"].dtype if dtype is None else dtype
     return mlcg_b200.AtomicData(pos=case["pos"].clone().to(device=device, dtype=dtype), atom_types=case["atom_types"].to(device),

@@ -9,7 +9,7 @@ import mlcg_b200
 from mlcg_b200 import nn as bnn
 from oracle import radius_ref, schnet_ref
 
-from helpers import data_from_case, prior_setup, random_walk_chain, regularized_schnet_from_case, schnet_from_case
+from helpers import attentive_schnet_from_case, data_from_case, prior_setup, random_walk_chain, regularized_schnet_from_case, schnet_from_case
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -72,6 +72,23 @@ def test_golden_periodic_structures(golden_periodic, name):
     out = bnn.GradientsOut(net.to(DEV), "forces").eval()(data)
     assert torch.allclose(out.out["SchNet"]["energy"].cpu(), c["energy"], rtol=E_RTOL, atol=1e-5)
     assert torch.allclose(out.out["SchNet"]["forces"].cpu(), c["forces"], rtol=0, atol=F_ATOL)
+
+
+@pytest.mark.parametrize("name", ["normal_exact", "v2_favor", "normal_favor_single"])
+def test_golden_attentive_schnet(golden_attentive, name):
+    """`AttentiveSchNet` on the device against the reference's energies, forces and force-matching loss."""
+    c = golden_attentive[name]
+    net = attentive_schnet_from_case(c, device=DEV)
+    out = bnn.GradientsOut(net, "forces").eval()(data_from_case(c, device=DEV))
+    assert torch.allclose(out.out["SchNet"]["energy"].cpu(), c["energy"], rtol=E_RTOL, atol=2e-5)
+    assert torch.allclose(out.out["SchNet"]["forces"].cpu(), c["forces"], rtol=0, atol=F_ATOL)
+    out = bnn.GradientsOut(net, "forces").train()(data_from_case(c, device=DEV))
+    loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], c["target_forces"].to(DEV))
+    loss.backward()
+    assert torch.allclose(loss.detach().cpu(), c["loss"], rtol=2e-5)
+    grads = dict(net.named_parameters())
+    for k, g in c["param_grads"].items():
+        assert torch.allclose(grads[k].grad.cpu(), g, rtol=2e-3, atol=2e-4 * float(g.abs().max() + 1e-30)), k
 
 
 def _make(kind, B, n, n_types, upper, R, H, L, seed, min_dist=None, jitter=0.0):

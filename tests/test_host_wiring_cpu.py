@@ -10,7 +10,7 @@ from mlcg_b200 import autograd as ag
 from mlcg_b200 import backend, nn as bnn
 from oracle.primitives import OracleBackend
 
-from helpers import data_from_case, prior_setup, regularized_schnet_from_case, schnet_from_case
+from helpers import attentive_schnet_from_case, data_from_case, prior_setup, regularized_schnet_from_case, schnet_from_case
 
 
 @pytest.fixture(autouse=True)
@@ -90,6 +90,26 @@ def test_periodic_structures_vs_reference(golden_periodic, name):
     out = bnn.GradientsOut(net, "forces").eval()(mk())
     assert torch.allclose(out.out["SchNet"]["energy"], c["energy"], rtol=2e-6, atol=2e-6)
     assert torch.allclose(out.out["SchNet"]["forces"], c["forces"], rtol=2e-6, atol=2e-5)
+
+
+@pytest.mark.parametrize("name", ["normal_exact", "v2_favor", "normal_favor_single"])
+def test_attentive_schnet_vs_reference(golden_attentive, name):
+    """`AttentiveSchNet` (src/mlcg/nn/schnet.py:478-674, src/mlcg/nn/attention.py): state_dict keys, energies, forces and the
+    force-matching gradients of the small parameters, for both block versions and both attention kernels."""
+    c = golden_attentive[name]
+    net = attentive_schnet_from_case(c)
+    assert set(net.state_dict().keys()) == set(c["state_dict"].keys())
+    out = bnn.GradientsOut(net, "forces").eval()(data_from_case(c))
+    assert torch.allclose(out.out["SchNet"]["energy"], c["energy"], rtol=5e-6, atol=5e-6)
+    assert torch.allclose(out.out["SchNet"]["forces"], c["forces"], rtol=1e-5, atol=5e-5)
+    out = bnn.GradientsOut(net, "forces").train()(data_from_case(c))
+    loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], c["target_forces"])
+    loss.backward()
+    assert torch.allclose(loss.detach(), c["loss"], rtol=1e-5)
+    grads = dict(net.named_parameters())
+    for k, g in c["param_grads"].items():
+        assert grads[k].grad is not None, k
+        assert torch.allclose(grads[k].grad, g, rtol=1e-3, atol=2e-5 * float(g.abs().max() + 1e-30)), k
 
 
 def test_state_dict_keys_match_reference(golden):
