@@ -6,8 +6,13 @@
 Workload at every N: 512 structures per GPU of a 100-bead C-alpha chain (3.8 A self-avoiding random
 walk, 20 bead types), SchNet with 3 interaction blocks, hidden = filters = 128, 128 exp-normal radial
 basis functions, 15 A cosine cutoff, float32; one step = radius graph + energy + forces for the batch.
-Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU restatement of mlcg's own PyTorch
-path (``oracle/``) on the host cores, on a bounded sample of the same workload.
+Prints ONE JSON line (rank 0).
+
+After the timed region the run checks itself: the first 64 structures of the timed batch are evaluated on the host
+cores by the CPU arm and the run fails if the energies leave 1e-5 relative or the forces 1e-4 kcal/mol/A.  The
+CPU arm is mlcg's own modules (``oracle/_ref/site``, installed by ``oracle/build_ref.py``; torch_geometric's and
+torch_cluster's calls replaced by the stand-ins of ``oracle/mlcg_loader.py``) when they are there, else the
+restatement in ``oracle/schnet_ref.py``; the same arm, timed, is the ``cpu_baseline`` and ``--impl reference``.
 """
 import argparse
 import datetime
@@ -24,12 +29,14 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "energy+force evaluations per second (structures/s), SchNet CG"
-WORKLOAD = dict(workload="cfg1: 100-bead CA chains, 512 structures/GPU, SchNet 3x(H=128,F=128), 128 expnorm RBF, rc=15A, energy+forces",
+WORKLOAD = dict(workload="cfg2: 100-bead CA chains, 512 structures/GPU, SchNet 3x(H=128,F=128), 128 expnorm RBF, rc=15A, energy+forces",
                 structures_per_gpu=512, beads=100, bead_types=20, hidden=128, filters=128, num_rbf=128, interactions=3,
                 cutoff_A=15.0, l2="flushed between steps (256 MiB write); edge tensors (>= 500 MB) exceed L2 as well")
+E_RTOL, F_ATOL = 1e-5, 1e-4          # float32 parity bars: energies relative, forces kcal/mol/A absolute
+KCAL_BETA_300K = 1.0 / (0.0019872041 * 300)
 
 
-# ----------------------------------------------------------------------------------------- workload
+# ----------------------------------------------------------------------------------------- workloads
 def self_avoiding_chains(B, n, gen, step=3.8, min_dist=4.0):
     """B chains grown together: a bead is redrawn while it is closer than ``min_dist`` to any bead of its own
     chain except its predecessor; after 200 failed draws the chain steps back five beads."""
@@ -57,6 +64,14 @@ def self_avoiding_chains(B, n, gen, step=3.8, min_dist=4.0):
     return pos.reshape(B * n, 3)
 
 
+def random_walks(B, n, gen, step=3.8, jitter=0.0):
+    v = torch.randn(B, n, 3, generator=gen)
+    pos = torch.cumsum(step * v / v.norm(dim=2, keepdim=True), dim=1)
+    if jitter:
+        pos = pos + jitter * torch.randn(B, n, 3, generator=gen)
+    return pos.reshape(B * n, 3)
+
+
 def make_inputs(B, n, n_types, seed):
     gen = torch.Generator().manual_seed(seed)
     pos = self_avoiding_chains(B, n, gen)
@@ -65,58 +80,104 @@ def make_inputs(B, n, n_types, seed):
     return pos, types_, batch
 
 
-def make_model():
-    from mlcg_b200 import nn as bnn
-    torch.manual_seed(0)
-    cut = bnn.CosineCutoff(0.0, WORKLOAD["cutoff_A"])
-    rbf = bnn.ExpNormalBasis(cut, WORKLOAD["num_rbf"], trainable=False)
-    return bnn.StandardSchNet(rbf, cut, [WORKLOAD["hidden"]], hidden_channels=WORKLOAD["hidden"], embedding_size=WORKLOAD["bead_types"],
-                              num_filters=WORKLOAD["filters"], num_interactions=WORKLOAD["interactions"])
+def make_model(ns=None, kind="expnormal", cutoff=None, num_rbf=None, interactions=None, n_types=None, seed=0):
+    """StandardSchNet of the benchmark's widths from the classes of ``ns`` (this package's ``nn`` by default; the reference's
+    namespace for the CPU arm: same constructor)."""
+    if ns is None:
+        from mlcg_b200 import nn as ns
+    cutoff = WORKLOAD["cutoff_A"] if cutoff is None else cutoff
+    num_rbf = WORKLOAD["num_rbf"] if num_rbf is None else num_rbf
+    torch.manual_seed(seed)
+    cut = ns.CosineCutoff(0.0, cutoff)
+    rbf = ns.GaussianBasis(cut, num_rbf, trainable=False) if kind == "gaussian" else ns.ExpNormalBasis(cut, num_rbf, trainable=False)
+    return ns.StandardSchNet(rbf, cut, [WORKLOAD["hidden"]], hidden_channels=WORKLOAD["hidden"],
+                             embedding_size=WORKLOAD["bead_types"] if n_types is None else n_types, num_filters=WORKLOAD["filters"],
+                             num_interactions=WORKLOAD["interactions"] if interactions is None else interactions)
 
 
-# ----------------------------------------------------------------------------------------- CPU legs
-def oracle_step_fn(model_sd, pos, types_, batch, B):
-    """One energy+force evaluation with the CPU oracle (radius graph included), returns (E, F)."""
-    from oracle import radius_ref, schnet_ref
-    cut = {"cutoff": "cosine", "lower": 0.0, "upper": WORKLOAD["cutoff_A"]}
-    spec = {"kind": "expnormal", "rbf_cutoff": cut, "cutoff": cut, "activation": "tanh", "num_interactions": WORKLOAD["interactions"]}
-    ptr = radius_ref.batch_to_ptr(batch.numpy(), B)
+# ----------------------------------------------------------------------------------------- CPU arm
+class CpuArm:
+    """The reference's CPU implementation of the path on the host cores.  ``kind`` "reference": mlcg's own modules from
+    ``oracle/_ref/site`` (SchNet, CFConv, MLP, bases, cutoffs, priors, GradientsOut, SumOut unmodified; message passing,
+    scatter and the radius graph through the stand-ins of ``oracle/mlcg_loader.py``); "port": the restatement in ``oracle/``."""
 
-    def step():
-        ei = torch.from_numpy(radius_ref.radius_graph_c(pos.numpy(), ptr, WORKLOAD["cutoff_A"], 1000, False, "cluster"))
-        e, f, _ = schnet_ref.energy_and_forces(lambda p: schnet_ref.schnet_energy(model_sd, spec, p, types_, batch, ei, B), pos)
-        return e, f
+    def __init__(self):
+        from oracle import mlcg_loader
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        self.kind = "reference" if mlcg_loader.available() else "port"
+        self.ns = None
+        if self.kind == "reference":
+            mlcg_loader.install()
+            self.ns = mlcg_loader.modules()
 
-    return step
+    def describe(self):
+        if self.kind == "reference":
+            return "mlcg's own modules on torch CPU float32 (torch_geometric propagate/scatter and torch_cluster.radius_graph replaced by stand-ins; radius graph by the C oracle)"
+        return "restatement of mlcg's modules (oracle/schnet_ref.py) on torch CPU float32 + C radius oracle"
+
+    def schnet_evaluator(self, state_dict, n, **arch):
+        """``fn(pos, types, batch, B) -> (energy, forces)`` of a SchNet with this state_dict, radius graph rebuilt per call."""
+        kind, cutoff = arch.get("kind", "expnormal"), arch.get("cutoff", WORKLOAD["cutoff_A"])
+        L = arch.get("interactions", WORKLOAD["interactions"])
+        if self.kind == "reference":
+            ns = self.ns
+            model = make_model(ns, **arch)
+            model.load_state_dict(state_dict)
+            wrapped = ns.GradientsOut(model, "forces").eval()
+
+            def fn(pos, types_, batch, B):
+                data = ns.AtomicData(pos=pos.clone(), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list={})
+                out = wrapped(data)
+                return out.out["SchNet"]["energy"].detach(), out.out["SchNet"]["forces"].detach()
+
+            return fn
+        from oracle import radius_ref, schnet_ref
+        cut = {"cutoff": "cosine", "lower": 0.0, "upper": cutoff}
+        spec = {"kind": kind, "rbf_cutoff": cut, "cutoff": cut, "activation": "tanh", "num_interactions": L}
+
+        def fn(pos, types_, batch, B):
+            ptr = radius_ref.batch_to_ptr(batch.numpy(), B)
+            ei = torch.from_numpy(radius_ref.radius_graph_c(pos.numpy(), ptr, cutoff, 1000, False, "cluster"))
+            e, f, _ = schnet_ref.energy_and_forces(lambda p: schnet_ref.schnet_energy(state_dict, spec, p, types_, batch, ei, B), pos)
+            return e, f
+
+        return fn
 
 
-def cpu_leg(sample_B, steps, warmup):
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    model = make_model()
-    sd = {k: v.detach() for k, v in model.state_dict().items()}
-    pos, types_, batch = make_inputs(sample_B, WORKLOAD["beads"], WORKLOAD["bead_types"], seed=0)
-    step = oracle_step_fn(sd, pos, types_, batch, sample_B)
+def timed_host(fn, steps, warmup):
     for _ in range(warmup):
-        step()
+        fn()
     t0 = time.perf_counter()
     for _ in range(steps):
-        step()
-    dt = time.perf_counter() - t0
-    return sample_B * steps / dt, dt / steps * 1e3, cores
+        out = fn()
+    return (time.perf_counter() - t0) / steps, out
+
+
+def parity(e, f, e_ref, f_ref):
+    de = (e - e_ref).abs()
+    rel = float((de / e_ref.abs().clamp_min(1e-30)).max())
+    df = float((f - f_ref).abs().max())
+    return dict(max_rel_dE=rel, max_abs_dE=float(de.max()), max_abs_dF=df, max_abs_F=float(f_ref.abs().max()), energy_rtol=E_RTOL, force_atol=F_ATOL,
+                ok=bool(rel <= E_RTOL and df <= F_ATOL))
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample_B = 128
-    value, ms, cores = cpu_leg(sample_B, max(args.steps, 1), max(args.warmup, 1))
-    sample = f"{sample_B} structures of the same workload per step (of 512), torch CPU float32, radius graph rebuilt each step"
-    line = dict(metric=METRIC, value=value, unit="structures/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup, ms_per_step=ms,
+    arm = CpuArm()
+    sample_B, n = 128, WORKLOAD["beads"]
+    sd = {k: v.detach() for k, v in make_model().state_dict().items()}
+    pos, types_, batch = make_inputs(sample_B, n, WORKLOAD["bead_types"], seed=1000)
+    fn = arm.schnet_evaluator(sd, n)
+    sec, _ = timed_host(lambda: fn(pos, types_, batch, sample_B), max(args.steps, 1), max(args.warmup, 1))
+    value = sample_B / sec
+    sample = f"{sample_B} structures of the same workload per step (of {WORKLOAD['structures_per_gpu']}), radius graph rebuilt each step; {arm.describe()}"
+    line = dict(metric=METRIC, value=value, unit="structures/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup, ms_per_step=sec * 1e3,
                 higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
                 config=dict(WORKLOAD, sample_structures_per_step=sample_B),
-                cpu_baseline=dict(value=value, unit="structures/s", cores=cores, kind="port", sample=sample),
+                cpu_baseline=dict(value=value, unit="structures/s", cores=arm.cores, kind=arm.kind, sample=sample),
                 e2e=dict(value=value, unit="structures/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
     print(json.dumps(line))
 
@@ -161,8 +222,6 @@ class ClockSampler:
         return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None, reasons=sorted(reasons), samples=len(sm))
 
 
-
-# ----------------------------------------------------------------------------------------- other kernel families
 def time_cuda(fn, iters=5, warm=2):
     for _ in range(warm):
         fn()
@@ -178,85 +237,154 @@ def time_cuda(fn, iters=5, warm=2):
     return statistics.median(ts)
 
 
-def extra_measurements(dev, hbm_peak):
-    """Kernel families that the headline step exercises only lightly, at the sizes of the other configurations:
-    the stand-alone radius graph (256 x 4000 points, 60 A cube, 10 A cutoff) and the prior terms of the simulation
-    configuration (1024 x 268 beads).  Device time, CUDA events; inputs are far larger than L2."""
+# ----------------------------------------------------------------------------------------- the other configurations
+def _uniform_tables(prior, T):
+    """Give a prior built from one statistics entry the same parameters for all ``T`` bead types (its tables are indexed by the
+    bead types of each term; their trailing ``order`` dimensions grow from 1 to T)."""
+    order = prior.order
+    for name, buf in list(prior.named_buffers()):
+        lead = buf.dim() - order
+        setattr(prior, name, buf.expand(*buf.shape[:lead], *([T] * order)).contiguous())
+    return prior
+
+
+def _chain_terms(n):
+    idx = torch.arange(n)
+    full = torch.cartesian_prod(idx, idx).t()
+    return {"bonds": torch.stack([idx[:-1], idx[1:]]), "angles": torch.stack([idx[:-2], idx[1:-1], idx[2:]]),
+            "dihedrals": torch.stack([idx[:-3], idx[1:-2], idx[2:-1], idx[3:]]), "repulsion": full[:, (full[0] - full[1]).abs() >= 3]}
+
+
+def _prior_modules(ns, T):
+    cos19 = float(torch.cos(torch.tensor(1.9)))
+    pri = {"bonds": ns.HarmonicBonds({(0, 0): {"k": 100.0, "x_0": 3.8}}), "angles": ns.HarmonicAngles({(0, 0, 0): {"k": 50.0, "x_0": cos19}}),
+           "dihedrals": ns.Dihedral({(0, 0, 0, 0): {"v_0": 0.0, "k1s": {"k1_1": 0.3, "k1_2": -0.2, "k1_3": 0.1}, "k2s": {"k2_1": 0.2, "k2_2": 0.1, "k2_3": -0.1}}}),
+           "repulsion": ns.Repulsion({(0, 0): {"sigma": 4.0}})}
+    return {k: _uniform_tables(p, T) for k, p in pri.items()}
+
+
+def _batched_lists(terms, B, n, dev="cpu"):
+    offs = torch.arange(B) * n
+    out = {}
+    for name, m in terms.items():
+        M = m.shape[1] * B
+        out[name] = ((m[:, None, :] + offs[None, :, None]).reshape(m.shape[0], M).contiguous().to(dev),
+                     torch.arange(B).repeat_interleave(m.shape[1]).to(dev))
+    return out
+
+
+def _baoab_host(model_fn, pos, vel, forces, masses, beta_mass_ratio, noises, dt, friction):
+    """The reference's BAOAB step on the host (src/mlcg/simulation/langevin.py:100-144), for the CPU leg of the simulation
+    configuration: forces at t in, positions / velocities / forces at t+1 out, one model evaluation per step."""
+    import math
+    vscale = math.exp(-dt * friction)
+    noisescale = math.sqrt(1 - vscale * vscale)
+    pot = None
+    for noise in noises:
+        v = vel + 0.5 * dt * forces / masses[:, None]
+        x = pos + v * dt * 0.5
+        v = v * vscale + noisescale * beta_mass_ratio[:, None] * noise
+        x = x + v * dt * 0.5
+        pot, forces = model_fn(x)
+        vel = v + 0.5 * dt * forces / masses[:, None]
+        pos = x
+    return pos, vel, pot, forces
+
+
+def extra_measurements(dev, hbm_peak, arm):
+    """The other configurations on one GPU: the small CPU-runnable system (64 x 10 beads), the stand-alone radius graph (256 x 4000
+    points, 60 A cube, 10 A cutoff, compared bit for bit with the CPU oracle on all 256 structures), the prior terms and the
+    Langevin dynamics of the simulation configuration (1024 x 268 beads).  Device time by CUDA events; inputs far larger than L2
+    except where the configuration itself is small.  Each GPU figure has the CPU arm's figure beside it (bounded samples)."""
     import mlcg_b200
     from mlcg_b200 import nn as bnn
     from mlcg_b200.backend import get_backend
+    from mlcg_b200.simulation import LangevinSimulation
+    from oracle import radius_ref
     be = get_backend()
     out = {}
     gen = torch.Generator().manual_seed(0)
+
+    # ---- the CPU-runnable configuration: 64 structures x 10 beads, types 0..9, 50 Gaussians on 0-30 A, 2 blocks
+    B1, n1 = 64, 10
+    arch1 = dict(kind="gaussian", cutoff=30.0, num_rbf=50, interactions=2, n_types=10)
+    net1 = make_model(**arch1)
+    pos1 = random_walks(B1, n1, gen, jitter=0.3)
+    types1, batch1 = torch.arange(n1).repeat(B1), torch.arange(B1).repeat_interleave(n1)
+    m1 = bnn.GradientsOut(net1.to(dev), "forces").eval()
+    d1 = dict(pos=pos1.to(dev), atom_types=types1.to(dev), batch=batch1.to(dev), n_atoms=torch.full((B1,), n1, device=dev))
+
+    def eval1():
+        o = m1(mlcg_b200.AtomicData(pos=d1["pos"].clone(), atom_types=d1["atom_types"], batch=d1["batch"], n_atoms=d1["n_atoms"]))
+        return o.out["SchNet"]["energy"], o.out["SchNet"]["forces"]
+
+    ms = time_cuda(eval1, iters=20, warm=5)
+    e1, f1 = eval1()
+    fn1 = arm.schnet_evaluator({k: v.detach().cpu() for k, v in net1.state_dict().items()}, n1, **arch1)
+    sec1, (e1r, f1r) = timed_host(lambda: fn1(pos1, types1, batch1, B1), 10, 2)
+    out["eval_64x10"] = dict(ms=ms, structures_per_s=B1 / (ms / 1e3), cpu_ms=sec1 * 1e3, cpu_structures_per_s=B1 / sec1,
+                             parity=parity(e1.cpu(), f1.cpu(), e1r, f1r),
+                             note="64 structures x 10 beads, 2 blocks, 50 Gaussian functions on 0-30 A; radius graph + energy + forces per call; "
+                                  "GPU time is the host's launch path at this size; CPU: all 64 structures, 10 calls")
+    del m1, net1
+
+    # ---- stand-alone radius graph
     B, n = 256, 4000
-    pos = (torch.rand(B * n, 3, generator=gen) * 60.0).to(dev)
+    pos_h = torch.rand(B * n, 3, generator=gen) * 60.0
+    pos = pos_h.to(dev)
     ptr = torch.arange(B + 1, device=dev) * n
     res = be.radius_graph(pos, ptr, 10.0, 1000, False, 1)
     E = int(res["edge_index"].shape[1])
-    del res
+    t0 = time.perf_counter()
+    ei_cpu = radius_ref.radius_graph_c(pos_h.numpy(), (torch.arange(B + 1) * n).numpy(), 10.0, 1000, False, "cluster")
+    cpu_s = time.perf_counter() - t0
+    same = bool(torch.equal(res["edge_index"].cpu(), torch.from_numpy(ei_cpu)))
+    del res, ei_cpu
+    if not same:
+        raise RuntimeError("radius graph of 256 x 4000 points differs from the CPU oracle's")
     ms = time_cuda(lambda: be.radius_graph(pos, ptr, 10.0, 1000, False, 1), iters=5, warm=1)
     nbytes = 16 * E + 20 * B * n
     out["radius_graph_256x4000"] = dict(edges=E, ms=ms, edges_per_s=E / (ms / 1e3), algorithmic_GBps=nbytes / ms / 1e6,
-                                        frac_of_hbm=nbytes / ms / 1e6 / hbm_peak,
-                                        note="count + scan + host read of E + fill, allocation of the outputs included; "
-                                             "algorithmic bytes = 16 B/edge written + 20 B/point read")
+                                        frac_of_hbm=nbytes / ms / 1e6 / hbm_peak, bit_exact_vs_cpu_oracle=same, cpu_ms=cpu_s * 1e3,
+                                        cpu_edges_per_s=E / cpu_s, cpu_cores=arm.cores,
+                                        note="count + scan + host read of E + fill, allocation of the outputs included; algorithmic bytes = 16 B/edge "
+                                             "written + 20 B/point read; CPU: the C oracle (all pairs of each structure, OpenMP over structures), "
+                                             "all 256 structures, one call; the two edge lists are compared whole")
     del pos
-    # priors of the simulation configuration
-    Bp, npb = 1024, 268
-    idx = torch.arange(npb, device=dev)
-    full = torch.cartesian_prod(idx, idx).t()
-    lists = {"bonds": torch.stack([idx[:-1], idx[1:]]), "angles": torch.stack([idx[:-2], idx[1:-1], idx[2:]]),
-             "dihedrals": torch.stack([idx[:-3], idx[1:-2], idx[2:-1], idx[3:]]), "repulsion": full[:, (full[0] - full[1]).abs() >= 3]}
-    ppos = self_avoiding_chains(Bp, npb, gen).to(dev)    # 3.8 A walk, no two beads closer than 4 A
-    offs = (torch.arange(Bp, device=dev) * npb)
+
+    # ---- priors of the simulation configuration
+    Bp, npb, T = 1024, 268, 20
+    terms = _chain_terms(npb)
+    lists = _batched_lists(terms, Bp, npb, dev)
+    ppos_h = self_avoiding_chains(Bp, npb, gen)
+    ppos = ppos_h.to(dev)
     n_par = {"bonds": 2, "angles": 2, "dihedrals": 7, "repulsion": 1}
     for kind, name in enumerate(["bonds", "angles", "dihedrals", "repulsion"]):
-        m = lists[name]
-        M = m.shape[1] * Bp
-        mapping = (m[:, None, :] + offs[None, :, None]).reshape(m.shape[0], M).contiguous()
-        mb = torch.arange(Bp, device=dev).repeat_interleave(m.shape[1])
+        mapping, mb = lists[name]
+        M = mapping.shape[1]
         params = torch.rand(n_par[name], M, device=dev) + (3.0 if name in ("bonds", "repulsion") else 0.0)
         ms = time_cuda(lambda: be.prior_terms(kind, ppos, mapping, mb, params, Bp), iters=5, warm=1)
-        nbytes = M * (8 * m.shape[0] + 8 + 4 * n_par[name]) + 2 * ppos.numel() * 4
+        nbytes = M * (8 * mapping.shape[0] + 8 + 4 * n_par[name]) + 2 * ppos.numel() * 4
         out[f"prior_{name}_1024x268"] = dict(terms=M, ms=ms, terms_per_s=M / (ms / 1e3), algorithmic_GBps=nbytes / ms / 1e6,
                                              frac_of_hbm=nbytes / ms / 1e6 / hbm_peak)
-        del mapping, mb, params
-    # Langevin dynamics of the simulation configuration: 1024 replicas x 268 beads, SchNet (3 blocks, 12 A) + the four
-    # priors, BAOAB, graph rebuilt every step
-    from mlcg_b200.simulation import LangevinSimulation
-    import itertools
-    T = 20
-    torch.manual_seed(0)
-    cut = bnn.CosineCutoff(0.0, 12.0)
-    net = bnn.StandardSchNet(bnn.ExpNormalBasis(cut, 128, trainable=False), cut, [128], hidden_channels=128, embedding_size=T,
-                             num_filters=128, num_interactions=3)
-    stats2 = lambda d: {k: d for k in itertools.product(range(1), repeat=2)}
-    pri = {"bonds": bnn.HarmonicBonds({(0, 0): {"k": 100.0, "x_0": 3.8}}), "angles": bnn.HarmonicAngles({(0, 0, 0): {"k": 50.0, "x_0": float(torch.cos(torch.tensor(1.9)))}}),
-           "dihedrals": bnn.Dihedral({(0, 0, 0, 0): {"v_0": 0.0, "k1s": {"k1_1": 0.3, "k1_2": -0.2, "k1_3": 0.1}, "k2s": {"k2_1": 0.2, "k2_2": 0.1, "k2_3": -0.1}}}),
-           "repulsion": bnn.Repulsion({(0, 0): {"sigma": 4.0}})}
+        del params
+
+    # ---- Langevin dynamics: 1024 replicas x 268 beads, SchNet (3 blocks, 12 A) + the four priors, BAOAB, graph rebuilt every step
+    arch5 = dict(cutoff=12.0, n_types=T)
+    net = make_model(**arch5)
+    sd5 = {k: v.detach().clone() for k, v in net.state_dict().items()}
     models = {"SchNet": bnn.GradientsOut(net, "forces")}
-    models.update({k: bnn.GradientsOut(p, "forces") for k, p in pri.items()})
+    models.update({k: bnn.GradientsOut(p, "forces") for k, p in _prior_modules(bnn, T).items()})
     model = bnn.SumOut(torch.nn.ModuleDict(models)).eval().to(dev)
-    nls = {}
-    for name in ["bonds", "angles", "dihedrals", "repulsion"]:
-        m = lists[name]
-        M = m.shape[1] * Bp
-        nls[name] = mlcg_b200.make_neighbor_list(name, m.shape[0], (m[:, None, :] + offs[None, :, None]).reshape(m.shape[0], M).contiguous(),
-                                                 torch.arange(Bp, device=dev).repeat_interleave(m.shape[1]))
-    class _Data(mlcg_b200.AtomicData):
-        pass
-    data = _Data(pos=ppos.clone(), atom_types=torch.randint(0, T, (Bp * npb,), generator=gen).to(dev), batch=torch.arange(Bp, device=dev).repeat_interleave(npb),
-                 n_atoms=torch.full((Bp,), npb, device=dev), neighbor_list=nls)
-    # priors use bead type 0 tables: give them a type vector of zeros through their cached parameters
-    zero_types = torch.zeros(Bp * npb, dtype=torch.long, device=dev)
-    real_types = data.atom_types
-    data.atom_types = zero_types
-    for name, p in pri.items():
-        p._cached_params(data)
-    data.atom_types = real_types
-    sim = LangevinSimulation(model, dt=0.002, friction=1.0, beta=1.0 / (0.0019872041 * 300), rng=torch.Generator(device=dev).manual_seed(0))
-    sim.attach(data, torch.full((Bp * npb,), 12.0 / 418.39, device=dev))
+    nls = {name: mlcg_b200.make_neighbor_list(name, m.shape[0], m, mb) for name, (m, mb) in lists.items()}
+    types5_h = torch.randint(0, T, (Bp * npb,), generator=gen)
+    data = mlcg_b200.AtomicData(pos=ppos.clone(), atom_types=types5_h.to(dev), batch=torch.arange(Bp, device=dev).repeat_interleave(npb),
+                                n_atoms=torch.full((Bp,), npb, device=dev), neighbor_list=nls)
+    mass = 12.0 / 418.39
+    sim = LangevinSimulation(model, dt=0.002, friction=1.0, beta=KCAL_BETA_300K, rng=torch.Generator(device=dev).manual_seed(0))
+    sim.attach(data, torch.full((Bp * npb,), mass, device=dev))
     pot, forces = sim.calculate_potential_and_forces(sim.data)
+    e0, f0 = pot.cpu(), forces.cpu()               # energies and forces of the starting structures, for the check below
     for _ in range(2):
         _, pot, forces = sim.timestep(sim.data, forces)
     torch.cuda.synchronize()
@@ -268,17 +396,157 @@ def extra_measurements(dev, hbm_peak):
     b.record()
     torch.cuda.synchronize()
     ms = a.elapsed_time(b) / nsteps
+    be.check_pending()
+    # CPU leg: 64 replicas x 5 BAOAB steps with the CPU arm's SchNet + four priors (reference modules when installed)
+    Bc = 64
+    cpu = None
+    if arm.kind == "reference":
+        ns = arm.ns
+        cnet = make_model(ns, **arch5)
+        cnet.load_state_dict(sd5)
+        cmods = {"SchNet": ns.GradientsOut(cnet, "forces")}
+        cmods.update({k: ns.GradientsOut(p, "forces") for k, p in _prior_modules(ns, T).items()})
+        cmodel = ns.SumOut(torch.nn.ModuleDict(cmods)).eval()
+        clists = _batched_lists(terms, Bc, npb)
+        cnl = {name: dict(tag=name, order=m.shape[0], index_mapping=m, mapping_batch=mb, cell_shifts=None, rcut=None, self_interaction=False)
+               for name, (m, mb) in clists.items()}
+        ctypes_, cbatch = types5_h[: Bc * npb], torch.arange(Bc).repeat_interleave(npb)
+
+        def model_fn(x):
+            d = ns.AtomicData(pos=x.clone(), atom_types=ctypes_, batch=cbatch, n_atoms=torch.full((Bc,), npb), neighbor_list=dict(cnl))
+            o = cmodel(d)
+            return o.out["energy"].detach(), o.out["forces"].detach()
+
+        x0 = ppos_h[: Bc * npb].clone()
+        ec, fc = model_fn(x0)
+        chk = parity(e0[:Bc], f0[: Bc * npb], ec, fc)
+        cgen = torch.Generator().manual_seed(1)
+        masses_c = torch.full((Bc * npb,), mass)
+        bmr = torch.sqrt(1.0 / (KCAL_BETA_300K * masses_c))
+        noises = [torch.randn(Bc * npb, 3, generator=cgen) for _ in range(5)]
+        t0 = time.perf_counter()
+        _baoab_host(model_fn, x0, torch.zeros_like(x0), fc, masses_c, bmr, noises, 0.002, 1.0)
+        cpu_s = (time.perf_counter() - t0) / len(noises)
+        cpu = dict(ms_per_md_step_64_replicas=cpu_s * 1e3, replica_steps_per_s=Bc / cpu_s, parity_first_evaluation=chk,
+                   sample="64 of the 1024 replicas, 5 BAOAB steps (mlcg's SchNet, priors, GradientsOut and SumOut; the step loop restates "
+                          "langevin.py:100-144), scaled per replica-step")
+        if not chk["ok"]:
+            raise RuntimeError(f"SchNet + priors on 64 x 268 beads differ from the CPU arm: {chk}")
     out["langevin_1024x268"] = dict(ms_per_md_step=ms, md_steps_per_s=1e3 / ms, replica_steps_per_s=Bp * 1e3 / ms, finite=bool(torch.isfinite(pot).all()),
+                                    cpu=cpu, cpu_cores=arm.cores,
                                     note="SchNet (3 blocks, 128 expnorm RBF, 12 A) + bonds/angles/dihedrals/repulsion(|i-j|>=3), BAOAB dt=2 fs, "
                                          "radius graph rebuilt every step, 1024 replicas on one GPU")
     return out
 
+
+# ----------------------------------------------------------------------------------------- force-matching training step
+def training_step_measurement(dev, world, steps=10, warmup=3):
+    """Force-matching training step of the training configuration on every rank: 256 structures x 73 beads per GPU (3.8 A random
+    walk, 20 types), SchNet 3 blocks / 128 / 128 exp-normal functions / 10 A, ``model.train()`` so that the force pass keeps its graph,
+    MSE on forces against N(0,1) targets, gradient all-reduce over the ranks (NCCL; mean), AdamW(lr 1e-4, weight decay 0) — the step
+    of src/mlcg/pl/model.py:113-131 under examples/input_yamls/slurm_example/train.yaml:9.  Returns this rank's
+    (ms per step, ms in the all-reduce per step, last loss)."""
+    import mlcg_b200
+    from mlcg_b200 import nn as bnn
+    from mlcg_b200.distributed import allreduce_gradients
+    rank = int(os.environ.get("RANK", "0"))
+    B, n, T = 256, 73, 20
+    net = make_model(cutoff=10.0, n_types=T).to(dev)        # the same initial weights on every rank
+    model = bnn.GradientsOut(net, "forces").train()
+    gen = torch.Generator().manual_seed(4000 + rank)         # every rank its own structures and targets
+    pos = random_walks(B, n, gen).to(dev)
+    types_ = torch.randint(0, T, (B * n,), generator=gen).to(dev)
+    batch = torch.arange(B).repeat_interleave(n).to(dev)
+    target = torch.randn(B * n, 3, generator=gen).to(dev)
+    n_atoms = torch.full((B,), n, device=dev)
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, weight_decay=0)
+    params = list(net.parameters())
+    ar_events = []
+
+    def step(timed):
+        opt.zero_grad(set_to_none=True)
+        out = model(mlcg_b200.AtomicData(pos=pos.clone(), atom_types=types_, batch=batch, n_atoms=n_atoms))
+        loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], target)
+        loss.backward()
+        if world > 1:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            allreduce_gradients(params)
+            b.record()
+            if timed:
+                ar_events.append((a, b))
+        opt.step()
+        return loss
+
+    for _ in range(warmup):
+        step(False)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        loss = step(True)
+    b.record()
+    torch.cuda.synchronize()
+    from mlcg_b200.backend import get_backend
+    get_backend().check_pending()
+    ar_ms = sum(x.elapsed_time(y) for x, y in ar_events) / steps if ar_events else 0.0
+    return a.elapsed_time(b) / steps, ar_ms, float(loss), B, sum(p.numel() for p in params)
+
+
+def training_cpu_leg(arm, steps=2):
+    """The same step on the host cores with the CPU arm's modules, 64 structures (a quarter of one GPU's batch)."""
+    if arm.kind != "reference":
+        return None
+    ns = arm.ns
+    B, n, T = 64, 73, 20
+    net = make_model(ns, cutoff=10.0, n_types=T)
+    model = ns.GradientsOut(net, "forces").train()
+    gen = torch.Generator().manual_seed(4000)
+    pos, types_ = random_walks(B, n, gen), torch.randint(0, T, (B * n,), generator=gen)
+    batch, target = torch.arange(B).repeat_interleave(n), torch.randn(B * n, 3, generator=gen)
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, weight_decay=0)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        out = model(ns.AtomicData(pos=pos.clone(), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list={}))
+        loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], target)
+        loss.backward()
+        opt.step()
+        return loss
+
+    sec, _ = timed_host(step, steps, 1)
+    return dict(ms_per_step_64_structures=sec * 1e3, structures_per_s=B / sec, cores=arm.cores, kind=arm.kind,
+                sample=f"64 structures x 73 beads per step, {steps} steps after 1 warm-up; {arm.describe()}")
+
+
 # ----------------------------------------------------------------------------------------- GPU arm
+def kernel_work(name, E, P, N, F, R):
+    """Algorithmic (bytes, flops) of one call of a library entry point at the benchmark's sizes: E directed edges, P = E/2
+    unordered pairs, N beads, F filters, R radial functions.  Index arrays at their stored width (int32 rows, int64 pointers)."""
+    if name == "filter_forward":        # d in, one filter row per pair out; two GEMMs per row
+        return P * (4 * F + 4), 2 * P * F * (R + F)
+    if name == "filter_backward":       # d, two index rows, gd; node rows x'[row0], g[row1] from L2; recompute + two backward GEMMs per row
+        return 16 * E + 2 * N * F * 4, 4 * P * F * (R + F)
+    if name == "seg_mul_sum":           # one filter row per pair, neighbour index and pair index per edge, node rows in and out
+        return P * F * 4 + 8 * E + 2 * N * F * 4 + 8 * N, 2 * E * F
+    if name.startswith("gemm_tc"):      # node-sized Linear layers, 128 wide
+        return (2 * N * F + F * F) * 4, 2 * N * F * F
+    if name == "radius_graph_capacity":
+        return 24 * N + 8 * E, 0
+    if name == "pair_plan":
+        return 28 * E + 20 * N, 0
+    if name == "edge_distance":
+        return 12 * E + 12 * N, 0
+    if name == "edge_distance_backward":
+        return 2 * E * 24 + 24 * N, 0
+    return 0, 0
+
+
 def run_ours(args):
     import torch.distributed as dist
     import mlcg_b200
     from mlcg_b200 import nn as bnn
-    from mlcg_b200.backend import KernelProfiler, get_backend
+    from mlcg_b200.backend import get_backend
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -290,7 +558,9 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     B, n = WORKLOAD["structures_per_gpu"], WORKLOAD["beads"]
     pos_h, types_h, batch_h = make_inputs(B, n, WORKLOAD["bead_types"], seed=1000 + rank)   # every rank its own replicas
-    model = bnn.GradientsOut(make_model().to(dev), "forces").eval()
+    net = make_model()
+    state_dict_h = {k: v.detach().clone() for k, v in net.state_dict().items()}
+    model = bnn.GradientsOut(net.to(dev), "forces").eval()
     be = get_backend()
     n_atoms = torch.full((B,), n, device=dev)
     pos_d, types_d, batch_d = pos_h.to(dev), types_h.to(dev), batch_h.to(dev)
@@ -358,14 +628,13 @@ def run_ours(args):
     step_ms = timed_steps()
     ms_total = sum(step_ms)
     be.check_pending()          # status words of the timed steps (edge capacity, tensor-core waits): raises if any is set
-    # ---- the same K steps once more with a CUDA-event pair around every launch of the library (the per-kernel
-    # durations behind `roofline` and `kernels`); kept out of the region above because ~170 event records per step
-    # cost the host about as much as the launches themselves
-    prof = KernelProfiler()
-    be.profiler = prof
-    ms_profiled = sum(timed_steps())
-    stats = prof.summary()
-    be.profiler = None
+    # ---- the same K steps once more, on the same route (one library call per evaluation), with the library's timeline on: a
+    # CUDA-event pair around every kernel-launching entry point, recorded inside the library call (the per-kernel durations
+    # behind `roofline` and `kernels`).  Kept out of the region above because a recorded launch cannot start its set-up under
+    # the tail of the launch before it.
+    be.timeline_begin()
+    ms_recorded = sum(timed_steps())
+    timeline = be.timeline_end()
     clk = clocks.stop()
 
     # ---- end to end through the public API: pinned host inputs in, energies and forces back to the host
@@ -382,12 +651,31 @@ def run_ours(args):
     last = slots[(args.steps - 1) % 2]
     if not (torch.equal(last["e"], e_res.cpu()) and torch.equal(last["f"], f_res.cpu())):
         raise RuntimeError("end-to-end results differ from the device-resident evaluation of the same structures")
+    e_timed, f_timed = e_res.cpu(), f_res.cpu()
     barrier()
 
-    t = torch.tensor([ms_total, e2e_s * 1e3, ms_profiled], dtype=torch.float64, device=dev)
+    t = torch.tensor([ms_total, e2e_s * 1e3, ms_recorded], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms, ms_profiled = float(t[0]), float(t[1]), float(t[2])
+    ms_total, e2e_ms, ms_recorded = float(t[0]), float(t[1]), float(t[2])
+
+    # ---- the training configuration's step, on every rank, with the gradient all-reduce when there are several
+    training = None
+    if not args.no_extras:
+        del flush
+        torch.cuda.empty_cache()
+        bnn.set_edge_capacity(model, None)
+        tr_ms, ar_ms, tr_loss, tr_B, n_params = training_step_measurement(dev, world)
+        tt = torch.tensor([tr_ms, ar_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        training = dict(ms_per_step=float(tt[0]), structures_per_s=world * tr_B / (float(tt[0]) / 1e3), allreduce_ms_per_step=float(tt[1]),
+                        allreduce_bytes=4 * n_params, structures_per_gpu=tr_B, n_gpus=world, loss=tr_loss,
+                        note="256 structures x 73 beads per GPU, SchNet 3 blocks / 128 / 128 expnorm / 10 A, train mode (second-order pass), "
+                             "MSE on forces, gradient all-reduce (mean) over the ranks, AdamW(1e-4); 10 steps after 3 warm-ups, CUDA events, "
+                             "maximum over ranks")
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        bnn.set_edge_capacity(model, int(1.1 * n_edges))
     # the ranks part here: everything below is rank 0's own reporting (no collective may follow)
     if world > 1:
         dist.barrier()
@@ -396,9 +684,6 @@ def run_ours(args):
     if rank != 0:
         return
 
-    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels on this workload, from the
-    # Nsight Compute capture summarised under profiles/ (full-size launches; scaled by the row count for other sizes)
-    ncu_traffic = {"filter_backward": 75.1e6, "filter_forward": 230.5e6, "seg_mul_sum": 343.3e6, "gemm_tc": 39.0e6}
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -407,46 +692,75 @@ def run_ours(args):
     hbm_peak = peaks.get("hbm_gbs", 6650.0)
     tf_peak = peaks.get("bf16_tflops_sustained", 1400.0)
     peak_src = "measured" if peaks else "fallback"
-    top = max(stats.items(), key=lambda kv: kv[1]["ms"])
-    name, st = top
-    per_launch_ms = st["ms"] / max(st["calls"], 1)
-    tensor_kernels = {"gemm": "gemm_kernel<float> (filter-network GEMMs, fp32 FMA)",
-                      "filter_forward": "filter_fwd_pipe_kernel (tcgen05: RBF prologue, 2 GEMMs, tanh, cutoff; one row per unordered pair)",
-                      "filter_backward": "filter_bwd_pipe_kernel (tcgen05: recompute + 4 GEMMs per tile, gather of gW; one row per unordered pair)"}
-    if name in tensor_kernels:
-        achieved = st["flops"] / max(st["ms"], 1e-9) / 1e9            # TFLOP/s of algorithmic (fp32-equivalent) flops
-        roof = dict(kernel=tensor_kernels[name], bound="tensor", achieved=achieved, peak=tf_peak, unit="TFLOP/s", frac=achieved / tf_peak,
-                    traffic=ncu_traffic.get(name, 0) * B / 512 or None, peak_source=f"{peak_src} bf16 sustained", avg_launch_ms=per_launch_ms,
-                    note="algorithmic flops 2*F*(R+F) per evaluated row and GEMM pair (rows = E/2 on a symmetric edge list); the fp32-equivalent "
-                         "mode issues three fp16 products per algorithmic product, so tensor-pipe work is 3x this figure")
-    else:
-        achieved = st["bytes"] / max(st["ms"], 1e-9) / 1e6            # GB/s
-        roof = dict(kernel=name, bound="hbm", achieved=achieved, peak=hbm_peak, unit="GB/s", frac=achieved / hbm_peak,
-                    traffic=ncu_traffic.get(name, 0) * B / 512 or None,
-                    peak_source=f"{peak_src} copy bandwidth", avg_launch_ms=per_launch_ms)
-    seg = stats.get("seg_mul_sum")
-    cfconv = None
-    if seg and seg["ms"] > 0:
-        # algorithmic bytes of the CFConv aggregation per edge: the filter row (4F), the [2,E] int64 indices (16) and the node
-        # tensors read and written once (8F N/E); what the kernel really moves is less, because it reads one filter row per
-        # unordered pair and int32 indices (`unique_GBps`)
-        F, n_nodes = WORKLOAD["filters"], B * n
-        per_edge = 4 * F + 16 + 8 * F * n_nodes / n_edges
-        edges_per_s = seg["calls"] * n_edges / (seg["ms"] / 1e3)
-        gbs = per_edge * edges_per_s / 1e9
-        cfconv = dict(kernel="seg_mul_sum_kernel<float,32,true,true> (CFConv gather * filter, segmented sum; filters stored once per pair)", bound="hbm", achieved=gbs,
-                      peak=hbm_peak, unit="GB/s", frac=gbs / hbm_peak, edges_per_s=edges_per_s, bytes_per_edge=per_edge,
-                      unique_GBps=seg["bytes"] / seg["ms"] / 1e6, traffic=ncu_traffic["seg_mul_sum"] * B / 512, avg_launch_ms=seg["ms"] / seg["calls"])
-    kernels = {k: dict(calls=v["calls"], ms_per_step=v["ms"] / args.steps,
-                       GBps=(v["bytes"] / v["ms"] / 1e6 if v["ms"] > 0 else None),
-                       TFLOPs=(v["flops"] / v["ms"] / 1e9 if v["ms"] > 0 and v["flops"] else None)) for k, v in sorted(stats.items(), key=lambda kv: -kv[1]["ms"])}
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the Nsight Compute captures summarised under
+    # profiles/: one record per kernel with the row count of the captured launch, scaled here to this run's rows
+    try:
+        traffic_table = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))
+    except OSError:
+        traffic_table = {}
+    F, R, N, P = WORKLOAD["filters"], WORKLOAD["num_rbf"], B * n, n_edges // 2
 
-    cpu = None
+    def traffic_of(name):
+        rec = traffic_table.get(name)
+        if not rec:
+            return None, None
+        rows_now = {"pairs": P, "edges": n_edges, "nodes": N}[rec["rows_are"]]
+        return rec["dram_bytes_per_launch"] * rows_now / rec["rows"], rec["source"]
+
+    kernels = {}
+    for name, rec in sorted(timeline.items(), key=lambda kv: -kv[1]["ms"]):
+        nbytes, flops = kernel_work(name, n_edges, P, N, F, R)
+        per_launch = rec["ms"] / rec["calls"]
+        kernels[name] = dict(calls_per_step=rec["calls"] / args.steps, ms_per_step=rec["ms"] / args.steps, ms_per_launch=per_launch,
+                             GBps=(nbytes / per_launch / 1e6 if nbytes else None), TFLOPs=(flops / per_launch / 1e9 if flops else None))
+    tensor_kernels = {"filter_forward": "filter_fwd_pipe_kernel (tcgen05: RBF prologue, 2 GEMMs, tanh, cutoff; one row per unordered pair)",
+                      "filter_backward": "filter_bwd_pipe_kernel (tcgen05: recompute + 4 GEMMs per tile, gather of gW; one row per unordered pair)"}
+    name = next(iter(kernels))
+    k = kernels[name]
+    tr, tr_src = traffic_of(name)
+    if name in tensor_kernels:
+        roof = dict(kernel=tensor_kernels[name], bound="tensor", achieved=k["TFLOPs"], peak=tf_peak, unit="TFLOP/s", frac=k["TFLOPs"] / tf_peak,
+                    traffic=tr, traffic_source=tr_src, peak_source=f"{peak_src} bf16 sustained", avg_launch_ms=k["ms_per_launch"],
+                    share_of_recorded_step=k["ms_per_step"] / (ms_recorded / args.steps),
+                    note="algorithmic flops 2*F*(R+F) per evaluated row and GEMM pair (rows = E/2 on a symmetric edge list: per edge this is the "
+                         "2(F^2+RF) of a backward to the input, or half the forward's); the fp32-equivalent mode issues three fp16 products per "
+                         "algorithmic product, so tensor-pipe work is 3x this figure; duration from CUDA events recorded inside the library call "
+                         "on the timed route")
+    else:
+        roof = dict(kernel=name, bound="hbm", achieved=k["GBps"], peak=hbm_peak, unit="GB/s", frac=(k["GBps"] or 0) / hbm_peak, traffic=tr,
+                    traffic_source=tr_src, peak_source=f"{peak_src} copy bandwidth", avg_launch_ms=k["ms_per_launch"],
+                    share_of_recorded_step=k["ms_per_step"] / (ms_recorded / args.steps))
+    cfconv = None
+    seg = timeline.get("seg_mul_sum")
+    if seg and seg["ms"] > 0:
+        # two figures.  `reference_algorithm_*`: the bytes the reference's formulation of the aggregation moves per edge (a filter
+        # row per directed edge, [2,E] int64 indices, node tensors once) at this kernel's edge rate: can exceed the peak, because
+        # this kernel reads one filter row per unordered pair and int32 indices.  `achieved` / `frac`: the bytes this kernel has to
+        # move (kernel_work) over its duration: its position on the HBM roofline.
+        per_edge = 4 * F + 16 + 8 * F * N / n_edges
+        per_launch = seg["ms"] / seg["calls"]
+        moved, _ = kernel_work("seg_mul_sum", n_edges, P, N, F, R)
+        s_tr, s_src = traffic_of("seg_mul_sum")
+        cfconv = dict(kernel="seg_mul_sum_kernel<float,32,true,true> (CFConv gather * filter, segmented sum; filters stored once per pair)", bound="hbm",
+                      achieved=moved / per_launch / 1e6, peak=hbm_peak, unit="GB/s", frac=moved / per_launch / 1e6 / hbm_peak,
+                      edges_per_s=n_edges / (per_launch / 1e3), reference_algorithm_bytes_per_edge=per_edge,
+                      reference_algorithm_GBps=per_edge * n_edges / per_launch / 1e6, reference_algorithm_frac=per_edge * n_edges / per_launch / 1e6 / hbm_peak,
+                      traffic=s_tr, traffic_source=s_src, avg_launch_ms=per_launch)
+
+    # ---- parity of what was timed + the CPU baseline: the first 64 structures of the timed batch on the host cores
+    cpu = check = None
+    arm = None
     if not args.no_cpu and world == 1:        # the CPU leg is timed at N = 1 only (other ranks would share the host cores)
-        sample_B = 128
-        v, ms, cores = cpu_leg(sample_B, 16, 1)     # about 10 s of host work
-        cpu = dict(value=v, unit="structures/s", cores=cores, kind="port",
-                   sample=f"{sample_B} structures of the same workload per step, 16 steps after 1 warm-up, torch CPU float32 + C radius oracle")
+        arm = CpuArm()
+        sample_B = min(64, B)
+        fn = arm.schnet_evaluator(state_dict_h, n)
+        sl = slice(0, sample_B * n)
+        sec, (e_cpu, f_cpu) = timed_host(lambda: fn(pos_h[sl], types_h[sl], batch_h[sl], sample_B), 12, 1)
+        check = parity(e_timed[:sample_B], f_timed[sl], e_cpu, f_cpu)
+        cpu = dict(value=sample_B / sec, unit="structures/s", cores=arm.cores, kind=arm.kind,
+                   sample=f"the first {sample_B} structures of the timed batch per step, 12 steps after 1 warm-up, radius graph rebuilt each step; {arm.describe()}")
+        if not check["ok"]:
+            raise RuntimeError(f"timed batch differs from the CPU arm beyond the parity bars: {check}")
 
     extras = None
     if not args.no_extras and world == 1:      # side measurements of other kernels and configurations: single-GPU runs only
@@ -456,14 +770,22 @@ def run_ours(args):
             for _ in range(3):
                 step_resident()
             bf16_ms = timed_steps()
+            e_b, f_b = step_resident()
             bnn.set_filter_precision(model, "fp32")
+            rel_rms = float(((f_b.cpu() - f_timed).pow(2).mean() / f_timed.pow(2).mean()).sqrt())
             del flush
             torch.cuda.empty_cache()
-            extras = extra_measurements(dev, hbm_peak)
+            arm = arm or CpuArm()
+            extras = extra_measurements(dev, hbm_peak, arm)
             extras["bf16_filter_mode"] = dict(ms_per_step=sum(bf16_ms) / len(bf16_ms), structures_per_s=B / (sum(bf16_ms) / len(bf16_ms) / 1e3),
+                                              force_rel_rms_vs_fp32_mode=rel_rms,
                                               note="same workload, filter-network GEMMs with bf16 operands (one product, tanh.approx)")
+            if training is not None:
+                training["cpu"] = training_cpu_leg(arm)
         except Exception as exc:   # the headline line is still printed
             extras = {"error": repr(exc)}
+    if training is not None:
+        extras = dict(extras or {}, training_step_256x73=training)
 
     # kernels of the library per evaluation on the route the timed region takes (one library call for the model): radius graph 7
     # (cells, count, three scan kernels, clamp to the capacity, fill), reverse-edge map / pair selection / pair index 5 (count of
@@ -479,11 +801,12 @@ def run_ours(args):
     line = dict(metric=METRIC, value=value, unit="structures/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
                 ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
                 config=dict(WORKLOAD, edges_per_gpu=n_edges, edge_capacity=int(1.1 * n_edges) + int(1.1 * n_edges) % 2, global_structures=world * B, parallelism=f"replicas x{world}, no collective",
-                            kernel_timing="second pass over the same K steps with a CUDA-event pair around every library launch "
-                                          "(the package then issues its kernels one by one instead of one library call per evaluation)"),
+                            kernel_timing="second pass over the same K steps on the same route (one library call per evaluation) with the "
+                                          "library's timeline on: a CUDA-event pair around every kernel-launching entry point"),
                 e2e=dict(value=world * B * args.steps / (e2e_ms / 1e3), unit="structures/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
-                gpu_launches=launches_timed, gpu_launches_kernel_timing_pass=prof.total_launches, ms_per_step_median=sorted(step_ms)[len(step_ms) // 2], ms_per_step_min=min(step_ms),
-                ms_per_step_with_kernel_events=ms_profiled / args.steps, roofline=roof, cfconv_roofline=cfconv, other_kernels=extras, cpu_baseline=cpu, clocks=clk, kernels=kernels,
+                gpu_launches=launches_timed, ms_per_step_median=sorted(step_ms)[len(step_ms) // 2], ms_per_step_min=min(step_ms),
+                ms_per_step_with_kernel_events=ms_recorded / args.steps, roofline=roof, cfconv_roofline=cfconv, parity_of_timed_batch=check,
+                other_kernels=extras, cpu_baseline=cpu, clocks=clk, kernels=kernels,
                 edges_per_s=world * n_edges * args.steps / (ms_total / 1e3))
     print(json.dumps(line))
 
@@ -495,8 +818,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--structures", type=int, default=None, help="structures per GPU (default 512; smaller values are for profiler captures)")
-    ap.add_argument("--no-extras", action="store_true", help="skip the stand-alone radius-graph and prior-kernel measurements")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiler captures)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the other configurations (radius graph, priors, dynamics, training step)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU arm: no baseline and no parity check of the timed batch (profiler captures)")
     args = ap.parse_args()
     if args.structures:
         WORKLOAD["structures_per_gpu"] = args.structures

@@ -42,6 +42,18 @@ const char *mlcgb_strerror(int code);
 int mlcgb_last_cuda_error(void); /* cudaError_t of the last failed launch on this host thread */
 int mlcgb_version(void);
 
+/* Device time per entry point, without a profiler.  No counterpart in the reference (mlcg times whole steps on the host).
+ * Between mlcgb_timeline_begin and mlcgb_timeline_end, every kernel-launching entry point called from the same host thread
+ * brackets its launches with a CUDA event pair on its stream (the events are created on first use and kept: host-side
+ * objects, no device memory).  mlcgb_timeline_end waits for the recorded events and returns the number of distinct entry
+ * points seen (or a negative code); mlcgb_timeline_entry(i, ...) then gives name, number of calls and summed milliseconds of
+ * the i-th.  Entry points that only sequence others (mlcgb_interaction_*, mlcgb_schnet_eval*) are not recorded themselves:
+ * their parts are.  A recorded launch cannot overlap its set-up with the tail of the launch before it, so a recorded step
+ * is a little slower than an unrecorded one. */
+int mlcgb_timeline_begin(void);
+int mlcgb_timeline_end(void);
+int mlcgb_timeline_entry(int index, const char **name /* out: static string */, int64_t *calls, double *ms);
+
 /* ------------------------------------------------------------------------------------------------
  * Radius graph.  Replaces torch_cluster.radius_graph as called at
  * src/mlcg/neighbor_list/torch_impl.py:216-224 and mlcg::radius_cuda
@@ -49,7 +61,8 @@ int mlcgb_version(void);
  * count: `count` builds the per-structure cell lists in the workspace, writes deg[N] and the
  * exclusive prefix sum offsets[N+1] (offsets[N] = E); `fill` writes the edges, centre-major with
  * neighbours ascending, which is the order both reference back ends produce.
- * The pair test is ((dx*dx + dy*dy) + dz*dz) < (T)(r*r) with every operation rounded separately.
+ * The pair test is fma(dz, dz, fma(dy, dy, dx*dx)) < (T)(r*r): the loop of radius.cu:126-130 as nvcc contracts it, which is
+ * what the reference's compiled kernel decides by (compared with it pair by pair, tests/test_gpu_radius_reference.py).
  * ---------------------------------------------------------------------------------------------- */
 int mlcgb_batch_to_ptr(const int64_t *batch, int64_t N, int64_t B, int64_t *ptr /* [B+1] */, void *stream);
 /* radius.py:64-75 (bucketize of arange(B+1) into the sorted batch vector). */

@@ -6,6 +6,7 @@ second derivatives) and the classical prior terms, behind the Python interface o
 ``include/mlcg_b200.h``); there is no CPU path.
 """
 from . import nn  # noqa: F401
+from . import ops  # noqa: F401  (registers torch.ops.mlcg.radius_cuda / exclusion_pair_to_ptr)
 from .data import AtomicData  # noqa: F401
 from .graphed import GraphedForceField  # noqa: F401
 from .neighbor_list import (atomic_data2neighbor_list, exclusion_pair_to_ptr, make_neighbor_list, radius_cuda,  # noqa: F401

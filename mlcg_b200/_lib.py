@@ -39,6 +39,9 @@ SIGNATURES = {
     "mlcgb_strerror": (ctypes.c_char_p, [c_int]),
     "mlcgb_last_cuda_error": (c_int, []),
     "mlcgb_version": (c_int, []),
+    "mlcgb_timeline_begin": (c_int, []),
+    "mlcgb_timeline_end": (c_int, []),
+    "mlcgb_timeline_entry": (c_int, [c_int, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(c_i64), ctypes.POINTER(c_dbl)]),
     "mlcgb_batch_to_ptr": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp]),
     "mlcgb_radius_workspace_bytes": (c_sz, [c_i64, c_i64, c_int]),
     "mlcgb_radius_count": (c_int, [c_vp, c_int, c_vp, c_i64, c_i64, c_dbl, c_i64, c_int, c_int, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]),

@@ -1,9 +1,8 @@
 """Tensor-level wrappers over the C ABI: allocate outputs with torch, pass raw pointers and the current stream.
 
 Every operator of the package goes through the object returned by :func:`get_backend`.  The only
-back end shipped is :class:`CudaBackend`; it refuses tensors that are not on a CUDA device.
-(:func:`set_backend` exists so that the test-suite can check the autograd wiring on a machine
-without a GPU by substituting reference implementations of the same primitives.)
+back end is :class:`CudaBackend`; it refuses tensors that are not on a CUDA device, and constructing it
+raises if ``libmlcg_b200.so`` is missing.
 """
 import ctypes
 from dataclasses import dataclass
@@ -162,6 +161,23 @@ class CudaBackend:
             for st, _ in pending:
                 st.zero_()
             _raise_for_status(*bad[0])
+
+    # ------------------------------------------------------------------ device time per entry point
+    def timeline_begin(self):
+        """Start recording a CUDA event pair around every kernel-launching library call made from this thread."""
+        _lib.check(self.lib.mlcgb_timeline_begin(), "timeline_begin")
+
+    def timeline_end(self):
+        """Stop recording, wait for the events and return ``{entry point: {"calls": n, "ms": total}}``."""
+        n = self.lib.mlcgb_timeline_end()
+        if n < 0:
+            _lib.check(n, "timeline_end")
+        out = {}
+        name, calls, ms = ctypes.c_char_p(), ctypes.c_int64(), ctypes.c_double()
+        for i in range(n):
+            _lib.check(self.lib.mlcgb_timeline_entry(i, ctypes.byref(name), ctypes.byref(calls), ctypes.byref(ms)), "timeline_entry")
+            out[name.value.decode()] = {"calls": int(calls.value), "ms": float(ms.value)}
+        return out
 
     def _run(self, name, fn, args, what=None, launches=1, nbytes=0, flops=0):
         prof = self.profiler
@@ -711,10 +727,3 @@ def get_backend():
     if _backend is None:
         _backend = CudaBackend()   # raises ExtensionMissing if the library is absent
     return _backend
-
-
-def set_backend(be):
-    """Replace the back end (test harness only). Returns the previous one."""
-    global _backend
-    old, _backend = _backend, be
-    return old

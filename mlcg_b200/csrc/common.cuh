@@ -21,6 +21,19 @@ inline int check_launch() {
     return MLCGB_OK;
 }
 
+// Device time per entry point, for hosts that want to know where an evaluation's time goes without a profiler attached:
+// while the calling host thread has a timeline open (mlcgb_timeline_begin), every kernel-launching entry point brackets its
+// launches with a CUDA event pair on its stream (only the outermost such entry point of a nest records).  Off, the scope
+// costs one thread-local read.
+struct TimelineScope {
+    int slot;
+    cudaStream_t st;
+    TimelineScope(const char *name, void *stream);
+    ~TimelineScope();
+    TimelineScope(const TimelineScope &) = delete;
+    TimelineScope &operator=(const TimelineScope &) = delete;
+};
+
 // Programmatic dependent launch: a kernel launched this way may start (on SMs the previous kernel of the stream has
 // already left) before that kernel has finished as a whole; it runs its own set-up — weight tiles, barriers, tensor-memory
 // allocation, nothing that depends on the previous kernel — and calls pdl_wait() before it touches any activation.
@@ -57,19 +70,25 @@ template <typename T> struct Vec4;
 template <> struct Vec4<float> { using type = float4; };
 template <> struct Vec4<double> { using type = double4; };
 
-// Explicitly rounded arithmetic: the pair test must not be contracted into fused multiply-adds,
-// so that the host oracle (compiled with -ffp-contract=off) takes the same decision bit for bit.
+// Explicitly rounded arithmetic for the pair test.  The squared distance is evaluated the way the reference's compiled
+// kernels evaluate it: `dist += diff * diff` over the three coordinates (src/opt_radius/mlcg_opt_radius/radius.cu:126-130,
+// and the same loop in torch_cluster's radius kernel), which nvcc contracts into fused multiply-adds by default:
+//   d2 = fma(dz, dz, fma(dy, dy, dx * dx)).
+// Writing the roundings out (instead of leaving the contraction to the compiler) fixes the decision for every pair,
+// including pairs within one rounding of the cutoff; the host oracle evaluates the same expression with libm's fma.
 __device__ __forceinline__ float mul_rn(float a, float b) { return __fmul_rn(a, b); }
 __device__ __forceinline__ float add_rn(float a, float b) { return __fadd_rn(a, b); }
 __device__ __forceinline__ double mul_rn(double a, double b) { return __dmul_rn(a, b); }
 __device__ __forceinline__ double add_rn(double a, double b) { return __dadd_rn(a, b); }
 __device__ __forceinline__ float sub_rn(float a, float b) { return __fsub_rn(a, b); }
 __device__ __forceinline__ double sub_rn(double a, double b) { return __dsub_rn(a, b); }
+__device__ __forceinline__ float fma_rn(float a, float b, float c) { return __fmaf_rn(a, b, c); }
+__device__ __forceinline__ double fma_rn(double a, double b, double c) { return __fma_rn(a, b, c); }
 
 template <typename T>
 __device__ __forceinline__ T dist2_rn(T xi, T yi, T zi, T xj, T yj, T zj) {
     const T dx = sub_rn(xj, xi), dy = sub_rn(yj, yi), dz = sub_rn(zj, zi);
-    return add_rn(add_rn(mul_rn(dx, dx), mul_rn(dy, dy)), mul_rn(dz, dz));
+    return fma_rn(dz, dz, fma_rn(dy, dy, mul_rn(dx, dx)));
 }
 
 __device__ __forceinline__ unsigned lanemask_lt() {

@@ -309,6 +309,7 @@ extern "C" {
 
 int mlcgb_seg_mul_sum(const void *a, const void *V, int dtype, const int64_t *ptr, const int32_t *nbr, const int32_t *eperm,
                       int64_t N, int64_t E, int64_t F, void *out, void *stream) {
+    TimelineScope timeline_scope("seg_mul_sum", stream);
     if (N < 0 || E < 0 || F <= 0) return MLCGB_E_ARG;
     if (N == 0) return MLCGB_OK;
     if (!ptr || !out || (E > 0 && (!a || !V || !nbr))) return MLCGB_E_ARG;
@@ -317,6 +318,7 @@ int mlcgb_seg_mul_sum(const void *a, const void *V, int dtype, const int64_t *pt
 
 int mlcgb_edge_mul(const void *a, const void *b, int dtype, const int32_t *ia, const int32_t *ib, int64_t E, int64_t F, void *V,
                    void *stream) {
+    TimelineScope timeline_scope("edge_mul", stream);
     if (E < 0 || F <= 0) return MLCGB_E_ARG;
     if (E == 0) return MLCGB_OK;
     if (!a || !b || !ia || !ib || !V) return MLCGB_E_ARG;
@@ -333,6 +335,7 @@ int mlcgb_edge_mul(const void *a, const void *b, int dtype, const int32_t *ia, c
 
 int mlcgb_edge_diff(const void *pos, int dtype, const int32_t *row0, const int32_t *row1, int64_t E, int64_t N, void *dr,
                     int32_t *status, void *stream) {
+    TimelineScope timeline_scope("edge_diff", stream);
     if (E < 0 || N < 0 || !status) return MLCGB_E_ARG;
     if (E == 0) return MLCGB_OK;
     if (!pos || !row0 || !row1 || !dr) return MLCGB_E_ARG;
@@ -344,6 +347,7 @@ int mlcgb_edge_diff(const void *pos, int dtype, const int32_t *row0, const int32
 
 int mlcgb_node_scatter_diff(const void *g, int dtype, const int64_t *ptr_in, const int32_t *perm_in, const int64_t *ptr_out,
                             const int32_t *perm_out, int64_t N, int64_t E, void *out, void *stream) {
+    TimelineScope timeline_scope("node_scatter_diff", stream);
     if (N < 0 || E < 0) return MLCGB_E_ARG;
     if (N == 0) return MLCGB_OK;
     if (!ptr_in || !ptr_out || !out || (E > 0 && !g)) return MLCGB_E_ARG;
@@ -354,6 +358,7 @@ int mlcgb_node_scatter_diff(const void *g, int dtype, const int64_t *ptr_in, con
 }
 
 int mlcgb_segment_sum(const void *x, int dtype, const int64_t *ptr, int64_t B, void *out, void *stream) {
+    TimelineScope timeline_scope("segment_sum", stream);
     if (B < 0) return MLCGB_E_ARG;
     if (B == 0) return MLCGB_OK;
     if (!x || !ptr || !out) return MLCGB_E_ARG;
@@ -364,6 +369,7 @@ int mlcgb_segment_sum(const void *x, int dtype, const int64_t *ptr, int64_t B, v
 }
 
 int mlcgb_row_scale(const void *a, const void *c, int dtype, int64_t E, int64_t F, void *out, void *stream) {
+    TimelineScope timeline_scope("row_scale", stream);
     if (E < 0 || F <= 0) return MLCGB_E_ARG;
     if (E == 0) return MLCGB_OK;
     if (!a || !c || !out) return MLCGB_E_ARG;
@@ -378,6 +384,7 @@ int mlcgb_row_scale(const void *a, const void *c, int dtype, int64_t E, int64_t 
 }
 
 int mlcgb_row_dot(const void *a, const void *b, int dtype, int64_t E, int64_t F, void *out, void *stream) {
+    TimelineScope timeline_scope("row_dot", stream);
     if (E < 0 || F <= 0) return MLCGB_E_ARG;
     if (E == 0) return MLCGB_OK;
     if (!a || !b || !out) return MLCGB_E_ARG;
@@ -393,6 +400,7 @@ int mlcgb_row_dot(const void *a, const void *b, int dtype, int64_t E, int64_t F,
 
 int mlcgb_edge_distance(const void *pos, int dtype, const int32_t *row0, const int32_t *row1, int64_t E, int64_t N, void *d,
                         int32_t *status, void *stream) {
+    TimelineScope timeline_scope("edge_distance", stream);
     if (E < 0 || N < 0 || !status) return MLCGB_E_ARG;
     if (E == 0) return MLCGB_OK;
     if (!pos || !row0 || !row1 || !d) return MLCGB_E_ARG;
@@ -405,6 +413,7 @@ int mlcgb_edge_distance(const void *pos, int dtype, const int32_t *row0, const i
 int mlcgb_edge_distance_backward(const void *pos, const void *g, const void *d, int dtype, const int32_t *row0, const int32_t *row1,
                                  const int64_t *ptr_in, const int32_t *perm_in, const int64_t *ptr_out, const int32_t *perm_out,
                                  int64_t N, int64_t E, void *gpos, void *stream) {
+    TimelineScope timeline_scope("edge_distance_backward", stream);
     if (N < 0 || E < 0) return MLCGB_E_ARG;
     if (N == 0) return MLCGB_OK;
     if (!ptr_in || !ptr_out || !gpos || (E > 0 && (!pos || !g || !d || !row0 || !row1))) return MLCGB_E_ARG;

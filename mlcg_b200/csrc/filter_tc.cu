@@ -701,6 +701,7 @@ extern "C" int mlcgb_filter_forward_counted(const void *d, int64_t E, const int6
                                             const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper,
                                             const void *A1, const void *b1, const void *A2, int64_t F, int precision, void *W,
                                             int32_t *status, void *stream) {
+    TimelineScope timeline_scope("filter_forward", stream);
     if (int rc = check_spec(rbf, 0)) return rc;
     if (E < 0 || !status || (precision != 0 && precision != 1) || (conv_cutoff_kind != 0 && conv_cutoff_kind != 1)) return MLCGB_E_ARG;
     if (F != kF || rbf->num_rbf > 128) return MLCGB_E_LIMIT;
@@ -728,6 +729,7 @@ extern "C" int mlcgb_filter_forward_counted(const void *d, int64_t E, const int6
 extern "C" int mlcgb_filter_forward(const void *d, int64_t E, const int32_t *sel, const int32_t *twin, const mlcgb_rbf_spec *rbf,
                                     int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1,
                                     const void *A2, int64_t F, int precision, void *W, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("filter_forward", stream);
     return mlcgb_filter_forward_counted(d, E, nullptr, sel, twin, rbf, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, F, precision, W,
                                         status, stream);
 }
@@ -737,6 +739,7 @@ extern "C" int mlcgb_filter_backward_counted(const void *d, int64_t E, const int
                                              const void *A1, const void *b1, const void *A2, int64_t F, int precision,
                                              const int32_t *row0, const int32_t *row1, const void *xl, const void *gagg, int64_t N,
                                              void *gd, int accumulate, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("filter_backward", stream);
     if (int rc = check_spec(rbf, 1)) return rc;
     if (E < 0 || N < 0 || !status || (precision != 0 && precision != 1) || (conv_cutoff_kind != 0 && conv_cutoff_kind != 1)) return MLCGB_E_ARG;
     if (F != kF || rbf->num_rbf > 128) return MLCGB_E_LIMIT;
@@ -771,6 +774,7 @@ extern "C" int mlcgb_filter_backward(const void *d, int64_t E, const int32_t *se
                                      int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1,
                                      const void *A2, int64_t F, int precision, const int32_t *row0, const int32_t *row1, const void *xl,
                                      const void *gagg, int64_t N, void *gd, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("filter_backward", stream);
     return mlcgb_filter_backward_counted(d, E, nullptr, sel, twin, rbf, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, F, precision,
                                          row0, row1, xl, gagg, N, gd, 0, status, stream);
 }

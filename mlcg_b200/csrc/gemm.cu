@@ -112,6 +112,7 @@ size_t mlcgb_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, int
 
 int mlcgb_gemm(int mode, const void *A, const void *B, const void *bias, int dtype, int64_t M, int64_t N, int64_t K, void *C,
                void *workspace, size_t workspace_bytes, void *stream) {
+    TimelineScope timeline_scope("gemm", stream);
     if (mode < 0 || mode > 2 || M < 0 || N < 0 || K < 0) return MLCGB_E_ARG;
     if (M == 0 || N == 0) return MLCGB_OK;
     if (!C || (K > 0 && (!A || !B))) return MLCGB_E_ARG;

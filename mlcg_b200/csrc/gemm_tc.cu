@@ -719,6 +719,7 @@ extern "C" {
 
 int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias, const void *aux, int epilogue, int64_t M, int64_t N,
                         int64_t K, void *C, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("gemm_tc_fused", stream);
     if ((mode != 0 && mode != 1) || epilogue < 0 || epilogue > 4 || !status) return MLCGB_E_ARG;
     if ((epilogue == kEpiAdd || epilogue == kEpiTanhGrad || epilogue == kProTanhGradVec) && !aux) return MLCGB_E_ARG;
     if (!mlcgb_gemm_tc_supported(mode, M, N, K)) return MLCGB_E_LIMIT;
@@ -730,6 +731,7 @@ int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias
 
 int mlcgb_gemm_tc_tn_colsum(const void *A, const void *B, int64_t K, int64_t M, int64_t N, void *C, void *colsum, void *workspace,
                             size_t workspace_bytes, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("gemm_tc_tn_colsum", stream);
     if (!A || !B || !C || !colsum || !status) return MLCGB_E_ARG;
     if (!mlcgb_gemm_tc_supported(2, M, N, K) || (N & 3) != 0 || ((uintptr_t)B & 15) != 0) return MLCGB_E_LIMIT;
     const int parts = tn_parts(K);
@@ -763,6 +765,7 @@ size_t mlcgb_gemm_tc_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K) 
 
 int mlcgb_gemm_tc(int mode, const void *A, const void *B, const void *bias, int64_t M, int64_t N, int64_t K, void *C, void *workspace,
                   size_t workspace_bytes, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("gemm_tc", stream);
     if (!A || !B || !C || !status) return MLCGB_E_ARG;
     if (!mlcgb_gemm_tc_supported(mode, M, N, K)) return MLCGB_E_LIMIT;
     auto st = (cudaStream_t)stream;

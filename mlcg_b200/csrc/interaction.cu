@@ -201,7 +201,10 @@ int mlcgb_schnet_eval_counted(const void *pos, const int64_t *types, const int64
     float *d = ws + lay.d;
     int rc = mlcgb_edge_distance(pos, MLCGB_F32, row0, row1, E, N, d, status, stream);
     if (rc) return rc;
-    launch_pdl(embedding_rows_kernel, dim3(grid_for(N * (H >> 2), 256)), dim3(256), 0, st, (const float *)w->embedding, types, N, H, w->num_types, ws + lay.x[0], status);
+    {
+        TimelineScope timeline_scope("embedding", stream);
+        launch_pdl(embedding_rows_kernel, dim3(grid_for(N * (H >> 2), 256)), dim3(256), 0, st, (const float *)w->embedding, types, N, H, w->num_types, ws + lay.x[0], status);
+    }
     int cur = 0;
     for (int64_t l = 0; l < L; l++) {
         const mlcgb_schnet_block &bw = w->blocks[l];
@@ -216,7 +219,10 @@ int mlcgb_schnet_eval_counted(const void *pos, const int64_t *types, const int64
     // output network: tanh(x W^T + b) . w_out (+ b_out), summed per structure
     rc = mlcgb_gemm_tc_fused(0, ws + lay.x[cur], w->head_W, w->head_b, nullptr, 1, N, Wh, H, ws + lay.ah, status, stream);
     if (rc) return rc;
-    launch_pdl(head_out_kernel, dim3(grid_for(N * 32, 256)), dim3(256), 0, st, (const float *)(ws + lay.ah), (const float *)w->head_out, (const float *)w->head_out_b, N, Wh, ws + lay.en);
+    {
+        TimelineScope timeline_scope("head_out", stream);
+        launch_pdl(head_out_kernel, dim3(grid_for(N * 32, 256)), dim3(256), 0, st, (const float *)(ws + lay.ah), (const float *)w->head_out, (const float *)w->head_out_b, N, Wh, ws + lay.en);
+    }
     rc = mlcgb_segment_sum(ws + lay.en, MLCGB_F32, struct_ptr, B, energy, stream);
     if (rc || !grad_pos) return rc ? rc : check_launch();
 

@@ -40,6 +40,7 @@ extern "C" {
 
 int mlcgb_langevin_first_half(void *x, void *v, const void *f, const void *masses, const void *beta_mass_ratio, const void *noise, int dtype,
                               int64_t N, double dt, double vscale, double noisescale, void *stream) {
+    TimelineScope timeline_scope("langevin_first_half", stream);
     if (N < 0) return MLCGB_E_ARG;
     if (N == 0) return MLCGB_OK;
     if (!x || !v || !f || !masses || !beta_mass_ratio || !noise) return MLCGB_E_ARG;
@@ -53,6 +54,7 @@ int mlcgb_langevin_first_half(void *x, void *v, const void *f, const void *masse
 }
 
 int mlcgb_langevin_second_half(void *v, const void *f, const void *masses, int dtype, int64_t N, double dt, void *stream) {
+    TimelineScope timeline_scope("langevin_second_half", stream);
     if (N < 0) return MLCGB_E_ARG;
     if (N == 0) return MLCGB_OK;
     if (!v || !f || !masses) return MLCGB_E_ARG;

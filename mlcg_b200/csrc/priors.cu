@@ -175,6 +175,7 @@ using namespace mlcgb;
 extern "C" int mlcgb_prior_terms(int kind, const void *pos, int dtype, const int64_t *mapping, const int64_t *mapping_batch,
                                  const void *params, int n_params, int64_t M, int64_t N, int64_t B, void *energy, void *grad,
                                  int32_t *status, void *stream) {
+    TimelineScope timeline_scope("prior_terms", stream);
     if (kind < 0 || kind > 3 || M < 0 || N < 0 || B < 0 || !status) return MLCGB_E_ARG;
     if (M == 0) return MLCGB_OK;
     if (!pos || !mapping || !mapping_batch || !params || !energy) return MLCGB_E_ARG;

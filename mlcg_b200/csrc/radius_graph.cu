@@ -730,6 +730,7 @@ using namespace mlcgb;
 extern "C" {
 
 int mlcgb_batch_to_ptr(const int64_t *batch, int64_t N, int64_t B, int64_t *ptr, void *stream) {
+    TimelineScope timeline_scope("batch_to_ptr", stream);
     if (N < 0 || B < 0 || !ptr || (N > 0 && !batch)) return MLCGB_E_ARG;
     batch_to_ptr_kernel<<<(unsigned)((B + 1 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(batch, N, B, ptr);
     return check_launch();
@@ -760,12 +761,14 @@ static int radius_count_impl(const void *pos, int dtype, const int64_t *ptr, int
 int mlcgb_radius_count(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn, int loop,
                        int rule, void *workspace, size_t workspace_bytes, int32_t *deg, int64_t *offsets, int32_t *status,
                        void *stream) {
+    TimelineScope timeline_scope("radius_count", stream);
     return radius_count_impl(pos, dtype, ptr, N, B, r, max_nn, loop, rule, workspace, workspace_bytes, deg, offsets, status, stream, Exclusion{});
 }
 
 int mlcgb_radius_count_excl(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r, int64_t max_nn, int loop,
                             const int64_t *exclude_pair_xs, const int64_t *ptr_exclude_pair_xs, void *workspace, size_t workspace_bytes,
                             int32_t *deg, int64_t *offsets, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("radius_count", stream);
     if (!exclude_pair_xs != !ptr_exclude_pair_xs) return MLCGB_E_ARG;
     Exclusion ex;
     ex.xs = exclude_pair_xs;
@@ -791,6 +794,7 @@ int mlcgb_radius_fill(const void *pos, int dtype, const int64_t *ptr, int64_t N,
                       const void *workspace, size_t workspace_bytes, const int64_t *offsets, int64_t E, int64_t *edge_index,
                       void *distance, int64_t *mapping_batch, int32_t *row0_i32, int32_t *row1_i32, int32_t *status,
                       void *stream) {
+    TimelineScope timeline_scope("radius_fill", stream);
     return radius_fill_impl(pos, dtype, ptr, N, B, r, loop, workspace, workspace_bytes, offsets, E, edge_index, distance, mapping_batch,
                             row0_i32, row1_i32, status, stream, Exclusion{});
 }
@@ -799,6 +803,7 @@ int mlcgb_radius_fill_excl(const void *pos, int dtype, const int64_t *ptr, int64
                            const int64_t *exclude_pair_xs, const int64_t *ptr_exclude_pair_xs, const void *workspace,
                            size_t workspace_bytes, const int64_t *offsets, int64_t E, int64_t *edge_index, void *distance,
                            int64_t *mapping_batch, int32_t *row0_i32, int32_t *row1_i32, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("radius_fill", stream);
     if (!exclude_pair_xs != !ptr_exclude_pair_xs) return MLCGB_E_ARG;
     Exclusion ex;
     ex.xs = exclude_pair_xs;
@@ -809,6 +814,7 @@ int mlcgb_radius_fill_excl(const void *pos, int dtype, const int64_t *ptr, int64
 
 int mlcgb_edge_twin(const int32_t *row0, const int32_t *row1, const int64_t *offsets, int64_t E, int64_t N, int32_t *twin,
                     int32_t *status, void *stream) {
+    TimelineScope timeline_scope("edge_twin", stream);
     if (E < 0 || N < 0 || !status) return MLCGB_E_ARG;
     if (E == 0) return MLCGB_OK;
     if (!row0 || !row1 || !offsets || !twin) return MLCGB_E_ARG;
@@ -823,6 +829,7 @@ size_t mlcgb_pair_plan_workspace_bytes(int64_t N) {
 
 int mlcgb_pair_plan(const int32_t *row0, const int32_t *row1, const int64_t *offsets, int64_t E, int64_t N, void *workspace,
                     size_t workspace_bytes, int32_t *twin, int32_t *sel, int32_t *pair_of, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("pair_plan", stream);
     if (E < 0 || N < 0 || (E & 1) || !status) return MLCGB_E_ARG;
     if (E == 0) return MLCGB_OK;
     if (!row0 || !row1 || !offsets || !twin || !sel || !pair_of || !workspace) return MLCGB_E_ARG;
@@ -846,6 +853,7 @@ size_t mlcgb_radius_pbc_workspace_bytes(int64_t N) {
 int mlcgb_radius_pbc_count(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, const void *cells, const int32_t *repeats,
                            double r, int64_t max_nn, int loop, void *workspace, size_t workspace_bytes, int32_t *deg, int64_t *offsets,
                            int32_t *status, void *stream) {
+    TimelineScope timeline_scope("radius_pbc_count", stream);
     if (N < 0 || B < 0 || max_nn < 0 || !offsets || !status || !ptr || !workspace) return MLCGB_E_ARG;
     if (N >= (int64_t)1 << 31) return MLCGB_E_LIMIT;
     auto st = (cudaStream_t)stream;
@@ -873,6 +881,7 @@ int mlcgb_radius_pbc_fill(const void *pos, int dtype, const int64_t *ptr, int64_
                           double r, int64_t max_nn, int loop, const void *workspace, size_t workspace_bytes, const int64_t *offsets,
                           int64_t E, int64_t *edge_index, void *cell_shifts, void *distance, int64_t *mapping_batch, int32_t *status,
                           void *stream) {
+    TimelineScope timeline_scope("radius_pbc_fill", stream);
     if (N < 0 || B < 0 || E < 0 || max_nn < 0 || !offsets || !status || !ptr || !workspace) return MLCGB_E_ARG;
     if (E == 0 || N == 0) return MLCGB_OK;
     if (!pos || !cells || !repeats || !edge_index || !cell_shifts) return MLCGB_E_ARG;
@@ -889,6 +898,7 @@ int mlcgb_radius_pbc_fill(const void *pos, int dtype, const int64_t *ptr, int64_
 }
 
 int mlcgb_pair_index(const int32_t *sel, const int32_t *twin, int64_t P, int32_t *pair_of, void *stream) {
+    TimelineScope timeline_scope("pair_index", stream);
     if (P < 0) return MLCGB_E_ARG;
     if (P == 0) return MLCGB_OK;
     if (!sel || !twin || !pair_of) return MLCGB_E_ARG;
@@ -939,6 +949,7 @@ extern "C" int mlcgb_radius_graph_capacity(const void *pos, int dtype, const int
                                            int loop, int rule, void *workspace, size_t workspace_bytes, int32_t *deg, int64_t *offsets,
                                            int64_t capacity, int64_t *edge_index, int32_t *row0_i32, int32_t *row1_i32,
                                            int64_t *counts, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("radius_graph_capacity", stream);
     if (capacity < 0 || !counts || (!edge_index && (!row0_i32 || !row1_i32))) return MLCGB_E_ARG;
     if (N <= 0 || B <= 0) return MLCGB_E_ARG;
     int rc = mlcgb_radius_count(pos, dtype, ptr, N, B, r, max_nn, loop, rule, workspace, workspace_bytes, deg, offsets, status, stream);
@@ -956,6 +967,7 @@ extern "C" int mlcgb_radius_graph_capacity(const void *pos, int dtype, const int
 extern "C" int mlcgb_radius_graph_static(const void *pos, int dtype, const int64_t *ptr, int64_t N, int64_t B, double r,
                                          int64_t max_nn, int loop, int rule, int32_t *deg, int64_t *offsets, int64_t capacity,
                                          int64_t *edge_index, int64_t *n_edges_host, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("radius_graph_static", stream);
     if (N < 0 || B < 0 || max_nn < 0 || capacity < 0 || !offsets || !status || !ptr || !n_edges_host) return MLCGB_E_ARG;
     if (dtype != MLCGB_F32 && dtype != MLCGB_F64) return MLCGB_E_ARG;
     if (N > kStaticMaxPoints || B > kStaticMaxStructures) return MLCGB_E_LIMIT;   // beyond the built-in scratch

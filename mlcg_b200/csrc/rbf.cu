@@ -45,6 +45,7 @@ using namespace mlcgb;
 extern "C" {
 
 int mlcgb_rbf_expand(const void *d, int dtype, int64_t E, const mlcgb_rbf_spec *spec, int order, void *out, void *stream) {
+    TimelineScope timeline_scope("rbf_expand", stream);
     if (int rc = check_spec(spec, order)) return rc;
     if (E < 0) return MLCGB_E_ARG;
     if (E == 0) return MLCGB_OK;
@@ -65,6 +66,7 @@ int mlcgb_rbf_expand(const void *d, int dtype, int64_t E, const mlcgb_rbf_spec *
 
 int mlcgb_rbf_contract(const void *d, const void *G, int dtype, int64_t E, const mlcgb_rbf_spec *spec, int order, void *s_out,
                        void *stream) {
+    TimelineScope timeline_scope("rbf_contract", stream);
     if (int rc = check_spec(spec, order)) return rc;
     if (E < 0) return MLCGB_E_ARG;
     if (E == 0) return MLCGB_OK;

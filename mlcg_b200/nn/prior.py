@@ -13,7 +13,6 @@ import torch
 from ..backend import get_backend
 
 KIND_BOND, KIND_ANGLE, KIND_DIHEDRAL, KIND_REPULSION = 0, 1, 2, 3
-_PARAM_CACHE = "_mlcgb_prior_params"
 
 
 class _PriorEnergy(torch.autograd.Function):
@@ -47,18 +46,61 @@ def _table_from_statistics(statistics: Dict, order: int, field: str) -> torch.Te
     return table
 
 
-# differentiable torch restatements of the features, used only when second derivatives are needed
-def _distances(pos, m):
-    return (pos[m[1]] - pos[m[0]]).norm(p=2, dim=1)
+def compute_cell_shifts(pos, mapping, pbc, cell, batch):
+    """Minimum-image shifts of the points 1.. of every term relative to its point 0, ``[M, 3, order-1]`` in length units
+    (base.py:5-62, restated with its conventions: the fractional displacement is ``inv(cell) @ (pos[m0] - pos[mk])``, the
+    shift ``cell @ floor(frac + 0.5)``, zeroed along non-periodic directions; constants with respect to differentiation)."""
+    with torch.no_grad():
+        M, order = mapping.shape[1], mapping.shape[0]
+        shifts = torch.zeros(M, 3, order - 1, dtype=pos.dtype, device=pos.device)
+        if batch is None:
+            batch = torch.zeros(pos.shape[0], dtype=torch.long, device=pos.device)
+        ids = batch[mapping[0]]
+        cells = cell.view(-1, 3, 3)[ids].to(pos.dtype)
+        cell_inv = torch.linalg.inv(cells)
+        periodic = pbc.view(-1, 3)[ids].to(pos.dtype)
+        for k in range(order - 1):
+            drs = pos[mapping[0]] - pos[mapping[k + 1]]
+            n = torch.floor(torch.einsum("bij,bj->bi", cell_inv, drs) + 0.5)
+            shifts[:, :, k] = periodic * torch.einsum("bij,bj->bi", cells, n)
+    return shifts
 
 
-def _angles_cos(pos, m):
-    a, b = pos[m[0]] - pos[m[1]], pos[m[2]] - pos[m[1]]
+def _data_cell_shifts(data, mapping):
+    """The shifts of a prior's terms when the data carry ``pbc`` and ``cell`` (harmonic.py:214-242), else None."""
+    pbc, cell = getattr(data, "pbc", None), getattr(data, "cell", None)
+    if pbc is None or cell is None:
+        return None
+    return compute_cell_shifts(data.pos.detach(), mapping, pbc.to(data.pos.device), cell.to(data.pos.device), getattr(data, "batch", None))
+
+
+def _feature_shifts(pos, mapping, pbc, cell, batch):
+    return None if pbc is None or cell is None else compute_cell_shifts(pos.detach(), mapping, pbc, cell, batch)
+
+
+def _shifted(pos, m, shifts):
+    """Positions of the points of every term, point k >= 1 moved by its shift (internal_coordinates.py:95-99, 168-177, 233-244)."""
+    pts = [pos[m[k]] for k in range(m.shape[0])]
+    if shifts is not None:
+        pts = [pts[0]] + [pts[k] + shifts[:, :, k - 1] for k in range(1, len(pts))]
+    return pts
+
+
+# differentiable torch restatements of the features: used when second derivatives are needed and for periodic data
+def _distances(pos, m, shifts=None):
+    p = _shifted(pos, m, shifts)
+    return (p[1] - p[0]).norm(p=2, dim=1)
+
+
+def _angles_cos(pos, m, shifts=None):
+    p = _shifted(pos, m, shifts)
+    a, b = p[0] - p[1], p[2] - p[1]
     return (a * b).sum(dim=1) / a.norm(p=2, dim=1) / b.norm(p=2, dim=1)
 
 
-def _torsions(pos, m):
-    b1, b2, b3 = pos[m[1]] - pos[m[0]], pos[m[2]] - pos[m[1]], pos[m[3]] - pos[m[2]]
+def _torsions(pos, m, shifts=None):
+    p = _shifted(pos, m, shifts)
+    b1, b2, b3 = p[1] - p[0], p[2] - p[1], p[3] - p[2]
     b1, b2, b3 = (v / v.norm(p=2, dim=1)[:, None] for v in (b1, b2, b3))
     n1, n2 = torch.cross(b1, b2, dim=1), torch.cross(b2, b3, dim=1)
     m1 = torch.cross(n1, b2, dim=1)
@@ -73,7 +115,7 @@ class _Prior(torch.nn.Module):
     def _params(self, data) -> torch.Tensor:
         raise NotImplementedError
 
-    def _energy_terms(self, pos, mapping, params) -> torch.Tensor:
+    def _energy_terms(self, pos, mapping, params, shifts=None) -> torch.Tensor:
         raise NotImplementedError
 
     def _interaction_types(self, data):
@@ -81,22 +123,28 @@ class _Prior(torch.nn.Module):
         return tuple(data.atom_types[mapping[i]] for i in range(self.order))
 
     def _cached_params(self, data) -> torch.Tensor:
-        """[P, M] per-term parameters; the index lists and bead types are static, so they are gathered once
-        per data object and kept next to the neighbour list (what mlcg's StaticPrior specialisation does,
-        src/mlcg/simulation/specialize_prior.py:49-59)."""
-        nl = data.neighbor_list[self.name]
-        cache = nl.setdefault(_PARAM_CACHE, {})
-        key = (self.name, data.pos.dtype, data.pos.device)
-        if key not in cache:
-            cache[key] = self._params(data).to(data.pos.dtype).contiguous()
-        return cache[key]
+        """[P, M] per-term parameters.  The index lists and bead types of a simulation are static, so the gathered rows are
+        kept on the module (what mlcg's StaticPrior specialisation does, src/mlcg/simulation/specialize_prior.py:49-59) and
+        reused while nothing they were gathered from has changed: the key holds the identity and the in-place version counter
+        of the index list, the bead types and every parameter table of this prior, and the dtype and device asked for."""
+        mapping, types_ = data.neighbor_list[self.name]["index_mapping"], data.atom_types
+        tables = tuple(self.buffers())
+        key = tuple((t.data_ptr(), t._version, tuple(t.shape)) for t in (mapping, types_) + tables) + (data.pos.dtype, data.pos.device)
+        cached = self.__dict__.get("_param_cache")
+        if cached is None or cached[0] != key:
+            # (the tensors of the key are held too, so that their storage cannot be freed and handed to another tensor)
+            cached = (key, self._params(data).to(data.pos.dtype).contiguous(), (mapping, types_) + tables)
+            self.__dict__["_param_cache"] = cached
+        return cached[1]
 
     def energy_and_gradient(self, data):
         """(energy [B], d(sum of energies)/d(pos) [N,3]) straight from the prior kernel, without an autograd graph; None where
-        that route does not apply (training mode, tensors off the device)."""
+        that route does not apply (training mode, tensors off the device, periodic data)."""
         if self.training or not data.pos.is_cuda:
             return None
         nl = data.neighbor_list[self.name]
+        if _data_cell_shifts(data, nl["index_mapping"]) is not None:
+            return None
         return get_backend().prior_terms(self.kind, data.pos.detach(), nl["index_mapping"], nl["mapping_batch"], self._cached_params(data),
                                          _num_structures(data), want_grad=True)
 
@@ -105,8 +153,9 @@ class _Prior(torch.nn.Module):
         mapping, mapping_batch = nl["index_mapping"], nl["mapping_batch"]
         B = _num_structures(data)
         params = self._cached_params(data)
-        if self.training and torch.is_grad_enabled():
-            y = self._energy_terms(data.pos, mapping, params)
+        shifts = _data_cell_shifts(data, mapping)
+        if shifts is not None or (self.training and torch.is_grad_enabled()):
+            y = self._energy_terms(data.pos, mapping, params, shifts)
             energy = torch.zeros(B, dtype=y.dtype, device=y.device).index_add_(0, mapping_batch, y)
         else:
             energy = _PriorEnergy.apply(data.pos, self.kind, mapping, mapping_batch, params, data.batch, B)
@@ -147,12 +196,12 @@ class HarmonicBonds(Harmonic):
     def __init__(self, statistics) -> None:
         super().__init__(statistics, HarmonicBonds.name, order=2)
 
-    def _energy_terms(self, pos, mapping, params):
-        return Harmonic.compute(_distances(pos, mapping), params[0], params[1])
+    def _energy_terms(self, pos, mapping, params, shifts=None):
+        return Harmonic.compute(_distances(pos, mapping, shifts), params[0], params[1])
 
     @staticmethod
     def compute_features(pos, mapping, pbc=None, cell=None, batch=None):
-        return _distances(pos, mapping)
+        return _distances(pos, mapping, _feature_shifts(pos, mapping, pbc, cell, batch))
 
 
 class HarmonicAngles(Harmonic):
@@ -165,12 +214,12 @@ class HarmonicAngles(Harmonic):
     def __init__(self, statistics) -> None:
         super().__init__(statistics, HarmonicAngles.name, order=3)
 
-    def _energy_terms(self, pos, mapping, params):
-        return Harmonic.compute(_angles_cos(pos, mapping), params[0], params[1])
+    def _energy_terms(self, pos, mapping, params, shifts=None):
+        return Harmonic.compute(_angles_cos(pos, mapping, shifts), params[0], params[1])
 
     @staticmethod
     def compute_features(pos, mapping, pbc=None, cell=None, batch=None):
-        return _angles_cos(pos, mapping)
+        return _angles_cos(pos, mapping, _feature_shifts(pos, mapping, pbc, cell, batch))
 
 
 class Repulsion(_Prior):
@@ -189,12 +238,12 @@ class Repulsion(_Prior):
     def _params(self, data):
         return self.sigma[self._interaction_types(data)].flatten().unsqueeze(0)
 
-    def _energy_terms(self, pos, mapping, params):
-        return Repulsion.compute(_distances(pos, mapping), params[0])
+    def _energy_terms(self, pos, mapping, params, shifts=None):
+        return Repulsion.compute(_distances(pos, mapping, shifts), params[0])
 
     @staticmethod
     def compute_features(pos, mapping, pbc=None, cell=None, batch=None):
-        return _distances(pos, mapping)
+        return _distances(pos, mapping, _feature_shifts(pos, mapping, pbc, cell, batch))
 
     @staticmethod
     def compute(x, sigma):
@@ -236,9 +285,9 @@ class FourierSeries(_Prior):
         v_0 = p["v_0"][:, :1]            # (a merged prior pads v_0 to the width of the series; only column 0 counts)
         return torch.cat([v_0.t(), p["k1s"].t(), p["k2s"].t()], dim=0)   # rows: v0, k1_1..k1_n, k2_1..k2_n
 
-    def _energy_terms(self, pos, mapping, params):
+    def _energy_terms(self, pos, mapping, params, shifts=None):
         n = self.n_degs
-        return FourierSeries.compute(_torsions(pos, mapping), params[0], params[1:1 + n].t(), params[1 + n:1 + 2 * n].t())
+        return FourierSeries.compute(_torsions(pos, mapping, shifts), params[0], params[1:1 + n].t(), params[1 + n:1 + 2 * n].t())
 
     @staticmethod
     def compute(theta, v_0, k1s, k2s):
@@ -259,4 +308,4 @@ class Dihedral(FourierSeries):
 
     @staticmethod
     def compute_features(pos, mapping, pbc=None, cell=None, batch=None):
-        return _torsions(pos, mapping)
+        return _torsions(pos, mapping, _feature_shifts(pos, mapping, pbc, cell, batch))

@@ -2,7 +2,7 @@
 
 :class:`OracleBackend` has the same methods as ``mlcg_b200.backend.CudaBackend``.  The test-suite uses
 it in two ways: as the checker the CUDA kernels are compared against (same inputs, ``-m gpu``), and,
-substituted through ``mlcg_b200.backend.set_backend``, to exercise the host-side autograd wiring on a
+substituted by the tests' ``monkeypatch`` fixture for the package's back-end object, to exercise the host-side autograd wiring on a
 machine without a GPU.  It is never selected by the package itself.
 """
 import numpy as np

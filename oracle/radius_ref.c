@@ -14,14 +14,18 @@
  *     the point itself and removes the self pair afterwards.
  * Output order is what both produce: centre index ascending, neighbour index ascending.
  *
- * The squared distance is ((dx*dx + dy*dy) + dz*dz) with every operation rounded
- * separately (compile with -ffp-contract=off), which is the expression the CUDA
- * kernels evaluate with explicit round-to-nearest multiplies and adds.
+ * The squared distance is fma(dz, dz, fma(dy, dy, dx*dx)): the loop `dist += diff * diff`
+ * of radius.cu:126-130 as nvcc compiles it with its default contraction into fused
+ * multiply-adds (compile this file with -ffp-contract=off so that nothing else is fused).
  *
- * Parity status: pinned against the numpy restatement in radius_ref.py and the
- * worked cases in tests/test_oracle_radius.py; the reference's own tests compare
- * against torch_cluster / ASE, neither of which can run here, so ulp-level edge
- * decisions at the cutoff are pinned only by this definition.
+ * Parity status: PINNED.  The reference's kernel, compiled unmodified (oracle/build_ref.py),
+ * was run on a B200 against this rule through the product's kernels on the reference's own
+ * test grid, lattices, a 4 x 4000 cube, exclusion lists and pairs whose squared distance is
+ * within one rounding of r*r (tests/test_gpu_radius_reference.py): the reference decides
+ * every such pair as the fused form does, never as separately rounded operations would.
+ * torch_cluster itself (not vendored, not installable here) stays unpinned; its CUDA kernel
+ * has the same loop.  The numpy restatement in radius_ref.py emulates the fused operations
+ * exactly and pins this file on the CPU (tests/test_oracle_radius.py).
  */
 #include <stdint.h>
 #include <math.h>
@@ -30,7 +34,7 @@
 #define RULE_NATIVE 0   /* radius.cu: skip self first, keep first max_nn hits        */
 #define RULE_CLUSTER 1  /* torch_cluster: cap = max_nn+1 with self counted, drop self */
 
-#define DEFINE_ORACLE(NAME, T, SQRT)                                                     \
+#define DEFINE_ORACLE(NAME, T, SQRT, FMA)                                                \
     static int64_t NAME##_centre(const T *pos, int64_t lo, int64_t hi, int64_t i, T r2, \
                                  int64_t max_nn, int loop, int rule, int64_t *oi,       \
                                  int64_t *oj, T *od) {                                   \
@@ -41,7 +45,7 @@
         for (int64_t j = lo; j < hi && hits < cap; j++) {                                \
             const T dx = pos[3 * j] - xi, dy = pos[3 * j + 1] - yi,                      \
                     dz = pos[3 * j + 2] - zi;                                            \
-            const T d2 = (dx * dx + dy * dy) + dz * dz;                                  \
+            const T d2 = FMA(dz, dz, FMA(dy, dy, dx * dx));                              \
             if (!(d2 < r2)) continue;                                                    \
             if (j == i) {                                                                \
                 if (!count_self) continue;                                               \
@@ -85,8 +89,8 @@
                               row0 + off[i], row1 + off[i], dist ? dist + off[i] : 0);   \
     }
 
-DEFINE_ORACLE(radius_ref_f32, float, sqrtf)
-DEFINE_ORACLE(radius_ref_f64, double, sqrt)
+DEFINE_ORACLE(radius_ref_f32, float, sqrtf, fmaf)
+DEFINE_ORACLE(radius_ref_f64, double, sqrt, fma)
 
 /*
  * exclusion_pairs.cpp:7-62 — sort pairs (x, y) by (y, x), return the xs and a CSR

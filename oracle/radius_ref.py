@@ -2,8 +2,12 @@
 
 Two independent restatements of the same rule, used to pin each other:
 
-* :func:`radius_graph_numpy` — vectorised numpy, all pairs of one structure at a time;
-* :func:`radius_graph_c` — ``radius_ref.c`` compiled with ``-ffp-contract=off`` and OpenMP.
+* :func:`radius_graph_numpy` — vectorised numpy, all pairs of one structure at a time, with the fused multiply-adds of the
+  squared distance emulated exactly (:func:`fma_exact`);
+* :func:`radius_graph_c` — ``radius_ref.c`` compiled with ``-ffp-contract=off`` and OpenMP, using libm's ``fma``.
+
+Both evaluate ``fma(dz, dz, fma(dy, dy, dx*dx)) < (T)(r*r)``, the form the reference's compiled kernel follows (checked against
+that kernel on a B200 by ``tests/test_gpu_radius_reference.py``).
 
 The rule follows ``src/opt_radius/mlcg_opt_radius/radius.cu:106-141`` (strict ``<`` on the squared
 distance, optional self exclusion, the first ``max_num_neighbors`` hits in index order) and, for
@@ -58,6 +62,49 @@ def _ptr_of(a, ctype):
     return a.ctypes.data_as(ctypes.POINTER(ctype))
 
 
+def _two_sum(a, b):
+    s = a + b
+    bb = s - a
+    return s, (a - (s - bb)) + (b - bb)
+
+
+def _two_prod(a, b):
+    """a*b = p + e exactly (Dekker's product with Veltkamp's splitting; no overflow or underflow at the magnitudes used here)."""
+    T = a.dtype.type
+    split = T(4097.0) if a.dtype == np.float32 else T(134217729.0)      # 2^12 + 1, 2^27 + 1
+    p = a * b
+    ca, cb = split * a, split * b
+    ah, bh = ca - (ca - a), cb - (cb - b)
+    al, bl = a - ah, b - bh
+    return p, ((ah * bh - p) + ah * bl + al * bh) + al * bl
+
+
+def _add_round_to_odd(a, b):
+    """a + b rounded to odd: the nearest-rounded sum, moved to its neighbour on the side of the rounding error when the sum
+    is inexact and its last mantissa bit is even."""
+    s, e = _two_sum(a, b)
+    bits = s.view(np.int32 if s.dtype == np.float32 else np.int64)
+    fix = (e != 0) & ((bits & 1) == 0)
+    toward = np.where(e > 0, np.inf, -np.inf).astype(s.dtype)
+    return np.where(fix, np.nextafter(s, toward), s)
+
+
+def fma_exact(a, b, c):
+    """round(a*b + c) with a single rounding, elementwise, in the dtype of the inputs (float32 or float64), from operations
+    of that same dtype: exact product, exact sum of its head with c, the two tails added with rounding to odd, one final
+    rounding (Boldo and Melquiond's emulation of the fused multiply-add)."""
+    a, b, c = np.broadcast_arrays(np.asarray(a), np.asarray(b), np.asarray(c))
+    with np.errstate(invalid="ignore", over="ignore"):
+        uh, ul = _two_prod(a, b)
+        th, tl = _two_sum(c, uh)
+        return th + _add_round_to_odd(tl, ul)
+
+
+def squared_distance(d):
+    """fma(dz, dz, fma(dy, dy, dx*dx)) for displacement vectors ``d[..., 3]``."""
+    return fma_exact(d[..., 2], d[..., 2], fma_exact(d[..., 1], d[..., 1], d[..., 0] * d[..., 0]))
+
+
 def batch_to_ptr(batch: np.ndarray, num_structures=None) -> np.ndarray:
     """``ptr[b]`` = first index whose batch id is >= b (radius.py:64-75 uses bucketize for this)."""
     batch = np.asarray(batch, dtype=np.int64)
@@ -89,7 +136,7 @@ def radius_graph_c(pos, ptr, r, max_num_neighbors=1000, loop=False, rule="cluste
 
 
 def radius_graph_numpy(pos, ptr, r, max_num_neighbors=1000, loop=False, rule="cluster", with_distance=False, exclude=None):
-    """Same rule, all pairs of one structure at a time with separately rounded numpy operations.
+    """Same rule, all pairs of one structure at a time.
 
     ``exclude = (xs, y_ptr)`` as :func:`exclusion_pair_to_ptr` returns them (rule "native" only): centre ``i`` never gets a
     neighbour listed in ``xs[y_ptr[i]:y_ptr[i+1]]``, and excluded points do not count towards the cap (radius.cu:122-141)."""
@@ -102,8 +149,7 @@ def radius_graph_numpy(pos, ptr, r, max_num_neighbors=1000, loop=False, rule="cl
         lo, hi = int(ptr[b]), int(ptr[b + 1])
         p = pos[lo:hi]
         d = p[None, :, :] - p[:, None, :]          # d[i, j] = pos[j] - pos[i]
-        sq = d * d
-        d2 = (sq[..., 0] + sq[..., 1]) + sq[..., 2]
+        d2 = squared_distance(d)
         hit = d2 < r2
         n = hi - lo
         eye = np.eye(n, dtype=bool)
@@ -166,8 +212,7 @@ def radius_graph_pbc_numpy(pos, ptr, cells, pbc, r, max_num_neighbors=1000, loop
         shifts = (sf[:, 0:1] * c[0][None, :] + sf[:, 1:2] * c[1][None, :]) + sf[:, 2:3] * c[2][None, :]     # [S,3]
         images = (p[None, :, :] + shifts[:, None, :]).reshape(-1, 3)                                   # copy-major
         d = images[None, :, :] - p[:, None, :]
-        sq = d * d
-        d2 = (sq[..., 0] + sq[..., 1]) + sq[..., 2]
+        d2 = squared_distance(d)
         hit = d2 < r2
         keep = hit & (np.cumsum(hit, axis=1) <= max_num_neighbors)
         i, im = np.nonzero(keep)

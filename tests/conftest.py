@@ -38,3 +38,10 @@ def golden_attentive():
     import torch
 
     return torch.load(os.path.join(ROOT, "tests", "golden", "reference_vectors_attentive.pt"), weights_only=False)
+
+
+@pytest.fixture(scope="session")
+def golden_fullwidth():
+    import torch
+
+    return torch.load(os.path.join(ROOT, "tests", "golden", "reference_vectors_fullwidth.pt"), weights_only=False)

@@ -6,15 +6,9 @@ Run once, in a container where the reference checkout is available::
 
 The reference package cannot be imported as a whole (its ``__init__`` files need torch_geometric,
 torch_cluster, ase, mdtraj, e3nn, ... which are not installed), so the hot-path files are loaded by
-path under synthetic parent packages, and the three third-party calls they make are replaced by small
-stand-ins that restate the published behaviour:
-
-* ``torch_geometric.nn.MessagePassing.propagate`` (``aggr="add"``): gather ``x[edge_index[0]]``, call
-  ``message``, index-add at ``edge_index[1]``;
-* ``torch_geometric.utils.scatter(reduce="sum")``: index-add over dim 0;
-* ``torch_cluster.radius_graph``: the oracle in ``oracle/radius_ref.py`` (rule "cluster");
-* ``torch_cluster.radius`` (periodic structures only): all points of the same structure within the radius, in index
-  order, cut after ``max_num_neighbors``.
+path under synthetic parent packages, and the three third-party calls they make are replaced by the small
+stand-ins of ``oracle/mlcg_loader.py`` (``MessagePassing.propagate``, ``utils.scatter``, ``torch_cluster.radius_graph`` and
+``torch_cluster.radius``).
 
 Everything else that runs — SchNet, CFConv, MLP, the radial bases, the cutoffs, compute_distances /
 angles / torsions, the prior classes, GradientsOut — is the reference's unmodified code.
@@ -31,94 +25,12 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-from oracle import radius_ref  # noqa: E402
+from oracle import mlcg_loader, radius_ref  # noqa: E402
 
 
 def install_shims(ref_src: str):
-    ref = os.path.join(ref_src, "src", "mlcg")
-
-    def pkg(name, path):
-        m = types.ModuleType(name)
-        m.__path__ = [path]
-        m.__package__ = name
-        sys.modules[name] = m
-
-    for name, sub in [("mlcg", ""), ("mlcg.nn", "nn"), ("mlcg.nn.prior", "nn/prior"), ("mlcg.geometry", "geometry"),
-                      ("mlcg.data", "data"), ("mlcg.neighbor_list", "neighbor_list")]:
-        pkg(name, os.path.join(ref, sub))
-
-    class MessagePassing(torch.nn.Module):
-        def __init__(self, aggr="add"):
-            super().__init__()
-            assert aggr == "add"
-            self.aggr = aggr
-
-        def propagate(self, edge_index, size=None, **kw):
-            x = kw.pop("x")
-            msg = self.message(x_j=x.index_select(0, edge_index[0]), **kw)
-            out = torch.zeros(x.size(0), msg.size(1), dtype=msg.dtype, device=msg.device)
-            return out.index_add_(0, edge_index[1], msg)
-
-    def scatter(src, index, dim=0, reduce="sum", dim_size=None):
-        assert dim == 0 and reduce == "sum"
-        n = int(index.max()) + 1 if dim_size is None else dim_size
-        out = torch.zeros((n,) + tuple(src.shape[1:]), dtype=src.dtype, device=src.device)
-        return out.index_add_(0, index, src)
-
-    class Data:
-        def __init__(self, **kw):
-            self.__dict__.update(kw)
-
-        def __contains__(self, k):
-            return self.__dict__.get(k) is not None
-
-        def __getitem__(self, k):
-            return self.__dict__[k]
-
-        def __setitem__(self, k, v):
-            self.__dict__[k] = v
-
-    def radius_graph(x, r, batch=None, loop=False, max_num_neighbors=32, flow="source_to_target", num_workers=1):
-        b = batch.numpy() if batch is not None else np.zeros(len(x), np.int64)
-        ei = radius_ref.radius_graph_c(x.detach().numpy(), radius_ref.batch_to_ptr(b), r, max_num_neighbors, loop, "cluster")
-        ei = torch.from_numpy(ei)
-        return ei if flow == "target_to_source" else ei.flip(0)
-
-    def radius(x, y, r, batch_x=None, batch_y=None, max_num_neighbors=32, num_workers=1):
-        """torch_cluster.radius as its CUDA kernel states it: for every point of y, the points of x of the same structure
-        with squared distance < r*r (float arithmetic of the inputs' dtype), in index order, at most max_num_neighbors;
-        row 0 indexes y, row 1 indexes x."""
-        xn, yn = x.detach().numpy(), y.detach().numpy()
-        bx = batch_x.numpy() if batch_x is not None else np.zeros(len(xn), np.int64)
-        by = batch_y.numpy() if batch_y is not None else np.zeros(len(yn), np.int64)
-        r2 = xn.dtype.type(float(r) * float(r))
-        rows = [[], []]
-        for i in range(len(yn)):
-            cand = np.nonzero(bx == by[i])[0]
-            d = xn[cand] - yn[i]
-            sq = d * d
-            d2 = (sq[:, 0] + sq[:, 1]) + sq[:, 2]
-            hit = cand[d2 < r2][:max_num_neighbors]
-            rows[0].extend([i] * len(hit))
-            rows[1].extend(hit.tolist())
-        return torch.tensor(rows, dtype=torch.long).reshape(2, -1)
-
-    mods = {n: types.ModuleType(n) for n in
-            ["torch_geometric", "torch_geometric.nn", "torch_geometric.utils", "torch_geometric.data", "torch_cluster",
-             "mdtraj", "mdtraj.core", "mdtraj.core.element", "ase", "ase.geometry", "ase.geometry.analysis", "ase.atoms",
-             "ase.build", "ase.neighborlist", "mlcg.geometry.topology"]}
-    mods["torch_geometric.nn"].MessagePassing = MessagePassing
-    mods["torch_geometric.utils"].scatter = scatter
-    mods["torch_geometric.data"].Data = Data
-    mods["torch_cluster"].radius_graph = radius_graph
-    mods["torch_cluster"].radius = radius
-    mods["mdtraj.core.element"].Element = object
-    mods["ase.geometry.analysis"].Analysis = object
-    mods["ase"].Atoms = object
-    mods["ase.atoms"].Atoms = object
-    mods["mdtraj"].Topology = object
-    mods["mlcg.geometry.topology"].Topology = object
-    sys.modules.update(mods)
+    """The stand-ins and parent packages of ``oracle/mlcg_loader.py``, over the checkout at ``ref_src``."""
+    mlcg_loader.install(os.path.join(ref_src, "src", "mlcg"))
 
 
 def chain(n, step=3.8, jitter=0.0, gen=None):
@@ -376,8 +288,96 @@ def main_regularized(ref_src):
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def avoiding_chain(n, gen, step=3.8, min_dist=4.0):
+    """3.8 A random walk; a step is redrawn while the new bead is closer than ``min_dist`` to any bead except its predecessor
+    (five beads back after 200 failures)."""
+    pos = torch.zeros(n, 3)
+    i, fails = 1, 0
+    while i < n:
+        v = torch.randn(3, generator=gen)
+        cand = pos[i - 1] + step * v / v.norm()
+        if i > 1 and bool(((pos[: i - 1] - cand).norm(dim=1) < min_dist).any()):
+            fails += 1
+            if fails > 200:
+                i, fails = max(1, i - 5), 0
+            continue
+        pos[i] = cand
+        i, fails = i + 1, 0
+    return pos
+
+
+def main_fullwidth(ref_src):
+    """SchNet at the widths and shapes of the benchmark configurations (hidden = filters = 128, which is what the fused
+    tensor-core route of this package needs): energies, forces, the force-matching loss and its parameter gradients, from the
+    reference's unmodified modules.
+
+    * ``chain100``: 3 x 100-bead self-avoiding chains, 20 types, 128 exp-normal functions, 15 A, 3 blocks;
+    * ``chain10``: 16 x 10-bead chains with 0.3 A jitter, types 0..9 in order, 50 Gaussians on 0-30 A, 2 blocks;
+    * ``chain268``: one 268-bead self-avoiding chain, 20 types, 128 exp-normal functions, 12 A, 3 blocks;
+    * ``chain73``: 4 x 73-bead walks, 20 types, 128 exp-normal functions, 10 A, 3 blocks, target forces N(0,1);
+    * ``chain73_trainable``: the same structures with the reference's default ``trainable=True`` basis (only the loss, the
+      forces and the gradients of the basis parameters are stored).
+    """
+    install_shims(ref_src)
+    schnet = importlib.import_module("mlcg.nn.schnet")
+    from mlcg.nn.radial_basis import GaussianBasis, ExpNormalBasis
+    from mlcg.nn.cutoff import CosineCutoff
+    from mlcg.nn.gradients import GradientsOut
+    from mlcg.data.atomic_data import AtomicData
+    sys.modules["mlcg.data"].AtomicData = AtomicData
+    gen = torch.Generator().manual_seed(97531)
+    out = {}
+
+    def case(name, kind, chains, types_, upper, R, L, n_types, trainable=False, keep=None, weights_of=None):
+        torch.manual_seed(13)
+        H = 128
+        cut = CosineCutoff(0.0, upper)
+        rbf = GaussianBasis(cut, R, trainable=trainable) if kind == "gaussian" else ExpNormalBasis(cut, R, trainable=trainable)
+        model = schnet.StandardSchNet(rbf, cut, [H], hidden_channels=H, embedding_size=n_types, num_filters=H, num_interactions=L)
+        if weights_of is not None:
+            model.load_state_dict(out[weights_of]["state_dict"])
+        else:
+            with torch.no_grad():
+                for k, p in model.named_parameters():
+                    if k.endswith("bias"):
+                        p.copy_(0.1 * torch.randn(p.shape, generator=gen))
+        B, n = len(chains), chains[0].shape[0]
+        pos = torch.cat(chains)
+        batch = torch.arange(B).repeat_interleave(n)
+        mk = lambda: AtomicData(pos=pos.clone(), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list={})
+        res = GradientsOut(model, "forces").eval()(mk())
+        c = dict(kind=kind, upper=upper, R=R, H=H, L=L, B=B, n=n, pos=pos, atom_types=types_, batch=batch, trainable=trainable,
+                 state_dict={k: v.detach().clone() for k, v in model.state_dict().items()},
+                 energy=res.out["SchNet"]["energy"].detach(), forces=res.out["SchNet"]["forces"].detach())
+        c["edge_index"] = model.neighbor_list(mk(), upper, model.max_num_neighbors)["SchNet"]["index_mapping"]
+        target = torch.randn(pos.shape, generator=gen)
+        tr = GradientsOut(model, "forces").train()
+        model.zero_grad()
+        loss = torch.nn.functional.mse_loss(tr(mk()).out["SchNet"]["forces"], target)
+        loss.backward()
+        c["target_forces"], c["loss"] = target, loss.detach()
+        c["param_grads"] = {k: p.grad.detach().clone() for k, p in model.named_parameters() if p.grad is not None and (keep is None or keep(k))}
+        if keep is not None:       # the weights are those of the case this one repeats: do not store them twice
+            c["state_dict"] = {k: v for k, v in c["state_dict"].items() if keep(k)}
+        out[name] = c
+        print(name, "E", [round(v, 4) for v in c["energy"].tolist()[:3]], "max|F|", float(c["forces"].abs().max()), "edges", c["edge_index"].shape[1],
+              "loss", float(loss), "grads", len(c["param_grads"]))
+
+    rt = lambda n, T: torch.randint(0, T, (n,), generator=gen)
+    case("chain100", "expnormal", [avoiding_chain(100, gen) for _ in range(3)], rt(300, 20), 15.0, 128, 3, 20)
+    case("chain10", "gaussian", [chain(10, jitter=0.3, gen=gen) for _ in range(16)], torch.arange(10).repeat(16), 30.0, 50, 2, 10)
+    case("chain268", "expnormal", [avoiding_chain(268, gen)], rt(268, 20), 12.0, 128, 3, 20)
+    walks, wt = [chain(73, gen=gen) for _ in range(4)], rt(292, 20)
+    case("chain73", "expnormal", walks, wt, 10.0, 128, 3, 20)
+    case("chain73_trainable", "expnormal", walks, wt, 10.0, 128, 3, 20, trainable=True, keep=lambda k: k.startswith("rbf_layer"),
+         weights_of="chain73")
+    path = os.path.join(HERE, "reference_vectors_fullwidth.pt")
+    torch.save(out, path)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
-    extra = {"regularized": main_regularized, "periodic": main_periodic, "attentive": main_attentive}
+    extra = {"regularized": main_regularized, "periodic": main_periodic, "attentive": main_attentive, "fullwidth": main_fullwidth}
     if len(sys.argv) not in (2, 3) or (len(sys.argv) == 3 and sys.argv[2] not in extra):
-        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg> [regularized|periodic|attentive]")
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg> [regularized|periodic|attentive|fullwidth]")
     (extra[sys.argv[2]] if len(sys.argv) == 3 else main)(sys.argv[1])

@@ -10,15 +10,25 @@ from mlcg_b200 import nn as bnn
 def schnet_from_case(case, dtype=None, device="cpu", trainable=None):
     """mlcg_b200 StandardSchNet with the architecture and weights of a golden case."""
     cut = bnn.CosineCutoff(0.0, case["upper"])
-    trainable = ("rbf_layer.means" in case.get("param_grads", {})) if trainable is None else trainable
+    trainable = case.get("trainable", "rbf_layer.means" in case.get("param_grads", {})) if trainable is None else trainable
     rbf = bnn.GaussianBasis(cut, case["R"], trainable=trainable) if case["kind"] == "gaussian" else bnn.ExpNormalBasis(cut, case["R"], trainable=trainable)
     emb = case["state_dict"]["embedding_layer.weight"].shape[0]
     model = bnn.StandardSchNet(rbf, cut, [case["H"]], hidden_channels=case["H"], embedding_size=emb, num_filters=case["H"],
                                num_interactions=case["L"])
     model = model.to(case["pos"].dtype)          # cast first: loading float64 weights into float32 would round them
+    assert set(model.state_dict().keys()) == set(case["state_dict"].keys())
     model.load_state_dict(case["state_dict"])
     dtype = case["pos"].dtype if dtype is None else dtype
     return model.to(device=device, dtype=dtype)
+
+
+def fullwidth_case(golden_fullwidth, name):
+    """A case of ``reference_vectors_fullwidth.pt`` with its complete ``state_dict`` (the case that repeats another case's
+    structures with a trainable basis stores the basis parameters only; the other weights are those of ``chain73``)."""
+    c = dict(golden_fullwidth[name])
+    if name == "chain73_trainable":
+        c["state_dict"] = {**golden_fullwidth["chain73"]["state_dict"], **c["state_dict"]}
+    return c
 
 
 def regularized_schnet_from_case(case, device="cpu"):

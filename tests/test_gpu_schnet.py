@@ -9,7 +9,8 @@ import mlcg_b200
 from mlcg_b200 import nn as bnn
 from oracle import radius_ref, schnet_ref
 
-from helpers import attentive_schnet_from_case, data_from_case, prior_setup, random_walk_chain, regularized_schnet_from_case, schnet_from_case
+from helpers import (attentive_schnet_from_case, data_from_case, fullwidth_case, prior_setup, random_walk_chain, regularized_schnet_from_case,
+                     schnet_from_case)
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -40,6 +41,71 @@ def test_golden_force_matching_gradients(golden, name):
     for k, g in c["param_grads"].items():
         tol_ = 1e-8 if f64 else 1e-4
         assert torch.allclose(grads[k].grad.cpu(), g, rtol=tol_, atol=tol_ * float(g.abs().max() + 1e-30)), k
+
+
+FULLWIDTH_EVAL = ["chain100", "chain10", "chain268", "chain73"]
+
+
+def _report(tag, e, f, c):
+    de = (e - c["energy"]).abs()
+    print(f"{tag}: max |dE| {float(de.max()):.3e} (max |dE|/|E| {float((de / c['energy'].abs()).max()):.3e}, |E| {float(c['energy'].abs().min()):.3f}.."
+          f"{float(c['energy'].abs().max()):.3f}), max |dF| {float((f - c['forces']).abs().max()):.3e} (max |F| {float(c['forces'].abs().max()):.2f})")
+
+
+@pytest.mark.parametrize("name", FULLWIDTH_EVAL)
+def test_fullwidth_golden_fused_routes(golden_fullwidth, name):
+    """The routes the benchmark times — the one-call evaluation (``mlcgb_schnet_eval``) and the fused tensor-core kernels launched
+    one by one — against energies and forces produced by the reference's own modules at the same widths (hidden = filters = 128,
+    128 exp-normal / 50 Gaussian functions): energies to 1e-5 relative, forces to 1e-4 kcal/mol/A."""
+    from mlcg_b200.backend import KernelProfiler, get_backend
+    c = fullwidth_case(golden_fullwidth, name)
+    net = schnet_from_case(c, device=DEV)
+    model = bnn.GradientsOut(net, "forces").eval()
+    be = get_backend()
+    assert c["B"] * c["n"] >= 128 and net.packed_weights() is not None and net._whole_model_setup(c["pos"].to(DEV)) is not None
+    nl = mlcg_b200.atomic_data2neighbor_list(data_from_case(c, device=DEV), c["upper"])
+    assert torch.equal(nl["index_mapping"].cpu(), c["edge_index"])                      # the reference's edge list, in its order
+    out = model(data_from_case(c, device=DEV))                                           # one library call per evaluation
+    e1, f1 = out.out["SchNet"]["energy"].cpu(), out.out["SchNet"]["forces"].cpu()
+    be.profiler = KernelProfiler(time_kernels=False)                                     # per-kernel route: each launch is counted
+    try:
+        out = model(data_from_case(c, device=DEV))
+        ran = set(be.profiler.stats)
+    finally:
+        be.profiler = None
+    be.check_pending()
+    assert {"filter_forward", "filter_backward", "seg_mul_sum", "gemm_tc"} <= ran and "gemm" not in ran and "rbf_expand" not in ran, ran
+    e2, f2 = out.out["SchNet"]["energy"].cpu(), out.out["SchNet"]["forces"].cpu()
+    for tag, e, f in ((f"{name} one-call", e1, f1), (f"{name} per-kernel", e2, f2)):
+        _report(tag, e, f, c)
+        assert torch.allclose(e, c["energy"], rtol=E_RTOL, atol=0.0), tag
+        assert float((f - c["forces"]).abs().max()) < F_ATOL, tag
+
+
+@pytest.mark.parametrize("name", ["chain100", "chain10", "chain73", "chain73_trainable"])
+def test_fullwidth_golden_force_matching_step(golden_fullwidth, name):
+    """Force-matching loss and its parameter gradients (second-order pass) at full width against the reference's."""
+    c = fullwidth_case(golden_fullwidth, name)
+    net = schnet_from_case(c, device=DEV)
+    out = bnn.GradientsOut(net, "forces").train()(data_from_case(c, device=DEV))
+    _report(f"{name} training-mode forward", out.out["SchNet"]["energy"].detach().cpu(), out.out["SchNet"]["forces"].detach().cpu(), c)
+    loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], c["target_forces"].to(DEV))
+    loss.backward()
+    get_backend_check()
+    assert torch.allclose(loss.detach().cpu(), c["loss"], rtol=1e-5)
+    grads = dict(net.named_parameters())
+    worst = 0.0
+    for k, g in c["param_grads"].items():
+        assert grads[k].grad is not None, k
+        err = float((grads[k].grad.cpu() - g).abs().max() / (g.abs().max() + 1e-30))
+        worst = max(worst, err)
+        assert err < 2e-4, (k, err)
+    print(f"{name}: loss {float(loss):.6f} vs {float(c['loss']):.6f}; worst parameter-gradient error {worst:.2e} of the gradient's maximum")
+
+
+def get_backend_check():
+    from mlcg_b200.backend import get_backend
+    get_backend().check_pending()
 
 
 @pytest.mark.parametrize("name", ["shared", "independent"])

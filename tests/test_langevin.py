@@ -55,13 +55,10 @@ def run_case(device, dtype, steps=4):
         assert torch.allclose(pot, pot_ref, rtol=max(tol, 1e-5), atol=max(tol, 1e-4))
 
 
-def test_langevin_step_cpu_wiring():
+def test_langevin_step_cpu_wiring(monkeypatch):
     from oracle.primitives import OracleBackend
-    old = backend.set_backend(OracleBackend())
-    try:
-        run_case("cpu", torch.float64)
-    finally:
-        backend.set_backend(old)
+    monkeypatch.setattr(backend, "_backend", OracleBackend())
+    run_case("cpu", torch.float64)
 
 
 def test_maxwell_boltzmann_moments():
@@ -130,17 +127,14 @@ def test_simulation_replayed_from_a_cuda_graph():
     backend.get_backend().check_pending()
 
 
-def test_simulation_trajectory_buffer_cpu_wiring():
+def test_simulation_trajectory_buffer_cpu_wiring(monkeypatch):
     from oracle.primitives import OracleBackend
-    old = backend.set_backend(OracleBackend())
-    try:
-        data, priors = prior_setup(14, 3, 4, torch.Generator().manual_seed(3))
-        model = bnn.SumOut(torch.nn.ModuleDict({k: bnn.GradientsOut(p, "forces") for k, p in priors.items()})).eval()
-        data.pos = data.pos.to(torch.float64)
-        sim = LangevinSimulation(model, dt=0.002, friction=1.0, beta=1.0 / (0.0019872041 * 300), rng=torch.Generator().manual_seed(1))
-        sim.attach(data, torch.ones(data.pos.shape[0], dtype=torch.float64))
-        sim.simulate(7, save_interval=3)
-        assert sim.trajectory.shape == (2, data.pos.shape[0], 3) and sim.potentials.shape == (2, 3)
-        assert bool(torch.isfinite(sim.trajectory).all()) and not torch.equal(sim.trajectory[0], sim.trajectory[1])
-    finally:
-        backend.set_backend(old)
+    monkeypatch.setattr(backend, "_backend", OracleBackend())
+    data, priors = prior_setup(14, 3, 4, torch.Generator().manual_seed(3))
+    model = bnn.SumOut(torch.nn.ModuleDict({k: bnn.GradientsOut(p, "forces") for k, p in priors.items()})).eval()
+    data.pos = data.pos.to(torch.float64)
+    sim = LangevinSimulation(model, dt=0.002, friction=1.0, beta=1.0 / (0.0019872041 * 300), rng=torch.Generator().manual_seed(1))
+    sim.attach(data, torch.ones(data.pos.shape[0], dtype=torch.float64))
+    sim.simulate(7, save_interval=3)
+    assert sim.trajectory.shape == (2, data.pos.shape[0], 3) and sim.potentials.shape == (2, 3)
+    assert bool(torch.isfinite(sim.trajectory).all()) and not torch.equal(sim.trajectory[0], sim.trajectory[1])

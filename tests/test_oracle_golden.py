@@ -50,6 +50,30 @@ def test_force_matching_gradients_match_reference(golden, name):
         assert torch.allclose(sd[k].grad, g, rtol=10 * tol, atol=tol * float(g.abs().max() + 1e-30)), k
 
 
+FULLWIDTH = ["chain100", "chain10", "chain268", "chain73", "chain73_trainable"]
+
+
+@pytest.mark.parametrize("name", FULLWIDTH)
+def test_fullwidth_oracle_matches_reference(golden_fullwidth, name):
+    """The restatement at the widths the benchmark runs (128 hidden channels and filters, 128 exp-normal or 50 Gaussian
+    functions): edges, energies, forces, force-matching loss and parameter gradients against the reference's own modules."""
+    from helpers import fullwidth_case
+    c = fullwidth_case(golden_fullwidth, name)
+    ptr = radius_ref.batch_to_ptr(c["batch"].numpy())
+    assert np.array_equal(radius_ref.radius_graph_c(c["pos"].numpy(), ptr, c["upper"], 1000, False, "cluster"), c["edge_index"].numpy())
+    spec = _spec(c)
+    sd = {k: v.clone().requires_grad_(k in c["param_grads"]) for k, v in c["state_dict"].items()}
+    fn = lambda p: schnet_ref.schnet_energy(sd, spec, p, c["atom_types"], c["batch"], c["edge_index"], c["B"])
+    e, f, _ = schnet_ref.energy_and_forces(fn, c["pos"], create_graph=True)
+    assert torch.allclose(e.detach(), c["energy"], rtol=1e-5, atol=1e-5)
+    assert float((f.detach() - c["forces"]).abs().max()) < 1e-4
+    loss = torch.nn.functional.mse_loss(f, c["target_forces"])
+    loss.backward()
+    assert torch.allclose(loss.detach(), c["loss"], rtol=1e-5)
+    for k, g in c["param_grads"].items():
+        assert torch.allclose(sd[k].grad, g, rtol=1e-3, atol=1e-4 * float(g.abs().max() + 1e-30)), k
+
+
 def test_priors_match_reference(golden):
     c = golden["priors_f32"]
     pos, t, B = c["pos"], c["atom_types"], c["B"]

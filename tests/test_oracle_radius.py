@@ -22,6 +22,27 @@ def test_c_equals_numpy(dtype, rule, loop, max_nn):
     assert np.all(a[1][1:][same] > a[1][:-1][same])             # neighbours ascending
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_fused_multiply_add_emulation_is_exact(dtype):
+    """`fma_exact` (operations of one dtype only) against libm's correctly rounded fma on random, cancelling, tiny and huge
+    addends; separately rounded `a*b + c` differs from both on a large share of these inputs."""
+    import ctypes
+    libm = ctypes.CDLL("libm.so.6")
+    f = libm.fmaf if dtype == np.float32 else libm.fma
+    ct = ctypes.c_float if dtype == np.float32 else ctypes.c_double
+    f.restype, f.argtypes = ct, [ct] * 3
+    rng = np.random.default_rng(1)
+    n = 20000
+    a, b = (rng.standard_normal(n) * 10).astype(dtype), (rng.standard_normal(n) * 10).astype(dtype)
+    c = (rng.standard_normal(n) * 100).astype(dtype)
+    c[: n // 4] = (-(a[: n // 4].astype(np.float64) * b[: n // 4])).astype(dtype)
+    c[n // 4: n // 2] *= dtype(1e-6)
+    c[n // 2: 3 * n // 4] *= dtype(1e6)
+    want = np.array([f(float(x), float(y), float(z)) for x, y, z in zip(a, b, c)], dtype=dtype)
+    assert np.array_equal(radius_ref.fma_exact(a, b, c), want)
+    assert (a * b + c != want).sum() > n // 10
+
+
 def test_strict_cutoff_on_a_lattice():
     """Integer lattice, integer cutoff: pairs at exactly r are excluded (strict <, radius.cu:134)."""
     g = np.stack(np.meshgrid(*[np.arange(4)] * 3, indexing="ij"), -1).reshape(-1, 3).astype(np.float32)
