@@ -116,30 +116,36 @@ class CpuArm:
             return "mlcg's own modules on torch CPU float32 (torch_geometric propagate/scatter and torch_cluster.radius_graph replaced by stand-ins; radius graph by the C oracle)"
         return "restatement of mlcg's modules (oracle/schnet_ref.py) on torch CPU float32 + C radius oracle"
 
-    def schnet_evaluator(self, state_dict, n, **arch):
-        """``fn(pos, types, batch, B) -> (energy, forces)`` of a SchNet with this state_dict, radius graph rebuilt per call."""
+    def schnet_evaluator(self, state_dict, n, dtype=torch.float32, **arch):
+        """``fn(pos, types, batch, B) -> (energy, forces)`` of a SchNet with this state_dict, radius graph rebuilt per call.
+        ``dtype=torch.float64``: the same float32 weights and positions evaluated in double precision (the value every float32
+        evaluation rounds towards)."""
         kind, cutoff = arch.get("kind", "expnormal"), arch.get("cutoff", WORKLOAD["cutoff_A"])
         L = arch.get("interactions", WORKLOAD["interactions"])
+        from oracle import radius_ref, schnet_ref
         if self.kind == "reference":
             ns = self.ns
             model = make_model(ns, **arch)
             model.load_state_dict(state_dict)
+            model = model.to(dtype)
             wrapped = ns.GradientsOut(model, "forces").eval()
 
             def fn(pos, types_, batch, B):
-                data = ns.AtomicData(pos=pos.clone(), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list={})
+                # (in double precision the model rebuilds its graph from the same coordinates; a pair that changes sides within one
+                # float32 rounding of the cutoff carries a filter of size ~1e-14, the cosine envelope vanishing there)
+                data = ns.AtomicData(pos=pos.clone().to(dtype), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list={})
                 out = wrapped(data)
                 return out.out["SchNet"]["energy"].detach(), out.out["SchNet"]["forces"].detach()
 
             return fn
-        from oracle import radius_ref, schnet_ref
         cut = {"cutoff": "cosine", "lower": 0.0, "upper": cutoff}
         spec = {"kind": kind, "rbf_cutoff": cut, "cutoff": cut, "activation": "tanh", "num_interactions": L}
+        sd = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in state_dict.items()}
 
         def fn(pos, types_, batch, B):
             ptr = radius_ref.batch_to_ptr(batch.numpy(), B)
             ei = torch.from_numpy(radius_ref.radius_graph_c(pos.numpy(), ptr, cutoff, 1000, False, "cluster"))
-            e, f, _ = schnet_ref.energy_and_forces(lambda p: schnet_ref.schnet_energy(state_dict, spec, p, types_, batch, ei, B), pos)
+            e, f, _ = schnet_ref.energy_and_forces(lambda p: schnet_ref.schnet_energy(sd, spec, p, types_, batch, ei, B), pos.to(dtype))
             return e, f
 
         return fn
@@ -154,12 +160,22 @@ def timed_host(fn, steps, warmup):
     return (time.perf_counter() - t0) / steps, out
 
 
-def parity(e, f, e_ref, f_ref):
-    de = (e - e_ref).abs()
-    rel = float((de / e_ref.abs().clamp_min(1e-30)).max())
-    df = float((f - f_ref).abs().max())
-    return dict(max_rel_dE=rel, max_abs_dE=float(de.max()), max_abs_dF=df, max_abs_F=float(f_ref.abs().max()), energy_rtol=E_RTOL, force_atol=F_ATOL,
-                ok=bool(rel <= E_RTOL and df <= F_ATOL))
+def parity(e, f, e32, f32, e64, f64):
+    """Energies and forces of this package (``e``, ``f``) against the CPU arm in float32 (``e32``, ``f32``) and against the CPU
+    arm's double-precision evaluation of the same float32 weights and positions (``e64``, ``f64``).  Bars: forces within 1e-4
+    kcal/mol/A of the double-precision value; energies within 1e-5 of it relative, plus the largest distance of the float32 CPU
+    arm itself from it over the sample (a structure whose energy nearly cancels cannot be met to 1e-5 of its own size by any
+    float32 evaluation, the reference's included)."""
+    e, f, e32, f32 = e.double(), f.double(), e32.double(), f32.double()
+    ours_e, cpu_e = (e - e64).abs(), (e32 - e64).abs()
+    ours_f, cpu_f = float((f - f64).abs().max()), float((f32 - f64).abs().max())
+    bar = E_RTOL * e64.abs() + float(cpu_e.max())
+    return dict(max_abs_dE_vs_f64=float(ours_e.max()), max_rel_dE_vs_f64=float((ours_e / e64.abs().clamp_min(1e-30)).max()),
+                cpu_f32_max_abs_dE_vs_f64=float(cpu_e.max()), cpu_f32_max_rel_dE_vs_f64=float((cpu_e / e64.abs().clamp_min(1e-30)).max()),
+                max_abs_dE_vs_cpu_f32=float((e - e32).abs().max()), min_abs_E=float(e64.abs().min()), max_abs_E=float(e64.abs().max()),
+                max_abs_dF_vs_f64=ours_f, cpu_f32_max_abs_dF_vs_f64=cpu_f, max_abs_dF_vs_cpu_f32=float((f - f32).abs().max()),
+                max_abs_F=float(f64.abs().max()), energy_rtol=E_RTOL, force_atol=F_ATOL,
+                ok=bool((ours_e <= bar).all() and ours_f <= F_ATOL))
 
 
 def run_reference(args):
@@ -320,10 +336,12 @@ def extra_measurements(dev, hbm_peak, arm):
 
     ms = time_cuda(eval1, iters=20, warm=5)
     e1, f1 = eval1()
-    fn1 = arm.schnet_evaluator({k: v.detach().cpu() for k, v in net1.state_dict().items()}, n1, **arch1)
+    sd1 = {k: v.detach().cpu() for k, v in net1.state_dict().items()}
+    fn1 = arm.schnet_evaluator(sd1, n1, **arch1)
     sec1, (e1r, f1r) = timed_host(lambda: fn1(pos1, types1, batch1, B1), 10, 2)
+    e1x, f1x = arm.schnet_evaluator(sd1, n1, dtype=torch.float64, **arch1)(pos1, types1, batch1, B1)
     out["eval_64x10"] = dict(ms=ms, structures_per_s=B1 / (ms / 1e3), cpu_ms=sec1 * 1e3, cpu_structures_per_s=B1 / sec1,
-                             parity=parity(e1.cpu(), f1.cpu(), e1r, f1r),
+                             parity=parity(e1.cpu(), f1.cpu(), e1r, f1r, e1x, f1x),
                              note="64 structures x 10 beads, 2 blocks, 50 Gaussian functions on 0-30 A; radius graph + energy + forces per call; "
                                   "GPU time is the host's launch path at this size; CPU: all 64 structures, 10 calls")
     del m1, net1
@@ -402,24 +420,30 @@ def extra_measurements(dev, hbm_peak, arm):
     cpu = None
     if arm.kind == "reference":
         ns = arm.ns
-        cnet = make_model(ns, **arch5)
-        cnet.load_state_dict(sd5)
-        cmods = {"SchNet": ns.GradientsOut(cnet, "forces")}
-        cmods.update({k: ns.GradientsOut(p, "forces") for k, p in _prior_modules(ns, T).items()})
-        cmodel = ns.SumOut(torch.nn.ModuleDict(cmods)).eval()
         clists = _batched_lists(terms, Bc, npb)
-        cnl = {name: dict(tag=name, order=m.shape[0], index_mapping=m, mapping_batch=mb, cell_shifts=None, rcut=None, self_interaction=False)
-               for name, (m, mb) in clists.items()}
         ctypes_, cbatch = types5_h[: Bc * npb], torch.arange(Bc).repeat_interleave(npb)
 
-        def model_fn(x):
-            d = ns.AtomicData(pos=x.clone(), atom_types=ctypes_, batch=cbatch, n_atoms=torch.full((Bc,), npb), neighbor_list=dict(cnl))
-            o = cmodel(d)
-            return o.out["energy"].detach(), o.out["forces"].detach()
+        def cpu_model(dtype):
+            cnet = make_model(ns, **arch5)
+            cnet.load_state_dict(sd5)
+            cmods = {"SchNet": ns.GradientsOut(cnet, "forces")}
+            cmods.update({k: ns.GradientsOut(p, "forces") for k, p in _prior_modules(ns, T).items()})
+            cmodel = ns.SumOut(torch.nn.ModuleDict(cmods)).eval().to(dtype)
+            cnl = {name: dict(tag=name, order=m.shape[0], index_mapping=m, mapping_batch=mb, cell_shifts=None, rcut=None, self_interaction=False)
+                   for name, (m, mb) in clists.items()}
 
+            def model_fn(x):
+                d = ns.AtomicData(pos=x.clone().to(dtype), atom_types=ctypes_, batch=cbatch, n_atoms=torch.full((Bc,), npb), neighbor_list=dict(cnl))
+                o = cmodel(d)
+                return o.out["energy"].detach(), o.out["forces"].detach()
+
+            return model_fn
+
+        model_fn = cpu_model(torch.float32)
         x0 = ppos_h[: Bc * npb].clone()
         ec, fc = model_fn(x0)
-        chk = parity(e0[:Bc], f0[: Bc * npb], ec, fc)
+        ex, fx = cpu_model(torch.float64)(x0)
+        chk = parity(e0[:Bc], f0[: Bc * npb], ec, fc, ex, fx)
         cgen = torch.Generator().manual_seed(1)
         masses_c = torch.full((Bc * npb,), mass)
         bmr = torch.sqrt(1.0 / (KCAL_BETA_300K * masses_c))
@@ -756,7 +780,8 @@ def run_ours(args):
         fn = arm.schnet_evaluator(state_dict_h, n)
         sl = slice(0, sample_B * n)
         sec, (e_cpu, f_cpu) = timed_host(lambda: fn(pos_h[sl], types_h[sl], batch_h[sl], sample_B), 12, 1)
-        check = parity(e_timed[:sample_B], f_timed[sl], e_cpu, f_cpu)
+        e_64, f_64 = arm.schnet_evaluator(state_dict_h, n, dtype=torch.float64)(pos_h[sl], types_h[sl], batch_h[sl], sample_B)
+        check = parity(e_timed[:sample_B], f_timed[sl], e_cpu, f_cpu, e_64, f_64)
         cpu = dict(value=sample_B / sec, unit="structures/s", cores=arm.cores, kind=arm.kind,
                    sample=f"the first {sample_B} structures of the timed batch per step, 12 steps after 1 warm-up, radius graph rebuilt each step; {arm.describe()}")
         if not check["ok"]:

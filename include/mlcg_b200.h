@@ -104,10 +104,12 @@ int mlcgb_radius_fill_excl(const void *pos, int dtype, const int64_t *ptr, int64
  *   deg[N], offsets[N+1] and edge_index[2, capacity] are the caller's; row 0 starts at edge_index, row 1 at
  *   edge_index + capacity; *n_edges_host (a HOST pointer) receives the number of edges, also when it
  *   exceeds `capacity`, in which case nothing is written to edge_index and MLCGB_E_LIMIT is returned.
- * The call waits for the stream once (to read the edge count).  The first call on each device looks up
- * the scratch address; make that first call outside any stream capture.  All calls on a device share
- * the scratch: calls that may overlap on the GPU (different streams or threads) race on it and must be
- * serialised by the caller.  Nothing in the scratch has to start at zero and nothing is kept between calls. */
+ * Every call copies the edge count to the host and waits for the stream, so the entry point cannot be used while the stream
+ * is being captured into a CUDA graph (mlcgb_radius_graph_capacity is the capturable form; it takes a caller's workspace).
+ * The first call on each device also looks up the scratch address; concurrent first calls from several host threads may both
+ * do the look-up and store the same value.  All calls on a device share the scratch: calls that may overlap on the GPU
+ * (different streams or threads) race on it and must be serialised by the caller.  Nothing in the scratch has to start at zero
+ * and nothing is kept between calls. */
 int mlcgb_radius_graph_static(const void *pos /* [N,3] */, int dtype, const int64_t *ptr /* [B+1] */, int64_t N, int64_t B,
                               double r, int64_t max_num_neighbors, int loop, int rule, int32_t *deg /* [N] */,
                               int64_t *offsets /* [N+1] */, int64_t capacity, int64_t *edge_index /* [2,capacity] */,

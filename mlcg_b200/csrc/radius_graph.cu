@@ -14,6 +14,8 @@
 //        the canonical order without a sort).
 #include "common.cuh"
 
+#include <atomic>
+
 namespace mlcgb {
 
 constexpr int kBruteMax = 384;     // structures up to this size scan all their points
@@ -924,23 +926,23 @@ constexpr size_t kStaticScratchBytes = (size_t)3 << 20;   // >= ws_layout(65536,
 static __device__ __align__(256) unsigned char g_radius_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-static void *g_scratch_addr[kMaxDevices] = {nullptr};
+static std::atomic<void *> g_scratch_addr[kMaxDevices];      // zero-initialised; every writer stores the same address per device
 
 // The array's name is only a host-side handle; the device address has to be asked for, once per
 // device, with that device current.
 static int static_scratch_address(void **out) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return MLCGB_E_ARG;
-    if (!g_scratch_addr[dev]) {
-        void *p = nullptr;
+    void *p = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!p) {
         cudaError_t e = cudaGetSymbolAddress(&p, g_radius_scratch);
         if (e != cudaSuccess || !p) {
             g_last_cuda_error = (int)e;
             return MLCGB_E_LAUNCH;
         }
-        g_scratch_addr[dev] = p;
+        g_scratch_addr[dev].store(p, std::memory_order_release);
     }
-    *out = g_scratch_addr[dev];
+    *out = p;
     return MLCGB_OK;
 }
 }  // namespace mlcgb

@@ -29,11 +29,17 @@ class _PriorEnergy(torch.autograd.Function):
         return g.index_select(0, batch).unsqueeze(-1) * grad, None, None, None, None, None, None
 
 
+def _batch_or_zeros(data):
+    batch = getattr(data, "batch", None)
+    return torch.zeros(data.pos.shape[0], dtype=torch.long, device=data.pos.device) if batch is None else batch
+
+
 def _num_structures(data) -> int:
     n_atoms = getattr(data, "n_atoms", None)
     if n_atoms is not None and torch.is_tensor(n_atoms) and n_atoms.dim() == 1:
         return int(n_atoms.numel())
-    return int(data.batch[-1]) + 1
+    batch = getattr(data, "batch", None)
+    return 1 if batch is None else int(batch[-1]) + 1
 
 
 def _table_from_statistics(statistics: Dict, order: int, field: str) -> torch.Tensor:
@@ -158,7 +164,7 @@ class _Prior(torch.nn.Module):
             y = self._energy_terms(data.pos, mapping, params, shifts)
             energy = torch.zeros(B, dtype=y.dtype, device=y.device).index_add_(0, mapping_batch, y)
         else:
-            energy = _PriorEnergy.apply(data.pos, self.kind, mapping, mapping_batch, params, data.batch, B)
+            energy = _PriorEnergy.apply(data.pos, self.kind, mapping, mapping_batch, params, _batch_or_zeros(data), B)
         data.out[self.name] = {"energy": energy}
         return data
 

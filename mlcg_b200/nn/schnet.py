@@ -39,6 +39,30 @@ def _tag_symmetric(t: torch.Tensor, flag: bool) -> torch.Tensor:
     return t
 
 
+def _batch_of(data, ptr):
+    """Structure index per bead; built from the structure pointer for data that carry no ``batch`` (a single structure)."""
+    batch = getattr(data, "batch", None)
+    if batch is None:
+        batch = torch.repeat_interleave(torch.arange(ptr.numel() - 1, device=ptr.device), ptr[1:] - ptr[:-1], output_size=data.pos.shape[0])
+    return batch
+
+
+_FROZEN_WARNED = False
+
+
+def _warn_frozen_weights(model):
+    """Eval-mode evaluations run on kernels that treat every weight as a constant: energies and forces are exact, but the energy
+    carries no graph to the parameters.  Say so, once, when someone may be relying on such a graph (gradients enabled and a
+    parameter that requires them); ``model.train()`` keeps every parameter differentiable."""
+    global _FROZEN_WARNED
+    if _FROZEN_WARNED or not torch.is_grad_enabled() or not any(p.requires_grad for p in model.parameters()):
+        return
+    _FROZEN_WARNED = True
+    warnings.warn("mlcg_b200: in eval mode SchNet is evaluated with its weights as constants (energies and position gradients only); "
+                  "a backward pass will not reach the parameters. Use model.train() to differentiate with respect to parameters, or "
+                  "p.requires_grad_(False) / torch.no_grad() to silence this message.", stacklevel=3)
+
+
 class CFConv(torch.nn.Module):
     """Continuous-filter convolution (schnet.py:265-368): ``lin2( sum_j lin1(x)_j * W_ij )`` with
     ``W = filter_network(rbf) * cutoff(d)``.  Same constructor and sub-module names as the reference,
@@ -218,6 +242,8 @@ class SchNet(torch.nn.Module):
             ptr = torch.zeros(n_atoms.numel() + 1, dtype=torch.int64, device=data.pos.device)
             torch.cumsum(n_atoms.to(device=data.pos.device, dtype=torch.int64), 0, out=ptr[1:])
             return ptr
+        if getattr(data, "batch", None) is None:       # a single structure
+            return torch.tensor([0, data.pos.shape[0]], dtype=torch.int64, device=data.pos.device)
         return get_backend().batch_to_ptr(data.batch, int(data.batch[-1]) + 1)
 
     # ---- whole-model evaluation in one library call (eval mode, standard layout)
@@ -300,6 +326,7 @@ class SchNet(torch.nn.Module):
                  for b in self.interaction_blocks]
         lazy_ok = not self.training and distances.dtype == torch.float32 and all(s is not None for s in specs)
         if lazy_ok:
+            _warn_frozen_weights(self)
             rbf_expansion = LazyRadialBasis(distances, self.rbf_layer, plan.symmetric)
         else:
             rbf_expansion = _tag_symmetric(self.rbf_layer(distances), plan.symmetric)
@@ -314,10 +341,9 @@ class SchNet(torch.nn.Module):
         ptr = neighbor_list.get("_mlcgb_ptr")
         if ptr is None or ptr.device != x.device or ptr[-1:].numel() == 0:
             ptr = self._structure_ptr(data)
-        energy = SegmentSum.apply(energy, ptr, data.batch).flatten()
+        energy = SegmentSum.apply(energy, ptr, _batch_of(data, ptr)).flatten()
         data.out[self.name] = {ENERGY_KEY: energy}
         return data
-
 
     def energy_and_gradient(self, data):
         """(energy [B], d(sum of energies)/d(pos) [N,3]) from one library call, without an autograd graph; None where the
@@ -374,7 +400,7 @@ class SchNet(torch.nn.Module):
         n_atoms = getattr(data, "n_atoms", None)
         if n_atoms is not None and torch.is_tensor(n_atoms) and n_atoms.dim() == 1:
             return int(n_atoms.numel())
-        return int(data.batch[-1]) + 1
+        return 1 if getattr(data, "batch", None) is None else int(data.batch[-1]) + 1
 
     def _forward_whole_model(self, data, neighbor_list):
         setup = self._whole_model_setup(data.pos)
@@ -387,7 +413,8 @@ class SchNet(torch.nn.Module):
         if ptr is None or ptr.device != data.pos.device:
             ptr = self._structure_ptr(data)
         spec, conv_cut, weights, precision = setup
-        data.out[self.name] = {ENERGY_KEY: SchNetEval.apply(data.pos, self._types(data), ptr, data.batch, plan, spec, conv_cut, weights, precision)}
+        _warn_frozen_weights(self)
+        data.out[self.name] = {ENERGY_KEY: SchNetEval.apply(data.pos, self._types(data), ptr, _batch_of(data, ptr), plan, spec, conv_cut, weights, precision)}
         return data
 
     @staticmethod

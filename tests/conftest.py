@@ -45,3 +45,10 @@ def golden_fullwidth():
     import torch
 
     return torch.load(os.path.join(ROOT, "tests", "golden", "reference_vectors_fullwidth.pt"), weights_only=False)
+
+
+@pytest.fixture(scope="session")
+def golden_priors_periodic():
+    import torch
+
+    return torch.load(os.path.join(ROOT, "tests", "golden", "reference_vectors_priors_periodic.pt"), weights_only=False)

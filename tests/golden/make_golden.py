@@ -288,6 +288,65 @@ def main_regularized(ref_src):
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def main_priors_periodic(ref_src):
+    """The four priors on periodic data (harmonic.py:214-242, fourier_series.py:95-101,477-483, repulsion.py:78-134 with
+    base.py:5-62): chains wrapped into their cell, so that bonds, angles, dihedrals and repulsion pairs cross the box; an
+    orthorhombic box periodic along all directions, the same box periodic along two, and a sheared box (where the reference's
+    shift convention, as written, is not the minimum image; it is followed as written)."""
+    install_shims(ref_src)
+    from mlcg.nn.gradients import GradientsOut
+    from mlcg.data.atomic_data import AtomicData
+    sys.modules["mlcg.data"].AtomicData = AtomicData
+    harmonic = importlib.import_module("mlcg.nn.prior.harmonic")
+    repulsion = importlib.import_module("mlcg.nn.prior.repulsion")
+    fourier = importlib.import_module("mlcg.nn.prior.fourier_series")
+    import itertools
+    gen = torch.Generator().manual_seed(8642)
+    n, B, T = 14, 2, 3
+    idx = torch.arange(n)
+    per = {"bonds": torch.stack([idx[:-1], idx[1:]]), "angles": torch.stack([idx[:-2], idx[1:-1], idx[2:]]),
+           "dihedrals": torch.stack([idx[:-3], idx[1:-2], idx[2:-1], idx[3:]])}
+    full = torch.cartesian_prod(idx, idx).t()
+    per["repulsion"] = full[:, (full[0] - full[1]).abs() >= 3]
+    r = lambda *s: torch.rand(*s, generator=gen)
+    bond_stats = {k: {"k": float(50 + 100 * r(1)), "x_0": float(3.5 + 0.6 * r(1))} for k in itertools.product(range(T), repeat=2)}
+    ang_stats = {k: {"k": float(20 + 60 * r(1)), "x_0": float(-0.8 + 1.0 * r(1))} for k in itertools.product(range(T), repeat=3)}
+    dih_stats = {k: {"v_0": float(r(1)), "k1s": {f"k1_{i}": float(r(1) - 0.5) for i in (1, 2, 3)},
+                     "k2s": {f"k2_{i}": float(r(1) - 0.5) for i in (1, 2, 3)}} for k in itertools.product(range(T), repeat=4)}
+    rep_stats = {k: {"sigma": float(3.0 + 2.0 * r(1))} for k in itertools.product(range(T), repeat=2)}
+    priors = {"bonds": harmonic.HarmonicBonds(bond_stats), "angles": harmonic.HarmonicAngles(ang_stats),
+              "dihedrals": fourier.Dihedral(dih_stats, n_degs=3), "repulsion": repulsion.Repulsion(rep_stats)}
+    boxes = {"orthorhombic": (torch.tensor([[13.0, 0, 0], [0, 15.0, 0], [0, 0, 17.0]]), [True, True, True]),
+             "slab": (torch.tensor([[13.0, 0, 0], [0, 15.0, 0], [0, 0, 17.0]]), [True, True, False]),
+             "triclinic": (torch.tensor([[13.0, 0, 0], [3.0, 15.0, 0], [2.0, -2.5, 17.0]]), [True, True, True])}
+    out = dict(tables={k: {bk: bv.clone() for bk, bv in p.state_dict().items()} for k, p in priors.items()}, n=n, B=B, T=T,
+               stats=dict(bonds=bond_stats, angles=ang_stats, dihedrals=dih_stats, repulsion=rep_stats))
+    for name, (cell, pbc) in boxes.items():
+        cells = torch.stack([cell, cell * 1.15])
+        free = torch.cat([chain(n, jitter=0.3, gen=gen) + 6.0 for _ in range(B)]).view(B, n, 3)
+        # wrap into the cell along the periodic directions (fractional coordinates modulo 1)
+        frac = torch.einsum("bnd,bdk->bnk", free, torch.linalg.inv(cells))
+        frac = torch.where(torch.tensor(pbc)[None, None, :], frac - torch.floor(frac), frac)
+        pos = torch.einsum("bnk,bkd->bnd", frac, cells).reshape(-1, 3)
+        types_ = torch.randint(0, T, (B * n,), generator=gen)
+        batch = torch.arange(B).repeat_interleave(n)
+        nls = {k: nl(torch.cat([m + b * n for b in range(B)], dim=1), torch.arange(B).repeat_interleave(m.shape[1])) for k, m in per.items()}
+        case = dict(cells=cells, pbc=torch.tensor([pbc] * B), pos=pos, atom_types=types_, batch=batch, energy={}, forces={},
+                    mappings={k: v["index_mapping"] for k, v in nls.items()}, mapping_batch={k: v["mapping_batch"] for k, v in nls.items()})
+        for k, p in priors.items():
+            d = AtomicData(pos=pos.clone(), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list=dict(nls),
+                           cell=cells.clone(), pbc=case["pbc"].clone())
+            o = GradientsOut(p, "forces")(d)
+            case["energy"][k], case["forces"][k] = o.out[k]["energy"].detach(), o.out[k]["forces"].detach()
+            free_d = AtomicData(pos=pos.clone(), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list=dict(nls))
+            e_open = GradientsOut(p, "forces")(free_d).out[k]["energy"].detach()
+            print(name, k, "periodic", [round(v, 3) for v in case["energy"][k].tolist()], "open", [round(v, 3) for v in e_open.tolist()])
+        out[name] = case
+    path = os.path.join(HERE, "reference_vectors_priors_periodic.pt")
+    torch.save(out, path)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 def avoiding_chain(n, gen, step=3.8, min_dist=4.0):
     """3.8 A random walk; a step is redrawn while the new bead is closer than ``min_dist`` to any bead except its predecessor
     (five beads back after 200 failures)."""
@@ -357,6 +416,10 @@ def main_fullwidth(ref_src):
         loss.backward()
         c["target_forces"], c["loss"] = target, loss.detach()
         c["param_grads"] = {k: p.grad.detach().clone() for k, p in model.named_parameters() if p.grad is not None and (keep is None or keep(k))}
+        # the same float32 weights and positions evaluated in double precision: the value every float32 evaluation rounds towards
+        mk64 = lambda: AtomicData(pos=pos.clone().double(), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list={})
+        res64 = GradientsOut(model.double(), "forces").eval()(mk64())
+        c["energy_f64"], c["forces_f64"] = res64.out["SchNet"]["energy"].detach(), res64.out["SchNet"]["forces"].detach()
         if keep is not None:       # the weights are those of the case this one repeats: do not store them twice
             c["state_dict"] = {k: v for k, v in c["state_dict"].items() if keep(k)}
         out[name] = c
@@ -377,7 +440,8 @@ def main_fullwidth(ref_src):
 
 
 if __name__ == "__main__":
-    extra = {"regularized": main_regularized, "periodic": main_periodic, "attentive": main_attentive, "fullwidth": main_fullwidth}
+    extra = {"regularized": main_regularized, "periodic": main_periodic, "attentive": main_attentive, "fullwidth": main_fullwidth,
+             "priors_periodic": main_priors_periodic}
     if len(sys.argv) not in (2, 3) or (len(sys.argv) == 3 and sys.argv[2] not in extra):
-        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg> [regularized|periodic|attentive|fullwidth]")
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg> [regularized|periodic|attentive|fullwidth|priors_periodic]")
     (extra[sys.argv[2]] if len(sys.argv) == 3 else main)(sys.argv[1])

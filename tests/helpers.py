@@ -104,3 +104,21 @@ def prior_setup(n, B, T, gen, min_sep=3):
               "repulsion": bnn.Repulsion(rep)}
     data = mlcg_b200.AtomicData(pos=pos, atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list=nls)
     return data, priors
+
+
+def periodic_prior_cases(golden_priors_periodic, box, device="cpu"):
+    """(name, prior module, data) for the four priors on one box of ``reference_vectors_priors_periodic.pt``."""
+    g = golden_priors_periodic
+    c = g[box]
+    st = g["stats"]
+    priors = {"bonds": bnn.HarmonicBonds(st["bonds"]), "angles": bnn.HarmonicAngles(st["angles"]), "dihedrals": bnn.Dihedral(st["dihedrals"], n_degs=3),
+              "repulsion": bnn.Repulsion(st["repulsion"])}
+    out = []
+    for k, p in priors.items():
+        p.load_state_dict(g["tables"][k])
+        nl = {k: mlcg_b200.make_neighbor_list(k, c["mappings"][k].shape[0], c["mappings"][k].to(device), c["mapping_batch"][k].to(device))}
+        data = mlcg_b200.AtomicData(pos=c["pos"].clone().to(device), atom_types=c["atom_types"].to(device), batch=c["batch"].to(device),
+                                    n_atoms=torch.full((g["B"],), g["n"]).to(device), neighbor_list=nl, cell=c["cells"].clone().to(device),
+                                    pbc=c["pbc"].clone().to(device))
+        out.append((k, p.to(device), data))
+    return c, out

@@ -10,7 +10,7 @@ from mlcg_b200 import autograd as ag
 from mlcg_b200 import backend, nn as bnn
 from oracle.primitives import OracleBackend
 
-from helpers import attentive_schnet_from_case, data_from_case, prior_setup, regularized_schnet_from_case, schnet_from_case
+from helpers import attentive_schnet_from_case, data_from_case, periodic_prior_cases, prior_setup, regularized_schnet_from_case, schnet_from_case
 
 
 @pytest.fixture(autouse=True)
@@ -211,6 +211,47 @@ def test_priors_eval_and_train_paths_vs_reference(golden):
             assert torch.allclose(o.out[k]["energy"], c["energy"][k], rtol=1e-5), (mode, k)
             f = o.out[k]["forces"].detach()
             assert torch.allclose(f, c["forces"][k], rtol=1e-4, atol=1e-4 * float(c["forces"][k].abs().max())), (mode, k)
+
+
+@pytest.mark.parametrize("box", ["orthorhombic", "slab", "triclinic"])
+def test_priors_on_periodic_data_vs_reference(golden_priors_periodic, box):
+    """Bonds, angles, dihedrals and repulsion pairs that cross the box: the reference applies its cell shifts whenever the data
+    carry ``pbc`` and ``cell`` (harmonic.py:214-242 with base.py:5-62)."""
+    c, cases = periodic_prior_cases(golden_priors_periodic, box)
+    for mode in ("eval", "train"):
+        for k, p, data in cases:
+            m = bnn.GradientsOut(p, "forces")
+            o = (m.eval() if mode == "eval" else m.train())(data)
+            assert torch.allclose(o.out[k]["energy"].detach(), c["energy"][k], rtol=2e-5), (mode, k)
+            assert torch.allclose(o.out[k]["forces"].detach(), c["forces"][k], rtol=1e-4, atol=1e-4 * float(c["forces"][k].abs().max())), (mode, k)
+
+
+def test_two_priors_of_one_class_on_one_data_object():
+    """Each prior gathers its own per-term parameters: a second prior of the same class and name with other statistics, a
+    changed parameter table and changed bead types must all be seen (nothing stale is reused)."""
+    data, priors = prior_setup(12, 2, 3, torch.Generator().manual_seed(4))
+    a = priors["bonds"]
+    b = bnn.HarmonicBonds({k: {"k": 2.0 * v["k"], "x_0": v["x_0"] + 0.5} for k, v in
+                           {key: {"k": float(a.k[key]), "x_0": float(a.x_0[key])} for key in a.allowed_interaction_keys}.items()})
+    run = lambda p: bnn.GradientsOut(p, "forces").eval()(data).out["bonds"]["energy"].clone()
+    ea, eb = run(a), run(b)
+    assert not torch.allclose(ea, eb)
+    assert set(data.neighbor_list["bonds"].keys()) == {"tag", "order", "index_mapping", "cell_shifts", "rcut", "self_interaction", "mapping_batch"}
+    assert torch.allclose(run(a), ea)                       # the first prior again: its own parameters
+    with torch.no_grad():
+        a.k.mul_(3.0)                                        # a table edited in place
+    assert torch.allclose(run(a), 3.0 * ea, rtol=1e-5)
+    data.atom_types = (data.atom_types + 1) % 3              # other bead types on the same lists
+    want = ag_free_bond_energy(a, data)
+    assert torch.allclose(run(a), want, rtol=1e-5)
+
+
+def ag_free_bond_energy(prior, data):
+    m = data.neighbor_list["bonds"]["index_mapping"]
+    t0, t1 = data.atom_types[m[0]], data.atom_types[m[1]]
+    d = (data.pos[m[1]] - data.pos[m[0]]).norm(dim=1)
+    y = prior.k[t0, t1] * (d - prior.x_0[t0, t1]) ** 2
+    return torch.zeros(int(data.batch.max()) + 1).index_add_(0, data.neighbor_list["bonds"]["mapping_batch"], y)
 
 
 def test_sumout_additivity(golden):
