@@ -250,8 +250,12 @@ int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias
 int mlcgb_filter_forward(const void *d /* [.] */, int64_t rows, const int32_t *sel /* [rows] or NULL */,
                          const int32_t *twin /* [E] or NULL */, const mlcgb_rbf_spec *rbf /* host */, int conv_cutoff_kind,
                          double conv_lower, double conv_upper, const void *A1 /* [F,R] */, const void *b1 /* [F] */,
-                         const void *A2 /* [F,F] */, int64_t F, int precision, void *W /* [E,F] or [rows,F] */, int32_t *status,
-                         void *stream);
+                         const void *A2 /* [F,F] */, int64_t F, int precision, void *W /* [E,F] or [rows,F] */,
+                         void *h_save /* mlcgb_filter_hidden_bytes(rows) or NULL */, int32_t *status, void *stream);
+/* `h_save`: where the hidden layer tanh(phi(d) A1^T + b1) of every computed row is kept for mlcgb_filter_backward (in the
+ * kernels' own tile order; opaque to the caller).  What autograd keeps of the filter network's first layer in the reference
+ * (src/mlcg/nn/mlp.py:56-58), here at 512 bytes per computed row. */
+size_t mlcgb_filter_hidden_bytes(int64_t rows);
 /* `rows` = E and sel = twin = NULL: row k is edge k.  For a symmetric edge list the filter of an edge equals that of its
  * reverse (same distance), so the caller may pass one edge per unordered pair in `sel` (rows = E/2).  With the
  * reverse-edge map `twin` (mlcgb_edge_twin) each computed row is written to both edges of W[E,F]; without it W has
@@ -262,12 +266,14 @@ int mlcgb_filter_forward(const void *d /* [.] */, int64_t rows, const int32_t *s
 /* Backward of the above with respect to the distance, fused with the message product:
  *   gd[e] = sum_f gW[e,f] * dW[e,f]/dd_e,  gW[e,:] = xl[row0[e],:] * gagg[row1[e],:]
  * (the gradient CFConv's aggregation, src/mlcg/nn/schnet.py:346,350-368, sends back to its filters).
- * Recomputes the forward per tile; four tensor-core GEMMs per tile; nothing edge-sized is read or
- * written in HBM except d, the two index rows and gd. */
+ * With `h_saved` (what mlcgb_filter_forward left in `h_save` for the same d, rows, sel and weights): two tensor-core GEMMs per
+ * tile, two tiles in flight, nothing recomputed.  With h_saved = NULL the forward is recomputed per tile (four GEMMs) and
+ * nothing edge-sized is read or written in HBM except d, the two index rows and gd. */
 int mlcgb_filter_backward(const void *d, int64_t rows, const int32_t *sel, const int32_t *twin, const mlcgb_rbf_spec *rbf,
                           int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1, const void *A2,
                           int64_t F, int precision, const int32_t *row0, const int32_t *row1, const void *xl /* [N,F] */,
-                          const void *gagg /* [N,F] */, int64_t N, void *gd /* [E] */, int32_t *status, void *stream);
+                          const void *gagg /* [N,F] */, int64_t N, const void *h_saved /* or NULL */, void *gd /* [E] */,
+                          int32_t *status, void *stream);
 
 /* The product of the filter network's output with the per-edge cutoff, W = net(rbf) * C[:, None]
  * (src/mlcg/nn/schnet.py:341), and the contraction its derivatives need:
@@ -287,7 +293,8 @@ int mlcgb_row_dot(const void *a /* [E,F] */, const void *b /* [E,F] */, int dtyp
  * They exist so that a host pays one foreign call per block and direction: for small systems the evaluation time is the
  * launch path.  W1 [F,H] (no bias), fA1 [F,R], fb1 [F], fA2 [F,F] the filter network, W2 [H2,F], b2, W3 [H,H2], b3.
  * sel [P] one edge per unordered pair, pair_of [E] (mlcgb_pair_index), twin [E] (mlcgb_edge_twin), ptr_out / nbr_out the
- * CSR of the centre-sorted list.  xl [N,F], Wp [P,F], a [N,H2] are written by the forward and read by the backward; agg,
+ * CSR of the centre-sorted list.  xl [N,F], Wp [P,F], a [N,H2] and hsave (mlcgb_filter_hidden_bytes(P) bytes, or NULL: the
+ * backward then recomputes the filter network's hidden layer) are written by the forward and read by the backward; agg,
  * gy, gagg, gxl are scratch of the shapes [N,F], [N,H2], [N,F], [N,F].  MLCGB_E_LIMIT when N < 128 or a width is not a
  * multiple of four / beyond 128 (use the individual entry points then).
  * ---------------------------------------------------------------------------------------------- */
@@ -295,9 +302,9 @@ int mlcgb_interaction_forward(const void *x, const void *d, const int64_t *ptr_o
                               const int32_t *pair_of, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower,
                               double conv_upper, const void *W1, const void *fA1, const void *fb1, const void *fA2, const void *W2,
                               const void *b2, const void *W3, const void *b3, int64_t N, int64_t E, int64_t P, int64_t H, int64_t F,
-                              int64_t H2, int precision, void *xl, void *Wp, void *agg, void *a, void *out, int32_t *status,
-                              void *stream);
-int mlcgb_interaction_backward(const void *g, const void *a, const void *Wp, const void *xl, const void *d, const int64_t *ptr_out,
+                              int64_t H2, int precision, void *xl, void *Wp, void *hsave, void *agg, void *a, void *out,
+                              int32_t *status, void *stream);
+int mlcgb_interaction_backward(const void *g, const void *a, const void *Wp, const void *xl, const void *hsave, const void *d, const int64_t *ptr_out,
                                const int32_t *nbr_out, const int32_t *sel, const int32_t *pair_of, const int32_t *twin,
                                const int32_t *row0, const int32_t *row1, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind,
                                double conv_lower, double conv_upper, const void *W1, const void *fA1, const void *fb1,
@@ -381,11 +388,12 @@ int mlcgb_radius_graph_capacity(const void *pos, int dtype, const int64_t *ptr, 
                                 int32_t *status, void *stream);
 int mlcgb_filter_forward_counted(const void *d, int64_t E, const int64_t *rows_dev, const int32_t *sel, const int32_t *twin,
                                  const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1,
-                                 const void *b1, const void *A2, int64_t F, int precision, void *W, int32_t *status, void *stream);
+                                 const void *b1, const void *A2, int64_t F, int precision, void *W, void *h_save, int32_t *status,
+                                 void *stream);
 int mlcgb_filter_backward_counted(const void *d, int64_t E, const int64_t *rows_dev, const int32_t *sel, const int32_t *twin,
                                   const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1,
                                   const void *b1, const void *A2, int64_t F, int precision, const int32_t *row0, const int32_t *row1,
-                                  const void *xl, const void *gagg, int64_t N, void *gd,
+                                  const void *xl, const void *gagg, int64_t N, const void *h_saved, void *gd,
                                   int accumulate /* 1: add to gd (same rows as the call that set it) instead of setting it */,
                                   int32_t *status, void *stream);
 int mlcgb_schnet_eval_counted(const void *pos, const int64_t *types, const int64_t *struct_ptr, int64_t N, int64_t B,

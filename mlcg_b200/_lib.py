@@ -71,8 +71,8 @@ SIGNATURES = {
     "mlcgb_row_scale": (c_int, [c_vp, c_vp, c_int, c_i64, c_i64, c_vp, c_vp]),
     "mlcgb_row_dot": (c_int, [c_vp, c_vp, c_int, c_i64, c_i64, c_vp, c_vp]),
     "mlcgb_gemm_tc_tn_colsum": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp]),
-    "mlcgb_interaction_forward": (c_int, [c_vp] * 6 + [c_vp, c_int, c_dbl, c_dbl] + [c_vp] * 8 + [c_i64] * 6 + [c_int] + [c_vp] * 7),
-    "mlcgb_interaction_backward": (c_int, [c_vp] * 12 + [c_vp, c_int, c_dbl, c_dbl] + [c_vp] * 6 + [c_i64] * 6 + [c_int] + [c_vp] * 7),
+    "mlcgb_interaction_forward": (c_int, [c_vp] * 6 + [c_vp, c_int, c_dbl, c_dbl] + [c_vp] * 8 + [c_i64] * 6 + [c_int] + [c_vp] * 8),
+    "mlcgb_interaction_backward": (c_int, [c_vp] * 13 + [c_vp, c_int, c_dbl, c_dbl] + [c_vp] * 6 + [c_i64] * 6 + [c_int] + [c_vp] * 7),
     "mlcgb_schnet_eval_workspace_bytes": (c_sz, [c_i64] * 8),
     "mlcgb_radius_pbc_workspace_bytes": (c_sz, [c_i64]),
     "mlcgb_radius_pbc_count": (c_int, [c_vp, c_int, c_vp, c_i64, c_i64, c_vp, c_vp, c_dbl, c_i64, c_int, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]),
@@ -81,17 +81,19 @@ SIGNATURES = {
     "mlcgb_radius_graph_capacity": (c_int, [c_vp, c_int, c_vp, c_i64, c_i64, c_dbl, c_i64, c_int, c_int, c_vp, c_sz, c_vp, c_vp, c_i64, c_vp, c_vp,
                                             c_vp, c_vp, c_vp, c_vp]),
     "mlcgb_filter_forward_counted": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, ctypes.POINTER(RbfSpecStruct), c_int, c_dbl, c_dbl, c_vp, c_vp, c_vp, c_i64,
-                                             c_int, c_vp, c_vp, c_vp]),
+                                             c_int, c_vp, c_vp, c_vp, c_vp]),
+    "mlcgb_filter_hidden_bytes": (c_sz, [c_i64]),
     "mlcgb_filter_backward_counted": (c_int, [c_vp, c_i64, c_vp, c_vp, c_vp, ctypes.POINTER(RbfSpecStruct), c_int, c_dbl, c_dbl, c_vp, c_vp, c_vp, c_i64,
-                                              c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_int, c_vp, c_vp]),
+                                              c_int, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_int, c_vp, c_vp]),
     "mlcgb_schnet_eval_counted": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_int, c_dbl,
                                           c_dbl, c_vp, c_int, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]),
     "mlcgb_schnet_eval": (c_int, [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_int, c_dbl, c_dbl,
                                   c_vp, c_int, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]),
     "mlcgb_gemm_tc_fused": (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp]),
-    "mlcgb_filter_forward": (c_int, [c_vp, c_i64, c_vp, c_vp, ctypes.POINTER(RbfSpecStruct), c_int, c_dbl, c_dbl, c_vp, c_vp, c_vp, c_i64, c_int, c_vp, c_vp, c_vp]),
+    "mlcgb_filter_forward": (c_int, [c_vp, c_i64, c_vp, c_vp, ctypes.POINTER(RbfSpecStruct), c_int, c_dbl, c_dbl, c_vp, c_vp, c_vp, c_i64, c_int, c_vp, c_vp, c_vp,
+                                     c_vp]),
     "mlcgb_filter_backward": (c_int, [c_vp, c_i64, c_vp, c_vp, ctypes.POINTER(RbfSpecStruct), c_int, c_dbl, c_dbl, c_vp, c_vp, c_vp, c_i64, c_int,
-                                      c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
+                                      c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp]),
     "mlcgb_segment_sum": (c_int, [c_vp, c_int, c_vp, c_i64, c_vp, c_vp]),
     "mlcgb_langevin_first_half": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_dbl, c_dbl, c_dbl, c_vp]),
     "mlcgb_langevin_second_half": (c_int, [c_vp, c_vp, c_vp, c_int, c_i64, c_dbl, c_vp]),

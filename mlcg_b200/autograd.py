@@ -387,13 +387,15 @@ class FusedFilterConv(torch.autograd.Function):
     def forward(ctx, xl, d, A1, b1, A2, plan: EdgePlan, spec: RbfSpec, conv_cut, precision: int):
         be = get_backend()
         sel = plan.half_selection()
-        W, status = be.filter_forward(d, spec, conv_cut[0], conv_cut[1], conv_cut[2], A1, b1, A2, precision, sel, None)
+        keep = bool(ctx.needs_input_grad[1])  # the hidden layer is kept only when the distance gradient will be asked for
+        W, status, *hs = be.filter_forward(d, spec, conv_cut[0], conv_cut[1], conv_cut[2], A1, b1, A2, precision, sel, None, save_hidden=keep)
         be.defer_status(status, "fused filter network (forward)")
         if sel is not None:   # W[pair]; grouping by row1 read as the grouping by row0 of the reversed edges
             agg = be.seg_mul_sum(xl, W, plan.ptr_out, plan.nbr_out, plan.pair_index(), plan.N)
         else:
             agg = be.seg_mul_sum(xl, W, plan.ptr_in, plan.nbr_in, plan.perm_in, plan.N)
         ctx.plan, ctx.spec, ctx.conv_cut, ctx.precision = plan, spec, conv_cut, precision
+        ctx.hidden = hs[0] if hs else None
         ctx.save_for_backward(xl, d, W, A1, b1, A2)
         return agg
 
@@ -410,7 +412,7 @@ class FusedFilterConv(torch.autograd.Function):
         gd = None
         if ctx.needs_input_grad[1]:     # d(e) and d(reverse(e)) are the same distance: one gradient per pair
             gd, status = be.filter_backward(d, ctx.spec, ctx.conv_cut[0], ctx.conv_cut[1], ctx.conv_cut[2], A1, b1, A2, plan.row0, plan.row1,
-                                            xl, g, ctx.precision, sel, plan.perm_in if sel is not None else None)
+                                            xl, g, ctx.precision, sel, plan.perm_in if sel is not None else None, hidden=ctx.hidden)
             be.defer_status(status, "fused filter network (backward)")
         return gxl, gd, None, None, None, None, None, None, None
 
@@ -430,12 +432,16 @@ class FusedInteraction(torch.autograd.Function):
         ctx.plan, ctx.spec, ctx.conv_cut, ctx.precision = plan, spec, conv_cut, precision
         if be.interaction_ok(x, plan, x.shape[1], W1.shape[0], W2.shape[0]):        # the whole block in one library call
             d = d.contiguous()
-            out, xl, W, a = be.interaction_forward(x, d, plan, spec, conv_cut, W1, fA1, fb1, fA2, W2, b2, W3, b3, precision)
+            out, xl, W, a, hs = be.interaction_forward(x, d, plan, spec, conv_cut, W1, fA1, fb1, fA2, W2, b2, W3, b3, precision,
+                                                       save_hidden=bool(ctx.needs_input_grad[1]))
+            ctx.hidden = hs
             ctx.save_for_backward(xl, d, W, a, W1, fA1, fb1, fA2, W2, W3)
             return out
         xl = be.gemm(0, x, W1)
         sel = plan.half_selection()
-        W, status = be.filter_forward(d, spec, conv_cut[0], conv_cut[1], conv_cut[2], fA1, fb1, fA2, precision, sel, None)
+        W, status, *hs = be.filter_forward(d, spec, conv_cut[0], conv_cut[1], conv_cut[2], fA1, fb1, fA2, precision, sel, None,
+                                           save_hidden=bool(ctx.needs_input_grad[1]))
+        ctx.hidden = hs[0] if hs else None
         be.defer_status(status, "fused filter network (forward)")
         if sel is not None:
             agg = be.seg_mul_sum(xl, W, plan.ptr_out, plan.nbr_out, plan.pair_index(), plan.N)
@@ -454,7 +460,7 @@ class FusedInteraction(torch.autograd.Function):
         plan, be = ctx.plan, get_backend()
         g = g.contiguous()
         if be.interaction_ok(g, plan, g.shape[1], W1.shape[0], W2.shape[0]):
-            gx, gd = be.interaction_backward(g, a, W, xl, d, plan, ctx.spec, ctx.conv_cut, W1, fA1, fb1, fA2, W2, W3, ctx.precision,
+            gx, gd = be.interaction_backward(g, a, W, xl, ctx.hidden, d, plan, ctx.spec, ctx.conv_cut, W1, fA1, fb1, fA2, W2, W3, ctx.precision,
                                              ctx.needs_input_grad[0], ctx.needs_input_grad[1])
             return (gx, gd) + (None,) * 12
         gy = be.gemm_fused(1, g, W3, None, a, be.EPI_TANH_GRAD)        # through lin and the activation
@@ -466,7 +472,7 @@ class FusedInteraction(torch.autograd.Function):
             gx = be.gemm_fused(1, gxl, W1, None, g, be.EPI_ADD)        # through lin1, plus the residual branch
         if ctx.needs_input_grad[1]:
             gd, status = be.filter_backward(d, ctx.spec, ctx.conv_cut[0], ctx.conv_cut[1], ctx.conv_cut[2], fA1, fb1, fA2, plan.row0, plan.row1,
-                                            xl, gagg, ctx.precision, sel, plan.perm_in if sel is not None else None)
+                                            xl, gagg, ctx.precision, sel, plan.perm_in if sel is not None else None, hidden=ctx.hidden)
             be.defer_status(status, "fused filter network (backward)")
         return (gx, gd) + (None,) * 12
 

@@ -569,8 +569,9 @@ class CudaBackend:
         return (self.profiler is None and self.tensor_core_gemm and x.dtype == torch.float32 and x.shape[0] >= 128 and F == 128
                 and H <= 128 and H2 <= 128 and H % 4 == 0 and H2 % 4 == 0 and plan.half_selection() is not None)
 
-    def interaction_forward(self, x, d, plan, spec: RbfSpec, conv_cut, W1, fA1, fb1, fA2, W2, b2, W3, b3, precision):
-        """x + lin(tanh(lin2(aggregate(lin1(x), W(d))))) in one library call; returns (x_new, xl, Wp, a)."""
+    def interaction_forward(self, x, d, plan, spec: RbfSpec, conv_cut, W1, fA1, fb1, fA2, W2, b2, W3, b3, precision, save_hidden=True):
+        """x + lin(tanh(lin2(aggregate(lin1(x), W(d))))) in one library call; returns (x_new, xl, Wp, a, hs) with ``hs`` the
+        filter network's hidden layer kept for the backward (None when ``save_hidden`` is off: the backward recomputes it)."""
         N, H = x.shape
         W1, fA1, fb1, fA2, W2, b2, W3, b3 = (t.contiguous() for t in (W1, fA1, fb1, fA2, W2, b2, W3, b3))
         F, H2 = W1.shape[0], W2.shape[0]
@@ -579,17 +580,18 @@ class CudaBackend:
         s, keep = self._spec(spec, torch.float32)
         new = lambda *shape: torch.empty(shape, dtype=torch.float32, device=dev)
         xl, Wp, agg, a, out = new(N, F), new(P, F), new(N, F), new(N, H2), new(N, H)
+        hs = new(self.lib.mlcgb_filter_hidden_bytes(P) // 4) if save_hidden else None
         status = self._sticky_status(dev)
         with _on(dev):
             _lib.check(self.lib.mlcgb_interaction_forward(
                 _ptr(x), _ptr(d), _ptr(plan.ptr_out), _ptr(plan.nbr_out), _ptr(sel), _ptr(pair_of), ctypes.byref(s), int(conv_cut[0]),
                 float(conv_cut[1]), float(conv_cut[2]), _ptr(W1), _ptr(fA1), _ptr(fb1), _ptr(fA2), _ptr(W2), _ptr(b2), _ptr(W3), _ptr(b3),
-                N, plan.E, P, H, F, H2, int(precision), _ptr(xl), _ptr(Wp), _ptr(agg), _ptr(a), _ptr(out), _ptr(status), _stream()),
+                N, plan.E, P, H, F, H2, int(precision), _ptr(xl), _ptr(Wp), _ptr(hs), _ptr(agg), _ptr(a), _ptr(out), _ptr(status), _stream()),
                 "interaction_forward")
         self.defer_status(status, "interaction block (forward)")
-        return out, xl, Wp, a
+        return out, xl, Wp, a, hs
 
-    def interaction_backward(self, g, a, Wp, xl, d, plan, spec: RbfSpec, conv_cut, W1, fA1, fb1, fA2, W2, W3, precision, want_gx=True, want_gd=True):
+    def interaction_backward(self, g, a, Wp, xl, hs, d, plan, spec: RbfSpec, conv_cut, W1, fA1, fb1, fA2, W2, W3, precision, want_gx=True, want_gd=True):
         N, H = g.shape
         W1, fA1, fb1, fA2, W2, W3 = (t.contiguous() for t in (W1, fA1, fb1, fA2, W2, W3))
         F, H2 = W1.shape[0], W2.shape[0]
@@ -603,7 +605,7 @@ class CudaBackend:
         status = self._sticky_status(dev)
         with _on(dev):
             _lib.check(self.lib.mlcgb_interaction_backward(
-                _ptr(g), _ptr(a), _ptr(Wp), _ptr(xl), _ptr(d), _ptr(plan.ptr_out), _ptr(plan.nbr_out), _ptr(sel), _ptr(pair_of),
+                _ptr(g), _ptr(a), _ptr(Wp), _ptr(xl), _ptr(hs), _ptr(d), _ptr(plan.ptr_out), _ptr(plan.nbr_out), _ptr(sel), _ptr(pair_of),
                 _ptr(plan.perm_in), _ptr(plan.row0), _ptr(plan.row1), ctypes.byref(s), int(conv_cut[0]), float(conv_cut[1]), float(conv_cut[2]),
                 _ptr(W1), _ptr(fA1), _ptr(fb1), _ptr(fA2), _ptr(W2), _ptr(W3), N, plan.E, P, H, F, H2, int(precision),
                 _ptr(gy), _ptr(gagg), _ptr(gxl), _ptr(gx), _ptr(gd), _ptr(status), _stream()),
@@ -636,10 +638,12 @@ class CudaBackend:
         return energy, grad
 
     # ------------------------------------------------------------------ fused filter network (tensor cores)
-    def filter_forward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, precision=0, sel=None, twin=None):
+    def filter_forward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, precision=0, sel=None, twin=None, save_hidden=False):
         """W[E,F] = (tanh(phi(d) A1^T + b1) A2^T) * C(d); float32, F = 128, R <= 128.
         ``sel`` / ``twin``: compute one row per unordered pair and write it to both edges (symmetric edge lists);
-        ``sel`` alone: W has one row per selected edge, in the order of ``sel``."""
+        ``sel`` alone: W has one row per selected edge, in the order of ``sel``.
+        Returns ``(W, status)``, or ``(W, status, hidden)`` with ``save_hidden``: the first layer's output kept (in the kernels'
+        own order) for :meth:`filter_backward`."""
         _need_cuda(d, A1, b1, A2, spec.p0, spec.p1)
         if d.dtype != torch.float32:
             raise TypeError("filter_forward is a float32 kernel")
@@ -648,17 +652,19 @@ class CudaBackend:
         E, F = d.numel(), A2.shape[0]
         rows = E if sel is None else sel.numel()
         W = torch.empty((E if (sel is None or twin is not None) else rows, F), dtype=d.dtype, device=d.device)
+        hs = torch.empty(self.lib.mlcgb_filter_hidden_bytes(rows) // 4, dtype=torch.float32, device=d.device) if save_hidden else None
         status = self._sticky_status(d.device)
         with _on(d.device):
             self._run("filter_forward", self.lib.mlcgb_filter_forward,
                       (_ptr(d), rows, _ptr(sel), _ptr(twin), ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
-                       int(precision), _ptr(W), _ptr(status), _stream()),
-                      nbytes=W.shape[0] * 4 * F + 4 * rows, flops=2 * rows * F * (spec.num_rbf + F))
-        return W, status
+                       int(precision), _ptr(W), _ptr(hs), _ptr(status), _stream()),
+                      nbytes=W.shape[0] * 4 * F + 4 * rows + (hs.numel() * 4 if save_hidden else 0), flops=2 * rows * F * (spec.num_rbf + F))
+        return (W, status, hs) if save_hidden else (W, status)
 
     def filter_backward(self, d, spec: RbfSpec, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, row0, row1, xl, gagg, precision=0,
-                        sel=None, twin=None):
-        """gd[E] = sum_f (xl[row0] * gagg[row1])_f * dW_f/dd."""
+                        sel=None, twin=None, hidden=None):
+        """gd[E] = sum_f (xl[row0] * gagg[row1])_f * dW_f/dd.  ``hidden``: what :meth:`filter_forward` kept for the same
+        distances, selection and weights (the hidden layer is recomputed without it)."""
         _need_cuda(d, A1, b1, A2, row0, row1, xl, gagg)
         d, A1, b1, A2 = d.contiguous(), A1.detach().contiguous(), b1.detach().contiguous(), A2.detach().contiguous()
         xl, gagg = xl.detach().contiguous(), gagg.detach().contiguous()
@@ -670,8 +676,8 @@ class CudaBackend:
         with _on(d.device):
             self._run("filter_backward", self.lib.mlcgb_filter_backward,
                       (_ptr(d), rows, _ptr(sel), _ptr(twin), ctypes.byref(s), int(conv_cutoff_kind), float(conv_lower), float(conv_upper), _ptr(A1), _ptr(b1), _ptr(A2), F,
-                       int(precision), _ptr(row0), _ptr(row1), _ptr(xl), _ptr(gagg), xl.shape[0], _ptr(gd), _ptr(status), _stream()),
-                      nbytes=E * 16 + 2 * xl.numel() * 4, flops=2 * rows * F * 2 * (spec.num_rbf + F))
+                       int(precision), _ptr(row0), _ptr(row1), _ptr(xl), _ptr(gagg), xl.shape[0], _ptr(hidden), _ptr(gd), _ptr(status), _stream()),
+                      nbytes=E * 16 + 2 * xl.numel() * 4 + (hidden.numel() * 4 if hidden is not None else 0), flops=2 * rows * F * 2 * (spec.num_rbf + F))
         return gd, status
 
     def segment_sum(self, x, ptr):

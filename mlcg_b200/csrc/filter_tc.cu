@@ -38,8 +38,14 @@ struct FilterFwdParams {
     const float *b1;     // [kF]
     const float *A2;     // [kF][kF]
     float *W;            // [E][kF]
+    float *H;            // NULL, or where the forward keeps h = tanh(phi A1^T + b1) for the backward (hidden_offset() order)
     int32_t *status;
 };
+
+// The hidden layer of a tile is kept in the order the threads hold it: thread (row r, 32-column quarter q) owns eight 16-byte
+// chunks j; chunk (q, j) of all 128 rows is contiguous, so both kernels move it with fully coalesced 128-bit accesses and
+// no staging.  Offset, in float4 units, of chunk j of quarter q of row r of tile t; a tile takes 16384 floats.
+__device__ __forceinline__ int64_t hidden_offset(int64_t tile, int q, int j, int r) { return ((tile * 4 + q) * 8 + j) * 128 + r; }
 
 // rows the kernel works on; read after the wait on the preceding kernels
 __device__ __forceinline__ int64_t live_rows(const FilterFwdParams &p) {
@@ -59,6 +65,9 @@ struct FilterSmem {
     // fp32 staging tile for coalesced global traffic: in the A region (free when the A operands live in TMEM) or its own
     static constexpr int kStage = SPLIT ? kA : kMisc + 7168;
     static constexpr int kTotal = kMisc + 7168 + (SPLIT ? 0 : kStageBytes) + 1024;   // + alignment slack
+    // the backward that reads the saved hidden layer: two more [4][128] f32 exchange arrays behind everything else
+    static constexpr int kExtra = kMisc + 7168 + (SPLIT ? 0 : kStageBytes);
+    static constexpr int kTotalExtra = kExtra + 4096 + 1024;
 };
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -304,6 +313,11 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
             tmem_ld_cols<NC>(t_lane + col0, v);
             tanh_row32<SPLIT, NC>(v, s_b1 + kF, col0, unscale * (2.f * kLog2e));
             store_a_tmem_cols<SPLIT, NC>(ta + lane_off, col0, v, 1.f);
+            if (NC == 32 && p.H) {                               // kept for the backward (rows past the end hold finite filler)
+                float4 *hb = reinterpret_cast<float4 *>(p.H);
+#pragma unroll
+                for (int j = 0; j < NC / 4; j++) hb[hidden_offset(tile, col0 >> 5, j, r)] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
             tmem_wait_st();
         }
         bulk_wait_read<0>();                                     // the copies of (a) have read the stage
@@ -376,6 +390,7 @@ struct FilterBwdParams {
     FilterFwdParams f;       // d, E, rbf, conv, A1, b1, A2, status (W unused)
     const int32_t *row0, *row1;
     const float *xl, *gagg;  // [N][kF]
+    const float *H;          // NULL (recompute the forward per tile), or the hidden layer the forward kept
     float *gd;               // [E]
     int accumulate;          // 0: gd[e] is set (and the reverse edge's entry zeroed in pair mode); 1: added to what gd holds
 };
@@ -676,6 +691,320 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
     if (warp == 0) tmem_free(tmem, 512);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Backward with the forward's hidden layer at hand (FilterBwdParams::H): nothing of the forward is recomputed and two GEMMs
+// per tile remain,
+//   GH' = gW A2        gC = sum_k h_k GH'_k        gz = C(d) GH' (1 - h^2)        GPHI = gz A1
+//   gd  = sum_r GPHI_r phi'_r(d) + gC C'(d)
+// (gC is sum_f gW_f y_f of the kernel above: y = h A2^T, so sum_f gW_f y_f = sum_k h_k (gW A2)_k — the filter output is not
+// needed either.)  A tile holds one accumulator block and one operand block of tensor memory, so two tiles are in flight
+// and the tensor core works on one tile while the threads work on the other:
+//
+//   iteration j:   B(j)   wait GH'(j); gC, gz -> operand; issue GPHI(j)
+//                  C(j)   basis derivatives under that GEMM; wait; reduce; store gd
+//                  A(j+2) gather gW of tile j+2 into the slot tile j has left, issue GH'(j+2)
+//
+// GH'(j+1), issued an iteration earlier, has the whole of B(j) and C(j) to finish.  The index rows and distances of a tile
+// are loaded two iterations, its edge ids three iterations before they are used; the hidden rows are prefetched into L2
+// one phase ahead and loaded at the top of the iteration.
+// ------------------------------------------------------------------------------------------------
+template <bool SPLIT>
+__global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_saved_kernel(FilterBwdParams q) {
+    using namespace tc;
+    using L = FilterSmem<SPLIT>;
+    const FilterFwdParams &p = q.f;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *stage = SPLIT ? smem + L::kA : smem + L::kStage;
+    const float2 *s_tab = reinterpret_cast<const float2 *>(smem + L::kMisc + L::kTable);
+    float *s_redA = reinterpret_cast<float *>(smem + L::kMisc + L::kRed);       // row maxima of gW
+    float *s_redB = reinterpret_cast<float *>(smem + L::kMisc + L::kRed2);      // row maxima of gz
+    float *s_redB2 = reinterpret_cast<float *>(smem + L::kExtra);               // partial sums of gC
+    float *s_redC = reinterpret_cast<float *>(smem + L::kExtra + 2048);         // partial sums of gd
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar);
+    uint64_t *s_bars = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar + 64);   // GH' of slot 0, 1; GPHI of slot 0, 1
+    int *s_err = reinterpret_cast<int *>(reinterpret_cast<uint32_t *>(s_bar + 1) + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = tid & 127, qt = tid >> 7, col0 = qt * 32;
+    const int R = p.rbf.R;
+    const int Kpad1 = R <= 64 ? 64 : 128;
+    const float wscale = SPLIT ? kWScale : 1.f;
+
+    const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 512);
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) mbar_init(smem_u32(s_bars + i), 1);
+    }
+    __syncthreads();
+    pdl_wait();                    // set-up done (weights only); everything below reads what earlier kernels wrote
+    pdl_launch_dependents();
+    const int64_t nE = live_rows(p);
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t t_lane = tmem + lane_off;
+    // tensor memory: accumulator of slot s at columns [128 s, 128 s + 128), operand of slot s at [256 + 128 s, ...)
+    const uint32_t b1_hi = smem_u32(smem + L::kB1), b1_lo = b1_hi + 32768, b2_hi = smem_u32(smem + L::kB2), b2_lo = b2_hi + 32768;
+    bool failed = false;
+
+    const bool same_env = p.conv.cutoff_kind == p.rbf.cutoff_kind && p.conv.lower == p.rbf.lower && p.conv.upper == p.rbf.upper;
+    auto row_group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + (warp & 3)) : "memory"); };
+    struct EdgeScalars { float t, dt, e0, e1, c0, c1; };
+    auto scalars = [&](float de) {
+        EdgeScalars s;
+        edge_arg(de, p.rbf, s.t, s.dt);
+        const Jet<float, 1> env = envelope_jet<float, 1>(de, p.rbf);
+        s.e0 = env.c[0];
+        s.e1 = env.c[1];
+        if (same_env) {
+            s.c0 = s.e0;
+            s.c1 = s.e1;
+        } else {
+            const Jet<float, 1> cj = envelope_jet<float, 1>(de, p.conv);
+            s.c0 = cj.c[0];
+            s.c1 = cj.c[1];
+        }
+        return s;
+    };
+    const bool paired = p.sel && p.twin;          // one row per unordered pair: both directions' gW are summed
+    const int64_t ntiles = (nE + kRows - 1) / kRows;
+    const int64_t first = blockIdx.x, step = gridDim.x;
+    const int64_t n_local = first < ntiles ? (ntiles - first + step - 1) / step : 0;
+    auto tile_of = [&](int64_t j) { return first + j * step; };
+    auto edge_of = [&](int64_t j) -> int32_t {      // edge handled by this thread's row of local tile j (-1: past the end)
+        if (j >= n_local) return -1;
+        const int64_t krow = tile_of(j) * kRows + r;
+        if (krow >= nE) return -1;
+        return p.sel ? p.sel[krow] : (int32_t)krow;
+    };
+
+    // gW = xl[row0] * gagg[row1] (+ the reverse edge's product in pair mode) of one tile -> operand block `ta`, rows scaled by
+    // a power of two; returns the row's scale.  Four rows per load instruction, turned row-per-lane through this warp's own
+    // 32 x 32 block of the stage.
+    auto gather_pack = [&](int32_t i0, int32_t i1, bool live, uint32_t ta) -> float {
+        const int sub = lane >> 3, cc = (col0 >> 2) + (lane & 7);
+        auto gather = [&](auto paired_tag) {
+            constexpr bool kPaired = decltype(paired_tag)::value;
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                float4 a[4], b[4], a2[4], b2[4];
+                float m[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int rl = (half * 4 + u) * 4 + sub;
+                    const int64_t j0 = __shfl_sync(0xffffffffu, i0, rl), j1 = __shfl_sync(0xffffffffu, i1, rl);
+                    m[u] = __shfl_sync(0xffffffffu, (int)live, rl) ? 1.f : 0.f;
+                    a[u] = __ldg(reinterpret_cast<const float4 *>(q.xl + j0 * kF) + cc);
+                    b[u] = __ldg(reinterpret_cast<const float4 *>(q.gagg + j1 * kF) + cc);
+                    if (kPaired) {   // the reverse edge: xl[row1] * gagg[row0]
+                        a2[u] = __ldg(reinterpret_cast<const float4 *>(q.xl + j1 * kF) + cc);
+                        b2[u] = __ldg(reinterpret_cast<const float4 *>(q.gagg + j0 * kF) + cc);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int rl = (half * 4 + u) * 4 + sub;
+                    float4 gw = make_float4(a[u].x * b[u].x * m[u], a[u].y * b[u].y * m[u], a[u].z * b[u].z * m[u], a[u].w * b[u].w * m[u]);
+                    if (kPaired) {
+                        gw.x = fmaf(a2[u].x * b2[u].x, m[u], gw.x); gw.y = fmaf(a2[u].y * b2[u].y, m[u], gw.y);
+                        gw.z = fmaf(a2[u].z * b2[u].z, m[u], gw.z); gw.w = fmaf(a2[u].w * b2[u].w, m[u], gw.w);
+                    }
+                    *stage_chunk(stage, (r & ~31) + rl, cc) = gw;
+                }
+            }
+        };
+        if (paired) gather(std::true_type{});
+        else gather(std::false_type{});
+        __syncwarp();
+        float g[32];
+        float rmax = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const float4 gw4 = *stage_chunk(stage, r, (col0 >> 2) + w);
+            g[4 * w] = gw4.x; g[4 * w + 1] = gw4.y; g[4 * w + 2] = gw4.z; g[4 * w + 3] = gw4.w;
+            rmax = fmaxf(fmaxf(rmax, fmaxf(fabsf(gw4.x), fabsf(gw4.y))), fmaxf(fabsf(gw4.z), fabsf(gw4.w)));
+        }
+        __syncwarp();
+        s_redA[qt * 128 + r] = rmax;
+        row_group_sync();
+        const float sc = SPLIT ? row_scale(fmaxf(fmaxf(s_redA[r], s_redA[128 + r]), fmaxf(s_redA[256 + r], s_redA[384 + r]))) : 1.f;
+        store_a_tmem<SPLIT>(ta + lane_off, col0, g, sc);
+        tmem_wait_st();
+        return sc;
+    };
+    // one GEMM of slot s after everybody's operand stores are visible; returns false for every thread if a wait has run out
+    auto issue = [&](int s, bool gphi) -> bool {
+        if (failed) s_err[0] = 1;
+        tc_fence_before();
+        __syncthreads();
+        if (s_err[0]) return false;
+        if (tid == 0) {
+            tc_fence_after();
+            if (gphi) issue_gemm_ts<SPLIT>(tmem + 128 * s, tmem + 256 + 128 * s, b1_hi, b1_lo, kF / 16, 1, Kpad1);
+            else issue_gemm_ts<SPLIT>(tmem + 128 * s, tmem + 256 + 128 * s, b2_hi, b2_lo, kF / 16, 1, 128);
+            mma_commit(smem_u32(s_bars + (gphi ? 2 : 0) + s));
+        }
+        return true;
+    };
+    auto prefetch_hidden = [&](int64_t j) {      // the tile's 64 KB of hidden rows into L2, one 128-byte line per thread
+        if (j < n_local) asm volatile("prefetch.global.L2 [%0];" ::"l"(q.H + tile_of(j) * (kRows * kF) + tid * 32));
+    };
+
+    // ---- state of the tiles in flight: (edge, scalars, gW scale) of tile j (being finished) and j+1 (GH' issued)
+    int32_t e_cur = -1, e_nx = -1;
+    EdgeScalars es_cur{}, es_nx{};
+    float sc3_cur = 1.f, sc3_nx = 1.f;
+    bool ok = true;
+    // prologue: gather tiles 0 and 1
+    int32_t e_a = edge_of(0), e_b = edge_of(1);
+    int32_t e_pre = edge_of(2);                   // edge id of the tile after those: its rows are loaded in the first iteration
+    {
+        const bool la = e_a >= 0, lb = e_b >= 0;
+        const int32_t a0 = la ? q.row0[e_a] : 0, a1 = la ? q.row1[e_a] : 0, b0 = lb ? q.row0[e_b] : 0, b1i = lb ? q.row1[e_b] : 0;
+        const float da = la ? p.d[e_a] : 1.f, db = lb ? p.d[e_b] : 1.f;
+        if (n_local > 0) {
+            prefetch_hidden(0);
+            e_cur = e_a;
+            es_cur = scalars(da);
+            sc3_cur = gather_pack(a0, a1, la, tmem + 256);
+            ok = issue(0, false);
+        }
+        if (ok && n_local > 1) {
+            prefetch_hidden(1);
+            e_nx = e_b;
+            es_nx = scalars(db);
+            sc3_nx = gather_pack(b0, b1i, lb, tmem + 256 + 128);
+            ok = issue(1, false);
+        }
+    }
+    for (int64_t j = 0; ok && j < n_local; j++) {
+        const int s = (int)(j & 1);
+        const uint32_t par = (uint32_t)((j >> 1) & 1);
+        const uint32_t D = 128u * s, TA = 256u + 128u * s;
+        const bool live = e_cur >= 0;
+        // ---- loads whose results are needed later: the hidden rows of this tile (B), rows and distance of tile j+2 (A below),
+        //      edge id of tile j+3 (next iteration)
+        float4 hq[8];
+        {
+            const float4 *hb = reinterpret_cast<const float4 *>(q.H);
+            const int64_t t = tile_of(j);
+#pragma unroll
+            for (int c = 0; c < 8; c++) hq[c] = hb[hidden_offset(t, qt, c, r)];
+        }
+        const int32_t e_g = e_pre;                 // tile j+2
+        const bool lg = e_g >= 0;
+        const int32_t g0 = lg ? q.row0[e_g] : 0, g1 = lg ? q.row1[e_g] : 0;
+        const float dg = lg ? p.d[e_g] : 1.f;
+        e_pre = edge_of(j + 3);
+
+        // ---- B(j): GH' done.  gC = sum h GH', gz = C GH' (1 - h^2) -> operand (row-scaled); issue GPHI = gz A1
+        if (!mbar_wait(smem_u32(s_bars + s), par)) failed = true;
+        tc_fence_after();
+        float g[32];
+        float gC = 0.f, rmax = 0.f;
+        {
+            const float inv3 = 1.f / (sc3_cur * wscale);
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                float v[16];
+                tmem_ld16(t_lane + D + col0 + half * 16, v);
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const float4 h4 = hq[half * 4 + c];
+                    const float hh[4] = {h4.x, h4.y, h4.z, h4.w};
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float gh = v[4 * c + i] * inv3;
+                        gC = fmaf(hh[i], gh, gC);
+                        const float gz = es_cur.c0 * gh * fmaf(-hh[i], hh[i], 1.f);
+                        g[half * 16 + 4 * c + i] = gz;
+                        rmax = fmaxf(rmax, fabsf(gz));
+                    }
+                }
+            }
+        }
+        s_redB[qt * 128 + r] = rmax;
+        s_redB2[qt * 128 + r] = gC;
+        row_group_sync();
+        gC = (s_redB2[r] + s_redB2[128 + r]) + (s_redB2[256 + r] + s_redB2[384 + r]);
+        const float sc4 = SPLIT ? row_scale(fmaxf(fmaxf(s_redB[r], s_redB[128 + r]), fmaxf(s_redB[256 + r], s_redB[384 + r]))) : 1.f;
+        store_a_tmem<SPLIT>(tmem + TA + lane_off, col0, g, sc4);
+        tmem_wait_st();
+        if (!(ok = issue(s, true))) break;
+
+        // ---- C(j), under GPHI: basis derivatives phi'_k = g_k (env' - env 2 ln2 w_k (t - c_k) t') for this thread's columns
+        if (col0 < Kpad1) {
+            const float m2 = -2.f * kLn2 * es_cur.dt * es_cur.e0;
+            const float4 *tab4 = reinterpret_cast<const float4 *>(s_tab + col0);
+#pragma unroll
+            for (int c = 0; c < 16; c++) {
+                const float4 cw = tab4[c];
+                const float u0 = es_cur.t - cw.x, wu0 = cw.y * u0, u1 = es_cur.t - cw.z, wu1 = cw.w * u1;
+                g[2 * c] = ex2_fast(-wu0 * u0) * fmaf(m2, wu0, es_cur.e1);      // columns at or beyond R: exactly 0
+                g[2 * c + 1] = ex2_fast(-wu1 * u1) * fmaf(m2, wu1, es_cur.e1);
+            }
+        }
+        const float gC_dC = gC * es_cur.c1, inv4 = 1.f / (sc4 * wscale);
+        if (j + 1 < n_local) prefetch_hidden(j + 1);
+        if (!mbar_wait(smem_u32(s_bars + 2 + s), par)) failed = true;
+        tc_fence_after();
+        float acc = 0.f;
+        if (col0 < Kpad1) {
+            float v[32];
+            tmem_ld32(t_lane + D + col0, v);
+#pragma unroll
+            for (int c = 0; c < 32; c++) acc = fmaf(v[c], g[c], acc);
+            acc *= inv4;
+        }
+        if (qt == 0) acc += gC_dC;
+        s_redC[qt * 128 + r] = acc;
+        tc_fence_before();
+        row_group_sync();
+        if (qt == 0 && live) {
+            const float v = (s_redC[r] + s_redC[128 + r]) + (s_redC[256 + r] + s_redC[384 + r]);
+            if (q.accumulate) {
+                q.gd[e_cur] += v;
+            } else {
+                q.gd[e_cur] = v;
+                if (paired) q.gd[p.twin[e_cur]] = 0.f;   // the pair's whole gradient is carried by one of its two edges
+            }
+        }
+
+        // ---- A(j+2): the slot is free (GPHI(j) has been read): gather gW of tile j+2 into it and issue its GH'
+        e_cur = e_nx;
+        es_cur = es_nx;
+        sc3_cur = sc3_nx;
+        if (j + 2 < n_local) {
+            e_nx = e_g;
+            es_nx = scalars(dg);
+            sc3_nx = gather_pack(g0, g1, lg, tmem + TA);
+            if (!(ok = issue(s, false))) break;
+        }
+    }
+
+    if (failed) s_err[0] = 1;
+    tc_fence_before();
+    __syncthreads();
+    if (s_err[0] && tid == 0) atomicOr(p.status, 8);
+    if (warp == 0) tmem_free(tmem, 512);
+}
+
+template <bool SPLIT>
+static int filter_bwd_saved_launch(const FilterBwdParams &q, cudaStream_t st) {
+    using L = FilterSmem<SPLIT>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(filter_bwd_saved_kernel<SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalExtra) != cudaSuccess)
+            return check_launch();
+        configured[dev] = true;
+    }
+    const int64_t ntiles = (q.f.E + tc::kRows - 1) / tc::kRows;
+    const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
+    launch_pdl(filter_bwd_saved_kernel<SPLIT>, dim3(grid), dim3(kTcThreads), L::kTotalExtra, st, q);
+    return check_launch();
+}
+
 template <bool SPLIT>
 static int filter_bwd_launch(const FilterBwdParams &q, cudaStream_t st) {
     using L = FilterSmem<SPLIT>;
@@ -697,10 +1026,14 @@ static int filter_bwd_launch(const FilterBwdParams &q, cudaStream_t st) {
 
 using namespace mlcgb;
 
+extern "C" size_t mlcgb_filter_hidden_bytes(int64_t rows) {
+    return rows <= 0 ? 0 : (size_t)((rows + tc::kRows - 1) / tc::kRows) * tc::kRows * kF * sizeof(float);
+}
+
 extern "C" int mlcgb_filter_forward_counted(const void *d, int64_t E, const int64_t *rows_dev, const int32_t *sel, const int32_t *twin,
                                             const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper,
                                             const void *A1, const void *b1, const void *A2, int64_t F, int precision, void *W,
-                                            int32_t *status, void *stream) {
+                                            void *h_save, int32_t *status, void *stream) {
     TimelineScope timeline_scope("filter_forward", stream);
     if (int rc = check_spec(rbf, 0)) return rc;
     if (E < 0 || !status || (precision != 0 && precision != 1) || (conv_cutoff_kind != 0 && conv_cutoff_kind != 1)) return MLCGB_E_ARG;
@@ -722,23 +1055,24 @@ extern "C" int mlcgb_filter_forward_counted(const void *d, int64_t E, const int6
     p.b1 = (const float *)b1;
     p.A2 = (const float *)A2;
     p.W = (float *)W;
+    p.H = (float *)h_save;
     p.status = status;
     return precision == 0 ? filter_fwd_launch<true>(p, (cudaStream_t)stream) : filter_fwd_launch<false>(p, (cudaStream_t)stream);
 }
 
 extern "C" int mlcgb_filter_forward(const void *d, int64_t E, const int32_t *sel, const int32_t *twin, const mlcgb_rbf_spec *rbf,
                                     int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1,
-                                    const void *A2, int64_t F, int precision, void *W, int32_t *status, void *stream) {
+                                    const void *A2, int64_t F, int precision, void *W, void *h_save, int32_t *status, void *stream) {
     TimelineScope timeline_scope("filter_forward", stream);
     return mlcgb_filter_forward_counted(d, E, nullptr, sel, twin, rbf, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, F, precision, W,
-                                        status, stream);
+                                        h_save, status, stream);
 }
 
 extern "C" int mlcgb_filter_backward_counted(const void *d, int64_t E, const int64_t *rows_dev, const int32_t *sel, const int32_t *twin,
                                              const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower, double conv_upper,
                                              const void *A1, const void *b1, const void *A2, int64_t F, int precision,
                                              const int32_t *row0, const int32_t *row1, const void *xl, const void *gagg, int64_t N,
-                                             void *gd, int accumulate, int32_t *status, void *stream) {
+                                             const void *h_saved, void *gd, int accumulate, int32_t *status, void *stream) {
     TimelineScope timeline_scope("filter_backward", stream);
     if (int rc = check_spec(rbf, 1)) return rc;
     if (E < 0 || N < 0 || !status || (precision != 0 && precision != 1) || (conv_cutoff_kind != 0 && conv_cutoff_kind != 1)) return MLCGB_E_ARG;
@@ -760,21 +1094,24 @@ extern "C" int mlcgb_filter_backward_counted(const void *d, int64_t E, const int
     q.f.b1 = (const float *)b1;
     q.f.A2 = (const float *)A2;
     q.f.W = nullptr;
+    q.f.H = nullptr;
     q.f.status = status;
     q.row0 = row0;
     q.row1 = row1;
     q.xl = (const float *)xl;
     q.gagg = (const float *)gagg;
+    q.H = (const float *)h_saved;
     q.gd = (float *)gd;
     q.accumulate = accumulate ? 1 : 0;
+    if (q.H) return precision == 0 ? filter_bwd_saved_launch<true>(q, (cudaStream_t)stream) : filter_bwd_saved_launch<false>(q, (cudaStream_t)stream);
     return precision == 0 ? filter_bwd_launch<true>(q, (cudaStream_t)stream) : filter_bwd_launch<false>(q, (cudaStream_t)stream);
 }
 
 extern "C" int mlcgb_filter_backward(const void *d, int64_t E, const int32_t *sel, const int32_t *twin, const mlcgb_rbf_spec *rbf,
                                      int conv_cutoff_kind, double conv_lower, double conv_upper, const void *A1, const void *b1,
                                      const void *A2, int64_t F, int precision, const int32_t *row0, const int32_t *row1, const void *xl,
-                                     const void *gagg, int64_t N, void *gd, int32_t *status, void *stream) {
+                                     const void *gagg, int64_t N, const void *h_saved, void *gd, int32_t *status, void *stream) {
     TimelineScope timeline_scope("filter_backward", stream);
     return mlcgb_filter_backward_counted(d, E, nullptr, sel, twin, rbf, conv_cutoff_kind, conv_lower, conv_upper, A1, b1, A2, F, precision,
-                                         row0, row1, xl, gagg, N, gd, 0, status, stream);
+                                         row0, row1, xl, gagg, N, h_saved, gd, 0, status, stream);
 }

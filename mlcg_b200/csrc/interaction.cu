@@ -13,9 +13,9 @@ static int interaction_forward_counted(const void *x, const void *d, const int64
                                       const int32_t *pair_of, const int64_t *pairs_dev, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind,
                                       double conv_lower, double conv_upper, const void *W1, const void *fA1, const void *fb1,
                                       const void *fA2, const void *W2, const void *b2, const void *W3, const void *b3, int64_t N, int64_t E,
-                                      int64_t P, int64_t H, int64_t F, int64_t H2, int precision, void *xl, void *Wp, void *agg, void *a,
+                                      int64_t P, int64_t H, int64_t F, int64_t H2, int precision, void *xl, void *Wp, void *hsave, void *agg, void *a,
                                       void *out, int32_t *status, void *stream);
-static int interaction_backward_counted(const void *g, const void *a, const void *Wp, const void *xl, const void *d, const int64_t *ptr_out,
+static int interaction_backward_counted(const void *g, const void *a, const void *Wp, const void *xl, const void *hsave, const void *d, const int64_t *ptr_out,
                                        const int32_t *nbr_out, const int32_t *sel, const int32_t *pair_of, const int32_t *twin,
                                        const int64_t *pairs_dev, const int32_t *row0, const int32_t *row1, const mlcgb_rbf_spec *rbf,
                                        int conv_cutoff_kind, double conv_lower, double conv_upper, const void *W1, const void *fA1,
@@ -27,10 +27,11 @@ int mlcgb_interaction_forward(const void *x, const void *d, const int64_t *ptr_o
                               const int32_t *pair_of, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind, double conv_lower,
                               double conv_upper, const void *W1, const void *fA1, const void *fb1, const void *fA2, const void *W2,
                               const void *b2, const void *W3, const void *b3, int64_t N, int64_t E, int64_t P, int64_t H, int64_t F,
-                              int64_t H2, int precision, void *xl, void *Wp, void *agg, void *a, void *out, int32_t *status,
-                              void *stream) {
+                              int64_t H2, int precision, void *xl, void *Wp, void *hsave, void *agg, void *a, void *out,
+                              int32_t *status, void *stream) {
     return interaction_forward_counted(x, d, ptr_out, nbr_out, sel, pair_of, nullptr, rbf, conv_cutoff_kind, conv_lower, conv_upper, W1,
-                                             fA1, fb1, fA2, W2, b2, W3, b3, N, E, P, H, F, H2, precision, xl, Wp, agg, a, out, status, stream);
+                                             fA1, fb1, fA2, W2, b2, W3, b3, N, E, P, H, F, H2, precision, xl, Wp, hsave, agg, a, out, status,
+                                             stream);
 }
 
 // pairs_dev: NULL, or the number of pairs in device memory; P then only sizes the buffers (see mlcgb_filter_forward_counted)
@@ -38,7 +39,7 @@ static int interaction_forward_counted(const void *x, const void *d, const int64
                                       const int32_t *pair_of, const int64_t *pairs_dev, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind,
                                       double conv_lower, double conv_upper, const void *W1, const void *fA1, const void *fb1,
                                       const void *fA2, const void *W2, const void *b2, const void *W3, const void *b3, int64_t N, int64_t E,
-                                      int64_t P, int64_t H, int64_t F, int64_t H2, int precision, void *xl, void *Wp, void *agg, void *a,
+                                      int64_t P, int64_t H, int64_t F, int64_t H2, int precision, void *xl, void *Wp, void *hsave, void *agg, void *a,
                                       void *out, int32_t *status, void *stream) {
     if (N < 0 || E < 0 || P < 0 || !status) return MLCGB_E_ARG;
     if (N == 0) return MLCGB_OK;
@@ -48,7 +49,7 @@ static int interaction_forward_counted(const void *x, const void *d, const int64
     int rc = mlcgb_gemm_tc_fused(0, x, W1, nullptr, nullptr, 0, N, F, H, xl, status, stream);                 // lin1 (no bias)
     if (rc) return rc;
     rc = mlcgb_filter_forward_counted(d, P, pairs_dev, sel, nullptr, rbf, conv_cutoff_kind, conv_lower, conv_upper, fA1, fb1, fA2, F, precision,
-                                      Wp, status, stream);
+                                      Wp, hsave, status, stream);
     if (rc) return rc;
     rc = mlcgb_seg_mul_sum(xl, Wp, MLCGB_F32, ptr_out, nbr_out, pair_of, N, P, F, agg, stream);                // aggregation
     if (rc) return rc;
@@ -57,19 +58,19 @@ static int interaction_forward_counted(const void *x, const void *d, const int64
     return mlcgb_gemm_tc_fused(0, a, W3, b3, x, 2, N, H, H2, out, status, stream);                             // lin + residual
 }
 
-int mlcgb_interaction_backward(const void *g, const void *a, const void *Wp, const void *xl, const void *d, const int64_t *ptr_out,
+int mlcgb_interaction_backward(const void *g, const void *a, const void *Wp, const void *xl, const void *hsave, const void *d, const int64_t *ptr_out,
                                const int32_t *nbr_out, const int32_t *sel, const int32_t *pair_of, const int32_t *twin,
                                const int32_t *row0, const int32_t *row1, const mlcgb_rbf_spec *rbf, int conv_cutoff_kind,
                                double conv_lower, double conv_upper, const void *W1, const void *fA1, const void *fb1,
                                const void *fA2, const void *W2, const void *W3, int64_t N, int64_t E, int64_t P, int64_t H, int64_t F,
                                int64_t H2, int precision, void *gy, void *gagg, void *gxl, void *gx /* or NULL */,
                                void *gd /* [E] or NULL */, int32_t *status, void *stream) {
-    return interaction_backward_counted(g, a, Wp, xl, d, ptr_out, nbr_out, sel, pair_of, twin, nullptr, row0, row1, rbf, conv_cutoff_kind,
+    return interaction_backward_counted(g, a, Wp, xl, hsave, d, ptr_out, nbr_out, sel, pair_of, twin, nullptr, row0, row1, rbf, conv_cutoff_kind,
                                               conv_lower, conv_upper, W1, fA1, fb1, fA2, W2, W3, N, E, P, H, F, H2, precision, gy, gagg, gxl,
                                               gx, gd, 0, status, stream);
 }
 
-static int interaction_backward_counted(const void *g, const void *a, const void *Wp, const void *xl, const void *d, const int64_t *ptr_out,
+static int interaction_backward_counted(const void *g, const void *a, const void *Wp, const void *xl, const void *hsave, const void *d, const int64_t *ptr_out,
                                        const int32_t *nbr_out, const int32_t *sel, const int32_t *pair_of, const int32_t *twin,
                                        const int64_t *pairs_dev, const int32_t *row0, const int32_t *row1, const mlcgb_rbf_spec *rbf,
                                        int conv_cutoff_kind, double conv_lower, double conv_upper, const void *W1, const void *fA1,
@@ -94,7 +95,7 @@ static int interaction_backward_counted(const void *g, const void *a, const void
     }
     if (gd && E > 0)
         rc = mlcgb_filter_backward_counted(d, P, pairs_dev, sel, twin, rbf, conv_cutoff_kind, conv_lower, conv_upper, fA1, fb1, fA2, F, precision,
-                                           row0, row1, xl, gagg, N, gd, gd_accumulate, status, stream);
+                                           row0, row1, xl, gagg, N, hsave, gd, gd_accumulate, status, stream);
     return rc;
 }
 
@@ -138,7 +139,7 @@ __global__ void head_out_kernel(const float *__restrict__ a, const float *__rest
 static inline int64_t up4(int64_t n) { return (n + 3) & ~(int64_t)3; }
 
 struct SchnetLayout {
-    int64_t d, x[2], g[2], agg, gy, gxl, ah, en, gd, block0, block_stride, xl_off, a_off, wp_off, total;
+    int64_t d, x[2], g[2], agg, gy, gxl, ah, en, gd, block0, block_stride, xl_off, a_off, wp_off, h_off, total;
 };
 static SchnetLayout schnet_layout(int64_t N, int64_t E, int64_t P, int64_t H, int64_t F, int64_t H2, int64_t Wh, int64_t L) {
     SchnetLayout o;
@@ -151,7 +152,8 @@ static SchnetLayout schnet_layout(int64_t N, int64_t E, int64_t P, int64_t H, in
     o.ah = take(N * Wh); o.en = take(N);
     o.gd = take(E);
     o.xl_off = 0; o.a_off = up4(N * F); o.wp_off = o.a_off + up4(N * H2);
-    o.block_stride = o.wp_off + up4(P * F);
+    o.h_off = o.wp_off + up4(P * F);                                         // hidden layer of the filter network, whole tiles
+    o.block_stride = o.h_off + (int64_t)(mlcgb_filter_hidden_bytes(P) / sizeof(float));
     o.block0 = at;
     at += L * o.block_stride;
     o.total = at;
@@ -211,8 +213,8 @@ int mlcgb_schnet_eval_counted(const void *pos, const int64_t *types, const int64
         float *blk = ws + lay.block0 + l * lay.block_stride;
         rc = interaction_forward_counted(ws + lay.x[cur], d, offsets, row1, sel, pair_of, pairs_dev, rbf, conv_cutoff_kind, conv_lower, conv_upper, bw.lin1_w,
                                        bw.filter_w1, bw.filter_b1, bw.filter_w2, bw.lin2_w, bw.lin2_b, bw.lin_w, bw.lin_b, N, E, P, H, F, H2,
-                                       precision, blk + lay.xl_off, blk + lay.wp_off, ws + lay.agg, blk + lay.a_off, ws + lay.x[cur ^ 1], status,
-                                       stream);
+                                       precision, blk + lay.xl_off, blk + lay.wp_off, grad_pos ? blk + lay.h_off : nullptr, ws + lay.agg, blk + lay.a_off,
+                                       ws + lay.x[cur ^ 1], status, stream);
         if (rc) return rc;
         cur ^= 1;
     }
@@ -235,7 +237,7 @@ int mlcgb_schnet_eval_counted(const void *pos, const int64_t *types, const int64
         const mlcgb_schnet_block &bw = w->blocks[l];
         float *blk = ws + lay.block0 + l * lay.block_stride;
         // every block's filter kernel writes the same rows of gd (one edge per pair): the last block sets them, the others add
-        rc = interaction_backward_counted(ws + lay.g[gcur], blk + lay.a_off, blk + lay.wp_off, blk + lay.xl_off, d, offsets, row1, sel, pair_of, twin,
+        rc = interaction_backward_counted(ws + lay.g[gcur], blk + lay.a_off, blk + lay.wp_off, blk + lay.xl_off, blk + lay.h_off, d, offsets, row1, sel, pair_of, twin,
                                         pairs_dev, row0, row1, rbf, conv_cutoff_kind, conv_lower, conv_upper, bw.lin1_w, bw.filter_w1, bw.filter_b1,
                                         bw.filter_w2, bw.lin2_w, bw.lin_w, N, E, P, H, F, H2, precision, ws + lay.gy, ws + lay.agg, ws + lay.gxl,
                                         l > 0 ? ws + lay.g[gcur ^ 1] : nullptr, E > 0 ? ws + lay.gd : nullptr, l != L - 1, status, stream);

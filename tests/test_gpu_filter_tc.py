@@ -65,8 +65,10 @@ def test_filter_forward_is_row_independent():
 @pytest.mark.parametrize("E", [100, 5000])
 @pytest.mark.parametrize("precision", [0, 1])
 @pytest.mark.parametrize("gscale", [1.0, 1e4, 1e-6])
-def test_filter_backward(kind, R, upper, E, precision, gscale):
-    """gd = d/dd sum(gW * W(d)) with gW = xl[row0] * gagg[row1]; checked against autograd of the float64 oracle."""
+@pytest.mark.parametrize("saved", [False, True])
+def test_filter_backward(kind, R, upper, E, precision, gscale, saved):
+    """gd = d/dd sum(gW * W(d)) with gW = xl[row0] * gagg[row1]; checked against autograd of the float64 oracle.  ``saved``: the
+    backward that reads the hidden layer the forward kept (two GEMMs per tile, two tiles in flight) instead of recomputing it."""
     gen = torch.Generator().manual_seed(E + R)
     F, N = 128, 300
     d = torch.rand(E, generator=gen) * (upper * 1.02) + 0.5
@@ -83,13 +85,53 @@ def test_filter_backward(kind, R, upper, E, precision, gscale):
     W, p0, p1 = reference(dd, kind, upper, R, A1, b1, A2)
     (want,) = torch.autograd.grad((gW * W).sum(), dd)
     spec = RbfSpec(0 if kind == "gaussian" else 1, R, 1, 0.0, upper, 5.0 / upper, p0.to(DEV), p1.reshape(-1).to(DEV))
+    hidden = None
+    if saved:
+        _, _, hidden = get_backend().filter_forward(d.to(DEV), spec, 1, 0.0, upper, A1.to(DEV), b1.to(DEV), A2.to(DEV), precision, save_hidden=True)
     gd, status = get_backend().filter_backward(d.to(DEV), spec, 1, 0.0, upper, A1.to(DEV), b1.to(DEV), A2.to(DEV), row0.to(DEV), row1.to(DEV),
-                                               xl.to(DEV), gagg.to(DEV), precision)
+                                               xl.to(DEV), gagg.to(DEV), precision, hidden=hidden)
     torch.cuda.synchronize()
     assert int(status[0]) == 0
     err = float((gd.cpu().double() - want).abs().max())
     scale = float(want.abs().max()) + 1e-30
     assert err < (2e-5 if precision == 0 else 5e-2) * scale, (err, scale)
+
+
+@pytest.mark.parametrize("precision", [0, 1])
+@pytest.mark.parametrize("E", [19000, 100003])
+def test_filter_backward_many_tiles_per_block(E, precision):
+    """Enough rows that every thread block walks several tiles (two, and five to six): the saved-hidden-layer backward keeps two
+    tiles in flight and prefetches the indices of later ones, so its steady state, start and end are all exercised; compared
+    with the float64 oracle and with the recomputing kernel."""
+    kind, R, upper, F, N = "expnormal", 128, 15.0, 128, 4000
+    gen = torch.Generator().manual_seed(E)
+    d = torch.rand(E, generator=gen) * (upper * 1.02) + 0.5
+    A1 = (torch.rand(F, R, generator=gen) * 2 - 1) * (6.0 / (R + F)) ** 0.5
+    A2 = (torch.rand(F, F, generator=gen) * 2 - 1) * (6.0 / (2 * F)) ** 0.5
+    b1 = torch.randn(F, generator=gen) * 0.1
+    row0, row1 = torch.randint(0, N, (E,), generator=gen).int(), torch.randint(0, N, (E,), generator=gen).int()
+    xl, gagg = torch.randn(N, F, generator=gen), torch.randn(N, F, generator=gen)
+    gW = (xl[row0.long()] * gagg[row1.long()]).double()
+    dd = d.double().requires_grad_(True)
+    W, p0, p1 = reference(dd, kind, upper, R, A1, b1, A2)
+    (want,) = torch.autograd.grad((gW * W).sum(), dd)
+    spec = RbfSpec(1, R, 1, 0.0, upper, 5.0 / upper, p0.to(DEV), p1.reshape(-1).to(DEV))
+    be = get_backend()
+    args = (d.to(DEV), spec, 1, 0.0, upper, A1.to(DEV), b1.to(DEV), A2.to(DEV))
+    Wg, _, hidden = be.filter_forward(*args, precision, save_hidden=True)
+    tol = 3e-6 if precision == 0 else 3e-2
+    assert float((Wg.cpu().double() - W.detach()).abs().max()) < tol * max(1.0, float(W.detach().abs().max()))
+    more = (row0.to(DEV), row1.to(DEV), xl.to(DEV), gagg.to(DEV), precision)
+    gd_saved, status = be.filter_backward(*args, *more, hidden=hidden)
+    gd_again, _ = be.filter_backward(*args, *more, hidden=hidden)
+    gd_recomputed, _ = be.filter_backward(*args, *more)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    scale = float(want.abs().max())
+    tol = 2e-5 if precision == 0 else 5e-2
+    assert torch.equal(gd_saved, gd_again)                                     # no dependence on timing
+    assert float((gd_saved.cpu().double() - want).abs().max()) < tol * scale
+    assert float((gd_recomputed.cpu().double() - want).abs().max()) < tol * scale
 
 
 def test_pair_mode_equals_per_edge_mode():
@@ -132,6 +174,14 @@ def test_pair_mode_equals_per_edge_mode():
     total_pair = g_pair + g_pair[tw]
     assert bool((g_pair[tw[sel.long()]] == 0).all())
     assert float((total_full - total_pair).abs().max()) < 2e-5 * float(total_full.abs().max())
+    # the same with the hidden layer kept by the forward (per pair and per edge)
+    _, _, h_half = be.filter_forward(d, spec, 1, 0.0, upper, A1, b1, A2, 0, sel, save_hidden=True)
+    g_pair_h, _ = be.filter_backward(d, spec, 1, 0.0, upper, A1, b1, A2, plan.row0, plan.row1, xl, gagg, 0, sel, plan.perm_in, hidden=h_half)
+    assert bool((g_pair_h[tw[sel.long()]] == 0).all())
+    assert float((g_pair_h - g_pair).abs().max()) < 2e-5 * float(total_full.abs().max())
+    _, _, h_full = be.filter_forward(d, spec, 1, 0.0, upper, A1, b1, A2, 0, save_hidden=True)
+    g_full_h, _ = be.filter_backward(d, spec, 1, 0.0, upper, A1, b1, A2, plan.row0, plan.row1, xl, gagg, 0, hidden=h_full)
+    assert float((g_full_h - g_full).abs().max()) < 2e-5 * float(g_full.abs().max())
 
 
 def test_weights_beyond_the_fp16_pair_range_are_reported():
