@@ -8,7 +8,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmlcg_b200.so")
+#: the library next to this file, unless MLCGB_LIBRARY names another build of the same sources (e.g. one with extra checks)
+LIB_PATH = os.environ.get("MLCGB_LIBRARY") or os.path.join(_HERE, "libmlcg_b200.so")
 
 c_i64, c_int, c_dbl, c_vp, c_sz = ctypes.c_int64, ctypes.c_int, ctypes.c_double, ctypes.c_void_p, ctypes.c_size_t
 

@@ -19,6 +19,22 @@
 
 namespace mlcgb {
 
+// Phase timing of the saved-hidden-layer backward (development builds only, -DMLCGB_PHASE_TIMING): thread 0 of every block adds
+// the cycles between consecutive marks to per-phase totals that mlcgb_debug_phase_cycles reads back.
+#ifdef MLCGB_PHASE_TIMING
+__device__ unsigned long long g_phase_cycles[16];
+#define PHASE_DECL long long ph_last = clock64();
+#define PHASE(k)                                                          \
+    if (tid == 0) {                                                       \
+        const long long ph_now = clock64();                               \
+        atomicAdd(&g_phase_cycles[k], (unsigned long long)(ph_now - ph_last)); \
+        ph_last = clock64();                                              \
+    }
+#else
+#define PHASE_DECL
+#define PHASE(k)
+#endif
+
 constexpr int kF = 128;                 // filters / hidden width of the filter network
 constexpr int kTcThreads = 512;         // thread t: row t % 128 of the tile, 32-column quarter t / 128
 constexpr float kWScale = 64.f;         // power-of-two weight scaling keeps the fp16 "low" parts of the weights normal
@@ -316,7 +332,7 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
             if (NC == 32 && p.H) {                               // kept for the backward (rows past the end hold finite filler)
                 float4 *hb = reinterpret_cast<float4 *>(p.H);
 #pragma unroll
-                for (int j = 0; j < NC / 4; j++) hb[hidden_offset(tile, col0 >> 5, j, r)] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                for (int j = 0; j < NC / 4; j++) __stcs(hb + hidden_offset(tile, col0 >> 5, j, r), make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
             }
             tmem_wait_st();
         }
@@ -708,8 +724,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_pipe_kernel(FilterBw
 // are loaded two iterations, its edge ids three iterations before they are used; the hidden rows are prefetched into L2
 // one phase ahead and loaded at the top of the iteration.
 // ------------------------------------------------------------------------------------------------
+constexpr int kSavedThreads = kTcThreads + 32;     // 16 compute warps + one warp that only issues the tensor-core instructions
+
 template <bool SPLIT>
-__global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_saved_kernel(FilterBwdParams q) {
+__global__ void __launch_bounds__(kSavedThreads, 1) filter_bwd_saved_kernel(FilterBwdParams q) {
     using namespace tc;
     using L = FilterSmem<SPLIT>;
     const FilterFwdParams &p = q.f;
@@ -722,11 +740,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_saved_kernel(FilterB
     float *s_redB2 = reinterpret_cast<float *>(smem + L::kExtra);               // partial sums of gC
     float *s_redC = reinterpret_cast<float *>(smem + L::kExtra + 2048);         // partial sums of gd
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar);
-    uint64_t *s_bars = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar + 64);   // GH' of slot 0, 1; GPHI of slot 0, 1
+    // GEMM finished: GH' of slot 0, 1; GPHI of slot 0, 1 (one arrival, from tcgen05.commit).  Operands ready and accumulator
+    // free: the same four (one arrival per compute warp).
+    uint64_t *s_done = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar + 64);
+    uint64_t *s_ready = s_done + 4;
     int *s_err = reinterpret_cast<int *>(reinterpret_cast<uint32_t *>(s_bar + 1) + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int r = tid & 127, qt = tid >> 7, col0 = qt * 32;
+    const int r = tid & 127, qt = (tid >> 7) & 3, col0 = qt * 32;
     const int R = p.rbf.R;
     const int Kpad1 = R <= 64 ? 64 : 128;
     const float wscale = SPLIT ? kWScale : 1.f;
@@ -734,250 +755,295 @@ __global__ void __launch_bounds__(kTcThreads, 1) filter_bwd_saved_kernel(FilterB
     const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 512);
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) mbar_init(smem_u32(s_bars + i), 1);
+        for (int i = 0; i < 4; i++) {
+            mbar_init(smem_u32(s_done + i), 1);
+            mbar_init(smem_u32(s_ready + i), kTcThreads / 32);
+        }
     }
     __syncthreads();
     pdl_wait();                    // set-up done (weights only); everything below reads what earlier kernels wrote
     pdl_launch_dependents();
     const int64_t nE = live_rows(p);
-    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t t_lane = tmem + lane_off;
-    // tensor memory: accumulator of slot s at columns [128 s, 128 s + 128), operand of slot s at [256 + 128 s, ...)
     const uint32_t b1_hi = smem_u32(smem + L::kB1), b1_lo = b1_hi + 32768, b2_hi = smem_u32(smem + L::kB2), b2_lo = b2_hi + 32768;
-    bool failed = false;
-
-    const bool same_env = p.conv.cutoff_kind == p.rbf.cutoff_kind && p.conv.lower == p.rbf.lower && p.conv.upper == p.rbf.upper;
-    auto row_group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + (warp & 3)) : "memory"); };
-    struct EdgeScalars { float t, dt, e0, e1, c0, c1; };
-    auto scalars = [&](float de) {
-        EdgeScalars s;
-        edge_arg(de, p.rbf, s.t, s.dt);
-        const Jet<float, 1> env = envelope_jet<float, 1>(de, p.rbf);
-        s.e0 = env.c[0];
-        s.e1 = env.c[1];
-        if (same_env) {
-            s.c0 = s.e0;
-            s.c1 = s.e1;
-        } else {
-            const Jet<float, 1> cj = envelope_jet<float, 1>(de, p.conv);
-            s.c0 = cj.c[0];
-            s.c1 = cj.c[1];
-        }
-        return s;
-    };
-    const bool paired = p.sel && p.twin;          // one row per unordered pair: both directions' gW are summed
     const int64_t ntiles = (nE + kRows - 1) / kRows;
     const int64_t first = blockIdx.x, step = gridDim.x;
     const int64_t n_local = first < ntiles ? (ntiles - first + step - 1) / step : 0;
-    auto tile_of = [&](int64_t j) { return first + j * step; };
-    auto edge_of = [&](int64_t j) -> int32_t {      // edge handled by this thread's row of local tile j (-1: past the end)
-        if (j >= n_local) return -1;
-        const int64_t krow = tile_of(j) * kRows + r;
-        if (krow >= nE) return -1;
-        return p.sel ? p.sel[krow] : (int32_t)krow;
+    bool failed = false;
+    // a wait that has run out is not repeated: the block runs on (on whatever the accumulators hold), so that every
+    // barrier of the schedule below is still reached by everybody, and reports the failure at the end
+    auto await = [&](uint64_t *bar, uint32_t parity) {
+        if (!failed && !mbar_wait(smem_u32(bar), parity)) failed = true;
+        tc_fence_after();
     };
 
-    // gW = xl[row0] * gagg[row1] (+ the reverse edge's product in pair mode) of one tile -> operand block `ta`, rows scaled by
-    // a power of two; returns the row's scale.  Four rows per load instruction, turned row-per-lane through this warp's own
-    // 32 x 32 block of the stage.
-    auto gather_pack = [&](int32_t i0, int32_t i1, bool live, uint32_t ta) -> float {
-        const int sub = lane >> 3, cc = (col0 >> 2) + (lane & 7);
-        auto gather = [&](auto paired_tag) {
-            constexpr bool kPaired = decltype(paired_tag)::value;
-#pragma unroll
-            for (int half = 0; half < 2; half++) {
-                float4 a[4], b[4], a2[4], b2[4];
-                float m[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int rl = (half * 4 + u) * 4 + sub;
-                    const int64_t j0 = __shfl_sync(0xffffffffu, i0, rl), j1 = __shfl_sync(0xffffffffu, i1, rl);
-                    m[u] = __shfl_sync(0xffffffffu, (int)live, rl) ? 1.f : 0.f;
-                    a[u] = __ldg(reinterpret_cast<const float4 *>(q.xl + j0 * kF) + cc);
-                    b[u] = __ldg(reinterpret_cast<const float4 *>(q.gagg + j1 * kF) + cc);
-                    if (kPaired) {   // the reverse edge: xl[row1] * gagg[row0]
-                        a2[u] = __ldg(reinterpret_cast<const float4 *>(q.xl + j1 * kF) + cc);
-                        b2[u] = __ldg(reinterpret_cast<const float4 *>(q.gagg + j0 * kF) + cc);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int rl = (half * 4 + u) * 4 + sub;
-                    float4 gw = make_float4(a[u].x * b[u].x * m[u], a[u].y * b[u].y * m[u], a[u].z * b[u].z * m[u], a[u].w * b[u].w * m[u]);
-                    if (kPaired) {
-                        gw.x = fmaf(a2[u].x * b2[u].x, m[u], gw.x); gw.y = fmaf(a2[u].y * b2[u].y, m[u], gw.y);
-                        gw.z = fmaf(a2[u].z * b2[u].z, m[u], gw.z); gw.w = fmaf(a2[u].w * b2[u].w, m[u], gw.w);
-                    }
-                    *stage_chunk(stage, (r & ~31) + rl, cc) = gw;
-                }
+    if (warp == kTcThreads / 32) {
+        // ---- the issuing warp: GH'(0), GH'(1), then per tile GPHI(j), GH'(j+2), each when its operands are ready.  The
+        //      tensor core's queue is short, so issuing a GEMM takes about as long as the GEMM: kept off the compute warps
+        auto gemm = [&](int s, bool gphi) {
+            if (lane == 0) {
+                if (gphi) issue_gemm_ts<SPLIT>(tmem + 128 * s, tmem + 256 + 128 * s, b1_hi, b1_lo, kF / 16, 1, Kpad1);
+                else issue_gemm_ts<SPLIT>(tmem + 128 * s, tmem + 256 + 128 * s, b2_hi, b2_lo, kF / 16, 1, 128);
+                mma_commit(smem_u32(s_done + (gphi ? 2 : 0) + s));
             }
+            __syncwarp();
         };
-        if (paired) gather(std::true_type{});
-        else gather(std::false_type{});
-        __syncwarp();
-        float g[32];
-        float rmax = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; w++) {
-            const float4 gw4 = *stage_chunk(stage, r, (col0 >> 2) + w);
-            g[4 * w] = gw4.x; g[4 * w + 1] = gw4.y; g[4 * w + 2] = gw4.z; g[4 * w + 3] = gw4.w;
-            rmax = fmaxf(fmaxf(rmax, fmaxf(fabsf(gw4.x), fabsf(gw4.y))), fmaxf(fabsf(gw4.z), fabsf(gw4.w)));
+        for (int64_t t = 0; t < 2 && t < n_local; t++) {
+            await(s_ready + t, 0);
+            gemm((int)t, false);
         }
-        __syncwarp();
-        s_redA[qt * 128 + r] = rmax;
-        row_group_sync();
-        const float sc = SPLIT ? row_scale(fmaxf(fmaxf(s_redA[r], s_redA[128 + r]), fmaxf(s_redA[256 + r], s_redA[384 + r]))) : 1.f;
-        store_a_tmem<SPLIT>(ta + lane_off, col0, g, sc);
-        tmem_wait_st();
-        return sc;
-    };
-    // one GEMM of slot s after everybody's operand stores are visible; returns false for every thread if a wait has run out
-    auto issue = [&](int s, bool gphi) -> bool {
-        if (failed) s_err[0] = 1;
-        tc_fence_before();
-        __syncthreads();
-        if (s_err[0]) return false;
-        if (tid == 0) {
-            tc_fence_after();
-            if (gphi) issue_gemm_ts<SPLIT>(tmem + 128 * s, tmem + 256 + 128 * s, b1_hi, b1_lo, kF / 16, 1, Kpad1);
-            else issue_gemm_ts<SPLIT>(tmem + 128 * s, tmem + 256 + 128 * s, b2_hi, b2_lo, kF / 16, 1, 128);
-            mma_commit(smem_u32(s_bars + (gphi ? 2 : 0) + s));
+        for (int64_t j = 0; j < n_local; j++) {
+            const int s = (int)(j & 1);
+            await(s_ready + 2 + s, (uint32_t)((j >> 1) & 1));
+            gemm(s, true);
+            if (j + 2 < n_local) {
+                await(s_ready + s, (uint32_t)(((j + 2) >> 1) & 1));
+                gemm(s, false);
+            }
         }
-        return true;
-    };
-    auto prefetch_hidden = [&](int64_t j) {      // the tile's 64 KB of hidden rows into L2, one 128-byte line per thread
-        if (j < n_local) asm volatile("prefetch.global.L2 [%0];" ::"l"(q.H + tile_of(j) * (kRows * kF) + tid * 32));
-    };
+    } else {
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t t_lane = tmem + lane_off;
+        // tensor memory: accumulator of slot s at columns [128 s, 128 s + 128), operand of slot s at [256 + 128 s, ...)
+        const bool same_env = p.conv.cutoff_kind == p.rbf.cutoff_kind && p.conv.lower == p.rbf.lower && p.conv.upper == p.rbf.upper;
+        // The four column quarters of a row sit in warps w, w+4, w+8, w+12: exchanges between them need only those 128 threads,
+        // on a named barrier of their own (ids 1-4).  Nothing in the loop below synchronises the whole block: the four row groups
+        // meet only through the GEMMs, so that one group computes while another waits for memory.
+        auto row_group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + (warp & 3)) : "memory"); };
+        // this warp's operand stores and accumulator reads are done: one arrival on the barrier the issuing warp waits for
+        auto signal = [&](uint64_t *bar) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(bar));
+        };
+        struct EdgeScalars { float t, dt, e0, e1, c0, c1; };
+        auto scalars = [&](float de) {
+            EdgeScalars s;
+            edge_arg(de, p.rbf, s.t, s.dt);
+            const Jet<float, 1> env = envelope_jet<float, 1>(de, p.rbf);
+            s.e0 = env.c[0];
+            s.e1 = env.c[1];
+            if (same_env) {
+                s.c0 = s.e0;
+                s.c1 = s.e1;
+            } else {
+                const Jet<float, 1> cj = envelope_jet<float, 1>(de, p.conv);
+                s.c0 = cj.c[0];
+                s.c1 = cj.c[1];
+            }
+            return s;
+        };
+        const bool paired = p.sel && p.twin;          // one row per unordered pair: both directions' gW are summed
+        const bool zero_twin = paired && !q.accumulate && qt == 0;
+        auto tile_of = [&](int64_t j) { return first + j * step; };
+        auto edge_of = [&](int64_t j) -> int32_t {      // edge handled by this thread's row of local tile j (-1: past the end)
+            if (j >= n_local) return -1;
+            const int64_t krow = tile_of(j) * kRows + r;
+            if (krow >= nE) return -1;
+            return p.sel ? p.sel[krow] : (int32_t)krow;
+        };
 
-    // ---- state of the tiles in flight: (edge, scalars, gW scale) of tile j (being finished) and j+1 (GH' issued)
-    int32_t e_cur = -1, e_nx = -1;
-    EdgeScalars es_cur{}, es_nx{};
-    float sc3_cur = 1.f, sc3_nx = 1.f;
-    bool ok = true;
-    // prologue: gather tiles 0 and 1
-    int32_t e_a = edge_of(0), e_b = edge_of(1);
-    int32_t e_pre = edge_of(2);                   // edge id of the tile after those: its rows are loaded in the first iteration
-    {
-        const bool la = e_a >= 0, lb = e_b >= 0;
-        const int32_t a0 = la ? q.row0[e_a] : 0, a1 = la ? q.row1[e_a] : 0, b0 = lb ? q.row0[e_b] : 0, b1i = lb ? q.row1[e_b] : 0;
-        const float da = la ? p.d[e_a] : 1.f, db = lb ? p.d[e_b] : 1.f;
-        if (n_local > 0) {
-            prefetch_hidden(0);
-            e_cur = e_a;
-            es_cur = scalars(da);
-            sc3_cur = gather_pack(a0, a1, la, tmem + 256);
-            ok = issue(0, false);
-        }
-        if (ok && n_local > 1) {
-            prefetch_hidden(1);
-            e_nx = e_b;
-            es_nx = scalars(db);
-            sc3_nx = gather_pack(b0, b1i, lb, tmem + 256 + 128);
-            ok = issue(1, false);
-        }
-    }
-    for (int64_t j = 0; ok && j < n_local; j++) {
-        const int s = (int)(j & 1);
-        const uint32_t par = (uint32_t)((j >> 1) & 1);
-        const uint32_t D = 128u * s, TA = 256u + 128u * s;
-        const bool live = e_cur >= 0;
-        // ---- loads whose results are needed later: the hidden rows of this tile (B), rows and distance of tile j+2 (A below),
-        //      edge id of tile j+3 (next iteration)
-        float4 hq[8];
-        {
-            const float4 *hb = reinterpret_cast<const float4 *>(q.H);
-            const int64_t t = tile_of(j);
+        // gW = xl[row0] * gagg[row1] (+ the reverse edge's product in pair mode) of one tile -> operand block `ta`, rows scaled
+        // by a power of two; returns the row's scale.  Four rows per load instruction, turned row-per-lane through this warp's
+        // own 32 x 32 block of the stage.  Rows past the end use node 0: finite values nobody reads.
+        auto gather_pack = [&](int32_t i0, int32_t i1, uint32_t ta) -> float {
+            const int sub = lane >> 3, cc = (col0 >> 2) + (lane & 7);
+            auto gather = [&](auto paired_tag) {
+                constexpr bool kPaired = decltype(paired_tag)::value;
 #pragma unroll
-            for (int c = 0; c < 8; c++) hq[c] = hb[hidden_offset(t, qt, c, r)];
-        }
-        const int32_t e_g = e_pre;                 // tile j+2
-        const bool lg = e_g >= 0;
-        const int32_t g0 = lg ? q.row0[e_g] : 0, g1 = lg ? q.row1[e_g] : 0;
-        const float dg = lg ? p.d[e_g] : 1.f;
-        e_pre = edge_of(j + 3);
+                for (int half = 0; half < 2; half++) {
+                    float4 a[4], b[4], a2[4], b2[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int rl = (half * 4 + u) * 4 + sub;
+                        const int64_t j0 = __shfl_sync(0xffffffffu, i0, rl), j1 = __shfl_sync(0xffffffffu, i1, rl);
+                        a[u] = __ldg(reinterpret_cast<const float4 *>(q.xl + j0 * kF) + cc);
+                        b[u] = __ldg(reinterpret_cast<const float4 *>(q.gagg + j1 * kF) + cc);
+                        if (kPaired) {   // the reverse edge: xl[row1] * gagg[row0]
+                            a2[u] = __ldg(reinterpret_cast<const float4 *>(q.xl + j1 * kF) + cc);
+                            b2[u] = __ldg(reinterpret_cast<const float4 *>(q.gagg + j0 * kF) + cc);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int rl = (half * 4 + u) * 4 + sub;
+                        float4 gw = make_float4(a[u].x * b[u].x, a[u].y * b[u].y, a[u].z * b[u].z, a[u].w * b[u].w);
+                        if (kPaired) {
+                            gw.x = fmaf(a2[u].x, b2[u].x, gw.x); gw.y = fmaf(a2[u].y, b2[u].y, gw.y);
+                            gw.z = fmaf(a2[u].z, b2[u].z, gw.z); gw.w = fmaf(a2[u].w, b2[u].w, gw.w);
+                        }
+                        *stage_chunk(stage, (r & ~31) + rl, cc) = gw;
+                    }
+                }
+            };
+            if (paired) gather(std::true_type{});
+            else gather(std::false_type{});
+            __syncwarp();
+            float g[32];
+            float rmax = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) {
+                const float4 gw4 = *stage_chunk(stage, r, (col0 >> 2) + w);
+                g[4 * w] = gw4.x; g[4 * w + 1] = gw4.y; g[4 * w + 2] = gw4.z; g[4 * w + 3] = gw4.w;
+                rmax = fmaxf(fmaxf(rmax, fmaxf(fabsf(gw4.x), fabsf(gw4.y))), fmaxf(fabsf(gw4.z), fabsf(gw4.w)));
+            }
+            __syncwarp();
+            s_redA[qt * 128 + r] = rmax;
+            row_group_sync();
+            const float sc = SPLIT ? row_scale(fmaxf(fmaxf(s_redA[r], s_redA[128 + r]), fmaxf(s_redA[256 + r], s_redA[384 + r]))) : 1.f;
+            store_a_tmem<SPLIT>(ta + lane_off, col0, g, sc);
+            tmem_wait_st();
+            return sc;
+        };
+        auto prefetch_hidden = [&](int64_t j) {      // the tile's 64 KB of hidden rows into L2, one 128-byte line per thread
+            if (j < n_local) asm volatile("prefetch.global.L2 [%0];" ::"l"(q.H + tile_of(j) * (kRows * kF) + tid * 32));
+        };
 
-        // ---- B(j): GH' done.  gC = sum h GH', gz = C GH' (1 - h^2) -> operand (row-scaled); issue GPHI = gz A1
-        if (!mbar_wait(smem_u32(s_bars + s), par)) failed = true;
-        tc_fence_after();
-        float g[32];
-        float gC = 0.f, rmax = 0.f;
+        // ---- state of the tiles in flight: (edge, reverse edge, scalars, gW scale) of tile j (being finished) and j+1 (GH' issued)
+        int32_t e_cur = -1, e_nx = -1, tw_cur = 0, tw_nx = 0;
+        EdgeScalars es_cur{}, es_nx{};
+        float sc3_cur = 1.f, sc3_nx = 1.f;
+        // prologue: gather tiles 0 and 1
         {
-            const float inv3 = 1.f / (sc3_cur * wscale);
+            const int32_t e_a = edge_of(0), e_b = edge_of(1);
+            const bool la = e_a >= 0, lb = e_b >= 0;
+            const int32_t a0 = la ? q.row0[e_a] : 0, a1 = la ? q.row1[e_a] : 0, b0 = lb ? q.row0[e_b] : 0, b1i = lb ? q.row1[e_b] : 0;
+            const float da = la ? p.d[e_a] : 1.f, db = lb ? p.d[e_b] : 1.f;
+            if (n_local > 0) {
+                prefetch_hidden(0);
+                e_cur = e_a;
+                tw_cur = (zero_twin && la) ? p.twin[e_a] : 0;
+                es_cur = scalars(da);
+                sc3_cur = gather_pack(a0, a1, tmem + 256);
+                signal(s_ready + 0);
+            }
+            if (n_local > 1) {
+                prefetch_hidden(1);
+                e_nx = e_b;
+                tw_nx = (zero_twin && lb) ? p.twin[e_b] : 0;
+                es_nx = scalars(db);
+                sc3_nx = gather_pack(b0, b1i, tmem + 256 + 128);
+                signal(s_ready + 1);
+            }
+        }
+        int32_t e_pre = edge_of(2);                   // edge id of the tile after those: its rows are loaded in the first iteration
+        PHASE_DECL
+        for (int64_t j = 0; j < n_local; j++) {
+            PHASE(0)
+            const int s = (int)(j & 1);
+            const uint32_t par = (uint32_t)((j >> 1) & 1);
+            const uint32_t D = 128u * s, TA = 256u + 128u * s;
+            const bool live = e_cur >= 0;
+            // ---- loads whose results are needed later: the hidden rows of this tile (B), rows, distance and reverse edge of tile
+            //      j+2 (A below), edge id of tile j+3 (next iteration)
+            float4 hq[8];
+            {
+                const float4 *hb = reinterpret_cast<const float4 *>(q.H);
+                const int64_t t = tile_of(j);
 #pragma unroll
-            for (int half = 0; half < 2; half++) {
-                float v[16];
-                tmem_ld16(t_lane + D + col0 + half * 16, v);
+                for (int c = 0; c < 8; c++) hq[c] = hb[hidden_offset(t, qt, c, r)];
+            }
+            const int32_t e_g = e_pre;                 // tile j+2
+            const bool lg = e_g >= 0;
+            const int32_t g0 = lg ? q.row0[e_g] : 0, g1 = lg ? q.row1[e_g] : 0;
+            const float dg = lg ? p.d[e_g] : 1.f;
+            const int32_t tw_g = (zero_twin && lg) ? p.twin[e_g] : 0;
+            e_pre = edge_of(j + 3);
+
+            // ---- B(j): GH' done.  gC = sum h GH', gz = C GH' (1 - h^2) -> operand (row-scaled); GPHI = gz A1 can go
+            PHASE(1)
+            await(s_done + s, par);
+            PHASE(2)
+            float g[32];
+            float gC = 0.f, rmax = 0.f;
+            {
+                const float inv3 = 1.f / (sc3_cur * wscale);
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const float4 h4 = hq[half * 4 + c];
-                    const float hh[4] = {h4.x, h4.y, h4.z, h4.w};
+                for (int half = 0; half < 2; half++) {
+                    float v[16];
+                    tmem_ld16(t_lane + D + col0 + half * 16, v);
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const float gh = v[4 * c + i] * inv3;
-                        gC = fmaf(hh[i], gh, gC);
-                        const float gz = es_cur.c0 * gh * fmaf(-hh[i], hh[i], 1.f);
-                        g[half * 16 + 4 * c + i] = gz;
-                        rmax = fmaxf(rmax, fabsf(gz));
+                    for (int c = 0; c < 4; c++) {
+                        const float4 h4 = hq[half * 4 + c];
+                        const float hh[4] = {h4.x, h4.y, h4.z, h4.w};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const float gh = v[4 * c + i] * inv3;
+                            gC = fmaf(hh[i], gh, gC);
+                            const float gz = es_cur.c0 * gh * fmaf(-hh[i], hh[i], 1.f);
+                            g[half * 16 + 4 * c + i] = gz;
+                            rmax = fmaxf(rmax, fabsf(gz));
+                        }
                     }
                 }
             }
-        }
-        s_redB[qt * 128 + r] = rmax;
-        s_redB2[qt * 128 + r] = gC;
-        row_group_sync();
-        gC = (s_redB2[r] + s_redB2[128 + r]) + (s_redB2[256 + r] + s_redB2[384 + r]);
-        const float sc4 = SPLIT ? row_scale(fmaxf(fmaxf(s_redB[r], s_redB[128 + r]), fmaxf(s_redB[256 + r], s_redB[384 + r]))) : 1.f;
-        store_a_tmem<SPLIT>(tmem + TA + lane_off, col0, g, sc4);
-        tmem_wait_st();
-        if (!(ok = issue(s, true))) break;
+            PHASE(3)
+            s_redB[qt * 128 + r] = rmax;
+            s_redB2[qt * 128 + r] = gC;
+            row_group_sync();
+            gC = (s_redB2[r] + s_redB2[128 + r]) + (s_redB2[256 + r] + s_redB2[384 + r]);
+            const float sc4 = SPLIT ? row_scale(fmaxf(fmaxf(s_redB[r], s_redB[128 + r]), fmaxf(s_redB[256 + r], s_redB[384 + r]))) : 1.f;
+            store_a_tmem<SPLIT>(tmem + TA + lane_off, col0, g, sc4);
+            tmem_wait_st();
+            PHASE(4)
+            signal(s_ready + 2 + s);
+            PHASE(5)
 
-        // ---- C(j), under GPHI: basis derivatives phi'_k = g_k (env' - env 2 ln2 w_k (t - c_k) t') for this thread's columns
-        if (col0 < Kpad1) {
-            const float m2 = -2.f * kLn2 * es_cur.dt * es_cur.e0;
-            const float4 *tab4 = reinterpret_cast<const float4 *>(s_tab + col0);
+            // ---- C(j), under GPHI: basis derivatives phi'_k = g_k (env' - env 2 ln2 w_k (t - c_k) t') for this thread's columns,
+            //      and the per-row scalars of tile j+2
+            if (col0 < Kpad1) {
+                const float m2 = -2.f * kLn2 * es_cur.dt * es_cur.e0;
+                const float4 *tab4 = reinterpret_cast<const float4 *>(s_tab + col0);
 #pragma unroll
-            for (int c = 0; c < 16; c++) {
-                const float4 cw = tab4[c];
-                const float u0 = es_cur.t - cw.x, wu0 = cw.y * u0, u1 = es_cur.t - cw.z, wu1 = cw.w * u1;
-                g[2 * c] = ex2_fast(-wu0 * u0) * fmaf(m2, wu0, es_cur.e1);      // columns at or beyond R: exactly 0
-                g[2 * c + 1] = ex2_fast(-wu1 * u1) * fmaf(m2, wu1, es_cur.e1);
+                for (int c = 0; c < 16; c++) {
+                    const float4 cw = tab4[c];
+                    const float u0 = es_cur.t - cw.x, wu0 = cw.y * u0, u1 = es_cur.t - cw.z, wu1 = cw.w * u1;
+                    g[2 * c] = ex2_fast(-wu0 * u0) * fmaf(m2, wu0, es_cur.e1);      // columns at or beyond R: exactly 0
+                    g[2 * c + 1] = ex2_fast(-wu1 * u1) * fmaf(m2, wu1, es_cur.e1);
+                }
             }
-        }
-        const float gC_dC = gC * es_cur.c1, inv4 = 1.f / (sc4 * wscale);
-        if (j + 1 < n_local) prefetch_hidden(j + 1);
-        if (!mbar_wait(smem_u32(s_bars + 2 + s), par)) failed = true;
-        tc_fence_after();
-        float acc = 0.f;
-        if (col0 < Kpad1) {
-            float v[32];
-            tmem_ld32(t_lane + D + col0, v);
+            const float gC_dC = gC * es_cur.c1, inv4 = 1.f / (sc4 * wscale);
+            if (j + 1 < n_local) prefetch_hidden(j + 1);
+            const EdgeScalars es_g = scalars(dg);
+            PHASE(6)
+            await(s_done + 2 + s, par);
+            PHASE(7)
+            float acc = 0.f;
+            if (col0 < Kpad1) {
+                float v[32];
+                tmem_ld32(t_lane + D + col0, v);
 #pragma unroll
-            for (int c = 0; c < 32; c++) acc = fmaf(v[c], g[c], acc);
-            acc *= inv4;
-        }
-        if (qt == 0) acc += gC_dC;
-        s_redC[qt * 128 + r] = acc;
-        tc_fence_before();
-        row_group_sync();
-        if (qt == 0 && live) {
-            const float v = (s_redC[r] + s_redC[128 + r]) + (s_redC[256 + r] + s_redC[384 + r]);
-            if (q.accumulate) {
-                q.gd[e_cur] += v;
-            } else {
-                q.gd[e_cur] = v;
-                if (paired) q.gd[p.twin[e_cur]] = 0.f;   // the pair's whole gradient is carried by one of its two edges
+                for (int c = 0; c < 32; c++) acc = fmaf(v[c], g[c], acc);
+                acc *= inv4;
             }
-        }
+            if (qt == 0) acc += gC_dC;
+            s_redC[qt * 128 + r] = acc;
+            row_group_sync();
+            if (qt == 0 && live) {
+                const float v = (s_redC[r] + s_redC[128 + r]) + (s_redC[256 + r] + s_redC[384 + r]);
+                if (q.accumulate) {
+                    atomicAdd(q.gd + e_cur, v);         // (one addition per entry and launch: the result does not depend on timing)
+                } else {
+                    q.gd[e_cur] = v;
+                    if (paired) q.gd[tw_cur] = 0.f;     // the pair's whole gradient is carried by one of its two edges
+                }
+            }
+            PHASE(8)
 
-        // ---- A(j+2): the slot is free (GPHI(j) has been read): gather gW of tile j+2 into it and issue its GH'
-        e_cur = e_nx;
-        es_cur = es_nx;
-        sc3_cur = sc3_nx;
-        if (j + 2 < n_local) {
-            e_nx = e_g;
-            es_nx = scalars(dg);
-            sc3_nx = gather_pack(g0, g1, lg, tmem + TA);
-            if (!(ok = issue(s, false))) break;
+            // ---- A(j+2): the slot is free (GPHI(j) has been read): gather gW of tile j+2 into it; its GH' can go
+            e_cur = e_nx;
+            tw_cur = tw_nx;
+            es_cur = es_nx;
+            sc3_cur = sc3_nx;
+            if (j + 2 < n_local) {
+                e_nx = e_g;
+                tw_nx = tw_g;
+                es_nx = es_g;
+                PHASE(9)
+                sc3_nx = gather_pack(g0, g1, tmem + TA);
+                PHASE(10)
+                signal(s_ready + s);
+                PHASE(11)
+            }
         }
     }
 
@@ -1001,7 +1067,7 @@ static int filter_bwd_saved_launch(const FilterBwdParams &q, cudaStream_t st) {
     }
     const int64_t ntiles = (q.f.E + tc::kRows - 1) / tc::kRows;
     const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
-    launch_pdl(filter_bwd_saved_kernel<SPLIT>, dim3(grid), dim3(kTcThreads), L::kTotalExtra, st, q);
+    launch_pdl(filter_bwd_saved_kernel<SPLIT>, dim3(grid), dim3(kSavedThreads), L::kTotalExtra, st, q);
     return check_launch();
 }
 
@@ -1025,6 +1091,19 @@ static int filter_bwd_launch(const FilterBwdParams &q, cudaStream_t st) {
 }  // namespace mlcgb
 
 using namespace mlcgb;
+
+#ifdef MLCGB_PHASE_TIMING
+extern "C" int mlcgb_debug_phase_cycles(unsigned long long *out, int n, int reset) {
+    unsigned long long host[16];
+    if (cudaMemcpyFromSymbol(host, mlcgb::g_phase_cycles, sizeof(host)) != cudaSuccess) return MLCGB_E_LAUNCH;
+    for (int i = 0; i < n && i < 16; i++) out[i] = host[i];
+    if (reset) {
+        unsigned long long zero[16] = {0};
+        if (cudaMemcpyToSymbol(mlcgb::g_phase_cycles, zero, sizeof(zero)) != cudaSuccess) return MLCGB_E_LAUNCH;
+    }
+    return MLCGB_OK;
+}
+#endif
 
 extern "C" size_t mlcgb_filter_hidden_bytes(int64_t rows) {
     return rows <= 0 ? 0 : (size_t)((rows + tc::kRows - 1) / tc::kRows) * tc::kRows * kF * sizeof(float);

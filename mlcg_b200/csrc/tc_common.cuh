@@ -69,6 +69,10 @@ __device__ __forceinline__ void mbar_init(uint32_t bar_saddr, uint32_t count) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar_saddr) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_saddr) : "memory");
+}
+
 // Waits for the phase with the given parity; gives up after kSpinLimit polls and returns false.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar_saddr, uint32_t parity) {
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
