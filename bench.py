@@ -351,7 +351,7 @@ def extra_measurements(dev, hbm_peak, arm):
     pos_h = torch.rand(B * n, 3, generator=gen) * 60.0
     pos = pos_h.to(dev)
     ptr = torch.arange(B + 1, device=dev) * n
-    res = be.radius_graph(pos, ptr, 10.0, 1000, False, 1)
+    res = be.radius_graph(pos, ptr, 10.0, 1000, False, 1, want_batch=False)
     E = int(res["edge_index"].shape[1])
     t0 = time.perf_counter()
     ei_cpu = radius_ref.radius_graph_c(pos_h.numpy(), (torch.arange(B + 1) * n).numpy(), 10.0, 1000, False, "cluster")
@@ -360,13 +360,14 @@ def extra_measurements(dev, hbm_peak, arm):
     del res, ei_cpu
     if not same:
         raise RuntimeError("radius graph of 256 x 4000 points differs from the CPU oracle's")
-    ms = time_cuda(lambda: be.radius_graph(pos, ptr, 10.0, 1000, False, 1), iters=5, warm=1)
+    ms = time_cuda(lambda: be.radius_graph(pos, ptr, 10.0, 1000, False, 1, want_batch=False), iters=5, warm=1)
     nbytes = 16 * E + 20 * B * n
     out["radius_graph_256x4000"] = dict(edges=E, ms=ms, edges_per_s=E / (ms / 1e3), algorithmic_GBps=nbytes / ms / 1e6,
                                         frac_of_hbm=nbytes / ms / 1e6 / hbm_peak, bit_exact_vs_cpu_oracle=same, cpu_ms=cpu_s * 1e3,
                                         cpu_edges_per_s=E / cpu_s, cpu_cores=arm.cores,
                                         note="count + scan + host read of E + fill, allocation of the outputs included; algorithmic bytes = 16 B/edge "
-                                             "written + 20 B/point read; CPU: the C oracle (all pairs of each structure, OpenMP over structures), "
+                                             "written + 20 B/point read (the call also writes the two int32 index rows this package's kernels "
+                                             "read, 8 B/edge more); CPU: the C oracle (all pairs of each structure, OpenMP over structures), "
                                              "all 256 structures, one call; the two edge lists are compared whole")
     del pos
 

@@ -4,19 +4,37 @@
 // edges (centre i, neighbour j), both in the same structure, squared distance strictly below r*r,
 // centre-major with neighbours in ascending index order, at most max_num_neighbors per centre.
 //
-// Plan:  build_cells (one CTA per large structure: bounding box, cell grid, counting sort of the
-//        points by cell, all counters in shared memory)
-//     -> neighbours<COUNT> (one warp per centre, 3x3 rows of cells, each row a contiguous run of
-//        cell-sorted points; small structures scan all their points instead)
+// Plan:  build_cells (one CTA per large structure: bounding box, cell grid with cells of half the cutoff
+//        where the structure has points enough, counting sort of the points by cell, all counters in
+//        shared memory)
+//     -> neighbours_tile<COUNT> for structures of up to 8192 points with a cell grid: a block takes
+//        four neighbouring rows of cells of one layer, stages the points of every row within reach in
+//        shared memory once, and four threads per centre walk the centre's runs of candidates there;
+//        neighbours<COUNT> for the rest (one warp per centre over the rows of cells within reach, each
+//        row a contiguous run of cell-sorted points; small structures scan all their points instead)
 //     -> exclusive scan of the degrees (three small kernels, no spin-waits)
-//     -> [host reads E] -> neighbours<FILL> (same walk; hits are marked in a per-warp bitmask in
-//        shared memory indexed by local point index, then emitted in ascending order, which gives
-//        the canonical order without a sort).
+//     -> [host reads E] -> the same two kernels as FILL (same walk; hits are marked in a bitmask in
+//        shared memory indexed by local point index, per centre, then emitted in ascending order,
+//        which gives the canonical order without a sort).
 #include "common.cuh"
 
 #include <atomic>
 
 namespace mlcgb {
+
+#ifdef MLCGB_PHASE_TIMING
+__device__ unsigned long long g_radius_phase_cycles[16];
+#define RPHASE_DECL long long ph_last = clock64();
+#define RPHASE(k)                                                                  \
+    if (threadIdx.x == 0) {                                                        \
+        const long long ph_now = clock64();                                        \
+        atomicAdd(&g_radius_phase_cycles[k], (unsigned long long)(ph_now - ph_last)); \
+        ph_last = clock64();                                                       \
+    }
+#else
+#define RPHASE_DECL
+#define RPHASE(k)
+#endif
 
 constexpr int kBruteMax = 384;     // structures up to this size scan all their points
 constexpr int kSmemCells = 8192;   // upper bound on cells per structure (shared-memory counters)
@@ -25,7 +43,19 @@ constexpr int kCapBits = 8192;     // bitmask window per warp (local point indic
 constexpr int kBuildThreads = 512;
 constexpr int kScanBlock = 1024;
 
-struct CellParam { int gx, gy, gz, use_cells; };
+// Cell grid of one structure.  reach: cells to either side that can hold a neighbour (1: cell edge >= cutoff, 2: >= half
+// of it); tile: handled by the tile kernels (ngroups work items: layers x groups of kTileRY rows), else by the warp kernels.
+struct CellParam { int gx, gy, gz, use_cells, reach, tile, ngroups, pad; };
+
+constexpr int kTileCentres = 64;                          // centres per pass of a block (fewer when the masks of that many do not fit)
+constexpr int kTileTPC = 8;                               // threads per centre
+constexpr int kTileThreads = kTileCentres * kTileTPC;
+constexpr int kTileRY = 4;                                // rows of cells (along y) per work item
+constexpr int kTileMaxRows = (kTileRY + 4) * 5;           // candidate rows of a work item at reach 2
+constexpr int kTileRowsPerThread = (25 + kTileTPC - 1) / kTileTPC;
+constexpr int kTileCand = 2048;                           // candidate points staged per work item (read from global memory beyond that)
+constexpr int kTileMaskWords = 8192;                      // hit masks of one pass (FILL): centres x ceil(n / 32) words
+constexpr int kTileList = 256;                            // compacted bit positions of one emission round, per warp (FILL)
 
 template <typename T> using V4 = typename Vec4<T>::type;
 
@@ -37,7 +67,7 @@ __device__ __forceinline__ double4 make_v4(double x, double y, double z, int i) 
 }
 
 struct WsLayout {
-    size_t spos, cellparam, cell_of, cell_start, struct_of, bsum, total;
+    size_t spos, cellparam, cell_of, cell_start, struct_of, bsum, group_ptr, total;
 };
 static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 static WsLayout ws_layout(int64_t N, int64_t B, int dtype) {
@@ -50,6 +80,7 @@ static WsLayout ws_layout(int64_t N, int64_t B, int dtype) {
     L.cell_start = o;  o += align256((size_t)(N + B) * 4);
     L.struct_of = o;   o += align256((size_t)N * 4);
     L.bsum = o;        o += align256((size_t)((N + kScanBlock - 1) / kScanBlock + 1) * 8);
+    L.group_ptr = o;   o += align256((size_t)(B + 1) * 4);
     L.total = o;
     return L;
 }
@@ -57,7 +88,7 @@ static WsLayout ws_layout(int64_t N, int64_t B, int dtype) {
 // ------------------------------------------------------------------------------------------ build
 template <typename T>
 __global__ void __launch_bounds__(kBuildThreads)
-build_cells_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, T rcut,
+build_cells_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, T rcut, int allow_tile,
                    V4<T> *__restrict__ spos, CellParam *__restrict__ cellparam, int32_t *__restrict__ cell_of,
                    int32_t *__restrict__ cell_start, int32_t *__restrict__ struct_of) {
     __shared__ int counts[kSmemCells + 1];
@@ -72,7 +103,7 @@ build_cells_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, i
         const int64_t n64 = ptr[b + 1] - lo;
         for (int64_t i = tid; i < n64; i += kBuildThreads) struct_of[lo + i] = (int32_t)b;   // structure of every point
         if (n64 <= kBruteMax) {
-            if (tid == 0) cellparam[b] = CellParam{0, 0, 0, 0};
+            if (tid == 0) cellparam[b] = CellParam{0, 0, 0, 0, 0, 0, 0, 0};
             continue;
         }
         const int n = (int)n64;
@@ -107,12 +138,14 @@ build_cells_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, i
                 if (ext[a] > extmax) extmax = ext[a];
             }
             int g[3] = {1, 1, 1};
-            double h = 1.0;
+            double h = 1.0, reach_len = 1.0;
             if (finite && rcut > T(0)) {
-                // Cell edge: the cutoff plus a margin that covers every rounding between the
-                // pair test and the cell assignment, so that a pair passing the test always
-                // sits in adjacent cells.
-                h = (double)rcut * 1.001 + extmax * 1e-6 + 1e-30;
+                // Reach: the cutoff plus a margin that covers every rounding between the pair test and the cell
+                // assignment, so that two points passing the test are less than this apart along every axis.  Cells
+                // start at half of it (a neighbour then sits at most two cells away, and fewer candidates are tested
+                // per hit) and grow until the grid fits the counters.
+                reach_len = (double)rcut * 1.001 + extmax * 1e-6 + 1e-30;
+                h = 0.5 * reach_len;
                 const int maxcells = n < kSmemCells ? n : kSmemCells;
                 for (int it = 0; it < 64; it++) {
                     double prod = 1.0;
@@ -130,7 +163,13 @@ build_cells_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, i
             }
             for (int a = 0; a < 3; a++) { s_org[a] = (T)lo3[a]; s_g[a] = g[a]; }
             s_invh = (T)(1.0 / h);
-            cellparam[b] = CellParam{g[0], g[1], g[2], 1};
+            // cells per reach, rounded up (the cell index is floor((x - origin) / h) with a rounded 1/h: one more cell of slack
+            // is cheap next to a missed pair when h is within rounding of a whole fraction of the reach)
+            int reach = (int)ceil(reach_len / h * (1.0 + 1e-9));
+            if (!(finite && rcut > T(0))) reach = 1;
+            if (reach > 2) reach = 2;                      // h >= reach_len / 2 by construction
+            const int tile = allow_tile && n <= kCapBits;
+            cellparam[b] = CellParam{g[0], g[1], g[2], 1, reach, tile, tile ? g[2] * ((g[1] + kTileRY - 1) / kTileRY) : 0, 0};
         }
         __syncthreads();
         const int gx = s_g[0], gy = s_g[1], gz = s_g[2];
@@ -233,8 +272,9 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
         const int n = (int)(ptr[b + 1] - lo);
         const int il = (int)(i - lo);
         const int64_t ex0 = EXCL ? ex.ptr[i] : 0, ex1 = EXCL ? ex.ptr[i + 1] : 0;   // this centre's excluded neighbours
-        const T xi = pos[i * 3], yi = pos[i * 3 + 1], zi = pos[i * 3 + 2];
         const CellParam cp = cellparam[b];
+        if (cp.tile) continue;                       // this structure's centres belong to the tile kernel
+        const T xi = pos[i * 3], yi = pos[i * 3 + 1], zi = pos[i * 3 + 2];
 
         int64_t kept = 0, base_off = 0;
         if (FILL) {
@@ -271,7 +311,8 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
             const int gx = cp.gx, gy = cp.gy, gz = cp.gz;
             const int c = cell_of[i];
             const int cx = c % gx, cy = (c / gx) % gy, cz = c / (gx * gy);
-            const int x0 = max(cx - 1, 0), x1 = min(cx + 1, gx - 1);
+            const int reach = cp.reach, side = 2 * reach + 1, nrows = side * side;
+            const int x0 = max(cx - reach, 0), x1 = min(cx + reach, gx - 1);
             const int32_t *cs = cell_start + lo + b;
             const V4<T> *sp = spos + lo;
             const int nwin = FILL ? (n + kCapBits - 1) / kCapBits : 1;
@@ -284,11 +325,11 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
                     for (int w = lane; w < nwords; w += 32) mask[w] = 0u;
                     __syncwarp();
                 }
-                // lanes 0-8 fetch the candidate run of one (dy, dz) row each, so the nine pairs of cell-start
-                // reads are in flight together; every lane then keeps two loads per row in flight
+                // the first lanes fetch the candidate run of one (dy, dz) row each (9 rows at reach 1, 25 at reach 2), so
+                // the pairs of cell-start reads are in flight together; every lane then keeps two loads per row in flight
                 int rk0 = 0, rk1 = 0;
-                if (lane < 9) {
-                    const int yy = cy + lane % 3 - 1, zz = cz + lane / 3 - 1;
+                if (lane < nrows) {
+                    const int yy = cy + lane % side - reach, zz = cz + lane / side - reach;
                     if (yy >= 0 && yy < gy && zz >= 0 && zz < gz) {
                         const int rowbase = gx * (yy + gy * zz);
                         rk0 = cs[rowbase + x0];
@@ -308,8 +349,7 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
                         }
                     }
                 };
-#pragma unroll
-                for (int row = 0; row < 9; row++) {
+                for (int row = 0; row < nrows; row++) {
                     const int k0 = __shfl_sync(0xffffffffu, rk0, row), k1 = __shfl_sync(0xffffffffu, rk1, row);
                     const int ka = k0 + lane, kb = ka + 32;
                     V4<T> pa, pb;
@@ -464,6 +504,311 @@ static void launch_scan(const int32_t *deg, int64_t N, int64_t *bsum, int64_t *o
     scan_block_sums_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum);
     scan_of_sums_kernel<<<1, kScanBlock, 0, st>>>(bsum, nb, offsets + N);
     scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum, offsets);
+}
+
+// ------------------------------------------------------------------------------------- tile kernels
+// group_ptr[b] = work items of the structures before b (exclusive scan of CellParam::ngroups), group_ptr[B] = all of them
+__global__ void __launch_bounds__(kScanBlock) group_scan_kernel(const CellParam *__restrict__ cellparam, int64_t B, int32_t *__restrict__ group_ptr) {
+    __shared__ int64_t s_warp[33];
+    int64_t carry = 0;
+    for (int64_t c0 = 0; c0 < B; c0 += kScanBlock) {
+        const int64_t k = c0 + threadIdx.x;
+        const int64_t v = k < B ? cellparam[k].ngroups : 0;
+        int64_t total;
+        const int64_t ex = block_exclusive_scan(v, s_warp, &total);
+        if (k < B) group_ptr[k] = (int32_t)(carry + ex);
+        carry += total;
+    }
+    if (threadIdx.x == 0) group_ptr[B] = (int32_t)carry;
+}
+
+// One work item = the centres of up to kTileRY neighbouring rows of cells (along y) of one layer (z) of one structure: a
+// contiguous run of the cell-sorted points.  Their candidates lie in the rows within `reach` of those, (kTileRY + 2 reach)
+// x (2 reach + 1) whole rows of cells, each a contiguous run as well: staged in shared memory once per item (read straight
+// from global memory when they do not fit).  Four threads share a centre and split its (2 reach + 1)^2 rows; inside a row a
+// centre tests the cells within `reach` of its own along x.  COUNT: hits below / above the centre's own index, summed over
+// the four threads, give the degree under the neighbour-cap rule.  FILL: hits set bits in the centre's mask over the
+// structure's local indices; a warp per centre then walks the mask and writes the edges in ascending order.
+template <typename T, bool FILL>
+__global__ void __launch_bounds__(kTileThreads)
+neighbours_tile_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, T r2, int64_t max_nn, int loop, int rule,
+                       const V4<T> *__restrict__ spos, const CellParam *__restrict__ cellparam, const int32_t *__restrict__ cell_of,
+                       const int32_t *__restrict__ cell_start, const int32_t *__restrict__ group_ptr, int32_t *__restrict__ deg,
+                       const int64_t *__restrict__ offsets, FillOut out, int32_t *__restrict__ status) {
+    extern __shared__ __align__(16) unsigned char tile_smem[];
+    V4<T> *cand = reinterpret_cast<V4<T> *>(tile_smem);
+    unsigned *mask = reinterpret_cast<unsigned *>(tile_smem + (size_t)kTileCand * sizeof(V4<T>));     // FILL: [centres of a pass][nwords]
+    unsigned short *lists = reinterpret_cast<unsigned short *>(mask + kTileMaskWords);                  // FILL: [warps][kTileList]
+    __shared__ int s_k0[kTileMaxRows], s_off[kTileMaxRows + 1];
+    __shared__ int64_t s_base[FILL ? kTileCentres : 1], s_kept[FILL ? kTileCentres : 1];
+    __shared__ int s_il[FILL ? kTileCentres : 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int c = tid / kTileTPC, sub = tid % kTileTPC;
+    const int G = group_ptr[B];
+    RPHASE_DECL
+
+    for (int item = blockIdx.x; item < G; item += gridDim.x) {
+        RPHASE(0)
+        int b;
+        {   // largest b with group_ptr[b] <= item
+            int lo_b = 0, hi_b = (int)B;
+            while (hi_b - lo_b > 1) {
+                const int mid = (lo_b + hi_b) >> 1;
+                if (group_ptr[mid] <= item) lo_b = mid; else hi_b = mid;
+            }
+            b = lo_b;
+        }
+        const CellParam cp = cellparam[b];
+        const int gx = cp.gx, gy = cp.gy, gz = cp.gz, reach = cp.reach, side = 2 * reach + 1;
+        const int64_t lo = ptr[b];
+        const int n = (int)(ptr[b + 1] - lo);
+        const int g = item - group_ptr[b];
+        const int ngy = (gy + kTileRY - 1) / kTileRY;
+        const int cz = g / ngy, cy0 = (g % ngy) * kTileRY, cy1 = min(cy0 + kTileRY, gy);
+        const int32_t *cs = cell_start + lo + b;
+        const V4<T> *sp = spos + lo;
+        const int ylo = cy0 - reach, zlo = cz - reach, YW = (cy1 - cy0) + 2 * reach, nrows = YW * side;
+        // ---- candidate rows: bounds, shared-memory offsets, copy
+        RPHASE(1)
+        if (tid < nrows) {
+            const int yy = ylo + tid % YW, zz = zlo + tid / YW;
+            int k0 = 0, k1 = 0;
+            if (yy >= 0 && yy < gy && zz >= 0 && zz < gz) {
+                k0 = cs[gx * (yy + gy * zz)];
+                k1 = cs[gx * (yy + gy * zz) + gx];
+            }
+            s_k0[tid] = k0;
+            s_off[tid + 1] = k1 - k0;
+        }
+        __syncthreads();
+        if (warp == 0) {                 // exclusive prefix of the row lengths (at most 40 rows: two per lane)
+            const int a = 2 * lane < nrows ? s_off[2 * lane + 1] : 0, bb = 2 * lane + 1 < nrows ? s_off[2 * lane + 2] : 0;
+            int incl = a + bb;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const int excl = incl - a - bb;
+            __syncwarp();
+            if (lane == 0) s_off[0] = 0;
+            if (2 * lane < nrows) s_off[2 * lane + 1] = excl + a;
+            if (2 * lane + 1 < nrows) s_off[2 * lane + 2] = excl + a + bb;
+        }
+        __syncthreads();
+        RPHASE(2)
+        const bool staged = s_off[nrows] <= kTileCand;
+        if (staged) {
+            for (int rw = warp; rw < nrows; rw += kTileThreads / 32) {
+                const int k0 = s_k0[rw], off = s_off[rw], len = s_off[rw + 1] - off;
+                for (int k = lane; k < len; k += 32) cand[off + k] = sp[k0 + k];
+            }
+        }
+        const int c_begin = cs[gx * (cy0 + gy * cz)], c_end = cs[gx * (cy1 - 1 + gy * cz) + gx];
+        const int nwords = (n + 31) >> 5;
+        const int per_pass = FILL ? min(kTileCentres, kTileMaskWords / nwords) : kTileCentres;       // (n <= 8192: at least 32)
+        __syncthreads();
+        RPHASE(3)
+
+        for (int cbase = c_begin; cbase < c_end; cbase += per_pass) {
+            const int ncent = min(per_pass, c_end - cbase);
+            if (FILL) {
+                for (int w = tid; w < ncent * nwords; w += kTileThreads) mask[w] = 0u;
+                __syncthreads();
+            }
+            RPHASE(4)
+            const bool active = c < ncent;
+            int il = 0, cnt_lo = 0, cnt_hi = 0;
+            int64_t i = 0;
+            T xi = T(0), yi = T(0), zi = T(0);
+            if (active) {
+                const V4<T> pc = sp[cbase + c];
+                il = idx_of(pc);
+                i = lo + il;
+                xi = pc.x; yi = pc.y; zi = pc.z;
+                const int cell = cell_of[i];
+                const int cx = cell % gx, cy = (cell / gx) % gy;
+                const int xa = max(cx - reach, 0), xb = min(cx + reach, gx - 1);
+                if (FILL && sub == 0) {
+                    const int64_t o0 = offsets[i];
+                    s_base[c] = o0;
+                    s_kept[c] = offsets[i + 1] - o0;
+                    s_il[c] = il;
+                }
+                const uint32_t cmask = (uint32_t)__cvta_generic_to_shared(mask + (size_t)c * nwords);   // (FILL only)
+                // the bounds of all of this thread's rows first (their loads are in flight together), then the walks
+                int ka[kTileRowsPerThread], kb[kTileRowsPerThread], shift[kTileRowsPerThread];
+#pragma unroll
+                for (int m = 0; m < kTileRowsPerThread; m++) {
+                    const int rr = sub + m * kTileTPC;
+                    const int yy = cy + rr % side - reach, zz = cz + rr / side - reach;
+                    ka[m] = kb[m] = shift[m] = 0;
+                    if (rr < side * side && yy >= 0 && yy < gy && zz >= 0 && zz < gz) {
+                        const int rowbase = gx * (yy + gy * zz);
+                        ka[m] = cs[rowbase + xa];
+                        kb[m] = cs[rowbase + xb + 1];
+                        const int rw = (yy - ylo) + YW * (zz - zlo);
+                        shift[m] = s_off[rw] - s_k0[rw];      // position in the cell-sorted run -> position in the staged copy
+                    }
+                }
+                // four candidates per step, their loads and distance chains independent of one another
+                auto walk = [&](const V4<T> *base, bool shifted) {
+#pragma unroll
+                    for (int m = 0; m < kTileRowsPerThread; m++) {
+                        const V4<T> *q = shifted ? base + shift[m] : base;
+                        const int k1 = kb[m];
+                        for (int k = ka[m]; k < k1; k += 4) {
+                            V4<T> p[4];
+#pragma unroll
+                            for (int u = 0; u < 4; u++) p[u] = q[min(k + u, k1 - 1)];
+#pragma unroll
+                            for (int u = 0; u < 4; u++) {
+                                const T d2 = dist2_rn(xi, yi, zi, p[u].x, p[u].y, p[u].z);
+                                if (k + u < k1 && d2 < r2) {
+                                    const int j = idx_of(p[u]);
+                                    if (FILL) {
+                                        if (loop || j != il)
+                                            asm volatile("red.shared.or.b32 [%0], %1;" ::"r"(cmask + (uint32_t)((j >> 5) << 2)), "r"(1u << (j & 31)) : "memory");
+                                    } else {
+                                        cnt_lo += (j < il);
+                                        cnt_hi += (j > il);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                };
+                if (staged) walk(cand, true);
+                else walk(sp, false);
+            }
+            RPHASE(5)
+            if (!FILL) {
+#pragma unroll
+                for (int o = 1; o < kTileTPC; o <<= 1) {
+                    cnt_lo += __shfl_xor_sync(0xffffffffu, cnt_lo, o);
+                    cnt_hi += __shfl_xor_sync(0xffffffffu, cnt_hi, o);
+                }
+                if (active && sub == 0) {
+                    const int64_t nlo = cnt_lo, nhi = cnt_hi;
+                    const int self_hit = dist2_rn(xi, yi, zi, xi, yi, zi) < r2 ? 1 : 0;
+                    int64_t total, k;
+                    if (loop) {
+                        total = nlo + nhi + self_hit;
+                        k = total < max_nn ? total : max_nn;
+                    } else if (rule == MLCGB_RULE_CLUSTER && self_hit) {
+                        total = nlo + nhi;
+                        if (nlo >= max_nn + 1) k = max_nn + 1;
+                        else k = total < max_nn ? total : max_nn;
+                    } else {
+                        total = nlo + nhi;
+                        k = total < max_nn ? total : max_nn;
+                    }
+                    deg[i] = (int32_t)k;
+                    if (k < total) atomicOr(status, (int)kTruncated);
+                }
+            } else {
+                __syncthreads();
+                RPHASE(6)
+                // ---- emission: a warp per centre walks the mask, 32 words at a time: the set bits of a chunk are compacted
+                //      into a list, then written with consecutive lanes on consecutive slots
+                unsigned short *list = lists + warp * kTileList;
+                const unsigned lt = lanemask_lt();
+                for (int cc = warp; cc < ncent; cc += kTileThreads / 32) {
+                    const int64_t kept = s_kept[cc], base_off = s_base[cc];
+                    if (kept == 0) continue;
+                    const int64_t ic = lo + s_il[cc];
+                    T cxi = T(0), cyi = T(0), czi = T(0);
+                    if (out.distance) { cxi = pos[ic * 3]; cyi = pos[ic * 3 + 1]; czi = pos[ic * 3 + 2]; }
+                    const unsigned *cm = mask + (size_t)cc * nwords;
+                    int64_t emitted = 0;
+                    // four consecutive mask words per lane: 4096 local indices per round (a round whose bits would overflow the
+                    // list is redone word by word below)
+                    for (int w0 = 0; w0 < nwords && emitted < kept; w0 += 128) {
+                        unsigned bits[4];
+                        int cbits = 0;
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int w = w0 + 4 * lane + u;
+                            bits[u] = w < nwords ? cm[w] : 0u;
+                            cbits += __popc(bits[u]);
+                        }
+                        int incl = cbits;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                            if (lane >= o) incl += t;
+                        }
+                        const int total = __shfl_sync(0xffffffffu, incl, 31);
+                        if (total > kTileList) {
+                            // (more neighbours within these 4096 consecutive indices than the list takes: word by word, lane L
+                            // looking at bit L of the word, which keeps the order and needs no list)
+                            for (int ww = w0; ww < min(w0 + 128, nwords) && emitted < kept; ww++) {
+                                const unsigned word = cm[ww];
+                                const int64_t rank = emitted + __popc(word & lt);
+                                if (((word >> lane) & 1u) && rank < kept) {
+                                    const int j = (ww << 5) + lane;
+                                    T d2 = T(0);
+                                    if (out.distance) {
+                                        const int64_t gj = lo + j;
+                                        d2 = dist2_rn(cxi, cyi, czi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]);
+                                    }
+                                    emit_edge<T>(out, base_off + rank, ic, lo + j, b, d2);
+                                }
+                                emitted += __popc(word);
+                            }
+                            continue;
+                        }
+                        int pos_in = incl - cbits;
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            unsigned bw = bits[u];
+                            while (bw) {
+                                const int t = __ffs(bw) - 1;
+                                bw &= bw - 1;
+                                list[pos_in++] = (unsigned short)(((4 * lane + u) << 5) + t);
+                            }
+                        }
+                        __syncwarp();
+                        const int64_t room = kept - emitted;
+                        const int take = (int64_t)total < room ? total : (int)room;
+                        for (int t = lane; t < take; t += 32) {
+                            const int j = (w0 << 5) + (int)list[t];
+                            T d2 = T(0);
+                            if (out.distance) {
+                                const int64_t gj = lo + j;
+                                d2 = dist2_rn(cxi, cyi, czi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]);
+                            }
+                            emit_edge<T>(out, base_off + emitted + t, ic, lo + j, b, d2);
+                        }
+                        __syncwarp();
+                        emitted += total;
+                    }
+                }
+                RPHASE(7)
+                __syncthreads();
+                RPHASE(8)
+            }
+        }
+        __syncthreads();       // the staged rows and their tables are rewritten by the next item
+    }
+}
+
+#ifdef MLCGB_PHASE_TIMING
+extern "C" int mlcgb_debug_radius_phase_cycles(unsigned long long *out, int n, int reset) {
+    unsigned long long host[16];
+    if (cudaMemcpyFromSymbol(host, g_radius_phase_cycles, sizeof(host)) != cudaSuccess) return MLCGB_E_LAUNCH;
+    for (int i = 0; i < n && i < 16; i++) out[i] = host[i];
+    if (reset) {
+        unsigned long long zero[16] = {0};
+        if (cudaMemcpyToSymbol(g_radius_phase_cycles, zero, sizeof(zero)) != cudaSuccess) return MLCGB_E_LAUNCH;
+    }
+    return MLCGB_OK;
+}
+#endif
+
+template <typename T, bool FILL>
+static size_t tile_smem_bytes() {
+    return (size_t)kTileCand * sizeof(V4<T>) + (FILL ? (size_t)kTileMaskWords * sizeof(unsigned) + (size_t)(kTileThreads / 32) * kTileList * 2 : 0);
 }
 
 __global__ void batch_to_ptr_kernel(const int64_t *__restrict__ batch, int64_t N, int64_t B, int64_t *__restrict__ ptr) {
@@ -703,10 +1048,30 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
     auto *cell_start = (int32_t *)(w + L.cell_start);
     auto *struct_of = (int32_t *)(w + L.struct_of);
     auto *bsum = (int64_t *)(w + L.bsum);
+    auto *group_ptr = (int32_t *)(w + L.group_ptr);
     const T r2 = (T)(r * r);
     const int nbr_grid = grid_for(N, kNbrWarps, 32);
+    // the tile kernels take structures with a cell grid and at most kCapBits points (none when pairs are excluded); a batch
+    // of small structures only (fewer points than one cell-grid structure needs, on average) cannot hold one
+    const bool tiles = !ex.ptr && N > kBruteMax;
+    static bool configured[64][4] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int variant = (sizeof(T) == 8 ? 2 : 0) + (fill ? 1 : 0);
+    if (tiles && dev >= 0 && dev < 64 && !configured[dev][variant]) {
+        cudaError_t e = fill ? cudaFuncSetAttribute(neighbours_tile_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem_bytes<T, true>())
+                             : cudaFuncSetAttribute(neighbours_tile_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem_bytes<T, false>());
+        if (e != cudaSuccess) return check_launch();
+        configured[dev][variant] = true;
+    }
+    const int tile_grid = kNumSM * (fill ? 2 : 4);     // (blocks resident per SM: registers allow two of the fill kernel)
     if (!fill) {
-        build_cells_kernel<T><<<grid_for(B, 1, 8), kBuildThreads, 0, st>>>(pos, ptr, B, (T)r, spos, cellparam, cell_of, cell_start, struct_of);
+        build_cells_kernel<T><<<grid_for(B, 1, 8), kBuildThreads, 0, st>>>(pos, ptr, B, (T)r, tiles ? 1 : 0, spos, cellparam, cell_of, cell_start, struct_of);
+        if (tiles) {
+            group_scan_kernel<<<1, kScanBlock, 0, st>>>(cellparam, B, group_ptr);
+            neighbours_tile_kernel<T, false><<<tile_grid, kTileThreads, tile_smem_bytes<T, false>(), st>>>(
+                pos, ptr, B, r2, max_nn, loop, rule, spos, cellparam, cell_of, cell_start, group_ptr, deg, nullptr, out, status);
+        }
         if (ex.ptr)
             neighbours_kernel<T, false, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
                                                                                    cell_of, cell_start, struct_of, deg, nullptr, out, ex, status);
@@ -715,6 +1080,9 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
                                                                                     cell_of, cell_start, struct_of, deg, nullptr, out, ex, status);
         launch_scan(deg, N, bsum, offsets, st);
     } else {
+        if (tiles)
+            neighbours_tile_kernel<T, true><<<tile_grid, kTileThreads, tile_smem_bytes<T, true>(), st>>>(
+                pos, ptr, B, r2, 0, loop, 0, spos, cellparam, cell_of, cell_start, group_ptr, nullptr, offsets, out, status);
         if (ex.ptr)
             neighbours_kernel<T, true, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
                                                                                   cell_of, cell_start, struct_of, nullptr, offsets, out, ex, status);

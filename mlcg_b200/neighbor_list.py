@@ -38,9 +38,9 @@ def _structure_ptr(x, batch, batch_size):
     return be.batch_to_ptr(batch.to(torch.int64), batch_size)
 
 
-def _graph(x, r, ptr, loop, max_num_neighbors, rule, want_distance=False, exclude=None):
+def _graph(x, r, ptr, loop, max_num_neighbors, rule, want_distance=False, exclude=None, want_batch=False):
     be = get_backend()
-    res = be.radius_graph(_as_3d(x), ptr, r, max_num_neighbors, loop, rule, want_distance=want_distance, exclude=exclude)
+    res = be.radius_graph(_as_3d(x), ptr, r, max_num_neighbors, loop, rule, want_distance=want_distance, want_batch=want_batch, exclude=exclude)
     truncated = bool(res["status"] & STATUS_TRUNCATED)
     # an exclusion list need not hold both directions of a pair: such a graph is not taken to be symmetric
     plan = EdgePlan.from_centre_sorted(res["row0"], res["row1"], res["offsets"], x.shape[0], symmetric=not truncated and exclude is None,
@@ -218,7 +218,7 @@ def atomic_data2neighbor_list(data, rcut: float, self_interaction: bool = False,
         torch.cumsum(n_atoms.to(device=pos.device, dtype=torch.int64), 0, out=ptr[1:])
     else:
         ptr = _structure_ptr(pos, batch, None)
-    res = _graph(pos, rcut, ptr, self_interaction, max_num_neighbors, RULE_CLUSTER)
+    res = _graph(pos, rcut, ptr, self_interaction, max_num_neighbors, RULE_CLUSTER, want_batch=True)
     mapping = res["edge_index"]
     # The reference asserts batch[mapping[0]] == batch[mapping[1]] here (a device->host sync,
     # neighbor_list.py:89-91); the kernel only ever pairs points of one structure, by construction.
