@@ -515,7 +515,7 @@ def training_step_measurement(dev, world, steps=10, warmup=3):
     from mlcg_b200.backend import get_backend
     get_backend().check_pending()
     ar_ms = sum(x.elapsed_time(y) for x, y in ar_events) / steps if ar_events else 0.0
-    return a.elapsed_time(b) / steps, ar_ms, float(loss), B, sum(p.numel() for p in params)
+    return a.elapsed_time(b) / steps, ar_ms, float(loss.detach()), B, sum(p.numel() for p in params)
 
 
 def training_cpu_leg(arm, steps=2):
