@@ -307,11 +307,8 @@ def _baoab_host(model_fn, pos, vel, forces, masses, beta_mass_ratio, noises, dt,
     return pos, vel, pot, forces
 
 
-def extra_measurements(dev, hbm_peak, arm):
-    """The other configurations on one GPU: the small CPU-runnable system (64 x 10 beads), the stand-alone radius graph (256 x 4000
-    points, 60 A cube, 10 A cutoff, compared bit for bit with the CPU oracle on all 256 structures), the prior terms and the
-    Langevin dynamics of the simulation configuration (1024 x 268 beads).  Device time by CUDA events; inputs far larger than L2
-    except where the configuration itself is small.  Each GPU figure has the CPU arm's figure beside it (bounded samples)."""
+def measure_small(dev, hbm_peak, arm, seed=0):
+    """The CPU-runnable configuration: 64 structures x 10 beads, energy + forces, with the CPU arm beside it."""
     import mlcg_b200
     from mlcg_b200 import nn as bnn
     from mlcg_b200.backend import get_backend
@@ -319,8 +316,7 @@ def extra_measurements(dev, hbm_peak, arm):
     from oracle import radius_ref
     be = get_backend()
     out = {}
-    gen = torch.Generator().manual_seed(0)
-
+    gen = torch.Generator().manual_seed(seed)
     # ---- the CPU-runnable configuration: 64 structures x 10 beads, types 0..9, 50 Gaussians on 0-30 A, 2 blocks
     B1, n1 = 64, 10
     arch1 = dict(kind="gaussian", cutoff=30.0, num_rbf=50, interactions=2, n_types=10)
@@ -346,8 +342,22 @@ def extra_measurements(dev, hbm_peak, arm):
                                   "GPU time is the host's launch path at this size; CPU: all 64 structures, 10 calls")
     del m1, net1
 
+    return out
+
+
+def measure_radius(dev, hbm_peak, arm, radius_structures=256, seed=1):
+    """The stand-alone radius graph: structures of 4000 points uniform in a 60 A cube, 10 A cutoff, no loops; the whole edge list
+    is compared with the CPU oracle's."""
+    import mlcg_b200
+    from mlcg_b200 import nn as bnn
+    from mlcg_b200.backend import get_backend
+    from mlcg_b200.simulation import LangevinSimulation
+    from oracle import radius_ref
+    be = get_backend()
+    out = {}
+    gen = torch.Generator().manual_seed(seed)
     # ---- stand-alone radius graph
-    B, n = 256, 4000
+    B, n = radius_structures, 4000
     pos_h = torch.rand(B * n, 3, generator=gen) * 60.0
     pos = pos_h.to(dev)
     ptr = torch.arange(B + 1, device=dev) * n
@@ -359,18 +369,31 @@ def extra_measurements(dev, hbm_peak, arm):
     same = bool(torch.equal(res["edge_index"].cpu(), torch.from_numpy(ei_cpu)))
     del res, ei_cpu
     if not same:
-        raise RuntimeError("radius graph of 256 x 4000 points differs from the CPU oracle's")
+        raise RuntimeError(f"radius graph of {B} x 4000 points differs from the CPU oracle's")
     ms = time_cuda(lambda: be.radius_graph(pos, ptr, 10.0, 1000, False, 1, want_batch=False), iters=5, warm=1)
     nbytes = 16 * E + 20 * B * n
-    out["radius_graph_256x4000"] = dict(edges=E, ms=ms, edges_per_s=E / (ms / 1e3), algorithmic_GBps=nbytes / ms / 1e6,
+    out[f"radius_graph_{B}x4000"] = dict(edges=E, ms=ms, edges_per_s=E / (ms / 1e3), algorithmic_GBps=nbytes / ms / 1e6,
                                         frac_of_hbm=nbytes / ms / 1e6 / hbm_peak, bit_exact_vs_cpu_oracle=same, cpu_ms=cpu_s * 1e3,
                                         cpu_edges_per_s=E / cpu_s, cpu_cores=arm.cores,
                                         note="count + scan + host read of E + fill, allocation of the outputs included; algorithmic bytes = 16 B/edge "
                                              "written + 20 B/point read (the call also writes the two int32 index rows this package's kernels "
                                              "read, 8 B/edge more); CPU: the C oracle (all pairs of each structure, OpenMP over structures), "
-                                             "all 256 structures, one call; the two edge lists are compared whole")
+                                             "every structure, one call; the two edge lists are compared whole")
     del pos
 
+    return out
+
+
+def measure_priors_and_dynamics(dev, hbm_peak, arm, seed=2, dynamics=True):
+    """The prior terms and the Langevin dynamics of the simulation configuration (1024 replicas x 268 beads)."""
+    import mlcg_b200
+    from mlcg_b200 import nn as bnn
+    from mlcg_b200.backend import get_backend
+    from mlcg_b200.simulation import LangevinSimulation
+    from oracle import radius_ref
+    be = get_backend()
+    out = {}
+    gen = torch.Generator().manual_seed(seed)
     # ---- priors of the simulation configuration
     Bp, npb, T = 1024, 268, 20
     terms = _chain_terms(npb)
@@ -388,17 +411,32 @@ def extra_measurements(dev, hbm_peak, arm):
                                              frac_of_hbm=nbytes / ms / 1e6 / hbm_peak)
         del params
 
+    # ---- the four priors together, as SumOut evaluates them in eval mode: one launch, 32-bit indices, no scatter for the pair
+    #      list that holds both directions, sums in fixed point (reproducible) or with floating-point atomics
+    pri = {k: p.to(dev).eval() for k, p in _prior_modules(bnn, T).items()}
+    nls = {name: mlcg_b200.make_neighbor_list(name, m.shape[0], m, mb) for name, (m, mb) in lists.items()}
+    types5_h = torch.randint(0, T, (Bp * npb,), generator=gen)
+    data = mlcg_b200.AtomicData(pos=ppos.clone(), atom_types=types5_h.to(dev), batch=torch.arange(Bp, device=dev).repeat_interleave(npb),
+                                n_atoms=torch.full((Bp,), npb, device=dev), neighbor_list=nls)
+    M_all = sum(int(m.shape[1]) for m, _ in lists.values())
+    moved = sum(int(m.numel()) * 4 + int(m.shape[1]) * 4 * n_par[name] for name, (m, _) in lists.items()) + 2 * ppos.numel() * 4
+    for mode, flag in (("fixed_point", True), ("float_atomics", False)):
+        bnn.set_prior_determinism(flag)
+        ms = time_cuda(lambda: bnn.evaluate_priors(list(pri.values()), data), iters=5, warm=2)
+        out[f"priors_together_1024x268_{mode}"] = dict(terms=M_all, ms=ms, terms_per_s=M_all / (ms / 1e3), moved_GBps=moved / ms / 1e6,
+                                                        frac_of_hbm=moved / ms / 1e6 / hbm_peak,
+                                                        note="bonds + angles + dihedrals + repulsion in one launch; bytes moved: int32 indices, "
+                                                             "float32 per-term parameters, positions in, gradients out")
+    bnn.set_prior_determinism(True)
+    if not dynamics:
+        return out
     # ---- Langevin dynamics: 1024 replicas x 268 beads, SchNet (3 blocks, 12 A) + the four priors, BAOAB, graph rebuilt every step
     arch5 = dict(cutoff=12.0, n_types=T)
     net = make_model(**arch5)
     sd5 = {k: v.detach().clone() for k, v in net.state_dict().items()}
     models = {"SchNet": bnn.GradientsOut(net, "forces")}
-    models.update({k: bnn.GradientsOut(p, "forces") for k, p in _prior_modules(bnn, T).items()})
+    models.update({k: bnn.GradientsOut(p, "forces") for k, p in pri.items()})
     model = bnn.SumOut(torch.nn.ModuleDict(models)).eval().to(dev)
-    nls = {name: mlcg_b200.make_neighbor_list(name, m.shape[0], m, mb) for name, (m, mb) in lists.items()}
-    types5_h = torch.randint(0, T, (Bp * npb,), generator=gen)
-    data = mlcg_b200.AtomicData(pos=ppos.clone(), atom_types=types5_h.to(dev), batch=torch.arange(Bp, device=dev).repeat_interleave(npb),
-                                n_atoms=torch.full((Bp,), npb, device=dev), neighbor_list=nls)
     mass = 12.0 / 418.39
     sim = LangevinSimulation(model, dt=0.002, friction=1.0, beta=KCAL_BETA_300K, rng=torch.Generator(device=dev).manual_seed(0))
     sim.attach(data, torch.full((Bp * npb,), mass, device=dev))
@@ -461,6 +499,19 @@ def extra_measurements(dev, hbm_peak, arm):
                                     cpu=cpu, cpu_cores=arm.cores,
                                     note="SchNet (3 blocks, 128 expnorm RBF, 12 A) + bonds/angles/dihedrals/repulsion(|i-j|>=3), BAOAB dt=2 fs, "
                                          "radius graph rebuilt every step, 1024 replicas on one GPU")
+    return out
+
+
+def extra_measurements(dev, hbm_peak, arm):
+    """The other configurations on one GPU: the small CPU-runnable system (64 x 10 beads), the stand-alone radius graph (256 x 4000
+    points, 60 A cube, 10 A cutoff, compared bit for bit with the CPU oracle on all 256 structures), the prior terms and the
+    Langevin dynamics of the simulation configuration (1024 x 268 beads).  Device time by CUDA events; inputs far larger than L2
+    except where the configuration itself is small.  Each GPU figure has the CPU arm's figure beside it (bounded samples)."""
+    out = {}
+    out.update(measure_small(dev, hbm_peak, arm))
+    out.update(measure_radius(dev, hbm_peak, arm))
+    torch.cuda.empty_cache()
+    out.update(measure_priors_and_dynamics(dev, hbm_peak, arm))
     return out
 
 
@@ -837,6 +888,26 @@ def run_ours(args):
     print(json.dumps(line))
 
 
+def run_only(args):
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    try:
+        hbm_peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("hbm_gbs", 6650.0)
+    except OSError:
+        hbm_peak = 6650.0
+    arm = CpuArm()
+    if args.only == "small":
+        rec = measure_small(dev, hbm_peak, arm)
+    elif args.only == "radius":
+        rec = measure_radius(dev, hbm_peak, arm, radius_structures=args.radius_structures)
+    elif args.only in ("priors", "dynamics"):
+        rec = measure_priors_and_dynamics(dev, hbm_peak, arm, dynamics=args.only == "dynamics")
+    else:
+        ms, ar, loss, B, n_params = training_step_measurement(dev, 1, steps=max(args.steps, 1) if args.steps != 50 else 10, warmup=max(args.warmup, 1) if args.warmup != 10 else 3)
+        rec = {"training_step_256x73": dict(ms_per_step=ms, structures_per_s=B / (ms / 1e3), loss=loss, parameters=n_params)}
+    print(json.dumps(rec))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -846,11 +917,16 @@ def main():
     ap.add_argument("--structures", type=int, default=None, help="structures per GPU (default 512; smaller values are for profiler captures)")
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations (radius graph, priors, dynamics, training step)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU arm: no baseline and no parity check of the timed batch (profiler captures)")
+    ap.add_argument("--only", default=None, choices=["small", "radius", "priors", "dynamics", "training"],
+                    help="run one of the other configurations alone on one GPU and print its record (profiler captures)")
+    ap.add_argument("--radius-structures", type=int, default=256, help="structures of 4000 points for --only radius")
     args = ap.parse_args()
     if args.structures:
         WORKLOAD["structures_per_gpu"] = args.structures
         WORKLOAD["workload"] += f" [REDUCED to {args.structures} structures/GPU: not the benchmark configuration]"
-    if args.impl == "reference":
+    if args.only:
+        run_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

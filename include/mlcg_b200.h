@@ -417,6 +417,32 @@ int mlcgb_prior_terms(int kind, const void *pos /* [N,3] */, int dtype, const in
                       const void *params, int n_params, int64_t M, int64_t N, int64_t B, void *energy /* [B] */,
                       void *grad /* [N,3] or NULL */, int32_t *status, void *stream);
 
+/* Every prior of a model in one launch (what SumOut.forward adds up one model at a time, src/mlcg/nn/gradients.py:111-117, over
+ * the flat per-term parameters that condense_all_priors_for_simulation prepares, src/mlcg/simulation/specialize_prior.py:75-206).
+ * Each list has 32-bit indices idx [order, M], per-term parameters params [n_params, M] as for mlcgb_prior_terms, and its own
+ * row of energy [n_lists, B] and block of grad [n_lists, N, 3]; the structure of a term is struct_of[its first bead].
+ * `symmetric` (pair kinds only): the list holds (j, i) for every (i, j), as mlcg's fully connected lists do
+ * (src/mlcg/geometry/topology.py:131-135); the gradient of bead i is then formed from i's own terms alone (twice their sum)
+ * and nothing is scattered to the second bead; with `run_ptr` (lists grouped by first bead, as those lists are) a warp takes a
+ * whole run and adds once per bead, otherwise the reduction runs over what a warp happens to hold.  fixed_point = 0: energy and grad are ACCUMULATED into with floating-point
+ * atomics (zero them first; the order of the additions, and so the last bits, vary from run to run).  fixed_point = 1:
+ * sums are formed as 64-bit fixed-point integers in `workspace` (mlcgb_prior_eval_workspace_bytes) and then WRITTEN to energy and
+ * grad: bit-identical from run to run, resolution 2^-36, magnitudes up to 1.3e8. */
+#define MLCGB_MAX_PRIOR_SEGMENTS 8
+typedef struct {
+    int kind, n_params, symmetric, reserved;
+    int64_t M;
+    const int32_t *idx;
+    const void *params;
+    const int64_t *run_ptr; /* NULL, or [n_runs + 1]: the terms [run_ptr[k], run_ptr[k+1]) of a symmetric list share their first bead */
+    int64_t n_runs;
+} mlcgb_prior_list;
+size_t mlcgb_prior_eval_workspace_bytes(int n_lists, int64_t N, int64_t B, int fixed_point);
+int mlcgb_prior_eval(int n_lists, const mlcgb_prior_list *lists /* host */, const void *pos /* [N,3] */, int dtype,
+                     const int32_t *struct_of /* [N] */, int64_t N, int64_t B, void *energy /* [n_lists,B] */,
+                     void *grad /* [n_lists,N,3] */, int fixed_point, void *workspace, size_t workspace_bytes, int32_t *status,
+                     void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * BAOAB Langevin step around the force evaluation, LangevinSimulation.timestep,
  * src/mlcg/simulation/langevin.py:100-144.  x, v are updated in place; `noise` holds the normal deviates

@@ -35,6 +35,15 @@ class SchnetWeightsStruct(ctypes.Structure):
                 ("head_out_b", c_vp)]
 
 
+class PriorListStruct(ctypes.Structure):
+    """Mirror of ``mlcgb_prior_list``."""
+
+    _fields_ = [("kind", c_int), ("n_params", c_int), ("symmetric", c_int), ("reserved", c_int), ("M", c_i64), ("idx", c_vp), ("params", c_vp),
+                ("run_ptr", c_vp), ("n_runs", c_i64)]
+
+
+MAX_PRIOR_SEGMENTS = 8
+
 # name -> (restype, argtypes); one entry per symbol declared in include/mlcg_b200.h
 SIGNATURES = {
     "mlcgb_strerror": (ctypes.c_char_p, [c_int]),
@@ -99,6 +108,8 @@ SIGNATURES = {
     "mlcgb_langevin_first_half": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_dbl, c_dbl, c_dbl, c_vp]),
     "mlcgb_langevin_second_half": (c_int, [c_vp, c_vp, c_vp, c_int, c_i64, c_dbl, c_vp]),
     "mlcgb_prior_terms": (c_int, [c_int, c_vp, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp]),
+    "mlcgb_prior_eval_workspace_bytes": (c_sz, [c_int, c_i64, c_i64, c_int]),
+    "mlcgb_prior_eval": (c_int, [c_int, ctypes.POINTER(PriorListStruct), c_vp, c_int, c_vp, c_i64, c_i64, c_vp, c_vp, c_int, c_vp, c_sz, c_vp, c_vp]),
 }
 
 _lib = None

@@ -725,6 +725,43 @@ class CudaBackend:
         return energy, grad
 
 
+    def prior_eval(self, lists, pos, struct_of, B, deterministic=True):
+        """Every prior list of a model in one launch.  ``lists``: sequence of ``(kind, idx32 [order, M], params [P, M], symmetric,
+        run_ptr | None)`` (at most ``_lib.MAX_PRIOR_SEGMENTS``; ``run_ptr`` int64: runs of equal first bead of a symmetric pair list).  Returns ``(energy [n, B], dE/dpos [n, N, 3])``, one row / block per list.
+        ``deterministic``: sums formed as 64-bit fixed-point integers (bit-identical from run to run)."""
+        _need_cuda(pos, struct_of)
+        n = len(lists)
+        if n == 0 or n > _lib.MAX_PRIOR_SEGMENTS:
+            raise ValueError(f"between 1 and {_lib.MAX_PRIOR_SEGMENTS} prior lists per launch")
+        pos = pos.detach().contiguous()
+        N, dev = pos.shape[0], pos.device
+        arr = (_lib.PriorListStruct * n)()
+        keep = []
+        for k, (kind, idx, params, symmetric, run_ptr) in enumerate(lists):
+            _need_cuda(idx, params, run_ptr)
+            if idx.dtype != torch.int32 or params.dtype != pos.dtype or (run_ptr is not None and run_ptr.dtype != torch.int64):
+                raise TypeError("prior lists take int32 indices, int64 run pointers and parameters of the positions' dtype")
+            idx, params = idx.contiguous(), params.contiguous()
+            run_ptr = None if run_ptr is None else run_ptr.contiguous()
+            keep += [idx, params, run_ptr]
+            arr[k] = _lib.PriorListStruct(int(kind), int(params.shape[0]), int(bool(symmetric)), 0, int(idx.shape[1]), idx.data_ptr(), params.data_ptr(),
+                                          _ptr(run_ptr), 0 if run_ptr is None else run_ptr.numel() - 1)
+        fixed = 1 if deterministic else 0
+        make = torch.empty if fixed else torch.zeros               # (the fixed-point mode writes its outputs, the other adds to them)
+        buf = make(n * (3 * N + B), dtype=pos.dtype, device=dev)
+        grad, energy = buf[: n * 3 * N].view(n, N, 3), buf[n * 3 * N:].view(n, B)
+        status = self._sticky_status(dev)
+        with _on(dev):
+            wsb = self.lib.mlcgb_prior_eval_workspace_bytes(n, N, B, fixed)
+            ws = torch.empty(wsb, dtype=torch.uint8, device=dev) if wsb else None
+            M_total = sum(int(l[1].shape[1]) for l in lists)
+            self._run("prior_eval", self.lib.mlcgb_prior_eval,
+                      (n, arr, _ptr(pos), _dt(pos), _ptr(struct_of), N, B, _ptr(energy), _ptr(grad), fixed, _ptr(ws), wsb, _ptr(status), _stream()),
+                      launches=3 if fixed else 1, nbytes=sum(l[1].numel() * 4 + l[2].numel() * pos.element_size() for l in lists) + 2 * pos.numel() * pos.element_size(),
+                      flops=40 * M_total)
+        return energy, grad
+
+
 _backend = None
 
 

@@ -59,11 +59,32 @@ class SumOut(torch.nn.Module):
     def forward(self, data):
         for target in self.targets:
             data.out[target] = 0.00
+        together = self._priors_together(data)
         for name in self.models.keys():
-            data = self.models[name](data)
+            if name in together:
+                energy, dy_dr = together[name]
+                data.out[self.models[name].name] = {ENERGY_KEY: energy, FORCE_KEY: -dy_dr}
+            else:
+                data = self.models[name](data)
             for target in self.targets:
                 data.out[target] += data.out[name][target]
         return data
+
+    def _priors_together(self, data):
+        """Eval mode: every prior component that is wrapped for forces is evaluated in one launch with the others
+        (:func:`mlcg_b200.nn.prior.evaluate_priors`); the results are handed out component by component in ``forward``."""
+        from .prior import _Prior, evaluate_priors
+        if self.training:
+            return {}
+        picked = {name: m.model for name, m in self.models.items()
+                  if isinstance(m, GradientsOut) and isinstance(m.model, _Prior) and not m.training and FORCE_KEY in m.targets and m.name == name}
+        if len(picked) < 2:
+            return {}
+        res = evaluate_priors(picked.values(), data)
+        if res is None:
+            return {}
+        data.pos = data.pos.detach()
+        return {name: res[p.name] for name, p in picked.items()}
 
     def neighbor_list(self, **kwargs):
         nl = {}

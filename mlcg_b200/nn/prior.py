@@ -14,6 +14,15 @@ from ..backend import get_backend
 
 KIND_BOND, KIND_ANGLE, KIND_DIHEDRAL, KIND_REPULSION = 0, 1, 2, 3
 
+#: Energies and forces of the priors evaluated together (:func:`evaluate_priors`) are summed as 64-bit fixed-point integers, so they
+#: are bit-identical from run to run; ``set_prior_determinism(False)`` sums with floating-point atomics instead.
+_DETERMINISTIC = True
+
+
+def set_prior_determinism(on: bool) -> None:
+    global _DETERMINISTIC
+    _DETERMINISTIC = bool(on)
+
 
 class _PriorEnergy(torch.autograd.Function):
     @staticmethod
@@ -142,6 +151,37 @@ class _Prior(torch.nn.Module):
             cached = (key, self._params(data).to(data.pos.dtype).contiguous(), (mapping, types_) + tables)
             self.__dict__["_param_cache"] = cached
         return cached[1]
+
+    def _cached_list(self, data):
+        """``(kind, idx32 [order, M], params [P, M], symmetric, run_ptr | None)`` for :func:`evaluate_priors`: the index list as 32-bit integers and,
+        for pair priors, whether it holds (j, i) for every (i, j) with the same parameters (then forces need no scatter to the second
+        bead).  Both are worked out once per index list and parameter set (identity and version of the tensors) and kept on the
+        module."""
+        mapping = data.neighbor_list[self.name]["index_mapping"]
+        params = self._cached_params(data)
+        key = (mapping.data_ptr(), mapping._version, tuple(mapping.shape), mapping.device, id(params))
+        cached = self.__dict__.get("_list_cache")
+        if cached is None or cached[0] != key:
+            idx32 = mapping.to(torch.int32).contiguous()
+            symmetric = False
+            if self.kind in (KIND_BOND, KIND_REPULSION) and mapping.shape[1] > 0 and mapping.shape[1] % 2 == 0:
+                # (i, j) and (j, i) both listed, with the same parameters: the two sorted key lists agree, and so do the
+                # parameters taken along in the two orders
+                n = int(data.pos.shape[0])
+                fwd, pf = torch.sort(mapping[0] * n + mapping[1])
+                rev, pr = torch.sort(mapping[1] * n + mapping[0])
+                symmetric = bool(torch.equal(fwd, rev)) and bool(torch.equal(params[:, pf], params[:, pr]))
+                del fwd, rev, pf, pr
+            run_ptr = None
+            if symmetric:
+                # runs of equal first bead (lists built from a topology are grouped by it): a warp then takes a bead's whole run
+                first = idx32[0]
+                starts = torch.nonzero(first[1:] != first[:-1]).flatten() + 1
+                if mapping.shape[1] >= 8 * (starts.numel() + 1):
+                    run_ptr = torch.cat([starts.new_zeros(1), starts, starts.new_full((1,), mapping.shape[1])]).to(torch.int64)
+            cached = (key, idx32, symmetric, mapping, params, run_ptr)
+            self.__dict__["_list_cache"] = cached
+        return self.kind, cached[1], params, cached[2], cached[5]
 
     def energy_and_gradient(self, data):
         """(energy [B], d(sum of energies)/d(pos) [N,3]) straight from the prior kernel, without an autograd graph; None where
@@ -315,3 +355,25 @@ class Dihedral(FourierSeries):
     @staticmethod
     def compute_features(pos, mapping, pbc=None, cell=None, batch=None):
         return _torsions(pos, mapping, _feature_shifts(pos, mapping, pbc, cell, batch))
+
+
+def evaluate_priors(priors, data):
+    """Energies and position gradients of several priors on ``data`` from one kernel launch (per eight priors): ``{name: (energy
+    [B], dE/dpos [N,3])}``, or None where that route does not apply (training mode, tensors off the device, periodic data).  What
+    ``SumOut`` calls for its prior components in eval mode, instead of one launch and one pass over the positions per prior."""
+    priors = list(priors)
+    if not priors or not data.pos.is_cuda or any(p.training for p in priors):
+        return None
+    if getattr(data, "pbc", None) is not None and getattr(data, "cell", None) is not None:
+        return None
+    from .._lib import MAX_PRIOR_SEGMENTS
+    B = _num_structures(data)
+    struct_of = _batch_or_zeros(data).to(torch.int32)
+    out = {}
+    be = get_backend()
+    for lo in range(0, len(priors), MAX_PRIOR_SEGMENTS):
+        chunk = priors[lo:lo + MAX_PRIOR_SEGMENTS]
+        energy, grad = be.prior_eval([p._cached_list(data) for p in chunk], data.pos, struct_of, B, deterministic=_DETERMINISTIC)
+        for k, p in enumerate(chunk):
+            out[p.name] = (energy[k], grad[k])
+    return out

@@ -239,6 +239,53 @@ def test_forces_are_reproducible_run_to_run():
     assert torch.equal(a.out["SchNet"]["forces"], b.out["SchNet"]["forces"]) and torch.equal(a.out["SchNet"]["energy"], b.out["SchNet"]["energy"])
 
 
+def test_sumout_of_schnet_and_four_priors_is_reproducible_and_matches_the_parts():
+    """SumOut(SchNet + bonds + angles + dihedrals + repulsion) in eval mode: the priors are evaluated together in one launch with
+    fixed-point sums.  Two evaluations give bit-identical energies and forces; every component equals what the same prior gives
+    on its own (separate launches, floating-point atomics) to rounding; the totals are the sums of the components."""
+    from mlcg_b200.nn.prior import evaluate_priors
+    data, priors = prior_setup(60, 6, 4, torch.Generator().manual_seed(9))
+    with torch.no_grad():      # sigma[a, b] = sigma[b, a], as physical tables are: the (i, j) and (j, i) terms are then equal
+        priors["repulsion"].sigma.copy_(0.5 * (priors["repulsion"].sigma + priors["repulsion"].sigma.t()))
+    torch.manual_seed(1)
+    cut = bnn.CosineCutoff(0.0, 12.0)
+    net = bnn.StandardSchNet(bnn.ExpNormalBasis(cut, 32, trainable=False), cut, [128], hidden_channels=128, embedding_size=4, num_filters=128,
+                             num_interactions=2)
+    models = {"SchNet": bnn.GradientsOut(net, "forces")}
+    models.update({k: bnn.GradientsOut(p, "forces") for k, p in priors.items()})
+    model = bnn.SumOut(torch.nn.ModuleDict(models)).eval().to(DEV)
+    data = data.to(DEV)
+    assert priors["repulsion"].to(DEV)._cached_list(data)[3] is True           # both (i, j) and (j, i) are listed: no scatter
+    assert priors["bonds"].to(DEV)._cached_list(data)[3] is False
+    lopsided = bnn.Repulsion({(a, b): {"sigma": 3.0 + a + 0.1 * b} for a in range(4) for b in range(4)}).to(DEV)
+    assert lopsided._cached_list(data)[3] is False                              # sigma[a, b] != sigma[b, a]: every term scatters
+    def run():
+        data.out = {}
+        out = model(data)
+        return {k: (v["energy"].clone(), v["forces"].clone()) for k, v in out.out.items() if isinstance(v, dict)}, out.out["energy"].clone(), out.out["forces"].clone()
+    parts_a, e_a, f_a = run()
+    parts_b, e_b, f_b = run()
+    assert torch.equal(e_a, e_b) and torch.equal(f_a, f_b)
+    for k in parts_a:
+        assert torch.equal(parts_a[k][0], parts_b[k][0]) and torch.equal(parts_a[k][1], parts_b[k][1]), k
+    assert torch.allclose(e_a, sum(v[0] for v in parts_a.values()), rtol=1e-6)
+    assert torch.allclose(f_a, sum(v[1] for v in parts_a.values()), rtol=1e-5, atol=1e-4)
+    for k, p in priors.items():           # each prior alone: its own kernel launch, floating-point atomics
+        data.out = {}
+        alone = bnn.GradientsOut(p, "forces").eval()(data).out[k]
+        assert torch.allclose(parts_a[k][0], alone["energy"], rtol=1e-5), k
+        scale = float(alone["forces"].abs().max())
+        assert float((parts_a[k][1] - alone["forces"]).abs().max()) < 1e-5 * scale + 1e-5, k
+    bnn.set_prior_determinism(False)        # the same through floating-point atomics
+    try:
+        res = evaluate_priors(priors.values(), data)
+        for k in priors:
+            assert torch.allclose(res[k][0], parts_a[k][0], rtol=1e-5), k
+            assert float((-res[k][1] - parts_a[k][1]).abs().max()) < 1e-5 * float(parts_a[k][1].abs().max()) + 1e-5, k
+    finally:
+        bnn.set_prior_determinism(True)
+
+
 def test_truncated_neighbour_list_uses_general_plan():
     """max_num_neighbors below the real degree: the graph stops being symmetric and the general edge plan must agree with the oracle."""
     model, pos, types_, batch = _make("gaussian", 4, 40, 5, 12.0, 20, 32, 2, 4, jitter=0.2)
