@@ -599,10 +599,10 @@ def training_cpu_leg(arm, steps=2):
 def kernel_work(name, E, P, N, F, R):
     """Algorithmic (bytes, flops) of one call of a library entry point at the benchmark's sizes: E directed edges, P = E/2
     unordered pairs, N beads, F filters, R radial functions.  Index arrays at their stored width (int32 rows, int64 pointers)."""
-    if name == "filter_forward":        # d in, one filter row per pair out; two GEMMs per row
-        return P * (4 * F + 4), 2 * P * F * (R + F)
-    if name == "filter_backward":       # d, two index rows, gd; node rows x'[row0], g[row1] from L2; recompute + two backward GEMMs per row
-        return 16 * E + 2 * N * F * 4, 4 * P * F * (R + F)
+    if name == "filter_forward":        # d in, one filter row and one hidden row per pair out; 2(RF + F^2) flop per directed edge
+        return P * (8 * F + 4), 2 * E * F * (R + F)
+    if name == "filter_backward":       # d, two index rows, the saved hidden row, gd; node rows x'[row0], g[row1] from L2; 2(F^2 + RF) flop per edge
+        return 16 * E + P * 4 * F + 2 * N * F * 4, 2 * E * F * (R + F)
     if name == "seg_mul_sum":           # one filter row per pair, neighbour index and pair index per edge, node rows in and out
         return P * F * 4 + 8 * E + 2 * N * F * 4 + 8 * N, 2 * E * F
     if name.startswith("gemm_tc"):      # node-sized Linear layers, 128 wide
@@ -789,8 +789,8 @@ def run_ours(args):
         per_launch = rec["ms"] / rec["calls"]
         kernels[name] = dict(calls_per_step=rec["calls"] / args.steps, ms_per_step=rec["ms"] / args.steps, ms_per_launch=per_launch,
                              GBps=(nbytes / per_launch / 1e6 if nbytes else None), TFLOPs=(flops / per_launch / 1e9 if flops else None))
-    tensor_kernels = {"filter_forward": "filter_fwd_pipe_kernel (tcgen05: RBF prologue, 2 GEMMs, tanh, cutoff; one row per unordered pair)",
-                      "filter_backward": "filter_bwd_pipe_kernel (tcgen05: recompute + 4 GEMMs per tile, gather of gW; one row per unordered pair)"}
+    tensor_kernels = {"filter_forward": "filter_fwd_pipe_kernel (tcgen05: RBF prologue, 2 GEMMs, tanh, cutoff, hidden layer kept; one row per unordered pair)",
+                      "filter_backward": "filter_bwd_saved_kernel (tcgen05: gather of gW, 2 GEMMs per row on the forward's hidden layer; one row per unordered pair)"}
     name = next(iter(kernels))
     k = kernels[name]
     tr, tr_src = traffic_of(name)
@@ -798,10 +798,12 @@ def run_ours(args):
         roof = dict(kernel=tensor_kernels[name], bound="tensor", achieved=k["TFLOPs"], peak=tf_peak, unit="TFLOP/s", frac=k["TFLOPs"] / tf_peak,
                     traffic=tr, traffic_source=tr_src, peak_source=f"{peak_src} bf16 sustained", avg_launch_ms=k["ms_per_launch"],
                     share_of_recorded_step=k["ms_per_step"] / (ms_recorded / args.steps),
-                    note="algorithmic flops 2*F*(R+F) per evaluated row and GEMM pair (rows = E/2 on a symmetric edge list: per edge this is the "
-                         "2(F^2+RF) of a backward to the input, or half the forward's); the fp32-equivalent mode issues three fp16 products per "
-                         "algorithmic product, so tensor-pipe work is 3x this figure; duration from CUDA events recorded inside the library call "
-                         "on the timed route")
+                    executed_TFLOPs=k["TFLOPs"] / 2, tensor_pipe_TFLOPs=1.5 * k["TFLOPs"],
+                    note="algorithmic flops: 2*F*(R+F) per directed edge and pass (forward: R*F + F*F multiply-adds; backward to the input the "
+                         "same), times the E edges of the launch.  The kernels evaluate one row per unordered pair (E/2 rows: a pair's two "
+                         "edges share their filter), so the executed products are half of that (`executed_TFLOPs`); the fp32-equivalent mode "
+                         "issues three fp16 products per executed product (`tensor_pipe_TFLOPs`).  Duration from CUDA events recorded inside "
+                         "the library call on the timed route")
     else:
         roof = dict(kernel=name, bound="hbm", achieved=k["GBps"], peak=hbm_peak, unit="GB/s", frac=(k["GBps"] or 0) / hbm_peak, traffic=tr,
                     traffic_source=tr_src, peak_source=f"{peak_src} copy bandwidth", avg_launch_ms=k["ms_per_launch"],

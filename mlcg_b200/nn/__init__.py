@@ -1,7 +1,7 @@
 from .cutoff import CosineCutoff, IdentityCutoff
 from .gradients import EnergyOut, GradientsOut, SumOut
 from .mlp import MLP
-from .prior import Dihedral, FourierSeries, Harmonic, HarmonicAngles, HarmonicBonds, Repulsion, evaluate_priors, set_prior_determinism
+from .prior import Dihedral, FourierSeries, GeneralAngles, GeneralBonds, Harmonic, HarmonicAngles, HarmonicBonds, Repulsion, evaluate_priors, set_prior_determinism
 from .radial_basis import ExpNormalBasis, GaussianBasis, RegularizedBasis, SymmetricTensor
 from .attention import (AttentiveInteractionBlock, AttentiveInteractionBlock2, ExactAttention, FavorAttention, Nonlocalinteractionblock,  # noqa: F401
                         Residual, Residual_MLP, ResidualStack)

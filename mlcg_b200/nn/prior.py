@@ -268,6 +268,35 @@ class HarmonicAngles(Harmonic):
         return _angles_cos(pos, mapping, _feature_shifts(pos, mapping, pbc, cell, batch))
 
 
+class GeneralBonds(Harmonic):
+    """Harmonic bonds under a name of the caller's choosing, so that a model can hold several bond priors over different
+    index lists (harmonic.py:487-525)."""
+
+    name: Final[str] = "bonds"
+    _order = 2
+    kind = KIND_BOND
+
+    def __init__(self, statistics, name) -> None:
+        super().__init__(statistics, name, order=GeneralBonds._order)
+
+    _energy_terms = HarmonicBonds._energy_terms
+    compute_features = staticmethod(HarmonicBonds.compute_features)
+
+
+class GeneralAngles(Harmonic):
+    """Harmonic angles (in the cosine) under a name of the caller's choosing (harmonic.py:528-566)."""
+
+    name: Final[str] = "angles"
+    _order = 3
+    kind = KIND_ANGLE
+
+    def __init__(self, statistics, name) -> None:
+        super().__init__(statistics, name, order=GeneralAngles._order)
+
+    _energy_terms = HarmonicAngles._energy_terms
+    compute_features = staticmethod(HarmonicAngles.compute_features)
+
+
 class Repulsion(_Prior):
     """(sigma / d)^6 over the pair list as given (repulsion.py:14-140)."""
 

@@ -16,11 +16,12 @@ import torch
 from .data import AtomicData
 from .neighbor_list import make_neighbor_list
 from .nn.gradients import GradientsOut, SumOut
-from .nn.prior import Dihedral, HarmonicAngles, HarmonicBonds, _Prior
+from .nn.prior import Dihedral, GeneralAngles, GeneralBonds, HarmonicAngles, HarmonicBonds, _Prior
 
-#: prior classes that can be merged (the reference also lists its General* and improper variants, which this package
-#: does not define)
-to_reduce: Dict[str, Type[_Prior]] = {"Dihedral": Dihedral, "HarmonicBonds": HarmonicBonds, "HarmonicAngles": HarmonicAngles}
+#: prior classes that can be merged, in the reference's order (it also lists its improper variant, which this package does
+#: not define)
+to_reduce: Dict[str, Type[_Prior]] = {"Dihedral": Dihedral, "GeneralAngles": GeneralAngles, "GeneralBonds": GeneralBonds,
+                                      "HarmonicBonds": HarmonicBonds, "HarmonicAngles": HarmonicAngles}
 
 
 class StaticPrior(torch.nn.Module):

@@ -48,6 +48,13 @@ def golden_fullwidth():
 
 
 @pytest.fixture(scope="session")
+def golden_condensed_priors():
+    import torch
+
+    return torch.load(os.path.join(ROOT, "tests", "golden", "reference_vectors_condensed_priors.pt"), weights_only=False)
+
+
+@pytest.fixture(scope="session")
 def golden_priors_periodic():
     import torch
 

@@ -347,6 +347,89 @@ def main_priors_periodic(ref_src):
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def main_condensed(ref_src):
+    """src/mlcg/simulation/specialize_prior.py:75-206 run as it stands: two bond priors, one angle prior, two dihedral priors of
+    different expansion length and a repulsion prior over three structures of different length; the merged Static priors'
+    buffers, the rewritten neighbour lists, and the energies and forces of the merged model on the collated structures."""
+    install_shims(ref_src)
+    import itertools
+    import types
+    from mlcg.nn.gradients import GradientsOut, SumOut
+    from mlcg.data.atomic_data import AtomicData
+    sys.modules["mlcg.data"].AtomicData = AtomicData
+    harmonic = importlib.import_module("mlcg.nn.prior.harmonic")
+    repulsion = importlib.import_module("mlcg.nn.prior.repulsion")
+    fourier = importlib.import_module("mlcg.nn.prior.fourier_series")
+    base = importlib.import_module("mlcg.nn.prior.base")
+    # what the package __init__ files would have exported for `from ..nn import ...` / `from ..nn.prior import ...`
+    prior_pkg, nn_pkg = sys.modules["mlcg.nn.prior"], sys.modules["mlcg.nn"]
+    for name in ("HarmonicBonds", "HarmonicAngles", "HarmonicImpropers", "GeneralBonds", "GeneralAngles", "Harmonic"):
+        setattr(prior_pkg, name, getattr(harmonic, name))
+    prior_pkg.Dihedral, prior_pkg._Prior = fourier.Dihedral, base._Prior
+    nn_pkg.GradientsOut, nn_pkg.SumOut, nn_pkg.Dihedral = GradientsOut, SumOut, fourier.Dihedral
+    sim = types.ModuleType("mlcg.simulation")
+    sim.__path__ = [os.path.join(ref_src, "src", "mlcg", "simulation")]
+    sys.modules["mlcg.simulation"] = sim
+    sp = importlib.import_module("mlcg.simulation.specialize_prior")
+    make_neighbor_list = importlib.import_module("mlcg.neighbor_list.neighbor_list").make_neighbor_list
+
+    gen = torch.Generator().manual_seed(97531)
+    T, lengths = 3, (11, 9, 14)
+    r = lambda: float(torch.rand(1, generator=gen))
+    tab2 = lambda: {k: {"k": 50 + 100 * r(), "x_0": 3.5 + 0.6 * r()} for k in itertools.product(range(T), repeat=2)}
+    tab3 = {k: {"k": 20 + 60 * r(), "x_0": -0.8 + r()} for k in itertools.product(range(T), repeat=3)}
+    def tab4(nd):
+        return {k: {"v_0": r(), "k1s": {f"k1_{i}": r() - 0.5 for i in range(1, nd + 1)}, "k2s": {f"k2_{i}": r() - 0.5 for i in range(1, nd + 1)}}
+                for k in itertools.product(range(T), repeat=4)}
+    stats = {"bonds_even": tab2(), "bonds_odd": tab2(), "angles": tab3, "dih_short": tab4(2), "dih_long": tab4(3),
+             "repulsion": {k: {"sigma": 3.0 + 2.0 * r()} for k in itertools.product(range(T), repeat=2)}}
+    priors = {"bonds_even": harmonic.GeneralBonds(stats["bonds_even"], name="bonds_even"), "bonds_odd": harmonic.GeneralBonds(stats["bonds_odd"], name="bonds_odd"),
+              "angles": harmonic.HarmonicAngles(stats["angles"]),
+              "dih_short": fourier.Dihedral(stats["dih_short"], n_degs=2, name="dih_short"), "dih_long": fourier.Dihedral(stats["dih_long"], n_degs=3, name="dih_long"),
+              "repulsion": repulsion.Repulsion(stats["repulsion"])}
+    data_list, raw = [], []
+    for n in lengths:
+        idx = torch.arange(n)
+        bonds = torch.stack([idx[:-1], idx[1:]])
+        full = torch.cartesian_prod(idx, idx).t()
+        dih = torch.stack([idx[:-3], idx[1:-2], idx[2:-1], idx[3:]])
+        per = {"bonds_even": bonds[:, ::2], "bonds_odd": bonds[:, 1::2], "angles": torch.stack([idx[:-2], idx[1:-1], idx[2:]]),
+               "dih_short": dih[:, :4], "dih_long": dih[:, 4:], "repulsion": full[:, (full[0] - full[1]).abs() >= 3]}
+        pos, types_ = chain(n, jitter=0.3, gen=gen), torch.randint(0, T, (n,), generator=gen)
+        nls = {k: make_neighbor_list(tag=k, order=m.shape[0], index_mapping=m.clone()) for k, m in per.items()}
+        data_list.append(AtomicData(pos=pos.clone(), atom_types=types_, n_atoms=torch.tensor([n]), neighbor_list=nls))
+        raw.append(dict(pos=pos, atom_types=types_, mappings={k: m.clone() for k, m in per.items()}))
+    model = SumOut(torch.nn.ModuleDict({k: GradientsOut(p, "forces") for k, p in priors.items()}))
+    cmodel, cdata = sp.condense_all_priors_for_simulation(model, data_list)
+
+    def collated(dl):   # what torch_geometric's collate does to these fields: concatenation, index mappings shifted by the bead offsets
+        off, cat = 0, dict(pos=[], atom_types=[], batch=[], nls={})
+        for b, d in enumerate(dl):
+            n = d.pos.shape[0]
+            cat["pos"].append(d.pos); cat["atom_types"].append(d.atom_types); cat["batch"].append(torch.full((n,), b))
+            for k, v in d.neighbor_list.items():
+                e = cat["nls"].setdefault(k, dict(m=[], mb=[], order=v["order"]))
+                e["m"].append(v["index_mapping"] + off); e["mb"].append(torch.full((v["index_mapping"].shape[1],), b))
+            off += n
+        nls = {k: nl(torch.cat(e["m"], dim=1), torch.cat(e["mb"])) | {"order": e["order"], "tag": k} for k, e in cat["nls"].items()}
+        return AtomicData(pos=torch.cat(cat["pos"]), atom_types=torch.cat(cat["atom_types"]), batch=torch.cat(cat["batch"]),
+                          n_atoms=torch.tensor([d.pos.shape[0] for d in dl]), neighbor_list=nls)
+
+    res = cmodel.eval()(collated(cdata))
+    ref = model.eval()(collated(data_list))
+    print("keys", list(cmodel.models.keys()), "energy", res.out["energy"].tolist(), "separate", ref.out["energy"].tolist())
+    out = dict(T=T, lengths=lengths, stats=stats, structures=raw, model_keys=list(cmodel.models.keys()),
+               buffers={k: {bk: bv.clone() for bk, bv in m.model.state_dict().items()} for k, m in cmodel.models.items()},
+               class_names={k: type(m.model).__name__ for k, m in cmodel.models.items()},
+               condensed_mappings=[{k: v["index_mapping"].clone() for k, v in d.neighbor_list.items()} for d in cdata],
+               energy=res.out["energy"].detach(), forces=res.out["forces"].detach(),
+               energy_separate=ref.out["energy"].detach(), forces_separate=ref.out["forces"].detach(),
+               per_model_energy={k: res.out[k]["energy"].detach() for k in cmodel.models.keys()})
+    path = os.path.join(HERE, "reference_vectors_condensed_priors.pt")
+    torch.save(out, path)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 def avoiding_chain(n, gen, step=3.8, min_dist=4.0):
     """3.8 A random walk; a step is redrawn while the new bead is closer than ``min_dist`` to any bead except its predecessor
     (five beads back after 200 failures)."""
@@ -441,7 +524,7 @@ def main_fullwidth(ref_src):
 
 if __name__ == "__main__":
     extra = {"regularized": main_regularized, "periodic": main_periodic, "attentive": main_attentive, "fullwidth": main_fullwidth,
-             "priors_periodic": main_priors_periodic}
+             "priors_periodic": main_priors_periodic, "condensed": main_condensed}
     if len(sys.argv) not in (2, 3) or (len(sys.argv) == 3 and sys.argv[2] not in extra):
-        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg> [regularized|periodic|attentive|fullwidth|priors_periodic]")
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of ClementiGroup/mlcg> [regularized|periodic|attentive|fullwidth|priors_periodic|condensed]")
     (extra[sys.argv[2]] if len(sys.argv) == 3 else main)(sys.argv[1])

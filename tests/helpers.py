@@ -122,3 +122,19 @@ def periodic_prior_cases(golden_priors_periodic, box, device="cpu"):
                                     pbc=c["pbc"].clone().to(device))
         out.append((k, p.to(device), data))
     return c, out
+
+
+def condensed_prior_case(golden_condensed_priors):
+    """The model and the structures of ``reference_vectors_condensed_priors.pt`` built from this package's classes: two
+    named bond priors, angles, two dihedral priors of different length, repulsion; three structures of different length."""
+    g = golden_condensed_priors
+    st = g["stats"]
+    priors = {"bonds_even": bnn.GeneralBonds(st["bonds_even"], name="bonds_even"), "bonds_odd": bnn.GeneralBonds(st["bonds_odd"], name="bonds_odd"),
+              "angles": bnn.HarmonicAngles(st["angles"]), "dih_short": bnn.Dihedral(st["dih_short"], n_degs=2, name="dih_short"),
+              "dih_long": bnn.Dihedral(st["dih_long"], n_degs=3, name="dih_long"), "repulsion": bnn.Repulsion(st["repulsion"])}
+    data_list = []
+    for s in g["structures"]:
+        nls = {k: mlcg_b200.make_neighbor_list(k, m.shape[0], m.clone()) for k, m in s["mappings"].items()}
+        data_list.append(mlcg_b200.AtomicData(pos=s["pos"].clone(), atom_types=s["atom_types"].clone(), neighbor_list=nls))
+    model = bnn.SumOut(torch.nn.ModuleDict({k: bnn.GradientsOut(p, "forces") for k, p in priors.items()}))
+    return model, data_list

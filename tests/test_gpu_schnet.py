@@ -442,6 +442,33 @@ def test_condensed_priors_on_the_device():
     assert torch.allclose(out.out["forces"], ref.out["forces"], rtol=1e-4, atol=1e-4 * float(ref.out["forces"].abs().max()))
 
 
+def test_condensed_priors_equal_the_reference_s_on_the_device(golden_condensed_priors):
+    """The merged model of the reference's own specialize_prior.py (fixture `reference_vectors_condensed_priors.pt`) against this
+    package's merged model on the device: through the one-launch evaluation of all priors (eval mode, both summation modes)
+    and through the per-prior kernel route (train mode)."""
+    from helpers import condensed_prior_case
+    from mlcg_b200.data import collate
+    from mlcg_b200.specialize_prior import condense_all_priors_for_simulation
+    g = golden_condensed_priors
+    model, data_list = condensed_prior_case(g)
+    cmodel, cdata = condense_all_priors_for_simulation(model, data_list)
+    cmodel = cmodel.to(DEV)
+    fscale = float(g["forces"].abs().max())
+    runs = []
+    for mode in (True, False):
+        bnn.set_prior_determinism(mode)
+        try:
+            runs.append(cmodel.eval()(collate(cdata).to(DEV)))
+        finally:
+            bnn.set_prior_determinism(True)
+    runs.append(cmodel.train()(collate(cdata).to(DEV)))
+    for out in runs:
+        assert torch.allclose(out.out["energy"].detach().cpu(), g["energy"], rtol=1e-5)
+        assert float((out.out["forces"].detach().cpu() - g["forces"]).abs().max()) < 1e-4 * max(fscale, 1.0)
+        for k, e in g["per_model_energy"].items():
+            assert torch.allclose(out.out[k]["energy"].detach().cpu(), e, rtol=1e-5, atol=1e-4)
+
+
 def test_whole_model_call_matches_the_individual_kernels():
     """`mlcgb_schnet_eval` (one library call per evaluation) issues the same edge kernels as the per-kernel path; only the
     output network differs in its arithmetic (fused tanh epilogue, fp32 dot product for the last layer), so the two agree to

@@ -318,3 +318,31 @@ def test_condensed_priors_give_the_same_energies_and_forces():
     # and a second pass finds nothing left to merge
     again, _ = condense_all_priors_for_simulation(cmodel, cdata)
     assert set(again.models.keys()) == set(cmodel.models.keys())
+
+
+def test_condensed_priors_equal_the_reference_s(golden_condensed_priors):
+    """The reference's own specialize_prior.py:75-206 produced the fixture (tests/golden/make_golden.py, mode `condensed`):
+    same keys in the same order, same Static class names, identical parameter buffers and rewritten index mappings, and the
+    merged model's energies and forces on the collated structures."""
+    from helpers import condensed_prior_case
+    from mlcg_b200.data import collate
+    from mlcg_b200.specialize_prior import condense_all_priors_for_simulation
+    g = golden_condensed_priors
+    model, data_list = condensed_prior_case(g)
+    cmodel, cdata = condense_all_priors_for_simulation(model, data_list)
+    assert list(cmodel.models.keys()) == g["model_keys"]
+    for k, m in cmodel.models.items():
+        assert type(m.model).__name__ == g["class_names"][k]
+        ours = m.model.state_dict()
+        assert set(ours.keys()) == set(g["buffers"][k].keys())
+        for bk, bv in g["buffers"][k].items():
+            assert ours[bk].shape == bv.shape and torch.equal(ours[bk], bv), (k, bk)
+    for d, ref in zip(cdata, g["condensed_mappings"]):
+        assert set(d.neighbor_list.keys()) == set(ref.keys())
+        for k, m in ref.items():
+            assert torch.equal(d.neighbor_list[k]["index_mapping"], m)
+    out = cmodel.eval()(collate(cdata))
+    assert torch.allclose(out.out["energy"], g["energy"], rtol=1e-5)
+    assert torch.allclose(out.out["forces"], g["forces"], rtol=1e-4, atol=1e-4 * float(g["forces"].abs().max()))
+    for k, e in g["per_model_energy"].items():
+        assert torch.allclose(out.out[k]["energy"], e, rtol=1e-5, atol=1e-4)
