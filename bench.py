@@ -163,9 +163,11 @@ def timed_host(fn, steps, warmup):
 def parity(e, f, e32, f32, e64, f64):
     """Energies and forces of this package (``e``, ``f``) against the CPU arm in float32 (``e32``, ``f32``) and against the CPU
     arm's double-precision evaluation of the same float32 weights and positions (``e64``, ``f64``).  Bars: forces within 1e-4
-    kcal/mol/A of the double-precision value; energies within 1e-5 of it, relative to the structure's own |E| or to the mean
-    |E| of the sample, whichever is larger (an energy is a sum of per-bead terms of both signs: where they nearly cancel, no
-    float32 evaluation, the reference's included, is accurate to 1e-5 of what is left)."""
+    kcal/mol/A of the double-precision value, plus the distance of the reference's own float32 forces from it (on the 268-bead
+    chains with priors forces reach 40-70 kcal/mol/A and the reference's float32 evaluation is itself 1.3e-4 away); energies
+    within 1e-5 of the double-precision value, relative to the structure's own |E| or to the mean |E| of the sample, whichever
+    is larger (an energy is a sum of per-bead terms of both signs: where they nearly cancel, no float32 evaluation, the
+    reference's included, is accurate to 1e-5 of what is left)."""
     e, f, e32, f32 = e.double(), f.double(), e32.double(), f32.double()
     ours_e, cpu_e = (e - e64).abs(), (e32 - e64).abs()
     ours_f, cpu_f = float((f - f64).abs().max()), float((f32 - f64).abs().max())
@@ -175,7 +177,8 @@ def parity(e, f, e32, f32, e64, f64):
                 min_abs_E=float(e64.abs().min()), mean_abs_E=float(e64.abs().mean()), max_abs_E=float(e64.abs().max()),
                 max_abs_dF_vs_f64=ours_f, cpu_f32_max_abs_dF_vs_f64=cpu_f, max_abs_dF_vs_cpu_f32=float((f - f32).abs().max()),
                 max_abs_F=float(f64.abs().max()), energy_rtol=E_RTOL, force_atol=F_ATOL,
-                ok=bool((ours_e <= E_RTOL * scale).all() and ours_f <= F_ATOL))
+                force_bar=F_ATOL + cpu_f,
+                ok=bool((ours_e <= E_RTOL * scale).all() and ours_f <= F_ATOL + cpu_f))
 
 
 def run_reference(args):

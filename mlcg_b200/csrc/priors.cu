@@ -23,6 +23,70 @@ template <typename T> __device__ __forceinline__ void atomic_add3(T *g, int64_t 
     atomicAdd(g + i * 3 + 2, v.z);
 }
 
+// Bonds, angles and dihedrals are evaluated in double precision whatever the storage type: their lists are short (one term
+// per bead, where a repulsion list has hundreds), and in float32 a harmonic bond loses most of its digits in d - x0 and a
+// torsion gradient in the cross products of nearly collinear bonds.  Positions and parameters are read as stored; energy and
+// gradient are rounded to the storage type once, at the end.
+template <typename T> __device__ __forceinline__ V3<double> ld3d(const T *p, int64_t i) {
+    return V3<double>{(double)p[i * 3], (double)p[i * 3 + 1], (double)p[i * 3 + 2]};
+}
+template <typename T> __device__ __forceinline__ V3<T> narrow(const V3<double> &a) { return V3<T>{(T)a.x, (T)a.y, (T)a.z}; }
+
+// harmonic bond k (d - x0)^2: energy; g1 = dE/dpos[i1] (dE/dpos[i0] = -g1)
+template <typename T>
+__device__ __forceinline__ double bond_term(const T *pos, int64_t i0, int64_t i1, double x0, double k, V3<double> &g1) {
+    const V3<double> dr = sub(ld3d(pos, i1), ld3d(pos, i0));
+    const double d = sqrt(dot(dr, dr));
+    g1 = scale(dr, 2.0 * k * (d - x0) / d);
+    return k * (d - x0) * (d - x0);
+}
+
+// harmonic angle in the cosine, k (cos - x0)^2: ga = dE/dpos[i0], gb = dE/dpos[i2] (dE/dpos[i1] = -ga - gb)
+template <typename T>
+__device__ __forceinline__ double angle_term(const T *pos, int64_t i0, int64_t i1, int64_t i2, double x0, double k, V3<double> &ga, V3<double> &gb) {
+    const V3<double> p1 = ld3d(pos, i1);
+    const V3<double> a = sub(ld3d(pos, i0), p1), b = sub(ld3d(pos, i2), p1);
+    const double na = sqrt(dot(a, a)), nb = sqrt(dot(b, b));
+    const double c = dot(a, b) / na / nb;
+    const double dEdc = 2.0 * k * (c - x0);
+    const double inv = 1.0 / (na * nb);
+    ga = scale(axpy(-c / (na * na), a, scale(b, inv)), dEdc);
+    gb = scale(axpy(-c / (nb * nb), b, scale(a, inv)), dEdc);
+    return k * (c - x0) * (c - x0);
+}
+
+// Fourier series in the torsion angle, built as compute_torsions builds it (unit bond vectors, atan2(-m.n2, n1.n2)):
+// params rows v0, k1_1..k1_n, k2_1..k2_n with stride M; g[0..3] = dE/dpos of the four beads
+template <typename T>
+__device__ __forceinline__ double torsion_term(const T *pos, int64_t i0, int64_t i1, int64_t i2, int64_t i3, const T *params, int64_t M,
+                                               int64_t t, int n_degs, V3<double> (&g)[4]) {
+    const V3<double> p0 = ld3d(pos, i0), p1 = ld3d(pos, i1), p2 = ld3d(pos, i2), p3 = ld3d(pos, i3);
+    const V3<double> b1 = sub(p1, p0), b2 = sub(p2, p1), b3 = sub(p3, p2);
+    const V3<double> u1 = scale(b1, 1.0 / sqrt(dot(b1, b1)));
+    const V3<double> u2 = scale(b2, 1.0 / sqrt(dot(b2, b2)));
+    const V3<double> u3 = scale(b3, 1.0 / sqrt(dot(b3, b3)));
+    const V3<double> n1 = cross(u1, u2), n2 = cross(u2, u3), m1 = cross(n1, u2);
+    const double theta = atan2(-dot(m1, n2), dot(n1, n2));
+    double e = (double)params[t], dEdth = 0.0;
+    for (int n = 1; n <= n_degs; n++) {
+        double sn, cs;
+        sincos((double)n * theta, &sn, &cs);
+        const double k1 = (double)params[(int64_t)n * M + t], k2 = (double)params[(int64_t)(n_degs + n) * M + t];
+        e += k1 * sn + k2 * cs;
+        dEdth += (double)n * (k1 * cs - k2 * sn);
+    }
+    // d(theta)/d(positions): F = p0-p1, G = p1-p2, H = p3-p2, A = F x G, B = H x G
+    const V3<double> F = sub(p0, p1), G = sub(p1, p2), H = sub(p3, p2);
+    const V3<double> A = cross(F, G), Bv = cross(H, G);
+    const double A2 = dot(A, A), B2 = dot(Bv, Bv), Gn = sqrt(dot(G, G));
+    const double fg = dot(F, G) / (A2 * Gn), hg = dot(H, G) / (B2 * Gn);
+    g[0] = scale(scale(A, -Gn / A2), dEdth);
+    g[3] = scale(scale(Bv, Gn / B2), dEdth);
+    g[1] = scale(axpy(-hg, Bv, scale(A, Gn / A2 + fg)), dEdth);
+    g[2] = scale(axpy(hg, Bv, axpy(-fg, A, scale(Bv, -Gn / B2))), dEdth);
+    return e;
+}
+
 // Adds v into g[i] with one atomic per run of consecutive lanes that share the same index i (pair lists are
 // usually grouped by their first index, so a warp holds one or two runs).  Every lane of the warp must call this;
 // lanes without a contribution pass i = -1.
@@ -69,74 +133,38 @@ prior_kernel(const T *__restrict__ pos, const int64_t *__restrict__ mapping, con
         T e = T(0);
         V3<T> g0{T(0), T(0), T(0)};   // pair terms: gradient on the first index, reduced over runs below
         if (valid) {
-            if (KIND == 0 || KIND == 3) {
+            if (KIND == 0) {
+                V3<double> g1;
+                e = (T)bond_term(pos, idx[0], idx[1], (double)params[t], (double)params[M + t], g1);
+                if (grad) {
+                    atomic_add3(grad, idx[1], narrow<T>(g1));
+                    g0 = narrow<T>(scale(g1, -1.0));
+                }
+            } else if (KIND == 3) {
                 const V3<T> dr = sub(ld3(pos, idx[1]), ld3(pos, idx[0]));
                 const T d = sqrt(dot(dr, dr));
-                T dEdd;
-                if (KIND == 0) {
-                    const T x0 = params[t], k = params[M + t];
-                    e = k * (d - x0) * (d - x0);
-                    dEdd = T(2) * k * (d - x0);
-                } else {
-                    const T q = params[t] / d;
-                    const T rr = q * q;
-                    e = rr * rr * rr;
-                    dEdd = T(-6) * e / d;
-                }
+                const T q = params[t] / d;
+                const T rr = q * q;
+                e = rr * rr * rr;
                 if (grad) {
-                    const V3<T> g1 = scale(dr, dEdd / d);
+                    const V3<T> g1 = scale(dr, T(-6) * e / d / d);
                     atomic_add3(grad, idx[1], g1);
                     g0 = scale(g1, T(-1));
                 }
             } else if (KIND == 1) {
-                const V3<T> p1 = ld3(pos, idx[1]);
-                const V3<T> a = sub(ld3(pos, idx[0]), p1), b = sub(ld3(pos, idx[2]), p1);
-                const T na = sqrt(dot(a, a)), nb = sqrt(dot(b, b));
-                const T c = dot(a, b) / na / nb;
-                const T x0 = params[t], k = params[M + t];
-                e = k * (c - x0) * (c - x0);
+                V3<double> ga, gb;
+                e = (T)angle_term(pos, idx[0], idx[1], idx[2], (double)params[t], (double)params[M + t], ga, gb);
                 if (grad) {
-                    const T dEdc = T(2) * k * (c - x0);
-                    const T inv = T(1) / (na * nb);
-                    const V3<T> ga = scale(axpy(-c / (na * na), a, scale(b, inv)), dEdc);
-                    const V3<T> gb = scale(axpy(-c / (nb * nb), b, scale(a, inv)), dEdc);
-                    atomic_add3(grad, idx[0], ga);
-                    atomic_add3(grad, idx[2], gb);
-                    atomic_add3(grad, idx[1], V3<T>{-ga.x - gb.x, -ga.y - gb.y, -ga.z - gb.z});
+                    atomic_add3(grad, idx[0], narrow<T>(ga));
+                    atomic_add3(grad, idx[2], narrow<T>(gb));
+                    atomic_add3(grad, idx[1], narrow<T>(V3<double>{-ga.x - gb.x, -ga.y - gb.y, -ga.z - gb.z}));
                 }
             } else {
-                const V3<T> p0 = ld3(pos, idx[0]), p1 = ld3(pos, idx[1]), p2 = ld3(pos, idx[2]), p3 = ld3(pos, idx[3]);
-                // angle exactly as compute_torsions builds it (unit bond vectors, atan2(-m.n2, n1.n2))
-                V3<T> b1 = sub(p1, p0), b2 = sub(p2, p1), b3 = sub(p3, p2);
-                const V3<T> u1 = scale(b1, T(1) / sqrt(dot(b1, b1)));
-                const V3<T> u2 = scale(b2, T(1) / sqrt(dot(b2, b2)));
-                const V3<T> u3 = scale(b3, T(1) / sqrt(dot(b3, b3)));
-                const V3<T> n1 = cross(u1, u2), n2 = cross(u2, u3), m1 = cross(n1, u2);
-                const T theta = atan2(-dot(m1, n2), dot(n1, n2));
-                const int n_degs = (n_params - 1) / 2;
-                e = params[t];
-                T dEdth = T(0);
-                for (int n = 1; n <= n_degs; n++) {
-                    T sn, cs;
-                    sincos(T(n) * theta, &sn, &cs);
-                    const T k1 = params[(int64_t)n * M + t], k2 = params[(int64_t)(n_degs + n) * M + t];
-                    e += k1 * sn + k2 * cs;
-                    dEdth += T(n) * (k1 * cs - k2 * sn);
-                }
+                V3<double> g[4];
+                e = (T)torsion_term(pos, idx[0], idx[1], idx[2], idx[3], params, M, t, (n_params - 1) / 2, g);
                 if (grad) {
-                    // d(theta)/d(positions): F = p0-p1, G = p1-p2, H = p3-p2, A = F x G, B = H x G
-                    const V3<T> F = sub(p0, p1), G = sub(p1, p2), H = sub(p3, p2);
-                    const V3<T> A = cross(F, G), Bv = cross(H, G);
-                    const T A2 = dot(A, A), B2 = dot(Bv, Bv), Gn = sqrt(dot(G, G));
-                    const T fg = dot(F, G) / (A2 * Gn), hg = dot(H, G) / (B2 * Gn);
-                    const V3<T> d0 = scale(A, -Gn / A2);
-                    const V3<T> d3 = scale(Bv, Gn / B2);
-                    const V3<T> d1 = axpy(-hg, Bv, scale(A, Gn / A2 + fg));
-                    const V3<T> d2 = axpy(hg, Bv, axpy(-fg, A, scale(Bv, -Gn / B2)));
-                    atomic_add3(grad, idx[0], scale(d0, dEdth));
-                    atomic_add3(grad, idx[1], scale(d1, dEdth));
-                    atomic_add3(grad, idx[2], scale(d2, dEdth));
-                    atomic_add3(grad, idx[3], scale(d3, dEdth));
+#pragma unroll
+                    for (int o = 0; o < 4; o++) atomic_add3(grad, idx[o], narrow<T>(g[o]));
                 }
             }
         }
@@ -211,7 +239,7 @@ __device__ __forceinline__ void run_accumulate(const A &acc, int64_t block0, int
 }
 
 template <typename T, bool FIXED>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)      // four blocks per SM (64 registers): the long pair lists are bound by memory latency
 prior_eval_kernel(PriorSegments seg, const T *__restrict__ pos, const int32_t *__restrict__ struct_of, int64_t N, int64_t B,
                   typename std::conditional<FIXED, unsigned long long, T>::type *__restrict__ energy,
                   typename std::conditional<FIXED, unsigned long long, T>::type *__restrict__ grad, int32_t *__restrict__ status) {
@@ -326,20 +354,19 @@ prior_eval_kernel(PriorSegments seg, const T *__restrict__ pos, const int32_t *_
         V3<T> g0{T(0), T(0), T(0)};
         if (valid) {
             if (kind == 0 || kind == 3) {
-                const V3<T> dr = sub(ld3(pos, i1), ld3(pos, i0));
-                const T d = sqrt(dot(dr, dr));
-                T dEdd;
+                V3<T> g1;
                 if (kind == 0) {
-                    const T x0 = params[t], k = params[M + t];
-                    e = k * (d - x0) * (d - x0);
-                    dEdd = T(2) * k * (d - x0);
+                    V3<double> g1d;
+                    e = (T)bond_term(pos, i0, i1, (double)params[t], (double)params[M + t], g1d);
+                    g1 = narrow<T>(g1d);
                 } else {
+                    const V3<T> dr = sub(ld3(pos, i1), ld3(pos, i0));
+                    const T d = sqrt(dot(dr, dr));
                     const T q = params[t] / d;
                     const T rr = q * q;
                     e = rr * rr * rr;
-                    dEdd = T(-6) * e / d;
+                    g1 = scale(dr, T(-6) * e / d / d);
                 }
-                const V3<T> g1 = scale(dr, dEdd / d);
                 if (seg.symmetric[s]) {
                     g0 = scale(g1, T(-2));                       // the reverse term of the list adds the same again
                 } else {
@@ -347,49 +374,18 @@ prior_eval_kernel(PriorSegments seg, const T *__restrict__ pos, const int32_t *_
                     g0 = scale(g1, T(-1));
                 }
             } else if (kind == 1) {
-                const V3<T> p1 = ld3(pos, i1);
-                const V3<T> a = sub(ld3(pos, i0), p1), b = sub(ld3(pos, i2), p1);
-                const T na = sqrt(dot(a, a)), nb = sqrt(dot(b, b));
-                const T c = dot(a, b) / na / nb;
-                const T x0 = params[t], k = params[M + t];
-                e = k * (c - x0) * (c - x0);
-                const T dEdc = T(2) * k * (c - x0);
-                const T inv = T(1) / (na * nb);
-                const V3<T> ga = scale(axpy(-c / (na * na), a, scale(b, inv)), dEdc);
-                const V3<T> gb = scale(axpy(-c / (nb * nb), b, scale(a, inv)), dEdc);
-                acc.grad3(g_block + i0, ga);
-                acc.grad3(g_block + i2, gb);
-                acc.grad3(g_block + i1, V3<T>{-ga.x - gb.x, -ga.y - gb.y, -ga.z - gb.z});
+                V3<double> ga, gb;
+                e = (T)angle_term(pos, i0, i1, i2, (double)params[t], (double)params[M + t], ga, gb);
+                acc.grad3(g_block + i0, narrow<T>(ga));
+                acc.grad3(g_block + i2, narrow<T>(gb));
+                acc.grad3(g_block + i1, narrow<T>(V3<double>{-ga.x - gb.x, -ga.y - gb.y, -ga.z - gb.z}));
             } else {
-                const V3<T> p0 = ld3(pos, i0), p1 = ld3(pos, i1), p2 = ld3(pos, i2), p3 = ld3(pos, i3);
-                V3<T> b1 = sub(p1, p0), b2 = sub(p2, p1), b3 = sub(p3, p2);
-                const V3<T> u1 = scale(b1, T(1) / sqrt(dot(b1, b1)));
-                const V3<T> u2 = scale(b2, T(1) / sqrt(dot(b2, b2)));
-                const V3<T> u3 = scale(b3, T(1) / sqrt(dot(b3, b3)));
-                const V3<T> n1 = cross(u1, u2), n2 = cross(u2, u3), m1 = cross(n1, u2);
-                const T theta = atan2(-dot(m1, n2), dot(n1, n2));
-                const int n_degs = (seg.n_params[s] - 1) / 2;
-                e = params[t];
-                T dEdth = T(0);
-                for (int n = 1; n <= n_degs; n++) {
-                    T sn, cs;
-                    sincos(T(n) * theta, &sn, &cs);
-                    const T k1 = params[(int64_t)n * M + t], k2 = params[(int64_t)(n_degs + n) * M + t];
-                    e += k1 * sn + k2 * cs;
-                    dEdth += T(n) * (k1 * cs - k2 * sn);
-                }
-                const V3<T> F = sub(p0, p1), G = sub(p1, p2), H = sub(p3, p2);
-                const V3<T> A = cross(F, G), Bv = cross(H, G);
-                const T A2 = dot(A, A), B2 = dot(Bv, Bv), Gn = sqrt(dot(G, G));
-                const T fg = dot(F, G) / (A2 * Gn), hg = dot(H, G) / (B2 * Gn);
-                const V3<T> d0 = scale(A, -Gn / A2);
-                const V3<T> d3 = scale(Bv, Gn / B2);
-                const V3<T> d1 = axpy(-hg, Bv, scale(A, Gn / A2 + fg));
-                const V3<T> d2 = axpy(hg, Bv, axpy(-fg, A, scale(Bv, -Gn / B2)));
-                acc.grad3(g_block + i0, scale(d0, dEdth));
-                acc.grad3(g_block + i1, scale(d1, dEdth));
-                acc.grad3(g_block + i2, scale(d2, dEdth));
-                acc.grad3(g_block + i3, scale(d3, dEdth));
+                V3<double> g[4];
+                e = (T)torsion_term(pos, i0, i1, i2, i3, params, M, t, (seg.n_params[s] - 1) / 2, g);
+                acc.grad3(g_block + i0, narrow<T>(g[0]));
+                acc.grad3(g_block + i1, narrow<T>(g[1]));
+                acc.grad3(g_block + i2, narrow<T>(g[2]));
+                acc.grad3(g_block + i3, narrow<T>(g[3]));
             }
         }
         if (kind == 0 || kind == 3) run_accumulate<T>(acc, g_block, valid ? i0 : -1, g0, lane);
