@@ -183,6 +183,16 @@ int mlcgb_rbf_expand(const void *d /* [E] */, int dtype, int64_t E, const mlcgb_
 /* s[e] = sum_k G[e,k] * d^order/dd^order( basis_k * envelope )(d_e) */
 int mlcgb_rbf_contract(const void *d, const void *G /* [E,R] */, int dtype, int64_t E, const mlcgb_rbf_spec *spec,
                        int order, void *s /* [E] */, void *stream);
+/* Gradients with respect to the basis parameters, which the reference trains by default (ExpNormalBasis(trainable=True),
+ * src/mlcg/nn/radial_basis/exp_normal.py:52,80-94; GaussianBasis(trainable=True), gaussian.py:64-75):
+ *   gp0[k] = sum_e c[e] G[e,k] d/dp0_k [ d^order/dd^order( basis_k * envelope )(d_e) ]      (offsets | means)
+ *   gp1[k] = the same for p1                                                                (betas; Gaussian: gp1[0], the shared coeff)
+ * c may be NULL (all ones).  order 0..3, num_rbf <= 256.  Sums are formed block by block and added in a fixed order (no atomics).
+ * workspace: mlcgb_rbf_param_workspace_bytes(E, num_rbf, dtype) bytes. */
+size_t mlcgb_rbf_param_workspace_bytes(int64_t E, int num_rbf, int dtype);
+int mlcgb_rbf_param_contract(const void *d /* [E] */, const void *G /* [E,R] */, const void *c /* [E] or NULL */, int dtype, int64_t E,
+                             const mlcgb_rbf_spec *spec, int order, void *workspace, size_t workspace_bytes, void *gp0 /* [R] */,
+                             void *gp1 /* [R] | [1] */, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Continuous-filter convolution primitives.  CFConv.forward / .message, src/mlcg/nn/schnet.py:312-368:

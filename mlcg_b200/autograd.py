@@ -218,40 +218,59 @@ class EdgeDistanceOnce(torch.autograd.Function):
 MAX_RBF_ORDER = 3
 
 
+def _rbf_param_grads(ctx, d, G, c):
+    """Gradients for the basis parameters handed to RbfExpand / RbfContract as tensors (``None`` where not asked for).  They are
+    results of a reduction kernel, not differentiable further: parameter gradients are what the optimiser consumes."""
+    want0, want1 = ctx.needs_input_grad[ctx.param_slot], ctx.needs_input_grad[ctx.param_slot + 1]
+    if not (want0 or want1):
+        return None, None
+    with torch.no_grad():
+        gp0, gp1 = get_backend().rbf_param_contract(d.detach(), G.detach(), None if c is None else c.detach(), ctx.spec, ctx.order)
+    return (gp0.reshape(ctx.p_shapes[0]) if want0 else None), (gp1.reshape(ctx.p_shapes[1]) if want1 else None)
+
+
 class RbfExpand(torch.autograd.Function):
-    """``order``-th distance derivative of basis x envelope, ``[E, R]``."""
+    """``order``-th distance derivative of basis x envelope, ``[E, R]``.  ``p0`` / ``p1``: the basis' two parameter tensors when
+    they are trained (they are the tensors ``spec`` points at; passing them makes autograd ask for their gradients)."""
 
     @staticmethod
-    def forward(ctx, d, spec: RbfSpec, order: int):
+    def forward(ctx, d, spec: RbfSpec, order: int, p0=None, p1=None):
         if order > MAX_RBF_ORDER:
             raise NotImplementedError("radial-basis derivatives beyond third order are not implemented")
-        ctx.spec, ctx.order = spec, order
-        ctx.save_for_backward(d)
+        ctx.spec, ctx.order, ctx.param_slot = spec, order, 3
+        ctx.p_shapes = (None if p0 is None else p0.shape, None if p1 is None else p1.shape)
+        ctx.trained = p0 is not None or p1 is not None
+        ctx.save_for_backward(d, p0, p1)
         return get_backend().rbf_expand(d, spec, order)
 
     @staticmethod
     def backward(ctx, G):
-        (d,) = ctx.saved_tensors
-        return RbfContract.apply(d, G, ctx.spec, ctx.order + 1), None, None
+        d, p0, p1 = ctx.saved_tensors
+        gd = RbfContract.apply(d, G, ctx.spec, ctx.order + 1, p0, p1) if ctx.needs_input_grad[0] else None
+        gp0, gp1 = _rbf_param_grads(ctx, d, G, None) if ctx.trained else (None, None)
+        return gd, None, None, gp0, gp1
 
 
 class RbfContract(torch.autograd.Function):
     """s[e] = sum_k G[e,k] * d^order(basis_k x envelope)/dd^order."""
 
     @staticmethod
-    def forward(ctx, d, G, spec: RbfSpec, order: int):
+    def forward(ctx, d, G, spec: RbfSpec, order: int, p0=None, p1=None):
         if order > MAX_RBF_ORDER:
             raise NotImplementedError("radial-basis derivatives beyond third order are not implemented")
-        ctx.spec, ctx.order = spec, order
-        ctx.save_for_backward(d, G)
+        ctx.spec, ctx.order, ctx.param_slot = spec, order, 4
+        ctx.p_shapes = (None if p0 is None else p0.shape, None if p1 is None else p1.shape)
+        ctx.trained = p0 is not None or p1 is not None
+        ctx.save_for_backward(d, G, p0, p1)
         return get_backend().rbf_contract(d, G, spec, order)
 
     @staticmethod
     def backward(ctx, gs):
-        d, G = ctx.saved_tensors
-        gd = gs * RbfContract.apply(d, G, ctx.spec, ctx.order + 1) if ctx.needs_input_grad[0] else None
-        gG = RowScale.apply(RbfExpand.apply(d, ctx.spec, ctx.order), gs) if ctx.needs_input_grad[1] else None
-        return gd, gG, None, None
+        d, G, p0, p1 = ctx.saved_tensors
+        gd = gs * RbfContract.apply(d, G, ctx.spec, ctx.order + 1, p0, p1) if ctx.needs_input_grad[0] else None
+        gG = RowScale.apply(RbfExpand.apply(d, ctx.spec, ctx.order, p0, p1), gs) if ctx.needs_input_grad[1] else None
+        gp0, gp1 = _rbf_param_grads(ctx, d, G, gs) if ctx.trained else (None, None)
+        return gd, gG, None, None, gp0, gp1
 
 
 # ------------------------------------------------------------------------------- per-edge scalar x edge row

@@ -440,6 +440,23 @@ class CudaBackend:
             self._run("rbf_contract", self.lib.mlcgb_rbf_contract, (_ptr(d), _ptr(G), _dt(d), d.numel(), ctypes.byref(s), order, _ptr(out), _stream(),), **self._work("rbf_contract", locals()))
         return out
 
+    def rbf_param_contract(self, d, G, c, spec: RbfSpec, order: int):
+        """``(gp0 [R], gp1 [R] or [1])``: gradients with respect to the two parameter vectors of the basis of
+        ``sum_e c[e] sum_k G[e,k] phi_k^(order)(d_e)`` (``c`` may be ``None``)."""
+        _need_cuda(d, G, c, spec.p0, spec.p1)
+        d, G = d.contiguous(), G.contiguous()
+        c = None if c is None else c.contiguous()
+        s, keep = self._spec(spec, d.dtype)
+        gp0 = torch.empty(spec.num_rbf, dtype=d.dtype, device=d.device)
+        gp1 = torch.empty(spec.p1.numel(), dtype=d.dtype, device=d.device)
+        nbytes = self.lib.mlcgb_rbf_param_workspace_bytes(d.numel(), spec.num_rbf, _dt(d))
+        ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=d.device)
+        with _on(d.device):
+            self._run("rbf_param_contract", self.lib.mlcgb_rbf_param_contract,
+                      (_ptr(d), _ptr(G), _ptr(c), _dt(d), d.numel(), ctypes.byref(s), order, _ptr(ws), nbytes, _ptr(gp0), _ptr(gp1), _stream(),),
+                      **self._work("rbf_param_contract", locals()))
+        return gp0, gp1
+
     # ------------------------------------------------------------------ CFConv primitives
     def seg_mul_sum(self, a, V, ptr, nbr, eperm, N):
         _need_cuda(a, V, ptr, nbr)

@@ -114,6 +114,30 @@ __device__ __forceinline__ Jet<T, O> basis_jet(const Jet<T, O> &ej, int k, const
     return jet_exp<T, O>(q);
 }
 
+// d(basis_k)/d(p0_k) and d(basis_k)/d(p1) as jets in the distance, given the per-edge jet.  basis = exp(q), q = s v^2,
+// v = w(d) - p0_k, s = p1 (Gaussian: the shared coefficient) or -p1_k (exp-normal):
+//   d basis / d p0 = basis * (-2 s v)        d basis / d p1 = basis * (+v^2 | -v^2)
+template <typename T, int O>
+__device__ __forceinline__ void basis_param_jets(const Jet<T, O> &ej, int k, const RbfDev<T> &s, Jet<T, O> &dp0, Jet<T, O> &dp1) {
+    Jet<T, O> v = ej;
+    v.c[0] -= s.p0[k];
+    const Jet<T, O> v2 = jet_mul<T, O>(v, v);
+    const T scale = s.kind == 0 ? s.p1[0] : -s.p1[k];
+    Jet<T, O> q = v2;
+#pragma unroll
+    for (int m = 0; m <= O; m++) q.c[m] *= scale;
+    const Jet<T, O> b = jet_exp<T, O>(q);
+    Jet<T, O> f0 = v, f1 = v2;
+    const T sign1 = s.kind == 0 ? T(1) : T(-1);
+#pragma unroll
+    for (int m = 0; m <= O; m++) {
+        f0.c[m] *= T(-2) * scale;
+        f1.c[m] *= sign1;
+    }
+    dp0 = jet_mul<T, O>(b, f0);
+    dp1 = jet_mul<T, O>(b, f1);
+}
+
 template <int O> struct Fact;
 template <> struct Fact<0> { static constexpr double v = 1.0; };
 template <> struct Fact<1> { static constexpr double v = 1.0; };
@@ -129,6 +153,21 @@ __device__ __forceinline__ T phi_deriv(const Jet<T, O> &ej, const Jet<T, O> &env
     return acc * T(Fact<O>::v);
 }
 
+
+// order-O distance derivative of d(basis_k x envelope)/d(parameter), for both parameters
+template <typename T, int O>
+__device__ __forceinline__ void phi_param_deriv(const Jet<T, O> &ej, const Jet<T, O> &env, int k, const RbfDev<T> &s, T &g0, T &g1) {
+    Jet<T, O> dp0, dp1;
+    basis_param_jets<T, O>(ej, k, s, dp0, dp1);
+    T a0 = T(0), a1 = T(0);
+#pragma unroll
+    for (int j = 0; j <= O; j++) {
+        a0 += dp0.c[j] * env.c[O - j];
+        a1 += dp1.c[j] * env.c[O - j];
+    }
+    g0 = a0 * T(Fact<O>::v);
+    g1 = a1 * T(Fact<O>::v);
+}
 
 template <typename T>
 static inline RbfDev<T> to_dev(const mlcgb_rbf_spec *sp) {

@@ -27,10 +27,16 @@ class _RadialBasis(nn.Module):
         raise TypeError("Supplied cutoff {} is neither a number nor a _Cutoff instance.".format(cutoff))
 
     def _kernel_ok(self, dist: torch.Tensor) -> bool:
-        """The fused kernel treats the basis parameters as constants and knows two envelopes."""
-        # (in eval mode only position gradients are taken, as in GradientsOut with create_graph=False)
-        frozen = not self.training or not torch.is_grad_enabled() or not any(p.requires_grad for p in self.parameters())
-        return frozen and cutoff_kind(self.cutoff) is not None and dist.dim() == 1
+        """The kernels know two envelopes and take distances as a vector."""
+        return cutoff_kind(self.cutoff) is not None and dist.dim() == 1 and self.num_rbf <= 256
+
+    def _trained(self, p0: torch.Tensor, p1: torch.Tensor):
+        """The parameter tensors to hand to the kernels' autograd node: those that are being trained (training mode, gradients
+        on); their gradients then come from ``mlcgb_rbf_param_contract``.  In eval mode only position gradients are taken, as
+        in GradientsOut with create_graph=False."""
+        if not self.training or not torch.is_grad_enabled():
+            return None, None
+        return (p0 if p0.requires_grad else None), (p1 if p1.requires_grad else None)
 
 
 class GaussianBasis(_RadialBasis):
@@ -64,7 +70,7 @@ class GaussianBasis(_RadialBasis):
 
     def forward(self, dist: torch.Tensor) -> torch.Tensor:
         if self._kernel_ok(dist):
-            return RbfExpand.apply(dist, self.spec(), 0)
+            return RbfExpand.apply(dist, self.spec(), 0, *self._trained(self.offset, self.coeff))
         dist = dist.unsqueeze(-1)
         return torch.exp(self.coeff * torch.pow(dist - self.offset, 2)) * self.cutoff(dist)
 
@@ -103,7 +109,7 @@ class ExpNormalBasis(_RadialBasis):
 
     def forward(self, dist: torch.Tensor) -> torch.Tensor:
         if self._kernel_ok(dist):
-            return RbfExpand.apply(dist, self.spec(), 0)
+            return RbfExpand.apply(dist, self.spec(), 0, *self._trained(self.means, self.betas))
         dist = dist.unsqueeze(-1)
         inner = torch.exp(self.alpha * (-dist + self.cutoff.cutoff_lower)) - self.means
         return self.cutoff(dist) * torch.exp(-self.betas * inner ** 2)

@@ -104,11 +104,12 @@ class OracleBackend:
 
     # ------------------------------------------------------------------ radial basis
     @staticmethod
-    def _phi(d, spec):
+    def _phi(d, spec, keep_graph=False):
         cut = {"cutoff": "cosine" if spec.cutoff_kind == 1 else "identity", "lower": spec.lower, "upper": spec.upper}
         s = {"kind": "gaussian" if spec.kind == 0 else "expnormal", "rbf_cutoff": cut}
-        sd = {"rbf_layer.offset": spec.p0.detach().to(d.dtype), "rbf_layer.coeff": spec.p1.detach().to(d.dtype).reshape(-1)[0],
-              "rbf_layer.means": spec.p0.detach().to(d.dtype), "rbf_layer.betas": spec.p1.detach().to(d.dtype).reshape(-1)}
+        p0, p1 = (spec.p0, spec.p1) if keep_graph else (spec.p0.detach(), spec.p1.detach())
+        sd = {"rbf_layer.offset": p0.to(d.dtype), "rbf_layer.coeff": p1.to(d.dtype).reshape(-1)[0],
+              "rbf_layer.means": p0.to(d.dtype), "rbf_layer.betas": p1.to(d.dtype).reshape(-1)}
         return schnet_ref.radial_basis(d, s, sd)
 
     def rbf_expand(self, d, spec, order):
@@ -123,6 +124,21 @@ class OracleBackend:
 
     def rbf_contract(self, d, G, spec, order):
         return (G.detach() * self.rbf_expand(d, spec, order)).sum(dim=1)
+
+    def rbf_param_contract(self, d, G, c, spec, order):
+        """Gradients of sum_e c[e] sum_k G[e,k] phi_k^(order)(d_e) with respect to the basis' two parameter tensors, by
+        automatic differentiation of the oracle expression."""
+        import dataclasses
+        sp = dataclasses.replace(spec, p0=spec.p0.detach().clone().requires_grad_(True), p1=spec.p1.detach().clone().requires_grad_(True))
+        dd = d.detach().clone().requires_grad_(True)
+        with torch.enable_grad():
+            cur = self._phi(dd, sp, keep_graph=True)
+            for _ in range(order):
+                cols = [torch.autograd.grad(cur[:, k].sum(), dd, create_graph=True)[0] for k in range(cur.shape[1])]
+                cur = torch.stack(cols, dim=1)
+            w = G.detach() if c is None else G.detach() * c.detach().unsqueeze(-1)
+            gp0, gp1 = torch.autograd.grad((w * cur).sum(), [sp.p0, sp.p1])
+        return gp0.reshape(-1), gp1.reshape(-1)
 
     # ------------------------------------------------------------------ CFConv primitives
     def seg_mul_sum(self, a, V, ptr, nbr, eperm, N):

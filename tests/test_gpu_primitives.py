@@ -96,6 +96,32 @@ def test_rbf_derivatives_float64(kind, cutoff_kind, lower, order):
 
 
 @pytest.mark.parametrize("kind", [0, 1])
+@pytest.mark.parametrize("order", [0, 1, 2])
+@pytest.mark.parametrize("with_c", [False, True])
+def test_rbf_parameter_gradients_float64(kind, order, with_c):
+    """mlcgb_rbf_param_contract vs automatic differentiation of the oracle expression with respect to offsets / coefficient
+    (Gaussian, gaussian.py:64-75) and means / betas (exp-normal, exp_normal.py:80-94), for the distance-derivative orders a
+    force-matching step needs; 5000 edges so that several blocks' partial sums are reduced."""
+    from oracle import schnet_ref
+    lower, upper, R, E = 0.0, 9.0, 20, 5000
+    p0, p1 = (schnet_ref.gaussian_params(lower, upper, R, torch.float64) if kind == 0 else schnet_ref.expnormal_params(lower, upper, R, torch.float64))
+    gen = torch.Generator().manual_seed(3 + order)
+    p0 = p0 + 0.01 * torch.randn(R, dtype=torch.float64, generator=gen)          # (off the symmetric initial values)
+    spec = RbfSpec(kind, R, 1, lower, upper, 5.0 / (upper - lower), p0, p1.reshape(-1))
+    d = 0.3 + 9.5 * torch.rand(E, dtype=torch.float64, generator=gen)
+    G = torch.randn(E, R, dtype=torch.float64, generator=gen)
+    c = torch.randn(E, dtype=torch.float64, generator=gen) if with_c else None
+    want0, want1 = ORA.rbf_param_contract(d, G, c, spec, order)
+    spec_gpu = RbfSpec(kind, R, 1, lower, upper, 5.0 / (upper - lower), p0.to(DEV), p1.reshape(-1).to(DEV))
+    got0, got1 = get_backend().rbf_param_contract(d.to(DEV), G.to(DEV), None if c is None else c.to(DEV), spec_gpu, order)
+    assert got1.numel() == (1 if kind == 0 else R)
+    for got, want in ((got0, want0), (got1, want1)):
+        assert torch.allclose(got.cpu(), want, rtol=1e-9, atol=1e-10 * (float(want.abs().max()) + 1e-30))
+    again0, again1 = get_backend().rbf_param_contract(d.to(DEV), G.to(DEV), None if c is None else c.to(DEV), spec_gpu, order)
+    assert torch.equal(got0, again0) and torch.equal(got1, again1)              # fixed summation order
+
+
+@pytest.mark.parametrize("kind", [0, 1])
 def test_rbf_float32_matches_reference_expression(kind):
     from oracle import schnet_ref
     upper, R = 15.0, 128

@@ -103,13 +103,24 @@ def test_fullwidth_golden_fused_routes(golden_fullwidth, name):
 @pytest.mark.parametrize("name", ["chain100", "chain10", "chain73", "chain73_trainable"])
 def test_fullwidth_golden_force_matching_step(golden_fullwidth, name):
     """Force-matching loss and its parameter gradients (second-order pass) at full width against the reference's."""
+    from mlcg_b200.backend import KernelProfiler, get_backend
     c = fullwidth_case(golden_fullwidth, name)
     net = schnet_from_case(c, device=DEV)
-    out = bnn.GradientsOut(net, "forces").train()(data_from_case(c, device=DEV))
-    _report(f"{name} training-mode forward", out.out["SchNet"]["energy"].detach().cpu(), out.out["SchNet"]["forces"].detach().cpu(), c)
-    loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], c["target_forces"].to(DEV))
-    loss.backward()
+    be = get_backend()
+    be.profiler = KernelProfiler(time_kernels=False)
+    try:
+        out = bnn.GradientsOut(net, "forces").train()(data_from_case(c, device=DEV))
+        _report(f"{name} training-mode forward", out.out["SchNet"]["energy"].detach().cpu(), out.out["SchNet"]["forces"].detach().cpu(), c)
+        loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], c["target_forces"].to(DEV))
+        loss.backward()
+        ran = set(be.profiler.stats)
+    finally:
+        be.profiler = None
     get_backend_check()
+    # the basis runs on the kernels whether or not its parameters are trained; trained ones get their gradients from the
+    # reduction kernel (the reference's default is ExpNormalBasis(trainable=True), exp_normal.py:52)
+    assert {"rbf_expand", "rbf_contract"} <= ran, ran
+    assert ("rbf_param_contract" in ran) == name.endswith("_trainable"), ran
     assert torch.allclose(loss.detach().cpu(), c["loss"], rtol=1e-5)
     grads = dict(net.named_parameters())
     worst = 0.0

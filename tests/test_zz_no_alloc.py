@@ -18,6 +18,7 @@ import torch
 
 from mlcg_b200 import _lib
 from mlcg_b200.backend import get_backend
+from oracle import radius_ref
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -65,6 +66,9 @@ def test_two_calls_in_a_row_match_the_regular_path(dtype):
         assert torch.equal(ei[:, :E], want_ei)                      # bit-exact: integer output
         assert bool((ei[:, E:] == -7).all())                        # nothing written past the edges
         assert torch.equal(off, want_off) and status == want_status
+        # and directly against the CPU oracle's list for the same inputs
+        oracle_ei = radius_ref.radius_graph_c(pos.cpu().numpy(), ptr.cpu().numpy(), r, max_nn, loop, "cluster" if rule == 1 else "native")
+        assert np.array_equal(ei[:, :E].cpu().numpy(), oracle_ei)
 
 
 def test_limits_are_refused_with_an_error_code():
