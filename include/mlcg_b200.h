@@ -247,6 +247,15 @@ int mlcgb_gemm_tc_tn_colsum(const void *A, const void *B, int64_t K, int64_t M, 
 int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias, const void *aux, int epilogue, int64_t M,
                         int64_t N, int64_t K, void *C, int32_t *status, void *stream);
 
+/* Two of those layers chained in one kernel, all widths 128 (the row tile stays on the chip between the GEMMs): the tail of an
+ * interaction block, src/mlcg/nn/schnet.py:252-262 with the residual sum at schnet.py:150, and its part of the force pass.
+ *   backward = 0:  mid = tanh(A Wa^T + ba) -> mid_out [M,128];   C = aux + mid Wb^T + bb        (Wa, Wb as torch.nn.Linear stores them)
+ *   backward = 1:  mid = (A Wa) * (1 - aux^2)  (not stored);      C = mid Wb                     (ba, bb, mid_out ignored)
+ * aux [M,128]: the block's input x (forward) or the stored tanh output (backward).  16-byte aligned A, aux, C, mid_out
+ * (MLCGB_E_LIMIT otherwise).  Same arithmetic as two calls of mlcgb_gemm_tc_fused. */
+int mlcgb_gemm_tc_chain2(int backward, const void *A, const void *Wa, const void *ba, const void *Wb, const void *bb, const void *aux,
+                         int64_t M, void *mid_out, void *C, int32_t *status, void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Fused filter network on the tensor cores (tcgen05 / TMEM):
  *   W[e,:] = ( tanh( phi(d_e) A1^T + b1 ) A2^T ) * C(d_e)

@@ -579,6 +579,27 @@ class CudaBackend:
         self.defer_status(status, "tensor-core GEMM")
         return C
 
+    def gemm_chain2(self, backward: bool, A, Wa, ba, Wb, bb, aux):
+        """Two 128-wide layers in one kernel.  Forward: ``mid = tanh(A Wa^T + ba)``, ``C = aux + mid Wb^T + bb`` -> ``(mid, C)``;
+        backward: ``C = ((A Wa) * (1 - aux**2)) Wb`` -> ``(None, C)``."""
+        _need_cuda(A, Wa, ba, Wb, bb, aux)
+        A, aux = A.contiguous(), aux.contiguous()
+        Wa, Wb = Wa.detach().contiguous(), Wb.detach().contiguous()
+        ba = None if ba is None else ba.detach().contiguous()
+        bb = None if bb is None else bb.detach().contiguous()
+        if A.dtype != torch.float32 or A.shape[1] != 128 or tuple(Wa.shape) != (128, 128) or tuple(Wb.shape) != (128, 128) or aux.shape != A.shape:
+            raise ValueError("gemm_chain2 takes float32 operands of width 128")
+        M = A.shape[0]
+        mid = None if backward else torch.empty_like(A)
+        C = torch.empty_like(A)
+        status = self._sticky_status(A.device)
+        with _on(A.device):
+            self._run("gemm_tc", self.lib.mlcgb_gemm_tc_chain2, (int(bool(backward)), _ptr(A), _ptr(Wa), _ptr(ba), _ptr(Wb), _ptr(bb), _ptr(aux), M, _ptr(mid), _ptr(C),
+                                                                   _ptr(status), _stream()),
+                      nbytes=(3 if backward else 4) * M * 128 * 4 + 2 * 128 * 128 * 4, flops=4 * M * 128 * 128)
+        self.defer_status(status, "tensor-core GEMM")
+        return mid, C
+
     # ------------------------------------------------------------------ one interaction block per call
     def interaction_ok(self, x, plan, H, F, H2) -> bool:
         """Whether the per-block entry points take this case; with a profiler attached the individual kernels are launched

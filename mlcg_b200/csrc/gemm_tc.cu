@@ -363,6 +363,189 @@ gemm_tc_rows_pipe_kernel(const float *__restrict__ A, const float *__restrict__ 
     if (warp == 0) tmem_free(tmem, 512);
 }
 
+// ------------------------------------------------------------------------------------------------ two Linear layers chained
+// The two node-sized layers that follow the aggregation of an interaction block, and their counterparts in the force pass,
+// as one kernel: the 128-row tile stays on the chip between the two GEMMs.
+//   FWD (NT, NT):  mid = tanh(A Wa^T + ba)  (stored: the force pass reads it)      C = aux + mid Wb^T + bb
+//   BWD (NN, NN):  mid = (A Wa) * (1 - aux^2)                                       C = mid Wb
+// All widths are 128.  Shared memory: both weight tiles as fp16 hi/lo pairs (2 x 64 KB) and one 64 KB stage through which
+// every tile enters and leaves in whole rows.  One accumulator and one operand block of tensor memory, used by both GEMMs of
+// a tile one after the other.
+struct ChainSmem {
+    static constexpr int kWa = 0, kWb = 65536, kStage = 131072, kMisc = 196608;
+    static constexpr int kTotal = kMisc + 4096 + 1024;
+};
+
+template <int BWD>
+__global__ void __launch_bounds__(kGT, 1)
+gemm_tc_chain2_kernel(const float *__restrict__ A, const float *__restrict__ Wa, const float *__restrict__ ba, const float *__restrict__ Wb,
+                      const float *__restrict__ bb, const float *__restrict__ aux, int64_t E, float *__restrict__ mid_out,
+                      float *__restrict__ C, int32_t *__restrict__ status) {
+    using namespace tc;
+    using L = ChainSmem;
+    constexpr int W = 128, MODE = BWD ? 1 : 0;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t *sWa_hi = smem + L::kWa, *sWa_lo = sWa_hi + 32768, *sWb_hi = smem + L::kWb, *sWb_lo = sWb_hi + 32768;
+    uint8_t *stage = smem + L::kStage;
+    float *s_red = reinterpret_cast<float *>(smem + L::kMisc);
+    float *s_ba = s_red + 512, *s_bb = s_ba + 128;
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_bb + 128);
+    uint32_t *s_tmem = reinterpret_cast<uint32_t *>(s_bar + 1);
+    int *s_err = reinterpret_cast<int *>(s_tmem + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = tid & 127, qt = tid >> 7, col0 = qt * 32;
+    constexpr float kWS = 64.f;
+    bool range = load_weight_tile<true>(sWa_hi, sWa_lo, Wa, W, W, W, kWS);
+    range = load_weight_tile<true>(sWb_hi, sWb_lo, Wb, W, W, W, kWS) || range;
+    if (range && blockIdx.x == 0) atomicOr(status, (int)kWeightRange);
+    if (tid < 128) {
+        s_ba[tid] = ba ? ba[tid] : 0.f;
+        s_bb[tid] = bb ? bb[tid] : 0.f;
+    }
+    const uint32_t bar = smem_u32(s_bar);
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        *s_err = 0;
+    }
+    __syncwarp();
+    if (warp == 0) tmem_alloc(smem_u32(s_tmem), 256);
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    pdl_wait();                                    // set-up done (weights only); A and aux belong to the kernels before
+    pdl_launch_dependents();
+    const uint32_t tmem = *s_tmem;                 // accumulator at columns [0,128), operand at [128,256)
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t ta = tmem + 128;
+    const int64_t ntiles = (E + kRows - 1) / kRows;
+    uint32_t phase = 0;
+    bool failed = false;
+    if (blockIdx.x < ntiles) prefetch_tile_to_stage(stage, A, (int64_t)blockIdx.x * kRows, E, W);
+
+    // this thread's 32 values -> operand block (row-scaled fp16 pairs); returns the row's scale.  `fetch`: a tile to copy into
+    // the stage as soon as everybody has read the current contents out of it (rows of `fetch` starting at `fetch_row0`)
+    auto to_operand = [&](const float (&x)[32], const float *fetch, int64_t fetch_row0) {
+        float rmax = 0.f;
+#pragma unroll
+        for (int c = 0; c < 32; c++) rmax = fmaxf(rmax, fabsf(x[c]));
+        s_red[qt * 128 + r] = rmax;
+        __syncthreads();
+        if (fetch) prefetch_tile_to_stage(stage, fetch, fetch_row0, E, W);
+        const float sc = row_scale(fmaxf(fmaxf(s_red[r], s_red[128 + r]), fmaxf(s_red[256 + r], s_red[384 + r])));
+        store_a_tmem<true>(ta + lane_off, col0, x, sc);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncthreads();
+        return sc;
+    };
+    auto gemm = [&](uint8_t *w_hi, uint8_t *w_lo) {
+        if (tid == 0) {
+            tc_fence_after();
+            issue_gemm_ts<true>(tmem, ta, smem_u32(w_hi), smem_u32(w_lo), W / 16, MODE, W);
+            mma_commit(bar);
+        }
+    };
+    auto await = [&]() {
+        if (!failed && !mbar_wait(bar, phase)) failed = true;
+        phase ^= 1;
+        tc_fence_after();
+    };
+    // rows of the stage -> global memory, whole rows by consecutive lanes, eight rows per warp in flight
+    auto store_stage = [&](float *dst, int64_t tile) {
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = *gstage(stage, warp * 8 + i, lane);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int64_t gr = tile * kRows + warp * 8 + i;
+            if (gr < E) __stcs(reinterpret_cast<float4 *>(dst + gr * W) + lane, v[i]);
+        }
+    };
+
+    // Everything that crosses to or from global memory goes through the stage in whole rows (a thread's own 32 columns of a
+    // row are 128 bytes: 32 separate lines per warp instruction if moved directly).  The stage holds, in turn: the input tile;
+    // BWD: the tile of tanh outputs; FWD: mid on its way out, then the residual tile; the output tile on its way out.
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        wait_prefetch();
+        __syncthreads();                            // the input tile has landed
+        float x[32];
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const float4 v = *gstage(stage, r, (col0 >> 2) + w);
+            x[4 * w] = v.x; x[4 * w + 1] = v.y; x[4 * w + 2] = v.z; x[4 * w + 3] = v.w;
+        }
+        const float sc1 = to_operand(x, BWD ? aux : nullptr, tile * kRows);      // BWD: the tanh outputs arrive under the first GEMM
+        gemm(sWa_hi, sWa_lo);
+        await();
+        if (BWD) {
+            wait_prefetch();
+            __syncthreads();
+        }
+        {
+            float v[32];
+            tmem_ld32(tmem + lane_off + col0, v);
+            const float inv = 1.f / (sc1 * kWS);
+#pragma unroll
+            for (int w = 0; w < 8; w++) {
+                float4 o = make_float4(fmaf(v[4 * w], inv, s_ba[col0 + 4 * w]), fmaf(v[4 * w + 1], inv, s_ba[col0 + 4 * w + 1]),
+                                       fmaf(v[4 * w + 2], inv, s_ba[col0 + 4 * w + 2]), fmaf(v[4 * w + 3], inv, s_ba[col0 + 4 * w + 3]));
+                float4 *slot = gstage(stage, r, (col0 >> 2) + w);
+                if (BWD) {
+                    const float4 t4 = *slot;
+                    o = make_float4(o.x * fmaf(-t4.x, t4.x, 1.f), o.y * fmaf(-t4.y, t4.y, 1.f), o.z * fmaf(-t4.z, t4.z, 1.f), o.w * fmaf(-t4.w, t4.w, 1.f));
+                } else {
+                    o = make_float4(tanh_ex2(o.x), tanh_ex2(o.y), tanh_ex2(o.z), tanh_ex2(o.w));
+                    *slot = o;                       // on its way to mid_out
+                }
+                x[4 * w] = o.x; x[4 * w + 1] = o.y; x[4 * w + 2] = o.z; x[4 * w + 3] = o.w;
+            }
+        }
+        const float sc2 = to_operand(x, nullptr, 0);     // (the accumulator has been read, the first GEMM's operand consumed)
+        gemm(sWb_hi, sWb_lo);
+        if (!BWD) {                                  // under the second GEMM: mid leaves, the residual tile arrives
+            store_stage(mid_out, tile);
+            __syncthreads();
+            prefetch_tile_to_stage(stage, aux, tile * kRows, E, W);
+        }
+        await();
+        if (!BWD) {
+            wait_prefetch();
+            __syncthreads();
+        }
+        {
+            float v[32];
+            tmem_ld32(tmem + lane_off + col0, v);
+            const float inv = 1.f / (sc2 * kWS);
+#pragma unroll
+            for (int w = 0; w < 8; w++) {
+                float4 o = make_float4(fmaf(v[4 * w], inv, s_bb[col0 + 4 * w]), fmaf(v[4 * w + 1], inv, s_bb[col0 + 4 * w + 1]),
+                                       fmaf(v[4 * w + 2], inv, s_bb[col0 + 4 * w + 2]), fmaf(v[4 * w + 3], inv, s_bb[col0 + 4 * w + 3]));
+                float4 *slot = gstage(stage, r, (col0 >> 2) + w);
+                if (!BWD) {
+                    const float4 t4 = *slot;
+                    o = make_float4(o.x + t4.x, o.y + t4.y, o.z + t4.z, o.w + t4.w);
+                }
+                *slot = o;
+            }
+        }
+        tc_fence_before();
+        __syncthreads();
+        store_stage(C, tile);
+        __syncthreads();                            // the stage is free for the next input tile
+        const int64_t next = tile + gridDim.x;
+        if (next < ntiles) prefetch_tile_to_stage(stage, A, next * kRows, E, W);
+    }
+    wait_prefetch();
+    if (failed) *s_err = 1;
+    tc_fence_before();
+    __syncthreads();
+    if (*s_err && tid == 0) atomicOr(status, 8);
+    if (warp == 0) tmem_free(tmem, 256);
+}
+
 // ------------------------------------------------------------------------------------------------ TN
 __device__ __forceinline__ float block_max_512(float v, float *s_red) {
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
@@ -728,6 +911,35 @@ int mlcgb_gemm_tc_fused(int mode, const void *A, const void *B, const void *bias
     return rows_pipe_launch(mode, A, B, bias, aux, epilogue, M, N, K, C, status, (cudaStream_t)stream);
 }
 
+
+int mlcgb_gemm_tc_chain2(int backward, const void *A, const void *Wa, const void *ba, const void *Wb, const void *bb, const void *aux,
+                         int64_t M, void *mid_out, void *C, int32_t *status, void *stream) {
+    TimelineScope timeline_scope("gemm_tc_chain2", stream);
+    if (M < 0 || !status) return MLCGB_E_ARG;
+    if (M == 0) return MLCGB_OK;
+    if (!A || !Wa || !Wb || !aux || !C || (!backward && !mid_out)) return MLCGB_E_ARG;
+    if ((((uintptr_t)A | (uintptr_t)aux | (uintptr_t)C | (uintptr_t)mid_out) & 15) != 0) return MLCGB_E_LIMIT;
+    auto st = (cudaStream_t)stream;
+    const int64_t ntiles = (M + tc::kRows - 1) / tc::kRows;
+    const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
+    static bool f0[64] = {false}, f1[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    bool *flag = backward ? f1 : f0;
+    if (dev >= 0 && dev < 64 && !flag[dev]) {
+        const cudaError_t e = backward ? cudaFuncSetAttribute(gemm_tc_chain2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ChainSmem::kTotal)
+                                       : cudaFuncSetAttribute(gemm_tc_chain2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ChainSmem::kTotal);
+        if (e != cudaSuccess) return check_launch();
+        flag[dev] = true;
+    }
+    if (backward)
+        launch_pdl(gemm_tc_chain2_kernel<1>, dim3(grid), dim3(kGT), ChainSmem::kTotal, st, (const float *)A, (const float *)Wa, (const float *)ba,
+                   (const float *)Wb, (const float *)bb, (const float *)aux, M, (float *)mid_out, (float *)C, status);
+    else
+        launch_pdl(gemm_tc_chain2_kernel<0>, dim3(grid), dim3(kGT), ChainSmem::kTotal, st, (const float *)A, (const float *)Wa, (const float *)ba,
+                   (const float *)Wb, (const float *)bb, (const float *)aux, M, (float *)mid_out, (float *)C, status);
+    return check_launch();
+}
 
 int mlcgb_gemm_tc_tn_colsum(const void *A, const void *B, int64_t K, int64_t M, int64_t N, void *C, void *colsum, void *workspace,
                             size_t workspace_bytes, int32_t *status, void *stream) {

@@ -53,6 +53,10 @@ static int interaction_forward_counted(const void *x, const void *d, const int64
     if (rc) return rc;
     rc = mlcgb_seg_mul_sum(xl, Wp, MLCGB_F32, ptr_out, nbr_out, pair_of, N, P, F, agg, stream);                // aggregation
     if (rc) return rc;
+    if (H == 128 && F == 128 && H2 == 128) {                                                                   // lin2 + tanh -> lin + residual, one kernel
+        rc = mlcgb_gemm_tc_chain2(0, agg, W2, b2, W3, b3, x, N, a, out, status, stream);
+        if (rc != MLCGB_E_LIMIT) return rc;
+    }
     rc = mlcgb_gemm_tc_fused(0, agg, W2, b2, nullptr, 1, N, H2, F, a, status, stream);                         // lin2 + tanh
     if (rc) return rc;
     return mlcgb_gemm_tc_fused(0, a, W3, b3, x, 2, N, H, H2, out, status, stream);                             // lin + residual
@@ -83,9 +87,14 @@ static int interaction_backward_counted(const void *g, const void *a, const void
     if (!g || !a || !xl || !ptr_out || !W1 || !W2 || !W3 || !gy || !gagg || !gxl) return MLCGB_E_ARG;
     if (P > 0 && (!d || !nbr_out || !sel || !pair_of || !twin || !row0 || !row1 || !Wp)) return MLCGB_E_ARG;
     if (N < 128 || (H & 3) || (F & 3) || (H2 & 3) || H > 128 || F != 128 || H2 > 128) return MLCGB_E_LIMIT;
-    int rc = mlcgb_gemm_tc_fused(1, g, W3, nullptr, a, 3, N, H2, H, gy, status, stream);                      // through lin and tanh
-    if (rc) return rc;
-    rc = mlcgb_gemm_tc_fused(1, gy, W2, nullptr, nullptr, 0, N, F, H2, gagg, status, stream);                  // through lin2
+    int rc = MLCGB_E_LIMIT;
+    if (H == 128 && F == 128 && H2 == 128)                                                                     // through lin, tanh and lin2, one kernel
+        rc = mlcgb_gemm_tc_chain2(1, g, W3, nullptr, W2, nullptr, a, N, nullptr, gagg, status, stream);
+    if (rc == MLCGB_E_LIMIT) {
+        rc = mlcgb_gemm_tc_fused(1, g, W3, nullptr, a, 3, N, H2, H, gy, status, stream);                      // through lin and tanh
+        if (rc) return rc;
+        rc = mlcgb_gemm_tc_fused(1, gy, W2, nullptr, nullptr, 0, N, F, H2, gagg, status, stream);              // through lin2
+    }
     if (rc) return rc;
     if (gx) {
         rc = mlcgb_seg_mul_sum(gagg, Wp, MLCGB_F32, ptr_out, nbr_out, pair_of, N, P, F, gxl, stream);          // to the gathered features

@@ -283,3 +283,32 @@ def test_weight_and_bias_gradient_in_one_pass(K, M, N):
     assert float((P.cpu().double() - want_P).abs().max()) < 2e-5 * float(want_P.abs().max())
     assert float((s.cpu().double() - want_s).abs().max()) < 1e-5 * float(G.abs().sum(0).max())
     get_backend().check_pending()
+
+
+@pytest.mark.parametrize("M", [128, 1000, 51200])
+def test_two_chained_layers_equal_two_fused_gemms(M):
+    """mlcgb_gemm_tc_chain2 (the tail of an interaction block and its part of the force pass in one kernel, schnet.py:252-262
+    with the residual sum at :150) against two calls of mlcgb_gemm_tc_fused — the same arithmetic, so bit for bit — and against
+    float64."""
+    gen = torch.Generator().manual_seed(M)
+    be = get_backend()
+    r = lambda *s: torch.randn(*s, generator=gen)
+    A, X = r(M, 128).to(DEV), r(M, 128).to(DEV)
+    Wa, Wb = (r(128, 128) / 11).to(DEV), (r(128, 128) / 11).to(DEV)
+    ba, bb = (0.1 * r(128)).to(DEV), (0.1 * r(128)).to(DEV)
+    mid, out = be.gemm_chain2(False, A, Wa, ba, Wb, bb, X)
+    mid2 = be.gemm_fused(0, A, Wa, ba, None, 1)
+    out2 = be.gemm_fused(0, mid2, Wb, bb, X, 2)
+    assert torch.equal(mid, mid2) and torch.equal(out, out2)
+    mid64 = torch.tanh(A.double() @ Wa.double().t() + ba.double())
+    out64 = X.double() + mid64 @ Wb.double().t() + bb.double()
+    assert float((mid.double() - mid64).abs().max()) < 5e-6 and float((out.double() - out64).abs().max()) < 1e-5
+    # force pass: g -> (g W3) * (1 - a^2) -> . W2
+    G = r(M, 128).to(DEV)
+    _, gagg = be.gemm_chain2(True, G, Wb, None, Wa, None, mid)
+    gy2 = be.gemm_fused(1, G, Wb, None, mid, 3)
+    gagg2 = be.gemm_fused(1, gy2, Wa, None, None, 0)
+    assert torch.equal(gagg, gagg2)
+    g64 = ((G.double() @ Wb.double()) * (1 - mid64 ** 2)) @ Wa.double()
+    assert float((gagg.double() - g64).abs().max()) < 1e-5 * max(1.0, float(g64.abs().max()))
+    get_backend().check_pending()
