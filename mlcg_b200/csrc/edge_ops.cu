@@ -100,6 +100,81 @@ seg_mul_sum_kernel(const T *__restrict__ a, const T *__restrict__ V, const int64
     }
 }
 
+// The float32, 128-feature case (every configuration of the model): the rows of V — the one operand that comes from HBM — are
+// copied asynchronously into a ring of shared-memory slots, sixteen rows (8 KB) per warp in flight, instead of four per lane
+// through registers: the kernel above is bound by the latency of those loads at the number it can keep in flight.  A lane
+// copies and later reads its own 16 bytes of a row, so no synchronisation is needed beyond the copy groups.  Edge order
+// and accumulation order are those of the kernel above: identical results.
+constexpr int kSegSlots = 16, kSegWarps = 8;
+
+template <bool PERM>
+__global__ void __launch_bounds__(kSegWarps * 32)
+seg_mul_sum_async_kernel(const float *__restrict__ a, const float *__restrict__ V, const int64_t *__restrict__ ptr, const int32_t *__restrict__ nbr,
+                         const int32_t *__restrict__ eperm, int64_t N, float *__restrict__ out) {
+    extern __shared__ float4 seg_ring[];       // [warps][kSegSlots][32]
+    const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float4 *ring = seg_ring + (warp_in_block * kSegSlots) * 32 + lane;             // this lane's 16 bytes of slot s: ring[s * 32]
+    const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
+    const float4 *a4 = reinterpret_cast<const float4 *>(a) + lane, *V4 = reinterpret_cast<const float4 *>(V) + lane;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t n = warp; n < N; n += nwarps) {
+        const int64_t k0 = ptr[n], k1 = ptr[n + 1];
+        float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
+        for (int64_t c0 = k0; c0 < k1; c0 += 32) {               // the row's edges, 32 at a time: lane t holds edge c0 + t
+            const int len = (int)(k1 - c0 < 32 ? k1 - c0 : 32);
+            int32_t my_j = 0;
+            int64_t my_e = 0;
+            if (lane < len) {
+                my_j = nbr[c0 + lane];
+                my_e = PERM ? (int64_t)eperm[c0 + lane] : c0 + lane;
+            }
+            const int ngroups = (len + 3) >> 2;
+            // group g = edges 4g .. 4g+3 of the chunk -> slots (4g + u) % kSegSlots
+            auto issue = [&](int g) {
+                if (g < ngroups) {
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int t = 4 * g + u;
+                        const int64_t e = __shfl_sync(0xffffffffu, my_e, t & 31);
+                        if (t < len)
+                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring_addr + (uint32_t)((t % kSegSlots) * 512)), "l"(V4 + e * 32) : "memory");
+                    }
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");       // (an empty group keeps the count of pending groups fixed)
+            };
+#pragma unroll
+            for (int g = 0; g < kSegSlots / 4; g++) issue(g);
+            for (int g = 0; g < ngroups; g++) {
+                float4 x[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int t = 4 * g + u;
+                    const int32_t j = __shfl_sync(0xffffffffu, my_j, t & 31);
+                    x[u] = t < len ? __ldg(a4 + (int64_t)j * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                asm volatile("cp.async.wait_group %0;" ::"n"(kSegSlots / 4 - 1) : "memory");
+                const int full = 4 * g + 3 < len;
+                if (full) {
+                    const float4 v0 = ring[((4 * g) % kSegSlots) * 32], v1 = ring[((4 * g + 1) % kSegSlots) * 32];
+                    const float4 v2 = ring[((4 * g + 2) % kSegSlots) * 32], v3 = ring[((4 * g + 3) % kSegSlots) * 32];
+                    vfma(acc0, x[0], v0);
+                    vfma(acc1, x[1], v1);
+                    vfma(acc0, x[2], v2);
+                    vfma(acc1, x[3], v3);
+                } else {                                          // the last edges of the row, one by one into the first sum
+#pragma unroll
+                    for (int u = 0; u < 3; u++)
+                        if (4 * g + u < len) vfma(acc0, x[u], ring[((4 * g + u) % kSegSlots) * 32]);
+                }
+                issue(g + kSegSlots / 4);
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        reinterpret_cast<float4 *>(out)[n * 32 + lane] = make_float4(acc0.x + acc1.x, acc0.y + acc1.y, acc0.z + acc1.z, acc0.w + acc1.w);
+    }
+}
+
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 edge_mul_kernel(const T *__restrict__ a, const T *__restrict__ b, const int32_t *__restrict__ ia,
@@ -279,6 +354,25 @@ static int seg_mul_sum_launch(const void *a, const void *V, const int64_t *ptr, 
     constexpr int W = VecIO<T>::W;
     const bool vec = (F % W == 0) && ((uintptr_t)a % 16 == 0) && ((uintptr_t)V % 16 == 0) && ((uintptr_t)out % 16 == 0);
     const int64_t Fv = vec ? F / W : F;
+    if constexpr (sizeof(T) == 4) {
+        if (vec && F == 128) {
+            constexpr int kSmem = kSegWarps * kSegSlots * 512;
+            static bool done[64] = {false};
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (dev >= 0 && dev < 64 && !done[dev]) {
+                if (cudaFuncSetAttribute(seg_mul_sum_async_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess ||
+                    cudaFuncSetAttribute(seg_mul_sum_async_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
+                    return check_launch();
+                done[dev] = true;
+            }
+            const int64_t want = (N + kSegWarps - 1) / kSegWarps;
+            const int grid = (int)(want < (int64_t)kNumSM * 3 ? want : (int64_t)kNumSM * 3);      // three blocks of 64 KB per SM
+            if (eperm) seg_mul_sum_async_kernel<true><<<grid, kSegWarps * 32, kSmem, st>>>((const float *)a, (const float *)V, ptr, nbr, eperm, N, (float *)out);
+            else seg_mul_sum_async_kernel<false><<<grid, kSegWarps * 32, kSmem, st>>>((const float *)a, (const float *)V, ptr, nbr, eperm, N, (float *)out);
+            return check_launch();
+        }
+    }
     int G = 32;
     while (G > 1 && G / 2 >= Fv) G /= 2;  // smallest power of two >= Fv, capped at a warp
     const int grid = grid_for(N * G, 256, 16);

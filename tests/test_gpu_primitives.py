@@ -312,3 +312,27 @@ def test_two_chained_layers_equal_two_fused_gemms(M):
     g64 = ((G.double() @ Wb.double()) * (1 - mid64 ** 2)) @ Wa.double()
     assert float((gagg.double() - g64).abs().max()) < 1e-5 * max(1.0, float(g64.abs().max()))
     get_backend().check_pending()
+
+
+@pytest.mark.parametrize("with_perm", [False, True])
+def test_seg_mul_sum_rows_of_every_length(with_perm):
+    """The float32 / 128-feature kernel (rows of V through a ring of asynchronous copies, sixteen per warp in flight): rows with
+    no edge, fewer than a group of four, exactly 16, 17, 32, 33 and 100 edges, rows of V shared between edges; against the
+    oracle and run to run."""
+    gen = torch.Generator().manual_seed(5 + int(with_perm))
+    degs = [0, 1, 2, 3, 4, 5, 15, 16, 17, 31, 32, 33, 63, 64, 65, 100, 0, 7] * 9
+    N = len(degs)
+    ptr = torch.tensor([0] + degs).cumsum(0)
+    E = int(ptr[-1])
+    nbr = torch.cat([torch.randperm(N, generator=gen)[:d].sort().values if d <= N else torch.randint(0, N, (d,), generator=gen) for d in degs]).to(torch.int32)
+    a = torch.randn(N, 128, generator=gen)
+    P = E if not with_perm else E // 2 + 1
+    V = torch.randn(P, 128, generator=gen)
+    perm = torch.randint(0, P, (E,), generator=gen).to(torch.int32) if with_perm else None
+    be = get_backend()
+    dev = lambda t: None if t is None else t.to(DEV)
+    got = be.seg_mul_sum(dev(a), dev(V), dev(ptr), dev(nbr), dev(perm), N)
+    want = ORA.seg_mul_sum(a, V, ptr, nbr, perm, N)
+    assert torch.allclose(got.cpu(), want, rtol=1e-5, atol=1e-4)
+    assert not got[torch.tensor(degs) == 0].any()
+    assert torch.equal(got, be.seg_mul_sum(dev(a), dev(V), dev(ptr), dev(nbr), dev(perm), N))
