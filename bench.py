@@ -374,9 +374,17 @@ def measure_radius(dev, hbm_peak, arm, radius_structures=256, seed=1):
     if not same:
         raise RuntimeError(f"radius graph of {B} x 4000 points differs from the CPU oracle's")
     ms = time_cuda(lambda: be.radius_graph(pos, ptr, 10.0, 1000, False, 1, want_batch=False), iters=5, warm=1)
+    # the two library calls of that function on their own (CUDA events inside the library: no allocation, no host read between them)
+    be.timeline_begin()
+    for _ in range(5):
+        be.radius_graph(pos, ptr, 10.0, 1000, False, 1, want_batch=False)
+    tl = be.timeline_end()
+    parts = {k: v["ms"] / v["calls"] for k, v in tl.items()}
     nbytes = 16 * E + 20 * B * n
     out[f"radius_graph_{B}x4000"] = dict(edges=E, ms=ms, edges_per_s=E / (ms / 1e3), algorithmic_GBps=nbytes / ms / 1e6,
-                                        frac_of_hbm=nbytes / ms / 1e6 / hbm_peak, bit_exact_vs_cpu_oracle=same, cpu_ms=cpu_s * 1e3,
+                                        frac_of_hbm=nbytes / ms / 1e6 / hbm_peak, ms_library_calls=parts, ms_without_allocation_and_host_read=sum(parts.values()),
+                                        frac_of_hbm_without_allocation_and_host_read=nbytes / sum(parts.values()) / 1e6 / hbm_peak if parts else None,
+                                        bit_exact_vs_cpu_oracle=same, cpu_ms=cpu_s * 1e3,
                                         cpu_edges_per_s=E / cpu_s, cpu_cores=arm.cores,
                                         note="count + scan + host read of E + fill, allocation of the outputs included; algorithmic bytes = 16 B/edge "
                                              "written + 20 B/point read (the call also writes the two int32 index rows this package's kernels "
