@@ -741,10 +741,30 @@ def run_ours(args):
     e_timed, f_timed = e_res.cpu(), f_res.cpu()
     barrier()
 
-    t = torch.tensor([ms_total, e2e_s * 1e3, ms_recorded], dtype=torch.float64, device=dev)
+    # ---- the same evaluation recorded once into a CUDA graph and replayed: the step without the host's launch path (what the
+    # maximum over the ranks' host processes adds at N > 1 shows as the difference to `ms_per_step`)
+    ff = mlcg_b200.GraphedForceField(model, mlcg_b200.AtomicData(pos=pos_d.clone(), atom_types=types_d, batch=batch_d, n_atoms=n_atoms))
+    e_g, f_g = ff(pos_d)
+    if not (torch.equal(e_g, e_res) and torch.equal(f_g, f_res)):
+        raise RuntimeError("the replayed evaluation differs from the launched one")
+    pairs = []
+    barrier()
+    for _ in range(args.steps):
+        flush.fill_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        ff(pos_d)
+        b.record()
+        pairs.append((a, b))
+    barrier()
+    replay_ms = sum(a.elapsed_time(b) for a, b in pairs)
+    ff.check()
+    del ff
+
+    t = torch.tensor([ms_total, e2e_s * 1e3, ms_recorded, replay_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms, ms_recorded = float(t[0]), float(t[1]), float(t[2])
+    ms_total, e2e_ms, ms_recorded, replay_ms = float(t[0]), float(t[1]), float(t[2]), float(t[3])
 
     # ---- the training configuration's step, on every rank, with the gradient all-reduce when there are several
     training = None
@@ -895,7 +915,11 @@ def run_ours(args):
                                           "library's timeline on: a CUDA-event pair around every kernel-launching entry point"),
                 e2e=dict(value=world * B * args.steps / (e2e_ms / 1e3), unit="structures/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
                 gpu_launches=launches_timed, ms_per_step_median=sorted(step_ms)[len(step_ms) // 2], ms_per_step_min=min(step_ms),
-                ms_per_step_with_kernel_events=ms_recorded / args.steps, roofline=roof, cfconv_roofline=cfconv, parity_of_timed_batch=check,
+                ms_per_step_with_kernel_events=ms_recorded / args.steps,
+                graph_replay=dict(ms_per_step=replay_ms / args.steps, structures_per_s=world * B / (replay_ms / args.steps / 1e3),
+                                  note="the same evaluation recorded into a CUDA graph and replayed K times (positions copied in, radius graph rebuilt "
+                                       "in every replay); maximum over ranks"),
+                roofline=roof, cfconv_roofline=cfconv, parity_of_timed_batch=check,
                 other_kernels=extras, cpu_baseline=cpu, clocks=clk, kernels=kernels,
                 edges_per_s=world * n_edges * args.steps / (ms_total / 1e3))
     print(json.dumps(line))
