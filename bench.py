@@ -601,9 +601,44 @@ def training_cpu_leg(arm, steps=2):
         opt.step()
         return loss
 
+    # the first step's loss and parameter gradients (before any update), for the check against the GPU arm below
+    opt.zero_grad(set_to_none=True)
+    out = model(ns.AtomicData(pos=pos.clone(), atom_types=types_, batch=batch, n_atoms=torch.full((B,), n), neighbor_list={}))
+    loss0 = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], target)
+    loss0.backward()
+    grads0 = {k: p.grad.detach().clone() for k, p in net.named_parameters() if p.grad is not None}
     sec, _ = timed_host(step, steps, 1)
     return dict(ms_per_step_64_structures=sec * 1e3, structures_per_s=B / sec, cores=arm.cores, kind=arm.kind,
-                sample=f"64 structures x 73 beads per step, {steps} steps after 1 warm-up; {arm.describe()}")
+                sample=f"64 structures x 73 beads per step, {steps} steps after 1 warm-up; {arm.describe()}"), float(loss0.detach()), grads0
+
+
+def training_parity(dev, loss_cpu, grads_cpu):
+    """The GPU arm's first training step on the CPU leg's 64 structures (same seeds, same initial weights): loss within 1e-5
+    relative, every parameter gradient within 2e-4 of its tensor's largest entry (the bars of the test-suite's force-matching
+    cases); raises otherwise."""
+    import mlcg_b200
+    from mlcg_b200 import nn as bnn
+    B, n, T = 64, 73, 20
+    net = make_model(cutoff=10.0, n_types=T).to(dev)
+    model = bnn.GradientsOut(net, "forces").train()
+    gen = torch.Generator().manual_seed(4000)
+    pos, types_ = random_walks(B, n, gen), torch.randint(0, T, (B * n,), generator=gen)
+    batch, target = torch.arange(B).repeat_interleave(n), torch.randn(B * n, 3, generator=gen)
+    out = model(mlcg_b200.AtomicData(pos=pos.to(dev), atom_types=types_.to(dev), batch=batch.to(dev), n_atoms=torch.full((B,), n, device=dev)))
+    loss = torch.nn.functional.mse_loss(out.out["SchNet"]["forces"], target.to(dev))
+    loss.backward()
+    worst, worst_name = 0.0, None
+    for k, p in net.named_parameters():
+        if k in grads_cpu and p.grad is not None:
+            err = float((p.grad.cpu() - grads_cpu[k]).abs().max() / (grads_cpu[k].abs().max() + 1e-30))
+            if err > worst:
+                worst, worst_name = err, k
+    rel_loss = abs(float(loss.detach()) - loss_cpu) / abs(loss_cpu)
+    res = dict(loss=float(loss.detach()), cpu_loss=loss_cpu, rel_loss_difference=rel_loss, worst_gradient_error=worst, worst_gradient=worst_name,
+               loss_rtol=1e-5, gradient_bar=2e-4, ok=bool(rel_loss <= 1e-5 and worst <= 2e-4))
+    if not res["ok"]:
+        raise RuntimeError(f"first training step on 64 x 73 beads differs from the CPU arm: {res}")
+    return res
 
 
 # ----------------------------------------------------------------------------------------- GPU arm
@@ -891,7 +926,10 @@ def run_ours(args):
                                               force_rel_rms_vs_fp32_mode=rel_rms,
                                               note="same workload, filter-network GEMMs with bf16 operands (one product, tanh.approx)")
             if training is not None:
-                training["cpu"] = training_cpu_leg(arm)
+                leg = training_cpu_leg(arm)
+                if leg is not None:
+                    training["cpu"], loss_cpu, grads_cpu = leg
+                    training["parity_first_step"] = training_parity(dev, loss_cpu, grads_cpu)
         except Exception as exc:   # the headline line is still printed
             extras = {"error": repr(exc)}
     if training is not None:
