@@ -318,6 +318,8 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
     int s = 0;
     for (int64_t tile = first; tile < ntiles; tile += step, s ^= 1) {
         const uint32_t ta = tmem + 256 + s * 128, ta_next = tmem + 256 + (s ^ 1) * 128;
+        const int64_t next = tile + step;
+        const float d_next = next < ntiles ? load_d(next) : 1.f;      // (two dependent loads: on their way while (a) and (b) run)
         // (a) GEMM 1 of this tile is running: write out W of the previous tile
         if (tile != first) store_w(tile - step, c_prev);
         // (b) h = tanh(z + b1) -> A operand (over phi, which GEMM 1 has finished reading), then GEMM 2
@@ -345,9 +347,8 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
             mma_commit(bar2);
         }
         // (c) GEMM 2 is running: radial basis of the next tile into the other A block
-        const int64_t next = tile + step;
         c_prev = c_cur;
-        if (next < ntiles) c_cur = basis_to_tmem(load_d(next), ta_next);
+        if (next < ntiles) c_cur = basis_to_tmem(d_next, ta_next);
         if (!mbar_wait(bar2, ph2)) failed = true;
         ph2 ^= 1;
         tc_fence_after();
