@@ -199,7 +199,7 @@ __device__ __forceinline__ float4 *stage_chunk(uint8_t *stage, int row, int chun
 // the radial basis of tile i+1.
 // ------------------------------------------------------------------------------------------------
 template <bool SPLIT, int NT>
-__global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams p, const __grid_constant__ CUtensorMap wmap, int use_map) {
+__global__ void __launch_bounds__(NT + 32, 1) filter_fwd_pipe_kernel(FilterFwdParams p, const __grid_constant__ CUtensorMap wmap, int use_map) {
     constexpr int NC = 128 * 128 / NT;      // columns per thread: 32 with 512 threads (1024 threads x 16 columns measured no faster)
     constexpr int RPW = 128 * 32 / NT;      // rows each warp writes out: 8 or 4
     using namespace tc;
@@ -212,6 +212,7 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
     const float2 *s_tab = reinterpret_cast<const float2 *>(smem + L::kMisc + L::kTable);
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar);
     uint64_t *s_bar2 = reinterpret_cast<uint64_t *>(smem + L::kMisc + L::kBar + 64);
+    uint64_t *s_r1 = s_bar2 + 1, *s_r2 = s_bar2 + 2;      // operands of GEMM 1 / GEMM 2 ready (one arrival per compute warp)
     int *s_err = reinterpret_cast<int *>(reinterpret_cast<uint32_t *>(s_bar + 1) + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -222,7 +223,11 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
     const float unscale = 1.f / wscale;
 
     const uint32_t tmem = filter_setup<SPLIT>(p, smem, Kpad1, 512);
-    if (tid == 0) mbar_init(smem_u32(s_bar2), 1);
+    if (tid == 0) {
+        mbar_init(smem_u32(s_bar2), 1);
+        mbar_init(smem_u32(s_r1), NT / 32);
+        mbar_init(smem_u32(s_r2), NT / 32);
+    }
     __syncthreads();
     pdl_wait();                    // set-up done (weights only); from here on the distances of the previous kernels are read
     pdl_launch_dependents();
@@ -264,6 +269,7 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
         tmem_wait_st();
         return same_env ? env : envelope_jet<float, 0>(de, p.conv).c[0];
     };
+    auto compute_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory"); };     // the compute warps (not the issuing one)
     // W = y * C(d): D2 -> shared-memory stage -> global memory.  With a tensor map (rows written in order) the stage is four
     // 32-column boxes in the 128-byte swizzle and one thread hands them to the copy engine, which drains them while the
     // CTA goes on; otherwise (rows scattered to an edge and its reverse) warps copy whole 512-byte rows themselves.
@@ -271,14 +277,15 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
         C *= unscale;
         float v[NC];
         tmem_ld_cols<NC>(t_lane + 128 + col0, v);
+        if (tid == 0) bulk_wait_read<0>();                      // the copies of the tile before have read the stage
+        compute_sync();                                         // ... and every thread is done with it
         if (use_map) {
             const int chunk0 = (col0 & 31) >> 2;
 #pragma unroll
             for (int q = 0; q < NC / 4; q++)
                 *box_chunk(stage, col0 >> 5, r, chunk0 + q) = make_float4(v[4 * q] * C, v[4 * q + 1] * C, v[4 * q + 2] * C, v[4 * q + 3] * C);
             fence_async_smem();                                 // the copy engine reads the stage through the async proxy
-            tc_fence_before();
-            __syncthreads();
+            compute_sync();
             if (tid == 0) {
 #pragma unroll
                 for (int b = 0; b < 4; b++) tensor_store_box(&wmap, 32 * b, (int)(tile * kRows), stage + b * 16384);
@@ -289,8 +296,7 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
 #pragma unroll
         for (int q = 0; q < NC / 4; q++)
             *stage_chunk(stage, r, (col0 >> 2) + q) = make_float4(v[4 * q] * C, v[4 * q + 1] * C, v[4 * q + 2] * C, v[4 * q + 3] * C);
-        tc_fence_before();
-        __syncthreads();
+        compute_sync();
 #pragma unroll
         for (int i = 0; i < RPW; i++) {
             const int row = warp * RPW + i;
@@ -304,66 +310,85 @@ __global__ void __launch_bounds__(NT, 1) filter_fwd_pipe_kernel(FilterFwdParams 
         }
     };
 
-    float c_cur = 0.f, c_prev = 0.f;
-    if (first < ntiles) {
-        c_cur = basis_to_tmem(load_d(first), tmem + 256);
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-            issue_gemm_ts<SPLIT>(tmem, tmem + 256, b1_hi, b1_lo, Kpad1 / 16, 0, 128);
-            mma_commit(bar1);
-        }
-    }
-    int s = 0;
-    for (int64_t tile = first; tile < ntiles; tile += step, s ^= 1) {
-        const uint32_t ta = tmem + 256 + s * 128, ta_next = tmem + 256 + (s ^ 1) * 128;
-        const int64_t next = tile + step;
-        const float d_next = next < ntiles ? load_d(next) : 1.f;      // (two dependent loads: on their way while (a) and (b) run)
-        // (a) GEMM 1 of this tile is running: write out W of the previous tile
-        if (tile != first) store_w(tile - step, c_prev);
-        // (b) h = tanh(z + b1) -> A operand (over phi, which GEMM 1 has finished reading), then GEMM 2
-        if (!mbar_wait(bar1, ph1)) failed = true;
-        ph1 ^= 1;
+    // a wait that has run out is not repeated: the block runs on (on whatever the accumulators hold), so that every barrier
+    // of the schedule is still reached by everybody, and reports the failure at the end
+    auto await = [&](uint32_t bar, uint32_t parity) {
+        if (!failed && !mbar_wait(bar, parity)) failed = true;
         tc_fence_after();
-        {
-            float v[NC];
-            tmem_ld_cols<NC>(t_lane + col0, v);
-            tanh_row32<SPLIT, NC>(v, s_b1 + kF, col0, unscale * (2.f * kLog2e));
-            store_a_tmem_cols<SPLIT, NC>(ta + lane_off, col0, v, 1.f);
-            if (NC == 32 && p.H) {                               // kept for the backward (rows past the end hold finite filler)
-                float4 *hb = reinterpret_cast<float4 *>(p.H);
-#pragma unroll
-                for (int j = 0; j < NC / 4; j++) __stcs(hb + hidden_offset(tile, col0 >> 5, j, r), make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+    };
+    const int64_t n_local = first < ntiles ? (ntiles - first + step - 1) / step : 0;
+    if (warp == NT / 32) {
+        // ---- the issuing warp: per tile GEMM 1 when the basis is in its operand block, GEMM 2 when the hidden layer is.  The
+        //      tensor core's queue is short, so issuing a GEMM takes about as long as the GEMM: kept off the compute warps
+        for (int64_t j = 0; j < n_local; j++) {
+            const uint32_t ta = tmem + 256 + (uint32_t)(j & 1) * 128, par = (uint32_t)(j & 1);
+            await(smem_u32(s_r1), par);
+            if (lane == 0) {
+                issue_gemm_ts<SPLIT>(tmem, ta, b1_hi, b1_lo, Kpad1 / 16, 0, 128);
+                mma_commit(bar1);
             }
-            tmem_wait_st();
+            __syncwarp();
+            await(smem_u32(s_r2), par);
+            if (lane == 0) {
+                issue_gemm_ts<SPLIT>(tmem + 128, ta, b2_hi, b2_lo, kF / 16, 0, 128);
+                mma_commit(bar2);
+            }
+            __syncwarp();
         }
-        bulk_wait_read<0>();                                     // the copies of (a) have read the stage
-        tc_fence_before();
-        __syncthreads();                                         // also: every thread is done with the stage of (a)
-        if (tid == 0) {
-            tc_fence_after();
-            issue_gemm_ts<SPLIT>(tmem + 128, ta, b2_hi, b2_lo, kF / 16, 0, 128);
-            mma_commit(bar2);
+    } else {
+        // this warp's operand stores and accumulator reads are done: one arrival on the barrier the issuing warp waits for
+        auto signal = [&](uint64_t *bar) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(bar));
+        };
+        float c_cur = 0.f, c_prev = 0.f;
+        if (n_local > 0) {
+            c_cur = basis_to_tmem(load_d(first), tmem + 256);
+            signal(s_r1);
         }
-        // (c) GEMM 2 is running: radial basis of the next tile into the other A block
-        c_prev = c_cur;
-        if (next < ntiles) c_cur = basis_to_tmem(d_next, ta_next);
-        if (!mbar_wait(bar2, ph2)) failed = true;
-        ph2 ^= 1;
-        tc_fence_after();
-        if (failed) s_err[0] = 1;
-        tc_fence_before();
-        __syncthreads();
-        if (s_err[0]) break;
-        if (next < ntiles && tid == 0) {                          // GEMM 1 of the next tile (D1 was consumed in (b))
-            tc_fence_after();
-            issue_gemm_ts<SPLIT>(tmem, ta_next, b1_hi, b1_lo, Kpad1 / 16, 0, 128);
-            mma_commit(bar1);
+        int s = 0;
+        for (int64_t tile = first; tile < ntiles; tile += step, s ^= 1) {
+            const uint32_t ta = tmem + 256 + s * 128, ta_next = tmem + 256 + (s ^ 1) * 128;
+            const int64_t next = tile + step;
+            const float d_next = next < ntiles ? load_d(next) : 1.f;      // (two dependent loads: on their way while (a) and (b) run)
+            // (a) GEMM 1 of this tile is running (or about to): GEMM 2 of the previous tile done -> write out its W
+            if (tile != first) {
+                await(bar2, ph2);
+                ph2 ^= 1;
+                store_w(tile - step, c_prev);
+            }
+            // (b) h = tanh(z + b1) -> A operand (over phi, which GEMM 1 has finished reading); GEMM 2 can go
+            await(bar1, ph1);
+            ph1 ^= 1;
+            {
+                float v[NC];
+                tmem_ld_cols<NC>(t_lane + col0, v);
+                tanh_row32<SPLIT, NC>(v, s_b1 + kF, col0, unscale * (2.f * kLog2e));
+                store_a_tmem_cols<SPLIT, NC>(ta + lane_off, col0, v, 1.f);
+                if (NC == 32 && p.H) {                               // kept for the backward (rows past the end hold finite filler)
+                    float4 *hb = reinterpret_cast<float4 *>(p.H);
+#pragma unroll
+                    for (int j = 0; j < NC / 4; j++) __stcs(hb + hidden_offset(tile, col0 >> 5, j, r), make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+                }
+                tmem_wait_st();
+            }
+            signal(s_r2);
+            // (c) radial basis of the next tile into the other A block (GEMM 2 of the previous tile, its last reader, is done:
+            //     waited for in (a)); GEMM 1 of the next tile can go (its accumulator was read in (b))
+            c_prev = c_cur;
+            if (next < ntiles) {
+                c_cur = basis_to_tmem(d_next, ta_next);
+                signal(s_r1);
+            }
         }
-        if (next >= ntiles) store_w(tile, c_prev);                // last tile of this CTA
+        if (n_local > 0) {                       // W of the last tile
+            await(bar2, ph2);
+            store_w(first + (n_local - 1) * step, c_prev);
+        }
     }
 
+    if (failed) s_err[0] = 1;
     bulk_wait_all();
     tc_fence_before();
     __syncthreads();
@@ -387,7 +412,7 @@ static int filter_fwd_launch(const FilterFwdParams &p, cudaStream_t st) {
     const int use_map = (make_rows_map(&wmap, p.W, p.E, kF) && !(p.sel && p.twin)) ? 1 : 0;
     const int64_t ntiles = (p.E + tc::kRows - 1) / tc::kRows;
     const int grid = (int)(ntiles < kNumSM ? ntiles : kNumSM);
-    launch_pdl(filter_fwd_pipe_kernel<SPLIT, kTcThreads>, dim3(grid), dim3(kTcThreads), L::kTotal, st, p, wmap, use_map);
+    launch_pdl(filter_fwd_pipe_kernel<SPLIT, kTcThreads>, dim3(grid), dim3(kTcThreads + 32), L::kTotal, st, p, wmap, use_map);
     return check_launch();
 }
 
