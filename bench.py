@@ -339,11 +339,23 @@ def measure_small(dev, hbm_peak, arm, seed=0):
     fn1 = arm.schnet_evaluator(sd1, n1, **arch1)
     sec1, (e1r, f1r) = timed_host(lambda: fn1(pos1, types1, batch1, B1), 10, 2)
     e1x, f1x = arm.schnet_evaluator(sd1, n1, dtype=torch.float64, **arch1)(pos1, types1, batch1, B1)
-    out["eval_64x10"] = dict(ms=ms, structures_per_s=B1 / (ms / 1e3), cpu_ms=sec1 * 1e3, cpu_structures_per_s=B1 / sec1,
+    # the same evaluation with a fixed edge capacity (no host read of the edge count) recorded into a CUDA graph and replayed
+    n_edges1 = int(be.radius_graph(d1["pos"], torch.arange(B1 + 1, device=dev) * n1, 30.0, 1000, False, 1)["edge_index"].shape[1])
+    bnn.set_edge_capacity(m1, n_edges1 + (n_edges1 % 2) + 64)
+    ff = mlcg_b200.GraphedForceField(m1, mlcg_b200.AtomicData(pos=d1["pos"].clone(), atom_types=d1["atom_types"], batch=d1["batch"], n_atoms=d1["n_atoms"]))
+    ms_replay = time_cuda(lambda: ff(d1["pos"]), iters=20, warm=5)
+    e1g, f1g = ff(d1["pos"])
+    ff.check()
+    if not (torch.allclose(e1g, e1, rtol=1e-6, atol=1e-6) and torch.allclose(f1g, f1, rtol=0, atol=1e-5)):
+        raise RuntimeError("the replayed evaluation of 64 x 10 beads differs from the launched one")
+    bnn.set_edge_capacity(m1, None)
+    out["eval_64x10"] = dict(ms=ms, structures_per_s=B1 / (ms / 1e3), ms_graph_replay=ms_replay, structures_per_s_graph_replay=B1 / (ms_replay / 1e3),
+                             cpu_ms=sec1 * 1e3, cpu_structures_per_s=B1 / sec1,
                              parity=parity(e1.cpu(), f1.cpu(), e1r, f1r, e1x, f1x),
                              note="64 structures x 10 beads, 2 blocks, 50 Gaussian functions on 0-30 A; radius graph + energy + forces per call; "
-                                  "GPU time is the host's launch path at this size; CPU: all 64 structures, 10 calls")
-    del m1, net1
+                                  "GPU time is the host's launch path at this size (`ms`), or the chain of small kernels when the call is "
+                                  "replayed from a CUDA graph (`ms_graph_replay`); CPU: all 64 structures, 10 calls")
+    del ff, m1, net1
 
     return out
 
