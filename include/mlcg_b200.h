@@ -206,6 +206,11 @@ int mlcgb_seg_mul_sum(const void *a /* [Na,F] */, const void *V /* [E,F] */, int
 /* V[e,:] = a[ia[e],:] * b[ib[e],:] */
 int mlcgb_edge_mul(const void *a, const void *b, int dtype, const int32_t *ia, const int32_t *ib, int64_t E, int64_t F,
                    void *V /* [E,F] */, void *stream);
+/* V[p,:] = a[ia[p],:] * b[ib[p],:] + a[ib[p],:] * b[ia[p],:]: on a symmetric edge list the filter depends on the pair's distance
+ * only (W = net(rbf(d)) * C(d), src/mlcg/nn/schnet.py:340-341), so it can be kept once per unordered pair; this is the
+ * gradient of the aggregation (mlcgb_seg_mul_sum with eperm = the edge -> pair index) with respect to such a row. */
+int mlcgb_pair_mul(const void *a, const void *b, int dtype, const int32_t *ia /* [P] */, const int32_t *ib /* [P] */, int64_t P,
+                   int64_t F, void *V /* [P,F] */, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Filter-generating network GEMMs.  MLP([R,F,F]) built at src/mlcg/nn/schnet.py:446-450 and run by

@@ -75,6 +75,7 @@ SIGNATURES = {
     "mlcgb_rbf_param_contract": (c_int, [c_vp, c_vp, c_vp, c_int, c_i64, ctypes.POINTER(RbfSpecStruct), c_int, c_vp, c_sz, c_vp, c_vp, c_vp]),
     "mlcgb_seg_mul_sum": (c_int, [c_vp, c_vp, c_int, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp]),
     "mlcgb_edge_mul": (c_int, [c_vp, c_vp, c_int, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp]),
+    "mlcgb_pair_mul": (c_int, [c_vp, c_vp, c_int, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp]),
     "mlcgb_gemm_workspace_bytes": (c_sz, [c_int, c_i64, c_i64, c_i64, c_int]),
     "mlcgb_gemm": (c_int, [c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp]),
     "mlcgb_gemm_tc_supported": (c_int, [c_int, c_i64, c_i64, c_i64]),

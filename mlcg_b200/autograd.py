@@ -40,6 +40,7 @@ class EdgePlan:
     loops: bool = False                # the list may hold edges (i, i)
     _half: Optional[torch.Tensor] = None
     _pair_of: Optional[torch.Tensor] = None
+    _pair_rows: Optional[tuple] = None
 
     def half_selection(self) -> Optional[torch.Tensor]:
         """One edge per unordered pair (row0 < row1) of a symmetric, loop-free list; None if that does not apply."""
@@ -58,6 +59,16 @@ class EdgePlan:
         if self._pair_of is None:
             self._pair_of = get_backend().pair_index(sel, self.perm_in)
         return self._pair_of
+
+    def pair_rows(self):
+        """(row0, row1) of the selected edge of every unordered pair (int32 [E/2] each); None if that does not apply."""
+        sel = self.half_selection()
+        if sel is None:
+            return None
+        if self._pair_rows is None:
+            idx = sel.long()
+            self._pair_rows = (self.row0.index_select(0, idx).contiguous(), self.row1.index_select(0, idx).contiguous())
+        return self._pair_rows
 
     @staticmethod
     def from_centre_sorted(row0, row1, offsets, N, symmetric: bool, loops: bool = False) -> "EdgePlan":
@@ -165,6 +176,67 @@ class EdgeMul(torch.autograd.Function):
         ga = SegOut.apply(b, gV, ctx.plan) if ctx.needs_input_grad[0] else None
         gb = SegIn.apply(a, gV, ctx.plan) if ctx.needs_input_grad[1] else None
         return ga, gb, None
+
+
+# ------------------------------------------------------------------------------- the same family with V stored once per pair
+# On a symmetric, loop-free list W depends on the pair's distance only, so the filter network can run on one row per unordered
+# pair (half the rows of every edge-sized operator of a training step).  With V per pair the two aggregations coincide,
+#     SegPair(a, V)[n] = sum_{e: row0(e)=n} a[row1(e)] * V[pair(e)]          PairMul(a, b)[p] = a[i] b[j] + a[j] b[i],  p = {i, j}
+# and the family is closed again: d SegPair / da = SegPair(g, V), d SegPair / dV = PairMul(a, g), d PairMul / da = SegPair(b, G).
+class SegPair(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, V, plan: EdgePlan):
+        ctx.plan = plan
+        ctx.save_for_backward(a, V)
+        return get_backend().seg_mul_sum(a, V, plan.ptr_out, plan.nbr_out, plan.pair_index(), plan.N)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, V = ctx.saved_tensors
+        ga = SegPair.apply(g, V, ctx.plan) if ctx.needs_input_grad[0] else None
+        gV = PairMul.apply(a, g, ctx.plan) if ctx.needs_input_grad[1] else None
+        return ga, gV, None
+
+
+class PairMul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, plan: EdgePlan):
+        ctx.plan = plan
+        ctx.save_for_backward(a, b)
+        ia, ib = plan.pair_rows()
+        return get_backend().pair_mul(a, b, ia, ib)
+
+    @staticmethod
+    def backward(ctx, G):
+        a, b = ctx.saved_tensors
+        ga = SegPair.apply(b, G, ctx.plan) if ctx.needs_input_grad[0] else None
+        gb = SegPair.apply(a, G, ctx.plan) if ctx.needs_input_grad[1] else None
+        return ga, gb, None
+
+
+class PairSelect(torch.autograd.Function):
+    """One value per unordered pair out of one per edge (the selected edge's); its gradient goes back to that edge alone."""
+
+    @staticmethod
+    def forward(ctx, v, plan: EdgePlan):
+        ctx.plan = plan
+        return v.index_select(0, plan.half_selection().long())
+
+    @staticmethod
+    def backward(ctx, g):
+        return PairScatter.apply(g, ctx.plan), None
+
+
+class PairScatter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g, plan: EdgePlan):
+        ctx.plan = plan
+        out = torch.zeros((plan.E,) + tuple(g.shape[1:]), dtype=g.dtype, device=g.device)
+        return out.index_copy_(0, plan.half_selection().long(), g)       # (distinct positions: no accumulation, no atomics)
+
+    @staticmethod
+    def backward(ctx, gg):
+        return PairSelect.apply(gg, ctx.plan), None
 
 
 # ------------------------------------------------------------------------------- edge geometry

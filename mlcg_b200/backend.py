@@ -476,6 +476,16 @@ class CudaBackend:
             self._run("edge_mul", self.lib.mlcgb_edge_mul, (_ptr(a), _ptr(b), _dt(a), _ptr(ia), _ptr(ib), E, F, _ptr(out), _stream(),), **self._work("edge_mul", locals()))
         return out
 
+    def pair_mul(self, a, b, ia, ib):
+        """out[p,:] = a[ia[p],:] * b[ib[p],:] + a[ib[p],:] * b[ia[p],:]."""
+        _need_cuda(a, b, ia, ib)
+        a, b = a.contiguous(), b.contiguous()
+        E, F = ia.numel(), a.shape[1]
+        out = torch.empty((E, F), dtype=a.dtype, device=a.device)
+        with _on(a.device):
+            self._run("pair_mul", self.lib.mlcgb_pair_mul, (_ptr(a), _ptr(b), _dt(a), _ptr(ia), _ptr(ib), E, F, _ptr(out), _stream(),), **self._work("edge_mul", locals()))
+        return out
+
     def row_scale(self, a, c):
         """out[e,:] = a[e,:] * c[e]."""
         _need_cuda(a, c)

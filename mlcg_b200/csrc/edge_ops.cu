@@ -175,6 +175,31 @@ seg_mul_sum_async_kernel(const float *__restrict__ a, const float *__restrict__ 
     }
 }
 
+// V[p,:] = a[ia[p],:] * b[ib[p],:] + a[ib[p],:] * b[ia[p],:]: the two directed edges of an unordered pair share their row of V,
+// so the gradient with respect to that row is the sum of both edges' products
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+pair_mul_kernel(const T *__restrict__ a, const T *__restrict__ b, const int32_t *__restrict__ ia,
+                const int32_t *__restrict__ ib, int64_t P, int64_t F, T *__restrict__ V) {
+    using VT = typename VecIO<T>::V;
+    constexpr int W = VEC ? VecIO<T>::W : 1;
+    const int64_t Fv = F / W;
+    const int64_t total = P * Fv;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e = t / Fv, c = t - e * Fv;
+        const int64_t i = ia[e], j = ib[e];
+        if (VEC) {
+            const VT ai = __ldg(reinterpret_cast<const VT *>(a + i * F) + c), bj = __ldg(reinterpret_cast<const VT *>(b + j * F) + c);
+            const VT aj = __ldg(reinterpret_cast<const VT *>(a + j * F) + c), bi = __ldg(reinterpret_cast<const VT *>(b + i * F) + c);
+            VT acc = vmul(ai, bj);
+            vfma(acc, aj, bi);
+            st_stream(reinterpret_cast<VT *>(V + e * F) + c, acc);
+        } else {
+            V[e * F + c] = fma(a[j * F + c], b[i * F + c], a[i * F + c] * b[j * F + c]);
+        }
+    }
+}
+
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 edge_mul_kernel(const T *__restrict__ a, const T *__restrict__ b, const int32_t *__restrict__ ia,
@@ -423,6 +448,23 @@ int mlcgb_edge_mul(const void *a, const void *b, int dtype, const int32_t *ia, c
         const int grid = grid_for(work, 256, 32);
         if (vec) edge_mul_kernel<scalar_t, true><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)b, ia, ib, E, F, (scalar_t *)V);
         else edge_mul_kernel<scalar_t, false><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)b, ia, ib, E, F, (scalar_t *)V);
+        return check_launch();
+    });
+}
+
+int mlcgb_pair_mul(const void *a, const void *b, int dtype, const int32_t *ia, const int32_t *ib, int64_t P, int64_t F, void *V,
+                   void *stream) {
+    TimelineScope timeline_scope("pair_mul", stream);
+    if (P < 0 || F <= 0) return MLCGB_E_ARG;
+    if (P == 0) return MLCGB_OK;
+    if (!a || !b || !ia || !ib || !V) return MLCGB_E_ARG;
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        constexpr int W = VecIO<scalar_t>::W;
+        const bool vec = (F % W == 0) && ((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)V % 16 == 0);
+        const int64_t work = P * (vec ? F / W : F);
+        const int grid = grid_for(work, 256, 32);
+        if (vec) pair_mul_kernel<scalar_t, true><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)b, ia, ib, P, F, (scalar_t *)V);
+        else pair_mul_kernel<scalar_t, false><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)b, ia, ib, P, F, (scalar_t *)V);
         return check_launch();
     });
 }

@@ -9,8 +9,8 @@ from typing import Final, List
 import torch
 
 from .. import _lib
-from ..autograd import (EdgeDiff, EdgeDistanceOnce, FusedFilterConv, FusedInteraction, RowScale, SchNetEval, SegIn, SegmentSum, edge_distances,
-                        plan_of)
+from ..autograd import (EdgeDiff, EdgeDistanceOnce, FusedFilterConv, FusedInteraction, PairSelect, RowScale, SchNetEval, SegIn, SegmentSum, SegPair,
+                        edge_distances, plan_of)
 from ..backend import get_backend
 from ..data import ENERGY_KEY
 from ..neighbor_list import atomic_data2neighbor_list, edge_plan_for, validate_neighborlist
@@ -32,10 +32,16 @@ class LazyRadialBasis:
         return _tag_symmetric(self.rbf_layer(self.distances), self.symmetric)
 
 _SYM = "_mlcgb_symmetric"   # tag on edge tensors that are functions of the (symmetric) distance only
+_PAIRS = "_mlcgb_per_pair"  # tag on tensors that hold one row per unordered pair of the edge list instead of one per edge
 
 
 def _tag_symmetric(t: torch.Tensor, flag: bool) -> torch.Tensor:
     setattr(t, _SYM, flag)
+    return t
+
+
+def _tag_pairs(t: torch.Tensor) -> torch.Tensor:
+    setattr(t, _PAIRS, True)
     return t
 
 
@@ -144,7 +150,10 @@ class CFConv(torch.nn.Module):
         symmetric = bool(getattr(edge_weight, _SYM, False) and getattr(edge_attr, _SYM, False))
         W = self.filters(edge_weight, edge_attr)
         x = node_linear(self.lin1, x, self.training)
-        x = SegIn.apply(x, W, plan, symmetric)      # x_j = x[edge_index[0]], summed at edge_index[1]
+        if getattr(edge_weight, _PAIRS, False) and getattr(edge_attr, _PAIRS, False) and W.shape[0] * 2 == plan.E:
+            x = SegPair.apply(x, W, plan)           # one filter row per unordered pair, read from both of its ends
+        else:
+            x = SegIn.apply(x, W, plan, symmetric)  # x_j = x[edge_index[0]], summed at edge_index[1]
         return node_linear(self.lin2, x, self.training)
 
     def message(self, x_j: torch.Tensor, W: torch.Tensor) -> torch.Tensor:
@@ -325,9 +334,17 @@ class SchNet(torch.nn.Module):
         specs = [b.conv.fused_spec(self.rbf_layer) if (not self.training and type(b) is InteractionBlock and type(b.conv) is CFConv) else None
                  for b in self.interaction_blocks]
         lazy_ok = not self.training and distances.dtype == torch.float32 and all(s is not None for s in specs)
+        # Training on a symmetric, loop-free list: the filters depend on the pair's distance only, so the basis, the filter network
+        # and all their derivatives run on one row per unordered pair (half the rows); the aggregation reads a pair's row from
+        # both of its ends (autograd.SegPair).  Only for blocks known to pass these tensors straight to their CFConv.
+        per_pair = (self.training and not shifted and plan.half_selection() is not None
+                    and all(type(b) is InteractionBlock and type(b.conv) is CFConv for b in self.interaction_blocks))
         if lazy_ok:
             _warn_frozen_weights(self)
             rbf_expansion = LazyRadialBasis(distances, self.rbf_layer, plan.symmetric)
+        elif per_pair:
+            distances = _tag_pairs(PairSelect.apply(distances, plan))
+            rbf_expansion = _tag_pairs(self.rbf_layer(distances))
         else:
             rbf_expansion = _tag_symmetric(self.rbf_layer(distances), plan.symmetric)
         # (number of structures for blocks that ask for it, taken from n_atoms where that avoids reading batch[-1] on the host)

@@ -149,6 +149,9 @@ class OracleBackend:
     def edge_mul(self, a, b, ia, ib):
         return a[ia.long()] * b[ib.long()]
 
+    def pair_mul(self, a, b, ia, ib):
+        return a[ia.long()] * b[ib.long()] + a[ib.long()] * b[ia.long()]
+
     def gemm_tn_colsum(self, G, X):
         return G.t() @ X, G.sum(0)
 

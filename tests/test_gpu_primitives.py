@@ -336,3 +336,42 @@ def test_seg_mul_sum_rows_of_every_length(with_perm):
     assert torch.allclose(got.cpu(), want, rtol=1e-5, atol=1e-4)
     assert not got[torch.tensor(degs) == 0].any()
     assert torch.equal(got, be.seg_mul_sum(dev(a), dev(V), dev(ptr), dev(nbr), dev(perm), N))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_pair_family_is_closed_under_differentiation(dtype):
+    """SegPair / PairMul (filters stored once per unordered pair) against SegIn / EdgeMul on the same symmetric list with every
+    pair's row copied to both of its edges: values, first and second derivatives."""
+    from mlcg_b200 import autograd as ag2
+    gen = torch.Generator().manual_seed(9)
+    B, n = 3, 12
+    pos = torch.cat([torch.randn(n, 3, generator=gen) * 2.0 for _ in range(B)]).to(DEV)
+    ptr = (torch.arange(B + 1) * n).to(DEV)
+    res = get_backend().radius_graph(pos, ptr, 3.0, 1000, False, 1)
+    row0, row1 = res["edge_index"][0].to(torch.int32), res["edge_index"][1].to(torch.int32)
+    plan = ag2.EdgePlan.from_centre_sorted(row0.contiguous(), row1.contiguous(), res["offsets"], B * n, symmetric=True)
+    P = plan.E // 2
+    assert plan.half_selection() is not None and P > 10
+    a = torch.randn(B * n, 16, dtype=dtype, generator=gen).to(DEV).requires_grad_(True)
+    Vp = torch.randn(P, 16, dtype=dtype, generator=gen).to(DEV).requires_grad_(True)
+    Ve = Vp[plan.pair_index().long()]                          # the same rows, one copy per directed edge
+    out_p = ag2.SegPair.apply(a, Vp, plan)
+    out_e = ag2.SegIn.apply(a, Ve, plan, True)
+    t = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=1e-12, atol=1e-12)
+    assert torch.allclose(out_p, out_e, **t)
+    w = torch.randn(B * n, 16, dtype=dtype, generator=gen).to(DEV)
+    ga_p, gV_p = torch.autograd.grad((out_p * w).sum(), [a, Vp], create_graph=True)
+    ga_e, gV_e = torch.autograd.grad((out_e * w).sum(), [a, Vp], create_graph=True)
+    assert torch.allclose(ga_p, ga_e, **t) and torch.allclose(gV_p, gV_e, **t)
+    u = torch.randn(P, 16, dtype=dtype, generator=gen).to(DEV)
+    gg_p = torch.autograd.grad((gV_p * u).sum(), [a])[0]
+    gg_e = torch.autograd.grad((gV_e * u).sum(), [a])[0]
+    assert torch.allclose(gg_p, gg_e, **t)
+    if dtype == torch.float64:
+        a2 = torch.randn(B * n, 4, dtype=dtype, generator=gen).to(DEV).requires_grad_(True)
+        V2 = torch.randn(P, 4, dtype=dtype, generator=gen).to(DEV).requires_grad_(True)
+        assert torch.autograd.gradcheck(lambda x, v: ag2.SegPair.apply(x, v, plan), (a2, V2))
+        assert torch.autograd.gradgradcheck(lambda x, v: ag2.SegPair.apply(x, v, plan), (a2, V2))
+        d = torch.rand(plan.E, dtype=dtype, generator=gen).to(DEV).requires_grad_(True)
+        assert torch.autograd.gradcheck(lambda x: ag2.PairSelect.apply(x, plan), (d,))
+        assert torch.autograd.gradgradcheck(lambda x: ag2.PairSelect.apply(x, plan), (d,))

@@ -121,6 +121,8 @@ def test_fullwidth_golden_force_matching_step(golden_fullwidth, name):
     # reduction kernel (the reference's default is ExpNormalBasis(trainable=True), exp_normal.py:52)
     assert {"rbf_expand", "rbf_contract"} <= ran, ran
     assert ("rbf_param_contract" in ran) == name.endswith("_trainable"), ran
+    # the list is symmetric and loop-free: basis, filter network and their derivatives ran on one row per unordered pair
+    assert "pair_mul" in ran and "edge_mul" not in ran, ran
     assert torch.allclose(loss.detach().cpu(), c["loss"], rtol=1e-5)
     grads = dict(net.named_parameters())
     worst = 0.0
