@@ -853,11 +853,11 @@ __global__ void gemm_tc_reduce_kernel(const float *__restrict__ partial, int64_t
     }
 }
 
-// CTAs of the TN kernels (each writes one [M,N] partial): one per SM for edge-sized contractions; for short ones at least
-// four tiles per CTA, so that the set-up and the reduction over partials do not outweigh the tiles
+// CTAs of the TN kernels (each writes one [M,N] partial): one per SM for edge-sized contractions; for short ones two tiles
+// per CTA (one, two and four measured within a per cent of one another on a node-sized contraction)
 static int tn_parts(int64_t K) {
     const int64_t ntiles = (K + tc::kRows - 1) / tc::kRows;
-    int64_t parts = (ntiles + 3) / 4;
+    int64_t parts = (ntiles + 1) / 2;
     if (parts > kNumSM) parts = kNumSM;
     return (int)(parts < 1 ? 1 : parts);
 }
