@@ -845,10 +845,20 @@ gemm_tc_tn_pipe_kernel(const float *__restrict__ A, const float *__restrict__ B,
     if (warp == 0) tmem_free(tmem, 512);
 }
 
+// C = the partials added in their order (eight loads in flight at a time; the additions stay in sequence, so the result does
+// not depend on how the loop is unrolled)
 __global__ void gemm_tc_reduce_kernel(const float *__restrict__ partial, int64_t MN, int parts, float *__restrict__ C) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < MN; i += (int64_t)gridDim.x * blockDim.x) {
         float s = 0.f;
-        for (int z = 0; z < parts; z++) s += partial[(int64_t)z * MN + i];
+        int z = 0;
+        for (; z + 8 <= parts; z += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = __ldg(partial + (int64_t)(z + u) * MN + i);
+#pragma unroll
+            for (int u = 0; u < 8; u++) s += v[u];
+        }
+        for (; z < parts; z++) s += __ldg(partial + (int64_t)z * MN + i);
         C[i] = s;
     }
 }
