@@ -9,7 +9,7 @@
 //        shared memory)
 //     -> neighbours_tile<COUNT> for structures of up to 8192 points with a cell grid: a block takes
 //        four neighbouring rows of cells of one layer, stages the points of every row within reach in
-//        shared memory once, and four threads per centre walk the centre's runs of candidates there;
+//        shared memory once, and eight threads per centre walk the centre's runs of candidates there;
 //        neighbours<COUNT> for the rest (one warp per centre over the rows of cells within reach, each
 //        row a contiguous run of cell-sorted points; small structures scan all their points instead)
 //     -> exclusive scan of the degrees (three small kernels, no spin-waits)
@@ -525,9 +525,9 @@ __global__ void __launch_bounds__(kScanBlock) group_scan_kernel(const CellParam 
 // One work item = the centres of up to kTileRY neighbouring rows of cells (along y) of one layer (z) of one structure: a
 // contiguous run of the cell-sorted points.  Their candidates lie in the rows within `reach` of those, (kTileRY + 2 reach)
 // x (2 reach + 1) whole rows of cells, each a contiguous run as well: staged in shared memory once per item (read straight
-// from global memory when they do not fit).  Four threads share a centre and split its (2 reach + 1)^2 rows; inside a row a
+// from global memory when they do not fit).  Eight threads share a centre and split its (2 reach + 1)^2 rows; inside a row a
 // centre tests the cells within `reach` of its own along x.  COUNT: hits below / above the centre's own index, summed over
-// the four threads, give the degree under the neighbour-cap rule.  FILL: hits set bits in the centre's mask over the
+// the eight threads, give the degree under the neighbour-cap rule.  FILL: hits set bits in the centre's mask over the
 // structure's local indices; a warp per centre then walks the mask and writes the edges in ascending order.
 template <typename T, bool FILL>
 __global__ void __launch_bounds__(kTileThreads)
