@@ -196,7 +196,8 @@ __device__ __forceinline__ float4 *stage_chunk(uint8_t *stage, int row, int chun
 // leaves room for two tiles in flight.  TMEM columns: D1 [0,128) | D2 [128,256) | A of even tiles
 // [256,384) | A of odd tiles [384,512) (fp16 hi in the first 64 columns of an A block, lo in the last 64).
 // While GEMM 1 of tile i runs the threads store W of tile i-1; while GEMM 2 of tile i runs they evaluate
-// the radial basis of tile i+1.
+// the radial basis of tile i+1.  NT compute threads and one more warp that only issues the tensor-core instructions, when
+// the compute warps have told it (one mbarrier arrival each) that an operand block is written.
 // ------------------------------------------------------------------------------------------------
 template <bool SPLIT, int NT>
 __global__ void __launch_bounds__(NT + 32, 1) filter_fwd_pipe_kernel(FilterFwdParams p, const __grid_constant__ CUtensorMap wmap, int use_map) {
