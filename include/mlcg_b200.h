@@ -306,6 +306,10 @@ int mlcgb_row_scale(const void *a /* [E,F] */, const void *c /* [E] */, int dtyp
                     void *stream);
 int mlcgb_row_dot(const void *a /* [E,F] */, const void *b /* [E,F] */, int dtype, int64_t E, int64_t F, void *out /* [E] */,
                   void *stream);
+/* The derivative of the tanh activation (src/mlcg/nn/schnet.py:252-262, 446-450) given its output y, over n elements:
+ *   mode 0: out = g * (1 - y^2)   (first derivative: the force pass)       mode 1: out = -2 * G * g * y   (its derivative with
+ * respect to y: the second-order pass of force matching).  G is ignored in mode 0. */
+int mlcgb_tanh_grad(int mode, const void *G, const void *g, const void *y, int dtype, int64_t n, void *out, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * One interaction block per call (eval mode, symmetric edge list, float32, 128 filters):

@@ -82,6 +82,7 @@ SIGNATURES = {
     "mlcgb_gemm_tc_workspace_bytes": (c_sz, [c_int, c_i64, c_i64, c_i64]),
     "mlcgb_gemm_tc": (c_int, [c_int, c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_sz, c_vp, c_vp]),
     "mlcgb_gemm_tc_chain2": (c_int, [c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_vp]),
+    "mlcgb_tanh_grad": (c_int, [c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_vp, c_vp]),
     "mlcgb_row_scale": (c_int, [c_vp, c_vp, c_int, c_i64, c_i64, c_vp, c_vp]),
     "mlcgb_row_dot": (c_int, [c_vp, c_vp, c_int, c_i64, c_i64, c_vp, c_vp]),
     "mlcgb_gemm_tc_tn_colsum": (c_int, [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp]),

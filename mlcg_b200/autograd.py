@@ -362,6 +362,61 @@ class RowScale(torch.autograd.Function):
         return ga, gc
 
 
+# ------------------------------------------------------------------------------- tanh and its derivatives
+class Tanh(torch.autograd.Function):
+    """``tanh`` whose derivatives of every order are single elementwise kernels (torch expands the second derivative of tanh
+    into several multiplications over the edge-sized tensors of a force-matching step)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        y = torch.tanh(x)
+        ctx.save_for_backward(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        (y,) = ctx.saved_tensors
+        return TanhGrad.apply(g, y)
+
+
+class TanhGrad(torch.autograd.Function):
+    """g (1 - y^2)."""
+
+    @staticmethod
+    def forward(ctx, g, y):
+        ctx.save_for_backward(g, y)
+        return get_backend().tanh_grad(0, None, g, y)
+
+    @staticmethod
+    def backward(ctx, G):
+        g, y = ctx.saved_tensors
+        gg = TanhGrad.apply(G, y) if ctx.needs_input_grad[0] else None
+        gy = TanhGrad2.apply(G, g, y) if ctx.needs_input_grad[1] else None
+        return gg, gy
+
+
+class TanhGrad2(torch.autograd.Function):
+    """-2 G g y; beyond this order the derivatives are plain torch products."""
+
+    @staticmethod
+    def forward(ctx, G, g, y):
+        ctx.save_for_backward(G, g, y)
+        return get_backend().tanh_grad(1, G, g, y)
+
+    @staticmethod
+    def backward(ctx, u):
+        G, g, y = ctx.saved_tensors
+        return (-2 * u * g * y if ctx.needs_input_grad[0] else None, -2 * u * G * y if ctx.needs_input_grad[1] else None,
+                -2 * u * G * g if ctx.needs_input_grad[2] else None)
+
+
+def tanh(x: torch.Tensor) -> torch.Tensor:
+    """:class:`Tanh` for CUDA tensors that take part in a graph, ``torch.tanh`` otherwise."""
+    if x.is_cuda and x.requires_grad and torch.is_grad_enabled() and x.dtype in (torch.float32, torch.float64):
+        return Tanh.apply(x)
+    return torch.tanh(x)
+
+
 class RowDot(torch.autograd.Function):
     """out[e] = sum_f a[e,f] * b[e,f]."""
 

@@ -486,6 +486,17 @@ class CudaBackend:
             self._run("pair_mul", self.lib.mlcgb_pair_mul, (_ptr(a), _ptr(b), _dt(a), _ptr(ia), _ptr(ib), E, F, _ptr(out), _stream(),), **self._work("edge_mul", locals()))
         return out
 
+    def tanh_grad(self, mode: int, G, g, y):
+        """mode 0: ``g * (1 - y**2)``; mode 1: ``-2 * G * g * y`` (elementwise; ``G`` is ignored in mode 0)."""
+        _need_cuda(G, g, y)
+        g, y = g.contiguous(), y.contiguous()
+        G = None if G is None else G.contiguous()
+        out = torch.empty_like(y)
+        with _on(y.device):
+            self._run("tanh_grad", self.lib.mlcgb_tanh_grad, (int(mode), _ptr(G), _ptr(g), _ptr(y), _dt(y), y.numel(), _ptr(out), _stream(),),
+                      nbytes=(3 + mode) * y.numel() * y.element_size(), flops=(3 + mode) * y.numel())
+        return out
+
     def row_scale(self, a, c):
         """out[e,:] = a[e,:] * c[e]."""
         _need_cuda(a, c)

@@ -347,6 +347,33 @@ row_scale_kernel(const T *__restrict__ a, const T *__restrict__ c, int64_t E, in
     }
 }
 
+// The derivative of tanh given its output, and the derivative of that (the activation of the filter network and of the
+// interaction blocks, src/mlcg/nn/schnet.py:252-262, 446-450, differentiated once for the forces and again for force matching):
+//   MODE 0: out = g (1 - y^2)          MODE 1: out = -2 G g y
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+tanh_grad_kernel(const T *__restrict__ G, const T *__restrict__ g, const T *__restrict__ y, int64_t n, T *__restrict__ out) {
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x) {
+        const T yy = y[t], gg = g[t];
+        out[t] = MODE == 0 ? gg * (T(1) - yy * yy) : T(-2) * G[t] * gg * yy;
+    }
+}
+template <int MODE>
+__global__ void __launch_bounds__(256)
+tanh_grad_vec_kernel(const float4 *__restrict__ G, const float4 *__restrict__ g, const float4 *__restrict__ y, int64_t n4, float4 *__restrict__ out) {
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < n4; t += (int64_t)gridDim.x * blockDim.x) {
+        const float4 yy = ld_stream(y + t), gg = ld_stream(g + t);
+        float4 o;
+        if (MODE == 0) {
+            o = make_float4(gg.x * fmaf(-yy.x, yy.x, 1.f), gg.y * fmaf(-yy.y, yy.y, 1.f), gg.z * fmaf(-yy.z, yy.z, 1.f), gg.w * fmaf(-yy.w, yy.w, 1.f));
+        } else {
+            const float4 GG = ld_stream(G + t);
+            o = make_float4(-2.f * GG.x * gg.x * yy.x, -2.f * GG.y * gg.y * yy.y, -2.f * GG.z * gg.z * yy.z, -2.f * GG.w * gg.w * yy.w);
+        }
+        out[t] = o;
+    }
+}
+
 // out[e] = sum_f a[e,f] * b[e,f]: one warp per row, fixed-shape shuffle reduction
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
@@ -515,6 +542,26 @@ int mlcgb_row_scale(const void *a, const void *c, int dtype, int64_t E, int64_t 
         const int grid = grid_for(E * (vec ? F / W : F), 256, 32);
         if (vec) row_scale_kernel<scalar_t, true><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)c, E, F, (scalar_t *)out);
         else row_scale_kernel<scalar_t, false><<<grid, 256, 0, (cudaStream_t)stream>>>((const scalar_t *)a, (const scalar_t *)c, E, F, (scalar_t *)out);
+        return check_launch();
+    });
+}
+
+int mlcgb_tanh_grad(int mode, const void *G, const void *g, const void *y, int dtype, int64_t n, void *out, void *stream) {
+    TimelineScope timeline_scope("tanh_grad", stream);
+    if (n < 0 || (mode != 0 && mode != 1)) return MLCGB_E_ARG;
+    if (n == 0) return MLCGB_OK;
+    if (!g || !y || !out || (mode == 1 && !G)) return MLCGB_E_ARG;
+    auto st = (cudaStream_t)stream;
+    if (dtype == MLCGB_F32 && (n & 3) == 0 && (((uintptr_t)g | (uintptr_t)y | (uintptr_t)out | (uintptr_t)G) & 15) == 0) {
+        const int grid = grid_for(n / 4, 256, 32);
+        if (mode == 0) tanh_grad_vec_kernel<0><<<grid, 256, 0, st>>>((const float4 *)G, (const float4 *)g, (const float4 *)y, n / 4, (float4 *)out);
+        else tanh_grad_vec_kernel<1><<<grid, 256, 0, st>>>((const float4 *)G, (const float4 *)g, (const float4 *)y, n / 4, (float4 *)out);
+        return check_launch();
+    }
+    return MLCGB_DISPATCH_DTYPE(dtype, [&] {
+        const int grid = grid_for(n, 256, 32);
+        if (mode == 0) tanh_grad_kernel<scalar_t, 0><<<grid, 256, 0, st>>>((const scalar_t *)G, (const scalar_t *)g, (const scalar_t *)y, n, (scalar_t *)out);
+        else tanh_grad_kernel<scalar_t, 1><<<grid, 256, 0, st>>>((const scalar_t *)G, (const scalar_t *)g, (const scalar_t *)y, n, (scalar_t *)out);
         return check_launch();
     });
 }

@@ -3,7 +3,7 @@ from typing import List
 
 import torch
 
-from ..autograd import MatmulNT
+from ..autograd import MatmulNT, tanh as tanh_op
 
 
 def init_xavier_uniform(module: torch.nn.Module, zero_bias: bool = True) -> None:
@@ -62,6 +62,8 @@ class MLP(torch.nn.Module):
         for layer in self.layers:
             if isinstance(layer, torch.nn.Linear):
                 x = linear(layer, x, frozen)
+            elif type(layer) is torch.nn.Tanh:
+                x = tanh_op(x)
             else:
                 x = layer(x)
         return x

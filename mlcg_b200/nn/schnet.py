@@ -11,6 +11,7 @@ import torch
 from .. import _lib
 from ..autograd import (EdgeDiff, EdgeDistanceOnce, FusedFilterConv, FusedInteraction, PairSelect, RowScale, SchNetEval, SegIn, SegmentSum, SegPair,
                         edge_distances, plan_of)
+from ..autograd import tanh as tanh_op
 from ..backend import get_backend
 from ..data import ENERGY_KEY
 from ..neighbor_list import atomic_data2neighbor_list, edge_plan_for, validate_neighborlist
@@ -175,7 +176,9 @@ class InteractionBlock(torch.nn.Module):
         init_xavier_uniform(self.lin)
 
     def forward(self, x, edge_index, edge_weight, edge_attr, *args):
-        return node_linear(self.lin, self.activation(self.conv(x, edge_index, edge_weight, edge_attr)), self.training)
+        y = self.conv(x, edge_index, edge_weight, edge_attr)
+        y = tanh_op(y) if type(self.activation) is torch.nn.Tanh else self.activation(y)
+        return node_linear(self.lin, y, self.training)
 
     def forward_residual(self, x, edge_index, edge_weight, edge_attr, *args, fused=None):
         """``x + self(x, ...)`` (the sum at schnet.py:150).  In eval mode, when the block has the standard layout — a CFConv the

@@ -155,6 +155,9 @@ class OracleBackend:
     def gemm_tn_colsum(self, G, X):
         return G.t() @ X, G.sum(0)
 
+    def tanh_grad(self, mode, G, g, y):
+        return g * (1 - y * y) if mode == 0 else -2 * G * g * y
+
     def row_scale(self, a, c):
         return a * c.unsqueeze(-1)
 

@@ -375,3 +375,32 @@ def test_pair_family_is_closed_under_differentiation(dtype):
         d = torch.rand(plan.E, dtype=dtype, generator=gen).to(DEV).requires_grad_(True)
         assert torch.autograd.gradcheck(lambda x: ag2.PairSelect.apply(x, plan), (d,))
         assert torch.autograd.gradgradcheck(lambda x: ag2.PairSelect.apply(x, plan), (d,))
+
+
+def test_tanh_operator_derivatives():
+    """autograd.Tanh (derivatives as single kernels, mlcgb_tanh_grad) against torch.tanh: value, first, second and third
+    derivative in float64 (gradcheck / gradgradcheck) and float32 values."""
+    from mlcg_b200 import autograd as ag2
+    gen = torch.Generator().manual_seed(21)
+    x = (2 * torch.randn(37, 12, dtype=torch.float64, generator=gen)).to(DEV).requires_grad_(True)
+    assert torch.autograd.gradcheck(ag2.Tanh.apply, (x,))
+    assert torch.autograd.gradgradcheck(ag2.Tanh.apply, (x,))
+    w = torch.randn(37, 12, dtype=torch.float64, generator=gen).to(DEV)
+    for fn in (ag2.Tanh.apply, torch.tanh):
+        y = fn(x)
+        (g1,) = torch.autograd.grad((y * w).sum(), x, create_graph=True)
+        (g2,) = torch.autograd.grad((g1 * w).sum(), x, create_graph=True)
+        (g3,) = torch.autograd.grad((g2 * w).sum(), x)
+        if fn is torch.tanh:
+            assert torch.allclose(ours[0], g1, rtol=1e-12, atol=1e-12) and torch.allclose(ours[1], g2, rtol=1e-12, atol=1e-12)
+            assert torch.allclose(ours[2], g3, rtol=1e-11, atol=1e-11)
+        else:
+            ours = (g1.detach(), g2.detach(), g3.detach())
+    x32 = (2 * torch.randn(1000, 128, generator=gen)).to(DEV).requires_grad_(True)       # the vectorised float32 kernels
+    w32 = torch.randn(1000, 128, generator=gen).to(DEV)
+    res = []
+    for fn in (ag2.tanh, torch.tanh):
+        (g1,) = torch.autograd.grad((fn(x32) * w32).sum(), x32, create_graph=True)
+        (g2,) = torch.autograd.grad((g1 * w32).sum(), x32)
+        res.append((g1.detach(), g2))
+    assert torch.allclose(res[0][0], res[1][0], rtol=1e-5, atol=1e-6) and torch.allclose(res[0][1], res[1][1], rtol=1e-5, atol=1e-6)
