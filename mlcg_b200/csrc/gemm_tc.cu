@@ -863,6 +863,29 @@ __global__ void gemm_tc_reduce_kernel(const float *__restrict__ partial, int64_t
     }
 }
 
+// The same for two sets of partials in one launch (a weight gradient and its bias gradient): element i < MN of the first,
+// element i - MN of the second
+__global__ void gemm_tc_reduce2_kernel(const float *__restrict__ partial, int64_t MN, const float *__restrict__ partial2, int64_t M2, int parts,
+                                       float *__restrict__ C, float *__restrict__ C2) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < MN + M2; i += (int64_t)gridDim.x * blockDim.x) {
+        const bool second = i >= MN;
+        const float *src = second ? partial2 + (i - MN) : partial + i;
+        const int64_t stride = second ? M2 : MN;
+        float s = 0.f;
+        int z = 0;
+        for (; z + 8 <= parts; z += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = __ldg(src + (int64_t)(z + u) * stride);
+#pragma unroll
+            for (int u = 0; u < 8; u++) s += v[u];
+        }
+        for (; z < parts; z++) s += __ldg(src + (int64_t)z * stride);
+        if (second) C2[i - MN] = s;
+        else C[i] = s;
+    }
+}
+
 // CTAs of the TN kernels (each writes one [M,N] partial): one per SM for edge-sized contractions; for short ones two tiles
 // per CTA (one, two and four measured within a per cent of one another on a node-sized contraction)
 static int tn_parts(int64_t K) {
@@ -968,8 +991,7 @@ int mlcgb_gemm_tc_tn_colsum(const void *A, const void *B, int64_t K, int64_t M, 
     }
     float *part = (float *)workspace, *cpart = part + (size_t)parts * M * N;
     gemm_tc_tn_pipe_kernel<<<parts, kGT, GemmTnSmem::kTotal, st>>>((const float *)A, (const float *)B, K, (int)M, (int)N, part, cpart, status);
-    gemm_tc_reduce_kernel<<<grid_for(M * N, 256), 256, 0, st>>>(part, M * N, parts, (float *)C);
-    gemm_tc_reduce_kernel<<<grid_for(M, 256), 256, 0, st>>>(cpart, M, parts, (float *)colsum);
+    gemm_tc_reduce2_kernel<<<grid_for(M * N + M, 256), 256, 0, st>>>(part, M * N, cpart, M, parts, (float *)C, (float *)colsum);
     return check_launch();
 }
 
