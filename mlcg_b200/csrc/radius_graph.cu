@@ -57,6 +57,9 @@ constexpr int kTileCand = 2048;                           // candidate points st
 constexpr int kTileMaskWords = 8192;                      // hit masks of one pass (FILL): centres x ceil(n / 32) words
 constexpr int kTileList = 256;                            // compacted bit positions of one emission round, per warp (FILL)
 
+constexpr int kBlkMaxBY = 8;                               // block kernels: rows of cells in a block, at most
+constexpr int kBlkTargetCentres = 21;                      // mean number of centres per block the block's size aims at
+
 template <typename T> using V4 = typename Vec4<T>::type;
 
 __device__ __forceinline__ int idx_of(const float4 &p) { return __float_as_int(p.w); }
@@ -80,7 +83,7 @@ static WsLayout ws_layout(int64_t N, int64_t B, int dtype) {
     L.cell_start = o;  o += align256((size_t)(N + B) * 4);
     L.struct_of = o;   o += align256((size_t)N * 4);
     L.bsum = o;        o += align256((size_t)((N + kScanBlock - 1) / kScanBlock + 1) * 8);
-    L.group_ptr = o;   o += align256((size_t)(B + 1) * 4);
+    L.group_ptr = o;   o += align256((size_t)(B + 2) * 4);
     L.total = o;
     return L;
 }
@@ -169,7 +172,23 @@ build_cells_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, i
             if (!(finite && rcut > T(0))) reach = 1;
             if (reach > 2) reach = 2;                      // h >= reach_len / 2 by construction
             const int tile = allow_tile && n <= kCapBits;
-            cellparam[b] = CellParam{g[0], g[1], g[2], 1, reach, tile, tile ? g[2] * ((g[1] + kTileRY - 1) / kTileRY) : 0, 0};
+            // block of cells per work item of the block kernels: about kBlkTargetCentres points, as square as the grid allows
+            int bx = 1, by = 1;
+            if (tile) {
+                const double dens = (double)n / ((double)g[0] * g[1] * g[2]);
+                int area = (int)floor(kBlkTargetCentres / dens + 0.5);
+                if (area < 1) area = 1;
+                bx = (int)floor(sqrt((double)area) + 0.5);
+                bx = bx < 1 ? 1 : (bx > g[0] ? g[0] : bx);
+                by = (area + bx - 1) / bx;
+                const int by_max = g[1] < kBlkMaxBY ? g[1] : kBlkMaxBY;
+                by = by > by_max ? by_max : by;
+                if (bx * by < area) {
+                    bx = (area + by - 1) / by;
+                    bx = bx > g[0] ? g[0] : (bx > 255 ? 255 : bx);
+                }
+            }
+            cellparam[b] = CellParam{g[0], g[1], g[2], 1, reach, tile, tile ? g[2] * ((g[1] + by - 1) / by) * ((g[0] + bx - 1) / bx) : 0, bx | (by << 8)};
         }
         __syncthreads();
         const int gx = s_g[0], gy = s_g[1], gz = s_g[2];
@@ -258,7 +277,9 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
                   int64_t max_nn, int loop, int rule, const V4<T> *__restrict__ spos,
                   const CellParam *__restrict__ cellparam, const int32_t *__restrict__ cell_of,
                   const int32_t *__restrict__ cell_start, const int32_t *__restrict__ struct_of, int32_t *__restrict__ deg,
-                  const int64_t *__restrict__ offsets, FillOut out, Exclusion ex, int32_t *__restrict__ status) {
+                  const int64_t *__restrict__ offsets, FillOut out, Exclusion ex, int32_t *__restrict__ status,
+                  const int32_t *__restrict__ n_plain) {
+    if (n_plain && *n_plain == 0) return;          // every structure belongs to the block kernels
     __shared__ unsigned s_mask[FILL ? kNbrWarps * (kCapBits / 32) : 1];
     __shared__ unsigned short s_list[FILL ? kNbrWarps * 1024 : 1];   // per warp: bit positions of one 32-word chunk
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -507,19 +528,25 @@ static void launch_scan(const int32_t *deg, int64_t N, int64_t *bsum, int64_t *o
 }
 
 // ------------------------------------------------------------------------------------- tile kernels
-// group_ptr[b] = work items of the structures before b (exclusive scan of CellParam::ngroups), group_ptr[B] = all of them
+// group_ptr[b] = work items of the structures before b (exclusive scan of CellParam::ngroups), group_ptr[B] = all of them,
+// group_ptr[B + 1] = structures that have no work items (left to the warp kernels)
 __global__ void __launch_bounds__(kScanBlock) group_scan_kernel(const CellParam *__restrict__ cellparam, int64_t B, int32_t *__restrict__ group_ptr) {
     __shared__ int64_t s_warp[33];
     int64_t carry = 0;
+    int plain = 0;
     for (int64_t c0 = 0; c0 < B; c0 += kScanBlock) {
         const int64_t k = c0 + threadIdx.x;
         const int64_t v = k < B ? cellparam[k].ngroups : 0;
+        plain += __syncthreads_count(k < B && cellparam[k].tile == 0);
         int64_t total;
         const int64_t ex = block_exclusive_scan(v, s_warp, &total);
         if (k < B) group_ptr[k] = (int32_t)(carry + ex);
         carry += total;
     }
-    if (threadIdx.x == 0) group_ptr[B] = (int32_t)carry;
+    if (threadIdx.x == 0) {
+        group_ptr[B] = (int32_t)carry;
+        group_ptr[B + 1] = plain;
+    }
 }
 
 // One work item = the centres of up to kTileRY neighbouring rows of cells (along y) of one layer (z) of one structure: a
@@ -793,6 +820,837 @@ neighbours_tile_kernel(const T *__restrict__ pos, const int64_t *__restrict__ pt
     }
 }
 
+// ------------------------------------------------------------------------------------ block kernels
+// One work item = the centres in a block of bx x by cells of one layer (z) of one structure, about kBlkTargetCentres of
+// them, taken by ONE WARP (a block of 32 threads: the warps share nothing and never meet): a lane per centre.  Their
+// candidates are the cells within `reach` of the block: (by + 2 reach) x (2 reach + 1) runs of the cell-sorted points.  The
+// warp stages them in shared memory and every lane tests its centre against the whole staged list: the list is read with
+// broadcast loads, the loop is the same for all lanes, and a test is nine instructions (load, six for the squared distance
+// as the reference rounds it, compare, count).
+//   COUNT stages the candidates as they come (asynchronous copies, all in flight together).
+//   FILL stages them in ascending order of their local index: the warp marks the indices in a bitmask over the structure
+//   (at most kCapBits points), a prefix sum of the mask's population counts gives every candidate its rank, and the
+//   candidate is written to that position.  A lane appends the index of every hit to its centre's list in shared memory,
+//   which is then in the order the edges are listed in: no per-centre sort or mask.  The warp goes through the lists and
+//   writes the edges with consecutive lanes on consecutive slots.
+// More candidates than the stage holds are taken in windows (of ranks, in FILL), more than 32 centres in passes, more hits
+// than a list holds in several emissions.
+template <typename T> struct BlockCap { static constexpr int value = 768; };
+template <> struct BlockCap<double> { static constexpr int value = 384; };
+constexpr int kBlkList = 128;                             // FILL: entries of a centre's hit list between two emissions
+constexpr int kBlkListStride = kBlkList + 2;              // (in 16-bit entries: an odd number of words, so that lanes at the same
+                                                          //  position of their lists use different banks)
+
+template <typename T, bool FILL>
+struct BlockSmem {
+    static constexpr int kCap = BlockCap<T>::value;
+    static constexpr size_t cand = 0;                                         // V4<T>[kCap]: staged candidates
+    static constexpr size_t src = cand + (size_t)kCap * sizeof(V4<T>);        // u16[kCap]: where the candidates of a stage come from
+    static constexpr size_t rows = src + (size_t)kCap * 2;                    // int k0[64], off[65]
+    static constexpr size_t mask = rows + 544;                                // FILL: u32[kCapBits / 32]
+    static constexpr size_t pref = mask + (FILL ? kCapBits / 8 : 0);          // FILL: u16[kCapBits / 32]
+    static constexpr size_t hits = pref + (FILL ? kCapBits / 16 : 0);         // FILL: u16[32][kBlkListStride]
+    static constexpr size_t total = (hits + (FILL ? (size_t)32 * kBlkListStride * 2 : 0) + 31) & ~(size_t)31;
+};
+
+template <typename T> __device__ __forceinline__ V4<T> far_point();
+template <> __device__ __forceinline__ float4 far_point<float>() { return make_float4(INFINITY, INFINITY, INFINITY, 0.f); }
+template <> __device__ __forceinline__ double4 far_point<double>() { return make_double4((double)INFINITY, (double)INFINITY, (double)INFINITY, 0.0); }
+
+// d2 < r2 (false for NaN, like the C++ comparison): the 16-bit value goes to the shared-memory address `end`, which moves on
+// by one entry.  Two predicated instructions after the comparison; as a branch the compiler makes of the same, the hit path
+// of almost every test (some lane hits) costs several times that.
+__device__ __forceinline__ void push_if_below(float d2, float r2, uint32_t &end, int value) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.f32 p, %1, %2;\n\t@p st.shared.u16 [%0], %3;\n\t@p add.u32 %0, %0, 2;\n\t}"
+                 : "+r"(end) : "f"(d2), "f"(r2), "h"((unsigned short)value));
+}
+__device__ __forceinline__ void push_if_below(double d2, double r2, uint32_t &end, int value) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.f64 p, %1, %2;\n\t@p st.shared.u16 [%0], %3;\n\t@p add.u32 %0, %0, 2;\n\t}"
+                 : "+r"(end) : "d"(d2), "d"(r2), "h"((unsigned short)value));
+}
+
+template <typename T, bool FILL>
+__global__ void __launch_bounds__(32, 14)                  // (shared memory allows 14 one-warp blocks per SM)
+neighbours_block_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, T r2, int64_t max_nn, int loop, int rule,
+                        const V4<T> *__restrict__ spos, const CellParam *__restrict__ cellparam,
+                        const int32_t *__restrict__ cell_start, const int32_t *__restrict__ group_ptr, int32_t *__restrict__ deg,
+                        const int64_t *__restrict__ offsets, FillOut out, int32_t *__restrict__ status) {
+    using S = BlockSmem<T, FILL>;
+    constexpr int kCap = S::kCap, kPerLane = kCap / 32;
+    extern __shared__ __align__(32) unsigned char blk_smem[];
+    const int lane = threadIdx.x;
+    V4<T> *cand = reinterpret_cast<V4<T> *>(blk_smem + S::cand);
+    unsigned short *src = reinterpret_cast<unsigned short *>(blk_smem + S::src);
+    int *s_k0 = reinterpret_cast<int *>(blk_smem + S::rows), *s_off = s_k0 + 64;
+    unsigned *mask = reinterpret_cast<unsigned *>(blk_smem + S::mask);
+    unsigned short *pref = reinterpret_cast<unsigned short *>(blk_smem + S::pref);
+    unsigned short *my_hits = reinterpret_cast<unsigned short *>(blk_smem + S::hits) + lane * kBlkListStride;
+    const unsigned short *all_hits = reinterpret_cast<const unsigned short *>(blk_smem + S::hits);
+    const unsigned full = 0xffffffffu;
+    const int G = group_ptr[B];
+    // (the output pointers as scalars: read through the parameter struct inside the nested lambdas below they end up in
+    //  local memory, and with all of the L1 given to shared memory every such read is a trip to the L2)
+    int64_t *const o_row0 = out.row0, *const o_row1 = out.row1, *const o_batch = out.mapping_batch;
+    T *const o_dist = reinterpret_cast<T *>(out.distance);
+    int32_t *const o_row0_32 = out.row0_32, *const o_row1_32 = out.row1_32;
+    RPHASE_DECL
+
+    for (int item = blockIdx.x; item < G; item += gridDim.x) {
+        RPHASE(FILL ? 0 : 10 + 0)
+        int b = 0;
+        {   // largest b with group_ptr[b] <= item: every round looks at 32 entries of the range that is left
+            int span = (int)B;
+            while (span > 1) {
+                const int step = (span + 31) >> 5, k = b + lane * step;
+                const unsigned below = __ballot_sync(full, lane * step < span && group_ptr[k] <= item);     // (lane 0 always)
+                const int last = 31 - __clz(below);
+                span = min(step, span - last * step);
+                b += last * step;
+            }
+        }
+        const CellParam cp = cellparam[b];
+        const int gx = cp.gx, gy = cp.gy, gz = cp.gz, reach = cp.reach, bx = cp.pad & 255, by = cp.pad >> 8;
+        const int64_t lo = ptr[b];
+        const int n = (int)(ptr[b + 1] - lo);
+        const int g = item - group_ptr[b];
+        const int nbx = (gx + bx - 1) / bx, nby = (gy + by - 1) / by;
+        const int cz = g / (nbx * nby), gr = g % (nbx * nby);
+        const int y0 = (gr / nbx) * by, x0 = (gr % nbx) * bx, y1 = min(y0 + by, gy), x1 = min(x0 + bx, gx);
+        const int32_t *cs = cell_start + lo + b;
+        const V4<T> *sp = spos + lo;
+
+        // ---- the centres: one run of the cell-sorted points per row of the block
+        int run_k = 0, run_len = 0;
+        if (lane < y1 - y0) {
+            const int rb = gx * (y0 + lane + gy * cz);
+            run_k = cs[rb + x0];
+            run_len = cs[rb + x1] - run_k;
+        }
+        const int nc = warp_sum(run_len);
+        if (nc == 0) continue;
+
+        // ---- the candidate runs: bounds, exclusive prefix of their lengths (two runs per lane)
+        const int ya = max(y0 - reach, 0), yb = min(y1 - 1 + reach, gy - 1), za = max(cz - reach, 0), zb = min(cz + reach, gz - 1);
+        const int ny = yb - ya + 1, nrows = ny * (zb - za + 1);
+        const int xa = max(x0 - reach, 0), xb = min(x1 - 1 + reach, gx - 1);
+        int M;
+        {
+            int k0[2] = {0, 0}, len[2] = {0, 0};
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int rw = 2 * lane + h;
+                if (rw < nrows) {
+                    const int rb = gx * (ya + rw % ny + gy * (za + rw / ny));
+                    k0[h] = cs[rb + xa];
+                    len[h] = cs[rb + xb + 1] - k0[h];
+                }
+            }
+            int incl = len[0] + len[1];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(full, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const int excl = incl - len[0] - len[1];
+            M = __shfl_sync(full, incl, 31);
+            __syncwarp();
+            if (2 * lane < nrows) { s_k0[2 * lane] = k0[0]; s_off[2 * lane] = excl; }
+            if (2 * lane + 1 < nrows) { s_k0[2 * lane + 1] = k0[1]; s_off[2 * lane + 1] = excl + len[0]; }
+            if (lane == 0) s_off[nrows] = M;
+            // where the first stage's candidates come from: every lane writes out its own two runs (src[] is free here)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int off = excl + (h ? len[0] : 0), kb = min(len[h], kCap - off);
+                for (int k = 0; k < kb; k++) src[off + k] = (unsigned short)(k0[h] + k);
+            }
+            __syncwarp();
+        }
+        const bool single = M <= kCap;
+        RPHASE(FILL ? 1 : 10 + 1)
+
+        bool first_src = true;                         // src[] still holds the sources of candidates [0, kCap)
+        // positions (in the structure's cell-sorted run) of candidates [c0, c0 + kCap) of the concatenated runs -> src[];
+        // half a warp per run
+        auto build_src = [&](int c0) {
+            const int half = lane >> 4, l16 = lane & 15;
+            for (int rw = half; rw < nrows; rw += 2) {
+                const int off = s_off[rw] - c0, len = s_off[rw + 1] - s_off[rw], k0 = s_k0[rw];
+                const int ka = max(0, -off), kb = min(len, kCap - off);
+                for (int k = ka + l16; k < kb; k += 16) src[off + k] = (unsigned short)(k0 + k);
+            }
+            __syncwarp();
+        };
+        auto pad_stage = [&](int mw) {                 // the rest of the last 32 staged entries: points that hit nothing
+            const int f = mw + lane;
+            if (f < ((mw + 31) & ~31)) cand[f] = far_point<T>();
+        };
+        // COUNT: candidates [c0, c0 + kCap) as they come, copied without passing through registers
+        auto stage_plain = [&](int c0) {
+            const int mc = min(kCap, M - c0);
+            if (c0 > 0 || !first_src) build_src(c0);
+            first_src = false;
+            const uint32_t dst0 = (uint32_t)__cvta_generic_to_shared(cand);
+#pragma unroll
+            for (int u = 0; u < kPerLane; u++) {
+                const int f = u * 32 + lane;
+                if (f < mc) {
+                    const V4<T> *from = sp + src[f];
+#pragma unroll
+                    for (int h = 0; h < (int)sizeof(V4<T>) / 16; h++)
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst0 + (uint32_t)(f * sizeof(V4<T>) + 16 * h)),
+                                     "l"(reinterpret_cast<const char *>(from) + 16 * h) : "memory");
+                }
+            }
+            pad_stage(mc);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncwarp();
+        };
+        // FILL: rank of the candidate with local index j among all candidates of the item, in ascending order of index
+        auto rank_of = [&](int j) { return (int)pref[j >> 5] + __popc(mask[j >> 5] & ((1u << (j & 31)) - 1u)); };
+        // candidates [c0, c0 + kCap) whose rank lies in [wb, wb + kCap) -> their place in the stage, eight loads at a time
+        auto scatter_chunk = [&](int mc, int wb) {
+#pragma unroll
+            for (int u0 = 0; u0 < kPerLane; u0 += 8) {
+                V4<T> p[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) p[u] = sp[src[min((u0 + u) * 32 + lane, mc - 1)]];
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    if ((u0 + u) * 32 + lane < mc) {
+                        const int rw = rank_of(idx_of(p[u])) - wb;
+                        if (rw >= 0 && rw < kCap) cand[rw] = p[u];
+                    }
+            }
+        };
+        auto stage_window = [&](int wb) {                        // (several windows only)
+            for (int c0 = 0; c0 < M; c0 += kCap) {
+                build_src(c0);
+                scatter_chunk(min(kCap, M - c0), wb);
+                __syncwarp();
+            }
+            pad_stage(min(kCap, M - wb));
+            __syncwarp();
+        };
+
+        if (FILL) {
+            // ---- mark every candidate's local index, rank the marks
+            const int nwords = (n + 31) >> 5;                    // (n <= kCapBits)
+            for (int w = lane; w < nwords; w += 32) mask[w] = 0u;
+            __syncwarp();
+            int jj[kPerLane];                                    // (local indices of the first stage's candidates, kept for the ranking)
+            for (int c0 = 0; c0 < M; c0 += kCap) {
+                const int mc = min(kCap, M - c0);
+                if (c0 > 0) build_src(c0);
+                int jc[kPerLane];
+#pragma unroll
+                for (int u = 0; u < kPerLane; u++) jc[u] = idx_of(sp[src[min(u * 32 + lane, mc - 1)]]);
+#pragma unroll
+                for (int u = 0; u < kPerLane; u++) {
+                    if (u * 32 + lane < mc) atomicOr(&mask[jc[u] >> 5], 1u << (jc[u] & 31));
+                    if (c0 == 0) jj[u] = jc[u];
+                }
+                __syncwarp();
+            }
+            RPHASE(8)
+            auto rank_marks = [&]() {
+                constexpr int kPer = kCapBits / 32 / 32;         // words per lane
+                int cnt[kPer], sum = 0;
+#pragma unroll
+                for (int q = 0; q < kPer; q++) {
+                    const int w = kPer * lane + q;
+                    cnt[q] = w < nwords ? __popc(mask[w]) : 0;
+                    sum += cnt[q];
+                }
+                int incl = sum;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(full, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                int run = incl - sum;
+#pragma unroll
+                for (int q = 0; q < kPer; q++) {
+                    const int w = kPer * lane + q;
+                    if (w < nwords) pref[w] = (unsigned short)run;
+                    run += cnt[q];
+                }
+            };
+            rank_marks();
+            __syncwarp();
+            RPHASE(9)
+            if (single) {
+                // sources in the order of the ranks (in the space of the hit lists, empty now), then the candidates themselves,
+                // copied without passing through registers, all copies in flight together
+                unsigned short *ssrc = reinterpret_cast<unsigned short *>(blk_smem + S::hits);
+#pragma unroll
+                for (int u = 0; u < kPerLane; u++)
+                    if (u * 32 + lane < M) ssrc[rank_of(jj[u])] = src[u * 32 + lane];
+                __syncwarp();
+                const uint32_t dst0 = (uint32_t)__cvta_generic_to_shared(cand);
+#pragma unroll
+                for (int u = 0; u < kPerLane; u++) {
+                    const int f = u * 32 + lane;
+                    if (f < M) {
+                        const V4<T> *from = sp + ssrc[f];
+#pragma unroll
+                        for (int h = 0; h < (int)sizeof(V4<T>) / 16; h++)
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst0 + (uint32_t)(f * sizeof(V4<T>) + 16 * h)),
+                                         "l"(reinterpret_cast<const char *>(from) + 16 * h) : "memory");
+                    }
+                }
+                pad_stage(M);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncwarp();
+            }
+        } else if (single) {
+            stage_plain(0);
+        }
+
+        RPHASE(FILL ? 2 : 10 + 2)
+        for (int cp0 = 0; cp0 < nc; cp0 += 32) {
+            // ---- this lane's centre
+            int kc = -1;
+            {
+                int q = cp0 + lane;
+                for (int rr = 0; rr < y1 - y0; rr++) {
+                    const int len = __shfl_sync(full, run_len, rr), st = __shfl_sync(full, run_k, rr);
+                    if (kc < 0 && q >= 0 && q < len) kc = st + q;
+                    q -= len;
+                }
+            }
+            const bool active = kc >= 0;
+            const V4<T> pc = sp[max(kc, 0)];
+            const int il = idx_of(pc);
+            const int64_t i = lo + il;
+            // (a lane without a centre sits at infinity: no hits)
+            const T xi = active ? pc.x : T(INFINITY), yi = active ? pc.y : T(INFINITY), zi = active ? pc.z : T(INFINITY);
+
+            RPHASE(FILL ? 3 : 10 + 3)
+            if (!FILL) {
+                int cnt = 0, cnt_lo = 0;
+                auto count_windows = [&](auto with_lo_tag) {
+                    constexpr bool kLo = decltype(with_lo_tag)::value;
+                    cnt = cnt_lo = 0;
+                    for (int wb = 0; wb < M; wb += kCap) {
+                        if (!single) stage_plain(wb);
+                        const int mw = min(kCap, M - wb), nw = (mw + 31) >> 5;
+                        for (int w = 0; w < nw; w++) {
+                            const V4<T> *cw = cand + w * 32;
+#pragma unroll 8
+                            for (int u = 0; u < 32; u++) {
+                                const V4<T> p = cw[u];
+                                const T d2 = dist2_rn(xi, yi, zi, p.x, p.y, p.z);
+                                if (d2 < r2) {
+                                    cnt++;
+                                    if (kLo) cnt_lo += idx_of(p) < il;
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    }
+                };
+                count_windows(std::false_type{});
+                RPHASE(FILL ? 4 : 10 + 4)
+                const int self_hit = dist2_rn(xi, yi, zi, xi, yi, zi) < r2 ? 1 : 0;      // (the centre is one of its candidates)
+                // hits below the centre's own index matter only where the neighbour cap bites: counted in a second walk
+                const bool over = active && (int64_t)(loop ? cnt : cnt - self_hit) > max_nn;
+                if (__any_sync(full, over)) count_windows(std::true_type{});
+                if (active) {
+                    const int64_t nlo = cnt_lo, nhi = cnt - self_hit - cnt_lo;
+                    int64_t total, k;
+                    if (loop) {
+                        total = nlo + nhi + self_hit;
+                        k = total < max_nn ? total : max_nn;
+                    } else if (rule == MLCGB_RULE_CLUSTER && self_hit) {
+                        total = nlo + nhi;
+                        if (nlo >= max_nn + 1) k = max_nn + 1;
+                        else k = total < max_nn ? total : max_nn;
+                    } else {
+                        total = nlo + nhi;
+                        k = total < max_nn ? total : max_nn;
+                    }
+                    deg[i] = (int32_t)k;
+                    if (k < total) atomicOr(status, (int)kTruncated);
+                }
+            } else {
+                int64_t base_off = 0;
+                int kept = 0, emitted = 0;
+                if (active) {
+                    base_off = offsets[i];
+                    kept = (int)(offsets[i + 1] - base_off);
+                }
+                const uint32_t list0 = (uint32_t)__cvta_generic_to_shared(my_hits);
+                uint32_t list_end = list0;                       // shared-memory address past the last entry of this lane's list
+                // the lists so far -> edges: a centre at a time, consecutive lanes on consecutive slots; the centre's own entry
+                // is dropped here (unless loops are wanted) and entries beyond the centre's count are not written
+                auto emit_lists = [&]() {
+                    __syncwarp();
+                    RPHASE(FILL ? 4 : 10 + 4)
+                    const int nh = (int)(list_end - list0) >> 1;
+                    // where the centre itself sits in its (ascending) list: that entry is skipped, unless loops are wanted
+                    int self_at = INT_MAX;
+                    if (!loop) {
+                        int lo_t = 0, hi_t = nh;
+                        while (lo_t < hi_t) {
+                            const int mid = (lo_t + hi_t) >> 1;
+                            if ((int)my_hits[mid] < il) lo_t = mid + 1; else hi_t = mid;
+                        }
+                        if (lo_t < nh && (int)my_hits[lo_t] == il) self_at = lo_t;
+                    }
+                    RPHASE(5)
+                    // all the lists as one run of edges: entry f of it belongs to the centre whose first entry is the last at or
+                    // below f; 32 consecutive entries are written at a time, whatever centres they fall into
+                    const int avail = nh - (self_at != INT_MAX ? 1 : 0), take = max(0, min(avail, kept - emitted));
+                    int incl = take;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int t = __shfl_up_sync(full, incl, o);
+                        if (lane >= o) incl += t;
+                    }
+                    const int first = incl - take, total = __shfl_sync(full, incl, 31);
+                    const int64_t slot0 = base_off + emitted;
+                    RPHASE(6)
+                    // (four rounds per trip, independent of one another: the centre look-up is a chain of five exchanges)
+                    for (int f00 = 0; f00 < total; f00 += 128)
+#pragma unroll
+                    for (int f0 = f00; f0 < f00 + 128; f0 += 32) {
+                        const int f = f0 + lane;
+                        int cc = 0;
+#pragma unroll
+                        for (int st = 16; st > 0; st >>= 1)
+                            if (__shfl_sync(full, first, cc + st) <= f) cc += st;
+                        const int t = f - __shfl_sync(full, first, cc), at = __shfl_sync(full, self_at, cc);
+                        const int64_t slot = __shfl_sync(full, slot0, cc) + t, ic = lo + __shfl_sync(full, il, cc);
+                        T cxi = T(0), cyi = T(0), czi = T(0);
+                        if (o_dist) { cxi = __shfl_sync(full, xi, cc); cyi = __shfl_sync(full, yi, cc); czi = __shfl_sync(full, zi, cc); }
+                        if (f < total) {
+                            const int64_t gj = lo + (int)all_hits[cc * kBlkListStride + t + (t >= at ? 1 : 0)];
+                            if (o_row0) { o_row0[slot] = ic; o_row1[slot] = gj; }
+                            if (o_batch) o_batch[slot] = b;
+                            if (o_dist) o_dist[slot] = sqrt(dist2_rn(cxi, cyi, czi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]));
+                            if (o_row0_32) { o_row0_32[slot] = (int32_t)ic; o_row1_32[slot] = (int32_t)gj; }
+                        }
+                    }
+                    emitted += avail;
+                    list_end = list0;
+                    __syncwarp();
+                    RPHASE(FILL ? 7 : 10 + 5)
+                };
+                for (int wb = 0; wb < M; wb += kCap) {
+                    if (!__any_sync(full, active && emitted < kept)) break;
+                    if (!single) stage_window(wb);
+                    const int mw = min(kCap, M - wb), nw = (mw + 31) >> 5;
+                    for (int w = 0; w < nw; w++) {
+                        if (__any_sync(full, list_end > list0 + 2 * (kBlkList - 32))) emit_lists();   // room for this word's hits in every list
+                        const V4<T> *cw = cand + w * 32;
+                        // (sixteen loads and distances, then their pushes: a load cannot be moved above an earlier store to
+                        //  shared memory, so interleaved they would run one test at a time)
+#pragma unroll
+                        for (int g16 = 0; g16 < 2; g16++) {
+                            T d2[16];
+                            int id[16];
+#pragma unroll
+                            for (int u = 0; u < 16; u++) {
+                                const V4<T> q = cw[g16 * 16 + u];
+                                d2[u] = dist2_rn(xi, yi, zi, q.x, q.y, q.z);
+                                id[u] = idx_of(q);
+                            }
+#pragma unroll
+                            for (int u = 0; u < 16; u++) push_if_below(d2[u], r2, list_end, id[u]);
+                        }
+                        asm volatile("" ::: "memory");           // (the pushes write shared memory behind the compiler's back)
+                    }
+                    emit_lists();
+                }
+            }
+        }
+        __syncwarp();          // the stage and its tables are rewritten by the next item
+    }
+}
+
+// FILL with the candidates of an item split between the warps of a block (kFillWarps of them): the same work item, the same
+// staged list, lane l of every warp the same centre, warp w the w-th part of the (ascending) list.  A centre's edges are then
+// warp 0's hits followed by warp 1's ...: a warp writes its own hits, after the warps before it have published how many
+// they had (named barrier w: they arrive when they are through, warp w waits before its first emission; warp 0 never
+// waits, so nobody waits in a circle).  Twice the warps per staged list hide twice the latency: the staging, the
+// emission and the pushes are chains of dependent shared-memory operations, and shared memory, not registers, is what
+// limits the blocks per SM.
+constexpr int kFillWarps = 2;
+constexpr int kFillList = 80;                              // entries of a warp's hit list of a centre between two emissions
+constexpr int kFillListStride = kFillList + 2;             // (16-bit entries: an odd number of words, see kBlkListStride)
+
+template <typename T>
+struct FillSmem {
+    static constexpr int kCap = BlockCap<T>::value;
+    static constexpr size_t cand = 0;                                          // V4<T>[kCap]: staged candidates, ascending
+    static constexpr size_t hits = cand + (size_t)kCap * sizeof(V4<T>);        // u16[kFillWarps][32][kFillListStride]
+    static constexpr size_t hits_bytes = (size_t)kFillWarps * 32 * kFillListStride * 2;
+    // while an item is staged the lists are empty and their space holds:
+    static constexpr size_t src = hits;                                        // u16[kCap]: where a chunk's candidates come from
+    static constexpr size_t ssrc = src + (size_t)kCap * 2;                     // u16[kCap]: the same in ascending order
+    static constexpr size_t mask = ssrc + (size_t)kCap * 2;                    // u32[kCapBits / 32]
+    static constexpr size_t pref = mask + kCapBits / 8;                        // u16[kCapBits / 32]
+    static_assert(pref + kCapBits / 16 <= hits + hits_bytes, "staging tables must fit the space of the hit lists");
+    static constexpr size_t rows = hits + hits_bytes;                          // int k0[64], off[65]
+    static constexpr size_t avail = rows + 544;                                // int[kFillWarps][32]: entries the warps had
+    static constexpr size_t total = (avail + (size_t)kFillWarps * 32 * 4 + 31) & ~(size_t)31;
+};
+
+static_assert(kFillWarps == 2, "the hand-over below is written for two warps: one named barrier, warp 0 arrives, warp 1 waits");
+__device__ __forceinline__ void fill_handover_wait() { asm volatile("bar.sync 1, 64;" ::: "memory"); }
+__device__ __forceinline__ void fill_handover_arrive() { asm volatile("bar.arrive 1, 64;" ::: "memory"); }
+
+template <typename T>
+__global__ void __launch_bounds__(kFillWarps * 32, 8)      // (shared memory allows nine blocks per SM; with eight nothing spills)
+neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, T r2, int loop,
+                             const V4<T> *__restrict__ spos, const CellParam *__restrict__ cellparam,
+                             const int32_t *__restrict__ cell_start, const int32_t *__restrict__ group_ptr,
+                             const int64_t *__restrict__ offsets, FillOut out) {
+    using S = FillSmem<T>;
+    constexpr int kCap = S::kCap, kPerThread = kCap / (kFillWarps * 32), kThreads = kFillWarps * 32;
+    extern __shared__ __align__(32) unsigned char blk_smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    V4<T> *cand = reinterpret_cast<V4<T> *>(blk_smem + S::cand);
+    unsigned short *src = reinterpret_cast<unsigned short *>(blk_smem + S::src);
+    unsigned short *ssrc = reinterpret_cast<unsigned short *>(blk_smem + S::ssrc);
+    unsigned *mask = reinterpret_cast<unsigned *>(blk_smem + S::mask);
+    unsigned short *pref = reinterpret_cast<unsigned short *>(blk_smem + S::pref);
+    int *s_k0 = reinterpret_cast<int *>(blk_smem + S::rows), *s_off = s_k0 + 64;
+    int *s_avail = reinterpret_cast<int *>(blk_smem + S::avail);
+    unsigned short *warp_hits = reinterpret_cast<unsigned short *>(blk_smem + S::hits) + warp * 32 * kFillListStride;
+    unsigned short *my_hits = warp_hits + lane * kFillListStride;
+    const unsigned full = 0xffffffffu;
+    const int G = group_ptr[B];
+    // (the output pointers as scalars: read through the parameter struct inside the lambdas below they end up in local
+    //  memory, and with all of the L1 given to shared memory every such read is a trip to the L2)
+    int64_t *const o_row0 = out.row0, *const o_row1 = out.row1, *const o_batch = out.mapping_batch;
+    T *const o_dist = reinterpret_cast<T *>(out.distance);
+    int32_t *const o_row0_32 = out.row0_32, *const o_row1_32 = out.row1_32;
+    RPHASE_DECL
+
+    for (int item = blockIdx.x; item < G; item += gridDim.x) {
+        RPHASE(0)
+        // ---- the work item (every warp for itself: the same loads, no exchange)
+        int b = 0;
+        {   // largest b with group_ptr[b] <= item: every round looks at 32 entries of the range that is left
+            int span = (int)B;
+            while (span > 1) {
+                const int step = (span + 31) >> 5, k = b + lane * step;
+                const unsigned below = __ballot_sync(full, lane * step < span && group_ptr[k] <= item);     // (lane 0 always)
+                const int last = 31 - __clz(below);
+                span = min(step, span - last * step);
+                b += last * step;
+            }
+        }
+        const CellParam cp = cellparam[b];
+        const int gx = cp.gx, gy = cp.gy, gz = cp.gz, reach = cp.reach, bx = cp.pad & 255, by = cp.pad >> 8;
+        const int64_t lo = ptr[b];
+        const int n = (int)(ptr[b + 1] - lo);
+        const int g = item - group_ptr[b];
+        const int nbx = (gx + bx - 1) / bx, nby = (gy + by - 1) / by;
+        const int cz = g / (nbx * nby), gr = g % (nbx * nby);
+        const int y0 = (gr / nbx) * by, x0 = (gr % nbx) * bx, y1 = min(y0 + by, gy), x1 = min(x0 + bx, gx);
+        const int32_t *cs = cell_start + lo + b;
+        const V4<T> *sp = spos + lo;
+        int run_k = 0, run_len = 0;                          // the centres: one run of the cell-sorted points per row of the block
+        if (lane < y1 - y0) {
+            const int rb = gx * (y0 + lane + gy * cz);
+            run_k = cs[rb + x0];
+            run_len = cs[rb + x1] - run_k;
+        }
+        const int nc = warp_sum(run_len);
+        if (nc == 0) continue;                               // (the same in every warp)
+        const int ya = max(y0 - reach, 0), yb = min(y1 - 1 + reach, gy - 1), za = max(cz - reach, 0), zb = min(cz + reach, gz - 1);
+        const int ny = yb - ya + 1, nrows = ny * (zb - za + 1);
+        const int xa = max(x0 - reach, 0), xb = min(x1 - 1 + reach, gx - 1);
+        int M;
+        {   // the candidate runs, two per lane: bounds, exclusive prefix of the lengths; warp w writes out run 2 lane + w
+            int k0[2] = {0, 0}, len[2] = {0, 0};
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int rw = 2 * lane + h;
+                if (rw < nrows) {
+                    const int rb = gx * (ya + rw % ny + gy * (za + rw / ny));
+                    k0[h] = cs[rb + xa];
+                    len[h] = cs[rb + xb + 1] - k0[h];
+                }
+            }
+            int incl = len[0] + len[1];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(full, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const int excl = incl - len[0] - len[1];
+            M = __shfl_sync(full, incl, 31);
+            const int h = warp & 1, off = excl + (h ? len[0] : 0);
+            if (warp < 2) {
+                if (2 * lane + h < nrows) { s_k0[2 * lane + h] = k0[h]; s_off[2 * lane + h] = off; }
+                if (tid == 0) s_off[nrows] = M;
+                const int kb = min(len[h], kCap - off);
+                for (int k = 0; k < kb; k++) src[off + k] = (unsigned short)(k0[h] + k);
+            }
+        }
+        __syncthreads();
+        RPHASE(1)
+        const bool single = M <= kCap;
+        bool src_fresh = true;                               // src[] holds the sources of candidates [0, kCap)
+
+        auto build_src = [&](int c0) {                       // sources of candidates [c0, c0 + kCap) of the concatenated runs
+            const int half = tid >> 4, l16 = tid & 15;
+            for (int rw = half; rw < nrows; rw += kThreads / 16) {
+                const int off = s_off[rw] - c0, len = s_off[rw + 1] - s_off[rw], k0 = s_k0[rw];
+                const int ka = max(0, -off), kb = min(len, kCap - off);
+                for (int k = ka + l16; k < kb; k += 16) src[off + k] = (unsigned short)(k0 + k);
+            }
+            __syncthreads();
+        };
+        auto rank_of = [&](int j) { return (int)pref[j >> 5] + __popc(mask[j >> 5] & ((1u << (j & 31)) - 1u)); };
+        // candidates of ranks [wb, wb + kCap) -> the stage, ascending (the lists are empty: their space holds the tables)
+        auto stage = [&](int wb) {
+            const int nwords = (n + 31) >> 5;                // (n <= kCapBits)
+            for (int w = tid; w < nwords; w += kThreads) mask[w] = 0u;
+            __syncthreads();
+            int jj[kPerThread];                              // local indices of this thread's candidates (single chunk)
+            for (int c0 = 0; c0 < M; c0 += kCap) {
+                const int mc = min(kCap, M - c0);
+                if (c0 > 0 || !src_fresh) build_src(c0);
+                src_fresh = false;
+#pragma unroll
+                for (int u = 0; u < kPerThread; u++) jj[u] = idx_of(sp[src[min(u * kThreads + tid, mc - 1)]]);
+#pragma unroll
+                for (int u = 0; u < kPerThread; u++)
+                    if (u * kThreads + tid < mc) atomicOr(&mask[jj[u] >> 5], 1u << (jj[u] & 31));
+                __syncthreads();
+            }
+            if (warp == 0) {
+                constexpr int kPer = kCapBits / 32 / 32;     // words per lane
+                int cnt[kPer], sum = 0;
+#pragma unroll
+                for (int q = 0; q < kPer; q++) {
+                    const int w = kPer * lane + q;
+                    cnt[q] = w < nwords ? __popc(mask[w]) : 0;
+                    sum += cnt[q];
+                }
+                int incl = sum;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(full, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                int run = incl - sum;
+#pragma unroll
+                for (int q = 0; q < kPer; q++) {
+                    const int w = kPer * lane + q;
+                    if (w < nwords) pref[w] = (unsigned short)run;
+                    run += cnt[q];
+                }
+            }
+            __syncthreads();
+            const int mw = min(kCap, M - wb);
+            const uint32_t dst0 = (uint32_t)__cvta_generic_to_shared(cand);
+            auto copy_sorted = [&](int count) {              // cand[f] <- the point ssrc[f] names, f < count: asynchronous copies
+#pragma unroll
+                for (int u = 0; u < kPerThread; u++) {
+                    const int f = u * kThreads + tid;
+                    if (f < count) {
+                        const V4<T> *from = sp + ssrc[f];
+#pragma unroll
+                        for (int h = 0; h < (int)sizeof(V4<T>) / 16; h++)
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst0 + (uint32_t)(f * sizeof(V4<T>) + 16 * h)),
+                                         "l"(reinterpret_cast<const char *>(from) + 16 * h) : "memory");
+                    }
+                }
+            };
+            if (single) {
+#pragma unroll
+                for (int u = 0; u < kPerThread; u++)
+                    if (u * kThreads + tid < M) ssrc[rank_of(jj[u])] = src[u * kThreads + tid];
+                __syncthreads();
+                copy_sorted(M);
+            } else {
+                // (several chunks: a chunk's sources that fall into the window go to their place in ssrc, chunk after chunk)
+                for (int c0 = 0; c0 < M; c0 += kCap) {
+                    const int mc = min(kCap, M - c0);
+                    build_src(c0);
+#pragma unroll
+                    for (int u = 0; u < kPerThread; u++) jj[u] = idx_of(sp[src[min(u * kThreads + tid, mc - 1)]]);
+#pragma unroll
+                    for (int u = 0; u < kPerThread; u++)
+                        if (u * kThreads + tid < mc) {
+                            const int rw = rank_of(jj[u]) - wb;
+                            if (rw >= 0 && rw < kCap) ssrc[rw] = src[u * kThreads + tid];
+                        }
+                    __syncthreads();
+                }
+                copy_sorted(mw);
+            }
+            {   // the rest of the last 32 staged entries: points that hit nothing
+                const int f = mw + tid;
+                if (f < ((mw + 31) & ~31)) cand[f] = far_point<T>();
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+        };
+        if (single) stage(0);
+        RPHASE(2)
+
+        for (int cp0 = 0; cp0 < nc; cp0 += 32) {
+            // ---- this lane's centre (the same in every warp)
+            int kc = -1;
+            {
+                int q = cp0 + lane;
+                for (int rr = 0; rr < y1 - y0; rr++) {
+                    const int len = __shfl_sync(full, run_len, rr), st = __shfl_sync(full, run_k, rr);
+                    if (kc < 0 && q >= 0 && q < len) kc = st + q;
+                    q -= len;
+                }
+            }
+            const bool active = kc >= 0;
+            const V4<T> pc = sp[max(kc, 0)];
+            const int il = idx_of(pc);
+            // (a lane without a centre sits at infinity: no hits)
+            const T xi = active ? pc.x : T(INFINITY), yi = active ? pc.y : T(INFINITY), zi = active ? pc.z : T(INFINITY);
+            int64_t base_off = 0;
+            int kept = 0, emitted = 0;                       // emitted: entries (other than the centre itself) gone by so far
+            if (active) {
+                base_off = offsets[lo + il];
+                kept = (int)(offsets[lo + il + 1] - base_off);
+            }
+            const uint32_t list0 = (uint32_t)__cvta_generic_to_shared(my_hits);
+            RPHASE(3)
+
+            for (int wb = 0; wb < M; wb += kCap) {
+                if (!__any_sync(full, active && emitted < kept)) break;      // (the same in every warp)
+                if (!single) stage(wb);
+                const int mw = min(kCap, M - wb), nw = (mw + 31) >> 5, nwh = (nw + kFillWarps - 1) / kFillWarps;
+                const int w_lo = min(warp * nwh, nw), w_hi = min(w_lo + nwh, nw);
+                uint32_t list_end = list0;                   // shared-memory address past the last entry of this lane's list
+                int flushed = 0;                             // entries of this window this warp has dealt with, for this lane's centre
+                bool waited = warp == 0;
+                // this warp's lists so far -> edges, a centre at a time, consecutive lanes on consecutive slots; the centre's
+                // own entry is skipped (unless loops are wanted), entries beyond the centre's count are not written
+                auto emit_lists = [&](bool last) {
+                    __syncwarp();
+                    RPHASE(4)
+                    const int nh = (int)(list_end - list0) >> 1;
+                    int self_at = INT_MAX;                   // where the centre itself sits in its (ascending) list
+                    if (!loop) {
+                        int lo_t = 0, hi_t = nh;
+                        while (lo_t < hi_t) {
+                            const int mid = (lo_t + hi_t) >> 1;
+                            if ((int)my_hits[mid] < il) lo_t = mid + 1; else hi_t = mid;
+                        }
+                        if (lo_t < nh && (int)my_hits[lo_t] == il) self_at = lo_t;
+                    }
+                    const int avail = nh - (self_at != INT_MAX ? 1 : 0);
+                    if (last) {                              // this warp's count of the window is final: the next warp may go ahead
+                        s_avail[warp * 32 + lane] = flushed + avail;
+                        __threadfence_block();
+                        if (warp == 0) fill_handover_arrive();
+                    }
+                    if (!waited) {                           // the warps before this one are through: their counts are there
+                        fill_handover_wait();
+                        waited = true;
+                    }
+                    int start = emitted + flushed;
+                    for (int w2 = 0; w2 < warp; w2++) start += s_avail[w2 * 32 + lane];
+                    const int take = max(0, min(avail, kept - start));
+                    const int64_t slot0 = base_off + start;
+                    RPHASE(5)
+                    for (int cc = 0; cc < 32; cc++) {
+                        const int tk = __shfl_sync(full, take, cc);
+                        if (tk <= 0) continue;
+                        const int at = __shfl_sync(full, self_at, cc);
+                        const int64_t slot_c = __shfl_sync(full, slot0, cc), ic = lo + __shfl_sync(full, il, cc);
+                        T cxi = T(0), cyi = T(0), czi = T(0);
+                        if (o_dist) { cxi = __shfl_sync(full, xi, cc); cyi = __shfl_sync(full, yi, cc); czi = __shfl_sync(full, zi, cc); }
+                        const unsigned short *hl = warp_hits + cc * kFillListStride;
+                        for (int t = lane; t < tk; t += 32) {
+                            const int64_t gj = lo + (int)hl[t + (t >= at ? 1 : 0)], slot = slot_c + t;
+                            if (o_row0) { o_row0[slot] = ic; o_row1[slot] = gj; }
+                            if (o_batch) o_batch[slot] = b;
+                            if (o_dist) o_dist[slot] = sqrt(dist2_rn(cxi, cyi, czi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]));
+                            if (o_row0_32) { o_row0_32[slot] = (int32_t)ic; o_row1_32[slot] = (int32_t)gj; }
+                        }
+                    }
+                    flushed += avail;
+                    list_end = list0;
+                    __syncwarp();
+                    RPHASE(6)
+                };
+                for (int w = w_lo; w < w_hi; w++) {
+                    if (__any_sync(full, list_end > list0 + 2 * (kFillList - 32))) emit_lists(false);   // room for this word's hits in every list
+                    const V4<T> *cw = cand + w * 32;
+                    // (eight loads and distances, then their pushes: a load cannot be moved above an earlier store to
+                    //  shared memory, so interleaved they would run one test at a time)
+#pragma unroll
+                    for (int g8 = 0; g8 < 4; g8++) {
+                        T d2[8];
+                        int id[8];
+#pragma unroll
+                        for (int u = 0; u < 8; u++) {
+                            const V4<T> q = cw[g8 * 8 + u];
+                            d2[u] = dist2_rn(xi, yi, zi, q.x, q.y, q.z);
+                            id[u] = idx_of(q);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 8; u++) push_if_below(d2[u], r2, list_end, id[u]);
+                    }
+                    asm volatile("" ::: "memory");           // (the pushes write shared memory behind the compiler's back)
+                }
+                emit_lists(true);
+                __syncthreads();                             // everybody's counts of the window are there
+#pragma unroll
+                for (int w2 = 0; w2 < kFillWarps; w2++) emitted += s_avail[w2 * 32 + lane];
+                __syncthreads();                             // before the counts, the lists and the stage are written again
+            }
+        }
+    }
+}
+
+template <typename T>
+static int fill_kernel_grid(int *grid) {
+    static std::atomic<int> cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MLCGB_E_LAUNCH;
+    int per_sm = cached[dev].load(std::memory_order_relaxed);
+    if (per_sm == 0) {
+        const size_t bytes = FillSmem<T>::total;
+        if (cudaFuncSetAttribute(neighbours_block_fill_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess ||
+            cudaFuncSetAttribute(neighbours_block_fill_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, 100) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, neighbours_block_fill_kernel<T>, kFillWarps * 32, bytes) != cudaSuccess)
+            return check_launch();
+        if (per_sm < 1) per_sm = 1;
+        cached[dev].store(per_sm, std::memory_order_relaxed);
+    }
+    *grid = kNumSM * per_sm;
+    return MLCGB_OK;
+}
+
+template <typename T, bool FILL>
+static int block_kernel_grid(int *grid) {
+    // resident CTAs per SM, asked once per device and kernel
+    static std::atomic<int> cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MLCGB_E_LAUNCH;
+    int per_sm = cached[dev].load(std::memory_order_relaxed);
+    if (per_sm == 0) {
+        const size_t bytes = BlockSmem<T, FILL>::total;
+        if (cudaFuncSetAttribute(neighbours_block_kernel<T, FILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess ||
+            cudaFuncSetAttribute(neighbours_block_kernel<T, FILL>, cudaFuncAttributePreferredSharedMemoryCarveout, 100) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, neighbours_block_kernel<T, FILL>, 32, bytes) != cudaSuccess)
+            return check_launch();
+        if (per_sm < 1) per_sm = 1;
+        cached[dev].store(per_sm, std::memory_order_relaxed);
+    }
+    *grid = kNumSM * per_sm;
+    return MLCGB_OK;
+}
+
 #ifdef MLCGB_PHASE_TIMING
 extern "C" int mlcgb_debug_radius_phase_cycles(unsigned long long *out, int n, int reset) {
     unsigned long long host[16];
@@ -1064,31 +1922,38 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
         if (e != cudaSuccess) return check_launch();
         configured[dev][variant] = true;
     }
-    const int tile_grid = kNumSM * (fill ? 2 : 4);     // (blocks resident per SM: registers allow two of the fill kernel)
+    const int32_t *n_plain = tiles ? group_ptr + B + 1 : nullptr;
     if (!fill) {
         build_cells_kernel<T><<<grid_for(B, 1, 8), kBuildThreads, 0, st>>>(pos, ptr, B, (T)r, tiles ? 1 : 0, spos, cellparam, cell_of, cell_start, struct_of);
         if (tiles) {
             group_scan_kernel<<<1, kScanBlock, 0, st>>>(cellparam, B, group_ptr);
-            neighbours_tile_kernel<T, false><<<tile_grid, kTileThreads, tile_smem_bytes<T, false>(), st>>>(
-                pos, ptr, B, r2, max_nn, loop, rule, spos, cellparam, cell_of, cell_start, group_ptr, deg, nullptr, out, status);
+            int grid = 0;
+            const int rc = block_kernel_grid<T, false>(&grid);
+            if (rc != MLCGB_OK) return rc;
+            neighbours_block_kernel<T, false><<<grid, 32, BlockSmem<T, false>::total, st>>>(
+                pos, ptr, B, r2, max_nn, loop, rule, spos, cellparam, cell_start, group_ptr, deg, nullptr, out, status);
         }
         if (ex.ptr)
             neighbours_kernel<T, false, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
-                                                                                   cell_of, cell_start, struct_of, deg, nullptr, out, ex, status);
+                                                                                   cell_of, cell_start, struct_of, deg, nullptr, out, ex, status, n_plain);
         else
             neighbours_kernel<T, false, false><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
-                                                                                    cell_of, cell_start, struct_of, deg, nullptr, out, ex, status);
+                                                                                    cell_of, cell_start, struct_of, deg, nullptr, out, ex, status, n_plain);
         launch_scan(deg, N, bsum, offsets, st);
     } else {
-        if (tiles)
-            neighbours_tile_kernel<T, true><<<tile_grid, kTileThreads, tile_smem_bytes<T, true>(), st>>>(
-                pos, ptr, B, r2, 0, loop, 0, spos, cellparam, cell_of, cell_start, group_ptr, nullptr, offsets, out, status);
+        if (tiles) {
+            int grid = 0;
+            const int rc = fill_kernel_grid<T>(&grid);
+            if (rc != MLCGB_OK) return rc;
+            neighbours_block_fill_kernel<T><<<grid, kFillWarps * 32, FillSmem<T>::total, st>>>(
+                pos, ptr, B, r2, loop, spos, cellparam, cell_start, group_ptr, offsets, out);
+        }
         if (ex.ptr)
             neighbours_kernel<T, true, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
-                                                                                  cell_of, cell_start, struct_of, nullptr, offsets, out, ex, status);
+                                                                                  cell_of, cell_start, struct_of, nullptr, offsets, out, ex, status, n_plain);
         else
             neighbours_kernel<T, true, false><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
-                                                                                   cell_of, cell_start, struct_of, nullptr, offsets, out, ex, status);
+                                                                                   cell_of, cell_start, struct_of, nullptr, offsets, out, ex, status, n_plain);
     }
     return check_launch();
 }
