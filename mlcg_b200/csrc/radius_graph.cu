@@ -6,16 +6,17 @@
 //
 // Plan:  build_cells (one CTA per large structure: bounding box, cell grid with cells of half the cutoff
 //        where the structure has points enough, counting sort of the points by cell, all counters in
-//        shared memory)
-//     -> neighbours_tile<COUNT> for structures of up to 8192 points with a cell grid: a block takes
-//        four neighbouring rows of cells of one layer, stages the points of every row within reach in
-//        shared memory once, and eight threads per centre walk the centre's runs of candidates there;
+//        shared memory; the size of the blocks of cells the block kernels work on)
+//     -> neighbours_block_count for structures of up to 8192 points with a cell grid: a warp takes a
+//        block of cells of one layer (about 21 centres), stages every point within reach of the block
+//        in shared memory once, and each lane tests its centre against the whole staged list;
 //        neighbours<COUNT> for the rest (one warp per centre over the rows of cells within reach, each
 //        row a contiguous run of cell-sorted points; small structures scan all their points instead)
 //     -> exclusive scan of the degrees (three small kernels, no spin-waits)
-//     -> [host reads E] -> the same two kernels as FILL (same walk; hits are marked in a bitmask in
-//        shared memory indexed by local point index, per centre, then emitted in ascending order,
-//        which gives the canonical order without a sort).
+//     -> [host reads E] -> neighbours_block_fill (the same blocks, two warps each; the candidates staged
+//        in ascending order of their index, so that a lane's hits come out in the order the edges are
+//        listed in, without a sort) and neighbours<FILL> (hits are marked in a bitmask in shared memory
+//        indexed by local point index, per centre, then emitted in ascending order).
 #include "common.cuh"
 
 #include <atomic>
@@ -44,18 +45,9 @@ constexpr int kBuildThreads = 512;
 constexpr int kScanBlock = 1024;
 
 // Cell grid of one structure.  reach: cells to either side that can hold a neighbour (1: cell edge >= cutoff, 2: >= half
-// of it); tile: handled by the tile kernels (ngroups work items: layers x groups of kTileRY rows), else by the warp kernels.
+// of it); tile: handled by the block kernels (ngroups work items: blocks of bx x by cells, pad = bx | by << 8, in every
+// layer), else by the warp kernels.
 struct CellParam { int gx, gy, gz, use_cells, reach, tile, ngroups, pad; };
-
-constexpr int kTileCentres = 64;                          // centres per pass of a block (fewer when the masks of that many do not fit)
-constexpr int kTileTPC = 8;                               // threads per centre
-constexpr int kTileThreads = kTileCentres * kTileTPC;
-constexpr int kTileRY = 4;                                // rows of cells (along y) per work item
-constexpr int kTileMaxRows = (kTileRY + 4) * 5;           // candidate rows of a work item at reach 2
-constexpr int kTileRowsPerThread = (25 + kTileTPC - 1) / kTileTPC;
-constexpr int kTileCand = 2048;                           // candidate points staged per work item (read from global memory beyond that)
-constexpr int kTileMaskWords = 8192;                      // hit masks of one pass (FILL): centres x ceil(n / 32) words
-constexpr int kTileList = 256;                            // compacted bit positions of one emission round, per warp (FILL)
 
 constexpr int kBlkMaxBY = 8;                               // block kernels: rows of cells in a block, at most
 constexpr int kBlkTargetCentres = 21;                      // mean number of centres per block the block's size aims at
@@ -294,7 +286,7 @@ neighbours_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, in
         const int il = (int)(i - lo);
         const int64_t ex0 = EXCL ? ex.ptr[i] : 0, ex1 = EXCL ? ex.ptr[i + 1] : 0;   // this centre's excluded neighbours
         const CellParam cp = cellparam[b];
-        if (cp.tile) continue;                       // this structure's centres belong to the tile kernel
+        if (cp.tile) continue;                       // this structure's centres belong to the block kernels
         const T xi = pos[i * 3], yi = pos[i * 3 + 1], zi = pos[i * 3 + 2];
 
         int64_t kept = 0, base_off = 0;
@@ -527,7 +519,7 @@ static void launch_scan(const int32_t *deg, int64_t N, int64_t *bsum, int64_t *o
     scan_apply_kernel<<<(unsigned)nb, kScanBlock, 0, st>>>(deg, N, bsum, offsets);
 }
 
-// ------------------------------------------------------------------------------------- tile kernels
+// ---------------------------------------------------------------------------- work items of the block kernels
 // group_ptr[b] = work items of the structures before b (exclusive scan of CellParam::ngroups), group_ptr[B] = all of them,
 // group_ptr[B + 1] = structures that have no work items (left to the warp kernels)
 __global__ void __launch_bounds__(kScanBlock) group_scan_kernel(const CellParam *__restrict__ cellparam, int64_t B, int32_t *__restrict__ group_ptr) {
@@ -549,277 +541,6 @@ __global__ void __launch_bounds__(kScanBlock) group_scan_kernel(const CellParam 
     }
 }
 
-// One work item = the centres of up to kTileRY neighbouring rows of cells (along y) of one layer (z) of one structure: a
-// contiguous run of the cell-sorted points.  Their candidates lie in the rows within `reach` of those, (kTileRY + 2 reach)
-// x (2 reach + 1) whole rows of cells, each a contiguous run as well: staged in shared memory once per item (read straight
-// from global memory when they do not fit).  Eight threads share a centre and split its (2 reach + 1)^2 rows; inside a row a
-// centre tests the cells within `reach` of its own along x.  COUNT: hits below / above the centre's own index, summed over
-// the eight threads, give the degree under the neighbour-cap rule.  FILL: hits set bits in the centre's mask over the
-// structure's local indices; a warp per centre then walks the mask and writes the edges in ascending order.
-template <typename T, bool FILL>
-__global__ void __launch_bounds__(kTileThreads)
-neighbours_tile_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, T r2, int64_t max_nn, int loop, int rule,
-                       const V4<T> *__restrict__ spos, const CellParam *__restrict__ cellparam, const int32_t *__restrict__ cell_of,
-                       const int32_t *__restrict__ cell_start, const int32_t *__restrict__ group_ptr, int32_t *__restrict__ deg,
-                       const int64_t *__restrict__ offsets, FillOut out, int32_t *__restrict__ status) {
-    extern __shared__ __align__(16) unsigned char tile_smem[];
-    V4<T> *cand = reinterpret_cast<V4<T> *>(tile_smem);
-    unsigned *mask = reinterpret_cast<unsigned *>(tile_smem + (size_t)kTileCand * sizeof(V4<T>));     // FILL: [centres of a pass][nwords]
-    unsigned short *lists = reinterpret_cast<unsigned short *>(mask + kTileMaskWords);                  // FILL: [warps][kTileList]
-    __shared__ int s_k0[kTileMaxRows], s_off[kTileMaxRows + 1];
-    __shared__ int64_t s_base[FILL ? kTileCentres : 1], s_kept[FILL ? kTileCentres : 1];
-    __shared__ int s_il[FILL ? kTileCentres : 1];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int c = tid / kTileTPC, sub = tid % kTileTPC;
-    const int G = group_ptr[B];
-    RPHASE_DECL
-
-    for (int item = blockIdx.x; item < G; item += gridDim.x) {
-        RPHASE(0)
-        int b;
-        {   // largest b with group_ptr[b] <= item
-            int lo_b = 0, hi_b = (int)B;
-            while (hi_b - lo_b > 1) {
-                const int mid = (lo_b + hi_b) >> 1;
-                if (group_ptr[mid] <= item) lo_b = mid; else hi_b = mid;
-            }
-            b = lo_b;
-        }
-        const CellParam cp = cellparam[b];
-        const int gx = cp.gx, gy = cp.gy, gz = cp.gz, reach = cp.reach, side = 2 * reach + 1;
-        const int64_t lo = ptr[b];
-        const int n = (int)(ptr[b + 1] - lo);
-        const int g = item - group_ptr[b];
-        const int ngy = (gy + kTileRY - 1) / kTileRY;
-        const int cz = g / ngy, cy0 = (g % ngy) * kTileRY, cy1 = min(cy0 + kTileRY, gy);
-        const int32_t *cs = cell_start + lo + b;
-        const V4<T> *sp = spos + lo;
-        const int ylo = cy0 - reach, zlo = cz - reach, YW = (cy1 - cy0) + 2 * reach, nrows = YW * side;
-        // ---- candidate rows: bounds, shared-memory offsets, copy
-        RPHASE(1)
-        if (tid < nrows) {
-            const int yy = ylo + tid % YW, zz = zlo + tid / YW;
-            int k0 = 0, k1 = 0;
-            if (yy >= 0 && yy < gy && zz >= 0 && zz < gz) {
-                k0 = cs[gx * (yy + gy * zz)];
-                k1 = cs[gx * (yy + gy * zz) + gx];
-            }
-            s_k0[tid] = k0;
-            s_off[tid + 1] = k1 - k0;
-        }
-        __syncthreads();
-        if (warp == 0) {                 // exclusive prefix of the row lengths (at most 40 rows: two per lane)
-            const int a = 2 * lane < nrows ? s_off[2 * lane + 1] : 0, bb = 2 * lane + 1 < nrows ? s_off[2 * lane + 2] : 0;
-            int incl = a + bb;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += t;
-            }
-            const int excl = incl - a - bb;
-            __syncwarp();
-            if (lane == 0) s_off[0] = 0;
-            if (2 * lane < nrows) s_off[2 * lane + 1] = excl + a;
-            if (2 * lane + 1 < nrows) s_off[2 * lane + 2] = excl + a + bb;
-        }
-        __syncthreads();
-        RPHASE(2)
-        const bool staged = s_off[nrows] <= kTileCand;
-        if (staged) {
-            for (int rw = warp; rw < nrows; rw += kTileThreads / 32) {
-                const int k0 = s_k0[rw], off = s_off[rw], len = s_off[rw + 1] - off;
-                for (int k = lane; k < len; k += 32) cand[off + k] = sp[k0 + k];
-            }
-        }
-        const int c_begin = cs[gx * (cy0 + gy * cz)], c_end = cs[gx * (cy1 - 1 + gy * cz) + gx];
-        const int nwords = (n + 31) >> 5;
-        const int per_pass = FILL ? min(kTileCentres, kTileMaskWords / nwords) : kTileCentres;       // (n <= 8192: at least 32)
-        __syncthreads();
-        RPHASE(3)
-
-        for (int cbase = c_begin; cbase < c_end; cbase += per_pass) {
-            const int ncent = min(per_pass, c_end - cbase);
-            if (FILL) {
-                for (int w = tid; w < ncent * nwords; w += kTileThreads) mask[w] = 0u;
-                __syncthreads();
-            }
-            RPHASE(4)
-            const bool active = c < ncent;
-            int il = 0, cnt_lo = 0, cnt_hi = 0;
-            int64_t i = 0;
-            T xi = T(0), yi = T(0), zi = T(0);
-            if (active) {
-                const V4<T> pc = sp[cbase + c];
-                il = idx_of(pc);
-                i = lo + il;
-                xi = pc.x; yi = pc.y; zi = pc.z;
-                const int cell = cell_of[i];
-                const int cx = cell % gx, cy = (cell / gx) % gy;
-                const int xa = max(cx - reach, 0), xb = min(cx + reach, gx - 1);
-                if (FILL && sub == 0) {
-                    const int64_t o0 = offsets[i];
-                    s_base[c] = o0;
-                    s_kept[c] = offsets[i + 1] - o0;
-                    s_il[c] = il;
-                }
-                const uint32_t cmask = (uint32_t)__cvta_generic_to_shared(mask + (size_t)c * nwords);   // (FILL only)
-                // the bounds of all of this thread's rows first (their loads are in flight together), then the walks
-                int ka[kTileRowsPerThread], kb[kTileRowsPerThread], shift[kTileRowsPerThread];
-#pragma unroll
-                for (int m = 0; m < kTileRowsPerThread; m++) {
-                    const int rr = sub + m * kTileTPC;
-                    const int yy = cy + rr % side - reach, zz = cz + rr / side - reach;
-                    ka[m] = kb[m] = shift[m] = 0;
-                    if (rr < side * side && yy >= 0 && yy < gy && zz >= 0 && zz < gz) {
-                        const int rowbase = gx * (yy + gy * zz);
-                        ka[m] = cs[rowbase + xa];
-                        kb[m] = cs[rowbase + xb + 1];
-                        const int rw = (yy - ylo) + YW * (zz - zlo);
-                        shift[m] = s_off[rw] - s_k0[rw];      // position in the cell-sorted run -> position in the staged copy
-                    }
-                }
-                // four candidates per step, their loads and distance chains independent of one another
-                auto walk = [&](const V4<T> *base, bool shifted) {
-#pragma unroll
-                    for (int m = 0; m < kTileRowsPerThread; m++) {
-                        const V4<T> *q = shifted ? base + shift[m] : base;
-                        const int k1 = kb[m];
-                        for (int k = ka[m]; k < k1; k += 4) {
-                            V4<T> p[4];
-#pragma unroll
-                            for (int u = 0; u < 4; u++) p[u] = q[min(k + u, k1 - 1)];
-#pragma unroll
-                            for (int u = 0; u < 4; u++) {
-                                const T d2 = dist2_rn(xi, yi, zi, p[u].x, p[u].y, p[u].z);
-                                if (k + u < k1 && d2 < r2) {
-                                    const int j = idx_of(p[u]);
-                                    if (FILL) {
-                                        if (loop || j != il)
-                                            asm volatile("red.shared.or.b32 [%0], %1;" ::"r"(cmask + (uint32_t)((j >> 5) << 2)), "r"(1u << (j & 31)) : "memory");
-                                    } else {
-                                        cnt_lo += (j < il);
-                                        cnt_hi += (j > il);
-                                    }
-                                }
-                            }
-                        }
-                    }
-                };
-                if (staged) walk(cand, true);
-                else walk(sp, false);
-            }
-            RPHASE(5)
-            if (!FILL) {
-#pragma unroll
-                for (int o = 1; o < kTileTPC; o <<= 1) {
-                    cnt_lo += __shfl_xor_sync(0xffffffffu, cnt_lo, o);
-                    cnt_hi += __shfl_xor_sync(0xffffffffu, cnt_hi, o);
-                }
-                if (active && sub == 0) {
-                    const int64_t nlo = cnt_lo, nhi = cnt_hi;
-                    const int self_hit = dist2_rn(xi, yi, zi, xi, yi, zi) < r2 ? 1 : 0;
-                    int64_t total, k;
-                    if (loop) {
-                        total = nlo + nhi + self_hit;
-                        k = total < max_nn ? total : max_nn;
-                    } else if (rule == MLCGB_RULE_CLUSTER && self_hit) {
-                        total = nlo + nhi;
-                        if (nlo >= max_nn + 1) k = max_nn + 1;
-                        else k = total < max_nn ? total : max_nn;
-                    } else {
-                        total = nlo + nhi;
-                        k = total < max_nn ? total : max_nn;
-                    }
-                    deg[i] = (int32_t)k;
-                    if (k < total) atomicOr(status, (int)kTruncated);
-                }
-            } else {
-                __syncthreads();
-                RPHASE(6)
-                // ---- emission: a warp per centre walks the mask, 32 words at a time: the set bits of a chunk are compacted
-                //      into a list, then written with consecutive lanes on consecutive slots
-                unsigned short *list = lists + warp * kTileList;
-                const unsigned lt = lanemask_lt();
-                for (int cc = warp; cc < ncent; cc += kTileThreads / 32) {
-                    const int64_t kept = s_kept[cc], base_off = s_base[cc];
-                    if (kept == 0) continue;
-                    const int64_t ic = lo + s_il[cc];
-                    T cxi = T(0), cyi = T(0), czi = T(0);
-                    if (out.distance) { cxi = pos[ic * 3]; cyi = pos[ic * 3 + 1]; czi = pos[ic * 3 + 2]; }
-                    const unsigned *cm = mask + (size_t)cc * nwords;
-                    int64_t emitted = 0;
-                    // four consecutive mask words per lane: 4096 local indices per round (a round whose bits would overflow the
-                    // list is redone word by word below)
-                    for (int w0 = 0; w0 < nwords && emitted < kept; w0 += 128) {
-                        unsigned bits[4];
-                        int cbits = 0;
-#pragma unroll
-                        for (int u = 0; u < 4; u++) {
-                            const int w = w0 + 4 * lane + u;
-                            bits[u] = w < nwords ? cm[w] : 0u;
-                            cbits += __popc(bits[u]);
-                        }
-                        int incl = cbits;
-#pragma unroll
-                        for (int o = 1; o < 32; o <<= 1) {
-                            const int t = __shfl_up_sync(0xffffffffu, incl, o);
-                            if (lane >= o) incl += t;
-                        }
-                        const int total = __shfl_sync(0xffffffffu, incl, 31);
-                        if (total > kTileList) {
-                            // (more neighbours within these 4096 consecutive indices than the list takes: word by word, lane L
-                            // looking at bit L of the word, which keeps the order and needs no list)
-                            for (int ww = w0; ww < min(w0 + 128, nwords) && emitted < kept; ww++) {
-                                const unsigned word = cm[ww];
-                                const int64_t rank = emitted + __popc(word & lt);
-                                if (((word >> lane) & 1u) && rank < kept) {
-                                    const int j = (ww << 5) + lane;
-                                    T d2 = T(0);
-                                    if (out.distance) {
-                                        const int64_t gj = lo + j;
-                                        d2 = dist2_rn(cxi, cyi, czi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]);
-                                    }
-                                    emit_edge<T>(out, base_off + rank, ic, lo + j, b, d2);
-                                }
-                                emitted += __popc(word);
-                            }
-                            continue;
-                        }
-                        int pos_in = incl - cbits;
-#pragma unroll
-                        for (int u = 0; u < 4; u++) {
-                            unsigned bw = bits[u];
-                            while (bw) {
-                                const int t = __ffs(bw) - 1;
-                                bw &= bw - 1;
-                                list[pos_in++] = (unsigned short)(((4 * lane + u) << 5) + t);
-                            }
-                        }
-                        __syncwarp();
-                        const int64_t room = kept - emitted;
-                        const int take = (int64_t)total < room ? total : (int)room;
-                        for (int t = lane; t < take; t += 32) {
-                            const int j = (w0 << 5) + (int)list[t];
-                            T d2 = T(0);
-                            if (out.distance) {
-                                const int64_t gj = lo + j;
-                                d2 = dist2_rn(cxi, cyi, czi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]);
-                            }
-                            emit_edge<T>(out, base_off + emitted + t, ic, lo + j, b, d2);
-                        }
-                        __syncwarp();
-                        emitted += total;
-                    }
-                }
-                RPHASE(7)
-                __syncthreads();
-                RPHASE(8)
-            }
-        }
-        __syncthreads();       // the staged rows and their tables are rewritten by the next item
-    }
-}
-
 // ------------------------------------------------------------------------------------ block kernels
 // One work item = the centres in a block of bx x by cells of one layer (z) of one structure, about kBlkTargetCentres of
 // them, taken by ONE WARP (a block of 32 threads: the warps share nothing and never meet): a lane per centre.  Their
@@ -837,21 +558,7 @@ neighbours_tile_kernel(const T *__restrict__ pos, const int64_t *__restrict__ pt
 // than a list holds in several emissions.
 template <typename T> struct BlockCap { static constexpr int value = 768; };
 template <> struct BlockCap<double> { static constexpr int value = 384; };
-constexpr int kBlkList = 128;                             // FILL: entries of a centre's hit list between two emissions
-constexpr int kBlkListStride = kBlkList + 2;              // (in 16-bit entries: an odd number of words, so that lanes at the same
-                                                          //  position of their lists use different banks)
-
-template <typename T, bool FILL>
-struct BlockSmem {
-    static constexpr int kCap = BlockCap<T>::value;
-    static constexpr size_t cand = 0;                                         // V4<T>[kCap]: staged candidates
-    static constexpr size_t src = cand + (size_t)kCap * sizeof(V4<T>);        // u16[kCap]: where the candidates of a stage come from
-    static constexpr size_t rows = src + (size_t)kCap * 2;                    // int k0[64], off[65]
-    static constexpr size_t mask = rows + 544;                                // FILL: u32[kCapBits / 32]
-    static constexpr size_t pref = mask + (FILL ? kCapBits / 8 : 0);          // FILL: u16[kCapBits / 32]
-    static constexpr size_t hits = pref + (FILL ? kCapBits / 16 : 0);         // FILL: u16[32][kBlkListStride]
-    static constexpr size_t total = (hits + (FILL ? (size_t)32 * kBlkListStride * 2 : 0) + 31) & ~(size_t)31;
-};
+constexpr int kItemRun = 8;                               // consecutive work items a block takes at a time
 
 template <typename T> __device__ __forceinline__ V4<T> far_point();
 template <> __device__ __forceinline__ float4 far_point<float>() { return make_float4(INFINITY, INFINITY, INFINITY, 0.f); }
@@ -869,122 +576,160 @@ __device__ __forceinline__ void push_if_below(double d2, double r2, uint32_t &en
                  : "+r"(end) : "d"(d2), "d"(r2), "h"((unsigned short)value));
 }
 
-template <typename T, bool FILL>
+// The structure a work item belongs to and its cell grid, kept from item to item (a run of items seldom changes structure).
+struct ItemStruct {
+    int b = -1, item_lo = 0, item_hi = 0;                  // structure, and the items it owns
+    int gx = 0, gy = 0, gz = 0, reach = 0, bx = 1, by = 1, n = 0;
+    int64_t lo = 0;
+};
+__device__ __forceinline__ void find_struct(ItemStruct &q, int item, int64_t B, const int64_t *__restrict__ ptr,
+                                            const CellParam *__restrict__ cellparam, const int32_t *__restrict__ group_ptr, int lane) {
+    if (q.b >= 0 && item < q.item_hi) return;
+    int b = 0, span = (int)B;
+    // largest b with group_ptr[b] <= item: every round looks at 32 entries of the range that is left
+    while (span > 1) {
+        const int step = (span + 31) >> 5, k = b + lane * step;
+        const unsigned below = __ballot_sync(0xffffffffu, lane * step < span && group_ptr[k] <= item);     // (lane 0 always)
+        const int last = 31 - __clz(below);
+        span = min(step, span - last * step);
+        b += last * step;
+    }
+    const CellParam cp = cellparam[b];
+    q.b = b;
+    q.gx = cp.gx; q.gy = cp.gy; q.gz = cp.gz; q.reach = cp.reach; q.bx = cp.pad & 255; q.by = cp.pad >> 8;
+    q.lo = ptr[b];
+    q.n = (int)(ptr[b + 1] - q.lo);
+    q.item_lo = group_ptr[b];
+    q.item_hi = group_ptr[b + 1];
+}
+// A work item: block [x0, x1) x [y0, y1) of layer cz of the structure's cells; its candidates lie in cells [xa, xb] of the
+// nrows = ny x nz rows of cells from (ya, za) on.
+struct BlockGeom { int cz, x0, x1, y0, y1, xa, xb, ya, za, ny, nrows; };
+__device__ __forceinline__ BlockGeom block_geom(const ItemStruct &q, int item) {
+    BlockGeom o;
+    const int g = item - q.item_lo;
+    const int nbx = (q.gx + q.bx - 1) / q.bx, nby = (q.gy + q.by - 1) / q.by, gr = g % (nbx * nby);
+    o.cz = g / (nbx * nby);
+    o.y0 = (gr / nbx) * q.by; o.x0 = (gr % nbx) * q.bx;
+    o.y1 = min(o.y0 + q.by, q.gy); o.x1 = min(o.x0 + q.bx, q.gx);
+    o.ya = max(o.y0 - q.reach, 0); o.za = max(o.cz - q.reach, 0);
+    const int yb = min(o.y1 - 1 + q.reach, q.gy - 1), zb = min(o.cz + q.reach, q.gz - 1);
+    o.ny = yb - o.ya + 1; o.nrows = o.ny * (zb - o.za + 1);
+    o.xa = max(o.x0 - q.reach, 0); o.xb = min(o.x1 - 1 + q.reach, q.gx - 1);
+    return o;
+}
+// This lane's part of an item's tables: the run of centres in row `lane` of the block, and candidate runs 2 lane, 2 lane + 1
+// (positions in the structure's cell-sorted points).  Read an item ahead, under the tests of the item before.
+struct ItemRuns { int run_k, run_len, k0[2], len[2]; };
+__device__ __forceinline__ ItemRuns load_runs(const int32_t *__restrict__ cs, const ItemStruct &q, const BlockGeom &o, int lane) {
+    ItemRuns r;
+    r.run_k = r.run_len = 0;
+    if (lane < o.y1 - o.y0) {
+        const int rb = q.gx * (o.y0 + lane + q.gy * o.cz);
+        r.run_k = cs[rb + o.x0];
+        r.run_len = cs[rb + o.x1] - r.run_k;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int rw = 2 * lane + h;
+        r.k0[h] = r.len[h] = 0;
+        if (rw < o.nrows) {
+            const int rb = q.gx * (o.ya + rw % o.ny + q.gy * (o.za + rw / o.ny));
+            r.k0[h] = cs[rb + o.xa];
+            r.len[h] = cs[rb + o.xb + 1] - r.k0[h];
+        }
+    }
+    return r;
+}
+// position, among the block's centres, -> position in the structure's cell-sorted points (-1: past the last centre)
+__device__ __forceinline__ int centre_at(int q, const ItemRuns &r, int rows) {
+    int kc = -1;
+    for (int rr = 0; rr < rows; rr++) {
+        const int len = __shfl_sync(0xffffffffu, r.run_len, rr), st = __shfl_sync(0xffffffffu, r.run_k, rr);
+        if (kc < 0 && q >= 0 && q < len) kc = st + q;
+        q -= len;
+    }
+    return kc;
+}
+
+template <typename T>
+struct CountSmem {
+    static constexpr int kCap = BlockCap<T>::value;
+    static constexpr size_t cand = 0;                                         // V4<T>[kCap]: staged candidates
+    static constexpr size_t src = cand + (size_t)kCap * sizeof(V4<T>);        // u16[kCap]: where the candidates of a stage come from
+    static constexpr size_t rows = src + (size_t)kCap * 2;                    // int k0[64], off[65]
+    static constexpr size_t total = (rows + 544 + 31) & ~(size_t)31;
+};
+
+template <typename T>
 __global__ void __launch_bounds__(32, 14)                  // (shared memory allows 14 one-warp blocks per SM)
-neighbours_block_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, T r2, int64_t max_nn, int loop, int rule,
-                        const V4<T> *__restrict__ spos, const CellParam *__restrict__ cellparam,
-                        const int32_t *__restrict__ cell_start, const int32_t *__restrict__ group_ptr, int32_t *__restrict__ deg,
-                        const int64_t *__restrict__ offsets, FillOut out, int32_t *__restrict__ status) {
-    using S = BlockSmem<T, FILL>;
+neighbours_block_count_kernel(const int64_t *__restrict__ ptr, int64_t B, T r2, int64_t max_nn, int loop, int rule,
+                              const V4<T> *__restrict__ spos, const CellParam *__restrict__ cellparam,
+                              const int32_t *__restrict__ cell_start, const int32_t *__restrict__ group_ptr, int32_t *__restrict__ deg,
+                              int32_t *__restrict__ status) {
+    using S = CountSmem<T>;
     constexpr int kCap = S::kCap, kPerLane = kCap / 32;
     extern __shared__ __align__(32) unsigned char blk_smem[];
     const int lane = threadIdx.x;
     V4<T> *cand = reinterpret_cast<V4<T> *>(blk_smem + S::cand);
     unsigned short *src = reinterpret_cast<unsigned short *>(blk_smem + S::src);
     int *s_k0 = reinterpret_cast<int *>(blk_smem + S::rows), *s_off = s_k0 + 64;
-    unsigned *mask = reinterpret_cast<unsigned *>(blk_smem + S::mask);
-    unsigned short *pref = reinterpret_cast<unsigned short *>(blk_smem + S::pref);
-    unsigned short *my_hits = reinterpret_cast<unsigned short *>(blk_smem + S::hits) + lane * kBlkListStride;
-    const unsigned short *all_hits = reinterpret_cast<const unsigned short *>(blk_smem + S::hits);
     const unsigned full = 0xffffffffu;
     const int G = group_ptr[B];
-    // (the output pointers as scalars: read through the parameter struct inside the nested lambdas below they end up in
-    //  local memory, and with all of the L1 given to shared memory every such read is a trip to the L2)
-    int64_t *const o_row0 = out.row0, *const o_row1 = out.row1, *const o_batch = out.mapping_batch;
-    T *const o_dist = reinterpret_cast<T *>(out.distance);
-    int32_t *const o_row0_32 = out.row0_32, *const o_row1_32 = out.row1_32;
     RPHASE_DECL
 
-    for (int item = blockIdx.x; item < G; item += gridDim.x) {
-        RPHASE(FILL ? 0 : 10 + 0)
-        int b = 0;
-        {   // largest b with group_ptr[b] <= item: every round looks at 32 entries of the range that is left
-            int span = (int)B;
-            while (span > 1) {
-                const int step = (span + 31) >> 5, k = b + lane * step;
-                const unsigned below = __ballot_sync(full, lane * step < span && group_ptr[k] <= item);     // (lane 0 always)
-                const int last = 31 - __clz(below);
-                span = min(step, span - last * step);
-                b += last * step;
-            }
-        }
-        const CellParam cp = cellparam[b];
-        const int gx = cp.gx, gy = cp.gy, gz = cp.gz, reach = cp.reach, bx = cp.pad & 255, by = cp.pad >> 8;
-        const int64_t lo = ptr[b];
-        const int n = (int)(ptr[b + 1] - lo);
-        const int g = item - group_ptr[b];
-        const int nbx = (gx + bx - 1) / bx, nby = (gy + by - 1) / by;
-        const int cz = g / (nbx * nby), gr = g % (nbx * nby);
-        const int y0 = (gr / nbx) * by, x0 = (gr % nbx) * bx, y1 = min(y0 + by, gy), x1 = min(x0 + bx, gx);
-        const int32_t *cs = cell_start + lo + b;
-        const V4<T> *sp = spos + lo;
+    // Items are dealt in runs of kItemRun consecutive ones: neighbouring blocks of one structure, whose structure look-up and
+    // parameters are then read once per run and whose candidates overlap in the L2.
+    ItemStruct q;
+    ItemRuns ahead;
+    bool have_ahead = false;
+    const int nruns = (G + kItemRun - 1) / kItemRun;
+    for (int run = blockIdx.x; run < nruns; run += gridDim.x)
+    for (int item = run * kItemRun, item_end = min(G, (run + 1) * kItemRun); item < item_end; item++) {
+        RPHASE(10)
+        find_struct(q, item, B, ptr, cellparam, group_ptr, lane);
+        const BlockGeom o = block_geom(q, item);
+        const int32_t *cs = cell_start + q.lo + q.b;
+        const V4<T> *sp = spos + q.lo;
+        const ItemRuns rn = have_ahead ? ahead : load_runs(cs, q, o, lane);
+        have_ahead = false;
+        const int nc = warp_sum(rn.run_len), rows = o.y1 - o.y0;
+        // the first 32 centres' points: on their way while the candidates are staged
+        const int kc0 = centre_at(lane, rn, rows);
+        const V4<T> pc0 = sp[max(kc0, 0)];
 
-        // ---- the centres: one run of the cell-sorted points per row of the block
-        int run_k = 0, run_len = 0;
-        if (lane < y1 - y0) {
-            const int rb = gx * (y0 + lane + gy * cz);
-            run_k = cs[rb + x0];
-            run_len = cs[rb + x1] - run_k;
+        // ---- the candidate runs: exclusive prefix of their lengths; every lane writes out where its two runs come from
+        int incl = rn.len[0] + rn.len[1];
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+            const int t = __shfl_up_sync(full, incl, s);
+            if (lane >= s) incl += t;
         }
-        const int nc = warp_sum(run_len);
-        if (nc == 0) continue;
-
-        // ---- the candidate runs: bounds, exclusive prefix of their lengths (two runs per lane)
-        const int ya = max(y0 - reach, 0), yb = min(y1 - 1 + reach, gy - 1), za = max(cz - reach, 0), zb = min(cz + reach, gz - 1);
-        const int ny = yb - ya + 1, nrows = ny * (zb - za + 1);
-        const int xa = max(x0 - reach, 0), xb = min(x1 - 1 + reach, gx - 1);
-        int M;
-        {
-            int k0[2] = {0, 0}, len[2] = {0, 0};
+        const int excl = incl - rn.len[0] - rn.len[1], M = __shfl_sync(full, incl, 31);
+        if (nc > 0) {
+            if (2 * lane < o.nrows) { s_k0[2 * lane] = rn.k0[0]; s_off[2 * lane] = excl; }
+            if (2 * lane + 1 < o.nrows) { s_k0[2 * lane + 1] = rn.k0[1]; s_off[2 * lane + 1] = excl + rn.len[0]; }
+            if (lane == 0) s_off[o.nrows] = M;
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                const int rw = 2 * lane + h;
-                if (rw < nrows) {
-                    const int rb = gx * (ya + rw % ny + gy * (za + rw / ny));
-                    k0[h] = cs[rb + xa];
-                    len[h] = cs[rb + xb + 1] - k0[h];
-                }
+                const int off = excl + (h ? rn.len[0] : 0), kb = min(rn.len[h], kCap - off);
+                for (int k = 0; k < kb; k++) src[off + k] = (unsigned short)(rn.k0[h] + k);
             }
-            int incl = len[0] + len[1];
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(full, incl, o);
-                if (lane >= o) incl += t;
-            }
-            const int excl = incl - len[0] - len[1];
-            M = __shfl_sync(full, incl, 31);
-            __syncwarp();
-            if (2 * lane < nrows) { s_k0[2 * lane] = k0[0]; s_off[2 * lane] = excl; }
-            if (2 * lane + 1 < nrows) { s_k0[2 * lane + 1] = k0[1]; s_off[2 * lane + 1] = excl + len[0]; }
-            if (lane == 0) s_off[nrows] = M;
-            // where the first stage's candidates come from: every lane writes out its own two runs (src[] is free here)
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int off = excl + (h ? len[0] : 0), kb = min(len[h], kCap - off);
-                for (int k = 0; k < kb; k++) src[off + k] = (unsigned short)(k0[h] + k);
-            }
-            __syncwarp();
         }
+        __syncwarp();
         const bool single = M <= kCap;
-        RPHASE(FILL ? 1 : 10 + 1)
-
+        RPHASE(11)
         bool first_src = true;                         // src[] still holds the sources of candidates [0, kCap)
-        // positions (in the structure's cell-sorted run) of candidates [c0, c0 + kCap) of the concatenated runs -> src[];
-        // half a warp per run
-        auto build_src = [&](int c0) {
+        auto build_src = [&](int c0) {                 // sources of candidates [c0, c0 + kCap) of the concatenated runs; half a warp per run
             const int half = lane >> 4, l16 = lane & 15;
-            for (int rw = half; rw < nrows; rw += 2) {
+            for (int rw = half; rw < o.nrows; rw += 2) {
                 const int off = s_off[rw] - c0, len = s_off[rw + 1] - s_off[rw], k0 = s_k0[rw];
                 const int ka = max(0, -off), kb = min(len, kCap - off);
                 for (int k = ka + l16; k < kb; k += 16) src[off + k] = (unsigned short)(k0 + k);
             }
             __syncwarp();
         };
-        auto pad_stage = [&](int mw) {                 // the rest of the last 32 staged entries: points that hit nothing
-            const int f = mw + lane;
-            if (f < ((mw + 31) & ~31)) cand[f] = far_point<T>();
-        };
-        // COUNT: candidates [c0, c0 + kCap) as they come, copied without passing through registers
+        // candidates [c0, c0 + kCap) as they come, copied without passing through registers, all copies in flight together
         auto stage_plain = [&](int c0) {
             const int mc = min(kCap, M - c0);
             if (c0 > 0 || !first_src) build_src(c0);
@@ -1001,269 +746,75 @@ neighbours_block_kernel(const T *__restrict__ pos, const int64_t *__restrict__ p
                                      "l"(reinterpret_cast<const char *>(from) + 16 * h) : "memory");
                 }
             }
-            pad_stage(mc);
+            {   // the rest of the last 32 staged entries: points that hit nothing
+                const int f = mc + lane;
+                if (f < ((mc + 31) & ~31)) cand[f] = far_point<T>();
+            }
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncwarp();
         };
-        // FILL: rank of the candidate with local index j among all candidates of the item, in ascending order of index
-        auto rank_of = [&](int j) { return (int)pref[j >> 5] + __popc(mask[j >> 5] & ((1u << (j & 31)) - 1u)); };
-        // candidates [c0, c0 + kCap) whose rank lies in [wb, wb + kCap) -> their place in the stage, eight loads at a time
-        auto scatter_chunk = [&](int mc, int wb) {
-#pragma unroll
-            for (int u0 = 0; u0 < kPerLane; u0 += 8) {
-                V4<T> p[8];
-#pragma unroll
-                for (int u = 0; u < 8; u++) p[u] = sp[src[min((u0 + u) * 32 + lane, mc - 1)]];
-#pragma unroll
-                for (int u = 0; u < 8; u++)
-                    if ((u0 + u) * 32 + lane < mc) {
-                        const int rw = rank_of(idx_of(p[u])) - wb;
-                        if (rw >= 0 && rw < kCap) cand[rw] = p[u];
-                    }
-            }
-        };
-        auto stage_window = [&](int wb) {                        // (several windows only)
-            for (int c0 = 0; c0 < M; c0 += kCap) {
-                build_src(c0);
-                scatter_chunk(min(kCap, M - c0), wb);
-                __syncwarp();
-            }
-            pad_stage(min(kCap, M - wb));
-            __syncwarp();
-        };
-
-        if (FILL) {
-            // ---- mark every candidate's local index, rank the marks
-            const int nwords = (n + 31) >> 5;                    // (n <= kCapBits)
-            for (int w = lane; w < nwords; w += 32) mask[w] = 0u;
-            __syncwarp();
-            int jj[kPerLane];                                    // (local indices of the first stage's candidates, kept for the ranking)
-            for (int c0 = 0; c0 < M; c0 += kCap) {
-                const int mc = min(kCap, M - c0);
-                if (c0 > 0) build_src(c0);
-                int jc[kPerLane];
-#pragma unroll
-                for (int u = 0; u < kPerLane; u++) jc[u] = idx_of(sp[src[min(u * 32 + lane, mc - 1)]]);
-#pragma unroll
-                for (int u = 0; u < kPerLane; u++) {
-                    if (u * 32 + lane < mc) atomicOr(&mask[jc[u] >> 5], 1u << (jc[u] & 31));
-                    if (c0 == 0) jj[u] = jc[u];
-                }
-                __syncwarp();
-            }
-            RPHASE(8)
-            auto rank_marks = [&]() {
-                constexpr int kPer = kCapBits / 32 / 32;         // words per lane
-                int cnt[kPer], sum = 0;
-#pragma unroll
-                for (int q = 0; q < kPer; q++) {
-                    const int w = kPer * lane + q;
-                    cnt[q] = w < nwords ? __popc(mask[w]) : 0;
-                    sum += cnt[q];
-                }
-                int incl = sum;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int t = __shfl_up_sync(full, incl, o);
-                    if (lane >= o) incl += t;
-                }
-                int run = incl - sum;
-#pragma unroll
-                for (int q = 0; q < kPer; q++) {
-                    const int w = kPer * lane + q;
-                    if (w < nwords) pref[w] = (unsigned short)run;
-                    run += cnt[q];
-                }
-            };
-            rank_marks();
-            __syncwarp();
-            RPHASE(9)
-            if (single) {
-                // sources in the order of the ranks (in the space of the hit lists, empty now), then the candidates themselves,
-                // copied without passing through registers, all copies in flight together
-                unsigned short *ssrc = reinterpret_cast<unsigned short *>(blk_smem + S::hits);
-#pragma unroll
-                for (int u = 0; u < kPerLane; u++)
-                    if (u * 32 + lane < M) ssrc[rank_of(jj[u])] = src[u * 32 + lane];
-                __syncwarp();
-                const uint32_t dst0 = (uint32_t)__cvta_generic_to_shared(cand);
-#pragma unroll
-                for (int u = 0; u < kPerLane; u++) {
-                    const int f = u * 32 + lane;
-                    if (f < M) {
-                        const V4<T> *from = sp + ssrc[f];
-#pragma unroll
-                        for (int h = 0; h < (int)sizeof(V4<T>) / 16; h++)
-                            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst0 + (uint32_t)(f * sizeof(V4<T>) + 16 * h)),
-                                         "l"(reinterpret_cast<const char *>(from) + 16 * h) : "memory");
-                    }
-                }
-                pad_stage(M);
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-                __syncwarp();
-            }
-        } else if (single) {
-            stage_plain(0);
+        if (nc > 0 && single) stage_plain(0);
+        // the next item's tables: read under this item's tests
+        if (item + 1 < min(item_end, q.item_hi)) {
+            ahead = load_runs(cs, q, block_geom(q, item + 1), lane);
+            have_ahead = true;
         }
+        RPHASE(12)
 
-        RPHASE(FILL ? 2 : 10 + 2)
         for (int cp0 = 0; cp0 < nc; cp0 += 32) {
             // ---- this lane's centre
-            int kc = -1;
-            {
-                int q = cp0 + lane;
-                for (int rr = 0; rr < y1 - y0; rr++) {
-                    const int len = __shfl_sync(full, run_len, rr), st = __shfl_sync(full, run_k, rr);
-                    if (kc < 0 && q >= 0 && q < len) kc = st + q;
-                    q -= len;
-                }
-            }
+            const int kc = cp0 == 0 ? kc0 : centre_at(cp0 + lane, rn, rows);
             const bool active = kc >= 0;
-            const V4<T> pc = sp[max(kc, 0)];
+            const V4<T> pc = cp0 == 0 ? pc0 : sp[max(kc, 0)];
             const int il = idx_of(pc);
-            const int64_t i = lo + il;
             // (a lane without a centre sits at infinity: no hits)
             const T xi = active ? pc.x : T(INFINITY), yi = active ? pc.y : T(INFINITY), zi = active ? pc.z : T(INFINITY);
-
-            RPHASE(FILL ? 3 : 10 + 3)
-            if (!FILL) {
-                int cnt = 0, cnt_lo = 0;
-                auto count_windows = [&](auto with_lo_tag) {
-                    constexpr bool kLo = decltype(with_lo_tag)::value;
-                    cnt = cnt_lo = 0;
-                    for (int wb = 0; wb < M; wb += kCap) {
-                        if (!single) stage_plain(wb);
-                        const int mw = min(kCap, M - wb), nw = (mw + 31) >> 5;
-                        for (int w = 0; w < nw; w++) {
-                            const V4<T> *cw = cand + w * 32;
-#pragma unroll 8
-                            for (int u = 0; u < 32; u++) {
-                                const V4<T> p = cw[u];
-                                const T d2 = dist2_rn(xi, yi, zi, p.x, p.y, p.z);
-                                if (d2 < r2) {
-                                    cnt++;
-                                    if (kLo) cnt_lo += idx_of(p) < il;
-                                }
-                            }
-                        }
-                        __syncwarp();
-                    }
-                };
-                count_windows(std::false_type{});
-                RPHASE(FILL ? 4 : 10 + 4)
-                const int self_hit = dist2_rn(xi, yi, zi, xi, yi, zi) < r2 ? 1 : 0;      // (the centre is one of its candidates)
-                // hits below the centre's own index matter only where the neighbour cap bites: counted in a second walk
-                const bool over = active && (int64_t)(loop ? cnt : cnt - self_hit) > max_nn;
-                if (__any_sync(full, over)) count_windows(std::true_type{});
-                if (active) {
-                    const int64_t nlo = cnt_lo, nhi = cnt - self_hit - cnt_lo;
-                    int64_t total, k;
-                    if (loop) {
-                        total = nlo + nhi + self_hit;
-                        k = total < max_nn ? total : max_nn;
-                    } else if (rule == MLCGB_RULE_CLUSTER && self_hit) {
-                        total = nlo + nhi;
-                        if (nlo >= max_nn + 1) k = max_nn + 1;
-                        else k = total < max_nn ? total : max_nn;
-                    } else {
-                        total = nlo + nhi;
-                        k = total < max_nn ? total : max_nn;
-                    }
-                    deg[i] = (int32_t)k;
-                    if (k < total) atomicOr(status, (int)kTruncated);
-                }
-            } else {
-                int64_t base_off = 0;
-                int kept = 0, emitted = 0;
-                if (active) {
-                    base_off = offsets[i];
-                    kept = (int)(offsets[i + 1] - base_off);
-                }
-                const uint32_t list0 = (uint32_t)__cvta_generic_to_shared(my_hits);
-                uint32_t list_end = list0;                       // shared-memory address past the last entry of this lane's list
-                // the lists so far -> edges: a centre at a time, consecutive lanes on consecutive slots; the centre's own entry
-                // is dropped here (unless loops are wanted) and entries beyond the centre's count are not written
-                auto emit_lists = [&]() {
-                    __syncwarp();
-                    RPHASE(FILL ? 4 : 10 + 4)
-                    const int nh = (int)(list_end - list0) >> 1;
-                    // where the centre itself sits in its (ascending) list: that entry is skipped, unless loops are wanted
-                    int self_at = INT_MAX;
-                    if (!loop) {
-                        int lo_t = 0, hi_t = nh;
-                        while (lo_t < hi_t) {
-                            const int mid = (lo_t + hi_t) >> 1;
-                            if ((int)my_hits[mid] < il) lo_t = mid + 1; else hi_t = mid;
-                        }
-                        if (lo_t < nh && (int)my_hits[lo_t] == il) self_at = lo_t;
-                    }
-                    RPHASE(5)
-                    // all the lists as one run of edges: entry f of it belongs to the centre whose first entry is the last at or
-                    // below f; 32 consecutive entries are written at a time, whatever centres they fall into
-                    const int avail = nh - (self_at != INT_MAX ? 1 : 0), take = max(0, min(avail, kept - emitted));
-                    int incl = take;
-#pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        const int t = __shfl_up_sync(full, incl, o);
-                        if (lane >= o) incl += t;
-                    }
-                    const int first = incl - take, total = __shfl_sync(full, incl, 31);
-                    const int64_t slot0 = base_off + emitted;
-                    RPHASE(6)
-                    // (four rounds per trip, independent of one another: the centre look-up is a chain of five exchanges)
-                    for (int f00 = 0; f00 < total; f00 += 128)
-#pragma unroll
-                    for (int f0 = f00; f0 < f00 + 128; f0 += 32) {
-                        const int f = f0 + lane;
-                        int cc = 0;
-#pragma unroll
-                        for (int st = 16; st > 0; st >>= 1)
-                            if (__shfl_sync(full, first, cc + st) <= f) cc += st;
-                        const int t = f - __shfl_sync(full, first, cc), at = __shfl_sync(full, self_at, cc);
-                        const int64_t slot = __shfl_sync(full, slot0, cc) + t, ic = lo + __shfl_sync(full, il, cc);
-                        T cxi = T(0), cyi = T(0), czi = T(0);
-                        if (o_dist) { cxi = __shfl_sync(full, xi, cc); cyi = __shfl_sync(full, yi, cc); czi = __shfl_sync(full, zi, cc); }
-                        if (f < total) {
-                            const int64_t gj = lo + (int)all_hits[cc * kBlkListStride + t + (t >= at ? 1 : 0)];
-                            if (o_row0) { o_row0[slot] = ic; o_row1[slot] = gj; }
-                            if (o_batch) o_batch[slot] = b;
-                            if (o_dist) o_dist[slot] = sqrt(dist2_rn(cxi, cyi, czi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]));
-                            if (o_row0_32) { o_row0_32[slot] = (int32_t)ic; o_row1_32[slot] = (int32_t)gj; }
-                        }
-                    }
-                    emitted += avail;
-                    list_end = list0;
-                    __syncwarp();
-                    RPHASE(FILL ? 7 : 10 + 5)
-                };
+            RPHASE(13)
+            int cnt = 0, cnt_lo = 0;
+            auto count_windows = [&](auto with_lo_tag) {
+                constexpr bool kLo = decltype(with_lo_tag)::value;
+                cnt = cnt_lo = 0;
                 for (int wb = 0; wb < M; wb += kCap) {
-                    if (!__any_sync(full, active && emitted < kept)) break;
-                    if (!single) stage_window(wb);
+                    if (!single) stage_plain(wb);
                     const int mw = min(kCap, M - wb), nw = (mw + 31) >> 5;
                     for (int w = 0; w < nw; w++) {
-                        if (__any_sync(full, list_end > list0 + 2 * (kBlkList - 32))) emit_lists();   // room for this word's hits in every list
                         const V4<T> *cw = cand + w * 32;
-                        // (sixteen loads and distances, then their pushes: a load cannot be moved above an earlier store to
-                        //  shared memory, so interleaved they would run one test at a time)
-#pragma unroll
-                        for (int g16 = 0; g16 < 2; g16++) {
-                            T d2[16];
-                            int id[16];
-#pragma unroll
-                            for (int u = 0; u < 16; u++) {
-                                const V4<T> q = cw[g16 * 16 + u];
-                                d2[u] = dist2_rn(xi, yi, zi, q.x, q.y, q.z);
-                                id[u] = idx_of(q);
+#pragma unroll 8
+                        for (int u = 0; u < 32; u++) {
+                            const V4<T> p = cw[u];
+                            const T d2 = dist2_rn(xi, yi, zi, p.x, p.y, p.z);
+                            if (d2 < r2) {
+                                cnt++;
+                                if (kLo) cnt_lo += idx_of(p) < il;
                             }
-#pragma unroll
-                            for (int u = 0; u < 16; u++) push_if_below(d2[u], r2, list_end, id[u]);
                         }
-                        asm volatile("" ::: "memory");           // (the pushes write shared memory behind the compiler's back)
                     }
-                    emit_lists();
+                    __syncwarp();
                 }
+            };
+            count_windows(std::false_type{});
+            RPHASE(14)
+            const int self_hit = dist2_rn(xi, yi, zi, xi, yi, zi) < r2 ? 1 : 0;      // (the centre is one of its candidates)
+            // hits below the centre's own index matter only where the neighbour cap bites: counted in a second walk
+            const bool over = active && (int64_t)(loop ? cnt : cnt - self_hit) > max_nn;
+            if (__any_sync(full, over)) count_windows(std::true_type{});
+            if (active) {
+                const int64_t nlo = cnt_lo, nhi = cnt - self_hit - cnt_lo;
+                int64_t total, k;
+                if (loop) {
+                    total = nlo + nhi + self_hit;
+                    k = total < max_nn ? total : max_nn;
+                } else if (rule == MLCGB_RULE_CLUSTER && self_hit) {
+                    total = nlo + nhi;
+                    if (nlo >= max_nn + 1) k = max_nn + 1;
+                    else k = total < max_nn ? total : max_nn;
+                } else {
+                    total = nlo + nhi;
+                    k = total < max_nn ? total : max_nn;
+                }
+                deg[q.lo + il] = (int32_t)k;
+                if (k < total) atomicOr(status, (int)kTruncated);
             }
         }
         __syncwarp();          // the stage and its tables are rewritten by the next item
@@ -1279,7 +830,8 @@ neighbours_block_kernel(const T *__restrict__ pos, const int64_t *__restrict__ p
 // limits the blocks per SM.
 constexpr int kFillWarps = 2;
 constexpr int kFillList = 80;                              // entries of a warp's hit list of a centre between two emissions
-constexpr int kFillListStride = kFillList + 2;             // (16-bit entries: an odd number of words, see kBlkListStride)
+constexpr int kFillListStride = kFillList + 2;             // (in 16-bit entries: an odd number of words, so that lanes at the same
+                                                           //  position of their lists use different banks)
 
 template <typename T>
 struct FillSmem {
@@ -1295,7 +847,8 @@ struct FillSmem {
     static_assert(pref + kCapBits / 16 <= hits + hits_bytes, "staging tables must fit the space of the hit lists");
     static constexpr size_t rows = hits + hits_bytes;                          // int k0[64], off[65]
     static constexpr size_t avail = rows + 544;                                // int[kFillWarps][32]: entries the warps had
-    static constexpr size_t total = (avail + (size_t)kFillWarps * 32 * 4 + 31) & ~(size_t)31;
+    static constexpr size_t par = (avail + (size_t)kFillWarps * 32 * 4 + 15) & ~(size_t)15;   // int4[kFillWarps][32]: what an emission needs of a centre
+    static constexpr size_t total = (par + (size_t)kFillWarps * 32 * 16 + 31) & ~(size_t)31;
 };
 
 static_assert(kFillWarps == 2, "the hand-over below is written for two warps: one named barrier, warp 0 arrives, warp 1 waits");
@@ -1319,6 +872,7 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
     unsigned short *pref = reinterpret_cast<unsigned short *>(blk_smem + S::pref);
     int *s_k0 = reinterpret_cast<int *>(blk_smem + S::rows), *s_off = s_k0 + 64;
     int *s_avail = reinterpret_cast<int *>(blk_smem + S::avail);
+    int4 *s_par = reinterpret_cast<int4 *>(blk_smem + S::par) + warp * 32;
     unsigned short *warp_hits = reinterpret_cast<unsigned short *>(blk_smem + S::hits) + warp * 32 * kFillListStride;
     unsigned short *my_hits = warp_hits + lane * kFillListStride;
     const unsigned full = 0xffffffffu;
@@ -1330,67 +884,44 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
     int32_t *const o_row0_32 = out.row0_32, *const o_row1_32 = out.row1_32;
     RPHASE_DECL
 
-    for (int item = blockIdx.x; item < G; item += gridDim.x) {
+    // Items are dealt in runs of kItemRun consecutive ones: neighbouring blocks of one structure, whose structure look-up and
+    // parameters are then read once per run and whose candidates overlap in the L2.  (Every warp decodes the item for itself:
+    // the same loads, no exchange.)
+    ItemStruct q;
+    ItemRuns ahead;
+    bool have_ahead = false;
+    const int nruns = (G + kItemRun - 1) / kItemRun;
+    for (int run = blockIdx.x; run < nruns; run += gridDim.x)
+    for (int item = run * kItemRun, item_end = min(G, (run + 1) * kItemRun); item < item_end; item++) {
         RPHASE(0)
-        // ---- the work item (every warp for itself: the same loads, no exchange)
-        int b = 0;
-        {   // largest b with group_ptr[b] <= item: every round looks at 32 entries of the range that is left
-            int span = (int)B;
-            while (span > 1) {
-                const int step = (span + 31) >> 5, k = b + lane * step;
-                const unsigned below = __ballot_sync(full, lane * step < span && group_ptr[k] <= item);     // (lane 0 always)
-                const int last = 31 - __clz(below);
-                span = min(step, span - last * step);
-                b += last * step;
-            }
-        }
-        const CellParam cp = cellparam[b];
-        const int gx = cp.gx, gy = cp.gy, gz = cp.gz, reach = cp.reach, bx = cp.pad & 255, by = cp.pad >> 8;
-        const int64_t lo = ptr[b];
-        const int n = (int)(ptr[b + 1] - lo);
-        const int g = item - group_ptr[b];
-        const int nbx = (gx + bx - 1) / bx, nby = (gy + by - 1) / by;
-        const int cz = g / (nbx * nby), gr = g % (nbx * nby);
-        const int y0 = (gr / nbx) * by, x0 = (gr % nbx) * bx, y1 = min(y0 + by, gy), x1 = min(x0 + bx, gx);
+        find_struct(q, item, B, ptr, cellparam, group_ptr, lane);
+        const BlockGeom o = block_geom(q, item);
+        const int b = q.b, n = q.n, nrows = o.nrows, rows = o.y1 - o.y0;
+        const int64_t lo = q.lo;
         const int32_t *cs = cell_start + lo + b;
         const V4<T> *sp = spos + lo;
-        int run_k = 0, run_len = 0;                          // the centres: one run of the cell-sorted points per row of the block
-        if (lane < y1 - y0) {
-            const int rb = gx * (y0 + lane + gy * cz);
-            run_k = cs[rb + x0];
-            run_len = cs[rb + x1] - run_k;
-        }
-        const int nc = warp_sum(run_len);
-        if (nc == 0) continue;                               // (the same in every warp)
-        const int ya = max(y0 - reach, 0), yb = min(y1 - 1 + reach, gy - 1), za = max(cz - reach, 0), zb = min(cz + reach, gz - 1);
-        const int ny = yb - ya + 1, nrows = ny * (zb - za + 1);
-        const int xa = max(x0 - reach, 0), xb = min(x1 - 1 + reach, gx - 1);
+        const ItemRuns rn = have_ahead ? ahead : load_runs(cs, q, o, lane);
+        have_ahead = false;
+        const int nc = warp_sum(rn.run_len);
+        // the first 32 centres' points: on their way while the candidates are staged
+        const int kc0 = centre_at(lane, rn, rows);
+        const V4<T> pc0 = sp[max(kc0, 0)];
         int M;
-        {   // the candidate runs, two per lane: bounds, exclusive prefix of the lengths; warp w writes out run 2 lane + w
-            int k0[2] = {0, 0}, len[2] = {0, 0};
+        {   // the candidate runs: exclusive prefix of the lengths; warp w writes out where run 2 lane + w comes from
+            int incl = rn.len[0] + rn.len[1];
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int rw = 2 * lane + h;
-                if (rw < nrows) {
-                    const int rb = gx * (ya + rw % ny + gy * (za + rw / ny));
-                    k0[h] = cs[rb + xa];
-                    len[h] = cs[rb + xb + 1] - k0[h];
-                }
+            for (int s = 1; s < 32; s <<= 1) {
+                const int t = __shfl_up_sync(full, incl, s);
+                if (lane >= s) incl += t;
             }
-            int incl = len[0] + len[1];
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(full, incl, o);
-                if (lane >= o) incl += t;
-            }
-            const int excl = incl - len[0] - len[1];
+            const int excl = incl - rn.len[0] - rn.len[1];
             M = __shfl_sync(full, incl, 31);
-            const int h = warp & 1, off = excl + (h ? len[0] : 0);
-            if (warp < 2) {
-                if (2 * lane + h < nrows) { s_k0[2 * lane + h] = k0[h]; s_off[2 * lane + h] = off; }
+            const int h = warp & 1, off = excl + (h ? rn.len[0] : 0), k0h = h ? rn.k0[1] : rn.k0[0], lenh = h ? rn.len[1] : rn.len[0];
+            if (nc > 0 && warp < 2) {
+                if (2 * lane + h < nrows) { s_k0[2 * lane + h] = k0h; s_off[2 * lane + h] = off; }
                 if (tid == 0) s_off[nrows] = M;
-                const int kb = min(len[h], kCap - off);
-                for (int k = 0; k < kb; k++) src[off + k] = (unsigned short)(k0[h] + k);
+                const int kb = min(lenh, kCap - off);
+                for (int k = 0; k < kb; k++) src[off + k] = (unsigned short)(k0h + k);
             }
         }
         __syncthreads();
@@ -1495,36 +1026,43 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();
         };
-        if (single) stage(0);
+        if (nc > 0 && single) stage(0);
+        // the first 32 centres' places in the output (their points have arrived by now), read under the tests: the first
+        // window is tested without looking at them
+        int64_t base0 = 0, end0 = 0;
+        if (kc0 >= 0) {
+            base0 = offsets[lo + idx_of(pc0)];
+            end0 = offsets[lo + idx_of(pc0) + 1];
+        }
+        // the next item's tables: read under this item's tests
+        if (item + 1 < min(item_end, q.item_hi)) {
+            ahead = load_runs(cs, q, block_geom(q, item + 1), lane);
+            have_ahead = true;
+        }
         RPHASE(2)
 
         for (int cp0 = 0; cp0 < nc; cp0 += 32) {
             // ---- this lane's centre (the same in every warp)
-            int kc = -1;
-            {
-                int q = cp0 + lane;
-                for (int rr = 0; rr < y1 - y0; rr++) {
-                    const int len = __shfl_sync(full, run_len, rr), st = __shfl_sync(full, run_k, rr);
-                    if (kc < 0 && q >= 0 && q < len) kc = st + q;
-                    q -= len;
-                }
-            }
+            const int kc = cp0 == 0 ? kc0 : centre_at(cp0 + lane, rn, rows);
             const bool active = kc >= 0;
-            const V4<T> pc = sp[max(kc, 0)];
+            const V4<T> pc = cp0 == 0 ? pc0 : sp[max(kc, 0)];
             const int il = idx_of(pc);
             // (a lane without a centre sits at infinity: no hits)
             const T xi = active ? pc.x : T(INFINITY), yi = active ? pc.y : T(INFINITY), zi = active ? pc.z : T(INFINITY);
-            int64_t base_off = 0;
-            int kept = 0, emitted = 0;                       // emitted: entries (other than the centre itself) gone by so far
-            if (active) {
-                base_off = offsets[lo + il];
-                kept = (int)(offsets[lo + il + 1] - base_off);
+            int64_t base_off = base0, end_off = end0;
+            int emitted = 0;                                 // entries (other than the centre itself) gone by so far
+            if (cp0 > 0) {
+                base_off = end_off = 0;
+                if (active) {
+                    base_off = offsets[lo + il];
+                    end_off = offsets[lo + il + 1];
+                }
             }
             const uint32_t list0 = (uint32_t)__cvta_generic_to_shared(my_hits);
             RPHASE(3)
 
             for (int wb = 0; wb < M; wb += kCap) {
-                if (!__any_sync(full, active && emitted < kept)) break;      // (the same in every warp)
+                if (wb > 0 && !__any_sync(full, active && emitted < (int)(end_off - base_off))) break;      // (the same in every warp)
                 if (!single) stage(wb);
                 const int mw = min(kCap, M - wb), nw = (mw + 31) >> 5, nwh = (nw + kFillWarps - 1) / kFillWarps;
                 const int w_lo = min(warp * nwh, nw), w_hi = min(w_lo + nwh, nw);
@@ -1558,18 +1096,25 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
                     }
                     int start = emitted + flushed;
                     for (int w2 = 0; w2 < warp; w2++) start += s_avail[w2 * 32 + lane];
-                    const int take = max(0, min(avail, kept - start));
+                    const int take = max(0, min(avail, (int)(end_off - base_off) - start));
                     const int64_t slot0 = base_off + start;
                     RPHASE(5)
-                    for (int cc = 0; cc < 32; cc++) {
-                        const int tk = __shfl_sync(full, take, cc);
-                        if (tk <= 0) continue;
-                        const int at = __shfl_sync(full, self_at, cc);
-                        const int64_t slot_c = __shfl_sync(full, slot0, cc), ic = lo + __shfl_sync(full, il, cc);
+                    // what the emission needs of a centre goes through a table: half a warp takes a centre, two centres at a
+                    // time, and the next pair's entries are read while this pair's edges are written
+                    s_par[lane] = make_int4(take | (min(self_at, 0xffff) << 16), il, (int)(uint32_t)slot0, (int)(slot0 >> 32));
+                    __syncwarp();
+                    const int hsel = lane >> 4, l16 = lane & 15;
+                    int4 nxt = s_par[hsel];
+                    for (int pp = 0; pp < 16; pp++) {
+                        const int4 cur = nxt;
+                        const int cc = 2 * pp + hsel;
+                        if (pp < 15) nxt = s_par[cc + 2];
+                        const int tk = cur.x & 0xffff, at = (int)((unsigned)cur.x >> 16);
+                        const int64_t slot_c = (int64_t)(((uint64_t)(uint32_t)cur.w << 32) | (uint32_t)cur.z), ic = lo + cur.y;
                         T cxi = T(0), cyi = T(0), czi = T(0);
                         if (o_dist) { cxi = __shfl_sync(full, xi, cc); cyi = __shfl_sync(full, yi, cc); czi = __shfl_sync(full, zi, cc); }
                         const unsigned short *hl = warp_hits + cc * kFillListStride;
-                        for (int t = lane; t < tk; t += 32) {
+                        for (int t = l16; t < tk; t += 16) {
                             const int64_t gj = lo + (int)hl[t + (t >= at ? 1 : 0)], slot = slot_c + t;
                             if (o_row0) { o_row0[slot] = ic; o_row1[slot] = gj; }
                             if (o_batch) o_batch[slot] = b;
@@ -1631,18 +1176,18 @@ static int fill_kernel_grid(int *grid) {
     return MLCGB_OK;
 }
 
-template <typename T, bool FILL>
-static int block_kernel_grid(int *grid) {
-    // resident CTAs per SM, asked once per device and kernel
+template <typename T>
+static int count_kernel_grid(int *grid) {
+    // resident blocks per SM, asked once per device and kernel
     static std::atomic<int> cached[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MLCGB_E_LAUNCH;
     int per_sm = cached[dev].load(std::memory_order_relaxed);
     if (per_sm == 0) {
-        const size_t bytes = BlockSmem<T, FILL>::total;
-        if (cudaFuncSetAttribute(neighbours_block_kernel<T, FILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess ||
-            cudaFuncSetAttribute(neighbours_block_kernel<T, FILL>, cudaFuncAttributePreferredSharedMemoryCarveout, 100) != cudaSuccess ||
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, neighbours_block_kernel<T, FILL>, 32, bytes) != cudaSuccess)
+        const size_t bytes = CountSmem<T>::total;
+        if (cudaFuncSetAttribute(neighbours_block_count_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess ||
+            cudaFuncSetAttribute(neighbours_block_count_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, 100) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, neighbours_block_count_kernel<T>, 32, bytes) != cudaSuccess)
             return check_launch();
         if (per_sm < 1) per_sm = 1;
         cached[dev].store(per_sm, std::memory_order_relaxed);
@@ -1663,11 +1208,6 @@ extern "C" int mlcgb_debug_radius_phase_cycles(unsigned long long *out, int n, i
     return MLCGB_OK;
 }
 #endif
-
-template <typename T, bool FILL>
-static size_t tile_smem_bytes() {
-    return (size_t)kTileCand * sizeof(V4<T>) + (FILL ? (size_t)kTileMaskWords * sizeof(unsigned) + (size_t)(kTileThreads / 32) * kTileList * 2 : 0);
-}
 
 __global__ void batch_to_ptr_kernel(const int64_t *__restrict__ batch, int64_t N, int64_t B, int64_t *__restrict__ ptr) {
     const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1909,29 +1449,19 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
     auto *group_ptr = (int32_t *)(w + L.group_ptr);
     const T r2 = (T)(r * r);
     const int nbr_grid = grid_for(N, kNbrWarps, 32);
-    // the tile kernels take structures with a cell grid and at most kCapBits points (none when pairs are excluded); a batch
+    // the block kernels take structures with a cell grid and at most kCapBits points (none when pairs are excluded); a batch
     // of small structures only (fewer points than one cell-grid structure needs, on average) cannot hold one
     const bool tiles = !ex.ptr && N > kBruteMax;
-    static bool configured[64][4] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const int variant = (sizeof(T) == 8 ? 2 : 0) + (fill ? 1 : 0);
-    if (tiles && dev >= 0 && dev < 64 && !configured[dev][variant]) {
-        cudaError_t e = fill ? cudaFuncSetAttribute(neighbours_tile_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem_bytes<T, true>())
-                             : cudaFuncSetAttribute(neighbours_tile_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem_bytes<T, false>());
-        if (e != cudaSuccess) return check_launch();
-        configured[dev][variant] = true;
-    }
     const int32_t *n_plain = tiles ? group_ptr + B + 1 : nullptr;
     if (!fill) {
         build_cells_kernel<T><<<grid_for(B, 1, 8), kBuildThreads, 0, st>>>(pos, ptr, B, (T)r, tiles ? 1 : 0, spos, cellparam, cell_of, cell_start, struct_of);
         if (tiles) {
             group_scan_kernel<<<1, kScanBlock, 0, st>>>(cellparam, B, group_ptr);
             int grid = 0;
-            const int rc = block_kernel_grid<T, false>(&grid);
+            const int rc = count_kernel_grid<T>(&grid);
             if (rc != MLCGB_OK) return rc;
-            neighbours_block_kernel<T, false><<<grid, 32, BlockSmem<T, false>::total, st>>>(
-                pos, ptr, B, r2, max_nn, loop, rule, spos, cellparam, cell_start, group_ptr, deg, nullptr, out, status);
+            neighbours_block_count_kernel<T><<<grid, 32, CountSmem<T>::total, st>>>(ptr, B, r2, max_nn, loop, rule, spos, cellparam, cell_start,
+                                                                                 group_ptr, deg, status);
         }
         if (ex.ptr)
             neighbours_kernel<T, false, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
