@@ -897,7 +897,7 @@ def run_ours(args):
         per_launch = seg["ms"] / seg["calls"]
         moved, _ = kernel_work("seg_mul_sum", n_edges, P, N, F, R)
         s_tr, s_src = traffic_of("seg_mul_sum")
-        cfconv = dict(kernel="seg_mul_sum_kernel<float,32,true,true> (CFConv gather * filter, segmented sum; filters stored once per pair)", bound="hbm",
+        cfconv = dict(kernel="seg_mul_sum_async_kernel (CFConv gather * filter, segmented sum; filters stored once per pair, rows through a cp.async ring)", bound="hbm",
                       achieved=moved / per_launch / 1e6, peak=hbm_peak, unit="GB/s", frac=moved / per_launch / 1e6 / hbm_peak,
                       edges_per_s=n_edges / (per_launch / 1e3), reference_algorithm_bytes_per_edge=per_edge,
                       reference_algorithm_GBps=per_edge * n_edges / per_launch / 1e6, reference_algorithm_frac=per_edge * n_edges / per_launch / 1e6 / hbm_peak,
