@@ -94,6 +94,22 @@ def test_uniform_cube_cell_path(dtype):
     assert 40 < deg.mean() < 90 and not res["status"]
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("loop", [False, True])
+def test_dense_and_uneven_structures(dtype, loop):
+    """More candidates than one stage of the block kernels holds, more than 32 centres in a block of cells, hit lists
+    that are written out several times, neighbour caps that bite: a dense cube, and a blob inside a sparse cloud."""
+    rng = np.random.default_rng(11)
+    dense = (rng.random((3000, 3)) * 10).astype(dtype)
+    blob = np.concatenate([rng.random((2500, 3)) * 40, 18 + rng.random((1500, 3)) * 4]).astype(dtype)
+    blob = blob[rng.permutation(len(blob))]
+    for pos, r in ((dense, 4.0), (blob, 5.0)):
+        ptr = np.array([0, len(pos)], np.int64)
+        for max_nn in (1000, 40):
+            check_against_oracle(pos, ptr, r, max_nn, loop, "cluster")
+        check_against_oracle(pos, ptr, r, 9, loop, "native")
+
+
 def test_structure_larger_than_one_bitmask_window():
     rng = np.random.default_rng(1)
     sizes = [20000, 9000]
