@@ -1685,7 +1685,7 @@ int mlcgb_pair_index(const int32_t *sel, const int32_t *twin, int64_t P, int32_t
 namespace mlcgb {
 constexpr int64_t kStaticMaxPoints = 65536;
 constexpr int64_t kStaticMaxStructures = 8192;
-constexpr size_t kStaticScratchBytes = (size_t)3 << 20;   // >= ws_layout(65536, 8192, float64).total
+constexpr size_t kStaticScratchBytes = (size_t)13 << 18;  // 3.25 MB >= ws_layout(65536, 8192, float64).total = 3 212 288
 static __device__ __align__(256) unsigned char g_radius_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;

@@ -83,3 +83,13 @@ def test_limits_are_refused_with_an_error_code():
     rc = lib.mlcgb_radius_graph_static(big.data_ptr(), 0, big.data_ptr(), 65537, 1, 1.0, 10, 0, 1, big.data_ptr(), big.data_ptr(), 0,
                                        big.data_ptr(), ctypes.byref(n), big.data_ptr(), torch.cuda.current_stream().cuda_stream)
     assert rc == -4
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_the_largest_batch_the_scratch_is_sized_for(dtype):
+    """65 536 points in 8 192 structures, the documented limits at once: accepted in both dtypes, same list as the regular path."""
+    pos, ptr = inputs([8] * 8192, 6.0, dtype, 4)
+    want_ei, want_off, _ = regular_path(pos, ptr, 3.0, 1000, False, 1)
+    E = want_ei.shape[1]
+    rc, n_edges, ei, off, _ = call_static(pos, ptr, 3.0, 1000, False, 1, capacity=E)
+    assert rc == 0 and n_edges == E and torch.equal(ei, want_ei) and torch.equal(off, want_off)
