@@ -823,11 +823,13 @@ neighbours_block_count_kernel(const int64_t *__restrict__ ptr, int64_t B, T r2, 
 
 // FILL with the candidates of an item split between the warps of a block (kFillWarps of them): the same work item, the same
 // staged list, lane l of every warp the same centre, warp w the w-th part of the (ascending) list.  A centre's edges are then
-// warp 0's hits followed by warp 1's ...: a warp writes its own hits, after the warps before it have published how many
-// they had (named barrier w: they arrive when they are through, warp w waits before its first emission; warp 0 never
-// waits, so nobody waits in a circle).  Twice the warps per staged list hide twice the latency: the staging, the
-// emission and the pushes are chains of dependent shared-memory operations, and shared memory, not registers, is what
-// limits the blocks per SM.
+// warp 0's hits followed by warp 1's: each warp writes its own, warp 1 after warp 0 has published how many it had.  Warp 0
+// publishes its counts when its tests are done, before it writes its own edges, and arrives on a named barrier; warp 1 waits
+// on that barrier before its first emission.  Warp 0 never waits for warp 1 inside a window, so nobody waits in a circle, and
+// both warps write at the same time.  Twice the warps per staged list hide twice the latency: the staging, the pushes and
+// the emission are chains of dependent shared-memory operations, and shared memory, not registers, is what limits the
+// blocks per SM.  The emission takes what it needs of a centre (count, place of the centre's own entry, first slot, index)
+// from a table in shared memory, half a warp per centre, and reads the next pair's entries while this pair's edges go out.
 constexpr int kFillWarps = 2;
 constexpr int kFillList = 80;                              // entries of a warp's hit list of a centre between two emissions
 constexpr int kFillListStride = kFillList + 2;             // (in 16-bit entries: an odd number of words, so that lanes at the same
