@@ -49,6 +49,7 @@ constexpr int kScanBlock = 1024;
 // layer), else by the warp kernels.
 struct CellParam { int gx, gy, gz, use_cells, reach, tile, ngroups, pad; };
 
+constexpr int kHitWordsF32 = 24, kHitWordsF64 = 12;          // block kernels: words of a centre's hit mask (= staged candidates / 32)
 constexpr int kBlkMaxBY = 8;                               // block kernels: rows of cells in a block, at most
 constexpr int kBlkTargetCentres = 21;                      // mean number of centres per block the block's size aims at
 
@@ -62,7 +63,7 @@ __device__ __forceinline__ double4 make_v4(double x, double y, double z, int i) 
 }
 
 struct WsLayout {
-    size_t spos, cellparam, cell_of, cell_start, struct_of, bsum, group_ptr, total;
+    size_t spos, cellparam, cell_of, cell_start, struct_of, bsum, group_ptr, hits, cidx, total;
 };
 static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 static WsLayout ws_layout(int64_t N, int64_t B, int dtype) {
@@ -75,7 +76,9 @@ static WsLayout ws_layout(int64_t N, int64_t B, int dtype) {
     L.cell_start = o;  o += align256((size_t)(N + B) * 4);
     L.struct_of = o;   o += align256((size_t)N * 4);
     L.bsum = o;        o += align256((size_t)((N + kScanBlock - 1) / kScanBlock + 1) * 8);
-    L.group_ptr = o;   o += align256((size_t)(B + 2) * 4);
+    L.group_ptr = o;   o += align256((size_t)(B + 3) * 4);
+    L.hits = o;        o += align256((size_t)N * (dtype == MLCGB_F64 ? kHitWordsF64 : kHitWordsF32) * 4);   // hit words per point
+    L.cidx = o;        o += align256((size_t)N * 4);                      // local index of every cell-sorted point (= spos[].w, compact)
     L.total = o;
     return L;
 }
@@ -85,7 +88,7 @@ template <typename T>
 __global__ void __launch_bounds__(kBuildThreads)
 build_cells_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, T rcut, int allow_tile,
                    V4<T> *__restrict__ spos, CellParam *__restrict__ cellparam, int32_t *__restrict__ cell_of,
-                   int32_t *__restrict__ cell_start, int32_t *__restrict__ struct_of) {
+                   int32_t *__restrict__ cell_start, int32_t *__restrict__ struct_of, int32_t *__restrict__ cidx) {
     __shared__ int counts[kSmemCells + 1];
     __shared__ T red[6][kBuildThreads / 32];
     __shared__ T s_org[3];
@@ -223,6 +226,7 @@ build_cells_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, i
             const int c = cell_of[lo + i];
             const int slot = atomicAdd(&counts[c], 1);
             spos[lo + slot] = make_v4(pos[(lo + i) * 3], pos[(lo + i) * 3 + 1], pos[(lo + i) * 3 + 2], i);
+            cidx[lo + slot] = i;
         }
         __syncthreads();
     }
@@ -521,7 +525,8 @@ static void launch_scan(const int32_t *deg, int64_t N, int64_t *bsum, int64_t *o
 
 // ---------------------------------------------------------------------------- work items of the block kernels
 // group_ptr[b] = work items of the structures before b (exclusive scan of CellParam::ngroups), group_ptr[B] = all of them,
-// group_ptr[B + 1] = structures that have no work items (left to the warp kernels)
+// group_ptr[B + 1] = structures that have no work items (left to the warp kernels), group_ptr[B + 2] = 0: set by the
+// counting kernel when an item has more candidates than one stage holds (such items keep no hit masks)
 __global__ void __launch_bounds__(kScanBlock) group_scan_kernel(const CellParam *__restrict__ cellparam, int64_t B, int32_t *__restrict__ group_ptr) {
     __shared__ int64_t s_warp[33];
     int64_t carry = 0;
@@ -538,6 +543,7 @@ __global__ void __launch_bounds__(kScanBlock) group_scan_kernel(const CellParam 
     if (threadIdx.x == 0) {
         group_ptr[B] = (int32_t)carry;
         group_ptr[B + 1] = plain;
+        group_ptr[B + 2] = 0;
     }
 }
 
@@ -652,27 +658,66 @@ __device__ __forceinline__ int centre_at(int q, const ItemRuns &r, int rows) {
     return kc;
 }
 
+template <typename T> struct HitWords { static constexpr int value = BlockCap<T>::value / 32; };
+static_assert(HitWords<float>::value == kHitWordsF32 && HitWords<double>::value == kHitWordsF64, "the workspace is sized with these");
+
 template <typename T>
 struct CountSmem {
     static constexpr int kCap = BlockCap<T>::value;
     static constexpr size_t cand = 0;                                         // V4<T>[kCap]: staged candidates
     static constexpr size_t src = cand + (size_t)kCap * sizeof(V4<T>);        // u16[kCap]: where the candidates of a stage come from
-    static constexpr size_t rows = src + (size_t)kCap * 2;                    // int k0[64], off[65]
+    static constexpr size_t ssrc = src + (size_t)kCap * 2;                    // u16[kCap]: the same in ascending order of index
+    static constexpr size_t mask = ssrc + (size_t)kCap * 2;                   // u32[kCapBits / 32]: marks of the candidates' indices
+    static constexpr size_t pref = mask + kCapBits / 8;                       // u16[kCapBits / 32]: marks before a word
+    static constexpr size_t rows = pref + kCapBits / 16;                      // int k0[64], off[65]
     static constexpr size_t total = (rows + 544 + 31) & ~(size_t)31;
 };
 
+// The marks of an item's candidates (a bit per local index) -> pref[w] = marks before word w, by one warp.
+__device__ __forceinline__ void rank_marks(const unsigned *mask, unsigned short *pref, int nwords, int lane) {
+    constexpr int kPer = kCapBits / 32 / 32;         // words per lane
+    int cnt[kPer], sum = 0;
+#pragma unroll
+    for (int q = 0; q < kPer; q++) {
+        const int w = kPer * lane + q;
+        cnt[q] = w < nwords ? __popc(mask[w]) : 0;
+        sum += cnt[q];
+    }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    int run = incl - sum;
+#pragma unroll
+    for (int q = 0; q < kPer; q++) {
+        const int w = kPer * lane + q;
+        if (w < nwords) pref[w] = (unsigned short)run;
+        run += cnt[q];
+    }
+}
+
+// COUNT.  An item whose candidates fit one stage (the rule) is staged in ascending order of the candidates' indices, as FILL
+// needs them: the centre's hits, a bit per staged candidate, go to the workspace (hits[point][word], the centre's own bit
+// cleared unless loops are wanted), and the filling pass only expands them: the distance tests are done once.  The degree
+// under the neighbour-cap rule comes from the same words (hits before / after the centre's own place).  An item with more
+// candidates is counted in windows, as they come, sets the flag word after the work-item prefix and leaves no masks.
 template <typename T>
-__global__ void __launch_bounds__(32, 14)                  // (shared memory allows 14 one-warp blocks per SM)
+__global__ void __launch_bounds__(32, 12)                  // (shared memory allows 12 one-warp blocks per SM)
 neighbours_block_count_kernel(const int64_t *__restrict__ ptr, int64_t B, T r2, int64_t max_nn, int loop, int rule,
                               const V4<T> *__restrict__ spos, const CellParam *__restrict__ cellparam,
-                              const int32_t *__restrict__ cell_start, const int32_t *__restrict__ group_ptr, int32_t *__restrict__ deg,
-                              int32_t *__restrict__ status) {
+                              const int32_t *__restrict__ cell_start, int32_t *__restrict__ group_ptr, int32_t *__restrict__ deg,
+                              const int32_t *__restrict__ cidx, unsigned *__restrict__ hits, int32_t *__restrict__ status) {
     using S = CountSmem<T>;
-    constexpr int kCap = S::kCap, kPerLane = kCap / 32;
+    constexpr int kCap = S::kCap, kPerLane = kCap / 32, kWords = HitWords<T>::value;
     extern __shared__ __align__(32) unsigned char blk_smem[];
     const int lane = threadIdx.x;
     V4<T> *cand = reinterpret_cast<V4<T> *>(blk_smem + S::cand);
     unsigned short *src = reinterpret_cast<unsigned short *>(blk_smem + S::src);
+    unsigned short *ssrc = reinterpret_cast<unsigned short *>(blk_smem + S::ssrc);
+    unsigned *mask = reinterpret_cast<unsigned *>(blk_smem + S::mask);
+    unsigned short *pref = reinterpret_cast<unsigned short *>(blk_smem + S::pref);
     int *s_k0 = reinterpret_cast<int *>(blk_smem + S::rows), *s_off = s_k0 + 64;
     const unsigned full = 0xffffffffu;
     const int G = group_ptr[B];
@@ -729,17 +774,14 @@ neighbours_block_count_kernel(const int64_t *__restrict__ ptr, int64_t B, T r2, 
             }
             __syncwarp();
         };
-        // candidates [c0, c0 + kCap) as they come, copied without passing through registers, all copies in flight together
-        auto stage_plain = [&](int c0) {
-            const int mc = min(kCap, M - c0);
-            if (c0 > 0 || !first_src) build_src(c0);
-            first_src = false;
+        // the points from[f] names, f < mc, into the stage without passing through registers, all copies in flight together
+        auto copy_in = [&](const unsigned short *from_idx, int mc) {
             const uint32_t dst0 = (uint32_t)__cvta_generic_to_shared(cand);
 #pragma unroll
             for (int u = 0; u < kPerLane; u++) {
                 const int f = u * 32 + lane;
                 if (f < mc) {
-                    const V4<T> *from = sp + src[f];
+                    const V4<T> *from = sp + from_idx[f];
 #pragma unroll
                     for (int h = 0; h < (int)sizeof(V4<T>) / 16; h++)
                         asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst0 + (uint32_t)(f * sizeof(V4<T>) + 16 * h)),
@@ -754,7 +796,51 @@ neighbours_block_count_kernel(const int64_t *__restrict__ ptr, int64_t B, T r2, 
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncwarp();
         };
-        if (nc > 0 && single) stage_plain(0);
+        auto stage_plain = [&](int c0) {               // candidates [c0, c0 + kCap) as they come
+            if (c0 > 0 || !first_src) build_src(c0);
+            first_src = false;
+            copy_in(src, min(kCap, M - c0));
+        };
+        auto rank_of = [&](int j) { return (int)pref[j >> 5] + __popc(mask[j >> 5] & ((1u << (j & 31)) - 1u)); };
+        if (nc > 0 && single) {
+            // ---- in ascending order of index: mark the indices, rank the marks, sources by rank, copy
+            const int nwords = (q.n + 31) >> 5;                  // (n <= kCapBits)
+            for (int w = lane; w < nwords; w += 32) mask[w] = 0u;
+            __syncwarp();
+            // the candidates' indices, by asynchronous copies (all in flight together) into the stage, which is still empty;
+            // the loops are not unrolled: the instruction cache is small
+            const int32_t *ci = cidx + q.lo;
+            int *sj = reinterpret_cast<int *>(cand);
+            const uint32_t sj0 = (uint32_t)__cvta_generic_to_shared(sj);
+#pragma unroll 4
+            for (int f = lane; f < M; f += 32)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sj0 + 4u * (uint32_t)f), "l"(ci + src[f]) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncwarp();
+#pragma unroll 4
+            for (int f = lane; f < M; f += 32) {
+                const int j = sj[f];
+                atomicOr(&mask[j >> 5], 1u << (j & 31));
+            }
+            __syncwarp();
+            rank_marks(mask, pref, nwords, lane);
+            __syncwarp();
+#pragma unroll 1
+            for (int f0 = lane; f0 < M; f0 += 256) {
+                // (eight ranks first, then their stores: a load of shared memory cannot be moved above an earlier store)
+                int rk[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) rk[u] = rank_of(sj[min(f0 + 32 * u, M - 1)]);
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    if (f0 + 32 * u < M) ssrc[rk[u]] = src[f0 + 32 * u];
+            }
+            __syncwarp();
+            copy_in(ssrc, M);
+        } else if (nc > 0 && lane == 0) {
+            atomicOr(group_ptr + B + 2, 1);                      // an item without hit masks: the filling pass tests it again
+        }
         // the next item's tables: read under this item's tests
         if (item + 1 < min(item_end, q.item_hi)) {
             ahead = load_runs(cs, q, block_geom(q, item + 1), lane);
@@ -771,34 +857,58 @@ neighbours_block_count_kernel(const int64_t *__restrict__ ptr, int64_t B, T r2, 
             // (a lane without a centre sits at infinity: no hits)
             const T xi = active ? pc.x : T(INFINITY), yi = active ? pc.y : T(INFINITY), zi = active ? pc.z : T(INFINITY);
             RPHASE(13)
-            int cnt = 0, cnt_lo = 0;
-            auto count_windows = [&](auto with_lo_tag) {
-                constexpr bool kLo = decltype(with_lo_tag)::value;
-                cnt = cnt_lo = 0;
-                for (int wb = 0; wb < M; wb += kCap) {
-                    if (!single) stage_plain(wb);
-                    const int mw = min(kCap, M - wb), nw = (mw + 31) >> 5;
-                    for (int w = 0; w < nw; w++) {
-                        const V4<T> *cw = cand + w * 32;
+            const int self_hit = dist2_rn(xi, yi, zi, xi, yi, zi) < r2 ? 1 : 0;      // (the centre is one of its candidates)
+            int cnt = 0, cnt_lo = 0;                             // hits (the centre included), hits below the centre's own index
+            if (single) {
+                const int nw = (M + 31) >> 5;
+                const int self_rank = active ? rank_of(il) : -1, self_w = self_rank >> 5;
+                const unsigned self_bit = 1u << (self_rank & 31);
+                unsigned *my_words = hits + (size_t)(q.lo + il) * kWords;
+                for (int w = 0; w < nw; w++) {
+                    const V4<T> *cw = cand + w * 32;
+                    unsigned word = 0u;
+#pragma unroll
+                    for (int u = 0; u < 32; u++) {
+                        const V4<T> p = cw[u];
+                        const T d2 = dist2_rn(xi, yi, zi, p.x, p.y, p.z);
+                        if (d2 < r2) word |= 1u << u;
+                    }
+                    cnt += __popc(word);
+                    if (w < self_w) cnt_lo += __popc(word);
+                    if (w == self_w) {
+                        cnt_lo += __popc(word & (self_bit - 1u));
+                        if (!loop) word &= ~self_bit;
+                    }
+                    if (active) my_words[w] = word;
+                }
+            } else {
+                auto count_windows = [&](auto with_lo_tag) {
+                    constexpr bool kLo = decltype(with_lo_tag)::value;
+                    cnt = cnt_lo = 0;
+                    for (int wb = 0; wb < M; wb += kCap) {
+                        stage_plain(wb);
+                        const int mw = min(kCap, M - wb), nw = (mw + 31) >> 5;
+                        for (int w = 0; w < nw; w++) {
+                            const V4<T> *cw = cand + w * 32;
 #pragma unroll 8
-                        for (int u = 0; u < 32; u++) {
-                            const V4<T> p = cw[u];
-                            const T d2 = dist2_rn(xi, yi, zi, p.x, p.y, p.z);
-                            if (d2 < r2) {
-                                cnt++;
-                                if (kLo) cnt_lo += idx_of(p) < il;
+                            for (int u = 0; u < 32; u++) {
+                                const V4<T> p = cw[u];
+                                const T d2 = dist2_rn(xi, yi, zi, p.x, p.y, p.z);
+                                if (d2 < r2) {
+                                    cnt++;
+                                    if (kLo) cnt_lo += idx_of(p) < il;
+                                }
                             }
                         }
+                        __syncwarp();
                     }
-                    __syncwarp();
-                }
-            };
-            count_windows(std::false_type{});
+                };
+                count_windows(std::false_type{});
+                // hits below the centre's own index matter only where the neighbour cap bites: counted in a second walk
+                const bool over = active && (int64_t)(loop ? cnt : cnt - self_hit) > max_nn;
+                if (__any_sync(full, over)) count_windows(std::true_type{});
+            }
             RPHASE(14)
-            const int self_hit = dist2_rn(xi, yi, zi, xi, yi, zi) < r2 ? 1 : 0;      // (the centre is one of its candidates)
-            // hits below the centre's own index matter only where the neighbour cap bites: counted in a second walk
-            const bool over = active && (int64_t)(loop ? cnt : cnt - self_hit) > max_nn;
-            if (__any_sync(full, over)) count_windows(std::true_type{});
             if (active) {
                 const int64_t nlo = cnt_lo, nhi = cnt - self_hit - cnt_lo;
                 int64_t total, k;
@@ -879,6 +989,7 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
     unsigned short *my_hits = warp_hits + lane * kFillListStride;
     const unsigned full = 0xffffffffu;
     const int G = group_ptr[B];
+    if (group_ptr[B + 2] == 0) return;                     // every item left its hit masks: the expanding kernel fills them all
     // (the output pointers as scalars: read through the parameter struct inside the lambdas below they end up in local
     //  memory, and with all of the L1 given to shared memory every such read is a trip to the L2)
     int64_t *const o_row0 = out.row0, *const o_row1 = out.row1, *const o_batch = out.mapping_batch;
@@ -918,6 +1029,9 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
             }
             const int excl = incl - rn.len[0] - rn.len[1];
             M = __shfl_sync(full, incl, 31);
+            // (an item that fits one stage left its hit masks: the expanding kernel's.  Before anything of it is written to
+            //  shared memory: the warps meet only in the items this kernel takes.  The same in every warp.)
+            if (M <= kCap) continue;
             const int h = warp & 1, off = excl + (h ? rn.len[0] : 0), k0h = h ? rn.k0[1] : rn.k0[0], lenh = h ? rn.len[1] : rn.len[0];
             if (nc > 0 && warp < 2) {
                 if (2 * lane + h < nrows) { s_k0[2 * lane + h] = k0h; s_off[2 * lane + h] = off; }
@@ -928,7 +1042,7 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
         }
         __syncthreads();
         RPHASE(1)
-        const bool single = M <= kCap;
+        const bool single = false;
         bool src_fresh = true;                               // src[] holds the sources of candidates [0, kCap)
 
         auto build_src = [&](int c0) {                       // sources of candidates [c0, c0 + kCap) of the concatenated runs
@@ -1157,6 +1271,246 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
             }
         }
     }
+}
+
+// FILL for the items whose hit masks the counting pass has left in the workspace: no distance tests.  A warp takes an item,
+// puts the indices of the item's candidates in ascending order (the marks and ranks of the counting pass again, without the
+// points themselves), and every lane turns its centre's words into the centre's list of neighbours, which half a warp
+// per centre then writes out, consecutive lanes on consecutive slots.
+constexpr int kExpList = 128;                              // entries of a centre's list between two emissions
+constexpr int kExpListStride = kExpList + 2;               // (16-bit entries: an odd number of words)
+
+template <typename T>
+struct ExpandSmem {
+    static constexpr int kCap = BlockCap<T>::value;
+    static constexpr size_t sidx = 0;                                          // u16[kCap]: the candidates' local indices, ascending
+    static constexpr size_t src = sidx + (size_t)kCap * 2;                     // u16[kCap]: where the candidates come from
+    static constexpr size_t mask = src + (size_t)kCap * 2;                     // u32[kCapBits / 32]
+    static constexpr size_t pref = mask + kCapBits / 8;                        // u16[kCapBits / 32]
+    // once the indices are in order, src / mask / pref are free: the centres' hit words, u32[kCap / 32][32], go there
+    static constexpr size_t words = src;
+    static_assert((size_t)kCap * 4 <= (size_t)kCap * 2 + kCapBits / 8 + kCapBits / 16, "the hit words must fit the staging tables");
+    static constexpr size_t lists = pref + kCapBits / 16;                      // u16[32][kExpListStride]; while staging: int[kCap] indices
+    static_assert((size_t)kCap * 4 <= (size_t)32 * kExpListStride * 2, "the staged indices must fit the space of the lists");
+    static constexpr size_t par = (lists + (size_t)32 * kExpListStride * 2 + 15) & ~(size_t)15;   // int4[32]
+    static constexpr size_t total = (par + 32 * 16 + 31) & ~(size_t)31;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(32, 16)
+neighbours_block_expand_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, int loop,
+                               const V4<T> *__restrict__ spos, const CellParam *__restrict__ cellparam,
+                               const int32_t *__restrict__ cell_start, const int32_t *__restrict__ group_ptr,
+                               const int32_t *__restrict__ cidx, const unsigned *__restrict__ hits, const int64_t *__restrict__ offsets,
+                               FillOut out) {
+    using S = ExpandSmem<T>;
+    constexpr int kCap = S::kCap, kWords = HitWords<T>::value;
+    extern __shared__ __align__(32) unsigned char blk_smem[];
+    const int lane = threadIdx.x;
+    unsigned short *src = reinterpret_cast<unsigned short *>(blk_smem + S::src);
+    unsigned short *sidx = reinterpret_cast<unsigned short *>(blk_smem + S::sidx);
+    unsigned *mask = reinterpret_cast<unsigned *>(blk_smem + S::mask);
+    unsigned short *pref = reinterpret_cast<unsigned short *>(blk_smem + S::pref);
+    unsigned short *all_lists = reinterpret_cast<unsigned short *>(blk_smem + S::lists);
+    unsigned short *my_list = all_lists + lane * kExpListStride;
+    int4 *s_par = reinterpret_cast<int4 *>(blk_smem + S::par);
+    unsigned *my_hw = reinterpret_cast<unsigned *>(blk_smem + S::words) + lane;          // word w of this lane's centre at [32 w]
+    const unsigned full = 0xffffffffu;
+    const int G = group_ptr[B];
+    int64_t *const o_row0 = out.row0, *const o_row1 = out.row1, *const o_batch = out.mapping_batch;
+    T *const o_dist = reinterpret_cast<T *>(out.distance);
+    int32_t *const o_row0_32 = out.row0_32, *const o_row1_32 = out.row1_32;
+
+    RPHASE_DECL
+    ItemStruct q;
+    ItemRuns ahead;
+    bool have_ahead = false;
+    const int nruns = (G + kItemRun - 1) / kItemRun;
+    for (int run = blockIdx.x; run < nruns; run += gridDim.x)
+    for (int item = run * kItemRun, item_end = min(G, (run + 1) * kItemRun); item < item_end; item++) {
+        RPHASE(0)
+        find_struct(q, item, B, ptr, cellparam, group_ptr, lane);
+        const BlockGeom o = block_geom(q, item);
+        const int b = q.b, rows = o.y1 - o.y0;
+        const int64_t lo = q.lo;
+        const int32_t *cs = cell_start + lo + b;
+        const V4<T> *sp = spos + lo;
+        const ItemRuns rn = have_ahead ? ahead : load_runs(cs, q, o, lane);
+        have_ahead = false;
+        const int nc = warp_sum(rn.run_len);
+        const int kc0 = centre_at(lane, rn, rows);
+        const V4<T> pc0 = sp[max(kc0, 0)];                  // the first 32 centres' points: on their way during the staging
+        int incl = rn.len[0] + rn.len[1];
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) {
+            const int t = __shfl_up_sync(full, incl, s);
+            if (lane >= s) incl += t;
+        }
+        const int excl = incl - rn.len[0] - rn.len[1], M = __shfl_sync(full, incl, 31);
+        RPHASE(1)
+        const bool mine = nc > 0 && M <= kCap;              // (items with more candidates have no masks: the testing kernel fills them)
+        if (mine) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int off = excl + (h ? rn.len[0] : 0), kb = min(rn.len[h], kCap - off);
+                for (int k = 0; k < kb; k++) src[off + k] = (unsigned short)(rn.k0[h] + k);
+            }
+            const int nwords = (q.n + 31) >> 5;
+            for (int w = lane; w < nwords; w += 32) mask[w] = 0u;
+            __syncwarp();
+            // the candidates' indices, by asynchronous copies (all in flight together) into the space of the lists, empty now;
+            // the loops are not unrolled: the instruction cache is small
+            const int32_t *ci = cidx + lo;
+            int *sj = reinterpret_cast<int *>(all_lists);
+            const uint32_t sj0 = (uint32_t)__cvta_generic_to_shared(sj);
+#pragma unroll 4
+            for (int f = lane; f < M; f += 32)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sj0 + 4u * (uint32_t)f), "l"(ci + src[f]) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncwarp();
+#pragma unroll 4
+            for (int f = lane; f < M; f += 32) {
+                const int j = sj[f];
+                atomicOr(&mask[j >> 5], 1u << (j & 31));
+            }
+            __syncwarp();
+            rank_marks(mask, pref, nwords, lane);
+            __syncwarp();
+#pragma unroll 1
+            for (int f0 = lane; f0 < M; f0 += 256) {
+                // (eight ranks first, then their stores: a load of shared memory cannot be moved above an earlier store)
+                int jj[8], rk[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    jj[u] = sj[min(f0 + 32 * u, M - 1)];
+                    rk[u] = (int)pref[jj[u] >> 5] + __popc(mask[jj[u] >> 5] & ((1u << (jj[u] & 31)) - 1u));
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    if (f0 + 32 * u < M) sidx[rk[u]] = (unsigned short)jj[u];
+            }
+            __syncwarp();
+        }
+        if (item + 1 < min(item_end, q.item_hi)) {          // the next item's tables: read under this item's work
+            ahead = load_runs(cs, q, block_geom(q, item + 1), lane);
+            have_ahead = true;
+        }
+        RPHASE(2)
+        if (!mine) continue;
+        const int nw = (M + 31) >> 5;
+
+        for (int cp0 = 0; cp0 < nc; cp0 += 32) {
+            const int kc = cp0 == 0 ? kc0 : centre_at(cp0 + lane, rn, rows);
+            const bool active = kc >= 0;
+            const V4<T> pc = cp0 == 0 ? pc0 : sp[max(kc, 0)];
+            const int il = idx_of(pc);
+            int64_t base_off = 0;
+            int kept = 0;
+            const unsigned *my_words = hits + (size_t)(lo + il) * kWords;
+            if (active) {
+                base_off = offsets[lo + il];
+                kept = (int)(offsets[lo + il + 1] - base_off);
+            }
+            // the centre's words: loaded together, parked in shared memory (the loop over them below is not unrolled)
+            {
+                uint4 wd[kWords / 4];
+#pragma unroll
+                for (int g4 = 0; g4 < kWords / 4; g4++) {
+                    wd[g4] = make_uint4(0u, 0u, 0u, 0u);
+                    if (active && 4 * g4 < nw) wd[g4] = *reinterpret_cast<const uint4 *>(my_words + 4 * g4);
+                }
+#pragma unroll
+                for (int g4 = 0; g4 < kWords / 4; g4++) {
+                    my_hw[32 * (4 * g4)] = wd[g4].x; my_hw[32 * (4 * g4 + 1)] = wd[g4].y;
+                    my_hw[32 * (4 * g4 + 2)] = wd[g4].z; my_hw[32 * (4 * g4 + 3)] = wd[g4].w;
+                }
+            }
+            RPHASE(3)
+            // Entries [first, first + kExpList) of every centre's neighbours at a time (one round, unless a centre has more than
+            // kExpList neighbours to write): a word's set bits become entries of the centre's list, positions in the ascending
+            // candidate list, turned into indices when the edges are written (the centre's own bit was cleared by the counting
+            // pass unless loops are wanted).  One copy of the expansion and of the emission: the instruction cache is small.
+            for (int first = 0; __any_sync(full, first < kept); first += kExpList) {
+                int ord = 0;                                     // ordinal of the next set bit among the centre's neighbours
+#pragma unroll 1
+                for (int w = 0; w < nw; w++) {
+                    unsigned word = (ord < kept && ord < first + kExpList) ? my_hw[32 * w] : 0u;
+                    if (ord + __popc(word) <= first) {           // all of them before the window
+                        ord += __popc(word);
+                        word = 0u;
+                    }
+                    while (word) {
+                        const int t = __ffs(word) - 1;
+                        word &= word - 1;
+                        if ((unsigned)(ord - first) < (unsigned)kExpList) my_list[ord - first] = (unsigned short)(w * 32 + t);
+                        ord++;
+                    }
+                }
+                __syncwarp();
+                RPHASE(4)
+                // ---- the lists -> edges: half a warp per centre, what it needs of the centre from a table, the next pair's
+                //      entries read while this pair's edges are written
+                const int take = max(0, min(min(ord, kept) - first, kExpList));
+                const int64_t slot0 = base_off + first;
+                s_par[lane] = make_int4(take, il, (int)(uint32_t)slot0, (int)(slot0 >> 32));
+                __syncwarp();
+                const int hsel = lane >> 4, l16 = lane & 15;
+                int4 nxt = s_par[hsel];
+                for (int pp = 0; pp < 16; pp++) {
+                    const int4 cur = nxt;
+                    const int cc = 2 * pp + hsel;
+                    if (pp < 15) nxt = s_par[cc + 2];
+                    const int tk = cur.x;
+                    const int64_t slot_c = (int64_t)(((uint64_t)(uint32_t)cur.w << 32) | (uint32_t)cur.z), ic = lo + cur.y;
+                    T cxi = T(0), cyi = T(0), czi = T(0);
+                    if (o_dist) { cxi = __shfl_sync(full, pc.x, cc); cyi = __shfl_sync(full, pc.y, cc); czi = __shfl_sync(full, pc.z, cc); }
+                    const unsigned short *hl = all_lists + cc * kExpListStride;
+                    // (four rounds at a time: their list entries and indices are read together, then the edges written)
+                    for (int t0 = l16; t0 < tk; t0 += 64) {
+                        int jv[4];
+#pragma unroll
+                        for (int r = 0; r < 4; r++) jv[r] = t0 + 16 * r < tk ? (int)hl[t0 + 16 * r] : 0;
+#pragma unroll
+                        for (int r = 0; r < 4; r++) jv[r] = (int)sidx[jv[r]];
+#pragma unroll
+                        for (int r = 0; r < 4; r++) {
+                            const int t = t0 + 16 * r;
+                            if (t < tk) {
+                                const int64_t gj = lo + jv[r], slot = slot_c + t;
+                                if (o_row0) { o_row0[slot] = ic; o_row1[slot] = gj; }
+                                if (o_batch) o_batch[slot] = b;
+                                if (o_dist) o_dist[slot] = sqrt(dist2_rn(cxi, cyi, czi, pos[gj * 3], pos[gj * 3 + 1], pos[gj * 3 + 2]));
+                                if (o_row0_32) { o_row0_32[slot] = (int32_t)ic; o_row1_32[slot] = (int32_t)gj; }
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                RPHASE(5)
+            }
+        }
+        __syncwarp();
+    }
+}
+
+template <typename T>
+static int expand_kernel_grid(int *grid) {
+    static std::atomic<int> cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MLCGB_E_LAUNCH;
+    int per_sm = cached[dev].load(std::memory_order_relaxed);
+    if (per_sm == 0) {
+        const size_t bytes = ExpandSmem<T>::total;
+        if (cudaFuncSetAttribute(neighbours_block_expand_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess ||
+            cudaFuncSetAttribute(neighbours_block_expand_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, 100) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, neighbours_block_expand_kernel<T>, 32, bytes) != cudaSuccess)
+            return check_launch();
+        if (per_sm < 1) per_sm = 1;
+        cached[dev].store(per_sm, std::memory_order_relaxed);
+    }
+    *grid = kNumSM * per_sm;
+    return MLCGB_OK;
 }
 
 template <typename T>
@@ -1449,6 +1803,8 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
     auto *struct_of = (int32_t *)(w + L.struct_of);
     auto *bsum = (int64_t *)(w + L.bsum);
     auto *group_ptr = (int32_t *)(w + L.group_ptr);
+    auto *hits = (unsigned *)(w + L.hits);
+    auto *cidx = (int32_t *)(w + L.cidx);
     const T r2 = (T)(r * r);
     const int nbr_grid = grid_for(N, kNbrWarps, 32);
     // the block kernels take structures with a cell grid and at most kCapBits points (none when pairs are excluded); a batch
@@ -1456,14 +1812,14 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
     const bool tiles = !ex.ptr && N > kBruteMax;
     const int32_t *n_plain = tiles ? group_ptr + B + 1 : nullptr;
     if (!fill) {
-        build_cells_kernel<T><<<grid_for(B, 1, 8), kBuildThreads, 0, st>>>(pos, ptr, B, (T)r, tiles ? 1 : 0, spos, cellparam, cell_of, cell_start, struct_of);
+        build_cells_kernel<T><<<grid_for(B, 1, 8), kBuildThreads, 0, st>>>(pos, ptr, B, (T)r, tiles ? 1 : 0, spos, cellparam, cell_of, cell_start, struct_of, cidx);
         if (tiles) {
             group_scan_kernel<<<1, kScanBlock, 0, st>>>(cellparam, B, group_ptr);
             int grid = 0;
             const int rc = count_kernel_grid<T>(&grid);
             if (rc != MLCGB_OK) return rc;
             neighbours_block_count_kernel<T><<<grid, 32, CountSmem<T>::total, st>>>(ptr, B, r2, max_nn, loop, rule, spos, cellparam, cell_start,
-                                                                                 group_ptr, deg, status);
+                                                                                 group_ptr, deg, cidx, hits, status);
         }
         if (ex.ptr)
             neighbours_kernel<T, false, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
@@ -1475,7 +1831,12 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
     } else {
         if (tiles) {
             int grid = 0;
-            const int rc = fill_kernel_grid<T>(&grid);
+            int rc = expand_kernel_grid<T>(&grid);
+            if (rc != MLCGB_OK) return rc;
+            neighbours_block_expand_kernel<T><<<grid, 32, ExpandSmem<T>::total, st>>>(pos, ptr, B, loop, spos, cellparam, cell_start, group_ptr,
+                                                                                    cidx, hits, offsets, out);
+            // (the items that left no hit masks, if the counting pass met any: tested again)
+            rc = fill_kernel_grid<T>(&grid);
             if (rc != MLCGB_OK) return rc;
             neighbours_block_fill_kernel<T><<<grid, kFillWarps * 32, FillSmem<T>::total, st>>>(
                 pos, ptr, B, r2, loop, spos, cellparam, cell_start, group_ptr, offsets, out);
@@ -1687,7 +2048,7 @@ int mlcgb_pair_index(const int32_t *sel, const int32_t *twin, int64_t P, int32_t
 namespace mlcgb {
 constexpr int64_t kStaticMaxPoints = 65536;
 constexpr int64_t kStaticMaxStructures = 8192;
-constexpr size_t kStaticScratchBytes = (size_t)13 << 18;  // 3.25 MB >= ws_layout(65536, 8192, float64).total = 3 212 288
+constexpr size_t kStaticScratchBytes = (size_t)17 << 19;  // 8.5 MB >= ws_layout(65536, 8192, float32).total = 8 717 312 (float64: 6 620 160)
 static __device__ __align__(256) unsigned char g_radius_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
