@@ -9,14 +9,16 @@
 //        shared memory; the size of the blocks of cells the block kernels work on)
 //     -> neighbours_block_count for structures of up to 8192 points with a cell grid: a warp takes a
 //        block of cells of one layer (about 21 centres), stages every point within reach of the block
-//        in shared memory once, and each lane tests its centre against the whole staged list;
+//        in shared memory once, in ascending order of index, and each lane tests its centre against
+//        the whole staged list; the hits, a bit per staged candidate, stay in the workspace;
 //        neighbours<COUNT> for the rest (one warp per centre over the rows of cells within reach, each
 //        row a contiguous run of cell-sorted points; small structures scan all their points instead)
 //     -> exclusive scan of the degrees (three small kernels, no spin-waits)
-//     -> [host reads E] -> neighbours_block_fill (the same blocks, two warps each; the candidates staged
-//        in ascending order of their index, so that a lane's hits come out in the order the edges are
-//        listed in, without a sort) and neighbours<FILL> (hits are marked in a bitmask in shared memory
-//        indexed by local point index, per centre, then emitted in ascending order).
+//     -> [host reads E] -> neighbours_block_expand (the same blocks: the kept bits become edges, in
+//        the order the edges are listed in, without another distance test), neighbours_block_fill for
+//        the blocks with more candidates than a stage holds (tested again, two warps per block; it
+//        leaves at once when there are none), and neighbours<FILL> (hits are marked in a bitmask in
+//        shared memory indexed by local point index, per centre, then emitted in ascending order).
 #include "common.cuh"
 
 #include <atomic>
