@@ -947,15 +947,16 @@ def run_ours(args):
     if training is not None:
         extras = dict(extras or {}, training_step_256x73=training)
 
-    # kernels of the library per evaluation on the route the timed region takes (one library call for the model): radius graph 10
-    # (cells, work-item scan, count by the tile kernel and by the warp kernel, three scan kernels, clamp to the capacity, fill by
-    # both kernels), reverse-edge map / pair selection / pair index 5 (count of upper edges, three scan kernels, plan), distances
-    # 1, embedding 1, four per block forward (lin1, filter network, aggregation, the two chained layers), output network 3
-    # (layer + tanh, dot product, per-structure sum), its derivative 1, four per block backward (chained layers, aggregation,
-    # lin1 with the residual, filter network; two for the first block, whose input gradient nobody needs; the distance
-    # gradients of the blocks are added up by the filter kernels), distance backward 1
+    # kernels of the library per evaluation on the route the timed region takes (one library call for the model): radius graph 11
+    # (cells, work-item scan, count by the block kernel and by the warp kernel, three scan kernels, clamp to the capacity, fill by
+    # the expanding kernel, the testing block kernel and the warp kernel), reverse-edge map / pair selection / pair index 5 (count
+    # of upper edges, three scan kernels, plan), distances 1, embedding 1, four per block forward (lin1, filter network,
+    # aggregation, the two chained layers), output network 3 (layer + tanh, dot product, per-structure sum), its derivative 1,
+    # four per block backward (chained layers, aggregation, lin1 with the residual, filter network; two for the first block,
+    # whose input gradient nobody needs; the distance gradients of the blocks are added up by the filter kernels), distance
+    # backward 1
     L = WORKLOAD["interactions"]
-    launches_timed = args.steps * (10 + 5 + 1 + 1 + 4 * L + 3 + 1 + 4 * (L - 1) + 2 + 1)
+    launches_timed = args.steps * (11 + 5 + 1 + 1 + 4 * L + 3 + 1 + 4 * (L - 1) + 2 + 1)
     value = world * B * args.steps / (ms_total / 1e3)
     h2d = pos_h.numel() * 4 + types_h.numel() * 8 + batch_h.numel() * 8
     d2h = B * 4 + pos_h.numel() * 4
