@@ -61,8 +61,9 @@ int mlcgb_timeline_entry(int index, const char **name /* out: static string */, 
  * count: `count` builds the per-structure cell lists in the workspace, writes deg[N] and the
  * exclusive prefix sum offsets[N+1] (offsets[N] = E), and leaves in the workspace what it found (a
  * mask of each point's neighbours among the candidates it tested, about 100 bytes per float32
- * point); `fill`, given the same workspace untouched, writes the edges, centre-major with
- * neighbours ascending, which is the order both reference back ends produce.
+ * point); `fill`, given the same workspace untouched and the same pos, ptr, r and loop, writes the
+ * edges, centre-major with neighbours ascending, which is the order both reference back ends
+ * produce.
  * The pair test is fma(dz, dz, fma(dy, dy, dx*dx)) < (T)(r*r): the loop of radius.cu:126-130 as nvcc contracts it, which is
  * what the reference's compiled kernel decides by (compared with it pair by pair, tests/test_gpu_radius_reference.py).
  * ---------------------------------------------------------------------------------------------- */
