@@ -933,7 +933,8 @@ neighbours_block_count_kernel(const int64_t *__restrict__ ptr, int64_t B, T r2, 
     }
 }
 
-// FILL with the candidates of an item split between the warps of a block (kFillWarps of them): the same work item, the same
+// FILL for the items that left no hit masks (more candidates than a stage holds: tested again here, in windows of ranks), with
+// the candidates of an item split between the warps of a block (kFillWarps of them): the same work item, the same
 // staged list, lane l of every warp the same centre, warp w the w-th part of the (ascending) list.  A centre's edges are then
 // warp 0's hits followed by warp 1's: each warp writes its own, warp 1 after warp 0 has published how many it had.  Warp 0
 // publishes its counts when its tests are done, before it writes its own edges, and arrives on a named barrier; warp 1 waits
@@ -1044,7 +1045,6 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
         }
         __syncthreads();
         RPHASE(1)
-        const bool single = false;
         bool src_fresh = true;                               // src[] holds the sources of candidates [0, kCap)
 
         auto build_src = [&](int c0) {                       // sources of candidates [c0, c0 + kCap) of the concatenated runs
@@ -1062,7 +1062,7 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
             const int nwords = (n + 31) >> 5;                // (n <= kCapBits)
             for (int w = tid; w < nwords; w += kThreads) mask[w] = 0u;
             __syncthreads();
-            int jj[kPerThread];                              // local indices of this thread's candidates (single chunk)
+            int jj[kPerThread];                              // local indices of this thread's candidates of a chunk
             for (int c0 = 0; c0 < M; c0 += kCap) {
                 const int mc = min(kCap, M - c0);
                 if (c0 > 0 || !src_fresh) build_src(c0);
@@ -1113,29 +1113,21 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
                     }
                 }
             };
-            if (single) {
+            // (a chunk's sources that fall into the window go to their place in ssrc, chunk after chunk)
+            for (int c0 = 0; c0 < M; c0 += kCap) {
+                const int mc = min(kCap, M - c0);
+                build_src(c0);
+#pragma unroll
+                for (int u = 0; u < kPerThread; u++) jj[u] = idx_of(sp[src[min(u * kThreads + tid, mc - 1)]]);
 #pragma unroll
                 for (int u = 0; u < kPerThread; u++)
-                    if (u * kThreads + tid < M) ssrc[rank_of(jj[u])] = src[u * kThreads + tid];
+                    if (u * kThreads + tid < mc) {
+                        const int rw = rank_of(jj[u]) - wb;
+                        if (rw >= 0 && rw < kCap) ssrc[rw] = src[u * kThreads + tid];
+                    }
                 __syncthreads();
-                copy_sorted(M);
-            } else {
-                // (several chunks: a chunk's sources that fall into the window go to their place in ssrc, chunk after chunk)
-                for (int c0 = 0; c0 < M; c0 += kCap) {
-                    const int mc = min(kCap, M - c0);
-                    build_src(c0);
-#pragma unroll
-                    for (int u = 0; u < kPerThread; u++) jj[u] = idx_of(sp[src[min(u * kThreads + tid, mc - 1)]]);
-#pragma unroll
-                    for (int u = 0; u < kPerThread; u++)
-                        if (u * kThreads + tid < mc) {
-                            const int rw = rank_of(jj[u]) - wb;
-                            if (rw >= 0 && rw < kCap) ssrc[rw] = src[u * kThreads + tid];
-                        }
-                    __syncthreads();
-                }
-                copy_sorted(mw);
             }
+            copy_sorted(mw);
             {   // the rest of the last 32 staged entries: points that hit nothing
                 const int f = mw + tid;
                 if (f < ((mw + 31) & ~31)) cand[f] = far_point<T>();
@@ -1144,7 +1136,6 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();
         };
-        if (nc > 0 && single) stage(0);
         // the first 32 centres' places in the output (their points have arrived by now), read under the tests: the first
         // window is tested without looking at them
         int64_t base0 = 0, end0 = 0;
@@ -1181,7 +1172,7 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
 
             for (int wb = 0; wb < M; wb += kCap) {
                 if (wb > 0 && !__any_sync(full, active && emitted < (int)(end_off - base_off))) break;      // (the same in every warp)
-                if (!single) stage(wb);
+                stage(wb);
                 const int mw = min(kCap, M - wb), nw = (mw + 31) >> 5, nwh = (nw + kFillWarps - 1) / kFillWarps;
                 const int w_lo = min(warp * nwh, nw), w_hi = min(w_lo + nwh, nw);
                 uint32_t list_end = list0;                   // shared-memory address past the last entry of this lane's list
