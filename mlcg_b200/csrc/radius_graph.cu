@@ -53,7 +53,7 @@ struct CellParam { int gx, gy, gz, use_cells, reach, tile, ngroups, pad; };
 
 constexpr int kHitWordsF32 = 24, kHitWordsF64 = 12;          // block kernels: words of a centre's hit mask (= staged candidates / 32)
 constexpr int kBlkMaxBY = 8;                               // block kernels: rows of cells in a block, at most
-constexpr int kBlkTargetCentres = 21;                      // mean number of centres per block the block's size aims at
+constexpr int kBlkTargetCentres = 24;                      // mean number of centres per block the block's size aims at
 
 template <typename T> using V4 = typename Vec4<T>::type;
 
@@ -65,7 +65,7 @@ __device__ __forceinline__ double4 make_v4(double x, double y, double z, int i) 
 }
 
 struct WsLayout {
-    size_t spos, cellparam, cell_of, cell_start, struct_of, bsum, group_ptr, hits, cidx, total;
+    size_t spos, cellparam, cell_of, cell_start, struct_of, bsum, group_ptr, hits, cidx, item_flag, total;
 };
 static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 static WsLayout ws_layout(int64_t N, int64_t B, int dtype) {
@@ -81,6 +81,7 @@ static WsLayout ws_layout(int64_t N, int64_t B, int dtype) {
     L.group_ptr = o;   o += align256((size_t)(B + 3) * 4);
     L.hits = o;        o += align256((size_t)N * (dtype == MLCGB_F64 ? kHitWordsF64 : kHitWordsF32) * 4);   // hit words per point
     L.cidx = o;        o += align256((size_t)N * 4);                      // local index of every cell-sorted point (= spos[].w, compact)
+    L.item_flag = o;   o += align256((size_t)N);                          // per work item (at most one per cell, cells <= points): 1 = no hit masks
     L.total = o;
     return L;
 }
@@ -710,7 +711,8 @@ __global__ void __launch_bounds__(32, 12)                  // (shared memory all
 neighbours_block_count_kernel(const int64_t *__restrict__ ptr, int64_t B, T r2, int64_t max_nn, int loop, int rule,
                               const V4<T> *__restrict__ spos, const CellParam *__restrict__ cellparam,
                               const int32_t *__restrict__ cell_start, int32_t *__restrict__ group_ptr, int32_t *__restrict__ deg,
-                              const int32_t *__restrict__ cidx, unsigned *__restrict__ hits, int32_t *__restrict__ status) {
+                              const int32_t *__restrict__ cidx, unsigned *__restrict__ hits, unsigned char *__restrict__ item_flag,
+                              int32_t *__restrict__ status) {
     using S = CountSmem<T>;
     constexpr int kCap = S::kCap, kPerLane = kCap / 32, kWords = HitWords<T>::value;
     extern __shared__ __align__(32) unsigned char blk_smem[];
@@ -843,6 +845,7 @@ neighbours_block_count_kernel(const int64_t *__restrict__ ptr, int64_t B, T r2, 
         } else if (nc > 0 && lane == 0) {
             atomicOr(group_ptr + B + 2, 1);                      // an item without hit masks: the filling pass tests it again
         }
+        if (lane == 0) item_flag[item] = (nc > 0 && !single) ? 1 : 0;
         // the next item's tables: read under this item's tests
         if (item + 1 < min(item_end, q.item_hi)) {
             ahead = load_runs(cs, q, block_geom(q, item + 1), lane);
@@ -975,7 +978,7 @@ __global__ void __launch_bounds__(kFillWarps * 32, 8)      // (shared memory all
 neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restrict__ ptr, int64_t B, T r2, int loop,
                              const V4<T> *__restrict__ spos, const CellParam *__restrict__ cellparam,
                              const int32_t *__restrict__ cell_start, const int32_t *__restrict__ group_ptr,
-                             const int64_t *__restrict__ offsets, FillOut out) {
+                             const unsigned char *__restrict__ item_flag, const int64_t *__restrict__ offsets, FillOut out) {
     using S = FillSmem<T>;
     constexpr int kCap = S::kCap, kPerThread = kCap / (kFillWarps * 32), kThreads = kFillWarps * 32;
     extern __shared__ __align__(32) unsigned char blk_smem[];
@@ -1000,15 +1003,15 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
     int32_t *const o_row0_32 = out.row0_32, *const o_row1_32 = out.row1_32;
     RPHASE_DECL
 
-    // Items are dealt in runs of kItemRun consecutive ones: neighbouring blocks of one structure, whose structure look-up and
-    // parameters are then read once per run and whose candidates overlap in the L2.  (Every warp decodes the item for itself:
-    // the same loads, no exchange.)
+    // The items the counting pass has flagged, found 32 flags at a time.  (Every warp reads the flags and decodes an item for
+    // itself: the same loads, no exchange.)
     ItemStruct q;
     ItemRuns ahead;
     bool have_ahead = false;
-    const int nruns = (G + kItemRun - 1) / kItemRun;
-    for (int run = blockIdx.x; run < nruns; run += gridDim.x)
-    for (int item = run * kItemRun, item_end = min(G, (run + 1) * kItemRun); item < item_end; item++) {
+    const int item_end = 0;                                  // (nothing is read ahead here: the items are few and far between)
+    for (int base = blockIdx.x * 32; base < G; base += gridDim.x * 32)
+    for (unsigned todo = __ballot_sync(full, base + lane < G && item_flag[base + lane] != 0); todo; todo &= todo - 1) {
+        const int item = base + __ffs(todo) - 1;
         RPHASE(0)
         find_struct(q, item, B, ptr, cellparam, group_ptr, lane);
         const BlockGeom o = block_geom(q, item);
@@ -1798,6 +1801,7 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
     auto *group_ptr = (int32_t *)(w + L.group_ptr);
     auto *hits = (unsigned *)(w + L.hits);
     auto *cidx = (int32_t *)(w + L.cidx);
+    auto *item_flag = (unsigned char *)(w + L.item_flag);
     const T r2 = (T)(r * r);
     const int nbr_grid = grid_for(N, kNbrWarps, 32);
     // the block kernels take structures with a cell grid and at most kCapBits points (none when pairs are excluded); a batch
@@ -1812,7 +1816,7 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
             const int rc = count_kernel_grid<T>(&grid);
             if (rc != MLCGB_OK) return rc;
             neighbours_block_count_kernel<T><<<grid, 32, CountSmem<T>::total, st>>>(ptr, B, r2, max_nn, loop, rule, spos, cellparam, cell_start,
-                                                                                 group_ptr, deg, cidx, hits, status);
+                                                                                 group_ptr, deg, cidx, hits, item_flag, status);
         }
         if (ex.ptr)
             neighbours_kernel<T, false, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
@@ -1832,7 +1836,7 @@ static int radius_launch(bool fill, const void *pos_, const int64_t *ptr, int64_
             rc = fill_kernel_grid<T>(&grid);
             if (rc != MLCGB_OK) return rc;
             neighbours_block_fill_kernel<T><<<grid, kFillWarps * 32, FillSmem<T>::total, st>>>(
-                pos, ptr, B, r2, loop, spos, cellparam, cell_start, group_ptr, offsets, out);
+                pos, ptr, B, r2, loop, spos, cellparam, cell_start, group_ptr, item_flag, offsets, out);
         }
         if (ex.ptr)
             neighbours_kernel<T, true, true><<<nbr_grid, kNbrWarps * 32, 0, st>>>(pos, ptr, N, B, r2, max_nn, loop, rule, spos, cellparam,
@@ -2041,7 +2045,7 @@ int mlcgb_pair_index(const int32_t *sel, const int32_t *twin, int64_t P, int32_t
 namespace mlcgb {
 constexpr int64_t kStaticMaxPoints = 65536;
 constexpr int64_t kStaticMaxStructures = 8192;
-constexpr size_t kStaticScratchBytes = (size_t)17 << 19;  // 8.5 MB >= ws_layout(65536, 8192, float32).total = 8 717 312 (float64: 6 620 160)
+constexpr size_t kStaticScratchBytes = (size_t)17 << 19;  // 8.5 MB >= ws_layout(65536, 8192, float32).total = 8 782 848 (float64: 6 685 696)
 static __device__ __align__(256) unsigned char g_radius_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
