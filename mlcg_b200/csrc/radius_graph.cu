@@ -8,7 +8,7 @@
 //        where the structure has points enough, counting sort of the points by cell, all counters in
 //        shared memory; the size of the blocks of cells the block kernels work on)
 //     -> neighbours_block_count for structures of up to 8192 points with a cell grid: a warp takes a
-//        block of cells of one layer (about 21 centres), stages every point within reach of the block
+//        block of cells of one layer (about 24 centres), stages every point within reach of the block
 //        in shared memory once, in ascending order of index, and each lane tests its centre against
 //        the whole staged list; the hits, a bit per staged candidate, stay in the workspace;
 //        neighbours<COUNT> for the rest (one warp per centre over the rows of cells within reach, each
