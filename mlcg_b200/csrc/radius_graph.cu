@@ -661,6 +661,28 @@ __device__ __forceinline__ int centre_at(int q, const ItemRuns &r, int rows) {
     return kc;
 }
 
+// Exclusive prefix, over the warp's lanes, of the lengths of an item's candidate runs (two per lane): where this lane's first
+// run starts in the concatenated list; returns the length of the whole list.
+__device__ __forceinline__ int run_offsets(const ItemRuns &r, int lane, int &excl) {
+    int incl = r.len[0] + r.len[1];
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, s);
+        if (lane >= s) incl += t;
+    }
+    excl = incl - r.len[0] - r.len[1];
+    return __shfl_sync(0xffffffffu, incl, 31);
+}
+// Where candidates [0, cap) of the concatenated list come from (positions in the structure's cell-sorted points): every lane
+// writes out its own two runs.
+__device__ __forceinline__ void write_sources(unsigned short *src, const ItemRuns &r, int excl, int cap) {
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int off = excl + (h ? r.len[0] : 0), kb = min(r.len[h], cap - off);
+        for (int k = 0; k < kb; k++) src[off + k] = (unsigned short)(r.k0[h] + k);
+    }
+}
+
 template <typename T> struct HitWords { static constexpr int value = BlockCap<T>::value / 32; };
 static_assert(HitWords<float>::value == kHitWordsF32 && HitWords<double>::value == kHitWordsF64, "the workspace is sized with these");
 
@@ -699,6 +721,30 @@ __device__ __forceinline__ void rank_marks(const unsigned *mask, unsigned short 
         if (w < nwords) pref[w] = (unsigned short)run;
         run += cnt[q];
     }
+}
+
+// The local indices of the M candidates src[] names -> sj[f] (asynchronous copies, all in flight together), a mark per index
+// in mask[], and pref[w] = marks before word w: the rank of a candidate among the item's candidates, in ascending order of
+// index, is pref[j >> 5] + the marks below bit j & 31 of word j >> 5.  One warp; the loops are not unrolled (the
+// instruction cache is small).
+__device__ __forceinline__ void mark_and_rank(const int32_t *__restrict__ ci, const unsigned short *src, int M, int *sj, unsigned *mask,
+                                              unsigned short *pref, int nwords, int lane) {
+    for (int w = lane; w < nwords; w += 32) mask[w] = 0u;
+    const uint32_t sj0 = (uint32_t)__cvta_generic_to_shared(sj);
+#pragma unroll 4
+    for (int f = lane; f < M; f += 32)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sj0 + 4u * (uint32_t)f), "l"(ci + src[f]) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+#pragma unroll 4
+    for (int f = lane; f < M; f += 32) {
+        const int j = sj[f];
+        atomicOr(&mask[j >> 5], 1u << (j & 31));
+    }
+    __syncwarp();
+    rank_marks(mask, pref, nwords, lane);
+    __syncwarp();
 }
 
 // COUNT.  An item whose candidates fit one stage (the rule) is staged in ascending order of the candidates' indices, as FILL
@@ -748,22 +794,13 @@ neighbours_block_count_kernel(const int64_t *__restrict__ ptr, int64_t B, T r2, 
         const V4<T> pc0 = sp[max(kc0, 0)];
 
         // ---- the candidate runs: exclusive prefix of their lengths; every lane writes out where its two runs come from
-        int incl = rn.len[0] + rn.len[1];
-#pragma unroll
-        for (int s = 1; s < 32; s <<= 1) {
-            const int t = __shfl_up_sync(full, incl, s);
-            if (lane >= s) incl += t;
-        }
-        const int excl = incl - rn.len[0] - rn.len[1], M = __shfl_sync(full, incl, 31);
+        int excl;
+        const int M = run_offsets(rn, lane, excl);
         if (nc > 0) {
             if (2 * lane < o.nrows) { s_k0[2 * lane] = rn.k0[0]; s_off[2 * lane] = excl; }
             if (2 * lane + 1 < o.nrows) { s_k0[2 * lane + 1] = rn.k0[1]; s_off[2 * lane + 1] = excl + rn.len[0]; }
             if (lane == 0) s_off[o.nrows] = M;
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int off = excl + (h ? rn.len[0] : 0), kb = min(rn.len[h], kCap - off);
-                for (int k = 0; k < kb; k++) src[off + k] = (unsigned short)(rn.k0[h] + k);
-            }
+            write_sources(src, rn, excl, kCap);
         }
         __syncwarp();
         const bool single = M <= kCap;
@@ -808,28 +845,9 @@ neighbours_block_count_kernel(const int64_t *__restrict__ ptr, int64_t B, T r2, 
         auto rank_of = [&](int j) { return (int)pref[j >> 5] + __popc(mask[j >> 5] & ((1u << (j & 31)) - 1u)); };
         if (nc > 0 && single) {
             // ---- in ascending order of index: mark the indices, rank the marks, sources by rank, copy
-            const int nwords = (q.n + 31) >> 5;                  // (n <= kCapBits)
-            for (int w = lane; w < nwords; w += 32) mask[w] = 0u;
-            __syncwarp();
-            // the candidates' indices, by asynchronous copies (all in flight together) into the stage, which is still empty;
-            // the loops are not unrolled: the instruction cache is small
-            const int32_t *ci = cidx + q.lo;
+            // the candidates' indices go through the stage, which is still empty
             int *sj = reinterpret_cast<int *>(cand);
-            const uint32_t sj0 = (uint32_t)__cvta_generic_to_shared(sj);
-#pragma unroll 4
-            for (int f = lane; f < M; f += 32)
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sj0 + 4u * (uint32_t)f), "l"(ci + src[f]) : "memory");
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            __syncwarp();
-#pragma unroll 4
-            for (int f = lane; f < M; f += 32) {
-                const int j = sj[f];
-                atomicOr(&mask[j >> 5], 1u << (j & 31));
-            }
-            __syncwarp();
-            rank_marks(mask, pref, nwords, lane);
-            __syncwarp();
+            mark_and_rank(cidx + q.lo, src, M, sj, mask, pref, (q.n + 31) >> 5, lane);      // (n <= kCapBits)
 #pragma unroll 1
             for (int f0 = lane; f0 < M; f0 += 256) {
                 // (eight ranks first, then their stores: a load of shared memory cannot be moved above an earlier store)
@@ -1027,14 +1045,8 @@ neighbours_block_fill_kernel(const T *__restrict__ pos, const int64_t *__restric
         const V4<T> pc0 = sp[max(kc0, 0)];
         int M;
         {   // the candidate runs: exclusive prefix of the lengths; warp w writes out where run 2 lane + w comes from
-            int incl = rn.len[0] + rn.len[1];
-#pragma unroll
-            for (int s = 1; s < 32; s <<= 1) {
-                const int t = __shfl_up_sync(full, incl, s);
-                if (lane >= s) incl += t;
-            }
-            const int excl = incl - rn.len[0] - rn.len[1];
-            M = __shfl_sync(full, incl, 31);
+            int excl;
+            M = run_offsets(rn, lane, excl);
             // (an item that fits one stage left its hit masks: the expanding kernel's.  Before anything of it is written to
             //  shared memory: the warps meet only in the items this kernel takes.  The same in every warp.)
             if (M <= kCap) continue;
@@ -1336,43 +1348,15 @@ neighbours_block_expand_kernel(const T *__restrict__ pos, const int64_t *__restr
         const int nc = warp_sum(rn.run_len);
         const int kc0 = centre_at(lane, rn, rows);
         const V4<T> pc0 = sp[max(kc0, 0)];                  // the first 32 centres' points: on their way during the staging
-        int incl = rn.len[0] + rn.len[1];
-#pragma unroll
-        for (int s = 1; s < 32; s <<= 1) {
-            const int t = __shfl_up_sync(full, incl, s);
-            if (lane >= s) incl += t;
-        }
-        const int excl = incl - rn.len[0] - rn.len[1], M = __shfl_sync(full, incl, 31);
+        int excl;
+        const int M = run_offsets(rn, lane, excl);
         RPHASE(1)
         const bool mine = nc > 0 && M <= kCap;              // (items with more candidates have no masks: the testing kernel fills them)
         if (mine) {
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int off = excl + (h ? rn.len[0] : 0), kb = min(rn.len[h], kCap - off);
-                for (int k = 0; k < kb; k++) src[off + k] = (unsigned short)(rn.k0[h] + k);
-            }
-            const int nwords = (q.n + 31) >> 5;
-            for (int w = lane; w < nwords; w += 32) mask[w] = 0u;
-            __syncwarp();
-            // the candidates' indices, by asynchronous copies (all in flight together) into the space of the lists, empty now;
-            // the loops are not unrolled: the instruction cache is small
-            const int32_t *ci = cidx + lo;
+            write_sources(src, rn, excl, kCap);
+            // the candidates' indices go through the space of the lists, empty now
             int *sj = reinterpret_cast<int *>(all_lists);
-            const uint32_t sj0 = (uint32_t)__cvta_generic_to_shared(sj);
-#pragma unroll 4
-            for (int f = lane; f < M; f += 32)
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sj0 + 4u * (uint32_t)f), "l"(ci + src[f]) : "memory");
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            __syncwarp();
-#pragma unroll 4
-            for (int f = lane; f < M; f += 32) {
-                const int j = sj[f];
-                atomicOr(&mask[j >> 5], 1u << (j & 31));
-            }
-            __syncwarp();
-            rank_marks(mask, pref, nwords, lane);
-            __syncwarp();
+            mark_and_rank(cidx + lo, src, M, sj, mask, pref, (q.n + 31) >> 5, lane);
 #pragma unroll 1
             for (int f0 = lane; f0 < M; f0 += 256) {
                 // (eight ranks first, then their stores: a load of shared memory cannot be moved above an earlier store)
