@@ -47,3 +47,14 @@ def test_workspace_size_queries_are_host_only():
     assert 0 < small < big
     assert lib.mlcgb_gemm_workspace_bytes(0, 1000, 128, 128, 0) == 0
     assert lib.mlcgb_gemm_workspace_bytes(2, 128, 128, 1000000, 0) > 0
+
+
+def test_radius_workspace_fits_the_built_in_scratch_at_its_limits():
+    """`mlcgb_radius_graph_static` owns 17 x 512 KiB of scratch and accepts up to 65 536 points in 8 192 structures: the
+    workspace of the two-call interface at those sizes must fit in both precisions, and grow with the points (the hit masks)."""
+    lib = _lib.load()
+    scratch = 17 << 19
+    f32, f64 = lib.mlcgb_radius_workspace_bytes(65536, 8192, 0), lib.mlcgb_radius_workspace_bytes(65536, 8192, 1)
+    assert 0 < f64 <= scratch and 0 < f32 <= scratch
+    per_point = (lib.mlcgb_radius_workspace_bytes(200000, 10, 0) - lib.mlcgb_radius_workspace_bytes(100000, 10, 0)) / 100000
+    assert 100 <= per_point <= 160            # points, cell tables, indices, 24 mask words, a flag
