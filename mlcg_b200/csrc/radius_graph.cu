@@ -567,7 +567,7 @@ __global__ void __launch_bounds__(kScanBlock) group_scan_kernel(const CellParam 
 // than a list holds in several emissions.
 template <typename T> struct BlockCap { static constexpr int value = 768; };
 template <> struct BlockCap<double> { static constexpr int value = 384; };
-constexpr int kItemRun = 8;                               // consecutive work items a block takes at a time
+constexpr int kItemRun = 2;                               // consecutive work items a block takes at a time
 
 template <typename T> __device__ __forceinline__ V4<T> far_point();
 template <> __device__ __forceinline__ float4 far_point<float>() { return make_float4(INFINITY, INFINITY, INFINITY, 0.f); }
