@@ -553,18 +553,19 @@ __global__ void __launch_bounds__(kScanBlock) group_scan_kernel(const CellParam 
 // ------------------------------------------------------------------------------------ block kernels
 // One work item = the centres in a block of bx x by cells of one layer (z) of one structure, about kBlkTargetCentres of
 // them, taken by ONE WARP (a block of 32 threads: the warps share nothing and never meet): a lane per centre.  Their
-// candidates are the cells within `reach` of the block: (by + 2 reach) x (2 reach + 1) runs of the cell-sorted points.  The
-// warp stages them in shared memory and every lane tests its centre against the whole staged list: the list is read with
-// broadcast loads, the loop is the same for all lanes, and a test is nine instructions (load, six for the squared distance
-// as the reference rounds it, compare, count).
-//   COUNT stages the candidates as they come (asynchronous copies, all in flight together).
-//   FILL stages them in ascending order of their local index: the warp marks the indices in a bitmask over the structure
-//   (at most kCapBits points), a prefix sum of the mask's population counts gives every candidate its rank, and the
-//   candidate is written to that position.  A lane appends the index of every hit to its centre's list in shared memory,
-//   which is then in the order the edges are listed in: no per-centre sort or mask.  The warp goes through the lists and
-//   writes the edges with consecutive lanes on consecutive slots.
-// More candidates than the stage holds are taken in windows (of ranks, in FILL), more than 32 centres in passes, more hits
-// than a list holds in several emissions.
+// candidates are the cells within `reach` of the block: (by + 2 reach) x (2 reach + 1) runs of the cell-sorted points.
+//   COUNT stages them in shared memory in ascending order of their local index: the warp marks the indices in a bitmask
+//   over the structure (at most kCapBits points), a prefix sum of the mask's population counts gives every candidate its
+//   rank, and the candidate is copied to that position.  Every lane then tests its centre against the whole staged list:
+//   the list is read with broadcast loads, the loop is the same for all lanes, and a test is nine instructions (load, six
+//   for the squared distance as the reference rounds it, compare, bit).  The hits, a bit per staged candidate, go to the
+//   workspace; they are in the order the edges are listed in.
+//   EXPAND (after the scan of the degrees) puts the item's indices in the same order, turns every centre's words into a
+//   list of neighbours and writes the edges, consecutive lanes on consecutive slots: no second distance test, no
+//   per-centre sort.
+//   FILL takes the items with more candidates than the stage holds: those leave no masks, are counted in windows as the
+//   candidates come, and are tested again, in windows of ranks, by two warps per item.
+// More than 32 centres are taken in passes, more neighbours than a list holds in several rounds.
 template <typename T> struct BlockCap { static constexpr int value = 768; };
 template <> struct BlockCap<double> { static constexpr int value = 384; };
 constexpr int kItemRun = 2;                               // consecutive work items a block takes at a time
